@@ -1,0 +1,333 @@
+// extern "C" surface of include/kge_b200.h: argument marshalling and error mapping for the
+// engine, and the single-operator entry points.
+#include <cstring>
+#include <vector>
+
+#include "engine.hpp"
+
+using namespace kge;
+
+struct kge_engine {
+    std::unique_ptr<Engine> impl;
+    std::string last_error;
+};
+
+namespace {
+
+thread_local std::string g_error;  // last failure of kge_create or of an operator entry point
+
+template <class Fn>
+int guarded(std::string& error_slot, Fn&& fn) {
+    try {
+        fn();
+        return KGE_OK;
+    } catch (const Error& e) {
+        error_slot = e.message;
+        return e.code;
+    } catch (const std::invalid_argument& e) {
+        error_slot = e.what();
+        return KGE_INVALID_ARGUMENT;
+    } catch (const std::logic_error& e) {
+        error_slot = e.what();
+        return KGE_LOGIC_ERROR;
+    } catch (const std::exception& e) {
+        error_slot = e.what();
+        return KGE_RUNTIME_ERROR;
+    }
+}
+
+std::vector<HostArray> to_host_arrays(const kge_array* arrays, size_t n) {
+    std::vector<HostArray> out;
+    out.reserve(n);
+    for (size_t i = 0; i < n; ++i) {
+        const kge_array& a = arrays[i];
+        if (!a.name) fail(KGE_INVALID_ARGUMENT, "array without a name");
+        if (a.dtype != KGE_F32 && a.dtype != KGE_U32 && a.dtype != KGE_F16)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'" << a.name << "' has an unknown element type " << a.dtype);
+        if (a.rank < 0 || a.rank > 8 || (a.rank && !a.shape))
+            fail(KGE_INVALID_ARGUMENT, msg() << "'" << a.name << "' has a bad rank or no shape");
+        out.push_back({a.name, a.dtype, std::vector<size_t>(a.shape, a.shape + a.rank), a.data});
+    }
+    return out;
+}
+
+// Temporary device buffers for the operator entry points.
+struct DeviceBuffer {
+    void* p = nullptr;
+    explicit DeviceBuffer(size_t bytes) { KGE_CUDA(cudaMalloc(&p, bytes ? bytes : 16)); }
+    ~DeviceBuffer() { cudaFree(p); }
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    template <class T>
+    T* as() { return static_cast<T*>(p); }
+};
+void to_device(DeviceBuffer& dst, const void* src, size_t bytes) {
+    if (bytes) KGE_CUDA(cudaMemcpy(dst.p, src, bytes, cudaMemcpyHostToDevice));
+}
+void to_host(void* dst, DeviceBuffer& src, size_t bytes) {
+    if (bytes) KGE_CUDA(cudaMemcpy(dst, src.p, bytes, cudaMemcpyDeviceToHost));
+}
+void finish_kernels() {
+    KGE_CUDA(cudaGetLastError());
+    KGE_CUDA(cudaDeviceSynchronize());
+}
+unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per - 1) / per); }
+void require(bool ok, const char* what) {
+    if (!ok) fail(KGE_INVALID_ARGUMENT, what);
+}
+
+
+}  // namespace
+
+extern "C" {
+
+int kge_create(const kge_setting* settings, size_t n_settings, const char*, kge_engine** out) {
+    return guarded(g_error, [&] {
+        if (!out) fail(KGE_INVALID_ARGUMENT, "kge_create: out is null");
+        *out = nullptr;
+        SettingMap map;
+        for (size_t i = 0; i < n_settings; ++i) {
+            const kge_setting& s = settings[i];
+            if (!s.key) fail(KGE_INVALID_ARGUMENT, "setting without a key");
+            if (s.type < KGE_SET_STRING || s.type > KGE_SET_UNSIGNED)
+                fail(KGE_INVALID_ARGUMENT, msg() << "Key '" << s.key << "' holds value of unexpected type.");
+            map[s.key] = SettingValue{s.type, s.s ? s.s : "", s.f, s.u};
+        }
+        auto engine = std::make_unique<kge_engine>();
+        engine->impl = std::make_unique<Engine>(map);
+        *out = engine.release();
+    });
+}
+
+void kge_destroy(kge_engine* engine) { delete engine; }
+
+const char* kge_last_error(const kge_engine* engine) {
+    return engine ? engine->last_error.c_str() : g_error.c_str();
+}
+
+int kge_run(kge_engine* engine, const char* command, const kge_array* arrays, size_t n_arrays,
+            const char* variable_name) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] {
+        if (!command) fail(KGE_INVALID_ARGUMENT, "kge_run: command is null");
+        auto host = to_host_arrays(arrays, n_arrays);
+        const std::string cmd = command;
+        if ((cmd == "read" || cmd == "write") && !variable_name) fail(KGE_INVALID_ARGUMENT, "Key not found 'name'");
+        engine->impl->run(cmd, host, variable_name ? variable_name : "");
+    });
+}
+
+int kge_variable_count(kge_engine* engine, size_t* count) {
+    if (!engine || !count) return KGE_INVALID_ARGUMENT;
+    *count = engine->impl->variables().size();
+    return KGE_OK;
+}
+
+int kge_variable_info(kge_engine* engine, size_t index, const char** name, int* dtype, int* rank, size_t* shape) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] {
+        const auto& vars = engine->impl->variables();
+        if (index >= vars.size()) fail(KGE_INVALID_ARGUMENT, "kge_variable_info: index past the end");
+        const Variable& v = vars[index];
+        if (name) *name = v.name.c_str();
+        if (dtype) *dtype = v.dtype;
+        if (rank) *rank = (int)v.shape.size();
+        if (shape)
+            for (size_t i = 0; i < v.shape.size() && i < 4; ++i) shape[i] = v.shape[i];
+    });
+}
+
+size_t kge_comm_handle_bytes(void) { return Engine::comm_handle_bytes(); }
+
+int kge_comm_export(kge_engine* engine, void* handle_out) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] {
+        if (!handle_out) fail(KGE_INVALID_ARGUMENT, "kge_comm_export: handle_out is null");
+        engine->impl->comm_export(handle_out);
+    });
+}
+
+int kge_comm_connect(kge_engine* engine, const void* all_handles, size_t world_size) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] {
+        if (!all_handles) fail(KGE_INVALID_ARGUMENT, "kge_comm_connect: all_handles is null");
+        engine->impl->comm_connect(all_handles, world_size);
+    });
+}
+
+int kge_stage_batch(kge_engine* engine, const kge_array* arrays, size_t n_arrays) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] {
+        auto host = to_host_arrays(arrays, n_arrays);
+        engine->impl->stage_batch(host);
+    });
+}
+
+int kge_train_staged(kge_engine* engine, float learning_rate, float* loss) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] { engine->impl->train_staged(learning_rate, loss); });
+}
+
+int kge_last_run_stats(kge_engine* engine, float* device_ms, unsigned long long* kernel_launches) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    engine->impl->last_run_stats(device_ms, kernel_launches);
+    return KGE_OK;
+}
+
+int kge_debug_fetch(kge_engine* engine, const char* what, size_t shard, float* out, size_t capacity, size_t* count) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] {
+        if (!what || !out) fail(KGE_INVALID_ARGUMENT, "kge_debug_fetch: null argument");
+        const size_t n = engine->impl->debug_fetch(what, shard, out, capacity);
+        if (count) *count = n;
+    });
+}
+
+// ---------------------------------------------------------------------------
+// Single operators on host buffers.
+
+int kge_op_pairwise(int fn, const float* a, const float* b, size_t m, size_t n, size_t k, float* out) {
+    return guarded(g_error, [&] {
+        require(fn >= DIST_L1 && fn <= DIST_DOT, "kge_op_pairwise: fn must be 0 (L1), 1 (L2) or 2 (dot)");
+        require(a && b && out, "kge_op_pairwise: null argument");
+        if (m == 0 || n == 0) return;
+        DeviceBuffer da(m * k * 4), db(n * k * 4), dout(m * n * 4);
+        to_device(da, a, m * k * 4);
+        to_device(db, b, n * k * 4);
+        dim3 grid(blocks_for(n, 64), blocks_for(m, 32));
+        const int M = (int)m, N = (int)n, K = (int)k;
+        if (fn == DIST_L1) k_score<DIST_L1><<<grid, 128>>>(da.as<float>(), db.as<float>(), dout.as<float>(), M, N, K);
+        else if (fn == DIST_L2) k_score<DIST_L2><<<grid, 128>>>(da.as<float>(), db.as<float>(), dout.as<float>(), M, N, K);
+        else k_score<DIST_DOT><<<grid, 128>>>(da.as<float>(), db.as<float>(), dout.as<float>(), M, N, K);
+        finish_kernels();
+        to_host(out, dout, m * n * 4);
+    });
+}
+
+int kge_op_pairwise_grad(int fn, const float* a, const float* b, const float* grad_out, size_t m, size_t n,
+                         size_t k, float* grad_a, float* grad_b) {
+    return guarded(g_error, [&] {
+        require(fn >= DIST_L1 && fn <= DIST_DOT, "kge_op_pairwise_grad: fn must be 0 (L1), 1 (L2) or 2 (dot)");
+        require(a && b && grad_out && grad_a && grad_b, "kge_op_pairwise_grad: null argument");
+        if (m == 0 || n == 0 || k == 0) return;
+        DeviceBuffer da(m * k * 4), db(n * k * 4), dg(m * n * 4), dga(m * k * 4), dgb(n * k * 4);
+        to_device(da, a, m * k * 4);
+        to_device(db, b, n * k * 4);
+        std::vector<float> coeff(grad_out, grad_out + m * n);
+        if (fn == DIST_L2) {
+            // The L2 backward divides by the forward distance, and is zero where that is zero
+            // (src/poplar_extensions/l2distance.codelet.cpp:149-158): take the distance from
+            // the forward kernel, then fold the division into the coefficient.
+            DeviceBuffer ddist(m * n * 4);
+            dim3 grid(blocks_for(n, 64), blocks_for(m, 32));
+            k_score<DIST_L2><<<grid, 128>>>(da.as<float>(), db.as<float>(), ddist.as<float>(), (int)m, (int)n, (int)k);
+            finish_kernels();
+            std::vector<float> dist(m * n);
+            to_host(dist.data(), ddist, m * n * 4);
+            for (size_t i = 0; i < m * n; ++i) coeff[i] = dist[i] == 0.f ? 0.f : coeff[i] / dist[i];
+        }
+        to_device(dg, coeff.data(), m * n * 4);
+        PairBwdArgs pa{};
+        pa.D = (int)k;
+        pa.tiles_m0 = (int)blocks_for(m, 32);
+        pa.p[0] = {da.as<float>(), db.as<float>(), dg.as<float>(), (int)m, (int)n, (int)n, 1, dga.as<float>(), nullptr, 1};
+        pa.p[1] = {db.as<float>(), da.as<float>(), dg.as<float>(), (int)n, (int)m, 1, (int)n, dgb.as<float>(), nullptr, 1};
+        dim3 grid(blocks_for(m, 32) + blocks_for(n, 32), blocks_for(k, 64));
+        if (fn == DIST_L1) k_pair_bwd<DIST_L1><<<grid, 128>>>(pa);
+        else if (fn == DIST_L2) k_pair_bwd<DIST_L2><<<grid, 128>>>(pa);
+        else k_pair_bwd<DIST_DOT><<<grid, 128>>>(pa);
+        finish_kernels();
+        to_host(grad_a, dga, m * k * 4);
+        to_host(grad_b, dgb, n * k * 4);
+    });
+}
+
+int kge_op_gather_rows(const float* table, size_t rows, size_t width, const uint32_t* indices, size_t n, float* out) {
+    return guarded(g_error, [&] {
+        require(table && indices && out, "kge_op_gather_rows: null argument");
+        for (size_t i = 0; i < n; ++i)
+            if (indices[i] >= rows) fail(KGE_INVALID_ARGUMENT, msg() << "kge_op_gather_rows: index " << indices[i] << " is not below " << rows);
+        if (n == 0 || width == 0) return;
+        DeviceBuffer dt(rows * width * 4), di(n * 4), dout(n * width * 4);
+        to_device(dt, table, rows * width * 4);
+        to_device(di, indices, n * 4);
+        if (width % 4 == 0) k_gather_rows<4><<<(unsigned)n, 128>>>(dt.as<float>(), width, di.as<uint32_t>(), dout.as<float>());
+        else k_gather_rows<1><<<(unsigned)n, 128>>>(dt.as<float>(), width, di.as<uint32_t>(), dout.as<float>());
+        finish_kernels();
+        to_host(out, dout, n * width * 4);
+    });
+}
+
+int kge_op_scatter_add_rows(const float* grad_rows, const uint32_t* indices, size_t n, size_t rows, size_t width,
+                            float* grad_table) {
+    return guarded(g_error, [&] {
+        require(grad_rows && indices && grad_table, "kge_op_scatter_add_rows: null argument");
+        require(n <= (size_t)kMaxSortItems, "kge_op_scatter_add_rows: more rows than one sort block holds");
+        for (size_t i = 0; i < n; ++i)
+            if (indices[i] >= rows) fail(KGE_INVALID_ARGUMENT, msg() << "kge_op_scatter_add_rows: index " << indices[i] << " is not below " << rows);
+        if (rows == 0 || width == 0) return;
+        DeviceBuffer dg(n * width * 4), di(n * 4), dperm(n * 4), doff((rows + 1) * 4), dout(rows * width * 4);
+        DeviceBuffer unused_perm(n * 4), unused_off(16);
+        to_device(dg, grad_rows, n * width * 4);
+        to_device(di, indices, n * 4);
+        // All n lookups are passed as "head" lookups; there are no tail lookups, and the
+        // relation part (fed the same indices, with zero relation types) is not used.
+        k_prepare_segments<<<1, 512>>>(di.as<uint32_t>(), di.as<uint32_t>(), di.as<uint32_t>(), nullptr, (int)n, 0,
+                                       (int)rows, 0, dperm.as<uint32_t>(), doff.as<uint32_t>(),
+                                       unused_perm.as<uint32_t>(), unused_off.as<uint32_t>(), nullptr);
+        k_segment_sum_rows<<<(unsigned)rows, 128>>>(dg.as<float>(), dperm.as<uint32_t>(), doff.as<uint32_t>(), width,
+                                                    dout.as<float>());
+        finish_kernels();
+        to_host(grad_table, dout, rows * width * 4);
+    });
+}
+
+int kge_op_activation(int kind, const float* x, const float* grad_out, size_t rows, size_t cols, float* y, float* grad_x) {
+    return guarded(g_error, [&] {
+        require(kind == 0 || kind == 1, "kge_op_activation: kind must be 0 (log-sigmoid) or 1 (log-softmax)");
+        require(x && grad_out && y && grad_x, "kge_op_activation: null argument");
+        const size_t n = rows * cols;
+        if (n == 0) return;
+        DeviceBuffer dx(n * 4), dg(n * 4), dy(n * 4), dgx(n * 4);
+        to_device(dx, x, n * 4);
+        to_device(dg, grad_out, n * 4);
+        if (kind == 0)
+            k_log_sigmoid<<<std::min(blocks_for(n, 256), 1184u), 256>>>(dx.as<float>(), dg.as<float>(), n, dy.as<float>(), dgx.as<float>());
+        else
+            k_log_softmax<<<(unsigned)rows, 256>>>(dx.as<float>(), dg.as<float>(), (int)cols, dy.as<float>(), dgx.as<float>());
+        finish_kernels();
+        to_host(y, dy, n * 4);
+        to_host(grad_x, dgx, n * 4);
+    });
+}
+
+int kge_op_all_to_all(const float* in, size_t n_shard, size_t block, float* out) {
+    return guarded(g_error, [&] {
+        require(in && out, "kge_op_all_to_all: null argument");
+        const size_t total = n_shard * n_shard * block;
+        if (total == 0) return;
+        // Each emulated shard s holds `in[s]` = n_shard blocks and sends block d into slot s of
+        // shard d's receive buffer, with the same routing kernel the training step uses: the
+        // hidden table is in[s] viewed as rows of `block` floats, the lookup is the identity.
+        DeviceBuffer din(total * 4), dout(total * 4), didx(n_shard * 4), dtable(n_shard * sizeof(float*));
+        to_device(din, in, total * 4);
+        std::vector<uint32_t> identity(n_shard);
+        for (size_t i = 0; i < n_shard; ++i) identity[i] = (uint32_t)i;
+        to_device(didx, identity.data(), n_shard * 4);
+        for (size_t s = 0; s < n_shard; ++s) {
+            std::vector<float*> dst(n_shard);
+            for (size_t d = 0; d < n_shard; ++d) dst[d] = dout.as<float>() + (d * n_shard + s) * block;
+            to_device(dtable, dst.data(), n_shard * sizeof(float*));
+            const float* rows = din.as<float>() + s * n_shard * block;
+            if (block % 4 == 0)
+                k_route<4><<<(unsigned)n_shard, 64>>>(rows, rows, didx.as<uint32_t>(), nullptr, nullptr, nullptr,
+                                                      dtable.as<float*>(), nullptr, (int)n_shard, 1, 0, (int)block, SCORE_TRANSE);
+            else
+                k_route<1><<<(unsigned)n_shard, 64>>>(rows, rows, didx.as<uint32_t>(), nullptr, nullptr, nullptr,
+                                                      dtable.as<float*>(), nullptr, (int)n_shard, 1, 0, (int)block, SCORE_TRANSE);
+            finish_kernels();
+        }
+        to_host(out, dout, total * 4);
+    });
+}
+
+}  // extern "C"

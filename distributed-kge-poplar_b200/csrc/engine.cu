@@ -1,0 +1,938 @@
+// Host engine implementation.  See engine.hpp.
+#include "engine.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace kge {
+
+// ---------------------------------------------------------------------------
+// Settings (src/poplar_kge.cpp:39-67 for the error texts, :198-246 for the keys)
+
+namespace {
+
+const char* type_name(int type) {
+    switch (type) {
+        case KGE_SET_STRING: return "string";
+        case KGE_SET_BOOL: return "bool";
+        case KGE_SET_FLOAT: return "float";
+        case KGE_SET_UNSIGNED: return "unsigned";
+    }
+    return "?";
+}
+
+const SettingValue& lookup(const SettingMap& s, const std::string& key, int type) {
+    auto it = s.find(key);
+    if (it == s.end()) fail(KGE_INVALID_ARGUMENT, msg() << "Key not found '" << key << "'");
+    if (it->second.type != type) {
+        fail(KGE_INVALID_ARGUMENT, msg() << "Key '" << key
+                                         << "' holds value of unexpected type. Expected: '"
+                                         << type_name(type) << "', actual: '"
+                                         << type_name(it->second.type) << "'.");
+    }
+    return it->second;
+}
+std::string get_string(const SettingMap& s, const std::string& k) { return lookup(s, k, KGE_SET_STRING).s; }
+unsigned get_unsigned(const SettingMap& s, const std::string& k) {
+    return (unsigned)lookup(s, k, KGE_SET_UNSIGNED).u;
+}
+float get_float(const SettingMap& s, const std::string& k) { return (float)lookup(s, k, KGE_SET_FLOAT).f; }
+bool get_bool(const SettingMap& s, const std::string& k) { return lookup(s, k, KGE_SET_BOOL).u != 0; }
+
+template <class T, class Getter>
+T get_or(const SettingMap& s, const std::string& k, Getter getter, T fallback) {
+    return s.count(k) ? getter(s, k) : fallback;
+}
+
+int parse_storage(const std::string& key, const std::string& value) {
+    if (value == "float32") return ST_F32;
+    if (value == "float16") return ST_F16;
+    fail(KGE_INVALID_ARGUMENT, msg() << "'" << key << "' must either be 'float16' or 'float32', not '"
+                                     << value << "'");
+}
+
+void reject_regulariser(const SettingMap& s, const std::string& prefix) {
+    get_float(s, prefix + ".power");
+    if (get_float(s, prefix + ".weight") > 0.f) {
+        fail(KGE_INVALID_ARGUMENT, msg() << "'" << prefix << ".weight' > 0 is not supported by this engine");
+    }
+}
+
+}  // namespace
+
+Config parse_config(const SettingMap& s) {
+    Config c{};
+    c.n_shard = get_unsigned(s, "model.n_shard");
+    const std::string device = get_string(s, "execution.device");
+    if (device != "cpu" && device != "ipu" && device != "ipu_model" && device != "cuda") {
+        fail(KGE_INVALID_ARGUMENT, msg() << "Unexpected setting \"device\": '" << device
+                                         << "', expected \"cuda\" (or the reference's \"cpu\" / \"ipu\")");
+    }
+    c.seed = get_unsigned(s, "model.seed");
+    const std::string score_fn = get_string(s, "model.score_fn");
+    const std::string distance_fn = get_string(s, "model.distance_fn");
+    c.n_entity = get_unsigned(s, "model.n_entity");
+    c.n_relation_type = get_unsigned(s, "model.n_relation_type");
+    c.d = get_unsigned(s, "model.embedding_size");
+    c.f = get_unsigned(s, "model.entity_feature_size");
+    const unsigned mlp = get_unsigned(s, "model.feature_mlp_size");
+    const float dropout = get_float(s, "model.feature_dropout");
+    c.share_networks = get_bool(s, "model.share_feature_networks");
+    c.gamma = get_float(s, "model.gamma");
+    c.init_scale = get_float(s, "model.init_scale");
+    c.beta_m = get_float(s, "training.adam_beta_m");
+    c.beta_v = get_float(s, "training.adam_beta_v");
+    c.epsilon = get_float(s, "training.adam_epsilon");
+    c.weight_decay = get_float(s, "training.weight_decay");
+    const std::string mod_prefix = "training.learning_rate_modifiers.";
+    for (auto& kv : s) {
+        if (kv.first.compare(0, mod_prefix.size(), mod_prefix) == 0) {
+            c.lr_modifiers[kv.first.substr(mod_prefix.size())] = get_float(s, kv.first);
+        }
+    }
+    c.batch_size = get_unsigned(s, "data.batch_size");
+    c.a2a_size = get_unsigned(s, "data.a2a_size");
+    c.adversarial_scale = get_float(s, "model.negative_adversarial_scale");
+    const std::string loss = get_string(s, "training.loss.type");
+    reject_regulariser(s, "training.embedding_regularisation");
+    reject_regulariser(s, "training.feature_regularisation");
+    reject_regulariser(s, "training.hidden_regularisation");
+    c.correction_weight = loss == "softmax" ? get_float(s, "training.loss.correction_weight") : 0.f;
+    c.loss_scale = get_float(s, "training.loss_scale");
+    c.n_step = get_unsigned(s, "execution.train_steps_per_program_run");
+    c.rw_batch = get_unsigned(s, "execution.rw_batch_size");
+    c.predict_hr = get_unsigned(s, "execution.predict_hr_batch_size");
+    c.predict_tail_batch = get_unsigned(s, "execution.predict_tail_batch_size");
+    c.predict_n_best = get_unsigned(s, "execution.predict_n_best");
+    c.state_type = parse_storage("execution.dtype", get_string(s, "execution.dtype"));
+    c.feature_type = s.count("execution.feature_dtype")
+                         ? parse_storage("execution.feature_dtype", get_string(s, "execution.feature_dtype"))
+                         : c.state_type;
+    c.device_ordinal = get_or<unsigned>(s, "execution.device_ordinal", get_unsigned, 0u);
+    c.rank = get_or<unsigned>(s, "execution.rank", get_unsigned, 0u);
+    c.world = get_or<unsigned>(s, "execution.world_size", get_unsigned, 1u);
+    c.cuda_graph = get_or<bool>(s, "execution.cuda_graph", get_bool, true);
+
+    if (score_fn == "TransE") c.score_fn = SCORE_TRANSE;
+    else if (score_fn == "DistMult") c.score_fn = SCORE_DISTMULT;
+    else if (score_fn == "ComplEx") c.score_fn = SCORE_COMPLEX;
+    else if (score_fn == "RotatE" || score_fn == "TransH")
+        fail(KGE_INVALID_ARGUMENT, msg() << "'model.score_fn' '" << score_fn << "' is not supported by this engine");
+    else
+        fail(KGE_INVALID_ARGUMENT, msg() << "'model.score_fn' must be one of 'TransE', 'ComplEx', 'RotatE', "
+                                            "'TransH', or 'DistMult', not '" << score_fn << "'");
+    if (distance_fn == "L1" || distance_fn == "L1_old") c.dist_fn = DIST_L1;
+    else if (distance_fn == "L2" || distance_fn == "L2_old") c.dist_fn = DIST_L2;
+    else if (distance_fn == "MatMul") c.dist_fn = DIST_DOT;
+    else
+        fail(KGE_INVALID_ARGUMENT, msg() << "'model.distance_fn' must be one of 'L1', 'L1_old', 'L2', 'L2_old' "
+                                            "or 'MatMul', not '" << distance_fn << "'");
+    if (loss == "logsigmoid") c.loss_fn = LOSS_LOGSIGMOID;
+    else if (loss == "softmax") c.loss_fn = LOSS_SOFTMAX;
+    else
+        fail(KGE_INVALID_ARGUMENT, msg() << "'training.loss.type' must be one of 'logsigmoid' or 'softmax', not '"
+                                         << loss << "'");
+    if (mlp > 0) fail(KGE_INVALID_ARGUMENT, "'model.feature_mlp_size' > 0 is not supported by this engine");
+    if (dropout > 0.f) fail(KGE_INVALID_ARGUMENT, "'model.feature_dropout' > 0 is not supported by this engine");
+    if (c.state_type == ST_F16 && c.feature_type != ST_F16)
+        fail(KGE_INVALID_ARGUMENT, "'execution.feature_dtype' must be 'float16' when 'execution.dtype' is 'float16'");
+
+    // Parameters are sliced by rows over the shards (src/poplar_kge.cpp:294-300).
+    auto divisible = [&](const char* name, unsigned rows, unsigned cols) {
+        if (rows % c.n_shard)
+            fail(KGE_INVALID_ARGUMENT, msg() << "Parameter '" << name << "' shape[0] (" << rows
+                                             << ") is not divisible by n_shard (" << c.n_shard
+                                             << "). Note shape: (" << rows << ", " << cols << ")");
+    };
+    if (c.n_shard == 0 || c.world == 0 || c.n_shard % c.world || c.rank >= c.world)
+        fail(KGE_INVALID_ARGUMENT, msg() << "n_shard (" << c.n_shard << ") must be a positive multiple of "
+                                            "execution.world_size (" << c.world << ") and rank < world_size");
+    divisible("relation_embedding", c.n_relation_type, c.d);
+    if (c.f) divisible(c.share_networks ? "feature_projection" : "head_feature_projection", c.f, c.d);
+    for (auto& kv : c.lr_modifiers) {
+        const bool known = kv.first == "entity_embedding" || kv.first == "relation_embedding" ||
+                           (c.share_networks ? kv.first == "feature_projection"
+                                             : (kv.first == "head_feature_projection" ||
+                                                kv.first == "tail_feature_projection"));
+        if (!known)
+            fail(KGE_INVALID_ARGUMENT, msg() << "Bad training.learning_rate_modifier: unknown parameter '"
+                                             << kv.first << "'");
+    }
+    if (c.d == 0 || c.batch_size == 0 || c.a2a_size == 0 || c.n_step == 0 || c.n_entity == 0)
+        fail(KGE_INVALID_ARGUMENT, "embedding_size, batch_size, a2a_size, n_entity and "
+                                   "train_steps_per_program_run must be positive");
+    if (c.score_fn == SCORE_COMPLEX && (c.d & 1))
+        fail(KGE_INVALID_ARGUMENT, "ComplEx needs an even 'model.embedding_size'");
+    if (c.n_tail() < 2) fail(KGE_INVALID_ARGUMENT, "n_shard * a2a_size must be at least 2");
+    if ((size_t)c.batch_size + c.n_tail() > (size_t)kMaxSortItems)
+        fail(KGE_INVALID_ARGUMENT, msg() << "batch_size + n_shard * a2a_size (" << c.n_remote()
+                                         << ") exceeds this engine's limit of " << kMaxSortItems);
+    return c;
+}
+
+// ---------------------------------------------------------------------------
+// Dispatch over the row storage types.
+
+#define KGE_DISPATCH_ROW(cfg, ...)                                          \
+    do {                                                                     \
+        if ((cfg).state_type == ST_F32 && (cfg).feature_type == ST_F32) {    \
+            using ST = float; using FT = float; __VA_ARGS__;                 \
+        } else if ((cfg).state_type == ST_F32) {                             \
+            using ST = float; using FT = __half; __VA_ARGS__;                \
+        } else {                                                             \
+            using ST = __half; using FT = __half; __VA_ARGS__;               \
+        }                                                                    \
+    } while (0)
+
+namespace {
+size_t type_bytes(int storage) { return storage == ST_F32 ? 4 : 2; }
+unsigned ceil_div(unsigned a, unsigned b) { return (a + b - 1) / b; }
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Construction
+
+void* Engine::device_alloc(size_t bytes) {
+    void* p = nullptr;
+    KGE_CUDA(cudaMalloc(&p, std::max<size_t>(bytes, 16)));
+    allocations_.push_back(p);
+    return p;
+}
+
+size_t Engine::arena_offset_dense(int which) const {
+    const size_t flags = round_up(sizeof(unsigned) * 64, 256);
+    return flags + (size_t)which * round_up(n_dense_ * sizeof(float), 256);
+}
+size_t Engine::arena_offset_shard(unsigned local, int which) const {
+    const size_t row_block = round_up((size_t)cfg_.n_tail() * cfg_.d * sizeof(float), 256);
+    const size_t dense_block = round_up(n_dense_ * sizeof(float), 256);
+    const size_t per_shard = 2 * row_block + dense_block;
+    const size_t base = arena_offset_dense(3) + (size_t)local * per_shard;
+    return base + (which == 0 ? 0 : which == 1 ? row_block : 2 * row_block);
+}
+size_t Engine::arena_size() const { return arena_offset_shard(n_local_, 0); }
+
+Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || (int)cfg_.device_ordinal >= count) {
+        cudaGetLastError();
+        fail(KGE_RUNTIME_ERROR, msg() << "Could not attach to CUDA device " << cfg_.device_ordinal << " ("
+                                      << count << " visible)");
+    }
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    n_local_ = cfg_.n_shard / cfg_.world;
+    shard0_ = cfg_.rank * n_local_;
+
+    const size_t sb = type_bytes(cfg_.state_type), fb = type_bytes(cfg_.feature_type);
+    const uint32_t seg = (uint32_t)round_up(cfg_.d * sb, 16);
+    layout_.off_m = seg;
+    layout_.off_q = 2 * seg;
+    layout_.off_feat = 3 * seg;
+    layout_.row_bytes = 3 * seg + (uint32_t)round_up(cfg_.f * fb, 16);
+    layout_.d = cfg_.d;
+    layout_.f = cfg_.f;
+
+    adam_.beta_m = cfg_.beta_m;
+    adam_.beta_v = cfg_.beta_v;
+    adam_.one_minus_beta_m = 1.0f - cfg_.beta_m;
+    adam_.one_minus_beta_v = 1.0f - cfg_.beta_v;
+    adam_.epsilon = cfg_.epsilon;
+    adam_.weight_decay = cfg_.weight_decay;
+
+    // dense vector: relation table | projection(s)
+    proj_elems_ = (size_t)cfg_.f * cfg_.d;
+    dense_bounds_[0] = 0;
+    dense_bounds_[1] = (size_t)cfg_.n_relation_type * cfg_.d;
+    dense_bounds_[2] = dense_bounds_[1] + (cfg_.n_net() >= 1 ? proj_elems_ : 0);
+    dense_bounds_[3] = dense_bounds_[2] + (cfg_.n_net() >= 2 ? proj_elems_ : 0);
+    n_dense_ = dense_bounds_[3];
+    auto modifier = [&](const std::string& name) {
+        auto it = cfg_.lr_modifiers.find(name);
+        return it == cfg_.lr_modifiers.end() ? 1.0f : it->second;
+    };
+    entity_lr_mod_ = modifier("entity_embedding");
+    dense_lr_mod_[0] = modifier("relation_embedding");
+    std::vector<std::string> proj_names;
+    if (cfg_.n_net() == 1) proj_names = {"feature_projection"};
+    if (cfg_.n_net() == 2) proj_names = {"head_feature_projection", "tail_feature_projection"};
+    // With no features the reference still declares an empty projection; it is listed with
+    // shape [0, D] and carries no data.
+    if (cfg_.n_net() == 0)
+        proj_names = cfg_.share_networks
+                         ? std::vector<std::string>{"feature_projection"}
+                         : std::vector<std::string>{"head_feature_projection", "tail_feature_projection"};
+    for (size_t i = 0; i < proj_names.size() && i < 2; ++i) dense_lr_mod_[1 + i] = modifier(proj_names[i]);
+
+    auto add_variable = [&](const std::string& name, size_t rows, size_t cols, size_t offset) {
+        const char* suffix[3] = {"", "/adam_m", "/adam_v"};
+        for (int k = 0; k < 3; ++k)
+            variables_.push_back({name + suffix[k], KGE_F32, {rows, cols}, offset, k});
+    };
+    add_variable("relation_embedding", cfg_.n_relation_type, cfg_.d, 0);
+    for (size_t i = 0; i < proj_names.size(); ++i)
+        add_variable(proj_names[i], cfg_.f, cfg_.d, cfg_.f ? dense_bounds_[1 + i] : n_dense_);
+    variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3});
+
+    const size_t chunk = round_up((n_dense_ + cfg_.world - 1) / cfg_.world, 4);
+    own_lo_ = std::min(n_dense_, chunk * cfg_.rank);
+    own_hi_ = std::min(n_dense_, own_lo_ + chunk);
+
+    const unsigned tiles = ceil_div(cfg_.f, 64) * ceil_div(cfg_.d, 64) * std::max(1u, cfg_.n_net());
+    proj_splits_ = (int)std::min(8u, std::max(1u, ceil_div(148, std::max(1u, tiles))));
+    proj_rows_per_split_ = (int)round_up(ceil_div(cfg_.n_remote(), proj_splits_), 16);
+
+    KGE_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    KGE_CUDA(cudaEventCreate(&ev_begin_));
+    KGE_CUDA(cudaEventCreate(&ev_end_));
+    allocate();
+    peer_arena_.assign(cfg_.world, nullptr);
+    peer_arena_[cfg_.rank] = arena_;
+    if (cfg_.world == 1) {
+        build_pointer_tables();
+        connected_ = true;
+    }
+}
+
+Engine::~Engine() {
+    cudaSetDevice((int)cfg_.device_ordinal);
+    if (stream_) cudaStreamSynchronize(stream_);
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    for (unsigned p = 0; p < peer_arena_.size(); ++p)
+        if (p != cfg_.rank && peer_arena_[p]) cudaIpcCloseMemHandle(peer_arena_[p]);
+    for (void* p : allocations_) cudaFree(p);
+    if (pinned_) cudaFreeHost(pinned_);
+    if (ev_begin_) cudaEventDestroy(ev_begin_);
+    if (ev_end_) cudaEventDestroy(ev_end_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Engine::allocate() {
+    const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d;
+    const bool two_nets = cfg_.n_net() == 2;
+    const bool multiplicative = cfg_.score_fn != SCORE_TRANSE;
+
+    arena_ = (uint8_t*)device_alloc(arena_size());
+    KGE_CUDA(cudaMemset(arena_, 0, arena_size()));
+    dense_ = (float*)(arena_ + arena_offset_dense(0));
+    dense_m_ = (float*)(arena_ + arena_offset_dense(1));
+    dense_v_ = (float*)(arena_ + arena_offset_dense(2));
+
+    shards_.resize(n_local_);
+    const size_t table_bytes = (size_t)cfg_.n_entity * layout_.row_bytes;
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        b.table = (uint8_t*)device_alloc(table_bytes);
+        KGE_CUDA(cudaMemset(b.table, 0, table_bytes));
+        b.hid_h = (float*)device_alloc((size_t)R * D * 4);
+        b.hid_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : b.hid_h;
+        b.pred = (float*)device_alloc((size_t)B * D * 4);
+        b.raw = (float*)device_alloc((size_t)B * T * 4);
+        b.coeff = (float*)device_alloc((size_t)B * T * 4);
+        b.d_pred = (float*)device_alloc((size_t)B * D * 4);
+        b.d_head = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
+        b.d_relrow = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
+        b.d_hid_h = (float*)device_alloc((size_t)R * D * 4);
+        b.d_hid_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : nullptr;
+        b.proj_partial = (float*)device_alloc(std::max<size_t>(1, cfg_.n_net()) * proj_splits_ * proj_elems_ * 4);
+        b.loss_rows = (float*)device_alloc((size_t)B * 4);
+        b.tails = (float*)(arena_ + arena_offset_shard(l, 0));
+        b.grad_recv = (float*)(arena_ + arena_offset_shard(l, 1));
+        b.dense_partial = (float*)(arena_ + arena_offset_shard(l, 2));
+        b.send_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+        b.grad_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+    }
+    d_epoch_ = (unsigned*)device_alloc(sizeof(unsigned));
+    d_status_ = (unsigned*)device_alloc(sizeof(unsigned));
+    KGE_CUDA(cudaMemset(d_epoch_, 0, sizeof(unsigned)));
+    KGE_CUDA(cudaMemset(d_status_, 0, sizeof(unsigned)));
+    d_peer_flags_ = (unsigned**)device_alloc(sizeof(unsigned*) * cfg_.world);
+    d_partials_ = (const float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+    d_replicas_ = (float**)device_alloc(sizeof(float*) * cfg_.world);
+
+    const size_t steps = (size_t)n_local_ * cfg_.n_step;
+    d_remote_ = (uint32_t*)device_alloc(steps * R * 4);
+    d_a2a_ = (uint32_t*)device_alloc(steps * T * 4);
+    d_head_ = (uint32_t*)device_alloc(steps * B * 4);
+    d_relation_ = (uint32_t*)device_alloc(steps * B * 4);
+    d_tail_ = (uint32_t*)device_alloc(steps * B * 4);
+    d_ent_perm_ = (uint32_t*)device_alloc(steps * (B + T) * 4);
+    d_ent_off_ = (uint32_t*)device_alloc(steps * (R + 1) * 4);
+    d_rel_perm_ = (uint32_t*)device_alloc(steps * B * 4);
+    d_rel_off_ = (uint32_t*)device_alloc(steps * (cfg_.n_relation_type + 1) * 4);
+    d_first_slot_ = (uint32_t*)device_alloc(steps * R * 4);
+    d_step_size_ = (float*)device_alloc(cfg_.n_step * 4);
+    d_loss_total_ = (float*)device_alloc(n_local_ * 4);
+    d_loss_last_ = (float*)device_alloc(n_local_ * 4);
+
+    const size_t rw = (size_t)n_local_ * cfg_.rw_batch;
+    d_rw_idx_ = (uint32_t*)device_alloc(std::max<size_t>(rw, (size_t)n_local_ * cfg_.predict_hr * 2) * 4);
+    d_rw_data_ = (uint8_t*)device_alloc(rw * cfg_.row_width() * 4);
+
+    pinned_bytes_ = steps * ((size_t)R + T + 3 * B) * 4 + cfg_.n_step * 4 + 256;
+    KGE_CUDA(cudaMallocHost((void**)&pinned_, pinned_bytes_));
+    KGE_CUDA(cudaDeviceSynchronize());
+}
+
+void Engine::build_pointer_tables() {
+    const size_t block = (size_t)cfg_.a2a_size * cfg_.d;  // floats per (src, dst) block
+    std::vector<float*> send(cfg_.n_shard), grad(cfg_.n_shard);
+    std::vector<const float*> partials(cfg_.n_shard);
+    for (unsigned l = 0; l < n_local_; ++l) {
+        const unsigned me = shard0_ + l;
+        for (unsigned d = 0; d < cfg_.n_shard; ++d) {
+            const unsigned owner = d / n_local_, dl = d % n_local_;
+            uint8_t* base = peer_arena_[owner];
+            send[d] = (float*)(base + arena_offset_shard(dl, 0)) + (size_t)me * block;
+            grad[d] = (float*)(base + arena_offset_shard(dl, 1)) + (size_t)me * block;
+        }
+        KGE_CUDA(cudaMemcpy(shards_[l].send_dst, send.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
+        KGE_CUDA(cudaMemcpy(shards_[l].grad_dst, grad.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
+    }
+    for (unsigned d = 0; d < cfg_.n_shard; ++d)
+        partials[d] = (const float*)(peer_arena_[d / n_local_] + arena_offset_shard(d % n_local_, 2));
+    KGE_CUDA(cudaMemcpy(d_partials_, partials.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
+    std::vector<float*> replicas(cfg_.world);
+    std::vector<unsigned*> flags(cfg_.world);
+    for (unsigned p = 0; p < cfg_.world; ++p) {
+        replicas[p] = (float*)(peer_arena_[p] + arena_offset_dense(0));
+        flags[p] = (unsigned*)(peer_arena_[p] + arena_offset_flags());
+    }
+    KGE_CUDA(cudaMemcpy(d_replicas_, replicas.data(), sizeof(float*) * cfg_.world, cudaMemcpyHostToDevice));
+    KGE_CUDA(cudaMemcpy(d_peer_flags_, flags.data(), sizeof(unsigned*) * cfg_.world, cudaMemcpyHostToDevice));
+}
+
+// ---------------------------------------------------------------------------
+// Multi-process set-up
+
+namespace {
+struct CommHandle {
+    cudaIpcMemHandle_t mem;
+    uint32_t rank, world;
+    uint64_t arena_bytes;
+};
+}  // namespace
+
+size_t Engine::comm_handle_bytes() { return sizeof(CommHandle); }
+
+void Engine::comm_export(void* out) const {
+    CommHandle h{};
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    KGE_CUDA(cudaIpcGetMemHandle(&h.mem, arena_));
+    h.rank = cfg_.rank;
+    h.world = cfg_.world;
+    h.arena_bytes = arena_size();
+    std::memcpy(out, &h, sizeof(h));
+}
+
+void Engine::comm_connect(const void* handles, size_t world) {
+    if (world != cfg_.world)
+        fail(KGE_INVALID_ARGUMENT, msg() << "kge_comm_connect: got " << world << " handles, world_size is " << cfg_.world);
+    if (connected_) fail(KGE_LOGIC_ERROR, "kge_comm_connect: already connected");
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    const CommHandle* all = static_cast<const CommHandle*>(handles);
+    for (unsigned p = 0; p < cfg_.world; ++p) {
+        CommHandle h;
+        std::memcpy(&h, all + p, sizeof(h));
+        if (h.rank != p || h.world != cfg_.world || h.arena_bytes != arena_size())
+            fail(KGE_INVALID_ARGUMENT, msg() << "kge_comm_connect: handle " << p << " does not match this engine's settings");
+        if (p == cfg_.rank) continue;
+        void* ptr = nullptr;
+        cudaError_t err = cudaIpcOpenMemHandle(&ptr, h.mem, cudaIpcMemLazyEnablePeerAccess);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            fail(KGE_RUNTIME_ERROR, msg() << "Could not attach to the device memory of rank " << p << ": "
+                                          << cudaGetErrorString(err));
+        }
+        peer_arena_[p] = (uint8_t*)ptr;
+    }
+    build_pointer_tables();
+    connected_ = true;
+}
+
+// ---------------------------------------------------------------------------
+// Host array checks (src/poplar_kge.cpp:69-106)
+
+namespace {
+const char* dtype_name(int dtype) {
+    return dtype == KGE_F32 ? "float" : dtype == KGE_U32 ? "unsigned int" : "half";
+}
+std::string shape_string(const std::vector<size_t>& shape) {
+    msg m;
+    m << "(";
+    for (size_t i = 0; i < shape.size(); ++i) m << (i ? ", " : "") << shape[i];
+    m << ")";
+    return m;
+}
+}  // namespace
+
+HostArray& Engine::find_array(std::vector<HostArray>& arrays, const std::string& name, int dtype,
+                              const std::vector<size_t>& shape) {
+    for (HostArray& a : arrays) {
+        if (a.name != name) continue;
+        if (a.dtype != dtype)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'" << name << "' expected array of type " << dtype_name(dtype)
+                                             << ", actual: " << dtype_name(a.dtype));
+        if (a.shape != shape)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'" << name << "' expected array of shape " << shape_string(shape)
+                                             << ", actual: " << shape_string(a.shape));
+        if (!a.data && a.count()) fail(KGE_INVALID_ARGUMENT, msg() << "'" << name << "' has a null data pointer");
+        return a;
+    }
+    fail(KGE_INVALID_ARGUMENT, msg() << "Key not found '" << name << "'");
+}
+
+// ---------------------------------------------------------------------------
+// Commands
+
+void Engine::run(const std::string& command, std::vector<HostArray>& arrays, const std::string& variable) {
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    if (command == "train_step_loop") return cmd_train_step_loop(arrays);
+    if (command == "predict") return cmd_predict(arrays);
+    if (command == "read_entity") return cmd_read_entity(arrays);
+    if (command == "write_entity") return cmd_write_entity(arrays, false);
+    if (command == "write_entity_rows") return cmd_write_entity(arrays, true);
+    if (command == "read" || command == "write") return cmd_read_write_variable(arrays, variable, command == "write");
+    fail(KGE_INVALID_ARGUMENT, msg() << "Unknown command '" << command << "'");
+}
+
+void Engine::cmd_train_step_loop(std::vector<HostArray>& arrays) {
+    HostArray& lr = find_array(arrays, "learning_rate", KGE_F32, {n_local_});
+    HostArray& loss = find_array(arrays, "loss", KGE_F32, {n_local_});
+    stage_batch(arrays);
+    train_staged(static_cast<const float*>(lr.data)[0], static_cast<float*>(loss.data));
+}
+
+void Engine::stage_batch(std::vector<HostArray>& arrays) {
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    const size_t n = n_local_, S = cfg_.n_step, B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote();
+    HostArray& remote = find_array(arrays, "remote", KGE_U32, {n, S, R});
+    HostArray& a2a = find_array(arrays, "a2a", KGE_U32, {n, S, cfg_.n_shard, cfg_.a2a_size});
+    HostArray& head = find_array(arrays, "head", KGE_U32, {n, S, B});
+    HostArray& relation = find_array(arrays, "relation", KGE_U32, {n, S, B});
+    HostArray& tail = find_array(arrays, "tail", KGE_U32, {n, S, B});
+    // The reference would read out of bounds on a bad index; here it is refused on the host.
+    auto check_below = [](const HostArray& a, uint32_t limit, const char* what) {
+        const uint32_t* p = static_cast<const uint32_t*>(a.data);
+        const size_t count = a.count();
+        for (size_t i = 0; i < count; ++i)
+            if (p[i] >= limit)
+                fail(KGE_INVALID_ARGUMENT, msg() << "'" << a.name << "' holds index " << p[i] << " at position " << i
+                                                 << ", which is not below " << what << " (" << limit << ")");
+    };
+    check_below(remote, cfg_.n_entity, "model.n_entity");
+    check_below(a2a, (uint32_t)R, "the number of gathered rows");
+    check_below(head, (uint32_t)R, "the number of gathered rows");
+    check_below(relation, cfg_.n_relation_type, "model.n_relation_type");
+    check_below(tail, (uint32_t)T, "n_shard * a2a_size");
+
+    uint8_t* stage = pinned_;
+    auto upload = [&](const HostArray& a, uint32_t* dst) {
+        const size_t bytes = a.count() * 4;
+        std::memcpy(stage, a.data, bytes);
+        KGE_CUDA(cudaMemcpyAsync(dst, stage, bytes, cudaMemcpyHostToDevice, stream_));
+        stage += bytes;
+    };
+    KGE_CUDA(cudaStreamSynchronize(stream_));  // the pinned buffer may still be in flight
+    upload(remote, d_remote_);
+    upload(a2a, d_a2a_);
+    upload(head, d_head_);
+    upload(relation, d_relation_);
+    upload(tail, d_tail_);
+    k_prepare_segments<<<(unsigned)(n * S), 512, 0, stream_>>>(
+        d_head_, d_a2a_, d_relation_, d_remote_, (int)B, (int)T, (int)R, (int)cfg_.n_relation_type, d_ent_perm_,
+        d_ent_off_, d_rel_perm_, d_rel_off_, d_first_slot_);
+    KGE_CUDA(cudaGetLastError());
+    staged_ = true;
+}
+
+void Engine::train_staged(float learning_rate, float* loss) {
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    if (!staged_) fail(KGE_LOGIC_ERROR, "kge_train_staged called before kge_stage_batch");
+    if (!connected_) fail(KGE_LOGIC_ERROR, "world_size > 1 but kge_comm_connect has not been called");
+    // Adam step sizes of the staged steps (src/fructose/frnn.cpp:42-59), in fp32.
+    float* sizes = reinterpret_cast<float*>(pinned_ + pinned_bytes_ - 256 - (size_t)cfg_.n_step * 4);
+    for (unsigned i = 0; i < cfg_.n_step; ++i) {
+        const float t = (float)(step_ + 1 + i);
+        sizes[i] = (std::sqrt(1.0f - std::pow(cfg_.beta_v, t)) / (1.0f - std::pow(cfg_.beta_m, t))) * learning_rate;
+    }
+    KGE_CUDA(cudaMemcpyAsync(d_step_size_, sizes, (size_t)cfg_.n_step * 4, cudaMemcpyHostToDevice, stream_));
+    KGE_CUDA(cudaMemsetAsync(d_loss_total_, 0, n_local_ * 4, stream_));
+    KGE_CUDA(cudaEventRecord(ev_begin_, stream_));
+    if (cfg_.cuda_graph) {
+        if (!graph_exec_) {
+            cudaGraph_t graph = nullptr;
+            launch_counter_ = 0;
+            KGE_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+            try {
+                launch_steps();
+            } catch (...) {
+                cudaStreamEndCapture(stream_, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                throw;
+            }
+            KGE_CUDA(cudaStreamEndCapture(stream_, &graph));
+            cudaError_t err = cudaGraphInstantiate(&graph_exec_, graph, 0);
+            cudaGraphDestroy(graph);
+            KGE_CUDA(err);
+            last_launches_ = launch_counter_;
+        }
+        KGE_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    } else {
+        launch_counter_ = 0;
+        launch_steps();
+        last_launches_ = launch_counter_;
+    }
+    KGE_CUDA(cudaEventRecord(ev_end_, stream_));
+    float* host_loss = reinterpret_cast<float*>(pinned_ + pinned_bytes_ - 256);
+    if (loss)
+        KGE_CUDA(cudaMemcpyAsync(host_loss, d_loss_total_, n_local_ * 4, cudaMemcpyDeviceToHost, stream_));
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    KGE_CUDA(cudaEventElapsedTime(&last_ms_, ev_begin_, ev_end_));
+    step_ += cfg_.n_step;
+    check_device_status();
+    if (loss)
+        for (unsigned l = 0; l < n_local_; ++l) loss[l] = host_loss[l] / (float)cfg_.n_step;
+}
+
+void Engine::check_device_status() {
+    if (cfg_.world == 1) return;
+    unsigned status = 0;
+    KGE_CUDA(cudaMemcpy(&status, d_status_, sizeof(status), cudaMemcpyDeviceToHost));
+    if (status) {
+        KGE_CUDA(cudaMemset(d_status_, 0, sizeof(status)));
+        fail(KGE_DEVICE_STATUS, msg() << "a device-side wait for rank " << (status - 1)
+                                      << " gave up: that process did not reach the same step");
+    }
+}
+
+void Engine::last_run_stats(float* ms, unsigned long long* launches) const {
+    if (ms) *ms = last_ms_;
+    if (launches) *launches = last_launches_;
+}
+
+void Engine::launch_steps() {
+    for (unsigned step = 0; step < cfg_.n_step; ++step) launch_one_step(step);
+}
+
+void Engine::launch_barrier() {
+    if (cfg_.world == 1) return;
+    BarrierArgs a;
+    a.peer_flags = d_peer_flags_;
+    a.my_epoch = d_epoch_;
+    a.status = d_status_;
+    a.rank = (int)cfg_.rank;
+    a.world = (int)cfg_.world;
+    a.max_spins = 20ull * 1000 * 1000;  // about two seconds of 64 ns naps plus load latency
+    k_barrier<<<1, 64, 0, stream_>>>(a);
+    ++launch_counter_;
+    KGE_CUDA(cudaGetLastError());
+}
+
+void Engine::launch_one_step(unsigned step) {
+    const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d, F = cfg_.f;
+    const unsigned n_rel = cfg_.n_relation_type;
+    const bool two_nets = cfg_.n_net() == 2;
+    const bool vec = (D % 4) == 0;
+    const float* rel_table = dense_;
+    const float* W0 = cfg_.n_net() >= 1 ? dense_ + dense_bounds_[1] : nullptr;
+    const float* W1 = two_nets ? dense_ + dense_bounds_[2] : W0;
+
+    LossParams lp{};
+    lp.loss_fn = cfg_.loss_fn;
+    lp.score_fn = cfg_.score_fn;
+    lp.dist_fn = cfg_.dist_fn;
+    lp.n_tail = (int)T;
+    lp.gamma = cfg_.gamma;
+    lp.adversarial_scale = cfg_.adversarial_scale;
+    lp.w_neg = (0.5f * (float)T) / (float)(T - 1);
+    lp.w_pos = 0.5f * (float)T;
+    float normaliser;
+    if (cfg_.loss_fn == LOSS_LOGSIGMOID) {
+        normaliser = (float)(cfg_.n_shard * B * cfg_.a2a_size * cfg_.n_shard);
+        lp.softmax_shift = 0.f;
+    } else {
+        normaliser = (float)(cfg_.n_shard * B);
+        const float correction = (float)(std::log((double)(cfg_.n_entity * cfg_.n_shard - 1)) -
+                                         std::log((double)(cfg_.n_shard * cfg_.a2a_size - 1)));
+        lp.softmax_shift = cfg_.correction_weight != 0.f ? cfg_.correction_weight * correction : 0.f;
+    }
+    lp.grad_scale = cfg_.loss_scale / normaliser;
+
+    auto step_ptr = [&](uint32_t* base, unsigned l, size_t per_step) {
+        return base + ((size_t)l * cfg_.n_step + step) * per_step;
+    };
+
+    // 1./2. hidden rows, lookups, send half of the exchange
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        const uint32_t* remote = step_ptr(d_remote_, l, R);
+        dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
+        KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(b.table, layout_, remote, (int)R, W0, W1,
+                                                                           b.hid_h, b.hid_t));
+        ++launch_counter_;
+        const uint32_t* a2a = step_ptr(d_a2a_, l, T);
+        const uint32_t* head = step_ptr(d_head_, l, B);
+        const uint32_t* relation = step_ptr(d_relation_, l, B);
+        if (vec)
+            k_route<4><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table, b.send_dst,
+                                                  b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn);
+        else
+            k_route<1><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table, b.send_dst,
+                                                  b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn);
+        ++launch_counter_;
+    }
+    KGE_CUDA(cudaGetLastError());
+    launch_barrier();
+
+    // 3./4./5a. scores, loss, score backward with the return half of the exchange
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        const uint32_t* head = step_ptr(d_head_, l, B);
+        const uint32_t* relation = step_ptr(d_relation_, l, B);
+        const uint32_t* tail = step_ptr(d_tail_, l, B);
+        dim3 sgrid(ceil_div(T, 64), ceil_div(B, 32));
+        PairBwdArgs pa{};
+        pa.D = (int)D;
+        pa.tiles_m0 = (int)ceil_div(B, 32);
+        pa.p[0] = {b.pred, b.tails, b.coeff, (int)B, (int)T, (int)T, 1, b.d_pred, nullptr, 1};
+        pa.p[1] = {b.tails, b.pred, b.coeff, (int)T, (int)B, 1, (int)T, nullptr, b.grad_dst, (int)cfg_.a2a_size};
+        dim3 bgrid(ceil_div(B, 32) + ceil_div(T, 32), ceil_div(D, 64));
+        switch (cfg_.dist_fn) {
+            case DIST_L1: k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D); break;
+            case DIST_L2: k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D); break;
+            default: k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D); break;
+        }
+        k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp);
+        k_loss_finish<<<1, 256, 0, stream_>>>(b.loss_rows, (int)B, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l);
+        switch (cfg_.dist_fn) {
+            case DIST_L1: k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa); break;
+            case DIST_L2: k_pair_bwd<DIST_L2><<<bgrid, 128, 0, stream_>>>(pa); break;
+            default: k_pair_bwd<DIST_DOT><<<bgrid, 128, 0, stream_>>>(pa); break;
+        }
+        launch_counter_ += 4;
+        if (cfg_.score_fn != SCORE_TRANSE) {
+            k_pred_bwd<<<B, 64, 0, stream_>>>(b.d_pred, b.hid_h, head, relation, rel_table, b.d_head, b.d_relrow,
+                                              (int)D, cfg_.score_fn);
+            ++launch_counter_;
+        }
+    }
+    KGE_CUDA(cudaGetLastError());
+    launch_barrier();
+
+    // 5b. segment sums + row-wise Adam; projection and relation gradients of this shard
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        const size_t sidx = (size_t)l * cfg_.n_step + step;
+        const uint32_t* remote = step_ptr(d_remote_, l, R);
+        const uint32_t* perm = d_ent_perm_ + sidx * (B + T);
+        const uint32_t* off = d_ent_off_ + sidx * (R + 1);
+        const uint32_t* first = d_first_slot_ + sidx * R;
+        if (cfg_.state_type == ST_F32) {
+            if (vec)
+                k_entity_update<float, 4><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
+                                                                 (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
+                                                                 entity_lr_mod_, adam_);
+            else
+                k_entity_update<float, 1><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
+                                                                 (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
+                                                                 entity_lr_mod_, adam_);
+        } else {
+            if (vec)
+                k_entity_update<__half, 4><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
+                                                                  (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
+                                                                  entity_lr_mod_, adam_);
+            else
+                k_entity_update<__half, 1><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
+                                                                  (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
+                                                                  entity_lr_mod_, adam_);
+        }
+        ++launch_counter_;
+        if (F > 0) {
+            dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
+            const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
+            if (cfg_.feature_type == ST_F32)
+                k_projection_bwd<float><<<grid, 256, 0, stream_>>>(b.table, layout_, remote, (int)R, b.d_hid_h, dh1,
+                                                                   proj_splits_, proj_rows_per_split_, b.proj_partial);
+            else
+                k_projection_bwd<__half><<<grid, 256, 0, stream_>>>(b.table, layout_, remote, (int)R, b.d_hid_h, dh1,
+                                                                    proj_splits_, proj_rows_per_split_, b.proj_partial);
+            ++launch_counter_;
+        }
+        const unsigned blocks = (unsigned)std::min<size_t>((n_dense_ + 255) / 256, 148 * 8);
+        k_dense_partial<<<std::max(1u, blocks), 256, 0, stream_>>>(
+            b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel, (int)D, b.proj_partial,
+            (int)cfg_.n_net(), proj_splits_, proj_elems_, b.dense_partial);
+        ++launch_counter_;
+    }
+    KGE_CUDA(cudaGetLastError());
+    launch_barrier();
+
+    // 5c. dense parameters: reduce over shards, Adam on the owned slice, publish
+    if (own_hi_ > own_lo_) {
+        DenseUpdateArgs da{};
+        da.partials = d_partials_;
+        da.n_partial = (int)cfg_.n_shard;
+        da.replicas = d_replicas_;
+        da.n_replica = (int)cfg_.world;
+        da.adam_m = dense_m_;
+        da.adam_v = dense_v_;
+        da.lo = own_lo_;
+        da.hi = own_hi_;
+        for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
+        for (int i = 0; i < 3; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
+        da.step_size = d_step_size_ + step;
+        da.ap = adam_;
+        // The parameter itself is read from this process's own replica (entry `rank`).
+        const unsigned blocks = (unsigned)std::min<size_t>((own_hi_ - own_lo_ + 255) / 256, 148 * 8);
+        k_dense_update<<<std::max(1u, blocks), 256, 0, stream_>>>(da, (int)cfg_.rank);
+        ++launch_counter_;
+    }
+    KGE_CUDA(cudaGetLastError());
+    launch_barrier();
+}
+
+// ---------------------------------------------------------------------------
+// Table and variable I/O
+
+void Engine::cmd_read_entity(std::vector<HostArray>& arrays) {
+    const size_t n = n_local_, rw = cfg_.rw_batch, W = cfg_.row_width();
+    HostArray& idx = find_array(arrays, "read_indices", KGE_U32, {n, rw});
+    const int out_dtype = cfg_.state_type == ST_F32 ? KGE_F32 : KGE_F16;
+    HostArray& out = find_array(arrays, "read_data", out_dtype, {n, rw, W});
+    const uint32_t* h = static_cast<const uint32_t*>(idx.data);
+    for (size_t i = 0; i < n * rw; ++i)
+        if (h[i] >= cfg_.n_entity)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'read_indices' holds index " << h[i] << ", not below model.n_entity ("
+                                             << cfg_.n_entity << ")");
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    KGE_CUDA(cudaMemcpyAsync(d_rw_idx_, idx.data, n * rw * 4, cudaMemcpyHostToDevice, stream_));
+    const size_t elem = out_dtype == KGE_F32 ? 4 : 2;
+    for (unsigned l = 0; l < n; ++l) {
+        const uint32_t* di = d_rw_idx_ + l * rw;
+        void* dout = d_rw_data_ + l * rw * W * elem;
+        if (out_dtype == KGE_F32) {
+            KGE_DISPATCH_ROW(cfg_, k_read_rows<ST, FT, float><<<(unsigned)rw, 128, 0, stream_>>>(shards_[l].table, layout_, di,
+                                                                                                 (float*)dout));
+        } else {
+            k_read_rows<__half, __half, __half><<<(unsigned)rw, 128, 0, stream_>>>(shards_[l].table, layout_, di, (__half*)dout);
+        }
+    }
+    KGE_CUDA(cudaGetLastError());
+    KGE_CUDA(cudaMemcpyAsync(out.data, d_rw_data_, n * rw * W * elem, cudaMemcpyDeviceToHost, stream_));
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Engine::cmd_write_entity(std::vector<HostArray>& arrays, bool whole_rows) {
+    const size_t n = n_local_, rw = cfg_.rw_batch, W = cfg_.row_width(), F = cfg_.f;
+    HostArray& idx = find_array(arrays, "write_indices", KGE_U32, {n, rw});
+    const char* data_name = whole_rows ? "write_data" : "write_features";
+    const std::vector<size_t> shape = {n, rw, whole_rows ? W : F};
+    // The host array is in the state type (the reference's single dtype); a float16 array is
+    // also taken for features when they are stored as float16.
+    HostArray* data = nullptr;
+    for (HostArray& a : arrays)
+        if (a.name == data_name) data = &a;
+    if (!data) fail(KGE_INVALID_ARGUMENT, msg() << "Key not found '" << data_name << "'");
+    const int state_dtype = cfg_.state_type == ST_F32 ? KGE_F32 : KGE_F16;
+    const bool f16_features_ok = !whole_rows && cfg_.feature_type == ST_F16 && data->dtype == KGE_F16;
+    find_array(arrays, data_name, f16_features_ok ? KGE_F16 : state_dtype, shape);
+    const uint32_t* h = static_cast<const uint32_t*>(idx.data);
+    for (size_t i = 0; i < n * rw; ++i)
+        if (h[i] >= cfg_.n_entity)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'write_indices' holds index " << h[i] << ", not below model.n_entity ("
+                                             << cfg_.n_entity << ")");
+    const size_t elem = data->dtype == KGE_F32 ? 4 : 2, per_row = shape[2];
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    KGE_CUDA(cudaMemcpyAsync(d_rw_idx_, idx.data, n * rw * 4, cudaMemcpyHostToDevice, stream_));
+    KGE_CUDA(cudaMemcpyAsync(d_rw_data_, data->data, n * rw * per_row * elem, cudaMemcpyHostToDevice, stream_));
+    const float stddev = cfg_.init_scale / (float)cfg_.d;  // src/poplar_kge.cpp:865
+    for (unsigned l = 0; l < n; ++l) {
+        const uint32_t* di = d_rw_idx_ + l * rw;
+        const uint8_t* din = d_rw_data_ + l * rw * per_row * elem;
+        uint8_t* table = shards_[l].table;
+        const unsigned g = (unsigned)rw;
+        if (data->dtype == KGE_F32) {
+            using IT = float;
+            if (whole_rows) KGE_DISPATCH_ROW(cfg_, k_write_rows<ST, FT, IT><<<g, 128, 0, stream_>>>(table, layout_, di, (int)rw, (const IT*)din));
+            else KGE_DISPATCH_ROW(cfg_, k_write_entity<ST, FT, IT><<<g, 128, 0, stream_>>>(table, layout_, di, (int)rw, (const IT*)din, cfg_.seed, shard0_ + l, stddev));
+        } else {
+            using IT = __half;
+            if (whole_rows) KGE_DISPATCH_ROW(cfg_, k_write_rows<ST, FT, IT><<<g, 128, 0, stream_>>>(table, layout_, di, (int)rw, (const IT*)din));
+            else KGE_DISPATCH_ROW(cfg_, k_write_entity<ST, FT, IT><<<g, 128, 0, stream_>>>(table, layout_, di, (int)rw, (const IT*)din, cfg_.seed, shard0_ + l, stddev));
+        }
+    }
+    KGE_CUDA(cudaGetLastError());
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::string& name, bool write) {
+    const Variable* var = nullptr;
+    for (const Variable& v : variables_)
+        if (v.name == name) var = &v;
+    if (!var) fail(KGE_INVALID_ARGUMENT, msg() << "Key not found '" << name << "'");
+    HostArray& value = find_array(arrays, "value", var->dtype, var->shape);
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    if (var->kind == 3) {  // step: one counter, presented per shard
+        uint32_t* p = static_cast<uint32_t*>(value.data);
+        if (write) {
+            for (unsigned s = 1; s < cfg_.n_shard; ++s)
+                if (p[s] != p[0]) fail(KGE_INVALID_ARGUMENT, "'step' must hold the same value for every shard");
+            step_ = p[0];
+        } else {
+            for (unsigned s = 0; s < cfg_.n_shard; ++s) p[s] = (uint32_t)step_;
+        }
+        return;
+    }
+    const size_t count = value.count();
+    if (count == 0) return;
+    float* base = var->kind == 0 ? dense_ : var->kind == 1 ? dense_m_ : dense_v_;
+    if (write) {
+        KGE_CUDA(cudaMemcpy(base + var->offset, value.data, count * 4, cudaMemcpyHostToDevice));
+        return;
+    }
+    if (var->kind == 0 || cfg_.world == 1) {
+        KGE_CUDA(cudaMemcpy(value.data, base + var->offset, count * 4, cudaMemcpyDeviceToHost));
+        return;
+    }
+    // Optimiser state lives with the process that owns the slice (src/poplar_kge.cpp:329-339):
+    // collect each owner's part through its mapped arena.
+    const size_t chunk = round_up((n_dense_ + cfg_.world - 1) / cfg_.world, 4);
+    for (unsigned p = 0; p < cfg_.world; ++p) {
+        const size_t lo = std::max(var->offset, std::min(n_dense_, chunk * p));
+        const size_t hi = std::min(var->offset + count, std::min(n_dense_, chunk * (p + 1)));
+        if (hi <= lo) continue;
+        const float* src = (const float*)(peer_arena_[p] + arena_offset_dense(var->kind)) + lo;
+        KGE_CUDA(cudaMemcpy(static_cast<float*>(value.data) + (lo - var->offset), src, (hi - lo) * 4, cudaMemcpyDeviceToHost));
+    }
+}
+
+void Engine::cmd_predict(std::vector<HostArray>&) {
+    fail(KGE_INVALID_ARGUMENT, "command 'predict' is not available in this build");
+}
+
+size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, size_t capacity) {
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    if (shard >= n_local_) fail(KGE_INVALID_ARGUMENT, "kge_debug_fetch: shard out of range");
+    const ShardBuffers& b = shards_[shard];
+    const size_t B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d;
+    const float* src = nullptr;
+    size_t count = 0;
+    if (what == "hidden") { src = b.hid_h; count = R * D; }
+    else if (what == "tails") { src = b.tails; count = T * D; }
+    else if (what == "pred") { src = b.pred; count = B * D; }
+    else if (what == "raw_score") { src = b.raw; count = B * T; }
+    else if (what == "coeff") { src = b.coeff; count = B * T; }
+    else if (what == "d_pred") { src = b.d_pred; count = B * D; }
+    else if (what == "d_hidden") { src = b.d_hid_h; count = R * D; }
+    else if (what == "grad_recv") { src = b.grad_recv; count = T * D; }
+    else if (what == "dense_grad") { src = b.dense_partial; count = n_dense_; }
+    else if (what == "loss_last") { src = d_loss_last_ + shard; count = 1; }
+    else fail(KGE_INVALID_ARGUMENT, msg() << "kge_debug_fetch: unknown buffer '" << what << "'");
+    if (count > capacity) fail(KGE_INVALID_ARGUMENT, msg() << "kge_debug_fetch: '" << what << "' needs room for " << count << " floats");
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    if (count) KGE_CUDA(cudaMemcpy(out, src, count * 4, cudaMemcpyDeviceToHost));
+    return count;
+}
+
+}  // namespace kge

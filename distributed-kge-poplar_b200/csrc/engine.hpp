@@ -1,0 +1,170 @@
+// Host engine: owns the shard tables, the dense parameters and the per-step buffers of
+// the shards this process holds, and launches the kernels of one training step in the
+// order of the reference's Model::trainStep (src/poplar_kge.cpp:664-707).
+#pragma once
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.hpp"
+#include "kernels.cuh"
+
+namespace kge {
+
+struct SettingValue {
+    int type;
+    std::string s;
+    double f;
+    unsigned long long u;
+};
+using SettingMap = std::map<std::string, SettingValue>;
+
+enum StorageType : int { ST_F32 = 0, ST_F16 = 1 };
+
+// The keys the reference's Model reads (src/poplar_kge.cpp:198-246) plus this engine's own.
+struct Config {
+    unsigned seed, n_shard, n_entity, n_relation_type, d, f;
+    unsigned batch_size, a2a_size, n_step, rw_batch, predict_hr, predict_tail_batch, predict_n_best;
+    int score_fn, dist_fn, loss_fn;
+    bool share_networks;
+    float gamma, init_scale, adversarial_scale, correction_weight, loss_scale;
+    float beta_m, beta_v, epsilon, weight_decay;
+    std::map<std::string, float> lr_modifiers;
+    int state_type, feature_type;
+    unsigned device_ordinal, rank, world;
+    bool cuda_graph;
+
+    unsigned n_tail() const { return n_shard * a2a_size; }
+    unsigned n_remote() const { return batch_size + n_tail(); }
+    unsigned row_width() const { return 3 * d + f; }
+    unsigned n_net() const { return f == 0 ? 0 : (share_networks ? 1 : 2); }
+};
+
+Config parse_config(const SettingMap& settings);
+
+struct Variable {
+    std::string name;
+    int dtype;
+    std::vector<size_t> shape;
+    size_t offset;  // element offset inside the dense vector (params / adam_m / adam_v)
+    int kind;       // 0 = parameter, 1 = adam_m, 2 = adam_v, 3 = step
+};
+
+struct HostArray {
+    std::string name;
+    int dtype;
+    std::vector<size_t> shape;
+    void* data;
+    size_t count() const {
+        size_t n = 1;
+        for (size_t s : shape) n *= s;
+        return n;
+    }
+};
+
+class Engine {
+   public:
+    explicit Engine(const SettingMap& settings);
+    ~Engine();
+    Engine(const Engine&) = delete;
+    Engine& operator=(const Engine&) = delete;
+
+    void run(const std::string& command, std::vector<HostArray>& arrays, const std::string& variable);
+    const std::vector<Variable>& variables() const { return variables_; }
+
+    static size_t comm_handle_bytes();
+    void comm_export(void* out) const;
+    void comm_connect(const void* handles, size_t world);
+
+    void stage_batch(std::vector<HostArray>& arrays);
+    void train_staged(float learning_rate, float* loss);
+    void last_run_stats(float* ms, unsigned long long* launches) const;
+    size_t debug_fetch(const std::string& what, size_t shard, float* out, size_t capacity);
+
+    std::string last_error;
+
+   private:
+    struct ShardBuffers {
+        uint8_t* table = nullptr;
+        float *hid_h = nullptr, *hid_t = nullptr, *pred = nullptr, *raw = nullptr, *coeff = nullptr;
+        float *d_pred = nullptr, *d_head = nullptr, *d_relrow = nullptr;
+        float *d_hid_h = nullptr, *d_hid_t = nullptr, *proj_partial = nullptr, *loss_rows = nullptr;
+        float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
+        float** send_dst = nullptr;  // device table [n_shard]
+        float** grad_dst = nullptr;  // device table [n_shard]
+    };
+
+    // set-up
+    void allocate();
+    void build_pointer_tables();
+    size_t arena_offset_flags() const { return 0; }
+    size_t arena_offset_dense(int which) const;
+    size_t arena_offset_shard(unsigned local, int which) const;
+    size_t arena_size() const;
+
+    // commands
+    void cmd_train_step_loop(std::vector<HostArray>& arrays);
+    void cmd_read_entity(std::vector<HostArray>& arrays);
+    void cmd_write_entity(std::vector<HostArray>& arrays, bool whole_rows);
+    void cmd_read_write_variable(std::vector<HostArray>& arrays, const std::string& name, bool write);
+    void cmd_predict(std::vector<HostArray>& arrays);
+
+    // the step
+    void launch_steps();
+    void launch_one_step(unsigned step);
+    void launch_barrier();
+    void check_device_status();
+
+    HostArray& find_array(std::vector<HostArray>& arrays, const std::string& name, int dtype,
+                          const std::vector<size_t>& shape);
+    void* device_alloc(size_t bytes);
+
+    Config cfg_;
+    RowLayout layout_{};
+    AdamParams adam_{};
+    unsigned n_local_ = 0, shard0_ = 0;
+    cudaStream_t stream_ = nullptr;
+    cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+    std::vector<void*> allocations_;
+    std::vector<ShardBuffers> shards_;
+
+    // peer-visible arena
+    uint8_t* arena_ = nullptr;
+    std::vector<uint8_t*> peer_arena_;
+    bool connected_ = false;
+    unsigned* d_epoch_ = nullptr;
+    unsigned* d_status_ = nullptr;
+    unsigned** d_peer_flags_ = nullptr;
+    const float** d_partials_ = nullptr;  // [n_shard]
+    float** d_replicas_ = nullptr;        // [world]
+
+    // dense parameters: relation table | projection(s)
+    size_t n_dense_ = 0, proj_elems_ = 0, dense_bounds_[4] = {0, 0, 0, 0};
+    float dense_lr_mod_[3] = {1.f, 1.f, 1.f};
+    float entity_lr_mod_ = 1.f;
+    float *dense_ = nullptr, *dense_m_ = nullptr, *dense_v_ = nullptr;
+    size_t own_lo_ = 0, own_hi_ = 0;
+    std::vector<Variable> variables_;
+    unsigned long long step_ = 0;
+    int proj_splits_ = 1, proj_rows_per_split_ = 0;
+
+    // staged batch
+    uint32_t *d_remote_ = nullptr, *d_a2a_ = nullptr, *d_head_ = nullptr, *d_relation_ = nullptr,
+             *d_tail_ = nullptr;
+    uint32_t *d_ent_perm_ = nullptr, *d_ent_off_ = nullptr, *d_rel_perm_ = nullptr,
+             *d_rel_off_ = nullptr, *d_first_slot_ = nullptr;
+    float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
+    uint8_t* pinned_ = nullptr;
+    size_t pinned_bytes_ = 0;
+    bool staged_ = false;
+    uint32_t* d_rw_idx_ = nullptr;
+    uint8_t* d_rw_data_ = nullptr;
+
+    cudaGraphExec_t graph_exec_ = nullptr;
+    float last_ms_ = 0.f;
+    unsigned long long last_launches_ = 0, launch_counter_ = 0;
+};
+
+}  // namespace kge

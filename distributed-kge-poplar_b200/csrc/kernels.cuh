@@ -1,0 +1,1139 @@
+// Device kernels of the BESS training step for sm_100a.
+//
+// Naming follows the reference's step (src/poplar_kge.cpp:664-707): rows of the stacked
+// shard table are gathered by `remote`, turned into hidden vectors, looked up by `head`
+// and `a2a`, exchanged, scored against the batch-shared tails, and the gradients flow
+// back the same way into a row-wise Adam update.  All arithmetic is fp32.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kge {
+
+enum ScoreFn : int { SCORE_TRANSE = 0, SCORE_DISTMULT = 1, SCORE_COMPLEX = 2 };
+enum DistFn : int { DIST_L1 = 0, DIST_L2 = 1, DIST_DOT = 2 };
+enum LossFn : int { LOSS_LOGSIGMOID = 0, LOSS_SOFTMAX = 1 };
+
+// Byte layout of one table row: value | adam_m | sqrt(adam_v) | feature
+// (src/poplar_kge.cpp:405-417).  Every segment starts on a 16-byte boundary and
+// row_bytes is a multiple of 16, so 128-bit accesses are always aligned.
+struct RowLayout {
+    uint32_t row_bytes;
+    uint32_t off_m;
+    uint32_t off_q;
+    uint32_t off_feat;
+    uint32_t d;
+    uint32_t f;
+};
+
+struct AdamParams {
+    float beta_m;
+    float beta_v;
+    float one_minus_beta_m;
+    float one_minus_beta_v;
+    float epsilon;
+    float weight_decay;
+};
+
+__device__ __forceinline__ float load_as_float(const float* p) { return *p; }
+__device__ __forceinline__ float load_as_float(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ void store_from_float(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store_from_float(__half* p, float v) { *p = __float2half_rn(v); }
+
+// Four consecutive elements starting at an element index that is a multiple of 4.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __half* p) {
+    uint2 raw = *reinterpret_cast<const uint2*>(p);
+    __half2 lo = *reinterpret_cast<__half2*>(&raw.x);
+    __half2 hi = *reinterpret_cast<__half2*>(&raw.y);
+    float2 a = __half22float2(lo), b = __half22float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__half* p, float4 v) {
+    __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// Block-wide reductions with a fixed tree, so results do not depend on scheduling.
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) total += scratch[w];
+    return total;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = scratch[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; ++w) total = fmaxf(total, scratch[w]);
+    return total;
+}
+
+// ---------------------------------------------------------------------------
+// hidden = value + feature . W   (src/poplar_kge.cpp:439-467 with the gather of :405-410
+// folded in).  A [R, F] is read straight from the gathered table rows; W is [F, D].
+// blockIdx.z picks the feature network (head / tail) when they are not shared.
+// 64x64 output tile, 16-deep k slices, 256 threads with a 4x4 register tile each.
+template <class ST, class FT>
+__global__ void __launch_bounds__(256)
+k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote, int R,
+         const float* __restrict__ W0, const float* __restrict__ W1, float* __restrict__ out0,
+         float* __restrict__ out1) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ __align__(16) float As[BK][BM + 4];
+    __shared__ __align__(16) float Bs[BK][BN];
+    const float* __restrict__ W = blockIdx.z ? W1 : W0;
+    float* __restrict__ out = blockIdx.z ? out1 : out0;
+    const int D = L.d, F = L.f;
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+
+    const int a_row = t >> 2, a_k = (t & 3) * 4;
+    const bool a_ok = m0 + a_row < R;
+    const FT* __restrict__ a_ptr = nullptr;
+    if (a_ok) {
+        const size_t row = remote[m0 + a_row];
+        a_ptr = reinterpret_cast<const FT*>(table + row * L.row_bytes + L.off_feat);
+    }
+    const int b_k = t >> 4, b_n = (t & 15) * 4;
+    const bool d_vec = (D & 3) == 0;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < F; k0 += BK) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int ka = k0 + a_k;
+        if (a_ok) {
+            if (ka + 3 < F) {
+                a = load4(a_ptr + ka);
+            } else {
+                if (ka + 0 < F) a.x = load_as_float(a_ptr + ka + 0);
+                if (ka + 1 < F) a.y = load_as_float(a_ptr + ka + 1);
+                if (ka + 2 < F) a.z = load_as_float(a_ptr + ka + 2);
+            }
+        }
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int kb = k0 + b_k, nb = n0 + b_n;
+        if (kb < F) {
+            const float* wp = W + (size_t)kb * D + nb;
+            if (d_vec && nb + 3 < D) {
+                b = load4(wp);
+            } else {
+                if (nb + 0 < D) b.x = wp[0];
+                if (nb + 1 < D) b.y = wp[1];
+                if (nb + 2 < D) b.z = wp[2];
+                if (nb + 3 < D) b.w = wp[3];
+            }
+        }
+        __syncthreads();
+        As[a_k + 0][a_row] = a.x;
+        As[a_k + 1][a_row] = a.y;
+        As[a_k + 2][a_row] = a.z;
+        As[a_k + 3][a_row] = a.w;
+        store4(&Bs[b_k][b_n], b);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 av = load4(&As[kk][ty * 4]);
+            const float4 bv = load4(&Bs[kk][tx * 4]);
+            const float ar[4] = {av.x, av.y, av.z, av.w};
+            const float br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= R) continue;
+        const size_t row = remote[m];
+        const ST* vp = reinterpret_cast<const ST*>(table + row * L.row_bytes);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < D) out[(size_t)m * D + n] = load_as_float(vp + n) + acc[i][j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Lookups of the hidden table and the send half of the exchange
+// (src/poplar_kge.cpp:676-684).  Blocks [0, T) copy hidden_t[a2a[q]] straight into the
+// receive buffer of the destination shard (a peer's device memory when that shard lives
+// in another process): `send_dst[d]` already points at this shard's slot of shard d's
+// buffer.  Blocks [T, T+B) form the predicted tail h (+|*|complex*) r into `pred`.
+template <int V>
+__global__ void __launch_bounds__(64)
+k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
+        const uint32_t* __restrict__ a2a_idx, const uint32_t* __restrict__ head,
+        const uint32_t* __restrict__ relation, const float* __restrict__ rel_table,
+        float* const* __restrict__ send_dst, float* __restrict__ pred, int T, int a2a, int B, int D,
+        int score_fn) {
+    const int b = blockIdx.x;
+    if (b < T) {
+        const int dst = b / a2a, j = b - dst * a2a;
+        const float* __restrict__ src = hid_t + (size_t)a2a_idx[b] * D;
+        float* __restrict__ out = send_dst[dst] + (size_t)j * D;
+        if (V == 4) {
+            for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) store4(out + c, load4(src + c));
+        } else {
+            for (int c = threadIdx.x; c < D; c += blockDim.x) out[c] = src[c];
+        }
+        return;
+    }
+    const int i = b - T;
+    if (i >= B) return;
+    const float* __restrict__ h = hid_h + (size_t)head[i] * D;
+    const float* __restrict__ r = rel_table + (size_t)relation[i] * D;
+    float* __restrict__ p = pred + (size_t)i * D;
+    if (score_fn == SCORE_COMPLEX) {
+        const int half = D / 2;
+        for (int c = threadIdx.x; c < half; c += blockDim.x) {
+            const float hr = h[c], hi = h[c + half], rr = r[c], ri = r[c + half];
+            p[c] = hr * rr - hi * ri;
+            p[c + half] = hr * ri + hi * rr;
+        }
+    } else if (V == 4) {
+        for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
+            const float4 a = load4(h + c), q = load4(r + c);
+            float4 o;
+            if (score_fn == SCORE_TRANSE) {
+                o = make_float4(a.x + q.x, a.y + q.y, a.z + q.z, a.w + q.w);
+            } else {
+                o = make_float4(a.x * q.x, a.y * q.y, a.z * q.z, a.w * q.w);
+            }
+            store4(p + c, o);
+        }
+    } else {
+        for (int c = threadIdx.x; c < D; c += blockDim.x)
+            p[c] = score_fn == SCORE_TRANSE ? h[c] + r[c] : h[c] * r[c];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// raw[i, j] = sum_k |p_ik - t_jk|  (L1),  sqrt(sum_k (p_ik - t_jk)^2)  (L2),  sum_k p_ik t_jk (dot)
+// src/poplar_extensions/distance.cpp:70-104,151-185 and the codelets' l1dist / l2dist;
+// the dot form is matMul(a, b^T) of src/poplar_kge.cpp:478-479.
+// 32x64 output tile, 32-deep k slices staged in shared memory k-major, 128 threads, 4x4 each.
+template <int FN>
+__global__ void __launch_bounds__(128)
+k_score(const float* __restrict__ P, const float* __restrict__ Tl, float* __restrict__ raw, int B,
+        int T, int D) {
+    constexpr int BM = 32, BN = 64, BK = 32;
+    __shared__ __align__(16) float Ps[BK][BM];
+    __shared__ __align__(16) float Ts[BK][BN];
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const int i0 = blockIdx.y * BM, j0 = blockIdx.x * BN;
+    const bool vec = (D & 3) == 0;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+
+    for (int k0 = 0; k0 < D; k0 += BK) {
+        __syncthreads();
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int idx = t + it * 128, row = idx & 31, k4 = (idx >> 5) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int gi = i0 + row, gk = k0 + k4;
+            if (gi < B) {
+                const float* src = P + (size_t)gi * D + gk;
+                if (vec && gk + 3 < D) {
+                    v = load4(src);
+                } else {
+                    if (gk + 0 < D) v.x = src[0];
+                    if (gk + 1 < D) v.y = src[1];
+                    if (gk + 2 < D) v.z = src[2];
+                    if (gk + 3 < D) v.w = src[3];
+                }
+            }
+            Ps[k4 + 0][row] = v.x;
+            Ps[k4 + 1][row] = v.y;
+            Ps[k4 + 2][row] = v.z;
+            Ps[k4 + 3][row] = v.w;
+        }
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = t + it * 128, row = idx & 63, k4 = (idx >> 6) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int gj = j0 + row, gk = k0 + k4;
+            if (gj < T) {
+                const float* src = Tl + (size_t)gj * D + gk;
+                if (vec && gk + 3 < D) {
+                    v = load4(src);
+                } else {
+                    if (gk + 0 < D) v.x = src[0];
+                    if (gk + 1 < D) v.y = src[1];
+                    if (gk + 2 < D) v.z = src[2];
+                    if (gk + 3 < D) v.w = src[3];
+                }
+            }
+            Ts[k4 + 0][row] = v.x;
+            Ts[k4 + 1][row] = v.y;
+            Ts[k4 + 2][row] = v.z;
+            Ts[k4 + 3][row] = v.w;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 pv = load4(&Ps[kk][ty * 4]);
+            const float4 tv = load4(&Ts[kk][tx * 4]);
+            const float pr[4] = {pv.x, pv.y, pv.z, pv.w};
+            const float tr[4] = {tv.x, tv.y, tv.z, tv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (FN == DIST_L1) {
+                        acc[a][b] += fabsf(pr[a] - tr[b]);
+                    } else if (FN == DIST_L2) {
+                        const float d = pr[a] - tr[b];
+                        acc[a][b] = fmaf(d, d, acc[a][b]);
+                    } else {
+                        acc[a][b] = fmaf(pr[a], tr[b], acc[a][b]);
+                    }
+                }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = i0 + ty * 4 + a;
+        if (i >= B) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int j = j0 + tx * 4 + b;
+            if (j < T) raw[(size_t)i * T + j] = FN == DIST_L2 ? sqrtf(acc[a][b]) : acc[a][b];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Loss forward and backward for one row of scores per block
+// (src/poplar_kge.cpp:615-660; guarded log-sigmoid src/pag/pag.cpp:888-910; log-softmax
+// backward :851-860).  Reads raw distances / dot products, writes
+//   loss_rows[i] = the row's un-normalised loss term, and
+//   coeff[i, j]  = loss_scale * dloss/draw_ij, already divided by the distance for L2
+//                  (0 where the distance is 0: l2distance.codelet.cpp:149-158),
+// which is the only thing the score backward needs.
+struct LossParams {
+    int loss_fn;
+    int score_fn;
+    int dist_fn;
+    int n_tail;
+    float gamma;
+    float softmax_shift;     // correction_weight * (log(n_entity*n_shard-1) - log(n_tail-1)), or 0
+    float adversarial_scale; // 0 = off
+    float w_pos, w_neg;      // log-sigmoid weights of the label / of the other columns
+    float grad_scale;        // loss_scale / normaliser
+};
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float* __restrict__ coeff,
+       float* __restrict__ loss_rows, LossParams lp) {
+    __shared__ float scratch[THREADS / 32];
+    const int i = blockIdx.x, T = lp.n_tail;
+    const float* __restrict__ r = raw + (size_t)i * T;
+    float* __restrict__ c = coeff + (size_t)i * T;
+    const int lab = (int)label[i];
+    const bool transe = lp.score_fn == SCORE_TRANSE;
+    auto score_of = [&](int j) { return transe ? lp.gamma - r[j] : r[j]; };
+    auto to_coeff = [&](int j, float g_score) {
+        float g = transe ? -g_score : g_score;  // d score / d raw
+        if (lp.dist_fn == DIST_L2) {
+            const float dist = r[j];
+            g = dist == 0.f ? 0.f : g / dist;
+        }
+        return g;
+    };
+    if (lp.loss_fn == LOSS_SOFTMAX) {
+        float mx = -INFINITY;
+        for (int j = threadIdx.x; j < T; j += THREADS)
+            mx = fmaxf(mx, score_of(j) + (j == lab ? 0.f : lp.softmax_shift));
+        mx = block_max<THREADS>(mx, scratch);
+        float sum = 0.f;
+        for (int j = threadIdx.x; j < T; j += THREADS)
+            sum += expf(score_of(j) + (j == lab ? 0.f : lp.softmax_shift) - mx);
+        sum = block_sum<THREADS>(sum, scratch);
+        const float log_z = logf(sum);
+        for (int j = threadIdx.x; j < T; j += THREADS) {
+            const float logp = score_of(j) + (j == lab ? 0.f : lp.softmax_shift) - mx - log_z;
+            const float g = lp.grad_scale * (expf(logp) - (j == lab ? 1.f : 0.f));
+            c[j] = to_coeff(j, g);
+            if (j == lab) loss_rows[i] = -logp;
+        }
+        return;
+    }
+    // log-sigmoid, optionally with self-adversarial weights from a detached softmax
+    float adv_max = 0.f, adv_sum = 1.f;
+    const bool adv = lp.adversarial_scale > 0.f;
+    if (adv) {
+        float mx = -INFINITY;
+        for (int j = threadIdx.x; j < T; j += THREADS)
+            mx = fmaxf(mx, lp.adversarial_scale * score_of(j) + (j == lab ? -10000.f : 0.f));
+        adv_max = block_max<THREADS>(mx, scratch);
+        float sum = 0.f;
+        for (int j = threadIdx.x; j < T; j += THREADS)
+            sum += expf(lp.adversarial_scale * score_of(j) + (j == lab ? -10000.f : 0.f) - adv_max);
+        adv_sum = block_sum<THREADS>(sum, scratch);
+    }
+    float part = 0.f;
+    for (int j = threadIdx.x; j < T; j += THREADS) {
+        const float s = score_of(j);
+        const bool pos = j == lab;
+        float w = pos ? lp.w_pos : lp.w_neg;
+        if (adv) {
+            const float soft =
+                expf(lp.adversarial_scale * s + (pos ? -10000.f : 0.f) - adv_max) / adv_sum;
+            w *= (pos ? 1.f : 0.f) + (float)(T - 1) * soft;
+        }
+        const float x = pos ? s : -s;
+        const float ls = x > -11.f ? -log1pf(expf(-fmaxf(x, -11.f))) : x;
+        part += w * ls;
+        const float dx = (-w * lp.grad_scale) / (1.f + expf(fminf(x, 11.f)));
+        c[j] = to_coeff(j, pos ? dx : -dx);
+    }
+    part = block_sum<THREADS>(part, scratch);
+    if (threadIdx.x == 0) loss_rows[i] = -part;
+}
+
+// Sums the rows' loss terms in a fixed order and adds the step's loss to the running total
+// of the program run (src/poplar_kge.cpp:735-736).
+static __global__ void __launch_bounds__(256)
+k_loss_finish(const float* __restrict__ loss_rows, int B, float inv_normaliser,
+              float* __restrict__ loss_total, float* __restrict__ loss_last) {
+    __shared__ float scratch[8];
+    float part = 0.f;
+    for (int i = threadIdx.x; i < B; i += 256) part += loss_rows[i];
+    part = block_sum<256>(part, scratch);
+    if (threadIdx.x == 0) {
+        const float step_loss = part * inv_normaliser;
+        *loss_total += step_loss;
+        *loss_last = step_loss;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Score backward: out[m, k] = sum_n C(m, n) * f(x[m, k], y[n, k]) with
+//   f = sign(x - y)  (L1, sign(0) = 0: l1distance.codelet.cpp:76-79,138-145)
+//   f = x - y        (L2; C already holds grad / dist)
+//   f = y            (dot: src/pag/pag.cpp:685-701)
+// Problem 0 is the gradient of the predicted tails (x = pred, y = tails, C = coeff);
+// problem 1 the gradient of the tails (x = tails, y = pred, C = coeff transposed), whose
+// rows go straight to the shard that owns them: the return half of the exchange
+// (src/pag/pag.cpp:925-932).  32 rows x 64 columns per block, n in slices of 32.
+struct PairBwdProblem {
+    const float* X;
+    const float* Y;
+    const float* C;
+    int M, N;
+    int c_stride_m, c_stride_n;
+    float* out;               // [M, D] when out_blocks is null
+    float* const* out_blocks; // per block of `block_rows` rows, the base pointer of that block
+    int block_rows;
+};
+struct PairBwdArgs {
+    PairBwdProblem p[2];
+    int D;
+    int tiles_m0;
+};
+
+template <int FN>
+__global__ void __launch_bounds__(128) k_pair_bwd(PairBwdArgs args) {
+    constexpr int BM = 32, BD = 64, BN = 32;
+    __shared__ float Cs[BM][BN + 1];
+    __shared__ __align__(16) float Ys[BN][BD];
+    const int which = (int)blockIdx.x >= args.tiles_m0 ? 1 : 0;
+    const PairBwdProblem& pr = args.p[which];
+    const int D = args.D;
+    const int m0 = ((int)blockIdx.x - (which ? args.tiles_m0 : 0)) * BM, d0 = blockIdx.y * BD;
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const bool vec = (D & 3) == 0;
+
+    float x[4][4], acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int m = m0 + ty * 4 + a;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int k = d0 + tx * 4 + b;
+            x[a][b] = (m < pr.M && k < D) ? pr.X[(size_t)m * D + k] : 0.f;
+            acc[a][b] = 0.f;
+        }
+    }
+    const bool n_fast = pr.c_stride_n == 1;
+    for (int n0 = 0; n0 < pr.N; n0 += BN) {
+        __syncthreads();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int idx = t + it * 128;
+            const int m = n_fast ? (idx >> 5) : (idx & 31);
+            const int n = n_fast ? (idx & 31) : (idx >> 5);
+            const int gm = m0 + m, gn = n0 + n;
+            float v = 0.f;
+            if (gm < pr.M && gn < pr.N)
+                v = pr.C[(size_t)gm * pr.c_stride_m + (size_t)gn * pr.c_stride_n];
+            Cs[m][n] = v;
+        }
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = t + it * 128, k4 = (idx & 15) * 4, n = idx >> 4;
+            const int gn = n0 + n, gk = d0 + k4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gn < pr.N) {
+                const float* src = pr.Y + (size_t)gn * D + gk;
+                if (vec && gk + 3 < D) {
+                    v = load4(src);
+                } else {
+                    if (gk + 0 < D) v.x = src[0];
+                    if (gk + 1 < D) v.y = src[1];
+                    if (gk + 2 < D) v.z = src[2];
+                    if (gk + 3 < D) v.w = src[3];
+                }
+            }
+            store4(&Ys[n][k4], v);
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int nn = 0; nn < BN; ++nn) {
+            const float4 yv = load4(&Ys[nn][tx * 4]);
+            const float yr[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float c = Cs[ty * 4 + a][nn];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (FN == DIST_L1) {
+                        const float d = x[a][b] - yr[b];
+                        acc[a][b] += d > 0.f ? c : (d < 0.f ? -c : 0.f);
+                    } else if (FN == DIST_L2) {
+                        acc[a][b] = fmaf(c, x[a][b] - yr[b], acc[a][b]);
+                    } else {
+                        acc[a][b] = fmaf(c, yr[b], acc[a][b]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int m = m0 + ty * 4 + a;
+        if (m >= pr.M) continue;
+        float* dst;
+        if (pr.out_blocks) {
+            const int blk = m / pr.block_rows;
+            dst = pr.out_blocks[blk] + (size_t)(m - blk * pr.block_rows) * D;
+        } else {
+            dst = pr.out + (size_t)m * D;
+        }
+        const int k = d0 + tx * 4;
+        if (vec && k + 3 < D) {
+            store4(dst + k, make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]));
+        } else {
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (k + b < D) dst[k + b] = acc[a][b];
+        }
+    }
+}
+
+// Gradients of the head vector and of the relation row for the multiplicative score
+// functions (backward of src/poplar_kge.cpp:501-510, 567-569).  TransE needs no kernel:
+// both gradients equal d_pred.
+static __global__ void __launch_bounds__(64)
+k_pred_bwd(const float* __restrict__ d_pred, const float* __restrict__ hid_h,
+           const uint32_t* __restrict__ head, const uint32_t* __restrict__ relation,
+           const float* __restrict__ rel_table, float* __restrict__ d_head,
+           float* __restrict__ d_relrow, int D, int score_fn) {
+    const int i = blockIdx.x;
+    const float* __restrict__ dp = d_pred + (size_t)i * D;
+    const float* __restrict__ h = hid_h + (size_t)head[i] * D;
+    const float* __restrict__ r = rel_table + (size_t)relation[i] * D;
+    float* __restrict__ dh = d_head + (size_t)i * D;
+    float* __restrict__ dr = d_relrow + (size_t)i * D;
+    if (score_fn == SCORE_DISTMULT) {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            dh[c] = dp[c] * r[c];
+            dr[c] = dp[c] * h[c];
+        }
+    } else {
+        const int half = D / 2;
+        for (int c = threadIdx.x; c < half; c += blockDim.x) {
+            const float hr = h[c], hi = h[c + half], rr = r[c], ri = r[c + half];
+            const float gr = dp[c], gi = dp[c + half];
+            dh[c] = gr * rr + gi * ri;
+            dh[c + half] = -gr * ri + gi * rr;
+            dr[c] = gr * hr + gi * hi;
+            dr[c + half] = -gr * hi + gi * hr;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Sort-and-segment preparation, once per staged step and shard: orders the B head
+// lookups and the T tail lookups by the hidden row they read (ties by position, so the
+// order is unique) and records where each row's segment starts; the same for the B
+// relation lookups.  The scatter-add of src/pag/pag.cpp:721-743 then becomes one
+// sequential sum per row in a fixed order: no float atomics.
+// One block per (shard-step); bitonic sort of (row << 32 | position) keys in shared memory.
+constexpr int kMaxSortItems = 4096;
+
+__device__ __forceinline__ void bitonic_sort(unsigned long long* keys, int padded) {
+    for (int k = 2; k <= padded; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long a = keys[i], b = keys[ixj];
+                    const bool ascending = (i & k) == 0;
+                    if ((a > b) == ascending) {
+                        keys[i] = b;
+                        keys[ixj] = a;
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int lower_bound_key(const unsigned long long* keys, int n,
+                                                unsigned long long target) {
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (keys[mid] < target) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+static __global__ void __launch_bounds__(512)
+k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict__ a2a_idx,
+                   const uint32_t* __restrict__ relation, const uint32_t* __restrict__ remote, int B,
+                   int T, int R, int n_rel, uint32_t* __restrict__ ent_perm,
+                   uint32_t* __restrict__ ent_off, uint32_t* __restrict__ rel_perm,
+                   uint32_t* __restrict__ rel_off, uint32_t* __restrict__ first_slot) {
+    __shared__ unsigned long long keys[kMaxSortItems];
+    const int s = blockIdx.x;
+    head += (size_t)s * B;
+    relation += (size_t)s * B;
+    a2a_idx += (size_t)s * T;
+    ent_perm += (size_t)s * (B + T);
+    ent_off += (size_t)s * (R + 1);
+    rel_perm += (size_t)s * B;
+    rel_off += (size_t)s * (n_rel + 1);
+
+    int n = B + T, padded = 1;
+    while (padded < n) padded <<= 1;
+    for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+        unsigned long long key = ~0ull;
+        if (i < B) key = ((unsigned long long)head[i] << 32) | (unsigned)i;
+        else if (i < n) key = ((unsigned long long)a2a_idx[i - B] << 32) | (unsigned)i;
+        keys[i] = key;
+    }
+    bitonic_sort(keys, padded);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ent_perm[i] = (uint32_t)keys[i];
+    for (int r = threadIdx.x; r <= R; r += blockDim.x)
+        ent_off[r] = (uint32_t)lower_bound_key(keys, n, (unsigned long long)r << 32);
+    __syncthreads();
+
+    n = B;
+    padded = 1;
+    while (padded < n) padded <<= 1;
+    for (int i = threadIdx.x; i < padded; i += blockDim.x)
+        keys[i] = i < n ? (((unsigned long long)relation[i] << 32) | (unsigned)i) : ~0ull;
+    bitonic_sort(keys, padded);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) rel_perm[i] = (uint32_t)keys[i];
+    for (int r = threadIdx.x; r <= n_rel; r += blockDim.x)
+        rel_off[r] = (uint32_t)lower_bound_key(keys, n, (unsigned long long)r << 32);
+    if (!remote) return;
+    __syncthreads();
+
+    // Which gathered slot is the first to name its table row: only that slot writes the row
+    // back.  `remote` is unique apart from the zero padding at its end, whose slots all name
+    // row 0; the reference computes every slot from the same gathered copy, so its duplicate
+    // writes are identical, and one write reproduces them.
+    remote += (size_t)s * R;
+    first_slot += (size_t)s * R;
+    n = R;
+    padded = 1;
+    while (padded < n) padded <<= 1;
+    for (int i = threadIdx.x; i < padded; i += blockDim.x)
+        keys[i] = i < n ? (((unsigned long long)remote[i] << 32) | (unsigned)i) : ~0ull;
+    bitonic_sort(keys, padded);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const bool first = i == 0 || (keys[i - 1] >> 32) != (keys[i] >> 32);
+        first_slot[(uint32_t)keys[i]] = first ? 1u : 0u;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Segment-sum of the lookup gradients into the hidden rows, fused with the row-wise Adam
+// update and the write-back (src/pag/pag.cpp:721-743; src/poplar_kge.cpp:695-704;
+// src/fructose/frnn.cpp:61-90).  One block per gathered row.  Every gathered row is
+// updated, rows with a zero gradient and the padding row included, as in the reference.
+// d_hid_h / d_hid_t keep the hidden-row gradients for the projection backward.
+template <class ST, int V>
+__global__ void __launch_bounds__(64)
+k_entity_update(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote,
+                const uint32_t* __restrict__ perm, const uint32_t* __restrict__ off,
+                const uint32_t* __restrict__ first_slot, const float* __restrict__ d_head,
+                const float* __restrict__ grad_recv, int B,
+                float* __restrict__ d_hid_h, float* __restrict__ d_hid_t,
+                const float* __restrict__ step_size, float lr_modifier, AdamParams ap) {
+    const int r = blockIdx.x, D = L.d;
+    const uint32_t q0 = off[r], q1 = off[r + 1];
+    const size_t row = remote[r];
+    ST* __restrict__ xv = reinterpret_cast<ST*>(table + row * L.row_bytes);
+    ST* __restrict__ mv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_m);
+    ST* __restrict__ qv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_q);
+    const float alpha = *step_size * lr_modifier;
+    const bool writes_row = first_slot[r] != 0;
+    for (int c = threadIdx.x * V; c < D; c += blockDim.x * V) {
+        float gh[V], gt[V];
+#pragma unroll
+        for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
+        for (uint32_t q = q0; q < q1; ++q) {
+            const uint32_t e = perm[q];
+            const bool is_head = e < (uint32_t)B;
+            const float* src = is_head ? d_head + (size_t)e * D + c : grad_recv + (size_t)(e - B) * D + c;
+            if (V == 4) {
+                const float4 g = load4(src);
+                if (is_head) { gh[0] += g.x; gh[1 % V] += g.y; gh[2 % V] += g.z; gh[3 % V] += g.w; }
+                else { gt[0] += g.x; gt[1 % V] += g.y; gt[2 % V] += g.z; gt[3 % V] += g.w; }
+            } else {
+                if (is_head) gh[0] += src[0]; else gt[0] += src[0];
+            }
+        }
+        const size_t o = (size_t)r * D + c;
+        if (V == 4) {
+            if (d_hid_t) {
+                store4(d_hid_h + o, make_float4(gh[0], gh[1 % V], gh[2 % V], gh[3 % V]));
+                store4(d_hid_t + o, make_float4(gt[0], gt[1 % V], gt[2 % V], gt[3 % V]));
+            } else {
+                store4(d_hid_h + o, make_float4(gh[0] + gt[0], gh[1 % V] + gt[1 % V], gh[2 % V] + gt[2 % V],
+                                                gh[3 % V] + gt[3 % V]));
+            }
+        } else {
+            d_hid_h[o] = d_hid_t ? gh[0] : gh[0] + gt[0];
+            if (d_hid_t) d_hid_t[o] = gt[0];
+        }
+        if (!writes_row) continue;
+        float x[V], m[V], qq[V];
+        if (V == 4) {
+            const float4 a = load4(xv + c), b = load4(mv + c), d = load4(qv + c);
+            x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
+            m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
+            qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
+        } else {
+            x[0] = load_as_float(xv + c); m[0] = load_as_float(mv + c); qq[0] = load_as_float(qv + c);
+        }
+#pragma unroll
+        for (int u = 0; u < V; ++u) {
+            const float g = gh[u] + gt[u];
+            float v = qq[u] * qq[u];
+            m[u] = ap.beta_m * m[u] + ap.one_minus_beta_m * g;
+            v = ap.beta_v * v + ap.one_minus_beta_v * g * g;
+            x[u] = x[u] - alpha * (m[u] / (sqrtf(v) + ap.epsilon) + ap.weight_decay * x[u]);
+            qq[u] = sqrtf(v);
+        }
+        if (V == 4) {
+            store4(xv + c, make_float4(x[0], x[1 % V], x[2 % V], x[3 % V]));
+            store4(mv + c, make_float4(m[0], m[1 % V], m[2 % V], m[3 % V]));
+            store4(qv + c, make_float4(qq[0], qq[1 % V], qq[2 % V], qq[3 % V]));
+        } else {
+            store_from_float(xv + c, x[0]);
+            store_from_float(mv + c, m[0]);
+            store_from_float(qv + c, qq[0]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Projection backward: dW[f, d] (+)= sum_r feature[remote[r], f] * d_hidden[r, d]
+// (src/pag/pag.cpp:695-700).  A = feature^T is read from the gathered table rows; the r
+// range is split over blockIdx.z and each split writes its own partial, summed later in
+// a fixed order.  Same 64x64x16 tiling as k_hidden.  gridDim.z = n_net * splits.
+template <class FT>
+__global__ void __launch_bounds__(256)
+k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote,
+                 int R, const float* __restrict__ dh0, const float* __restrict__ dh1, int splits,
+                 int rows_per_split, float* __restrict__ partial) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ __align__(16) float As[BK][BM];
+    __shared__ __align__(16) float Bs[BK][BN];
+    const int D = L.d, F = L.f;
+    const int net = blockIdx.z / splits, split = blockIdx.z - net * splits;
+    const float* __restrict__ dh = net ? dh1 : dh0;
+    float* __restrict__ out = partial + ((size_t)net * splits + split) * (size_t)F * D;
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int r_lo = split * rows_per_split, r_hi = min(R, r_lo + rows_per_split);
+    const int ld_k = t >> 4, ld_c = (t & 15) * 4;
+    const bool d_vec = (D & 3) == 0;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int r0 = r_lo; r0 < r_hi; r0 += BK) {
+        const int r = r0 + ld_k;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (r < r_hi) {
+            const size_t row = remote[r];
+            const FT* fp = reinterpret_cast<const FT*>(table + row * L.row_bytes + L.off_feat);
+            const int f = m0 + ld_c;
+            if (f + 3 < F) {
+                a = load4(fp + f);
+            } else {
+                if (f + 0 < F) a.x = load_as_float(fp + f + 0);
+                if (f + 1 < F) a.y = load_as_float(fp + f + 1);
+                if (f + 2 < F) a.z = load_as_float(fp + f + 2);
+            }
+            const int n = n0 + ld_c;
+            const float* gp = dh + (size_t)r * D + n;
+            if (d_vec && n + 3 < D) {
+                b = load4(gp);
+            } else {
+                if (n + 0 < D) b.x = gp[0];
+                if (n + 1 < D) b.y = gp[1];
+                if (n + 2 < D) b.z = gp[2];
+                if (n + 3 < D) b.w = gp[3];
+            }
+        }
+        __syncthreads();
+        store4(&As[ld_k][ld_c], a);
+        store4(&Bs[ld_k][ld_c], b);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 av = load4(&As[kk][ty * 4]);
+            const float4 bv = load4(&Bs[kk][tx * 4]);
+            const float ar[4] = {av.x, av.y, av.z, av.w};
+            const float br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int f = m0 + ty * 4 + i;
+        if (f >= F) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < D) out[(size_t)f * D + n] = acc[i][j];
+        }
+    }
+}
+
+// This shard's contribution to the dense gradients, laid out like the dense parameter
+// vector: relation table | projection(s).  Relation rows are the segment sums of the
+// per-triple relation gradients (backward of the gather at src/poplar_kge.cpp:489);
+// projection entries sum the split partials of k_projection_bwd in split order.
+static __global__ void __launch_bounds__(256)
+k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
+                const uint32_t* __restrict__ rel_off, int n_rel, int D,
+                const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
+                float* __restrict__ dense_partial) {
+    const size_t rel_elems = (size_t)n_rel * D;
+    const size_t total = rel_elems + (size_t)n_net * proj_elems;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (size_t)gridDim.x * blockDim.x) {
+        float g = 0.f;
+        if (e < rel_elems) {
+            const int rho = (int)(e / D), c = (int)(e - (size_t)rho * D);
+            for (uint32_t q = rel_off[rho]; q < rel_off[rho + 1]; ++q)
+                g += d_relrow[(size_t)rel_perm[q] * D + c];
+        } else {
+            const size_t pe = e - rel_elems;
+            const size_t net = pe / proj_elems, idx = pe - net * proj_elems;
+            for (int z = 0; z < splits; ++z) g += proj_partial[(net * splits + z) * proj_elems + idx];
+        }
+        dense_partial[e] = g;
+    }
+}
+
+// Sum of the shards' dense contributions in shard order (the reduce-scatter of
+// src/pag/pag.cpp:980-994), Adam on the slice of the dense vector this process owns
+// (src/poplar_kge.cpp:329-339) and the write of the new values into every replica
+// (the all-gather on next use, :341-348).  Pointer tables live in device memory; entries
+// may point into peers' memory.
+struct DenseUpdateArgs {
+    const float* const* partials;  // [n_partial]
+    int n_partial;
+    float* const* replicas;  // [n_replica] dense parameter vectors
+    int n_replica;
+    float* adam_m;
+    float* adam_v;
+    size_t lo, hi;          // owned element range
+    size_t bounds[4];       // parameter p covers [bounds[p], bounds[p+1])
+    float lr_modifier[3];
+    const float* step_size;
+    AdamParams ap;
+};
+
+static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, int self) {
+    const float base_alpha = *a.step_size;
+    for (size_t e = a.lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < a.hi;
+         e += (size_t)gridDim.x * blockDim.x) {
+        float g = 0.f;
+        for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][e];
+        const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
+        const float alpha = base_alpha * a.lr_modifier[p];
+        float x = a.replicas[self][e], m = a.adam_m[e], v = a.adam_v[e];
+        m = a.ap.beta_m * m + a.ap.one_minus_beta_m * g;
+        v = a.ap.beta_v * v + a.ap.one_minus_beta_v * g * g;
+        x = x - alpha * (m / (sqrtf(v) + a.ap.epsilon) + a.ap.weight_decay * x);
+        a.adam_m[e] = m;
+        a.adam_v[e] = v;
+        for (int rep = 0; rep < a.n_replica; ++rep) a.replicas[rep][e] = x;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Cross-process barrier on flags in peer-visible memory.  Thread r publishes this
+// process's new epoch into peer r's flag array, then waits until peer r's epoch has
+// reached it.  The wait is bounded: on expiry the kernel records an error and returns.
+struct BarrierArgs {
+    unsigned* const* peer_flags;  // [world] base of each process's flag array
+    unsigned* my_epoch;           // device counter, incremented once per barrier
+    unsigned* status;             // device error word: non-zero = a wait gave up
+    int rank, world;
+    unsigned long long max_spins;
+};
+
+static __global__ void k_barrier(BarrierArgs a) {
+    __shared__ unsigned epoch;
+    if (threadIdx.x == 0) {
+        epoch = *a.my_epoch + 1;
+        *a.my_epoch = epoch;
+        __threadfence_system();
+    }
+    __syncthreads();
+    const int r = threadIdx.x;
+    if (r >= a.world) return;
+    volatile unsigned* remote_flag = a.peer_flags[r] + a.rank;
+    __threadfence_system();
+    *remote_flag = epoch;
+    volatile unsigned* mine = a.peer_flags[a.rank] + r;
+    unsigned long long spins = 0;
+    while ((int)(*mine - epoch) < 0) {
+        if (++spins > a.max_spins) {
+            atomicExch(a.status, 1u + (unsigned)r);
+            break;
+        }
+        __nanosleep(64);
+    }
+    __threadfence_system();
+}
+
+// ---------------------------------------------------------------------------
+// Table I/O (src/poplar_kge.cpp:857-871).
+
+// Counter-based normal numbers (Philox-4x32-10 + Box-Muller), keyed by (seed, shard) and
+// counted by (row, column / 4): the initial embedding of a row depends only on its
+// address, not on which call wrote it.
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+    c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+}
+__device__ __forceinline__ float4 philox_normal4(uint32_t seed, uint32_t stream, uint32_t row,
+                                                 uint32_t col4) {
+    uint32_t c[4] = {row, col4, stream, 0x6b676562u};
+    uint32_t k0 = seed, k1 = 0x9E3779B9u ^ stream;
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        philox_round(c, k0, k1);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    const float u0 = ((float)(c[0] >> 8) + 0.5f) * (1.0f / 16777216.0f);
+    const float u1 = ((float)(c[1] >> 8) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = ((float)(c[2] >> 8) + 0.5f) * (1.0f / 16777216.0f);
+    const float u3 = ((float)(c[3] >> 8) + 0.5f) * (1.0f / 16777216.0f);
+    const float r0 = sqrtf(-2.f * logf(u0)), r1 = sqrtf(-2.f * logf(u2));
+    float s0, c0, s1, c1;
+    sincospif(2.f * u1, &s0, &c0);
+    sincospif(2.f * u3, &s1, &c1);
+    return make_float4(r0 * c0, r0 * s0, r1 * c1, r1 * s1);
+}
+
+// A slot writes only if no later slot names the same row, so duplicate indices (the
+// overflow slots that the host redirects to row 0, src/python/poplar_kge.py:546-552)
+// resolve to the last one in order, deterministically.
+__device__ __forceinline__ bool is_last_writer(const uint32_t* idx, int n, int j) {
+    const uint32_t mine = idx[j];
+    for (int k = j + 1; k < n; ++k)
+        if (idx[k] == mine) return false;
+    return true;
+}
+
+// write_entity: fresh embedding ~ N(0, std), zero moments, features from the host array.
+template <class ST, class FT, class IT>
+__global__ void __launch_bounds__(128)
+k_write_entity(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ idx, int n,
+               const IT* __restrict__ features, uint32_t seed, uint32_t shard, float stddev) {
+    const int j = blockIdx.x;
+    __shared__ int go;
+    if (threadIdx.x == 0) go = is_last_writer(idx, n, j) ? 1 : 0;
+    __syncthreads();
+    if (!go) return;
+    const size_t row = idx[j];
+    ST* xv = reinterpret_cast<ST*>(table + row * L.row_bytes);
+    ST* mv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_m);
+    ST* qv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_q);
+    FT* fv = reinterpret_cast<FT*>(table + row * L.row_bytes + L.off_feat);
+    const int D = L.d, F = L.f;
+    for (int c4 = threadIdx.x; c4 * 4 < D; c4 += blockDim.x) {
+        const float4 z = philox_normal4(seed, shard, (uint32_t)row, (uint32_t)c4);
+        const float zz[4] = {z.x, z.y, z.z, z.w};
+        for (int u = 0; u < 4 && c4 * 4 + u < D; ++u) {
+            store_from_float(xv + c4 * 4 + u, stddev * zz[u]);
+            store_from_float(mv + c4 * 4 + u, 0.f);
+            store_from_float(qv + c4 * 4 + u, 0.f);
+        }
+    }
+    for (int c = threadIdx.x; c < F; c += blockDim.x)
+        store_from_float(fv + c, load_as_float(features + (size_t)j * F + c));
+}
+
+// write_entity_rows: whole rows [value | m | sqrt(v) | feature] from the host array.
+template <class ST, class FT, class IT>
+__global__ void __launch_bounds__(128)
+k_write_rows(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ idx, int n,
+             const IT* __restrict__ data) {
+    const int j = blockIdx.x;
+    __shared__ int go;
+    if (threadIdx.x == 0) go = is_last_writer(idx, n, j) ? 1 : 0;
+    __syncthreads();
+    if (!go) return;
+    const size_t row = idx[j];
+    const int D = L.d, F = L.f, W = 3 * D + F;
+    const IT* __restrict__ src = data + (size_t)j * W;
+    uint8_t* base = table + row * L.row_bytes;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = load_as_float(src + c);
+        if (c < D) store_from_float(reinterpret_cast<ST*>(base) + c, v);
+        else if (c < 2 * D) store_from_float(reinterpret_cast<ST*>(base + L.off_m) + (c - D), v);
+        else if (c < 3 * D) store_from_float(reinterpret_cast<ST*>(base + L.off_q) + (c - 2 * D), v);
+        else store_from_float(reinterpret_cast<FT*>(base + L.off_feat) + (c - 3 * D), v);
+    }
+}
+
+// read_entity: whole rows out, in the host array's element type.
+template <class ST, class FT, class OT>
+__global__ void __launch_bounds__(128)
+k_read_rows(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ idx,
+            OT* __restrict__ out) {
+    const int j = blockIdx.x;
+    const size_t row = idx[j];
+    const int D = L.d, F = L.f, W = 3 * D + F;
+    const uint8_t* base = table + row * L.row_bytes;
+    OT* __restrict__ dst = out + (size_t)j * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float v;
+        if (c < D) v = load_as_float(reinterpret_cast<const ST*>(base) + c);
+        else if (c < 2 * D) v = load_as_float(reinterpret_cast<const ST*>(base + L.off_m) + (c - D));
+        else if (c < 3 * D) v = load_as_float(reinterpret_cast<const ST*>(base + L.off_q) + (c - 2 * D));
+        else v = load_as_float(reinterpret_cast<const FT*>(base + L.off_feat) + (c - 3 * D));
+        store_from_float(dst + c, v);
+    }
+}
+
+// Plain fp32 row gather with 128-bit accesses (the operator form of fr::Buffer::read,
+// src/fructose/fructose.cpp:790-798), used by the operator entry point and the microbench.
+template <int V>
+__global__ void __launch_bounds__(128)
+k_gather_rows(const float* __restrict__ table, size_t width, const uint32_t* __restrict__ idx,
+              float* __restrict__ out) {
+    const size_t j = blockIdx.x;
+    const float* __restrict__ src = table + (size_t)idx[j] * width;
+    float* __restrict__ dst = out + j * width;
+    if (V == 4) {
+        for (size_t c = threadIdx.x * 4; c < width; c += blockDim.x * 4) store4(dst + c, load4(src + c));
+    } else {
+        for (size_t c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+// Operator form of the duplicate-combining scatter-add: one block per table row, summing
+// the rows of its segment in position order.
+static __global__ void __launch_bounds__(128)
+k_segment_sum_rows(const float* __restrict__ rows, const uint32_t* __restrict__ perm,
+                   const uint32_t* __restrict__ off, size_t width, float* __restrict__ out) {
+    const size_t r = blockIdx.x;
+    for (size_t c = threadIdx.x; c < width; c += blockDim.x) {
+        float g = 0.f;
+        for (uint32_t q = off[r]; q < off[r + 1]; ++q) g += rows[(size_t)perm[q] * width + c];
+        out[r * width + c] = g;
+    }
+}
+
+// Operator forms of the two activations with their backward (src/pag/pag.cpp:841-864, 888-910).
+static __global__ void __launch_bounds__(256)
+k_log_sigmoid(const float* __restrict__ x, const float* __restrict__ grad_out, size_t n,
+              float* __restrict__ y, float* __restrict__ grad_x) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n;
+         e += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[e];
+        y[e] = v > -11.f ? -log1pf(expf(-fmaxf(v, -11.f))) : v;
+        grad_x[e] = grad_out[e] / (1.f + expf(fminf(v, 11.f)));
+    }
+}
+static __global__ void __launch_bounds__(256)
+k_log_softmax(const float* __restrict__ x, const float* __restrict__ grad_out, int cols,
+              float* __restrict__ y, float* __restrict__ grad_x) {
+    __shared__ float scratch[8];
+    const size_t base = (size_t)blockIdx.x * cols;
+    float mx = -INFINITY;
+    for (int j = threadIdx.x; j < cols; j += 256) mx = fmaxf(mx, x[base + j]);
+    mx = block_max<256>(mx, scratch);
+    float sum = 0.f, gsum = 0.f;
+    for (int j = threadIdx.x; j < cols; j += 256) {
+        sum += expf(x[base + j] - mx);
+        gsum += grad_out[base + j];
+    }
+    sum = block_sum<256>(sum, scratch);
+    gsum = block_sum<256>(gsum, scratch);
+    const float log_z = logf(sum);
+    for (int j = threadIdx.x; j < cols; j += 256) {
+        const float logp = x[base + j] - mx - log_z;
+        y[base + j] = logp;
+        grad_x[base + j] = grad_out[base + j] - gsum * expf(logp);
+    }
+}
+
+}  // namespace kge

@@ -1,0 +1,496 @@
+"""numpy restatement of the reference's sharded KGE training step and predict.
+
+TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).  Every function names the
+reference lines it restates; paths are relative to the reference project root.
+
+All shards are evaluated in one process with a leading ``[n_shard]`` axis, which
+is exactly how the reference presents them to its host API
+(src/poplar_kge.cpp:874-877).  The compute dtype is a parameter: ``float64`` is
+the ground truth the CUDA path is compared with, ``float32`` reproduces the
+reference's arithmetic width.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+
+# ---------------------------------------------------------------------------
+# Configuration (the keys the engine reads: src/poplar_kge.cpp:198-246)
+
+
+@dataclasses.dataclass
+class StepConfig:
+    n_shard: int
+    n_entity: int  # rows per shard, including the padding row 0
+    n_relation_type: int
+    embedding_size: int
+    entity_feature_size: int
+    batch_size: int  # positives per shard
+    a2a_size: int  # tails sent to each peer
+    score_fn: str = "TransE"  # TransE | DistMult | ComplEx
+    distance_fn: str = "L1"  # L1 | L2 | MatMul
+    gamma: float = 10.0
+    loss_type: str = "logsigmoid"  # logsigmoid | softmax
+    correction_weight: float = 0.0
+    negative_adversarial_scale: float = 0.0
+    share_feature_networks: bool = True
+    adam_beta_m: float = 0.9
+    adam_beta_v: float = 0.999
+    adam_epsilon: float = 1e-8
+    weight_decay: float = 0.0
+    loss_scale: Optional[float] = None
+    learning_rate_modifiers: Dict[str, float] = dataclasses.field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.loss_scale is None:
+            # src/python/poplar_kge.py:259-262
+            self.loss_scale = float(self.batch_size * self.n_shard * self.a2a_size)
+
+    @property
+    def n_tail(self) -> int:  # src/python/poplar_kge.py:197-199
+        return self.n_shard * self.a2a_size
+
+    @property
+    def n_remote(self) -> int:  # src/python/poplar_kge.py:201-203
+        return self.batch_size + self.n_tail
+
+    @property
+    def row_size(self) -> int:  # src/poplar_kge.cpp:274-275
+        return 3 * self.embedding_size + self.entity_feature_size
+
+    @property
+    def projection_names(self) -> Tuple[str, ...]:  # src/poplar_kge.cpp:268-273
+        if self.share_feature_networks:
+            return ("feature_projection",)
+        return ("head_feature_projection", "tail_feature_projection")
+
+
+# ---------------------------------------------------------------------------
+# Elementary ops, each with the backward the reference's tape would replay
+
+
+def l1_distance(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """out[i, j] = sum_k abs(a[i, k] - b[j, k]).
+
+    src/poplar_extensions/l1distance.codelet.cpp:49-56 (portable ``l1dist``).
+    """
+    out = np.empty((a.shape[0], b.shape[0]), dtype=a.dtype)
+    for lo in range(0, a.shape[0], 64):
+        out[lo : lo + 64] = np.abs(a[lo : lo + 64, None, :] - b[None, :, :]).sum(-1)
+    return out
+
+
+def l1_distance_grad(a: np.ndarray, b: np.ndarray, grad_out: np.ndarray) -> np.ndarray:
+    """grad_a[i, k] = sum_j grad_out[i, j] * sign(a[i, k] - b[j, k]), sign(0) = 0.
+
+    src/poplar_extensions/l1distance.codelet.cpp:76-79,138-145 (``signum``,
+    ``l1distgrad``).  The gradient for ``b`` is the same function with the
+    arguments swapped and ``grad_out`` transposed (src/pag/pag.cpp:791-803).
+    """
+    out = np.empty_like(a)
+    for lo in range(0, a.shape[0], 64):
+        sgn = np.sign(a[lo : lo + 64, None, :] - b[None, :, :])
+        out[lo : lo + 64] = np.einsum("ij,ijk->ik", grad_out[lo : lo + 64], sgn)
+    return out
+
+
+def l2_distance(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """out[i, j] = sqrt(sum_k (a[i, k] - b[j, k])^2): a true Euclidean distance.
+
+    src/poplar_extensions/l2distance.codelet.cpp:54-62 (portable ``l2dist``).
+    """
+    out = np.empty((a.shape[0], b.shape[0]), dtype=a.dtype)
+    for lo in range(0, a.shape[0], 64):
+        diff = a[lo : lo + 64, None, :] - b[None, :, :]
+        out[lo : lo + 64] = np.sqrt((diff * diff).sum(-1))
+    return out
+
+
+def l2_distance_grad(
+    a: np.ndarray, b: np.ndarray, dist: np.ndarray, grad_out: np.ndarray
+) -> np.ndarray:
+    """grad_a[i, k] = sum_j grad_out[i, j] * (a[i, k] - b[j, k]) / dist[i, j], 0 where dist is 0.
+
+    src/poplar_extensions/l2distance.codelet.cpp:149-158 (portable ``l2distgrad``).
+    """
+    with np.errstate(divide="ignore", invalid="ignore"):
+        coeff = np.where(dist == 0, 0, grad_out / np.where(dist == 0, 1, dist))
+    out = np.empty_like(a)
+    for lo in range(0, a.shape[0], 64):
+        diff = a[lo : lo + 64, None, :] - b[None, :, :]
+        out[lo : lo + 64] = np.einsum("ij,ijk->ik", coeff[lo : lo + 64], diff)
+    return out
+
+
+def log_sigmoid(x: np.ndarray) -> np.ndarray:
+    """Guarded log-sigmoid: ``x`` itself at or below -11, else -log1p(exp(-x)).
+
+    src/pag/pag.cpp:893-896.
+    """
+    return np.where(x > -11, -np.log1p(np.exp(-np.maximum(x, -11))), x)
+
+
+def log_sigmoid_grad(x: np.ndarray, grad_out: np.ndarray) -> np.ndarray:
+    """grad_out / (1 + exp(min(x, 11))).  src/pag/pag.cpp:901-904."""
+    return grad_out / (1 + np.exp(np.minimum(x, 11)))
+
+
+def log_softmax(x: np.ndarray) -> np.ndarray:
+    """Row-wise stable log-softmax (popnn::logSoftmax, src/pag/pag.cpp:846-848)."""
+    shifted = x - x.max(axis=-1, keepdims=True)
+    return shifted - np.log(np.exp(shifted).sum(axis=-1, keepdims=True))
+
+
+def log_softmax_grad(logp: np.ndarray, grad_out: np.ndarray) -> np.ndarray:
+    """grad_out - sum(grad_out) * exp(logp).  src/pag/pag.cpp:851-860."""
+    return grad_out - grad_out.sum(axis=-1, keepdims=True) * np.exp(logp)
+
+
+def scatter_add_rows(n_rows: int, indices: np.ndarray, rows: np.ndarray) -> np.ndarray:
+    """Dense zero table with ``rows`` added at ``indices`` (duplicates accumulate).
+
+    The backward of a row gather: src/pag/pag.cpp:721-743 (``multiUpdateAdd``).
+    """
+    out = np.zeros((n_rows,) + rows.shape[1:], dtype=rows.dtype)
+    np.add.at(out, indices, rows)
+    return out
+
+
+def all_to_all(blocks: np.ndarray) -> np.ndarray:
+    """out[dst, src] = blocks[src, dst] on the stacked shard axis.
+
+    src/pag/pag.cpp:915-935; the backward is the same exchange applied to the
+    gradient (:925-932).
+    """
+    return np.swapaxes(blocks, 0, 1)
+
+
+def adam_step_size(step: int, lr, beta_m: float, beta_v: float, dtype) -> np.ndarray:
+    """lr * sqrt(1 - beta_v^t) / (1 - beta_m^t) with ``t`` already incremented.
+
+    src/fructose/frnn.cpp:42-59.
+    """
+    t = dtype(step)
+    return (np.sqrt(1 - dtype(beta_v) ** t) / (1 - dtype(beta_m) ** t)) * dtype(lr)
+
+
+def adam_update(x, m, v, grad, step_size, cfg: StepConfig):
+    """In-place Adam in the reference's form (epsilon outside the bias correction,
+    decoupled weight decay).  src/fructose/frnn.cpp:61-90.
+    """
+    dt = x.dtype.type
+    m *= dt(cfg.adam_beta_m)
+    m += dt(1 - cfg.adam_beta_m) * grad
+    v *= dt(cfg.adam_beta_v)
+    v += dt(1 - cfg.adam_beta_v) * grad * grad
+    x -= step_size * (m / (np.sqrt(v) + dt(cfg.adam_epsilon)) + dt(cfg.weight_decay) * x)
+
+
+# ---------------------------------------------------------------------------
+# Score functions (src/poplar_kge.cpp:488-613)
+
+
+def predict_tail(cfg: StepConfig, h: np.ndarray, r: np.ndarray) -> np.ndarray:
+    if cfg.score_fn == "TransE":  # :488-490
+        return h + r
+    if cfg.score_fn == "DistMult":  # :567-569
+        return h * r
+    if cfg.score_fn == "ComplEx":  # :501-510 (first half real, second half imaginary)
+        half = h.shape[-1] // 2
+        hr, hi, rr, ri = h[..., :half], h[..., half:], r[..., :half], r[..., half:]
+        return np.concatenate([hr * rr - hi * ri, hr * ri + hi * rr], axis=-1)
+    raise ValueError(f"score_fn {cfg.score_fn!r} is not covered by the oracle")
+
+
+def predict_tail_grad(cfg: StepConfig, h, r, dp) -> Tuple[np.ndarray, np.ndarray]:
+    if cfg.score_fn == "TransE":
+        return dp, dp
+    if cfg.score_fn == "DistMult":
+        return dp * r, dp * h
+    if cfg.score_fn == "ComplEx":
+        half = h.shape[-1] // 2
+        hr, hi, rr, ri = h[..., :half], h[..., half:], r[..., :half], r[..., half:]
+        dpr, dpi = dp[..., :half], dp[..., half:]
+        dh = np.concatenate([dpr * rr + dpi * ri, -dpr * ri + dpi * rr], axis=-1)
+        dr = np.concatenate([dpr * hr + dpi * hi, -dpr * hi + dpi * hr], axis=-1)
+        return dh, dr
+    raise ValueError(cfg.score_fn)
+
+
+def _distance(cfg: StepConfig, a, b):  # src/poplar_kge.cpp:469-486
+    if cfg.distance_fn in ("L1", "L1_old"):
+        return l1_distance(a, b)
+    if cfg.distance_fn in ("L2", "L2_old"):
+        return l2_distance(a, b)
+    if cfg.distance_fn == "MatMul":
+        return a @ b.T
+    raise ValueError(f"distance_fn {cfg.distance_fn!r}")
+
+
+def _distance_grad(cfg: StepConfig, a, b, dist, g):
+    if cfg.distance_fn in ("L1", "L1_old"):
+        return l1_distance_grad(a, b, g), l1_distance_grad(b, a, g.T)
+    if cfg.distance_fn in ("L2", "L2_old"):
+        return l2_distance_grad(a, b, dist, g), l2_distance_grad(b, a, dist.T, g.T)
+    return g @ b, g.T @ a  # src/pag/pag.cpp:685-701
+
+
+def score(cfg: StepConfig, p: np.ndarray, tails: np.ndarray):
+    """Scores [B, T] and the raw distance the backward needs.
+
+    TransE: gamma - distance (:492-499).  DistMult / ComplEx: distance(p, tails)
+    as is (:512-514, :571-573), normally with distance_fn "MatMul".
+    """
+    dist = _distance(cfg, p, tails)
+    if cfg.score_fn == "TransE":
+        return p.dtype.type(cfg.gamma) - dist, dist
+    return dist, dist
+
+
+def score_grad(cfg: StepConfig, p, tails, dist, g):
+    if cfg.score_fn == "TransE":
+        g = -g
+    return _distance_grad(cfg, p, tails, dist, g)
+
+
+# ---------------------------------------------------------------------------
+# Losses (src/poplar_kge.cpp:615-660).  Each returns (loss, dloss/dscores).
+
+
+def loss_logsigmoid(cfg: StepConfig, scores: np.ndarray, labels: np.ndarray):
+    dt = scores.dtype.type
+    n_tail = cfg.n_tail
+    onehot = np.zeros_like(scores)
+    onehot[np.arange(scores.shape[0]), labels] = 1
+    w_neg = dt((0.5 * n_tail) / (n_tail - 1))
+    w_pos = dt(0.5 * n_tail)
+    weight = (w_pos - w_neg) * onehot + w_neg
+    if cfg.negative_adversarial_scale > 0:  # :623-633, softmax is detached
+        z = dt(cfg.negative_adversarial_scale) * scores + dt(-10000.0) * onehot
+        z = z - z.max(axis=-1, keepdims=True)
+        soft = np.exp(z)
+        soft /= soft.sum(axis=-1, keepdims=True)
+        weight = weight * (onehot + dt(n_tail - 1) * soft)
+    mask = 2 * onehot - 1
+    denom = dt(cfg.n_shard * cfg.batch_size * cfg.a2a_size * cfg.n_shard)
+    x = mask * scores
+    loss = -(weight * log_sigmoid(x)).sum() / denom
+    dscores = mask * log_sigmoid_grad(x, -weight / denom)
+    return loss, dscores
+
+
+def softmax_correction(cfg: StepConfig) -> float:
+    """log(n_entity * n_shard - 1) - log(n_shard * a2a - 1), rounded to float32 (:644)."""
+    return float(
+        np.float32(
+            np.log(float(cfg.n_entity * cfg.n_shard - 1)) - np.log(float(cfg.n_tail - 1))
+        )
+    )
+
+
+def loss_softmax(cfg: StepConfig, scores: np.ndarray, labels: np.ndarray):
+    dt = scores.dtype.type
+    onehot = np.zeros_like(scores)
+    onehot[np.arange(scores.shape[0]), labels] = 1
+    corrected = scores
+    if cfg.correction_weight:
+        shift = dt(np.float32(cfg.correction_weight) * np.float32(softmax_correction(cfg)))
+        corrected = scores + shift * (1 - onehot)
+    logp = log_softmax(corrected)
+    denom = dt(cfg.n_shard * cfg.batch_size)
+    loss = -(logp * onehot).sum() / denom  # src/fructose/frnn.cpp:18-23
+    dscores = log_softmax_grad(logp, -onehot / denom)
+    return loss, dscores
+
+
+def loss_and_grad(cfg: StepConfig, scores, labels):
+    if cfg.loss_type == "logsigmoid":
+        return loss_logsigmoid(cfg, scores, labels)
+    if cfg.loss_type == "softmax":
+        return loss_softmax(cfg, scores, labels)
+    raise ValueError(f"loss type {cfg.loss_type!r}")
+
+
+# ---------------------------------------------------------------------------
+# The model state and the step
+
+
+class Oracle:
+    """State + ``train_step`` / ``train_step_loop`` / ``predict``.
+
+    ``entity_data`` is the stacked table ``[n_shard, n_entity, 3D+F]`` with row
+    layout value | adam_m | sqrt(adam_v) | feature (src/poplar_kge.cpp:405-417).
+    Dense parameters are held once (they are replicated across shards in effect:
+    slices are all-gathered on every use and gradients reduce-scattered,
+    src/poplar_kge.cpp:341-348, src/pag/pag.cpp:980-994).
+    """
+
+    def __init__(self, cfg: StepConfig, dtype=np.float64):
+        self.cfg = cfg
+        self.dtype = np.dtype(dtype).type
+        d, f = cfg.embedding_size, cfg.entity_feature_size
+        self.entity_data = np.zeros((cfg.n_shard, cfg.n_entity, cfg.row_size), dtype)
+        self.variables: Dict[str, np.ndarray] = {}
+        shapes = {"relation_embedding": (cfg.n_relation_type, d)}
+        for name in cfg.projection_names:
+            shapes[name] = (f, d)
+        for name, shape in shapes.items():
+            for suffix in ("", "/adam_m", "/adam_v"):
+                self.variables[name + suffix] = np.zeros(shape, dtype)
+        self.step = 0
+        self.last = {}  # intermediates of the most recent step, for kernel-level checks
+
+    # -- state I/O ---------------------------------------------------------
+
+    def set_state(self, state: Dict[str, np.ndarray]) -> None:
+        for key, value in state.items():
+            if key == "entity_data":
+                self.entity_data[...] = value
+            elif key == "step":
+                (self.step,) = {int(s) for s in np.atleast_1d(value)}
+            else:
+                self.variables[key][...] = value
+
+    def get_state(self) -> Dict[str, np.ndarray]:
+        out = {k: v.copy() for k, v in self.variables.items()}
+        out["entity_data"] = self.entity_data.copy()
+        out["step"] = np.full(self.cfg.n_shard, self.step, np.uint32)
+        return out
+
+    # -- training ----------------------------------------------------------
+
+    def _projection(self, part: str) -> str:
+        if self.cfg.share_feature_networks:
+            return "feature_projection"
+        return f"{part}_feature_projection"
+
+    def train_step(self, lr: float, remote, a2a, head, relation, tail) -> np.ndarray:
+        """One step of src/poplar_kge.cpp:664-707 for every shard; returns loss[n_shard]."""
+        cfg, dt = self.cfg, self.dtype
+        n, d = cfg.n_shard, cfg.embedding_size
+        remote, a2a, head, relation, tail = (
+            np.asarray(x).astype(np.int64) for x in (remote, a2a, head, relation, tail)
+        )
+        rel = self.variables["relation_embedding"]
+        w_head = self.variables[self._projection("head")]
+        w_tail = self.variables[self._projection("tail")]
+
+        # 1. gather rows (:671, :405-410)
+        rows = np.stack([self.entity_data[s, remote[s]] for s in range(n)])
+        value, adam_m, sqrt_v, feat = (
+            rows[..., :d],
+            rows[..., d : 2 * d].copy(),
+            rows[..., 2 * d : 3 * d],
+            rows[..., 3 * d :],
+        )
+        value = value.copy()
+        # 2. hidden, lookups, exchange (:676-681, :439-467)
+        hid_h = value + feat @ w_head
+        hid_t = hid_h if cfg.share_feature_networks else value + feat @ w_tail
+        heads = np.stack([hid_h[s, head[s]] for s in range(n)])
+        send = np.stack([hid_t[s, a2a[s]] for s in range(n)])  # [src, dst, a2a, D]
+        tails = all_to_all(send).reshape(n, cfg.n_tail, d)  # [dst, src*a2a, D]
+        # 3./4. scores and loss (:684-688)
+        losses = np.zeros(n, self.entity_data.dtype)
+        d_hid_h = np.zeros_like(hid_h)
+        d_tails = np.zeros_like(tails)
+        d_rel = np.zeros_like(rel)
+        keep = {"hidden": hid_h, "tails": tails, "scores": [], "dscores": [], "pred": []}
+        for s in range(n):
+            r = rel[relation[s]]
+            pred = predict_tail(cfg, heads[s], r)
+            scores, dist = score(cfg, pred, tails[s])
+            losses[s], dscores = loss_and_grad(cfg, scores, tail[s])
+            dscores = dscores * dt(cfg.loss_scale)  # root gradient, never unscaled (:691)
+            d_pred, d_tails[s] = score_grad(cfg, pred, tails[s], dist, dscores)
+            d_head, d_r = predict_tail_grad(cfg, heads[s], r, d_pred)
+            d_rel += scatter_add_rows(rel.shape[0], relation[s], d_r)
+            d_hid_h[s] = scatter_add_rows(cfg.n_remote, head[s], d_head)
+            keep["scores"].append(scores)
+            keep["dscores"].append(dscores)
+            keep["pred"].append(pred)
+        # 5. exchange backward, lookups backward, projection backward
+        d_send = all_to_all(d_tails.reshape(n, n, cfg.a2a_size, d))  # [src, dst, a2a, D]
+        d_hid_t = np.stack(
+            [
+                scatter_add_rows(cfg.n_remote, a2a[s].reshape(-1), d_send[s].reshape(-1, d))
+                for s in range(n)
+            ]
+        )
+        d_value = d_hid_h + d_hid_t
+        grads = {"relation_embedding": d_rel}
+        if cfg.share_feature_networks:
+            grads["feature_projection"] = np.einsum("srf,srd->fd", feat, d_value)
+        else:
+            grads["head_feature_projection"] = np.einsum("srf,srd->fd", feat, d_hid_h)
+            grads["tail_feature_projection"] = np.einsum("srf,srd->fd", feat, d_hid_t)
+        keep.update(d_value=d_value, grads=grads, d_tails=d_tails)
+        self.last = keep
+        # update (:692-704)
+        self.step += 1
+        alpha = adam_step_size(self.step, lr, cfg.adam_beta_m, cfg.adam_beta_v, dt)
+        for name, grad in grads.items():
+            mod = dt(cfg.learning_rate_modifiers.get(name, 1.0))
+            adam_update(
+                self.variables[name],
+                self.variables[name + "/adam_m"],
+                self.variables[name + "/adam_v"],
+                grad,
+                alpha * mod,
+                cfg,
+            )
+        adam_v = sqrt_v * sqrt_v
+        mod = dt(cfg.learning_rate_modifiers.get("entity_embedding", 1.0))
+        adam_update(value, adam_m, adam_v, d_value, alpha * mod, cfg)
+        new_rows = np.concatenate([value, adam_m, np.sqrt(adam_v), feat], axis=-1)
+        for s in range(n):
+            self.entity_data[s, remote[s]] = new_rows[s]
+        return losses
+
+    def train_step_loop(self, lr: float, batch: Dict[str, np.ndarray]) -> np.ndarray:
+        """Mean loss per shard over the steps of one program run (:709-741).
+
+        ``batch`` arrays carry axes ``[n_shard, n_step, ...]``.
+        """
+        n_step = batch["remote"].shape[1]
+        total = np.zeros(self.cfg.n_shard, self.entity_data.dtype)
+        for i in range(n_step):
+            total += self.train_step(
+                lr, *(batch[k][:, i] for k in ("remote", "a2a", "head", "relation", "tail"))
+            )
+        return total / self.dtype(n_step)
+
+    # -- inference ---------------------------------------------------------
+
+    def hidden_all(self, part: str) -> np.ndarray:
+        d = self.cfg.embedding_size
+        w = self.variables[self._projection(part)]
+        return self.entity_data[..., :d] + self.entity_data[..., 3 * d :] @ w
+
+    def predict(self, shard_idx_relation: np.ndarray, shard_to_count: np.ndarray, n_best: int):
+        """Brute-force ranking of every real entity for (head shard, head index, relation)
+        queries; ties broken by ascending (shard, index).
+
+        Scores follow src/poplar_kge.cpp:812-855; the reference leaves the tie
+        order undefined, so the id rule is this project's own.
+        Returns (shard_idx [q, n_best, 2] uint32, score [q, n_best]).
+        """
+        cfg = self.cfg
+        q = np.asarray(shard_idx_relation).astype(np.int64)
+        hid_h = self.hidden_all("head")
+        hid_t = self.hidden_all("tail").reshape(-1, cfg.embedding_size)
+        pred = predict_tail(
+            cfg, hid_h[q[:, 0], q[:, 1]], self.variables["relation_embedding"][q[:, 2]]
+        )
+        scores, _ = score(cfg, pred, hid_t)
+        valid = np.zeros((cfg.n_shard, cfg.n_entity), bool)
+        for s, count in enumerate(shard_to_count):
+            valid[s, 1 : 1 + int(count)] = True
+        scores = np.where(valid.reshape(1, -1), scores, -np.inf)
+        order = np.argsort(-scores, axis=1, kind="stable")[:, :n_best]
+        best = np.take_along_axis(scores, order, axis=1)
+        shard_idx = np.stack(np.divmod(order, cfg.n_entity), axis=-1).astype(np.uint32)
+        return shard_idx, best

@@ -1,0 +1,166 @@
+"""Shared pieces of the tests: settings for both sides, seeded state and batches."""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import numpy as np
+
+from oracle.step_oracle import Oracle, StepConfig
+
+BATCH_KEYS = ("remote", "a2a", "head", "relation", "tail")
+
+
+def engine_settings(cfg: StepConfig, n_step: int = 1, dtype: str = "float32",
+                    feature_dtype: Optional[str] = None, rw_batch: int = 64, cuda_graph: bool = True,
+                    seed: int = 1, **extra) -> Dict[str, object]:
+    """The flattened settings dictionary the engine reads, from an oracle configuration."""
+    s = {
+        "model.seed": seed, "model.score_fn": cfg.score_fn, "model.distance_fn": cfg.distance_fn,
+        "model.n_shard": cfg.n_shard, "model.n_entity": cfg.n_entity,
+        "model.n_relation_type": cfg.n_relation_type, "model.embedding_size": cfg.embedding_size,
+        "model.entity_feature_size": cfg.entity_feature_size, "model.feature_mlp_size": 0,
+        "model.feature_dropout": 0.0, "model.share_feature_networks": cfg.share_feature_networks,
+        "model.gamma": float(cfg.gamma), "model.init_scale": 1.0,
+        "model.negative_adversarial_scale": float(cfg.negative_adversarial_scale),
+        "training.adam_beta_m": cfg.adam_beta_m, "training.adam_beta_v": cfg.adam_beta_v,
+        "training.adam_epsilon": cfg.adam_epsilon, "training.weight_decay": float(cfg.weight_decay),
+        "training.learning_rate_modifiers": dict(cfg.learning_rate_modifiers),
+        "data.batch_size": cfg.batch_size, "data.a2a_size": cfg.a2a_size,
+        "training.loss.type": cfg.loss_type, "training.loss_scale": float(cfg.loss_scale),
+        "training.embedding_regularisation.power": 3.0, "training.embedding_regularisation.weight": 0.0,
+        "training.feature_regularisation.power": 3.0, "training.feature_regularisation.weight": 0.0,
+        "training.hidden_regularisation.power": 3.0, "training.hidden_regularisation.weight": 0.0,
+        "execution.device": "cuda", "execution.dtype": dtype,
+        "execution.train_steps_per_program_run": n_step, "execution.rw_batch_size": rw_batch,
+        "execution.predict_hr_batch_size": 8, "execution.predict_tail_batch_size": 64,
+        "execution.predict_n_best": 5, "execution.cuda_graph": cuda_graph,
+    }
+    if cfg.loss_type == "softmax":
+        s["training.loss.correction_weight"] = float(cfg.correction_weight)
+    if feature_dtype is not None:
+        s["execution.feature_dtype"] = feature_dtype
+    s.update(extra)
+    return s
+
+
+def random_state(cfg: StepConfig, seed: int, fp16_features: bool = False, warm: bool = False):
+    """Seeded initial state in float32: embeddings ~ N(0, 1/sqrt(d)), small dense parameters.
+
+    ``warm`` also fills the optimiser state (as after some training), which exercises the
+    sqrt(v) storage and the momentum terms instead of Adam's sign-like first step."""
+    rng = np.random.RandomState(seed)
+    d, f = cfg.embedding_size, cfg.entity_feature_size
+    rows = np.zeros((cfg.n_shard, cfg.n_entity, cfg.row_size), np.float32)
+    rows[..., :d] = rng.normal(size=rows[..., :d].shape) / np.sqrt(d)
+    if f:
+        feat = rng.normal(size=(cfg.n_shard, cfg.n_entity, f))
+        if fp16_features:
+            feat = feat.astype(np.float16)
+        rows[..., 3 * d :] = feat.astype(np.float32)
+        rows[:, 0, 3 * d :] = 0
+    state = {"entity_data": rows, "step": np.zeros(cfg.n_shard, np.uint32)}
+    state["relation_embedding"] = (rng.normal(size=(cfg.n_relation_type, d)) / np.sqrt(d)).astype(np.float32)
+    for name in cfg.projection_names:
+        state[name] = (rng.normal(size=(f, d)) / np.sqrt(max(f, 1)) / np.sqrt(d)).astype(np.float32)
+    for name in ("relation_embedding",) + cfg.projection_names:
+        state[name + "/adam_m"] = np.zeros_like(state[name])
+        state[name + "/adam_v"] = np.zeros_like(state[name])
+    if warm:
+        scale = float(cfg.loss_scale) * 1e-3
+        rows[..., d : 2 * d] = scale * rng.normal(size=rows[..., :d].shape)
+        rows[..., 2 * d : 3 * d] = np.abs(scale * rng.normal(size=rows[..., :d].shape)) + 0.1 * scale
+        for name in ("relation_embedding",) + cfg.projection_names:
+            state[name + "/adam_m"] = (scale * rng.normal(size=state[name].shape)).astype(np.float32)
+            state[name + "/adam_v"] = ((scale * rng.normal(size=state[name].shape)) ** 2 + (0.1 * scale) ** 2).astype(np.float32)
+        state["step"][:] = 37
+    return state
+
+
+def random_batch(cfg: StepConfig, n_step: int, seed: int, fixed_remote: bool = False,
+                 pad: int = 0) -> Dict[str, np.ndarray]:
+    """Index streams under the stream contract: ``remote`` rows unique, sorted, non-zero, then
+    ``pad`` zeros (as the sampler's unique_pad leaves them); lookups avoid the padded slots."""
+    rng = np.random.RandomState(seed)
+    n, R = cfg.n_shard, cfg.n_remote
+    used = R - pad
+    remote = np.zeros((n, n_step, R), np.uint32)
+    for s in range(n):
+        for i in range(n_step):
+            remote[s, i, :used] = np.sort(rng.permutation(np.arange(1, cfg.n_entity))[:used])
+    if fixed_remote:
+        remote[...] = remote[:, :1]
+    u32 = lambda hi, shape: rng.randint(hi, size=shape).astype(np.uint32)  # noqa: E731
+    return dict(remote=remote, a2a=u32(used, (n, n_step, n, cfg.a2a_size)),
+                head=u32(used, (n, n_step, cfg.batch_size)),
+                relation=u32(cfg.n_relation_type, (n, n_step, cfg.batch_size)),
+                tail=u32(cfg.n_tail, (n, n_step, cfg.batch_size)))
+
+
+def write_state(engine, cfg: StepConfig, state: Dict[str, np.ndarray], rw_batch: int,
+                dtype=np.float32, shards: slice = slice(None)) -> None:
+    """Load a state dictionary into a capi.CEngine through "write" and "write_entity_rows"."""
+    for name, value in state.items():
+        if name == "entity_data":
+            continue
+        engine.run("write", {"value": np.ascontiguousarray(value)}, name=name)
+    rows = state["entity_data"][shards]
+    n_local = rows.shape[0]
+    for offset in range(0, cfg.n_entity, rw_batch):
+        idx = np.arange(offset, offset + rw_batch, dtype=np.uint32)
+        idx[idx >= cfg.n_entity] = 0
+        chunk = rows[:, offset : offset + rw_batch]
+        if chunk.shape[1] < rw_batch:
+            # overflow slots point at row 0; give them row 0's data so the order does not matter
+            fill = np.repeat(rows[:, :1], rw_batch - chunk.shape[1], axis=1)
+            chunk = np.concatenate([chunk, fill], axis=1)
+        engine.run("write_entity_rows", {
+            "write_indices": np.ascontiguousarray(np.broadcast_to(idx, (n_local, rw_batch))),
+            "write_data": np.ascontiguousarray(chunk.astype(dtype)),
+        })
+
+
+def read_rows(engine, cfg: StepConfig, rw_batch: int, n_local: int, dtype=np.float32) -> np.ndarray:
+    out = []
+    for offset in range(0, cfg.n_entity, rw_batch):
+        idx = np.arange(offset, offset + rw_batch, dtype=np.uint32)
+        idx[idx >= cfg.n_entity] = 0
+        data = np.zeros((n_local, rw_batch, cfg.row_size), dtype)
+        engine.run("read_entity", {
+            "read_indices": np.ascontiguousarray(np.broadcast_to(idx, (n_local, rw_batch))),
+            "read_data": data,
+        })
+        out.append(data[:, : cfg.n_entity - offset])
+    return np.concatenate(out, axis=1)
+
+
+def read_state(engine, cfg: StepConfig, rw_batch: int, n_local: int) -> Dict[str, np.ndarray]:
+    state = {}
+    for name, shape in engine.variables().items():
+        value = np.zeros(shape, np.uint32 if name == "step" else np.float32)
+        engine.run("read", {"value": value}, name=name)
+        state[name] = value
+    state["entity_data"] = read_rows(engine, cfg, rw_batch, n_local)
+    return state
+
+
+def make_oracle(cfg: StepConfig, state: Dict[str, np.ndarray], dtype=np.float64) -> Oracle:
+    oracle = Oracle(cfg, dtype)
+    oracle.set_state(state)
+    return oracle
+
+
+def assert_close(actual, expected, rtol: float, what: str, atol_scale: float = 1.0) -> None:
+    """|actual - expected| <= rtol * (|expected| + atol_scale * typical magnitude of the tensor).
+
+    The magnitude term absorbs entries that are sums with heavy cancellation, whose own size
+    says nothing about the rounding error of the terms they were summed from."""
+    actual, expected = np.asarray(actual, np.float64), np.asarray(expected, np.float64)
+    assert actual.shape == expected.shape, f"{what}: shape {actual.shape} != {expected.shape}"
+    scale = float(np.sqrt(np.mean(expected**2))) if expected.size else 0.0
+    err = np.abs(actual - expected)
+    bound = rtol * (np.abs(expected) + atol_scale * scale) + 1e-30
+    worst = np.unravel_index(np.argmax(err / bound), err.shape) if err.size else ()
+    assert np.all(err <= bound), (
+        f"{what}: max violation at {worst}: actual {actual[worst]!r} expected {expected[worst]!r} "
+        f"(rtol {rtol}, tensor rms {scale:.3g})")
