@@ -1,0 +1,466 @@
+"""Throughput of the BESS training step on 1..8 B200s: one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: the full-scale configuration (TransE-L2, d=256 fp32 embeddings and Adam state, 768
+fp16 features through a learned 768x256 projection, 512 positives and 256 shared negatives per
+shard, sampled-softmax loss) with one shard per GPU and 11 375 001 rows per shard: 91 M entities
+at 8 GPUs, the same table per GPU at fewer (weak scaling; 91 M rows do not fit below 4 GPUs).
+Inputs are synthetic with the shapes of WikiKG90Mv2: entity ids Zipf(1.1) over a fixed
+pseudo-random permutation, relations Zipf(1.3), positives bucketed by (head shard, tail shard).
+
+One bench "step" is one program run of the engine: 100 training steps on pre-staged index
+arrays, the unit the reference's host loop works in (scripts/run_profile.py:43-51).
+  value  device time of K program runs with the batch already on the GPU (CUDA events on the
+         engine's stream), max over ranks
+  e2e    wall time of K calls of the public "train_step_loop" command with host arrays:
+         validation, host->device copy of the five index streams, segment preparation, the
+         steps, device->host copy of the loss
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS_PER_SHARD = 11_375_001  # ceil(91 000 000 / 8) + the padding row
+N_RELATION = 1387
+BATCH, NEGATIVES, D, F = 512, 256, 256, 768
+DEVICE_STEPS = 100
+
+
+# ---------------------------------------------------------------------------
+# Synthetic workload
+
+
+def workload_settings(n_shard: int, rows_per_shard: int, device_steps: int, rank: int = 0, world: int = 1,
+                      cuda_graph: bool = True) -> dict:
+    n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
+    a2a = (BATCH + NEGATIVES) // n_shard
+    return {
+        "model.seed": 2, "model.score_fn": "TransE", "model.distance_fn": "L2", "model.n_shard": n_shard,
+        "model.n_entity": rows_per_shard, "model.n_relation_type": n_rel, "model.embedding_size": D,
+        "model.entity_feature_size": F, "model.feature_mlp_size": 0, "model.feature_dropout": 0.0,
+        "model.share_feature_networks": True, "model.gamma": 10.0, "model.init_scale": 1.0,
+        "model.negative_adversarial_scale": 0.0,
+        "training.adam_beta_m": 0.9, "training.adam_beta_v": 0.999, "training.adam_epsilon": 1e-8,
+        "training.weight_decay": 0.0, "training.learning_rate_modifiers": {},
+        "data.batch_size": BATCH, "data.a2a_size": a2a,
+        "training.loss.type": "softmax", "training.loss.correction_weight": 1.0,
+        "training.loss_scale": float(BATCH * n_shard * a2a),
+        "training.embedding_regularisation.power": 3.0, "training.embedding_regularisation.weight": 0.0,
+        "training.feature_regularisation.power": 3.0, "training.feature_regularisation.weight": 0.0,
+        "training.hidden_regularisation.power": 3.0, "training.hidden_regularisation.weight": 0.0,
+        "execution.device": "cuda", "execution.dtype": "float32", "execution.feature_dtype": "float16",
+        "execution.train_steps_per_program_run": device_steps, "execution.rw_batch_size": 512,
+        "execution.predict_hr_batch_size": 128, "execution.predict_tail_batch_size": 1024,
+        "execution.predict_n_best": 100, "execution.cuda_graph": cuda_graph,
+        "execution.rank": rank, "execution.world_size": world, "execution.device_ordinal": rank if world > 1 else 0,
+    }
+
+
+def _bounded_zipf(rng: np.random.RandomState, alpha: float, limit: int, size: int) -> np.ndarray:
+    """Ranks in [0, limit) with P(k) ~ (k+1)^-alpha, by rejecting the unbounded sampler's tail."""
+    out = np.empty(0, np.int64)
+    while out.size < size:
+        draw = rng.zipf(alpha, size=int((size - out.size) * 1.4) + 16)
+        out = np.concatenate([out, draw[draw <= limit] - 1])
+    return out[:size]
+
+
+class TriplePool:
+    """Synthetic training triples, bucketed by (head shard, tail shard) as the reference's
+    dataset index does (src/python/poplar_kge_dataset.py:199-241).
+
+    Entity popularity is Zipf(1.1) over a fixed affine permutation of the ids; an entity's shard
+    is ``id % n_shard`` and its row ``id // n_shard + 1`` (row 0 is the padding row), the divmod
+    layout of src/python/poplar_kge_dataset.py:184-189.  Every rank builds the same pool from the
+    same seed, so no data moves between processes."""
+
+    def __init__(self, n_shard: int, rows_per_shard: int, n_relation: int, pool_size: int, seed: int = 2):
+        rng = np.random.RandomState(seed)
+        self.n_shard, self.rows = n_shard, rows_per_shard
+        n_entity = n_shard * (rows_per_shard - 1)
+        mult = 2_654_435_761 % n_entity
+        while np.gcd(mult, n_entity) != 1:
+            mult += 1
+        permute = lambda k: (k * mult + 12_345) % n_entity  # noqa: E731
+        head = permute(_bounded_zipf(rng, 1.1, n_entity, pool_size))
+        tail = permute(_bounded_zipf(rng, 1.1, n_entity, pool_size))
+        rel = _bounded_zipf(rng, 1.3, n_relation, pool_size)
+        pair = (head % n_shard) * n_shard + (tail % n_shard)
+        order = np.argsort(pair, kind="stable")
+        self.h = (head[order] // n_shard + 1).astype(np.uint32)
+        self.t = (tail[order] // n_shard + 1).astype(np.uint32)
+        self.r = rel[order].astype(np.uint32)
+        counts = np.bincount(pair, minlength=n_shard * n_shard)
+        self.count = counts.reshape(n_shard, n_shard)
+        self.offset = np.concatenate([[0], np.cumsum(counts)[:-1]]).reshape(n_shard, n_shard)
+        if np.any(self.count == 0):
+            raise RuntimeError("triple pool too small: an empty (head shard, tail shard) bucket")
+
+    def sample(self, n_step: int, batch: int, a2a: int, seed: int) -> dict:
+        """Index streams [n_shard, n_step, ...] for every shard: the layout of the reference's
+        ``Dataset.sample_batch`` (src/python/poplar_kge_dataset.py:310-393)."""
+        n, rng = self.n_shard, np.random.RandomState(seed)
+        pos = batch // n
+        neg = a2a - pos
+        pick = self.offset[:, None, :, None] + rng.randint(1 << 62, size=(n, n_step, n, pos)) % self.count[:, None, :, None]
+        h, r, t = self.h[pick], self.r[pick], self.t[pick]  # [head shard, step, tail shard, pos]
+        t_neg = (1 + rng.randint(1 << 62, size=(n, n_step, n, neg)) % (self.rows - 1)).astype(np.uint32)
+        # rows shard s must gather: its heads, the positive tails it owns, the negatives it serves
+        wanted = np.concatenate([h.reshape(n, n_step, -1),
+                                 t.transpose(2, 1, 0, 3).reshape(n, n_step, -1),
+                                 t_neg.transpose(2, 1, 0, 3).reshape(n, n_step, -1)], axis=2)
+        width = wanted.shape[2]
+        remote = np.zeros((n, n_step, width), np.uint32)
+        lookup = np.zeros((n, n_step, width), np.uint32)
+        for s in range(n):
+            for i in range(n_step):
+                unique, inverse = np.unique(wanted[s, i], return_inverse=True)
+                remote[s, i, : unique.size] = unique
+                lookup[s, i] = inverse
+        a2a_idx = np.concatenate([lookup[:, :, batch : 2 * batch].reshape(n, n_step, n, pos),
+                                  lookup[:, :, 2 * batch :].reshape(n, n_step, n, neg)], axis=3)
+        tail = (np.arange(pos)[None, :] + a2a * np.arange(n)[:, None]).reshape(-1)
+        return dict(remote=remote, a2a=np.ascontiguousarray(a2a_idx),
+                    head=np.ascontiguousarray(lookup[:, :, :batch]),
+                    relation=np.ascontiguousarray(r.reshape(n, n_step, batch)),
+                    tail=np.ascontiguousarray(np.broadcast_to(tail.astype(np.uint32), (n, n_step, batch))))
+
+
+def local_slice(batch: dict, rank: int, world: int) -> dict:
+    """The shards of one process: n_shard / world consecutive shards starting at rank * that."""
+    n = batch["remote"].shape[0] // world
+    return {k: np.ascontiguousarray(v[rank * n : (rank + 1) * n]) for k, v in batch.items()}
+
+
+# ---------------------------------------------------------------------------
+# Clocks
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.lines, self.proc = gpu_index, [], None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, sm_max, power, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "power_w": float(np.median(power)) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# Algorithmic traffic of one training step of one shard (bytes), per kernel
+
+
+def step_traffic(n_shard: int) -> dict:
+    B, T = BATCH, BATCH + NEGATIVES
+    R = B + T
+    n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
+    row_state, row_feat = 3 * D * 4, F * 2
+    return {
+        # reads value + features of R rows and the projection, writes the hidden rows
+        "hidden": R * (D * 4 + row_feat) + F * D * 4 + R * D * 4,
+        "route": 2 * (T + B) * D * 4 + B * D * 4,
+        "score": (B + T) * D * 4 + B * T * 4,
+        "loss": 2 * B * T * 4,
+        "score_bwd": 2 * B * T * 4 + 2 * (B + T) * D * 4,
+        # reads the lookup gradients and value/m/sqrt(v) of R rows, writes them back + hidden grads
+        "entity_update": (B + T) * D * 4 + 2 * R * row_state + R * D * 4,
+        "projection_bwd": R * row_feat + R * D * 4 + F * D * 4,
+        "dense_partial": (n_rel + F) * D * 4 + B * D * 4,
+        "dense_update": 5 * (n_rel + F) * D * 4,
+        # the step as the reference's host sees it: gather R whole rows, scatter their state back
+        "step": R * (row_state + row_feat) + R * row_state,
+    }
+
+
+# ---------------------------------------------------------------------------
+# Arms
+
+
+def measured_peak_gbs() -> tuple:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_baseline(seconds_target: float = 12.0, n_shard: int = 1, rows: int = 200_001) -> dict:
+    """The C++ / OpenMP restatement of the step on the host cores, same per-step shapes, a
+    smaller table (the step touches 1280 rows whatever the table size)."""
+    from oracle import build as oracle_build
+    from oracle.cpp_oracle import CppOracle
+    from oracle.step_oracle import StepConfig
+
+    oracle_build.build()
+    a2a = (BATCH + NEGATIVES) // n_shard
+    cfg = StepConfig(n_shard=n_shard, n_entity=rows, n_relation_type=int(n_shard * np.ceil(N_RELATION / n_shard)),
+                     embedding_size=D, entity_feature_size=F, batch_size=BATCH, a2a_size=a2a, score_fn="TransE",
+                     distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0)
+    oracle = CppOracle(cfg)
+    rng = np.random.RandomState(0)
+    oracle.entity_data[..., :D] = rng.normal(size=oracle.entity_data[..., :D].shape).astype(np.float32) / D
+    oracle.entity_data[..., 3 * D :] = rng.normal(size=oracle.entity_data[..., 3 * D :].shape).astype(np.float16)
+    oracle.rel[0][...] = rng.normal(size=oracle.rel[0].shape) / D
+    oracle.proj[0][...] = rng.normal(size=oracle.proj[0].shape) / D / np.sqrt(F)
+    pool = TriplePool(n_shard, rows, cfg.n_relation_type, 200_000)
+    batch = pool.sample(4, BATCH, a2a, seed=1)
+    steps, start = 0, time.perf_counter()
+    while True:
+        i = steps % 4
+        oracle.train_step(1e-3, *(np.ascontiguousarray(batch[k][:, i]) for k in ("remote", "a2a", "head", "relation", "tail")))
+        steps += 1
+        elapsed = time.perf_counter() - start
+        if elapsed >= seconds_target or steps >= 2000:
+            break
+    return {"value": n_shard * BATCH * steps / elapsed, "unit": "triples/s", "cores": oracle.threads, "kind": "port",
+            "sample": f"{steps} training steps of the C++/OpenMP restatement (oracle/csrc/bess_step.cpp), {n_shard} shard(s), "
+                      f"same per-step shapes, {rows} rows per shard, {elapsed:.1f} s"}
+
+
+def run_reference_arm(args) -> None:
+    """The reference's CPU path is Poplar's CPU target, which needs the Poplar SDK: it cannot be
+    installed here.  This arm times the oracle's C++/OpenMP port of the same step on the host."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_shard = args.gpus
+    per_step_target = 3.0
+    results = []
+    for i in range(args.warmup + args.steps):
+        r = cpu_baseline(seconds_target=per_step_target if i >= args.warmup else 0.5, n_shard=n_shard, rows=100_001)
+        if i >= args.warmup:
+            results.append(r)
+    value = float(np.mean([r["value"] for r in results]))
+    line = {
+        "impl": "reference", "metric": "train_triples_per_sec", "value": value, "unit": "triples/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * per_step_target, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(n_shard, 100_001, DEVICE_STEPS, note="CPU sample: a bounded number of steps per bench step"),
+        "cpu_baseline": {**results[-1], "value": value},
+        "e2e": {"value": value, "unit": "triples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_shard: int, rows: int, device_steps: int, note: str = "") -> dict:
+    cfg = {
+        "workload": f"BESS TransE-L2 training, {n_shard} shard(s) x {rows} rows (d=256 fp32 + 768 fp16 features), "
+                    f"512 positives + 256 shared negatives per shard, softmax loss, {device_steps} steps per program run",
+        "n_shard": n_shard, "rows_per_shard": rows, "per_shard_batch": BATCH, "shared_negatives": NEGATIVES,
+        "embedding_size": D, "feature_size": F, "steps_per_program_run": device_steps,
+        "cache": "inputs larger than L2: one program run touches about 0.5 GB of distinct table rows",
+    }
+    if note:
+        cfg["note"] = note
+    return cfg
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from distributed_kge_poplar_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run for N > 1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n_shard, rows, device_steps = world, args.rows_per_shard, args.device_steps
+    settings = workload_settings(n_shard, rows, device_steps, rank, world, cuda_graph=not args.no_graph)
+    settings["execution.device_ordinal"] = local_rank
+    engine = capi.CEngine(settings)
+    if world > 1:
+        handles = [None] * world
+        dist.all_gather_object(handles, engine.comm_export())
+        engine.comm_connect(b"".join(handles), world)
+    engine.run("initialise_entities", {})
+    rng = np.random.RandomState(2)
+    n_rel = settings["model.n_relation_type"]
+    engine.run("write", {"value": (rng.normal(size=(n_rel, D)) / D).astype(np.float32)}, name="relation_embedding")
+    engine.run("write", {"value": (rng.normal(size=(F, D)) / D / np.sqrt(F)).astype(np.float32)}, name="feature_projection")
+
+    a2a = settings["data.a2a_size"]
+    pool = TriplePool(n_shard, rows, n_rel, pool_size=max(400_000, 200_000 * n_shard * n_shard))
+    batches = [local_slice(pool.sample(device_steps, BATCH, a2a, seed=100 + i), rank, world) for i in range(4)]
+    lr = np.full(1, 1e-3, np.float32)
+    loss = np.zeros(1, np.float32)
+    h2d = sum(v.nbytes for v in batches[0].values()) + lr.nbytes
+    triples_per_call = n_shard * BATCH * device_steps
+
+    # -- value: batch resident on the device ---------------------------------
+    engine.stage_batch(batches[0])
+    for _ in range(args.warmup):
+        engine.train_staged(1e-3, None)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    device_ms, launches = 0.0, 0
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        engine.train_staged(1e-3, None)
+        ms, n_launch = engine.last_run_stats()
+        device_ms += ms
+        launches += n_launch
+    barrier()
+    wall_value = time.perf_counter() - t0
+    device_s = max_over_ranks(device_ms / 1e3)
+    value = triples_per_call * args.steps / device_s
+
+    # -- e2e: the public command with host arrays ----------------------------
+    for i in range(args.warmup):
+        engine.run("train_step_loop", dict(learning_rate=lr, loss=loss, **batches[i % 4]))
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        engine.run("train_step_loop", dict(learning_rate=lr, loss=loss, **batches[i % 4]))
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clocks = sampler.stop() if rank == 0 else None
+    final_loss = float(loss[0])
+
+    # -- per-kernel times (plain launches bracketed by events), for the roofline ----
+    engine.set_kernel_timing(True)
+    engine.stage_batch(batches[0])
+    for _ in range(2):
+        engine.train_staged(1e-3, None)
+    times = engine.kernel_times()
+    engine.set_kernel_timing(False)
+    engine.close()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peak_gbs()
+    traffic = step_traffic(n_shard)
+    total_kernel_ms = sum(ms for ms, _ in times.values())
+    kernels = {}
+    for name, (ms, count) in sorted(times.items(), key=lambda kv: -kv[1][0]):
+        per_launch_us = 1e3 * ms / max(count, 1)
+        entry = {"share": ms / total_kernel_ms, "us_per_launch": per_launch_us, "launches": count}
+        if name in traffic:
+            entry["algorithmic_bytes"] = traffic[name]
+            entry["gb_per_s"] = traffic[name] / (per_launch_us * 1e-6) / 1e9
+        kernels[name] = entry
+    dominant = next(iter(kernels))
+    dom = kernels[dominant]
+    achieved = dom.get("gb_per_s", 0.0)
+    step_us = 1e6 * device_s / (args.steps * device_steps)
+    line = {
+        "metric": "train_triples_per_sec", "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * device_s / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(n_shard, rows, device_steps),
+        "e2e": {"value": triples_per_call * args.steps / e2e_s, "unit": "triples/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": loss.nbytes, "ms_per_step": 1e3 * e2e_s / args.steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": peak_kind, "traffic": None,
+                     "algorithmic_bytes_per_launch": dom.get("algorithmic_bytes"), "us_per_launch": dom["us_per_launch"],
+                     "step_us": step_us, "step_hbm_gb_per_s": traffic["step"] / (step_us * 1e-6) / 1e9,
+                     "step_frac_of_hbm": traffic["step"] / (step_us * 1e-6) / 1e9 / peak},
+        "kernels": kernels,
+        "clocks": clocks,
+        "wall_ms_per_step_value_arm": 1e3 * wall_value / args.steps,
+        "final_loss": final_loss,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--rows-per-shard", type=int, default=ROWS_PER_SHARD, help="smaller tables for profiler captures")
+    ap.add_argument("--device-steps", type=int, default=DEVICE_STEPS, help="training steps per program run")
+    ap.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours" and args.rows_per_shard == ROWS_PER_SHARD:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

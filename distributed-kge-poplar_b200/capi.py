@@ -26,7 +26,8 @@ L1, L2, DOT = 0, 1, 2
 SYMBOLS = (
     "kge_create", "kge_destroy", "kge_last_error", "kge_run", "kge_variable_count",
     "kge_variable_info", "kge_comm_handle_bytes", "kge_comm_export", "kge_comm_connect",
-    "kge_stage_batch", "kge_train_staged", "kge_last_run_stats", "kge_debug_fetch",
+    "kge_stage_batch", "kge_train_staged", "kge_last_run_stats", "kge_set_kernel_timing",
+    "kge_kernel_time_count", "kge_kernel_time", "kge_debug_fetch",
     "kge_op_pairwise", "kge_op_pairwise_grad", "kge_op_gather_rows", "kge_op_scatter_add_rows",
     "kge_op_activation", "kge_op_all_to_all",
 )
@@ -71,6 +72,9 @@ def load_library() -> C.CDLL:
     lib.kge_stage_batch.argtypes = [vp, C.POINTER(Array), sz]
     lib.kge_train_staged.argtypes = [vp, C.c_float, fp]
     lib.kge_last_run_stats.argtypes = [vp, fp, C.POINTER(C.c_ulonglong)]
+    lib.kge_set_kernel_timing.argtypes = [vp, C.c_int]
+    lib.kge_kernel_time_count.argtypes = [vp, C.POINTER(sz)]
+    lib.kge_kernel_time.argtypes = [vp, sz, C.POINTER(C.c_char_p), fp, C.POINTER(C.c_ulonglong)]
     lib.kge_debug_fetch.argtypes = [vp, C.c_char_p, sz, fp, sz, C.POINTER(sz)]
     lib.kge_op_pairwise.argtypes = [C.c_int, fp, fp, sz, sz, sz, fp]
     lib.kge_op_pairwise_grad.argtypes = [C.c_int, fp, fp, fp, sz, sz, sz, fp, fp]
@@ -202,6 +206,20 @@ class CEngine:
         ms, launches = C.c_float(), C.c_ulonglong()
         self._check(self._lib.kge_last_run_stats(self._handle, C.byref(ms), C.byref(launches)))
         return ms.value, launches.value
+
+    def set_kernel_timing(self, on: bool) -> None:
+        self._check(self._lib.kge_set_kernel_timing(self._handle, int(on)))
+
+    def kernel_times(self) -> Dict[str, Tuple[float, int]]:
+        """{kernel name: (total device ms, launches)} since timing was switched on."""
+        count = C.c_size_t()
+        self._check(self._lib.kge_kernel_time_count(self._handle, C.byref(count)))
+        out = {}
+        for i in range(count.value):
+            name, ms, launches = C.c_char_p(), C.c_float(), C.c_ulonglong()
+            self._check(self._lib.kge_kernel_time(self._handle, i, C.byref(name), C.byref(ms), C.byref(launches)))
+            out[name.value.decode()] = (ms.value, launches.value)
+        return out
 
     def debug_fetch(self, what: str, shard: int, capacity: int) -> np.ndarray:
         out = np.empty(capacity, np.float32)

@@ -173,6 +173,23 @@ int kge_last_run_stats(kge_engine* engine, float* device_ms, unsigned long long*
     return KGE_OK;
 }
 
+int kge_set_kernel_timing(kge_engine* engine, int on) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    engine->impl->set_kernel_timing(on != 0);
+    return KGE_OK;
+}
+
+int kge_kernel_time_count(kge_engine* engine, size_t* count) {
+    if (!engine || !count) return KGE_INVALID_ARGUMENT;
+    *count = engine->impl->kernel_time_count();
+    return KGE_OK;
+}
+
+int kge_kernel_time(kge_engine* engine, size_t index, const char** name, float* total_ms, unsigned long long* launches) {
+    if (!engine) return KGE_INVALID_ARGUMENT;
+    return guarded(engine->last_error, [&] { engine->impl->kernel_time(index, name, total_ms, launches); });
+}
+
 int kge_debug_fetch(kge_engine* engine, const char* what, size_t shard, float* out, size_t capacity, size_t* count) {
     if (!engine) return KGE_INVALID_ARGUMENT;
     return guarded(engine->last_error, [&] {

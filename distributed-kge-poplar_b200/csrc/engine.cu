@@ -492,6 +492,7 @@ void Engine::run(const std::string& command, std::vector<HostArray>& arrays, con
     if (command == "read_entity") return cmd_read_entity(arrays);
     if (command == "write_entity") return cmd_write_entity(arrays, false);
     if (command == "write_entity_rows") return cmd_write_entity(arrays, true);
+    if (command == "initialise_entities") return cmd_initialise_entities();
     if (command == "read" || command == "write") return cmd_read_write_variable(arrays, variable, command == "write");
     fail(KGE_INVALID_ARGUMENT, msg() << "Unknown command '" << command << "'");
 }
@@ -559,7 +560,7 @@ void Engine::train_staged(float learning_rate, float* loss) {
     KGE_CUDA(cudaMemcpyAsync(d_step_size_, sizes, (size_t)cfg_.n_step * 4, cudaMemcpyHostToDevice, stream_));
     KGE_CUDA(cudaMemsetAsync(d_loss_total_, 0, n_local_ * 4, stream_));
     KGE_CUDA(cudaEventRecord(ev_begin_, stream_));
-    if (cfg_.cuda_graph) {
+    if (cfg_.cuda_graph && !kernel_timing_) {
         if (!graph_exec_) {
             cudaGraph_t graph = nullptr;
             launch_counter_ = 0;
@@ -589,6 +590,7 @@ void Engine::train_staged(float learning_rate, float* loss) {
         KGE_CUDA(cudaMemcpyAsync(host_loss, d_loss_total_, n_local_ * 4, cudaMemcpyDeviceToHost, stream_));
     KGE_CUDA(cudaStreamSynchronize(stream_));
     KGE_CUDA(cudaEventElapsedTime(&last_ms_, ev_begin_, ev_end_));
+    timing_collect();
     step_ += cfg_.n_step;
     check_device_status();
     if (loss)
@@ -606,10 +608,36 @@ void Engine::check_device_status() {
     }
 }
 
+void Engine::set_kernel_timing(bool on) {
+    kernel_timing_ = on;
+    if (on) kernel_times_.clear();
+}
+
+size_t Engine::kernel_time_count() const { return kernel_times_.size(); }
+
+void Engine::kernel_time(size_t index, const char** name, float* ms, unsigned long long* launches) const {
+    if (index >= kernel_times_.size()) fail(KGE_INVALID_ARGUMENT, "kge_kernel_time: index past the end");
+    auto it = kernel_times_.begin();
+    std::advance(it, index);
+    if (name) *name = it->first.c_str();
+    if (ms) *ms = it->second.ms;
+    if (launches) *launches = it->second.launches;
+}
+
 void Engine::last_run_stats(float* ms, unsigned long long* launches) const {
     if (ms) *ms = last_ms_;
     if (launches) *launches = last_launches_;
 }
+
+// Wraps one kernel launch: counts it and, when per-kernel timing is on, brackets it with a
+// pair of events on the engine's stream.
+#define KGE_LAUNCH(name, ...)            \
+    do {                                 \
+        timing_begin(name);              \
+        __VA_ARGS__;                     \
+        timing_end();                    \
+        ++launch_counter_;               \
+    } while (0)
 
 void Engine::launch_steps() {
     for (unsigned step = 0; step < cfg_.n_step; ++step) launch_one_step(step);
@@ -623,10 +651,37 @@ void Engine::launch_barrier() {
     a.status = d_status_;
     a.rank = (int)cfg_.rank;
     a.world = (int)cfg_.world;
-    a.max_spins = 20ull * 1000 * 1000;  // about two seconds of 64 ns naps plus load latency
-    k_barrier<<<1, 64, 0, stream_>>>(a);
-    ++launch_counter_;
+    a.max_spins = 2ull * 1000 * 1000;  // a second or two of 64 ns naps plus load latency
+    KGE_LAUNCH("barrier", k_barrier<<<1, 64, 0, stream_>>>(a));
     KGE_CUDA(cudaGetLastError());
+}
+
+void Engine::timing_begin(const char* name) {
+    if (!kernel_timing_) return;
+    cudaEvent_t a = nullptr, b = nullptr;
+    KGE_CUDA(cudaEventCreate(&a));
+    KGE_CUDA(cudaEventCreate(&b));
+    timed_.push_back({name, a, b});
+    KGE_CUDA(cudaEventRecord(a, stream_));
+}
+
+void Engine::timing_end() {
+    if (!kernel_timing_) return;
+    KGE_CUDA(cudaEventRecord(timed_.back().stop, stream_));
+}
+
+void Engine::timing_collect() {
+    for (TimedLaunch& t : timed_) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess) {
+            KernelTime& k = kernel_times_[t.name];
+            k.ms += ms;
+            k.launches += 1;
+        }
+        cudaEventDestroy(t.start);
+        cudaEventDestroy(t.stop);
+    }
+    timed_.clear();
 }
 
 void Engine::launch_one_step(unsigned step) {
@@ -668,19 +723,19 @@ void Engine::launch_one_step(unsigned step) {
         ShardBuffers& b = shards_[l];
         const uint32_t* remote = step_ptr(d_remote_, l, R);
         dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
-        KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(b.table, layout_, remote, (int)R, W0, W1,
-                                                                           b.hid_h, b.hid_t));
-        ++launch_counter_;
+        KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
+                                                        b.table, layout_, remote, (int)R, W0, W1, b.hid_h, b.hid_t)));
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
         if (vec)
-            k_route<4><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table, b.send_dst,
-                                                  b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn);
+            KGE_LAUNCH("route", k_route<4><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table,
+                                                                      b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
+                                                                      (int)B, (int)D, cfg_.score_fn));
         else
-            k_route<1><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table, b.send_dst,
-                                                  b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn);
-        ++launch_counter_;
+            KGE_LAUNCH("route", k_route<1><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table,
+                                                                      b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
+                                                                      (int)B, (int)D, cfg_.score_fn));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -699,23 +754,21 @@ void Engine::launch_one_step(unsigned step) {
         pa.p[1] = {b.tails, b.pred, b.coeff, (int)T, (int)B, 1, (int)T, nullptr, b.grad_dst, (int)cfg_.a2a_size};
         dim3 bgrid(ceil_div(B, 32) + ceil_div(T, 32), ceil_div(D, 64));
         switch (cfg_.dist_fn) {
-            case DIST_L1: k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D); break;
-            case DIST_L2: k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D); break;
-            default: k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D); break;
+            case DIST_L1: KGE_LAUNCH("score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
+            case DIST_L2: KGE_LAUNCH("score", k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
+            default: KGE_LAUNCH("score", k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
         }
-        k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp);
-        k_loss_finish<<<1, 256, 0, stream_>>>(b.loss_rows, (int)B, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l);
+        KGE_LAUNCH("loss", k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp));
+        KGE_LAUNCH("loss_finish", k_loss_finish<<<1, 256, 0, stream_>>>(b.loss_rows, (int)B, 1.0f / normaliser,
+                                                                        d_loss_total_ + l, d_loss_last_ + l));
         switch (cfg_.dist_fn) {
-            case DIST_L1: k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa); break;
-            case DIST_L2: k_pair_bwd<DIST_L2><<<bgrid, 128, 0, stream_>>>(pa); break;
-            default: k_pair_bwd<DIST_DOT><<<bgrid, 128, 0, stream_>>>(pa); break;
+            case DIST_L1: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa)); break;
+            case DIST_L2: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L2><<<bgrid, 128, 0, stream_>>>(pa)); break;
+            default: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_DOT><<<bgrid, 128, 0, stream_>>>(pa)); break;
         }
-        launch_counter_ += 4;
-        if (cfg_.score_fn != SCORE_TRANSE) {
-            k_pred_bwd<<<B, 64, 0, stream_>>>(b.d_pred, b.hid_h, head, relation, rel_table, b.d_head, b.d_relrow,
-                                              (int)D, cfg_.score_fn);
-            ++launch_counter_;
-        }
+        if (cfg_.score_fn != SCORE_TRANSE)
+            KGE_LAUNCH("pred_bwd", k_pred_bwd<<<B, 64, 0, stream_>>>(b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
+                                                                     b.d_relrow, (int)D, cfg_.score_fn));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -728,42 +781,43 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* perm = d_ent_perm_ + sidx * (B + T);
         const uint32_t* off = d_ent_off_ + sidx * (R + 1);
         const uint32_t* first = d_first_slot_ + sidx * R;
+        const float* alpha = d_step_size_ + step;
         if (cfg_.state_type == ST_F32) {
             if (vec)
-                k_entity_update<float, 4><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
-                                                                 (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
-                                                                 entity_lr_mod_, adam_);
+                KGE_LAUNCH("entity_update", k_entity_update<float, 4><<<R, 64, 0, stream_>>>(
+                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
             else
-                k_entity_update<float, 1><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
-                                                                 (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
-                                                                 entity_lr_mod_, adam_);
+                KGE_LAUNCH("entity_update", k_entity_update<float, 1><<<R, 64, 0, stream_>>>(
+                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
         } else {
             if (vec)
-                k_entity_update<__half, 4><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
-                                                                  (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
-                                                                  entity_lr_mod_, adam_);
+                KGE_LAUNCH("entity_update", k_entity_update<__half, 4><<<R, 64, 0, stream_>>>(
+                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
             else
-                k_entity_update<__half, 1><<<R, 64, 0, stream_>>>(b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv,
-                                                                  (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step,
-                                                                  entity_lr_mod_, adam_);
+                KGE_LAUNCH("entity_update", k_entity_update<__half, 1><<<R, 64, 0, stream_>>>(
+                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
         }
-        ++launch_counter_;
         if (F > 0) {
             dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
             if (cfg_.feature_type == ST_F32)
-                k_projection_bwd<float><<<grid, 256, 0, stream_>>>(b.table, layout_, remote, (int)R, b.d_hid_h, dh1,
-                                                                   proj_splits_, proj_rows_per_split_, b.proj_partial);
+                KGE_LAUNCH("projection_bwd", k_projection_bwd<float><<<grid, 256, 0, stream_>>>(
+                                                 b.table, layout_, remote, (int)R, b.d_hid_h, dh1, proj_splits_,
+                                                 proj_rows_per_split_, b.proj_partial));
             else
-                k_projection_bwd<__half><<<grid, 256, 0, stream_>>>(b.table, layout_, remote, (int)R, b.d_hid_h, dh1,
-                                                                    proj_splits_, proj_rows_per_split_, b.proj_partial);
-            ++launch_counter_;
+                KGE_LAUNCH("projection_bwd", k_projection_bwd<__half><<<grid, 256, 0, stream_>>>(
+                                                 b.table, layout_, remote, (int)R, b.d_hid_h, dh1, proj_splits_,
+                                                 proj_rows_per_split_, b.proj_partial));
         }
         const unsigned blocks = (unsigned)std::min<size_t>((n_dense_ + 255) / 256, 148 * 8);
-        k_dense_partial<<<std::max(1u, blocks), 256, 0, stream_>>>(
-            b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel, (int)D, b.proj_partial,
-            (int)cfg_.n_net(), proj_splits_, proj_elems_, b.dense_partial);
-        ++launch_counter_;
+        KGE_LAUNCH("dense_partial", k_dense_partial<<<std::max(1u, blocks), 256, 0, stream_>>>(
+                                        b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                        (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_, proj_elems_,
+                                        b.dense_partial));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -785,8 +839,7 @@ void Engine::launch_one_step(unsigned step) {
         da.ap = adam_;
         // The parameter itself is read from this process's own replica (entry `rank`).
         const unsigned blocks = (unsigned)std::min<size_t>((own_hi_ - own_lo_ + 255) / 256, 148 * 8);
-        k_dense_update<<<std::max(1u, blocks), 256, 0, stream_>>>(da, (int)cfg_.rank);
-        ++launch_counter_;
+        KGE_LAUNCH("dense_update", k_dense_update<<<std::max(1u, blocks), 256, 0, stream_>>>(da, (int)cfg_.rank));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -861,6 +914,16 @@ void Engine::cmd_write_entity(std::vector<HostArray>& arrays, bool whole_rows) {
             if (whole_rows) KGE_DISPATCH_ROW(cfg_, k_write_rows<ST, FT, IT><<<g, 128, 0, stream_>>>(table, layout_, di, (int)rw, (const IT*)din));
             else KGE_DISPATCH_ROW(cfg_, k_write_entity<ST, FT, IT><<<g, 128, 0, stream_>>>(table, layout_, di, (int)rw, (const IT*)din, cfg_.seed, shard0_ + l, stddev));
         }
+    }
+    KGE_CUDA(cudaGetLastError());
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Engine::cmd_initialise_entities() {
+    const float stddev = cfg_.init_scale / (float)cfg_.d;
+    for (unsigned l = 0; l < n_local_; ++l) {
+        KGE_DISPATCH_ROW(cfg_, k_init_table<ST, FT><<<148 * 8, 256, 0, stream_>>>(shards_[l].table, layout_, (size_t)cfg_.n_entity,
+                                                                               cfg_.seed, shard0_ + l, stddev));
     }
     KGE_CUDA(cudaGetLastError());
     KGE_CUDA(cudaStreamSynchronize(stream_));

@@ -81,6 +81,9 @@ class Engine {
     void stage_batch(std::vector<HostArray>& arrays);
     void train_staged(float learning_rate, float* loss);
     void last_run_stats(float* ms, unsigned long long* launches) const;
+    void set_kernel_timing(bool on);
+    size_t kernel_time_count() const;
+    void kernel_time(size_t index, const char** name, float* ms, unsigned long long* launches) const;
     size_t debug_fetch(const std::string& what, size_t shard, float* out, size_t capacity);
 
     std::string last_error;
@@ -110,12 +113,16 @@ class Engine {
     void cmd_write_entity(std::vector<HostArray>& arrays, bool whole_rows);
     void cmd_read_write_variable(std::vector<HostArray>& arrays, const std::string& name, bool write);
     void cmd_predict(std::vector<HostArray>& arrays);
+    void cmd_initialise_entities();
 
     // the step
     void launch_steps();
     void launch_one_step(unsigned step);
     void launch_barrier();
     void check_device_status();
+    void timing_begin(const char* name);
+    void timing_end();
+    void timing_collect();
 
     HostArray& find_array(std::vector<HostArray>& arrays, const std::string& name, int dtype,
                           const std::vector<size_t>& shape);
@@ -161,6 +168,18 @@ class Engine {
     bool staged_ = false;
     uint32_t* d_rw_idx_ = nullptr;
     uint8_t* d_rw_data_ = nullptr;
+
+    struct TimedLaunch {
+        const char* name;
+        cudaEvent_t start, stop;
+    };
+    struct KernelTime {
+        float ms = 0.f;
+        unsigned long long launches = 0;
+    };
+    bool kernel_timing_ = false;
+    std::vector<TimedLaunch> timed_;
+    std::map<std::string, KernelTime> kernel_times_;
 
     cudaGraphExec_t graph_exec_ = nullptr;
     float last_ms_ = 0.f;

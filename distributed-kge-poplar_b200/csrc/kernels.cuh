@@ -1030,6 +1030,40 @@ k_write_entity(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restr
         store_from_float(fv + c, load_as_float(features + (size_t)j * F + c));
 }
 
+// initialise_entities: every row of the shard on the device, no host data.  Embeddings as
+// write_entity would draw them; features ~ N(0, 1) from a second stream (row 0, the padding
+// row, keeps zero features); optimiser state zero.  Stands in for streaming a dataset's
+// features through write_entity when the table is tens of gigabytes of synthetic data.
+template <class ST, class FT>
+__global__ void __launch_bounds__(256)
+k_init_table(uint8_t* __restrict__ table, RowLayout L, size_t n_rows, uint32_t seed, uint32_t shard,
+             float stddev) {
+    const int D = L.d, F = L.f;
+    const int d4 = (D + 3) / 4, f4 = (F + 3) / 4, per_row = d4 + f4;
+    const size_t total = n_rows * (size_t)per_row;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = e / per_row;
+        const int q = (int)(e - row * per_row);
+        uint8_t* base = table + row * L.row_bytes;
+        if (q < d4) {
+            const float4 z = philox_normal4(seed, shard, (uint32_t)row, (uint32_t)q);
+            const float zz[4] = {z.x, z.y, z.z, z.w};
+            for (int u = 0; u < 4 && q * 4 + u < D; ++u) {
+                store_from_float(reinterpret_cast<ST*>(base) + q * 4 + u, stddev * zz[u]);
+                store_from_float(reinterpret_cast<ST*>(base + L.off_m) + q * 4 + u, 0.f);
+                store_from_float(reinterpret_cast<ST*>(base + L.off_q) + q * 4 + u, 0.f);
+            }
+        } else {
+            const int c4 = q - d4;
+            const float4 z = philox_normal4(seed ^ 0x5bd1e995u, shard, (uint32_t)row, (uint32_t)c4);
+            const float zz[4] = {z.x, z.y, z.z, z.w};
+            for (int u = 0; u < 4 && c4 * 4 + u < F; ++u)
+                store_from_float(reinterpret_cast<FT*>(base + L.off_feat) + c4 * 4 + u, row == 0 ? 0.f : zz[u]);
+        }
+    }
+}
+
 // write_entity_rows: whole rows [value | m | sqrt(v) | feature] from the host array.
 template <class ST, class FT, class IT>
 __global__ void __launch_bounds__(128)

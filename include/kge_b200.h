@@ -91,7 +91,11 @@ const char* kge_last_error(const kge_engine* engine);
  * "read"/"write" the variable is named by `variable_name` and the array is called "value"
  * (src/poplar_kge.cpp:977-991).  One command is added: "write_entity_rows"
  * (write_indices u32 [n, rw], write_data [n, rw, 3D+F]) writes whole rows, embedding and
- * optimiser state included, which the reference cannot do from the host.
+ * optimiser state included, which the reference cannot do from the host; and
+ * "initialise_entities" (no arrays) fills every row on the device: embeddings as
+ * "write_entity" draws them, features ~ N(0, 1), optimiser state zero.  It stands in for
+ * the reference's host loop that streams all features through "write_entity"
+ * (src/python/poplar_kge.py:690-705) when the data is synthetic.
  */
 int kge_run(kge_engine* engine, const char* command, const kge_array* arrays, size_t n_arrays,
             const char* variable_name);
@@ -128,6 +132,15 @@ int kge_train_staged(kge_engine* engine, float learning_rate, float* loss);
 /* Device time of the last kge_train_staged / "train_step_loop" run, from CUDA events on the
  * engine's stream, and the number of kernels it launched (graph nodes when replayed as a graph). */
 int kge_last_run_stats(kge_engine* engine, float* device_ms, unsigned long long* kernel_launches);
+
+/* Per-kernel device times.  While switched on, the step loop is launched kernel by kernel (not as
+ * a graph) with a pair of CUDA events on the engine's stream around every launch; the totals per
+ * kernel name accumulate until it is switched on again.  No counterpart in the reference, whose
+ * profile comes from Poplar's own report (scripts/run_profile.py:22-30). */
+int kge_set_kernel_timing(kge_engine* engine, int on);
+int kge_kernel_time_count(kge_engine* engine, size_t* count);
+int kge_kernel_time(kge_engine* engine, size_t index, const char** name, float* total_ms,
+                    unsigned long long* launches);
 
 /* Copies an intermediate of the last training step of local shard `shard` to the host, for
  * tests: "hidden", "tails", "pred", "raw_score", "coeff", "d_pred", "d_hidden", "dense_grad".
