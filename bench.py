@@ -141,6 +141,15 @@ class TriplePool:
                     tail=np.ascontiguousarray(np.broadcast_to(tail.astype(np.uint32), (n, n_step, batch))))
 
 
+def exchange_handles(blob: bytes, world: int) -> bytes:
+    """All-gather of the engines' connection handles over the default process group, in rank order."""
+    import torch.distributed as dist
+
+    handles = [None] * world
+    dist.all_gather_object(handles, blob)
+    return b"".join(handles)
+
+
 def local_slice(batch: dict, rank: int, world: int) -> dict:
     """The shards of one process: n_shard / world consecutive shards starting at rank * that."""
     n = batch["remote"].shape[0] // world
@@ -341,9 +350,7 @@ def run_ours(args) -> None:
     settings["execution.device_ordinal"] = local_rank
     engine = capi.CEngine(settings)
     if world > 1:
-        handles = [None] * world
-        dist.all_gather_object(handles, engine.comm_export())
-        engine.comm_connect(b"".join(handles), world)
+        engine.comm_connect(exchange_handles(engine.comm_export(), world), world)
     engine.run("initialise_entities", {})
     rng = np.random.RandomState(2)
     n_rel = settings["model.n_relation_type"]

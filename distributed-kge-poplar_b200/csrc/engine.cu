@@ -211,7 +211,14 @@ size_t Engine::arena_offset_shard(unsigned local, int which) const {
     const size_t base = arena_offset_dense(3) + (size_t)local * per_shard;
     return base + (which == 0 ? 0 : which == 1 ? row_block : 2 * row_block);
 }
-size_t Engine::arena_size() const { return arena_offset_shard(n_local_, 0); }
+size_t Engine::arena_offset_predict(int which) const {
+    // gathered queries [n_shard, hr, D] | result scores | result rows, each [n_local, n_shard, hr, n_best]
+    const size_t queries = round_up((size_t)cfg_.n_shard * cfg_.predict_hr * cfg_.d * sizeof(float), 256);
+    const size_t results = round_up((size_t)n_local_ * cfg_.n_shard * cfg_.predict_hr * cfg_.predict_n_best * 4, 256);
+    const size_t base = arena_offset_shard(n_local_, 0);
+    return base + (which == 0 ? 0 : which == 1 ? queries : which == 2 ? queries + results : queries + 2 * results);
+}
+size_t Engine::arena_size() const { return arena_offset_predict(3); }
 
 Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     int count = 0;
@@ -341,6 +348,8 @@ void Engine::allocate() {
         b.dense_partial = (float*)(arena_ + arena_offset_shard(l, 2));
         b.send_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.grad_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+        b.predict_score_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+        b.predict_index_dst = (uint32_t**)device_alloc(sizeof(uint32_t*) * cfg_.n_shard);
     }
     d_epoch_ = (unsigned*)device_alloc(sizeof(unsigned));
     d_status_ = (unsigned*)device_alloc(sizeof(unsigned));
@@ -388,6 +397,18 @@ void Engine::build_pointer_tables() {
         }
         KGE_CUDA(cudaMemcpy(shards_[l].send_dst, send.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
         KGE_CUDA(cudaMemcpy(shards_[l].grad_dst, grad.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
+        // predict: results of tail shard `me` for the queries of shard d land in d's [d_local][me] block
+        std::vector<float*> pscore(cfg_.n_shard);
+        std::vector<uint32_t*> pindex(cfg_.n_shard);
+        const size_t result_block = (size_t)cfg_.predict_hr * cfg_.predict_n_best;
+        for (unsigned d = 0; d < cfg_.n_shard; ++d) {
+            uint8_t* base = peer_arena_[d / n_local_];
+            const size_t slot = ((size_t)(d % n_local_) * cfg_.n_shard + me) * result_block;
+            pscore[d] = (float*)(base + arena_offset_predict(1)) + slot;
+            pindex[d] = (uint32_t*)(base + arena_offset_predict(2)) + slot;
+        }
+        KGE_CUDA(cudaMemcpy(shards_[l].predict_score_dst, pscore.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
+        KGE_CUDA(cudaMemcpy(shards_[l].predict_index_dst, pindex.data(), sizeof(uint32_t*) * cfg_.n_shard, cudaMemcpyHostToDevice));
     }
     for (unsigned d = 0; d < cfg_.n_shard; ++d)
         partials[d] = (const float*)(peer_arena_[d / n_local_] + arena_offset_shard(d % n_local_, 2));
@@ -724,7 +745,7 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* remote = step_ptr(d_remote_, l, R);
         dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
         KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
-                                                        b.table, layout_, remote, (int)R, W0, W1, b.hid_h, b.hid_t)));
+                                                        b.table, layout_, remote, 0u, (int)R, W0, W1, b.hid_h, b.hid_t)));
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
@@ -813,8 +834,9 @@ void Engine::launch_one_step(unsigned step) {
                                                  b.table, layout_, remote, (int)R, b.d_hid_h, dh1, proj_splits_,
                                                  proj_rows_per_split_, b.proj_partial));
         }
-        const unsigned blocks = (unsigned)std::min<size_t>((n_dense_ + 255) / 256, 148 * 8);
-        KGE_LAUNCH("dense_partial", k_dense_partial<<<std::max(1u, blocks), 256, 0, stream_>>>(
+        const size_t proj_total = (size_t)cfg_.n_net() * proj_elems_;
+        const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 63) / 64, 148 * 16) : 0;
+        KGE_LAUNCH("dense_partial", k_dense_partial<<<n_rel + proj_blocks, 64, 0, stream_>>>(
                                         b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                         (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_, proj_elems_,
                                         b.dense_partial));
@@ -970,8 +992,119 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
     }
 }
 
-void Engine::cmd_predict(std::vector<HostArray>&) {
-    fail(KGE_INVALID_ARGUMENT, "command 'predict' is not available in this build");
+void Engine::ensure_predict_buffers() {
+    if (p_raw_) return;
+    const size_t Q = (size_t)cfg_.n_shard * cfg_.predict_hr, D = cfg_.d;
+    p_head_hidden_ = (float*)device_alloc((size_t)cfg_.predict_hr * D * 4);
+    p_chunk_hidden_ = (float*)device_alloc((size_t)kPredictChunk * D * 4);
+    p_raw_ = (float*)device_alloc(Q * kPredictChunk * 4);
+    d_iota_ = (uint32_t*)device_alloc((size_t)cfg_.predict_hr * 4);
+    std::vector<uint32_t> iota(cfg_.predict_hr);
+    for (unsigned i = 0; i < cfg_.predict_hr; ++i) iota[i] = i;
+    KGE_CUDA(cudaMemcpy(d_iota_, iota.data(), iota.size() * 4, cudaMemcpyHostToDevice));
+    for (ShardBuffers& b : shards_) {
+        b.topk_state = (unsigned long long*)device_alloc(Q * kTopkCapacity * sizeof(unsigned long long));
+        b.topk_count = (int*)device_alloc(Q * sizeof(int));
+    }
+}
+
+// Ranks every real row of the local shards as a tail for the queries of all shards
+// (src/poplar_kge.cpp:812-855): predicted tails of the local queries are written into every
+// process's query buffer (the all-gather of :825-828); each local shard then streams its table in
+// batches, scores them and keeps the n_best per query; the results go back to the asking shard's
+// process (the two all-to-alls of :847-850).
+void Engine::cmd_predict(std::vector<HostArray>& arrays) {
+    const size_t n = n_local_, hr = cfg_.predict_hr, nb = cfg_.predict_n_best, D = cfg_.d;
+    const size_t Q = (size_t)cfg_.n_shard * hr;
+    HostArray& head = find_array(arrays, "predict_head", KGE_U32, {n, hr});
+    HostArray& relation = find_array(arrays, "predict_relation", KGE_U32, {n, hr});
+    HostArray& count = find_array(arrays, "predict_entity_count", KGE_U32, {n});
+    HostArray& scores = find_array(arrays, "predict_scores", KGE_F32, {n, cfg_.n_shard, hr, nb});
+    HostArray& indices = find_array(arrays, "predict_indices", KGE_U32, {n, cfg_.n_shard, hr, nb});
+    if (nb == 0 || nb > kTopkCapacity / 2)
+        fail(KGE_INVALID_ARGUMENT, msg() << "'execution.predict_n_best' must be between 1 and " << kTopkCapacity / 2);
+    if (!connected_) fail(KGE_LOGIC_ERROR, "world_size > 1 but kge_comm_connect has not been called");
+    const uint32_t* h_head = static_cast<const uint32_t*>(head.data);
+    const uint32_t* h_rel = static_cast<const uint32_t*>(relation.data);
+    const uint32_t* h_count = static_cast<const uint32_t*>(count.data);
+    for (size_t i = 0; i < n * hr; ++i) {
+        if (h_head[i] >= cfg_.n_entity)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'predict_head' holds index " << h_head[i] << ", not below model.n_entity (" << cfg_.n_entity << ")");
+        if (h_rel[i] >= cfg_.n_relation_type)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'predict_relation' holds index " << h_rel[i] << ", not below model.n_relation_type (" << cfg_.n_relation_type << ")");
+    }
+    for (size_t l = 0; l < n; ++l)
+        if (h_count[l] >= cfg_.n_entity)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'predict_entity_count' (" << h_count[l] << ") must be below model.n_entity (" << cfg_.n_entity << ")");
+    ensure_predict_buffers();
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    uint32_t* d_head = d_rw_idx_;
+    uint32_t* d_rel = d_rw_idx_ + n * hr;
+    KGE_CUDA(cudaMemcpyAsync(d_head, h_head, n * hr * 4, cudaMemcpyHostToDevice, stream_));
+    KGE_CUDA(cudaMemcpyAsync(d_rel, h_rel, n * hr * 4, cudaMemcpyHostToDevice, stream_));
+
+    const bool two_nets = cfg_.n_net() == 2, vec = (D % 4) == 0;
+    const float* W_head = cfg_.n_net() >= 1 ? dense_ + dense_bounds_[1] : nullptr;
+    const float* W_tail = two_nets ? dense_ + dense_bounds_[2] : W_head;
+    const unsigned dtiles = ceil_div((unsigned)D, 64);
+    launch_counter_ = 0;
+
+    // 1. predicted tails of the local queries, written into every process's gathered query buffer
+    for (unsigned l = 0; l < n; ++l) {
+        dim3 grid(ceil_div((unsigned)hr, 64), dtiles, 1);
+        KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
+                                                                shards_[l].table, layout_, d_head + l * hr, 0u, (int)hr, W_head,
+                                                                nullptr, p_head_hidden_, nullptr)));
+        for (unsigned p = 0; p < cfg_.world; ++p) {
+            float* dst = (float*)(peer_arena_[p] + arena_offset_predict(0)) + (size_t)(shard0_ + l) * hr * D;
+            if (vec)
+                KGE_LAUNCH("predict_query", k_route<4><<<(unsigned)hr, 64, 0, stream_>>>(
+                                                p_head_hidden_, p_head_hidden_, nullptr, d_iota_, d_rel + l * hr, dense_, nullptr,
+                                                dst, 0, 1, (int)hr, (int)D, cfg_.score_fn));
+            else
+                KGE_LAUNCH("predict_query", k_route<1><<<(unsigned)hr, 64, 0, stream_>>>(
+                                                p_head_hidden_, p_head_hidden_, nullptr, d_iota_, d_rel + l * hr, dense_, nullptr,
+                                                dst, 0, 1, (int)hr, (int)D, cfg_.score_fn));
+        }
+    }
+    KGE_CUDA(cudaGetLastError());
+    launch_barrier();
+
+    // 2. stream each local shard's rows past all queries
+    const float* queries = (const float*)(arena_ + arena_offset_predict(0));
+    TopkParams tp{(int)Q, (int)nb, cfg_.score_fn == SCORE_TRANSE ? 1 : 0, cfg_.gamma};
+    for (unsigned l = 0; l < n; ++l) {
+        ShardBuffers& b = shards_[l];
+        KGE_CUDA(cudaMemsetAsync(b.topk_count, 0, Q * sizeof(int), stream_));
+        const uint32_t last = h_count[l];
+        for (uint32_t start = 1; start <= last; start += kPredictChunk) {
+            const unsigned c = std::min<uint32_t>(kPredictChunk, last - start + 1);
+            dim3 hgrid(ceil_div(c, 64), dtiles, 1);
+            KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<hgrid, 256, 0, stream_>>>(
+                                                                    b.table, layout_, nullptr, start, (int)c, W_tail, nullptr,
+                                                                    p_chunk_hidden_, nullptr)));
+            dim3 sgrid(ceil_div(c, 64), ceil_div((unsigned)Q, 32));
+            switch (cfg_.dist_fn) {
+                case DIST_L1: KGE_LAUNCH("predict_score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D)); break;
+                case DIST_L2: KGE_LAUNCH("predict_score", k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D)); break;
+                default: KGE_LAUNCH("predict_score", k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D)); break;
+            }
+            KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div((unsigned)Q, 4), 128, 0, stream_>>>(
+                                           p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp));
+        }
+        KGE_LAUNCH("predict_finish", k_topk_finish<<<(unsigned)Q, 128, 0, stream_>>>(
+                                         b.topk_state, b.topk_count, (int)Q, (int)hr, (int)nb, b.predict_score_dst,
+                                         b.predict_index_dst));
+        KGE_CUDA(cudaGetLastError());
+    }
+    launch_barrier();
+    const size_t result_bytes = n * cfg_.n_shard * hr * nb * 4;
+    KGE_CUDA(cudaMemcpyAsync(scores.data, arena_ + arena_offset_predict(1), result_bytes, cudaMemcpyDeviceToHost, stream_));
+    KGE_CUDA(cudaMemcpyAsync(indices.data, arena_ + arena_offset_predict(2), result_bytes, cudaMemcpyDeviceToHost, stream_));
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    timing_collect();
+    last_launches_ = launch_counter_;
+    check_device_status();
 }
 
 size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, size_t capacity) {

@@ -97,6 +97,10 @@ class Engine {
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
         float** grad_dst = nullptr;  // device table [n_shard]
+        float** predict_score_dst = nullptr;     // device table [n_shard]: where each asking shard's results go
+        uint32_t** predict_index_dst = nullptr;  // device table [n_shard]
+        unsigned long long* topk_state = nullptr;
+        int* topk_count = nullptr;
     };
 
     // set-up
@@ -105,6 +109,7 @@ class Engine {
     size_t arena_offset_flags() const { return 0; }
     size_t arena_offset_dense(int which) const;
     size_t arena_offset_shard(unsigned local, int which) const;
+    size_t arena_offset_predict(int which) const;
     size_t arena_size() const;
 
     // commands
@@ -166,6 +171,12 @@ class Engine {
     uint8_t* pinned_ = nullptr;
     size_t pinned_bytes_ = 0;
     bool staged_ = false;
+    // predict: buffers made on first use
+    void ensure_predict_buffers();
+    float *p_head_hidden_ = nullptr, *p_chunk_hidden_ = nullptr, *p_raw_ = nullptr;
+    uint32_t* d_iota_ = nullptr;
+    static constexpr unsigned kPredictChunk = 4096;  // table rows scored per pass
+
     uint32_t* d_rw_idx_ = nullptr;
     uint8_t* d_rw_data_ = nullptr;
 

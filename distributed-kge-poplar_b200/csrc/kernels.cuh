@@ -89,13 +89,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // ---------------------------------------------------------------------------
 // hidden = value + feature . W   (src/poplar_kge.cpp:439-467 with the gather of :405-410
 // folded in).  A [R, F] is read straight from the gathered table rows; W is [F, D].
+// Rows are table[remote[m]], or the consecutive rows row_base + m when `remote` is null
+// (the tail batches of predict, src/poplar_kge.cpp:836-839).
 // blockIdx.z picks the feature network (head / tail) when they are not shared.
 // 64x64 output tile, 16-deep k slices, 256 threads with a 4x4 register tile each.
 template <class ST, class FT>
 __global__ void __launch_bounds__(256)
-k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote, int R,
-         const float* __restrict__ W0, const float* __restrict__ W1, float* __restrict__ out0,
-         float* __restrict__ out1) {
+k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote,
+         uint32_t row_base, int R, const float* __restrict__ W0, const float* __restrict__ W1,
+         float* __restrict__ out0, float* __restrict__ out1) {
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ __align__(16) float As[BK][BM + 4];
     __shared__ __align__(16) float Bs[BK][BN];
@@ -109,7 +111,7 @@ k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restr
     const bool a_ok = m0 + a_row < R;
     const FT* __restrict__ a_ptr = nullptr;
     if (a_ok) {
-        const size_t row = remote[m0 + a_row];
+        const size_t row = remote ? remote[m0 + a_row] : row_base + (uint32_t)(m0 + a_row);
         a_ptr = reinterpret_cast<const FT*>(table + row * L.row_bytes + L.off_feat);
     }
     const int b_k = t >> 4, b_n = (t & 15) * 4;
@@ -169,7 +171,7 @@ k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restr
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;
         if (m >= R) continue;
-        const size_t row = remote[m];
+        const size_t row = remote ? remote[m] : row_base + (uint32_t)m;
         const ST* vp = reinterpret_cast<const ST*>(table + row * L.row_bytes);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -719,16 +721,30 @@ k_entity_update(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __rest
         float gh[V], gt[V];
 #pragma unroll
         for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
-        for (uint32_t q = q0; q < q1; ++q) {
-            const uint32_t e = perm[q];
-            const bool is_head = e < (uint32_t)B;
-            const float* src = is_head ? d_head + (size_t)e * D + c : grad_recv + (size_t)(e - B) * D + c;
-            if (V == 4) {
-                const float4 g = load4(src);
-                if (is_head) { gh[0] += g.x; gh[1 % V] += g.y; gh[2 % V] += g.z; gh[3 % V] += g.w; }
-                else { gt[0] += g.x; gt[1 % V] += g.y; gt[2 % V] += g.z; gt[3 % V] += g.w; }
-            } else {
-                if (is_head) gh[0] += src[0]; else gt[0] += src[0];
+        // Four lookups at a time: their loads are issued together, the sums stay in segment order.
+        for (uint32_t q = q0; q < q1; q += 4) {
+            uint32_t e[4];
+            float4 g[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e[u] = q + u < q1 ? perm[q + u] : 0xffffffffu;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e[u] == 0xffffffffu) continue;
+                const float* src = e[u] < (uint32_t)B ? d_head + (size_t)e[u] * D + c
+                                                      : grad_recv + (size_t)(e[u] - B) * D + c;
+                if (V == 4) g[u] = load4(src); else g[u].x = src[0];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (e[u] == 0xffffffffu) continue;
+                if (e[u] < (uint32_t)B) {
+                    gh[0] += g[u].x;
+                    if (V == 4) { gh[1 % V] += g[u].y; gh[2 % V] += g[u].z; gh[3 % V] += g[u].w; }
+                } else {
+                    gt[0] += g[u].x;
+                    if (V == 4) { gt[1 % V] += g[u].y; gt[2 % V] += g[u].z; gt[3 % V] += g[u].w; }
+                }
             }
         }
         const size_t o = (size_t)r * D + c;
@@ -861,26 +877,38 @@ k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t*
 // vector: relation table | projection(s).  Relation rows are the segment sums of the
 // per-triple relation gradients (backward of the gather at src/poplar_kge.cpp:489);
 // projection entries sum the split partials of k_projection_bwd in split order.
-static __global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(64)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
                 float* __restrict__ dense_partial) {
-    const size_t rel_elems = (size_t)n_rel * D;
-    const size_t total = rel_elems + (size_t)n_net * proj_elems;
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
-         e += (size_t)gridDim.x * blockDim.x) {
-        float g = 0.f;
-        if (e < rel_elems) {
-            const int rho = (int)(e / D), c = (int)(e - (size_t)rho * D);
-            for (uint32_t q = rel_off[rho]; q < rel_off[rho + 1]; ++q)
-                g += d_relrow[(size_t)rel_perm[q] * D + c];
-        } else {
-            const size_t pe = e - rel_elems;
-            const size_t net = pe / proj_elems, idx = pe - net * proj_elems;
-            for (int z = 0; z < splits; ++z) g += proj_partial[(net * splits + z) * proj_elems + idx];
+    if ((int)blockIdx.x < n_rel) {
+        // one relation row: sum its triples' gradients in position order, four loads in flight
+        const int rho = blockIdx.x;
+        const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            float g = 0.f;
+            for (uint32_t q = q0; q < q1; q += 4) {
+                float v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = q + u < q1 ? d_relrow[(size_t)rel_perm[q + u] * D + c] : 0.f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (q + u < q1) g += v[u];
+            }
+            dense_partial[(size_t)rho * D + c] = g;
         }
-        dense_partial[e] = g;
+        return;
+    }
+    const size_t rel_elems = (size_t)n_rel * D;
+    const size_t total = (size_t)n_net * proj_elems;
+    const size_t first = ((size_t)blockIdx.x - n_rel) * blockDim.x + threadIdx.x;
+    const size_t stride = ((size_t)gridDim.x - n_rel) * blockDim.x;
+    for (size_t pe = first; pe < total; pe += stride) {
+        const size_t net = pe / proj_elems, idx = pe - net * proj_elems;
+        float g = 0.f;
+        for (int z = 0; z < splits; ++z) g += proj_partial[(net * splits + z) * proj_elems + idx];
+        dense_partial[rel_elems + pe] = g;
     }
 }
 
@@ -956,6 +984,121 @@ static __global__ void k_barrier(BarrierArgs a) {
         __nanosleep(64);
     }
     __threadfence_system();
+}
+
+// ---------------------------------------------------------------------------
+// Streaming top-k of predict (src/poplar_kge.cpp:743-810): every query keeps its n_best
+// highest-scoring candidates so far; a batch of scores is merged by one warp per query.
+// Candidates that beat the query's current cut-off are appended to a per-warp buffer in
+// shared memory (warp ballot: the order is fixed) and the buffer is sorted down to n_best
+// when it fills.  Order: higher score first, ties by lower row index, so the result does not
+// depend on the batch size.  The reference leaves the tie order undefined.
+constexpr int kTopkCapacity = 256;  // entries per query buffer; n_best <= capacity / 2
+
+__device__ __forceinline__ unsigned long long topk_key(float score, uint32_t index) {
+    uint32_t bits = __float_as_uint(score);
+    bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);  // monotone in the float order
+    return ((unsigned long long)bits << 32) | (uint32_t)(~index);
+}
+__device__ __forceinline__ float topk_score(unsigned long long key) {
+    uint32_t bits = (uint32_t)(key >> 32);
+    bits = (bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits;
+    return __uint_as_float(bits);
+}
+__device__ __forceinline__ uint32_t topk_index(unsigned long long key) { return ~(uint32_t)key; }
+
+// Sorts the warp's buffer in descending key order (empty slots hold key 0, which sorts last).
+__device__ __forceinline__ void warp_sort_desc(unsigned long long* buf) {
+    const int lane = threadIdx.x & 31;
+    for (int k = 2; k <= kTopkCapacity; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            __syncwarp();
+            for (int i = lane; i < kTopkCapacity; i += 32) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long a = buf[i], b = buf[ixj];
+                    const bool descending = (i & k) == 0;
+                    if ((a < b) == descending) {
+                        buf[i] = b;
+                        buf[ixj] = a;
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+struct TopkParams {
+    int n_query, n_best;
+    int score_is_gamma_minus;  // TransE: score = gamma - raw
+    float gamma;
+};
+
+// raw [n_query, n_cols] holds distances / dot products against rows first_row .. first_row+n_cols-1;
+// rows above last_valid_row are padding of the shard and are skipped (src/poplar_kge.cpp:836-842).
+// state [n_query, kTopkCapacity] keys, counts [n_query].  4 warps per block, one query each.
+static __global__ void __launch_bounds__(128)
+k_topk_update(const float* __restrict__ raw, int n_cols, uint32_t first_row, uint32_t last_valid_row,
+              unsigned long long* __restrict__ state, int* __restrict__ counts, TopkParams tp) {
+    __shared__ unsigned long long buffers[4][kTopkCapacity];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q = blockIdx.x * 4 + warp;
+    if (q >= tp.n_query) return;
+    unsigned long long* buf = buffers[warp];
+    unsigned long long* mine = state + (size_t)q * kTopkCapacity;
+    int count = counts[q];
+    for (int i = lane; i < kTopkCapacity; i += 32) buf[i] = i < count ? mine[i] : 0ull;
+    __syncwarp();
+    unsigned long long cutoff = count >= tp.n_best ? buf[tp.n_best - 1] : 0ull;
+    const float* __restrict__ row = raw + (size_t)q * n_cols;
+    for (int base = 0; base < n_cols; base += 32) {
+        const int j = base + lane;
+        unsigned long long key = 0ull;
+        if (j < n_cols && first_row + (uint32_t)j <= last_valid_row) {
+            const float v = row[j];
+            key = topk_key(tp.score_is_gamma_minus ? tp.gamma - v : v, first_row + (uint32_t)j);
+        }
+        const bool pass = key > cutoff;
+        const unsigned mask = __ballot_sync(0xffffffffu, pass);
+        if (mask == 0) continue;
+        if (count + 32 > kTopkCapacity) {  // no room for a full ballot: sort down to n_best first
+            warp_sort_desc(buf);
+            count = min(count, tp.n_best);
+            for (int i = count + lane; i < kTopkCapacity; i += 32) buf[i] = 0ull;
+            __syncwarp();
+            cutoff = count >= tp.n_best ? buf[tp.n_best - 1] : 0ull;
+        }
+        const bool still = pass && key > cutoff;
+        const unsigned mask2 = __ballot_sync(0xffffffffu, still);
+        if (still) buf[count + __popc(mask2 & ((1u << lane) - 1))] = key;
+        count += __popc(mask2);
+        __syncwarp();
+    }
+    warp_sort_desc(buf);
+    count = min(count, tp.n_best);
+    for (int i = lane; i < kTopkCapacity; i += 32) mine[i] = i < count ? buf[i] : 0ull;
+    if (lane == 0) counts[q] = count;
+}
+
+// Writes each query's sorted candidates to the shard that asked: query q = (asking shard, slot)
+// goes to out_blocks[asking shard] + slot * n_best (the return all-to-all of
+// src/poplar_kge.cpp:847-850).  Missing candidates get the reference's BadScore and row 0.
+static __global__ void __launch_bounds__(128)
+k_topk_finish(const unsigned long long* __restrict__ state, const int* __restrict__ counts, int n_query,
+              int queries_per_shard, int n_best, float* const* __restrict__ score_blocks,
+              uint32_t* const* __restrict__ index_blocks) {
+    const int q = blockIdx.x;
+    if (q >= n_query) return;
+    const int shard = q / queries_per_shard, slot = q - shard * queries_per_shard;
+    float* __restrict__ so = score_blocks[shard] + (size_t)slot * n_best;
+    uint32_t* __restrict__ io = index_blocks[shard] + (size_t)slot * n_best;
+    const int count = counts[q];
+    for (int i = threadIdx.x; i < n_best; i += blockDim.x) {
+        const unsigned long long key = state[(size_t)q * kTopkCapacity + i];
+        so[i] = i < count ? topk_score(key) : -1e6f;
+        io[i] = i < count ? topk_index(key) : 0u;
+    }
 }
 
 // ---------------------------------------------------------------------------

@@ -168,13 +168,19 @@ def all_to_all(blocks: np.ndarray) -> np.ndarray:
     return np.swapaxes(blocks, 0, 1)
 
 
+def _f32(x) -> np.float32:
+    """The engine holds its hyper-parameters as C++ ``float`` (src/poplar_kge.cpp:167-179, 213-216),
+    so constants derived from them, like 1 - beta, are float32 arithmetic on float32 values."""
+    return np.float32(x)
+
+
 def adam_step_size(step: int, lr, beta_m: float, beta_v: float, dtype) -> np.ndarray:
     """lr * sqrt(1 - beta_v^t) / (1 - beta_m^t) with ``t`` already incremented.
 
     src/fructose/frnn.cpp:42-59.
     """
     t = dtype(step)
-    return (np.sqrt(1 - dtype(beta_v) ** t) / (1 - dtype(beta_m) ** t)) * dtype(lr)
+    return (np.sqrt(1 - dtype(_f32(beta_v)) ** t) / (1 - dtype(_f32(beta_m)) ** t)) * dtype(_f32(lr))
 
 
 def adam_update(x, m, v, grad, step_size, cfg: StepConfig):
@@ -182,11 +188,12 @@ def adam_update(x, m, v, grad, step_size, cfg: StepConfig):
     decoupled weight decay).  src/fructose/frnn.cpp:61-90.
     """
     dt = x.dtype.type
-    m *= dt(cfg.adam_beta_m)
-    m += dt(1 - cfg.adam_beta_m) * grad
-    v *= dt(cfg.adam_beta_v)
-    v += dt(1 - cfg.adam_beta_v) * grad * grad
-    x -= step_size * (m / (np.sqrt(v) + dt(cfg.adam_epsilon)) + dt(cfg.weight_decay) * x)
+    beta_m, beta_v = _f32(cfg.adam_beta_m), _f32(cfg.adam_beta_v)
+    m *= dt(beta_m)
+    m += dt(_f32(1) - beta_m) * grad
+    v *= dt(beta_v)
+    v += dt(_f32(1) - beta_v) * grad * grad
+    x -= step_size * (m / (np.sqrt(v) + dt(_f32(cfg.adam_epsilon))) + dt(_f32(cfg.weight_decay)) * x)
 
 
 # ---------------------------------------------------------------------------
@@ -246,7 +253,7 @@ def score(cfg: StepConfig, p: np.ndarray, tails: np.ndarray):
     """
     dist = _distance(cfg, p, tails)
     if cfg.score_fn == "TransE":
-        return p.dtype.type(cfg.gamma) - dist, dist
+        return p.dtype.type(_f32(cfg.gamma)) - dist, dist
     return dist, dist
 
 
@@ -265,11 +272,11 @@ def loss_logsigmoid(cfg: StepConfig, scores: np.ndarray, labels: np.ndarray):
     n_tail = cfg.n_tail
     onehot = np.zeros_like(scores)
     onehot[np.arange(scores.shape[0]), labels] = 1
-    w_neg = dt((0.5 * n_tail) / (n_tail - 1))
-    w_pos = dt(0.5 * n_tail)
+    w_neg = dt(_f32(0.5 * n_tail) / _f32(n_tail - 1))  # float arithmetic in the reference (:619-620)
+    w_pos = dt(_f32(0.5 * n_tail))
     weight = (w_pos - w_neg) * onehot + w_neg
     if cfg.negative_adversarial_scale > 0:  # :623-633, softmax is detached
-        z = dt(cfg.negative_adversarial_scale) * scores + dt(-10000.0) * onehot
+        z = dt(_f32(cfg.negative_adversarial_scale)) * scores + dt(-10000.0) * onehot
         z = z - z.max(axis=-1, keepdims=True)
         soft = np.exp(z)
         soft /= soft.sum(axis=-1, keepdims=True)
@@ -404,7 +411,7 @@ class Oracle:
             pred = predict_tail(cfg, heads[s], r)
             scores, dist = score(cfg, pred, tails[s])
             losses[s], dscores = loss_and_grad(cfg, scores, tail[s])
-            dscores = dscores * dt(cfg.loss_scale)  # root gradient, never unscaled (:691)
+            dscores = dscores * dt(_f32(cfg.loss_scale))  # root gradient, never unscaled (:691)
             d_pred, d_tails[s] = score_grad(cfg, pred, tails[s], dist, dscores)
             d_head, d_r = predict_tail_grad(cfg, heads[s], r, d_pred)
             d_rel += scatter_add_rows(rel.shape[0], relation[s], d_r)
@@ -433,7 +440,7 @@ class Oracle:
         self.step += 1
         alpha = adam_step_size(self.step, lr, cfg.adam_beta_m, cfg.adam_beta_v, dt)
         for name, grad in grads.items():
-            mod = dt(cfg.learning_rate_modifiers.get(name, 1.0))
+            mod = dt(_f32(cfg.learning_rate_modifiers.get(name, 1.0)))
             adam_update(
                 self.variables[name],
                 self.variables[name + "/adam_m"],
@@ -443,7 +450,7 @@ class Oracle:
                 cfg,
             )
         adam_v = sqrt_v * sqrt_v
-        mod = dt(cfg.learning_rate_modifiers.get("entity_embedding", 1.0))
+        mod = dt(_f32(cfg.learning_rate_modifiers.get("entity_embedding", 1.0)))
         adam_update(value, adam_m, adam_v, d_value, alpha * mod, cfg)
         new_rows = np.concatenate([value, adam_m, np.sqrt(adam_v), feat], axis=-1)
         for s in range(n):

@@ -189,9 +189,10 @@ def test_hand_derived_backward_matches_autograd(variant):
             loss = torch.nn.functional.cross_entropy(scores + shift * (1 - onehot), idx["tail"][s], reduction="sum") / (n * cfg.batch_size)
         else:
             T = cfg.n_tail
-            weight = onehot * (0.5 * T - 0.5 * T / (T - 1)) + 0.5 * T / (T - 1)
+            w_pos, w_neg = float(np.float32(0.5 * T)), float(np.float32(0.5 * T) / np.float32(T - 1))
+            weight = onehot * (w_pos - w_neg) + w_neg
             if cfg.negative_adversarial_scale:
-                soft = torch.softmax(cfg.negative_adversarial_scale * scores.detach() - 10000.0 * onehot, dim=1)
+                soft = torch.softmax(float(np.float32(cfg.negative_adversarial_scale)) * scores.detach() - 10000.0 * onehot, dim=1)
                 weight = weight * (onehot + (T - 1) * soft)
             loss = -(weight * torch.nn.functional.logsigmoid((2 * onehot - 1) * scores)).sum() / (n * cfg.batch_size * cfg.a2a_size * n)
         np.testing.assert_allclose(float(loss.detach()), losses[s], rtol=1e-10)
