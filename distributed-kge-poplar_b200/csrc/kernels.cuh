@@ -975,6 +975,8 @@ static __global__ void k_barrier(BarrierArgs a) {
     __threadfence_system();
     *remote_flag = epoch;
     volatile unsigned* mine = a.peer_flags[a.rank] + r;
+    // Once a wait has given up, the run is lost: later barriers of the same run do not wait again.
+    if (*reinterpret_cast<volatile unsigned*>(a.status) != 0) return;
     unsigned long long spins = 0;
     while ((int)(*mine - epoch) < 0) {
         if (++spins > a.max_spins) {

@@ -1,0 +1,147 @@
+"""Sharded ranking ("predict") and the host-side Engine wrapper, on the GPU.
+
+Scores are checked against the float64 oracle (1e-5 relative) and against predictions recorded
+from the reference's torch model; candidate rows must be identical wherever the oracle's scores
+are not tied within rounding.  Ties are broken by ascending row, a rule of this engine (the
+reference leaves the order undefined)."""
+
+import numpy as np
+import pytest
+
+from distributed_kge_poplar_b200 import capi, poplar_kge as kge
+from helpers import engine_settings, make_oracle, random_state, write_state
+from oracle.step_oracle import StepConfig
+from test_engine_gpu import _golden
+
+pytestmark = pytest.mark.gpu
+RW = 64
+
+
+def _predict(engine, cfg, queries, counts, hr, n_best):
+    """Host side of predict as the reference's wrapper does it (src/python/poplar_kge.py:782-861):
+    queries bucketed by head shard into chunks of hr, per-shard results merged with top-k + sort."""
+    n = cfg.n_shard
+    out_idx = np.zeros((len(queries), n_best, 2), np.uint32)
+    out_score = np.zeros((len(queries), n_best), np.float32)
+    per_shard = [np.flatnonzero(queries[:, 0] == s) for s in range(n)]
+    for lo in range(0, max(len(x) for x in per_shard), hr):
+        head = np.zeros((n, hr), np.uint32)
+        rel = np.zeros((n, hr), np.uint32)
+        picks = [x[lo : lo + hr] for x in per_shard]
+        for s, rows in enumerate(picks):
+            head[s, : len(rows)] = queries[rows, 1]
+            rel[s, : len(rows)] = queries[rows, 2]
+        scores = np.full((n, n, hr, n_best), np.nan, np.float32)
+        indices = np.zeros((n, n, hr, n_best), np.uint32)
+        engine.run("predict", dict(predict_head=head, predict_relation=rel,
+                                   predict_entity_count=np.ascontiguousarray(counts, dtype=np.uint32),
+                                   predict_scores=scores, predict_indices=indices))
+        for s, rows in enumerate(picks):
+            for k, qi in enumerate(rows):
+                cand_score = scores[s, :, k].reshape(-1)
+                cand_shard = np.repeat(np.arange(n), n_best)
+                cand_row = indices[s, :, k].reshape(-1)
+                order = np.lexsort((cand_row, cand_shard, -cand_score))[:n_best]
+                out_score[qi] = cand_score[order]
+                out_idx[qi, :, 0], out_idx[qi, :, 1] = cand_shard[order], cand_row[order]
+    return out_idx, out_score
+
+
+def _clear(score, tol=1e-5):
+    """Positions whose score differs from both neighbours by more than rounding."""
+    gaps = np.abs(np.diff(score, axis=1)) > tol * np.maximum(1.0, np.abs(score[:, 1:]))
+    return np.concatenate([gaps[:, :1], gaps[:, :-1] & gaps[:, 1:], gaps[:, -1:]], axis=1)
+
+
+@pytest.mark.parametrize("score_fn,distance_fn", [("TransE", "L1"), ("TransE", "L2"), ("DistMult", "MatMul"), ("ComplEx", "MatMul")])
+def test_predict_matches_oracle(score_fn, distance_fn):
+    cfg = StepConfig(n_shard=3, n_entity=700, n_relation_type=6, embedding_size=32, entity_feature_size=12,
+                     batch_size=6, a2a_size=4, score_fn=score_fn, distance_fn=distance_fn, gamma=5.0)
+    hr, n_best = 8, 5
+    state = random_state(cfg, 21, warm=False)
+    engine = capi.CEngine(engine_settings(cfg, rw_batch=RW))
+    write_state(engine, cfg, state, RW)
+    oracle = make_oracle(cfg, state)
+    counts = np.array([699, 650, 3])  # a shard with fewer real rows than n_best
+    rng = np.random.RandomState(4)
+    queries = np.stack([rng.randint(3, size=21), 1 + rng.randint(600, size=21), rng.randint(6, size=21)], axis=1)
+    queries[queries[:, 0] == 2, 1] = 1 + queries[queries[:, 0] == 2, 1] % 3
+    got_idx, got_score = _predict(engine, cfg, queries, counts, hr, n_best)
+    want_idx, want_score = oracle.predict(queries, counts, n_best)
+    np.testing.assert_allclose(got_score, want_score, rtol=1e-5, atol=1e-5)
+    clear = _clear(want_score)
+    np.testing.assert_array_equal(got_idx[clear], want_idx[clear])
+    assert np.all(got_idx[..., 1] >= 1) and np.all(got_idx[..., 1] <= counts[got_idx[..., 0]])
+    engine.close()
+
+
+def test_predict_ties_are_broken_by_row():
+    cfg = StepConfig(n_shard=1, n_entity=300, n_relation_type=2, embedding_size=8, entity_feature_size=0,
+                     batch_size=4, a2a_size=4, score_fn="TransE", distance_fn="L1", gamma=1.0)
+    state = random_state(cfg, 3)
+    state["entity_data"][0, 1:, :8] = state["entity_data"][0, 1:2, :8]  # every row identical: all scores tie
+    engine = capi.CEngine(engine_settings(cfg, rw_batch=RW))
+    write_state(engine, cfg, state, RW)
+    idx, score = _predict(engine, cfg, np.array([[0, 5, 1]]), np.array([299]), 8, 5)
+    np.testing.assert_array_equal(idx[0, :, 1], [1, 2, 3, 4, 5])
+    assert np.all(score[0] == score[0, 0])
+    engine.close()
+
+
+@pytest.mark.parametrize("case", ["demo", "mid"])
+def test_predict_matches_reference_model(case):
+    g, s, cfg = _golden(case)
+    hr, n_best = int(s["execution.predict_hr_batch_size"]), int(s["execution.predict_n_best"])
+    engine = capi.CEngine(engine_settings(cfg, rw_batch=RW, **{"execution.predict_hr_batch_size": hr,
+                                                              "execution.predict_n_best": n_best}))
+    write_state(engine, cfg, {k[len("final/") :]: g[k] for k in g.files if k.startswith("final/")} | {"step": np.zeros(cfg.n_shard, np.uint32)}, RW)
+    idx, score = _predict(engine, cfg, g["predict/queries"].astype(np.int64), g["shard_to_count"], hr, n_best)
+    np.testing.assert_allclose(score, g["predict/score"], rtol=1e-4, atol=1e-5)
+    clear = _clear(g["predict/score"], 1e-4)
+    np.testing.assert_array_equal(idx[clear], g["predict/shard_idx"][clear])
+    engine.close()
+
+
+def test_engine_wrapper_operations():
+    """The reference's test_engine_ops (tests/python/test_poplar_kge.py:111-172) on the host-side
+    twin of its Engine class: initialise, train twice on one batch, variable round trip, features
+    read back from the rows, predictions well-formed and sorted."""
+    settings = kge.Settings.create_demo()
+    settings.seed = 100
+    settings.training.learning_rate = 0.01
+    settings.prepare()
+    m, e = settings.model, settings.execution
+    engine = kge.Engine(settings, np.full(m.n_shard, m.n_entity - 1))
+    features = engine.random_normal((m.n_shard, m.n_entity, m.entity_feature_size), np.float16)
+    features[:, 0, :] = 0
+    with pytest.raises(ValueError, match="uninitialised"):
+        engine.train_step_loop(None)
+    engine.initialise_all(features.astype(np.float32))
+
+    n_step, bshape = e.train_steps_per_program_run, (m.n_shard, e.train_steps_per_program_run)
+    remote = np.stack([np.sort(engine.random.permutation(np.arange(1, m.n_entity))[: settings.n_remote])
+                       for _ in range(m.n_shard * n_step)]).reshape(bshape + (settings.n_remote,)).astype(np.uint32)
+    batch = kge.Batch(remote=remote, a2a=engine.random_integers(settings.n_remote, bshape + (m.n_shard, settings.data.a2a_size)),
+                      head=engine.random_integers(settings.n_remote, bshape + (settings.data.batch_size,)),
+                      relation=engine.random_integers(m.n_relation_type, bshape + (settings.data.batch_size,)),
+                      tail=engine.random_integers(settings.n_tail, bshape + (settings.data.batch_size,)))
+    loss_0, _ = engine.train_step_loop(batch)
+    loss_1, _ = engine.train_step_loop(batch)
+    assert loss_1 < loss_0
+    assert engine.read_variable("step")[0] == 2 * n_step
+
+    new_relations = engine.random_normal(engine.variable_to_shape["relation_embedding"])
+    assert not np.allclose(engine.read_variable("relation_embedding"), new_relations)
+    engine.write_variable("relation_embedding", new_relations)
+    np.testing.assert_allclose(engine.read_variable("relation_embedding"), new_relations)
+    np.testing.assert_allclose(engine.read_entity_all()[:, :, -m.entity_feature_size :], features.astype(np.float32))
+
+    n_predict = e.predict_hr_batch_size + 5
+    queries = np.stack([engine.random_integers(m.n_shard, (n_predict,)), 1 + engine.random_integers(m.n_entity - 1, (n_predict,)),
+                        engine.random_integers(m.n_relation_type, (n_predict,))], axis=-1)
+    predictions = engine.predict(queries)
+    assert predictions.shard_idx.shape == (n_predict, e.predict_n_best, 2)
+    assert np.all(np.isin(predictions.shard_idx[:, :, 0], np.arange(m.n_shard)))
+    assert np.all(np.isin(predictions.shard_idx[:, :, 1], np.arange(1, m.n_entity)))
+    assert predictions.score.shape == (n_predict, e.predict_n_best) and not np.any(np.isnan(predictions.score))
+    np.testing.assert_equal(predictions.score, np.sort(predictions.score, axis=-1)[..., ::-1])
