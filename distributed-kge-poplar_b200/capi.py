@@ -29,6 +29,7 @@ SYMBOLS = (
     "kge_stage_batch", "kge_train_staged", "kge_last_run_stats", "kge_set_kernel_timing",
     "kge_kernel_time_count", "kge_kernel_time", "kge_debug_fetch",
     "kge_op_pairwise", "kge_op_pairwise_grad", "kge_op_gather_rows", "kge_op_scatter_add_rows",
+    "kge_op_scatter_add_rows_noalloc",
     "kge_op_activation", "kge_op_all_to_all",
 )
 
@@ -80,6 +81,7 @@ def load_library() -> C.CDLL:
     lib.kge_op_pairwise_grad.argtypes = [C.c_int, fp, fp, fp, sz, sz, sz, fp, fp]
     lib.kge_op_gather_rows.argtypes = [fp, sz, sz, u32p, sz, fp]
     lib.kge_op_scatter_add_rows.argtypes = [fp, u32p, sz, sz, sz, fp]
+    lib.kge_op_scatter_add_rows_noalloc.argtypes = [vp, vp, sz, sz, sz, vp, vp]
     lib.kge_op_activation.argtypes = [C.c_int, fp, fp, sz, sz, fp, fp]
     lib.kge_op_all_to_all.argtypes = [fp, sz, sz, fp]
     _lib = lib
@@ -276,6 +278,14 @@ def op_scatter_add_rows(grad_rows, indices, rows: int) -> np.ndarray:
     _op_check(load_library().kge_op_scatter_add_rows(_fp(g), idx.ctypes.data_as(C.POINTER(C.c_uint32)),
                                                      idx.size, rows, g.shape[1], _fp(out)))
     return out
+
+
+def op_scatter_add_rows_noalloc(grad_rows_ptr: int, indices_ptr: int, n: int, rows: int, width: int,
+                                grad_table_ptr: int, stream_ptr: int = 0) -> None:
+    """The allocation-free scatter-add on caller-owned DEVICE buffers (raw addresses); queued on
+    ``stream_ptr`` (a cudaStream_t as an integer, 0 = default stream), not waited for."""
+    _op_check(load_library().kge_op_scatter_add_rows_noalloc(grad_rows_ptr, indices_ptr, n, rows, width,
+                                                             grad_table_ptr, stream_ptr or None))
 
 
 def op_activation(kind: int, x, grad_out) -> Tuple[np.ndarray, np.ndarray]:

@@ -1,6 +1,7 @@
 // extern "C" surface of include/kge_b200.h: argument marshalling and error mapping for the
 // engine, and the single-operator entry points.
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "engine.hpp"
@@ -344,6 +345,72 @@ int kge_op_all_to_all(const float* in, size_t n_shard, size_t block, float* out)
             finish_kernels();
         }
         to_host(out, dout, total * 4);
+    });
+}
+
+// ---------------------------------------------------------------------------
+// Scatter-add for callers that must not allocate.
+//
+// The sort-and-segment scatter-add needs working memory beyond its inputs and outputs: the
+// lookups ordered by row and the start of each row's segment.  kge_op_scatter_add_rows gets it
+// from cudaMalloc.  Some callers cannot: a plugin running inside another framework's memory
+// pool, where a raw cudaMalloc fragments or exceeds the pool's budget; a service with a fixed
+// device-memory reservation; code on a latency path where the implicit device synchronisation
+// of cudaMalloc / cudaFree is not acceptable.  For them the working memory is this fixed array
+// in the library's own device image.  Every GPU that loads the library holds it (about 290 KB)
+// until the process exits.
+constexpr size_t kNoAllocMaxLookups = kMaxSortItems;  // 4096
+constexpr size_t kNoAllocMaxRows = 65536;
+
+struct NoAllocScratch {
+    uint32_t perm[kNoAllocMaxLookups];      // lookups ordered by (row, position)
+    uint32_t offsets[kNoAllocMaxRows + 1];  // segment start of each table row
+    uint32_t spare_perm[kNoAllocMaxLookups];
+    uint32_t spare_offsets[4];
+};
+
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[sizeof(NoAllocScratch)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_no_alloc_mutex;
+NoAllocScratch* g_no_alloc_ptr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; the kernels need its address on the current
+// device, which the runtime hands out per device.
+NoAllocScratch* no_alloc_scratch_for_current_device() {
+    int device = -1;
+    KGE_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) fail(KGE_RUNTIME_ERROR, "kge_op_scatter_add_rows_noalloc: device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (!g_no_alloc_ptr[device]) {
+        void* ptr = nullptr;
+        KGE_CUDA(cudaGetSymbolAddress(&ptr, g_no_alloc_scratch));
+        g_no_alloc_ptr[device] = static_cast<NoAllocScratch*>(ptr);
+    }
+    return g_no_alloc_ptr[device];
+}
+}  // namespace
+
+int kge_op_scatter_add_rows_noalloc(const float* grad_rows, const uint32_t* indices, size_t n, size_t rows, size_t width,
+                                    float* grad_table, void* cuda_stream) {
+    return guarded(g_error, [&] {
+        require(grad_rows && indices && grad_table, "kge_op_scatter_add_rows_noalloc: null argument");
+        if (n > kNoAllocMaxLookups)
+            fail(KGE_INVALID_ARGUMENT, msg() << "kge_op_scatter_add_rows_noalloc: " << n << " lookups exceed the fixed working memory ("
+                                             << kNoAllocMaxLookups << " lookups)");
+        if (rows > kNoAllocMaxRows)
+            fail(KGE_INVALID_ARGUMENT, msg() << "kge_op_scatter_add_rows_noalloc: " << rows << " table rows exceed the fixed working memory ("
+                                             << kNoAllocMaxRows << " rows)");
+        if (rows == 0 || width == 0) return;
+        NoAllocScratch* scratch = no_alloc_scratch_for_current_device();
+        cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+        // Every entry the second kernel reads (perm[0, n) and offsets[0, rows]) is rewritten by the
+        // first, so nothing left by an earlier call is ever read and nothing needs clearing.
+        k_prepare_segments<<<1, 512, 0, stream>>>(indices, indices, indices, nullptr, (int)n, 0, (int)rows, 0, scratch->perm,
+                                                  scratch->offsets, scratch->spare_perm, scratch->spare_offsets, nullptr);
+        k_segment_sum_rows<<<(unsigned)rows, 128, 0, stream>>>(grad_rows, scratch->perm, scratch->offsets, width, grad_table);
+        KGE_CUDA(cudaGetLastError());
     });
 }
 

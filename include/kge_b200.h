@@ -164,6 +164,28 @@ int kge_op_gather_rows(const float* table, size_t rows, size_t width, const uint
                        size_t n, float* out);
 int kge_op_scatter_add_rows(const float* grad_rows, const uint32_t* indices, size_t n, size_t rows,
                             size_t width, float* grad_table);
+/*
+ * kge_op_scatter_add_rows for callers that cannot allocate device memory.  It has no counterpart
+ * in the reference.  The operator's working memory (the sorted lookups and the per-row segment
+ * starts) lives in a fixed array inside the library's device image instead of coming from
+ * cudaMalloc, so this entry point calls no cudaMalloc, cudaFree or allocating library routine.
+ * That is for hosts where an allocation is not allowed or not affordable: an operator running
+ * inside a framework's caching allocator or a fixed memory reservation, or on a path that must not
+ * take the device-wide synchronisation an allocation implies.
+ *   - grad_rows [n, width], indices [n] and grad_table [rows, width] are DEVICE pointers owned by
+ *     the caller; the work is queued on `cuda_stream` (a cudaStream_t, or NULL for the default
+ *     stream) and the call returns without waiting for it.
+ *   - Limits: n <= 4096 lookups, rows <= 65536; larger sizes are refused with KGE_INVALID_ARGUMENT.
+ *     The array costs about 290 KB on every GPU that loads the library, until the process exits.
+ *   - An index >= rows cannot be refused here (the indices are on the device): it is ignored.
+ *   - The first call on a device looks up the array's address on that device (the device must be
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on one device share the array.  Nothing in it needs clearing between calls (each
+ *     call rewrites every entry it reads), but two calls whose kernels overlap on the GPU, from
+ *     different streams or threads, race on it: keep them ordered.
+ */
+int kge_op_scatter_add_rows_noalloc(const float* grad_rows, const uint32_t* indices, size_t n, size_t rows,
+                                    size_t width, float* grad_table, void* cuda_stream);
 /* Row-wise losses with gradients: kind 0 = guarded log-sigmoid (src/pag/pag.cpp:888-910,
  * elementwise, grad_x = grad_out * d/dx), kind 1 = log-softmax over the last axis (:841-864). */
 int kge_op_activation(int kind, const float* x, const float* grad_out, size_t rows, size_t cols,
