@@ -29,7 +29,7 @@ SYMBOLS = (
     "kge_stage_batch", "kge_train_staged", "kge_last_run_stats", "kge_set_kernel_timing",
     "kge_kernel_time_count", "kge_kernel_time", "kge_debug_fetch",
     "kge_op_pairwise", "kge_op_pairwise_grad", "kge_op_gather_rows", "kge_op_scatter_add_rows",
-    "kge_op_scatter_add_rows_noalloc",
+    "kge_op_scatter_add_rows_noalloc", "kge_op_tc_gemm",
     "kge_op_activation", "kge_op_all_to_all",
 )
 
@@ -82,6 +82,8 @@ def load_library() -> C.CDLL:
     lib.kge_op_gather_rows.argtypes = [fp, sz, sz, u32p, sz, fp]
     lib.kge_op_scatter_add_rows.argtypes = [fp, u32p, sz, sz, sz, fp]
     lib.kge_op_scatter_add_rows_noalloc.argtypes = [vp, vp, sz, sz, sz, vp, vp]
+    lib.kge_op_tc_gemm.argtypes = [vp, C.c_int, C.c_int, u32p, sz, sz, fp, C.c_int, sz, sz, sz, sz, sz, C.c_int, fp,
+                                   C.c_int, C.c_int, fp]
     lib.kge_op_activation.argtypes = [C.c_int, fp, fp, sz, sz, fp, fp]
     lib.kge_op_all_to_all.argtypes = [fp, sz, sz, fp]
     _lib = lib
@@ -286,6 +288,24 @@ def op_scatter_add_rows_noalloc(grad_rows_ptr: int, indices_ptr: int, n: int, ro
     ``stream_ptr`` (a cudaStream_t as an integer, 0 = default stream), not waited for."""
     _op_check(load_library().kge_op_scatter_add_rows_noalloc(grad_rows_ptr, indices_ptr, n, rows, width,
                                                              grad_table_ptr, stream_ptr or None))
+
+
+def op_tc_gemm(a, b, m: int, n: int, k: int, a_transposed: bool = False, b_transposed: bool = False, a_gather=None,
+               epilogue: int = 0, x=None, splits: int = 1, tile_n: int = 128) -> np.ndarray:
+    """Tensor-core contraction out[z, m, n] (see kge_op_tc_gemm); ``a`` may be float16 or float32."""
+    a = np.ascontiguousarray(a)
+    if a.dtype not in (np.float16, np.float32):
+        a = a.astype(np.float32)
+    b = _f32(b)
+    gather = np.ascontiguousarray(a_gather, dtype=np.uint32) if a_gather is not None else None
+    xx = _f32(x) if x is not None else None
+    out = np.empty((splits, m, n), np.float32)
+    _op_check(load_library().kge_op_tc_gemm(
+        a.ctypes.data, int(a.dtype == np.float16), int(a_transposed),
+        gather.ctypes.data_as(C.POINTER(C.c_uint32)) if gather is not None else None, a.shape[0], a.shape[1],
+        _fp(b), int(b_transposed), b.shape[0], b.shape[1], m, n, k, epilogue, _fp(xx) if xx is not None else None,
+        splits, tile_n, _fp(out)))
+    return out
 
 
 def op_activation(kind: int, x, grad_out) -> Tuple[np.ndarray, np.ndarray]:

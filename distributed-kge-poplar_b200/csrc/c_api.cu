@@ -5,6 +5,7 @@
 #include <vector>
 
 #include "engine.hpp"
+#include "tc_gemm.cuh"
 
 using namespace kge;
 
@@ -345,6 +346,63 @@ int kge_op_all_to_all(const float* in, size_t n_shard, size_t block, float* out)
             finish_kernels();
         }
         to_host(out, dout, total * 4);
+    });
+}
+
+// Operator form of the tensor-core contraction (tc_gemm.cuh) on host buffers:
+//   out[z, m, n] = epilogue( sum_{k in split z} A[m, k] * B[n, k] )
+// `a` is the stored A matrix [a_rows, a_cols] (fp32 or fp16), read as A[m, k] = a[m, k], or
+// a[k, m] when a_transposed; its stored rows may be picked by `a_gather`.  `b` likewise (fp32).
+int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* a_gather, size_t a_rows, size_t a_cols,
+                   const float* b, int b_transposed, size_t b_rows, size_t b_cols, size_t m, size_t n, size_t k,
+                   int epilogue, const float* x, int splits, int tile_n, float* out) {
+    return guarded(g_error, [&] {
+        require(a && b && out, "kge_op_tc_gemm: null argument");
+        require(epilogue >= 0 && epilogue <= 2 && (epilogue == 0 || x), "kge_op_tc_gemm: bad epilogue or missing x");
+        require(splits >= 1 && (tile_n == 64 || tile_n == 128), "kge_op_tc_gemm: splits >= 1 and tile_n in {64, 128}");
+        require(m > 0 && n > 0, "kge_op_tc_gemm: empty output");
+        const size_t ea = a_half ? 2 : 4;
+        const size_t gather_len = a_transposed ? k : m;
+        if (a_gather)
+            for (size_t i = 0; i < gather_len; ++i)
+                if (a_gather[i] >= a_rows) fail(KGE_INVALID_ARGUMENT, "kge_op_tc_gemm: gather index out of range");
+        require(a_gather || a_rows >= (a_transposed ? k : m), "kge_op_tc_gemm: a has too few rows");
+        require(a_cols >= (a_transposed ? m : k), "kge_op_tc_gemm: a has too few columns");
+        require(b_rows >= (b_transposed ? k : n) && b_cols >= (b_transposed ? n : k), "kge_op_tc_gemm: b is too small");
+        DeviceBuffer da(a_rows * a_cols * ea), db(b_rows * b_cols * 4), dout((size_t)splits * m * n * 4), dx(m * n * 4);
+        DeviceBuffer dg(gather_len * 4), dstatus(4);
+        to_device(da, a, a_rows * a_cols * ea);
+        to_device(db, b, b_rows * b_cols * 4);
+        if (x) to_device(dx, x, m * n * 4);
+        if (a_gather) to_device(dg, a_gather, gather_len * 4);
+        KGE_CUDA(cudaMemset(dstatus.p, 0, 4));
+        tc::GemmArgs g{};
+        g.A = tc::make_operand(da.p, (long long)(a_cols * ea), a_half != 0, a_transposed != 0, a_gather ? dg.as<uint32_t>() : nullptr);
+        g.B = tc::make_operand(db.p, (long long)(b_cols * 4), false, b_transposed != 0);
+        g.M = (int)m; g.N = (int)n; g.K = (int)k;
+        g.k_per_split = (int)(((k + splits - 1) / splits + 31) / 32 * 32);
+        if (g.k_per_split == 0) g.k_per_split = 32;
+        g.epilogue = epilogue;
+        g.out = dout.as<float>(); g.out_blocks = nullptr; g.block_rows = 1;
+        g.ldc = (long long)n; g.split_stride = (long long)(m * n);
+        g.x_base = static_cast<const uint8_t*>(dx.p); g.x_row_stride_bytes = (long long)(n * 4);
+        g.x_gather = nullptr; g.x_row_base = 0; g.x_is_half = 0;
+        g.status = dstatus.as<unsigned>();
+        const bool exact = a_half != 0, rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
+        cudaError_t err;
+        if (tile_n == 64) {
+            if (exact) err = rowsum ? tc::launch<64, true, true>(g, splits, nullptr) : tc::launch<64, true, false>(g, splits, nullptr);
+            else err = rowsum ? tc::launch<64, false, true>(g, splits, nullptr) : tc::launch<64, false, false>(g, splits, nullptr);
+        } else {
+            if (exact) err = rowsum ? tc::launch<128, true, true>(g, splits, nullptr) : tc::launch<128, true, false>(g, splits, nullptr);
+            else err = rowsum ? tc::launch<128, false, true>(g, splits, nullptr) : tc::launch<128, false, false>(g, splits, nullptr);
+        }
+        KGE_CUDA(err);
+        finish_kernels();
+        unsigned status = 0;
+        KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
+        if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_gemm: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");
+        to_host(out, dout, (size_t)splits * m * n * 4);
     });
 }
 

@@ -113,6 +113,7 @@ Config parse_config(const SettingMap& s) {
     c.rank = get_or<unsigned>(s, "execution.rank", get_unsigned, 0u);
     c.world = get_or<unsigned>(s, "execution.world_size", get_unsigned, 1u);
     c.cuda_graph = get_or<bool>(s, "execution.cuda_graph", get_bool, true);
+    c.tensor_cores = get_or<bool>(s, "execution.tensor_cores", get_bool, true);
 
     if (score_fn == "TransE") c.score_fn = SCORE_TRANSE;
     else if (score_fn == "DistMult") c.score_fn = SCORE_DISTMULT;
@@ -287,7 +288,7 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
 
     const unsigned tiles = ceil_div(cfg_.f, 64) * ceil_div(cfg_.d, 64) * std::max(1u, cfg_.n_net());
     proj_splits_ = (int)std::min(8u, std::max(1u, ceil_div(148, std::max(1u, tiles))));
-    proj_rows_per_split_ = (int)round_up(ceil_div(cfg_.n_remote(), proj_splits_), 16);
+    proj_rows_per_split_ = (int)round_up(ceil_div(cfg_.n_remote(), proj_splits_), 32);
 
     KGE_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     KGE_CUDA(cudaEventCreate(&ev_begin_));
@@ -355,6 +356,8 @@ void Engine::allocate() {
     d_status_ = (unsigned*)device_alloc(sizeof(unsigned));
     KGE_CUDA(cudaMemset(d_epoch_, 0, sizeof(unsigned)));
     KGE_CUDA(cudaMemset(d_status_, 0, sizeof(unsigned)));
+    d_tc_status_ = (unsigned*)device_alloc(sizeof(unsigned));
+    KGE_CUDA(cudaMemset(d_tc_status_, 0, sizeof(unsigned)));
     d_peer_flags_ = (unsigned**)device_alloc(sizeof(unsigned*) * cfg_.world);
     d_partials_ = (const float**)device_alloc(sizeof(float*) * cfg_.n_shard);
     d_replicas_ = (float**)device_alloc(sizeof(float*) * cfg_.world);
@@ -619,6 +622,14 @@ void Engine::train_staged(float learning_rate, float* loss) {
 }
 
 void Engine::check_device_status() {
+    if (cfg_.tensor_cores) {
+        unsigned tc_status = 0;
+        KGE_CUDA(cudaMemcpy(&tc_status, d_tc_status_, sizeof(tc_status), cudaMemcpyDeviceToHost));
+        if (tc_status) {
+            KGE_CUDA(cudaMemset(d_tc_status_, 0, sizeof(tc_status)));
+            fail(KGE_DEVICE_STATUS, msg() << "a bounded wait on the tensor-core pipeline gave up (code " << tc_status << ")");
+        }
+    }
     if (cfg_.world == 1) return;
     unsigned status = 0;
     KGE_CUDA(cudaMemcpy(&status, d_status_, sizeof(status), cudaMemcpyDeviceToHost));
@@ -705,6 +716,17 @@ void Engine::timing_collect() {
     timed_.clear();
 }
 
+void Engine::launch_tc(const char* name, tc::GemmArgs& g, int splits, bool a_exact, bool rowsum) {
+    g.status = d_tc_status_;
+    cudaError_t err;
+    timing_begin(name);
+    if (a_exact) err = rowsum ? tc::launch<64, true, true>(g, splits, stream_) : tc::launch<64, true, false>(g, splits, stream_);
+    else err = rowsum ? tc::launch<64, false, true>(g, splits, stream_) : tc::launch<64, false, false>(g, splits, stream_);
+    timing_end();
+    ++launch_counter_;
+    KGE_CUDA(err);
+}
+
 void Engine::launch_one_step(unsigned step) {
     const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d, F = cfg_.f;
     const unsigned n_rel = cfg_.n_relation_type;
@@ -743,9 +765,24 @@ void Engine::launch_one_step(unsigned step) {
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
         const uint32_t* remote = step_ptr(d_remote_, l, R);
-        dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
-        KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
-                                                        b.table, layout_, remote, 0u, (int)R, W0, W1, b.hid_h, b.hid_t)));
+        if (cfg_.tensor_cores && F > 0) {
+            // hidden = value + feature . W on the tensor cores: A = gathered feature rows, B = W stored [F, D]
+            for (unsigned net = 0; net < (two_nets ? 2u : 1u); ++net) {
+                tc::GemmArgs g{};
+                g.A = tc::make_operand(b.table + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, false, remote);
+                g.B = tc::make_operand(net ? W1 : W0, (long long)D * 4, false, true);
+                g.M = (int)R; g.N = (int)D; g.K = (int)F; g.k_per_split = (int)round_up(F, 32);
+                g.epilogue = tc::EPI_ADD_TABLE_VALUE;
+                g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
+                g.x_base = b.table; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = remote;
+                g.x_is_half = cfg_.state_type == ST_F16;
+                launch_tc("hidden", g, 1, cfg_.feature_type == ST_F16, false);
+            }
+        } else {
+            dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
+            KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
+                                                            b.table, layout_, remote, 0u, (int)R, W0, W1, b.hid_h, b.hid_t)));
+        }
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
@@ -774,6 +811,16 @@ void Engine::launch_one_step(unsigned step) {
         pa.p[0] = {b.pred, b.tails, b.coeff, (int)B, (int)T, (int)T, 1, b.d_pred, nullptr, 1};
         pa.p[1] = {b.tails, b.pred, b.coeff, (int)T, (int)B, 1, (int)T, nullptr, b.grad_dst, (int)cfg_.a2a_size};
         dim3 bgrid(ceil_div(B, 32) + ceil_div(T, 32), ceil_div(D, 64));
+        const bool tc_score = cfg_.tensor_cores && cfg_.dist_fn == DIST_DOT;
+        const bool tc_bwd = cfg_.tensor_cores && cfg_.dist_fn != DIST_L1;
+        if (tc_score) {
+            tc::GemmArgs g{};
+            g.A = tc::make_operand(b.pred, (long long)D * 4, false, false);
+            g.B = tc::make_operand(b.tails, (long long)D * 4, false, false);
+            g.M = (int)B; g.N = (int)T; g.K = (int)D; g.k_per_split = (int)round_up(D, 32);
+            g.epilogue = tc::EPI_STORE; g.out = b.raw; g.ldc = T; g.block_rows = 1;
+            launch_tc("score", g, 1, false, false);
+        } else
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
             case DIST_L2: KGE_LAUNCH("score", k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
@@ -782,6 +829,29 @@ void Engine::launch_one_step(unsigned step) {
         KGE_LAUNCH("loss", k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp));
         KGE_LAUNCH("loss_finish", k_loss_finish<<<1, 256, 0, stream_>>>(b.loss_rows, (int)B, 1.0f / normaliser,
                                                                         d_loss_total_ + l, d_loss_last_ + l));
+        if (tc_bwd) {
+            // Both input gradients are contractions with the coefficient matrix C [B, T]:
+            //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
+            //   L2:   d_pred = rowsum(C) * pred - C . tails,       d_tails = colsum(C) * tails - C^T . pred
+            // (sum_j C_ij (p_i - t_j) written out; C already holds gradient / distance).
+            const bool l2 = cfg_.dist_fn == DIST_L2;
+            tc::GemmArgs g{};
+            g.A = tc::make_operand(b.coeff, (long long)T * 4, false, false);
+            g.B = tc::make_operand(b.tails, (long long)D * 4, false, true);
+            g.M = (int)B; g.N = (int)D; g.K = (int)T; g.k_per_split = (int)round_up(T, 32);
+            g.epilogue = l2 ? tc::EPI_ROWSUM_X_MINUS : tc::EPI_STORE;
+            g.out = b.d_pred; g.ldc = D; g.block_rows = 1;
+            g.x_base = reinterpret_cast<const uint8_t*>(b.pred); g.x_row_stride_bytes = (long long)D * 4;
+            launch_tc("score_bwd", g, 1, false, l2);
+            tc::GemmArgs h{};
+            h.A = tc::make_operand(b.coeff, (long long)T * 4, false, true);
+            h.B = tc::make_operand(b.pred, (long long)D * 4, false, true);
+            h.M = (int)T; h.N = (int)D; h.K = (int)B; h.k_per_split = (int)round_up(B, 32);
+            h.epilogue = l2 ? tc::EPI_ROWSUM_X_MINUS : tc::EPI_STORE;
+            h.out = nullptr; h.out_blocks = b.grad_dst; h.block_rows = (int)cfg_.a2a_size; h.ldc = D;
+            h.x_base = reinterpret_cast<const uint8_t*>(b.tails); h.x_row_stride_bytes = (long long)D * 4;
+            launch_tc("score_bwd", h, 1, false, l2);
+        } else
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa)); break;
             case DIST_L2: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L2><<<bgrid, 128, 0, stream_>>>(pa)); break;
@@ -822,7 +892,19 @@ void Engine::launch_one_step(unsigned step) {
                                                 b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
         }
-        if (F > 0) {
+        if (F > 0 && cfg_.tensor_cores) {
+            // d W = feature^T . d_hidden: the gathered rows are the k index of both operands
+            for (unsigned net = 0; net < cfg_.n_net(); ++net) {
+                tc::GemmArgs g{};
+                g.A = tc::make_operand(b.table + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, true, remote);
+                g.B = tc::make_operand(net ? b.d_hid_t : b.d_hid_h, (long long)D * 4, false, true);
+                g.M = (int)F; g.N = (int)D; g.K = (int)R; g.k_per_split = proj_rows_per_split_;
+                g.epilogue = tc::EPI_STORE;
+                g.out = b.proj_partial + (size_t)net * proj_splits_ * proj_elems_; g.ldc = D; g.block_rows = 1;
+                g.split_stride = (long long)proj_elems_;
+                launch_tc("projection_bwd", g, proj_splits_, cfg_.feature_type == ST_F16, false);
+            }
+        } else if (F > 0) {
             dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
             if (cfg_.feature_type == ST_F32)

@@ -10,6 +10,7 @@
 
 #include "common.hpp"
 #include "kernels.cuh"
+#include "tc_gemm.cuh"
 
 namespace kge {
 
@@ -35,6 +36,7 @@ struct Config {
     int state_type, feature_type;
     unsigned device_ordinal, rank, world;
     bool cuda_graph;
+    bool tensor_cores;  // dense contractions on tcgen05 (3xTF32) instead of the FP32 pipe
 
     unsigned n_tail() const { return n_shard * a2a_size; }
     unsigned n_remote() const { return batch_size + n_tail(); }
@@ -124,6 +126,7 @@ class Engine {
     void launch_steps();
     void launch_one_step(unsigned step);
     void launch_barrier();
+    void launch_tc(const char* name, tc::GemmArgs& g, int splits, bool a_exact, bool rowsum);
     void check_device_status();
     void timing_begin(const char* name);
     void timing_end();
@@ -148,6 +151,7 @@ class Engine {
     bool connected_ = false;
     unsigned* d_epoch_ = nullptr;
     unsigned* d_status_ = nullptr;
+    unsigned* d_tc_status_ = nullptr;
     unsigned** d_peer_flags_ = nullptr;
     const float** d_partials_ = nullptr;  // [n_shard]
     float** d_replicas_ = nullptr;        // [world]

@@ -1,0 +1,430 @@
+// Dense contractions of the training step on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+//   acc[m, n] = sum_k A[m, k] * B[n, k]          A: M x K, B: N x K, fp32 result
+//
+// The reference multiplies in fp32 (src/pag/pag.cpp:681-699 on FLOAT tensors), and parity is
+// judged at 1e-5, which a single TF32 product (11-bit significands) cannot give.  Each operand
+// is therefore split into two TF32-exact parts, x = hi + lo with hi = x with its low 13
+// significand bits cleared and lo = (x - hi) likewise cleared, and three products are
+// accumulated in the fp32 TMEM accumulator: hi*hi + hi*lo + lo*hi (the dropped lo*lo term and
+// the second truncation are each below 2^-21 of |x||y|).  An operand that comes from fp16
+// storage is exact in TF32 and needs no lo part.
+//
+// One CTA owns a 128 x BN output tile.  Per 32-deep k slice all 128 threads bring the two operand
+// tiles from global memory (L2-resident at the step's sizes; rows may be gathered through an
+// index, may be fp16, and may be stored k-major or mn-major), split them and write them to
+// shared memory in the K-major 128-byte-swizzled layout the UMMA descriptors describe; one thread
+// then issues the tcgen05.mma instructions of the slice into a TMEM tile of its own and commits
+// them to an mbarrier; while they run, the threads read the previous slice's tile from TMEM
+// (tcgen05.ld, one lane = one output row) and add it to register accumulators, and then stage the
+// next slice (two stages of shared memory and of TMEM).  The epilogue applies one of:
+//   out = acc                                  (dot scores, projection gradient, dot backward)
+//   out = acc + value[row]                     (hidden = value + feature . W)
+//   out = rowsum(A)[m] * X[m, n] - acc         (L2 backward in contraction form, see engine.cu)
+// Every wait on an mbarrier is bounded; on expiry the kernel records an error word and goes on
+// to its clean-up (TMEM is always released).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kge {
+namespace tc {
+
+constexpr int kBM = 128;      // UMMA M
+constexpr int kBK = 32;       // fp32 elements per k slice: one 128-byte swizzle row
+constexpr int kStages = 2;
+constexpr int kThreads = 128;
+
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD_TABLE_VALUE = 1, EPI_ROWSUM_X_MINUS = 2 };
+
+// One operand as it lies in global memory.  Element (r, c) of the stored matrix is at
+//   base + (gather ? gather[r] : r) * row_stride_bytes + c * (is_half ? 2 : 4).
+// transposed == 0: stored rows are the operand's m / n index, columns are k (k contiguous);
+// transposed == 1: stored rows are k, columns are m / n.
+struct Operand {
+    const uint8_t* base;
+    long long row_stride_bytes;
+    const uint32_t* gather;
+    int is_half;
+    int transposed;
+    int vec_ok;  // rows start on a 16-byte (fp32) / 8-byte (fp16) boundary: 4-element vector loads allowed
+};
+
+struct GemmArgs {
+    Operand A, B;
+    int M, N, K;
+    int k_per_split;            // k range of blockIdx.z is [z * k_per_split, min(K, (z + 1) * k_per_split))
+    int epilogue;
+    // output: row m at out + m * ldc (+ blockIdx.z * split_stride), or, when out_blocks is set, at
+    // out_blocks[m / block_rows] + (m % block_rows) * ldc (rows routed to their owning shard)
+    float* out;
+    float* const* out_blocks;
+    int block_rows;
+    long long ldc;
+    long long split_stride;
+    // EPI_ADD_TABLE_VALUE: value row of output row m is x_base + (x_gather ? x_gather[m] : m) * x_row_stride_bytes
+    // EPI_ROWSUM_X_MINUS:  X[m, n] fp32 at x_base + m * x_row_stride_bytes + n * 4
+    const uint8_t* x_base;
+    long long x_row_stride_bytes;
+    const uint32_t* x_gather;
+    uint32_t x_row_base;
+    int x_is_half;
+    unsigned* status;           // device error word; non-zero = a bounded wait gave up
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about a second and reports through `status`.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned* status, unsigned code) {
+    for (uint32_t spins = 0; spins < (1u << 22); ++spins)
+        if (mbar_try_wait(bar, parity)) return;
+    atomicExch(status, code);
+}
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, TF32 inputs, fp32 accumulate, issued by one thread.
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier gets one arrival when every MMA this thread has issued so far has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive accumulator columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle:
+// rows are 128 B apart, groups of 8 rows 1024 B apart (stride byte offset), leading byte offset
+// 16 B (unused by this layout), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: fp32 accumulator (bits 4-5 = 1), A and B TF32 (format 2 at bits 7-9 and
+// 10-12), both K-major (bits 15, 16 = 0), N / 8 at bits 17-22, M / 16 at bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// Operand staging
+
+__device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
+
+// Byte offset of element (row, k) inside a K-major tile with 128-byte rows under the 128-byte
+// swizzle: the 16-byte chunk index is XOR-ed with the row index modulo 8.
+__device__ __forceinline__ uint32_t sw128_offset(int row, int k) {
+    return (uint32_t)row * 128u + ((((uint32_t)k >> 2) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)k & 3u) << 2);
+}
+
+__device__ __forceinline__ const uint8_t* operand_row(const Operand& op, int r) {
+    const size_t row = op.gather ? op.gather[r] : (uint32_t)r;
+    return op.base + row * (size_t)op.row_stride_bytes;
+}
+__device__ __forceinline__ float operand_elem(const Operand& op, const uint8_t* row, int c) {
+    return op.is_half ? __half2float(reinterpret_cast<const __half*>(row)[c]) : reinterpret_cast<const float*>(row)[c];
+}
+
+// Loads the [ROWS x 32] slice (mn0.., k0..) of an operand, splits it and stores hi (and lo) tiles.
+// Elements outside [0, MN) x [k0, k_end) are zero.  With ROWSUM, each thread also adds the exact
+// fp32 values it handles into per-row partial sums (the rows a thread handles never change).
+template <int ROWS, bool WRITE_LO, bool ROWSUM>
+__device__ __forceinline__ void stage_operand(const Operand& op, int mn0, int MN, int k0, int k_end, uint8_t* tile_hi,
+                                              uint8_t* tile_lo, float (&rowsum)[ROWS / 16]) {
+    const int tid = threadIdx.x;
+    if (!op.transposed) {
+        // 8 threads per row, 4 consecutive k each: coalesced 128-byte row segments
+#pragma unroll
+        for (int i = 0; i < ROWS / 16; ++i) {
+            const int u = tid + i * kThreads, row = u >> 3, ch = u & 7;
+            const int mn = mn0 + row, k = k0 + ch * 4;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (mn < MN && k < k_end) {
+                const uint8_t* rp = operand_row(op, mn);
+                if (op.vec_ok && k + 3 < k_end) {
+                    if (op.is_half) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(rp + (size_t)k * 2);
+                        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+                    } else {
+                        const float4 raw = *reinterpret_cast<const float4*>(rp + (size_t)k * 4);
+                        v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (k + j < k_end) v[j] = operand_elem(op, rp, k + j);
+                }
+            }
+            if (ROWSUM) rowsum[i] += (v[0] + v[1]) + (v[2] + v[3]);
+            float4 hi = make_float4(tf32_hi(v[0]), tf32_hi(v[1]), tf32_hi(v[2]), tf32_hi(v[3]));
+            const uint32_t off = (uint32_t)row * 128u + (((uint32_t)ch ^ ((uint32_t)row & 7u)) << 4);
+            *reinterpret_cast<float4*>(tile_hi + off) = hi;
+            if (WRITE_LO) {
+                float4 lo = make_float4(tf32_hi(v[0] - hi.x), tf32_hi(v[1] - hi.y), tf32_hi(v[2] - hi.z), tf32_hi(v[3] - hi.w));
+                *reinterpret_cast<float4*>(tile_lo + off) = lo;
+            }
+        }
+    } else {
+        // stored rows are k: a warp covers patches of 8 consecutive m/n (32-byte global segments per
+        // k) by 4 consecutive k; the 32 scalar stores of a patch fall into 32 different banks
+        const int warp = tid >> 5, lane = tid & 31;
+        const int r_in = lane & 7, k_in = lane >> 3;
+#pragma unroll
+        for (int i = 0; i < ROWS / 32; ++i) {
+            const int row = (warp + 4 * i) * 8 + r_in, mn = mn0 + row;
+            float part = 0.f;
+#pragma unroll
+            for (int kg = 0; kg < 8; ++kg) {
+                const int kk = kg * 4 + k_in, k = k0 + kk;
+                float v = 0.f;
+                if (mn < MN && k < k_end) v = operand_elem(op, operand_row(op, k), mn);
+                part += v;
+                const float hi = tf32_hi(v);
+                const uint32_t off = sw128_offset(row, kk);
+                *reinterpret_cast<float*>(tile_hi + off) = hi;
+                if (WRITE_LO) *reinterpret_cast<float*>(tile_lo + off) = tf32_hi(v - hi);
+            }
+            if (ROWSUM) rowsum[i] += part;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The kernel.  Dynamic shared memory: kStages x (A_hi, A_lo, B_hi, B_lo) tiles, 1024-byte aligned.
+
+template <int BN>
+constexpr size_t smem_bytes() {
+    return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128);
+}
+
+template <int BN, bool A_EXACT, bool ROWSUM>
+__global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[kStages];
+    __shared__ uint32_t tmem_slot;
+    __shared__ float s_rowsum[kBM];
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128, kStage = 2 * kATile + 2 * kBTile;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * kBM, n0 = blockIdx.y * BN;
+    const int k_begin = blockIdx.z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
+    const int n_slices = max(0, (k_end - k_begin + kBK - 1) / kBK);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, kStages * BN);  // one accumulator tile per stage
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
+
+    float rowsum[kBM / 16];
+#pragma unroll
+    for (int i = 0; i < kBM / 16; ++i) rowsum[i] = 0.f;
+    float unused[BN / 16];
+    // The tensor core truncates its fp32 accumulator once per MMA instruction, so a long k loop
+    // accumulated in TMEM drifts by about (instructions / 2) ulp.  Each 32-deep slice is therefore
+    // accumulated on its own in TMEM (12 instructions) and added here, in registers, with
+    // round-to-nearest; slice j's MMAs run while slice j-1 is drained.
+    float acc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+
+    auto drain = [&](int slice) {
+        const int b = slice % kStages;
+        mbar_wait(&bars[b], (uint32_t)((slice / kStages) & 1), g.status, 1u);
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * BN + c0), r);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+    };
+
+    for (int kc = 0; kc < n_slices; ++kc) {
+        const int s = kc % kStages;
+        // stage s (shared memory and TMEM tile) was released when slice kc - 2 was drained
+        uint8_t* stage = smem + (size_t)s * kStage;
+        uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
+        const int k0 = k_begin + kc * kBK;
+        stage_operand<kBM, !A_EXACT, ROWSUM>(g.A, m0, g.M, k0, k_end, a_hi, a_lo, rowsum);
+        stage_operand<BN, true, false>(g.B, n0, g.N, k0, k_end, b_hi, b_lo, unused);
+        fence_async_shared();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(s * BN);
+            const uint64_t da_hi = make_kmajor_sw128_desc(smem_u32(a_hi)), da_lo = make_kmajor_sw128_desc(smem_u32(a_lo));
+            const uint64_t db_hi = make_kmajor_sw128_desc(smem_u32(b_hi)), db_lo = make_kmajor_sw128_desc(smem_u32(b_lo));
+#pragma unroll
+            for (int ks = 0; ks < kBK / 8; ++ks) {
+                const uint64_t adv = (uint64_t)(ks * 32 >> 4);  // 8 TF32 = 32 bytes further along the swizzled row
+                // small cross terms first, the large hi*hi term last
+                umma_tf32(tmem_acc, da_hi + adv, db_lo + adv, idesc, ks > 0 ? 1u : 0u);
+                if (!A_EXACT) umma_tf32(tmem_acc, da_lo + adv, db_hi + adv, idesc, 1u);
+                umma_tf32(tmem_acc, da_hi + adv, db_hi + adv, idesc, 1u);
+            }
+            umma_commit(&bars[s]);
+        }
+        if (kc >= 1) drain(kc - 1);
+    }
+    if (n_slices > 0) drain(n_slices - 1);
+
+    if (ROWSUM) {
+        // combine the partial row sums of the threads that share a row; fixed order
+        if (!g.A.transposed) {
+#pragma unroll
+            for (int i = 0; i < kBM / 16; ++i) {
+                float v = rowsum[i];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if ((tid & 7) == 0) s_rowsum[(tid >> 3) + 16 * i] = v;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kBM / 32; ++i) {
+                float v = rowsum[i];
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if (lane < 8) s_rowsum[(warp + 4 * i) * 8 + lane] = v;
+            }
+        }
+    }
+    __syncthreads();
+
+    // epilogue: this thread holds output row m0 + tid, columns n0 .. n0 + BN
+    const int row = warp * 32 + lane, m = m0 + row;
+    if (m < g.M) {
+        float* out_row;
+        if (g.out_blocks) {
+            const int blk = m / g.block_rows;
+            out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+        } else {
+            out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
+        }
+        const uint8_t* x_row = nullptr;
+        if (g.epilogue != EPI_STORE) {
+            const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
+            x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
+        }
+        const float rs = ROWSUM ? s_rowsum[row] : 0.f;
+        const bool vec_store = ((g.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_row) & 15) == 0);
+#pragma unroll
+        for (int j = 0; j < BN; ++j) {
+            const int n = n0 + j;
+            if (n < g.N) {
+                if (g.epilogue == EPI_ADD_TABLE_VALUE) {
+                    const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n])
+                                                : reinterpret_cast<const float*>(x_row)[n];
+                    acc[j] = x + acc[j];
+                } else if (g.epilogue == EPI_ROWSUM_X_MINUS) {
+                    acc[j] = rs * reinterpret_cast<const float*>(x_row)[n] - acc[j];
+                }
+            }
+        }
+        if (vec_store && n0 + BN <= g.N) {
+#pragma unroll
+            for (int j = 0; j < BN; j += 4)
+                *reinterpret_cast<float4*>(out_row + n0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < BN; ++j)
+                if (n0 + j < g.N) out_row[n0 + j] = acc[j];
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, kStages * BN);
+}
+
+// Host side: grid = (ceil(M / 128), ceil(N / BN), splits).
+template <int BN, bool A_EXACT, bool ROWSUM>
+inline cudaError_t launch(const GemmArgs& g, int splits, cudaStream_t stream) {
+    static bool configured = false;  // one attribute call per instantiation and process is enough
+    auto kernel = k_tc_gemm<BN, A_EXACT, ROWSUM>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<BN>());
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    dim3 grid((g.M + kBM - 1) / kBM, (g.N + BN - 1) / BN, splits);
+    kernel<<<grid, kThreads, smem_bytes<BN>(), stream>>>(g);
+    return cudaGetLastError();
+}
+
+inline Operand make_operand(const void* base, long long row_stride_bytes, bool is_half, bool transposed,
+                            const uint32_t* gather = nullptr) {
+    Operand op;
+    op.base = static_cast<const uint8_t*>(base);
+    op.row_stride_bytes = row_stride_bytes;
+    op.gather = gather;
+    op.is_half = is_half ? 1 : 0;
+    op.transposed = transposed ? 1 : 0;
+    const uintptr_t align = is_half ? 8 : 16;
+    op.vec_ok = (reinterpret_cast<uintptr_t>(base) % align == 0 && row_stride_bytes % (long long)align == 0) ? 1 : 0;
+    return op;
+}
+
+}  // namespace tc
+}  // namespace kge

@@ -165,6 +165,20 @@ int kge_op_gather_rows(const float* table, size_t rows, size_t width, const uint
 int kge_op_scatter_add_rows(const float* grad_rows, const uint32_t* indices, size_t n, size_t rows,
                             size_t width, float* grad_table);
 /*
+ * The dense contraction of the step on the tensor cores, as an operator on host buffers: the fp32
+ * `matMul` of src/pag/pag.cpp:673-704 (forward and both gradients are this one form).
+ *   out[z, m, n] = epilogue( sum over k in split z of A[m, k] * B[n, k] )
+ * a: stored matrix [a_rows, a_cols], fp32 or fp16 (a_half); A[m, k] = a[m, k], or a[k, m] when
+ * a_transposed; a_gather (optional) picks the stored rows.  b: fp32, same conventions.
+ * epilogue 0: acc; 1: acc + x[m, n]; 2: rowsum(A)[m] * x[m, n] - acc (x fp32 [m, n]).
+ * tile_n: 64 or 128 output columns per thread block.  Products use the 3xTF32 split, so results
+ * agree with an fp32 product to about 1e-6 of sum |a||b|.
+ */
+int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* a_gather, size_t a_rows,
+                   size_t a_cols, const float* b, int b_transposed, size_t b_rows, size_t b_cols, size_t m,
+                   size_t n, size_t k, int epilogue, const float* x, int splits, int tile_n, float* out);
+
+/*
  * kge_op_scatter_add_rows for callers that cannot allocate device memory.  It has no counterpart
  * in the reference.  The operator's working memory (the sorted lookups and the per-row segment
  * starts) lives in a fixed array inside the library's device image instead of coming from

@@ -61,11 +61,12 @@ CASES = {
 }
 
 
-def _build(case, n_step=1, warm=False, cuda_graph=True, pad=0):
+def _build(case, n_step=1, warm=False, cuda_graph=True, pad=0, tensor_cores=True):
     cfg = case["cfg"]
     fdt = case.get("feature_dtype")
     state = random_state(cfg, case["seed"], fp16_features=fdt == "float16", warm=warm)
-    engine = capi.CEngine(engine_settings(cfg, n_step=n_step, feature_dtype=fdt, rw_batch=RW, cuda_graph=cuda_graph))
+    engine = capi.CEngine(engine_settings(cfg, n_step=n_step, feature_dtype=fdt, rw_batch=RW, cuda_graph=cuda_graph,
+                                          **{"execution.tensor_cores": tensor_cores}))
     write_state(engine, cfg, state, RW)
     batch = random_batch(cfg, n_step, case["seed"] + 100, pad=pad)
     return cfg, state, engine, batch
@@ -96,9 +97,15 @@ def _compare_state(engine, cfg, oracle, what):
 
 @pytest.mark.parametrize("name", sorted(CASES))
 @pytest.mark.parametrize("warm", [False, True], ids=["cold", "warm"])
-def test_single_step_matches_oracle(name, warm):
+@pytest.mark.parametrize("tensor_cores", [True, False], ids=["tcgen05", "fp32pipe"])
+def test_single_step_matches_oracle(name, warm, tensor_cores):
+    """Both forms of the contractions: on the tensor cores (3xTF32 split, the default) and on the
+    FP32 pipe (always used for L1, which has no contraction form)."""
     case = CASES[name]
-    cfg, state, engine, batch = _build(case, warm=warm, pad=3 if name != "config1_transe_l1" else 40)
+    if not tensor_cores and warm:
+        pytest.skip("the FP32-pipe form is covered by the cold start")
+    cfg, state, engine, batch = _build(case, warm=warm, pad=3 if name != "config1_transe_l1" else 40,
+                                       tensor_cores=tensor_cores)
     oracle = make_oracle(cfg, state)
     lr = 1e-3
     want_loss = oracle.train_step_loop(lr, batch)
