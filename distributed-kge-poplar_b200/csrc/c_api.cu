@@ -391,9 +391,10 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         const bool exact = a_half != 0, rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
         cudaError_t err;
         if (tile_n == 64) {
-            if (exact) err = rowsum ? tc::launch<64, true, true>(g, splits, nullptr) : tc::launch<64, true, false>(g, splits, nullptr);
-            else err = rowsum ? tc::launch<64, false, true>(g, splits, nullptr) : tc::launch<64, false, false>(g, splits, nullptr);
+            if (exact) err = rowsum ? tc::launch_pair<64, true, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, true, false>(&g, 1, splits, nullptr);
+            else err = rowsum ? tc::launch_pair<64, false, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, false, false>(&g, 1, splits, nullptr);
         } else {
+            // the 128-column tile exists only in the unpipelined form
             if (exact) err = rowsum ? tc::launch<128, true, true>(g, splits, nullptr) : tc::launch<128, true, false>(g, splits, nullptr);
             else err = rowsum ? tc::launch<128, false, true>(g, splits, nullptr) : tc::launch<128, false, false>(g, splits, nullptr);
         }

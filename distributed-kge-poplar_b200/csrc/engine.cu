@@ -716,12 +716,15 @@ void Engine::timing_collect() {
     timed_.clear();
 }
 
-void Engine::launch_tc(const char* name, tc::GemmArgs& g, int splits, bool a_exact, bool rowsum) {
-    g.status = d_tc_status_;
+// One launch for one or two contractions of the same kind (see tc_gemm.cuh).
+void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum) {
+    for (int i = 0; i < n_problems; ++i) problems[i].status = d_tc_status_;
     cudaError_t err;
     timing_begin(name);
-    if (a_exact) err = rowsum ? tc::launch<64, true, true>(g, splits, stream_) : tc::launch<64, true, false>(g, splits, stream_);
-    else err = rowsum ? tc::launch<64, false, true>(g, splits, stream_) : tc::launch<64, false, false>(g, splits, stream_);
+    if (a_exact) err = rowsum ? tc::launch_pair<64, true, true>(problems, n_problems, splits, stream_)
+                              : tc::launch_pair<64, true, false>(problems, n_problems, splits, stream_);
+    else err = rowsum ? tc::launch_pair<64, false, true>(problems, n_problems, splits, stream_)
+                      : tc::launch_pair<64, false, false>(problems, n_problems, splits, stream_);
     timing_end();
     ++launch_counter_;
     KGE_CUDA(err);
@@ -767,8 +770,10 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* remote = step_ptr(d_remote_, l, R);
         if (cfg_.tensor_cores && F > 0) {
             // hidden = value + feature . W on the tensor cores: A = gathered feature rows, B = W stored [F, D]
-            for (unsigned net = 0; net < (two_nets ? 2u : 1u); ++net) {
-                tc::GemmArgs g{};
+            tc::GemmArgs nets[2] = {};
+            const int n_nets = two_nets ? 2 : 1;
+            for (int net = 0; net < n_nets; ++net) {
+                tc::GemmArgs& g = nets[net];
                 g.A = tc::make_operand(b.table + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, false, remote);
                 g.B = tc::make_operand(net ? W1 : W0, (long long)D * 4, false, true);
                 g.M = (int)R; g.N = (int)D; g.K = (int)F; g.k_per_split = (int)round_up(F, 32);
@@ -776,8 +781,8 @@ void Engine::launch_one_step(unsigned step) {
                 g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
                 g.x_base = b.table; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = remote;
                 g.x_is_half = cfg_.state_type == ST_F16;
-                launch_tc("hidden", g, 1, cfg_.feature_type == ST_F16, false);
             }
+            launch_tc("hidden", nets, n_nets, 1, cfg_.feature_type == ST_F16, false);
         } else {
             dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
             KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
@@ -819,7 +824,7 @@ void Engine::launch_one_step(unsigned step) {
             g.B = tc::make_operand(b.tails, (long long)D * 4, false, false);
             g.M = (int)B; g.N = (int)T; g.K = (int)D; g.k_per_split = (int)round_up(D, 32);
             g.epilogue = tc::EPI_STORE; g.out = b.raw; g.ldc = T; g.block_rows = 1;
-            launch_tc("score", g, 1, false, false);
+            launch_tc("score", &g, 1, 1, false, false);
         } else
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
@@ -835,22 +840,23 @@ void Engine::launch_one_step(unsigned step) {
             //   L2:   d_pred = rowsum(C) * pred - C . tails,       d_tails = colsum(C) * tails - C^T . pred
             // (sum_j C_ij (p_i - t_j) written out; C already holds gradient / distance).
             const bool l2 = cfg_.dist_fn == DIST_L2;
-            tc::GemmArgs g{};
+            tc::GemmArgs both[2] = {};
+            tc::GemmArgs& g = both[0];
             g.A = tc::make_operand(b.coeff, (long long)T * 4, false, false);
             g.B = tc::make_operand(b.tails, (long long)D * 4, false, true);
             g.M = (int)B; g.N = (int)D; g.K = (int)T; g.k_per_split = (int)round_up(T, 32);
             g.epilogue = l2 ? tc::EPI_ROWSUM_X_MINUS : tc::EPI_STORE;
             g.out = b.d_pred; g.ldc = D; g.block_rows = 1;
             g.x_base = reinterpret_cast<const uint8_t*>(b.pred); g.x_row_stride_bytes = (long long)D * 4;
-            launch_tc("score_bwd", g, 1, false, l2);
-            tc::GemmArgs h{};
+            tc::GemmArgs& h = both[1];
             h.A = tc::make_operand(b.coeff, (long long)T * 4, false, true);
             h.B = tc::make_operand(b.pred, (long long)D * 4, false, true);
-            h.M = (int)T; h.N = (int)D; h.K = (int)B; h.k_per_split = (int)round_up(B, 32);
+            h.M = (int)T; h.N = (int)D; h.K = (int)B; h.k_per_split = (int)round_up(std::max(B, T), 32);
             h.epilogue = l2 ? tc::EPI_ROWSUM_X_MINUS : tc::EPI_STORE;
             h.out = nullptr; h.out_blocks = b.grad_dst; h.block_rows = (int)cfg_.a2a_size; h.ldc = D;
             h.x_base = reinterpret_cast<const uint8_t*>(b.tails); h.x_row_stride_bytes = (long long)D * 4;
-            launch_tc("score_bwd", h, 1, false, l2);
+            g.k_per_split = h.k_per_split;
+            launch_tc("score_bwd", both, 2, 1, false, l2);
         } else
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa)); break;
@@ -894,16 +900,17 @@ void Engine::launch_one_step(unsigned step) {
         }
         if (F > 0 && cfg_.tensor_cores) {
             // d W = feature^T . d_hidden: the gathered rows are the k index of both operands
+            tc::GemmArgs nets[2] = {};
             for (unsigned net = 0; net < cfg_.n_net(); ++net) {
-                tc::GemmArgs g{};
+                tc::GemmArgs& g = nets[net];
                 g.A = tc::make_operand(b.table + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, true, remote);
                 g.B = tc::make_operand(net ? b.d_hid_t : b.d_hid_h, (long long)D * 4, false, true);
                 g.M = (int)F; g.N = (int)D; g.K = (int)R; g.k_per_split = proj_rows_per_split_;
                 g.epilogue = tc::EPI_STORE;
                 g.out = b.proj_partial + (size_t)net * proj_splits_ * proj_elems_; g.ldc = D; g.block_rows = 1;
                 g.split_stride = (long long)proj_elems_;
-                launch_tc("projection_bwd", g, proj_splits_, cfg_.feature_type == ST_F16, false);
             }
+            launch_tc("projection_bwd", nets, (int)cfg_.n_net(), proj_splits_, cfg_.feature_type == ST_F16, false);
         } else if (F > 0) {
             dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;

@@ -126,7 +126,7 @@ class Engine {
     void launch_steps();
     void launch_one_step(unsigned step);
     void launch_barrier();
-    void launch_tc(const char* name, tc::GemmArgs& g, int splits, bool a_exact, bool rowsum);
+    void launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum);
     void check_device_status();
     void timing_begin(const char* name);
     void timing_end();

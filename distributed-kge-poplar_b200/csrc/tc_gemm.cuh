@@ -398,6 +398,340 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
     if (warp == 0) tmem_dealloc(tmem_base, kStages * BN);
 }
 
+// ---------------------------------------------------------------------------
+// Pipelined form.  Same arithmetic as k_tc_gemm, but the operand slices travel from global
+// memory to a ring of raw tiles in shared memory with cp.async (16 bytes per copy, zero-filled
+// outside the matrix), kRawStages - 1 slices ahead of their use, so the L2 latency is hidden
+// behind the split pass and the MMAs of earlier slices.  The split pass then reads the raw tile
+// from shared memory, splits (and, for mn-major operands, transposes) it into the swizzled
+// K-major hi / lo tiles.  The block has 4 * CG warps: the staging work is spread over all of
+// them, and warp w drains TMEM lanes 32 * (w % 4) .. (the quarter a warp may touch), columns of
+// group w / 4, so every thread keeps BN / CG accumulators.  Requires every operand row to start
+// on a 16-byte boundary; otherwise the launcher falls back to k_tc_gemm.  Two problems of the
+// same kind (the two gradients of the score, the two feature networks) can share one launch:
+// blockIdx.x picks the problem.
+
+constexpr int kRawStages = 3;
+
+struct GemmPair {
+    GemmArgs p[2];
+    int tiles_m0;  // blocks with blockIdx.x < tiles_m0 work on p[0], the others on p[1]
+};
+
+__device__ __forceinline__ void cp_async16(uint8_t* dst_smem, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ int clamp16(int bytes) { return bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes); }
+
+// 16 consecutive accumulator columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Queues the copies of the [ROWS x 32] slice (mn0.., k0..) into `raw`; NT threads share the work.
+//   k-major operand:  raw[row][32 k]   (128-byte rows for fp32, 64-byte rows for fp16)
+//   mn-major operand: raw[32 k][ROWS]  (rows of ROWS elements)
+template <int ROWS, int NT>
+__device__ __forceinline__ void issue_raw(const Operand& op, int mn0, int MN, int k0, int k_end, uint8_t* raw) {
+    const int tid = threadIdx.x;
+    if (!op.transposed) {
+        if (!op.is_half) {
+#pragma unroll
+            for (int u = tid; u < ROWS * 8; u += NT) {
+                const int row = u >> 3, ch = u & 7;
+                const int mn = mn0 + row, k = k0 + ch * 4;
+                const int bytes = mn < MN ? clamp16((k_end - k) * 4) : 0;
+                const uint8_t* src = bytes ? operand_row(op, mn) + (size_t)k * 4 : op.base;
+                cp_async16(raw + row * 128 + ch * 16, src, bytes);
+            }
+        } else {
+#pragma unroll
+            for (int u = tid; u < ROWS * 4; u += NT) {
+                const int row = u >> 2, ch = u & 3;
+                const int mn = mn0 + row, k = k0 + ch * 8;
+                const int bytes = mn < MN ? clamp16((k_end - k) * 2) : 0;
+                const uint8_t* src = bytes ? operand_row(op, mn) + (size_t)k * 2 : op.base;
+                cp_async16(raw + row * 64 + ch * 16, src, bytes);
+            }
+        }
+    } else {
+        if (!op.is_half) {
+            constexpr int kChunksPerRow = ROWS / 4;
+#pragma unroll
+            for (int u = tid; u < kBK * kChunksPerRow; u += NT) {
+                const int kk = u / kChunksPerRow, c = u % kChunksPerRow;
+                const int k = k0 + kk, mn = mn0 + c * 4;
+                const int bytes = k < k_end ? clamp16((MN - mn) * 4) : 0;
+                const uint8_t* src = bytes ? operand_row(op, k) + (size_t)mn * 4 : op.base;
+                cp_async16(raw + kk * (ROWS * 4) + c * 16, src, bytes);
+            }
+        } else {
+            constexpr int kChunksPerRow = ROWS / 8;
+#pragma unroll
+            for (int u = tid; u < kBK * kChunksPerRow; u += NT) {
+                const int kk = u / kChunksPerRow, c = u % kChunksPerRow;
+                const int k = k0 + kk, mn = mn0 + c * 8;
+                const int bytes = k < k_end ? clamp16((MN - mn) * 2) : 0;
+                const uint8_t* src = bytes ? operand_row(op, k) + (size_t)mn * 2 : op.base;
+                cp_async16(raw + kk * (ROWS * 2) + c * 16, src, bytes);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void store_split(uint8_t* tile_hi, uint8_t* tile_lo, int row, int chunk, const float (&v)[4],
+                                            bool write_lo) {
+    const float4 hi = make_float4(tf32_hi(v[0]), tf32_hi(v[1]), tf32_hi(v[2]), tf32_hi(v[3]));
+    const uint32_t off = (uint32_t)row * 128u + (((uint32_t)chunk ^ ((uint32_t)row & 7u)) << 4);
+    *reinterpret_cast<float4*>(tile_hi + off) = hi;
+    if (write_lo)
+        *reinterpret_cast<float4*>(tile_lo + off) =
+            make_float4(tf32_hi(v[0] - hi.x), tf32_hi(v[1] - hi.y), tf32_hi(v[2] - hi.z), tf32_hi(v[3] - hi.w));
+}
+
+// Raw tile -> swizzled K-major hi / lo tiles.  With ROWSUM (fp32 operands, ROWS = 128) the exact
+// values are also summed: `rowsum[i]` collects what this thread handled of its i-th row
+//   k-major:  rows (tid >> 3) + i * NT / 8, eight neighbouring threads share a row;
+//   mn-major: row tid % 128 for every i, the threads tid, tid + 128, ... share a row.
+template <int ROWS, int NT, bool WRITE_LO, bool ROWSUM>
+__device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw, uint8_t* tile_hi, uint8_t* tile_lo,
+                                          float (&rowsum)[2]) {
+    const int tid = threadIdx.x;
+    if (!op.transposed) {
+        if (!op.is_half) {
+            int i = 0;
+#pragma unroll
+            for (int u = tid; u < ROWS * 8; u += NT, ++i) {
+                const int row = u >> 3, ch = u & 7;
+                const float4 x = *reinterpret_cast<const float4*>(raw + row * 128 + ch * 16);
+                const float v[4] = {x.x, x.y, x.z, x.w};
+                if (ROWSUM) rowsum[i & 1] += (v[0] + v[1]) + (v[2] + v[3]);
+                store_split(tile_hi, tile_lo, row, ch, v, WRITE_LO);
+            }
+        } else {
+#pragma unroll
+            for (int u = tid; u < ROWS * 4; u += NT) {
+                const int row = u >> 2, ch = u & 3;
+                const uint4 x = *reinterpret_cast<const uint4*>(raw + row * 64 + ch * 16);
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+                const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+                const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
+                const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
+                const float v0[4] = {a.x, a.y, b.x, b.y}, v1[4] = {c.x, c.y, d.x, d.y};
+                store_split(tile_hi, tile_lo, row, 2 * ch, v0, WRITE_LO);
+                store_split(tile_hi, tile_lo, row, 2 * ch + 1, v1, WRITE_LO);
+            }
+        }
+    } else {
+        // unit = (row, 16-byte chunk of k): consecutive threads take consecutive rows, so the reads
+        // walk along a raw row (conflict-free) and the swizzle spreads the 16-byte stores of eight
+        // neighbouring rows over all banks
+#pragma unroll
+        for (int u = tid; u < ROWS * 8; u += NT) {
+            const int row = u % ROWS, ch = u / ROWS;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int kk = ch * 4 + j;
+                v[j] = op.is_half ? __half2float(reinterpret_cast<const __half*>(raw)[kk * ROWS + row])
+                                  : reinterpret_cast<const float*>(raw)[kk * ROWS + row];
+            }
+            if (ROWSUM) rowsum[0] += (v[0] + v[1]) + (v[2] + v[3]);
+            store_split(tile_hi, tile_lo, row, ch, v, WRITE_LO);
+        }
+    }
+}
+
+template <int BN>
+constexpr size_t smem_bytes_async() {
+    return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128) + (size_t)kRawStages * (kBM * 128 + BN * 128);
+}
+
+template <int BN, int CG, bool A_EXACT, bool ROWSUM>
+__global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_constant__ GemmPair gp) {
+    constexpr int NT = 128 * CG;      // threads
+    constexpr int CPT = BN / CG;      // accumulator columns per thread
+    static_assert(CPT == 16 || CPT == 32, "a thread drains 16 or 32 columns");
+    static_assert(!ROWSUM || (NT == 512 || NT == 256 || NT == 128), "row sums assume at most two k-major rows per thread");
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[kStages];
+    __shared__ uint32_t tmem_slot;
+    __shared__ float s_rowsum[kBM];
+    __shared__ float s_part[CG][kBM];
+
+    const int which = (int)blockIdx.x >= gp.tiles_m0 ? 1 : 0;
+    const GemmArgs& g = gp.p[which];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = warp & 3, group = warp >> 2;
+    const int m0 = ((int)blockIdx.x - (which ? gp.tiles_m0 : 0)) * kBM, n0 = blockIdx.y * BN;
+    if (n0 >= g.N || m0 >= g.M) return;  // the two problems may differ in size
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128, kStage = 2 * kATile + 2 * kBTile, kRaw = kATile + kBTile;
+    uint8_t* raw_ring = smem + (size_t)kStages * kStage;
+    const int k_begin = blockIdx.z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
+    const int n_slices = max(0, (k_end - k_begin + kBK - 1) / kBK);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, kStages * BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
+
+    float rowsum[2] = {0.f, 0.f};
+    float acc[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+
+    auto issue = [&](int slice) {
+        if (slice < n_slices) {
+            uint8_t* raw = raw_ring + (size_t)(slice % kRawStages) * kRaw;
+            const int k0 = k_begin + slice * kBK;
+            issue_raw<kBM, NT>(g.A, m0, g.M, k0, k_end, raw);
+            issue_raw<BN, NT>(g.B, n0, g.N, k0, k_end, raw + kATile);
+        }
+        cp_async_commit();  // one group per slice, empty past the end, so the counting stays uniform
+    };
+    auto drain = [&](int slice) {
+        const int b = slice % kStages;
+        mbar_wait(&bars[b], (uint32_t)((slice / kStages) & 1), g.status, 1u);
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + group * CPT);
+        if (CPT == 32) {
+            uint32_t r[32];
+            tmem_ld32(taddr, r);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j % CPT] += __uint_as_float(r[j]);
+        } else {
+            uint32_t r[16];
+            tmem_ld16(taddr, r);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+    };
+
+#pragma unroll
+    for (int s = 0; s < kRawStages - 1; ++s) issue(s);
+    for (int kc = 0; kc < n_slices; ++kc) {
+        issue(kc + kRawStages - 1);
+        cp_async_wait<kRawStages - 1>();  // this thread's copies of slice kc have landed
+        __syncthreads();                  // ... and everybody else's
+        const int s = kc % kStages;
+        uint8_t* stage = smem + (size_t)s * kStage;
+        uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
+        const uint8_t* raw = raw_ring + (size_t)(kc % kRawStages) * kRaw;
+        split_raw<kBM, NT, !A_EXACT, ROWSUM>(g.A, raw, a_hi, a_lo, rowsum);
+        float unused[2];
+        split_raw<BN, NT, true, false>(g.B, raw + kATile, b_hi, b_lo, unused);
+        fence_async_shared();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(s * BN);
+            const uint64_t da_hi = make_kmajor_sw128_desc(smem_u32(a_hi)), da_lo = make_kmajor_sw128_desc(smem_u32(a_lo));
+            const uint64_t db_hi = make_kmajor_sw128_desc(smem_u32(b_hi)), db_lo = make_kmajor_sw128_desc(smem_u32(b_lo));
+#pragma unroll
+            for (int ks = 0; ks < kBK / 8; ++ks) {
+                const uint64_t adv = (uint64_t)(ks * 32 >> 4);
+                umma_tf32(tmem_acc, da_hi + adv, db_lo + adv, idesc, ks > 0 ? 1u : 0u);
+                if (!A_EXACT) umma_tf32(tmem_acc, da_lo + adv, db_hi + adv, idesc, 1u);
+                umma_tf32(tmem_acc, da_hi + adv, db_hi + adv, idesc, 1u);
+            }
+            umma_commit(&bars[s]);
+        }
+        if (kc >= 1) drain(kc - 1);
+    }
+    cp_async_wait<0>();
+    if (n_slices > 0) drain(n_slices - 1);
+
+    if (ROWSUM) {
+        // fixed-order combination of the partial row sums
+        if (!g.A.transposed) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float v = rowsum[i];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                const int row = (tid >> 3) + i * (NT / 8);
+                if ((tid & 7) == 0 && row < kBM) s_rowsum[row] = v;
+            }
+            __syncthreads();
+        } else {
+            s_part[tid / kBM][tid % kBM] = rowsum[0];
+            __syncthreads();
+            if (tid < kBM) {
+                float v = 0.f;
+#pragma unroll
+                for (int c = 0; c < CG; ++c) v += s_part[c][tid];
+                s_rowsum[tid] = v;
+            }
+            __syncthreads();
+        }
+    }
+
+    const int row = quarter * 32 + lane, m = m0 + row;
+    const int nc0 = n0 + group * CPT;  // first output column of this thread
+    if (m < g.M && nc0 < g.N) {
+        float* out_row;
+        if (g.out_blocks) {
+            const int blk = m / g.block_rows;
+            out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+        } else {
+            out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
+        }
+        const uint8_t* x_row = nullptr;
+        if (g.epilogue != EPI_STORE) {
+            const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
+            x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
+        }
+        const float rs = ROWSUM ? s_rowsum[row] : 0.f;
+        const bool vec_store = ((g.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_row) & 15) == 0);
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+            const int n = nc0 + j;
+            if (n < g.N) {
+                if (g.epilogue == EPI_ADD_TABLE_VALUE) {
+                    const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n])
+                                                : reinterpret_cast<const float*>(x_row)[n];
+                    acc[j] = x + acc[j];
+                } else if (g.epilogue == EPI_ROWSUM_X_MINUS) {
+                    acc[j] = rs * reinterpret_cast<const float*>(x_row)[n] - acc[j];
+                }
+            }
+        }
+        if (vec_store && nc0 + CPT <= g.N) {
+#pragma unroll
+            for (int j = 0; j < CPT; j += 4)
+                *reinterpret_cast<float4*>(out_row + nc0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < CPT; ++j)
+                if (nc0 + j < g.N) out_row[nc0 + j] = acc[j];
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, kStages * BN);
+}
+
 // Host side: grid = (ceil(M / 128), ceil(N / BN), splits).
 template <int BN, bool A_EXACT, bool ROWSUM>
 inline cudaError_t launch(const GemmArgs& g, int splits, cudaStream_t stream) {
@@ -410,6 +744,44 @@ inline cudaError_t launch(const GemmArgs& g, int splits, cudaStream_t stream) {
     }
     dim3 grid((g.M + kBM - 1) / kBM, (g.N + BN - 1) / BN, splits);
     kernel<<<grid, kThreads, smem_bytes<BN>(), stream>>>(g);
+    return cudaGetLastError();
+}
+
+inline bool rows_16_byte_aligned(const Operand& op) {
+    return reinterpret_cast<uintptr_t>(op.base) % 16 == 0 && op.row_stride_bytes % 16 == 0;
+}
+
+// One or two problems in one launch, pipelined when every operand allows 16-byte copies.
+template <int BN, bool A_EXACT, bool ROWSUM>
+inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int splits, cudaStream_t stream) {
+    bool fast = true;
+    for (int i = 0; i < n_problems; ++i) fast = fast && rows_16_byte_aligned(problems[i].A) && rows_16_byte_aligned(problems[i].B);
+    if (!fast) {
+        for (int i = 0; i < n_problems; ++i) {
+            cudaError_t err = launch<BN, A_EXACT, ROWSUM>(problems[i], splits, stream);
+            if (err != cudaSuccess) return err;
+        }
+        return cudaSuccess;
+    }
+    static bool configured = false;
+    constexpr int CG = 4;  // 16 warps
+    auto kernel = k_tc_gemm_async<BN, CG, A_EXACT, ROWSUM>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_async<BN>());
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    GemmPair gp{};
+    gp.p[0] = problems[0];
+    gp.p[1] = problems[n_problems > 1 ? 1 : 0];
+    gp.tiles_m0 = (problems[0].M + kBM - 1) / kBM;
+    int tiles_m = gp.tiles_m0, tiles_n = (problems[0].N + BN - 1) / BN;
+    if (n_problems > 1) {
+        tiles_m += (problems[1].M + kBM - 1) / kBM;
+        tiles_n = tiles_n > (problems[1].N + BN - 1) / BN ? tiles_n : (problems[1].N + BN - 1) / BN;
+    }
+    dim3 grid(tiles_m, tiles_n, splits);
+    kernel<<<grid, 128 * CG, smem_bytes_async<BN>(), stream>>>(gp);
     return cudaGetLastError();
 }
 
