@@ -218,6 +218,8 @@ def step_traffic(n_shard: int) -> dict:
     n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
     row_state, row_feat = 3 * D * 4, F * 2
     return {
+        # the row gather: R whole rows out of the table, written once to the compact copy
+        "gather": 2 * R * (row_state + row_feat),
         # reads value + features of R rows and the projection, writes the hidden rows
         "hidden": R * (D * 4 + row_feat) + F * D * 4 + R * D * 4,
         "route": 2 * (T + B) * D * 4 + B * D * 4,

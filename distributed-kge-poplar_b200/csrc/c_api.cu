@@ -1,5 +1,7 @@
 // extern "C" surface of include/kge_b200.h: argument marshalling and error mapping for the
 // engine, and the single-operator entry points.
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -389,14 +391,38 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         g.x_gather = nullptr; g.x_row_base = 0; g.x_is_half = 0;
         g.status = dstatus.as<unsigned>();
         const bool exact = a_half != 0, rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
-        cudaError_t err;
-        if (tile_n == 64) {
-            if (exact) err = rowsum ? tc::launch_pair<64, true, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, true, false>(&g, 1, splits, nullptr);
-            else err = rowsum ? tc::launch_pair<64, false, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, false, false>(&g, 1, splits, nullptr);
-        } else {
-            // the 128-column tile exists only in the unpipelined form
-            if (exact) err = rowsum ? tc::launch<128, true, true>(g, splits, nullptr) : tc::launch<128, true, false>(g, splits, nullptr);
-            else err = rowsum ? tc::launch<128, false, true>(g, splits, nullptr) : tc::launch<128, false, false>(g, splits, nullptr);
+        cudaError_t err = cudaSuccess;
+        // Developer aid: KGE_TC_REPEAT=n launches the kernel n more times between two events and prints
+        // the mean time; KGE_TC_DEBUG=bits switches phases of the pipelined kernel off (results are then wrong).
+        const char* env_repeat = std::getenv("KGE_TC_REPEAT");
+        const char* env_debug = std::getenv("KGE_TC_DEBUG");
+        const int repeat = env_repeat ? std::atoi(env_repeat) : 0;
+        g.debug_skip = env_debug ? std::atoi(env_debug) : 0;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        for (int it = 0; it <= repeat && err == cudaSuccess; ++it) {
+            if (it == 1) {
+                KGE_CUDA(cudaEventCreate(&e0));
+                KGE_CUDA(cudaEventCreate(&e1));
+                KGE_CUDA(cudaEventRecord(e0, nullptr));
+            }
+            if (tile_n == 64) {
+                if (exact) err = rowsum ? tc::launch_pair<64, true, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, true, false>(&g, 1, splits, nullptr);
+                else err = rowsum ? tc::launch_pair<64, false, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, false, false>(&g, 1, splits, nullptr);
+            } else {
+                // the 128-column tile exists only in the unpipelined form
+                if (exact) err = rowsum ? tc::launch<128, true, true>(g, splits, nullptr) : tc::launch<128, true, false>(g, splits, nullptr);
+                else err = rowsum ? tc::launch<128, false, true>(g, splits, nullptr) : tc::launch<128, false, false>(g, splits, nullptr);
+            }
+        }
+        if (repeat > 0 && err == cudaSuccess) {
+            KGE_CUDA(cudaEventRecord(e1, nullptr));
+            KGE_CUDA(cudaEventSynchronize(e1));
+            float ms = 0.f;
+            KGE_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+            std::fprintf(stderr, "kge_op_tc_gemm m=%zu n=%zu k=%zu splits=%d debug=%d: %.2f us per launch\n", m, n, k, splits,
+                         g.debug_skip, 1e3f * ms / repeat);
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
         }
         KGE_CUDA(err);
         finish_kernels();

@@ -332,6 +332,7 @@ void Engine::allocate() {
         ShardBuffers& b = shards_[l];
         b.table = (uint8_t*)device_alloc(table_bytes);
         KGE_CUDA(cudaMemset(b.table, 0, table_bytes));
+        b.rows_c = (uint8_t*)device_alloc((size_t)R * layout_.row_bytes);
         b.hid_h = (float*)device_alloc((size_t)R * D * 4);
         b.hid_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : b.hid_h;
         b.pred = (float*)device_alloc((size_t)B * D * 4);
@@ -358,6 +359,15 @@ void Engine::allocate() {
     KGE_CUDA(cudaMemset(d_status_, 0, sizeof(unsigned)));
     d_tc_status_ = (unsigned*)device_alloc(sizeof(unsigned));
     KGE_CUDA(cudaMemset(d_tc_status_, 0, sizeof(unsigned)));
+    {
+        // room for the two problems of the largest paired launch, kTcMaxSplits partial tiles each
+        const size_t per_problem = std::max<size_t>({(size_t)R * D, (size_t)(std::max(B, T)) * D, (size_t)cfg_.f * D, (size_t)B * T});
+        tc_ws_floats_ = per_problem * kTcMaxSplits;
+        tc_ws_ = (float*)device_alloc(2 * tc_ws_floats_ * 4);
+        tc_ws_rowsum_ = (float*)device_alloc(2 * (size_t)kTcMaxSplits * std::max(B, T) * 4);
+        tc_counters_ = (unsigned*)device_alloc(2 * 4096 * sizeof(unsigned));
+        KGE_CUDA(cudaMemset(tc_counters_, 0, 2 * 4096 * sizeof(unsigned)));
+    }
     d_peer_flags_ = (unsigned**)device_alloc(sizeof(unsigned*) * cfg_.world);
     d_partials_ = (const float**)device_alloc(sizeof(float*) * cfg_.n_shard);
     d_replicas_ = (float**)device_alloc(sizeof(float*) * cfg_.world);
@@ -716,9 +726,37 @@ void Engine::timing_collect() {
     timed_.clear();
 }
 
-// One launch for one or two contractions of the same kind (see tc_gemm.cuh).
+// How many k splits fill the GPU: about one block per SM, at least two 32-deep slices per split.
+int Engine::tc_splits(unsigned tiles, unsigned k) const {
+    const unsigned by_sms = std::max(1u, 148u / std::max(1u, tiles));
+    const unsigned by_k = std::max(1u, k / 64u);
+    return (int)std::min<unsigned>({by_sms, by_k, (unsigned)kTcMaxSplits});
+}
+
+// One launch for one or two contractions of the same kind (see tc_gemm.cuh).  With splits > 1
+// the k range is divided and the partial tiles are reduced inside the kernel, in split order.
 void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum) {
-    for (int i = 0; i < n_problems; ++i) problems[i].status = d_tc_status_;
+    for (int i = 0; i < n_problems; ++i) {
+        tc::GemmArgs& g = problems[i];
+        g.status = d_tc_status_;
+        const unsigned tiles = ceil_div((unsigned)g.M, 128) * ceil_div((unsigned)g.N, 64);
+        if (splits > 1 && tiles <= 4096 && (size_t)g.M * g.N * splits <= tc_ws_floats_) {
+            g.k_per_split = (int)round_up(ceil_div((unsigned)g.K, (unsigned)splits), 32);
+            g.ws = tc_ws_ + (size_t)i * tc_ws_floats_;
+            g.ws_rowsum = tc_ws_rowsum_ + (size_t)i * kTcMaxSplits * std::max(cfg_.batch_size, cfg_.n_tail());
+            g.counters = tc_counters_ + (size_t)i * 4096;
+        } else {
+            g.k_per_split = std::max(32, (int)round_up((unsigned)g.K, 32));
+            g.ws = nullptr;
+        }
+    }
+    if (!problems[0].ws || (n_problems > 1 && !problems[1].ws)) {
+        splits = 1;
+        for (int i = 0; i < n_problems; ++i) {
+            problems[i].ws = nullptr;
+            problems[i].k_per_split = std::max(32, (int)round_up((unsigned)problems[i].K, 32));
+        }
+    }
     cudaError_t err;
     timing_begin(name);
     if (a_exact) err = rowsum ? tc::launch_pair<64, true, true>(problems, n_problems, splits, stream_)
@@ -768,25 +806,26 @@ void Engine::launch_one_step(unsigned step) {
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
         const uint32_t* remote = step_ptr(d_remote_, l, R);
+        KGE_LAUNCH("gather", k_gather_step_rows<<<ceil_div(R, 8), 256, 0, stream_>>>(b.table, layout_.row_bytes, remote, (int)R, b.rows_c));
         if (cfg_.tensor_cores && F > 0) {
             // hidden = value + feature . W on the tensor cores: A = gathered feature rows, B = W stored [F, D]
             tc::GemmArgs nets[2] = {};
             const int n_nets = two_nets ? 2 : 1;
             for (int net = 0; net < n_nets; ++net) {
                 tc::GemmArgs& g = nets[net];
-                g.A = tc::make_operand(b.table + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, false, remote);
+                g.A = tc::make_operand(b.rows_c + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, false);
                 g.B = tc::make_operand(net ? W1 : W0, (long long)D * 4, false, true);
                 g.M = (int)R; g.N = (int)D; g.K = (int)F; g.k_per_split = (int)round_up(F, 32);
                 g.epilogue = tc::EPI_ADD_TABLE_VALUE;
                 g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
-                g.x_base = b.table; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = remote;
+                g.x_base = b.rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = nullptr;
                 g.x_is_half = cfg_.state_type == ST_F16;
             }
-            launch_tc("hidden", nets, n_nets, 1, cfg_.feature_type == ST_F16, false);
+            launch_tc("hidden", nets, n_nets, tc_splits(n_nets * ceil_div(R, 128) * ceil_div(D, 64), F), cfg_.feature_type == ST_F16, false);
         } else {
             dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
             KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
-                                                            b.table, layout_, remote, 0u, (int)R, W0, W1, b.hid_h, b.hid_t)));
+                                                            b.rows_c, layout_, nullptr, 0u, (int)R, W0, W1, b.hid_h, b.hid_t)));
         }
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
@@ -824,7 +863,7 @@ void Engine::launch_one_step(unsigned step) {
             g.B = tc::make_operand(b.tails, (long long)D * 4, false, false);
             g.M = (int)B; g.N = (int)T; g.K = (int)D; g.k_per_split = (int)round_up(D, 32);
             g.epilogue = tc::EPI_STORE; g.out = b.raw; g.ldc = T; g.block_rows = 1;
-            launch_tc("score", &g, 1, 1, false, false);
+            launch_tc("score", &g, 1, tc_splits(ceil_div(B, 128) * ceil_div(T, 64), D), false, false);
         } else
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
@@ -856,7 +895,7 @@ void Engine::launch_one_step(unsigned step) {
             h.out = nullptr; h.out_blocks = b.grad_dst; h.block_rows = (int)cfg_.a2a_size; h.ldc = D;
             h.x_base = reinterpret_cast<const uint8_t*>(b.tails); h.x_row_stride_bytes = (long long)D * 4;
             g.k_per_split = h.k_per_split;
-            launch_tc("score_bwd", both, 2, 1, false, l2);
+            launch_tc("score_bwd", both, 2, tc_splits((ceil_div(B, 128) + ceil_div(T, 128)) * ceil_div(D, 64), std::min(B, T)), false, l2);
         } else
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa)); break;
@@ -881,21 +920,21 @@ void Engine::launch_one_step(unsigned step) {
         const float* alpha = d_step_size_ + step;
         if (cfg_.state_type == ST_F32) {
             if (vec)
-                KGE_LAUNCH("entity_update", k_entity_update<float, 4><<<R, 64, 0, stream_>>>(
-                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                KGE_LAUNCH("entity_update", k_entity_update<float, 4><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
             else
-                KGE_LAUNCH("entity_update", k_entity_update<float, 1><<<R, 64, 0, stream_>>>(
-                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                KGE_LAUNCH("entity_update", k_entity_update<float, 1><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
         } else {
             if (vec)
-                KGE_LAUNCH("entity_update", k_entity_update<__half, 4><<<R, 64, 0, stream_>>>(
-                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                KGE_LAUNCH("entity_update", k_entity_update<__half, 4><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
             else
-                KGE_LAUNCH("entity_update", k_entity_update<__half, 1><<<R, 64, 0, stream_>>>(
-                                                b.table, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                KGE_LAUNCH("entity_update", k_entity_update<__half, 1><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
         }
         if (F > 0 && cfg_.tensor_cores) {
@@ -903,32 +942,32 @@ void Engine::launch_one_step(unsigned step) {
             tc::GemmArgs nets[2] = {};
             for (unsigned net = 0; net < cfg_.n_net(); ++net) {
                 tc::GemmArgs& g = nets[net];
-                g.A = tc::make_operand(b.table + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, true, remote);
+                g.A = tc::make_operand(b.rows_c + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, true);
                 g.B = tc::make_operand(net ? b.d_hid_t : b.d_hid_h, (long long)D * 4, false, true);
                 g.M = (int)F; g.N = (int)D; g.K = (int)R; g.k_per_split = proj_rows_per_split_;
                 g.epilogue = tc::EPI_STORE;
-                g.out = b.proj_partial + (size_t)net * proj_splits_ * proj_elems_; g.ldc = D; g.block_rows = 1;
-                g.split_stride = (long long)proj_elems_;
+                g.out = b.proj_partial + (size_t)net * proj_elems_; g.ldc = D; g.block_rows = 1;
             }
-            launch_tc("projection_bwd", nets, (int)cfg_.n_net(), proj_splits_, cfg_.feature_type == ST_F16, false);
+            launch_tc("projection_bwd", nets, (int)cfg_.n_net(),
+                      tc_splits(cfg_.n_net() * ceil_div(F, 128) * ceil_div(D, 64), R), cfg_.feature_type == ST_F16, false);
         } else if (F > 0) {
             dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
             if (cfg_.feature_type == ST_F32)
                 KGE_LAUNCH("projection_bwd", k_projection_bwd<float><<<grid, 256, 0, stream_>>>(
-                                                 b.table, layout_, remote, (int)R, b.d_hid_h, dh1, proj_splits_,
+                                                 b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
                                                  proj_rows_per_split_, b.proj_partial));
             else
                 KGE_LAUNCH("projection_bwd", k_projection_bwd<__half><<<grid, 256, 0, stream_>>>(
-                                                 b.table, layout_, remote, (int)R, b.d_hid_h, dh1, proj_splits_,
+                                                 b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
                                                  proj_rows_per_split_, b.proj_partial));
         }
         const size_t proj_total = (size_t)cfg_.n_net() * proj_elems_;
-        const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 63) / 64, 148 * 16) : 0;
-        KGE_LAUNCH("dense_partial", k_dense_partial<<<n_rel + proj_blocks, 64, 0, stream_>>>(
+        const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 255) / 256, 148 * 8) : 0;
+        KGE_LAUNCH("dense_partial", k_dense_partial<<<n_rel + proj_blocks, 32 * kRelationLanes, 0, stream_>>>(
                                         b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                        (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_, proj_elems_,
-                                        b.dense_partial));
+                                        (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
+                                        proj_elems_, b.dense_partial));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();

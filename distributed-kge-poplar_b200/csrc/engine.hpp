@@ -93,6 +93,7 @@ class Engine {
    private:
     struct ShardBuffers {
         uint8_t* table = nullptr;
+        uint8_t* rows_c = nullptr;  // the step's gathered rows, table row layout, [R]
         float *hid_h = nullptr, *hid_t = nullptr, *pred = nullptr, *raw = nullptr, *coeff = nullptr;
         float *d_pred = nullptr, *d_head = nullptr, *d_relrow = nullptr;
         float *d_hid_h = nullptr, *d_hid_t = nullptr, *proj_partial = nullptr, *loss_rows = nullptr;
@@ -152,6 +153,12 @@ class Engine {
     unsigned* d_epoch_ = nullptr;
     unsigned* d_status_ = nullptr;
     unsigned* d_tc_status_ = nullptr;
+    // split-k workspace of the tensor-core contractions (shared by all of them: one stream)
+    float *tc_ws_ = nullptr, *tc_ws_rowsum_ = nullptr;
+    unsigned* tc_counters_ = nullptr;
+    size_t tc_ws_floats_ = 0;
+    static constexpr int kTcMaxSplits = 8;
+    int tc_splits(unsigned tiles, unsigned k) const;
     unsigned** d_peer_flags_ = nullptr;
     const float** d_partials_ = nullptr;  // [n_shard]
     float** d_replicas_ = nullptr;        // [world]

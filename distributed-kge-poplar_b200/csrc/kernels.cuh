@@ -87,6 +87,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 // ---------------------------------------------------------------------------
+// The step's row gather (fr::Buffer::read through getEntityData, src/fructose/fructose.cpp:790-798,
+// src/poplar_kge.cpp:405-410): the R rows named by `remote` are copied whole, with 128-bit
+// accesses, from the shard table (tens of gigabytes, so every row is a DRAM and TLB miss) into a
+// compact buffer with the same row layout.  One warp per row with all of its loads in flight
+// before the first store; everything after this kernel in the step reads the compact,
+// L2-resident copy.
+static __global__ void __launch_bounds__(256)
+k_gather_step_rows(const uint8_t* __restrict__ table, uint32_t row_bytes, const uint32_t* __restrict__ remote, int R,
+                   uint8_t* __restrict__ rows_c) {
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= R) return;
+    const uint4* __restrict__ src = reinterpret_cast<const uint4*>(table + (size_t)remote[r] * row_bytes);
+    uint4* __restrict__ dst = reinterpret_cast<uint4*>(rows_c + (size_t)r * row_bytes);
+    const int chunks = (int)(row_bytes >> 4);
+    for (int c0 = lane; c0 < chunks; c0 += 32 * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (c0 + 32 * u < chunks) v[u] = src[c0 + 32 * u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (c0 + 32 * u < chunks) dst[c0 + 32 * u] = v[u];
+    }
+}
+
+// ---------------------------------------------------------------------------
 // hidden = value + feature . W   (src/poplar_kge.cpp:439-467 with the gather of :405-410
 // folded in).  A [R, F] is read straight from the gathered table rows; W is [F, D].
 // Rows are table[remote[m]], or the consecutive rows row_base + m when `remote` is null
@@ -701,50 +727,82 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
 // src/fructose/frnn.cpp:61-90).  One block per gathered row.  Every gathered row is
 // updated, rows with a zero gradient and the padding row included, as in the reference.
 // d_hid_h / d_hid_t keep the hidden-row gradients for the projection backward.
+constexpr int kSegmentLanes = 4;  // threads groups that share one segment's lookups
+
 template <class ST, int V>
-__global__ void __launch_bounds__(64)
-k_entity_update(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote,
-                const uint32_t* __restrict__ perm, const uint32_t* __restrict__ off,
+__global__ void __launch_bounds__(64 * kSegmentLanes)
+k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c, RowLayout L,
+                const uint32_t* __restrict__ remote, const uint32_t* __restrict__ perm,
+                const uint32_t* __restrict__ off,
                 const uint32_t* __restrict__ first_slot, const float* __restrict__ d_head,
                 const float* __restrict__ grad_recv, int B,
                 float* __restrict__ d_hid_h, float* __restrict__ d_hid_t,
                 const float* __restrict__ step_size, float lr_modifier, AdamParams ap) {
+    // partial sums of the item lanes, [lane][head | tail][64 column threads][V]
+    __shared__ float part[kSegmentLanes][2][64 * V];
     const int r = blockIdx.x, D = L.d;
+    const int col = threadIdx.x & 63, lane = threadIdx.x >> 6;
     const uint32_t q0 = off[r], q1 = off[r + 1];
     const size_t row = remote[r];
     ST* __restrict__ xv = reinterpret_cast<ST*>(table + row * L.row_bytes);
     ST* __restrict__ mv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_m);
     ST* __restrict__ qv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_q);
+    // the state before the update comes from the step's gathered copy (slot r), not from the table
+    const ST* __restrict__ xs = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes);
+    const ST* __restrict__ ms = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes + L.off_m);
+    const ST* __restrict__ qs = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes + L.off_q);
     const float alpha = *step_size * lr_modifier;
     const bool writes_row = first_slot[r] != 0;
-    for (int c = threadIdx.x * V; c < D; c += blockDim.x * V) {
+    for (int c0 = 0; c0 < D; c0 += 64 * V) {
+        const int c = c0 + col * V;
         float gh[V], gt[V];
 #pragma unroll
         for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
-        // Four lookups at a time: their loads are issued together, the sums stay in segment order.
-        for (uint32_t q = q0; q < q1; q += 4) {
-            uint32_t e[4];
-            float4 g[4];
+        // Lane l sums the lookups q0 + l, q0 + l + lanes, ... in that order, four loads in flight;
+        // the lanes' partial sums are then added in lane order: a fixed tree, whatever the timing.
+        if (c < D) {
+            for (uint32_t q = q0 + lane; q < q1; q += 4 * kSegmentLanes) {
+                uint32_t e[4];
+                float4 g[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) e[u] = q + u < q1 ? perm[q + u] : 0xffffffffu;
+                for (int u = 0; u < 4; ++u) e[u] = q + u * kSegmentLanes < q1 ? perm[q + u * kSegmentLanes] : 0xffffffffu;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (e[u] == 0xffffffffu) continue;
-                const float* src = e[u] < (uint32_t)B ? d_head + (size_t)e[u] * D + c
-                                                      : grad_recv + (size_t)(e[u] - B) * D + c;
-                if (V == 4) g[u] = load4(src); else g[u].x = src[0];
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (e[u] == 0xffffffffu) continue;
-                if (e[u] < (uint32_t)B) {
-                    gh[0] += g[u].x;
-                    if (V == 4) { gh[1 % V] += g[u].y; gh[2 % V] += g[u].z; gh[3 % V] += g[u].w; }
-                } else {
-                    gt[0] += g[u].x;
-                    if (V == 4) { gt[1 % V] += g[u].y; gt[2 % V] += g[u].z; gt[3 % V] += g[u].w; }
+                for (int u = 0; u < 4; ++u) {
+                    g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (e[u] == 0xffffffffu) continue;
+                    const float* src = e[u] < (uint32_t)B ? d_head + (size_t)e[u] * D + c
+                                                          : grad_recv + (size_t)(e[u] - B) * D + c;
+                    if (V == 4) g[u] = load4(src); else g[u].x = src[0];
                 }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (e[u] == 0xffffffffu) continue;
+                    if (e[u] < (uint32_t)B) {
+                        gh[0] += g[u].x;
+                        if (V == 4) { gh[1 % V] += g[u].y; gh[2 % V] += g[u].z; gh[3 % V] += g[u].w; }
+                    } else {
+                        gt[0] += g[u].x;
+                        if (V == 4) { gt[1 % V] += g[u].y; gt[2 % V] += g[u].z; gt[3 % V] += g[u].w; }
+                    }
+                }
+            }
+        }
+        __syncthreads();  // the previous column block's partials have been consumed
+#pragma unroll
+        for (int u = 0; u < V; ++u) {
+            part[lane][0][col * V + u] = gh[u];
+            part[lane][1][col * V + u] = gt[u];
+        }
+        __syncthreads();
+        if (lane != 0 || c >= D) continue;
+#pragma unroll
+        for (int u = 0; u < V; ++u) {
+            gh[u] = part[0][0][col * V + u];
+            gt[u] = part[0][1][col * V + u];
+#pragma unroll
+            for (int l = 1; l < kSegmentLanes; ++l) {
+                gh[u] += part[l][0][col * V + u];
+                gt[u] += part[l][1][col * V + u];
             }
         }
         const size_t o = (size_t)r * D + c;
@@ -763,12 +821,12 @@ k_entity_update(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __rest
         if (!writes_row) continue;
         float x[V], m[V], qq[V];
         if (V == 4) {
-            const float4 a = load4(xv + c), b = load4(mv + c), d = load4(qv + c);
+            const float4 a = load4(xs + c), b = load4(ms + c), d = load4(qs + c);
             x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
             m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
             qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
         } else {
-            x[0] = load_as_float(xv + c); m[0] = load_as_float(mv + c); qq[0] = load_as_float(qv + c);
+            x[0] = load_as_float(xs + c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
         }
 #pragma unroll
         for (int u = 0; u < V; ++u) {
@@ -824,7 +882,7 @@ k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t*
         const int r = r0 + ld_k;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
         if (r < r_hi) {
-            const size_t row = remote[r];
+            const size_t row = remote ? remote[r] : (size_t)r;
             const FT* fp = reinterpret_cast<const FT*>(table + row * L.row_bytes + L.off_feat);
             const int f = m0 + ld_c;
             if (f + 3 < F) {
@@ -877,26 +935,49 @@ k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t*
 // vector: relation table | projection(s).  Relation rows are the segment sums of the
 // per-triple relation gradients (backward of the gather at src/poplar_kge.cpp:489);
 // projection entries sum the split partials of k_projection_bwd in split order.
-static __global__ void __launch_bounds__(64)
+constexpr int kRelationLanes = 8;
+
+static __global__ void __launch_bounds__(32 * kRelationLanes)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
                 float* __restrict__ dense_partial) {
+    __shared__ float part[kRelationLanes][32];
     if ((int)blockIdx.x < n_rel) {
-        // one relation row: sum its triples' gradients in position order, four loads in flight
-        const int rho = blockIdx.x;
+        // One relation row.  Relation popularity is skewed, so a few rows own most of the batch's
+        // triples: lane l sums triples q0 + l, q0 + l + lanes, ... (four loads in flight), and the
+        // lanes' partial sums are added in lane order.
+        const int rho = blockIdx.x, col = threadIdx.x & 31, lane = threadIdx.x >> 5;
         const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
-        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        if (q0 == q1) {
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dense_partial[(size_t)rho * D + c] = 0.f;
+            return;
+        }
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            const int c = c0 + col;
             float g = 0.f;
-            for (uint32_t q = q0; q < q1; q += 4) {
-                float v[4];
+            if (c < D) {
+                for (uint32_t q = q0 + lane; q < q1; q += 4 * kRelationLanes) {
+                    float v[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = q + u < q1 ? d_relrow[(size_t)rel_perm[q + u] * D + c] : 0.f;
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t qq = q + u * kRelationLanes;
+                        v[u] = qq < q1 ? d_relrow[(size_t)rel_perm[qq] * D + c] : 0.f;
+                    }
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (q + u < q1) g += v[u];
+                    for (int u = 0; u < 4; ++u)
+                        if (q + u * kRelationLanes < q1) g += v[u];
+                }
             }
-            dense_partial[(size_t)rho * D + c] = g;
+            __syncthreads();
+            part[lane][col] = g;
+            __syncthreads();
+            if (lane == 0 && c < D) {
+                float total = part[0][col];
+#pragma unroll
+                for (int l = 1; l < kRelationLanes; ++l) total += part[l][col];
+                dense_partial[(size_t)rho * D + c] = total;
+            }
         }
         return;
     }

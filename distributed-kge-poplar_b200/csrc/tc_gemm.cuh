@@ -72,6 +72,14 @@ struct GemmArgs {
     uint32_t x_row_base;
     int x_is_half;
     unsigned* status;           // device error word; non-zero = a bounded wait gave up
+    // In-kernel reduction of a k split (pipelined kernel only).  Every split writes its partial
+    // tile to ws [splits, M, N] (and its partial row sums to ws_rowsum [splits, M]); the block
+    // that arrives last at the tile's counter adds the partials in split order, applies the
+    // epilogue and resets the counter.  Null ws: each split writes its own output slice instead.
+    float* ws;
+    float* ws_rowsum;
+    unsigned* counters;         // one per output tile, zero between launches
+    int debug_skip;             // developer aid: bit 0 no copies, 1 no split pass, 2 no MMAs, 3 no drain (timing only)
 };
 
 // ---------------------------------------------------------------------------
@@ -600,7 +608,7 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
     for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 
     auto issue = [&](int slice) {
-        if (slice < n_slices) {
+        if (slice < n_slices && !(g.debug_skip & 1)) {
             uint8_t* raw = raw_ring + (size_t)(slice % kRawStages) * kRaw;
             const int k0 = k_begin + slice * kBK;
             issue_raw<kBM, NT>(g.A, m0, g.M, k0, k_end, raw);
@@ -637,12 +645,14 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
         uint8_t* stage = smem + (size_t)s * kStage;
         uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
         const uint8_t* raw = raw_ring + (size_t)(kc % kRawStages) * kRaw;
-        split_raw<kBM, NT, !A_EXACT, ROWSUM>(g.A, raw, a_hi, a_lo, rowsum);
         float unused[2];
-        split_raw<BN, NT, true, false>(g.B, raw + kATile, b_hi, b_lo, unused);
+        if (!(g.debug_skip & 2)) {
+            split_raw<kBM, NT, !A_EXACT, ROWSUM>(g.A, raw, a_hi, a_lo, rowsum);
+            split_raw<BN, NT, true, false>(g.B, raw + kATile, b_hi, b_lo, unused);
+        }
         fence_async_shared();
         __syncthreads();
-        if (tid == 0) {
+        if (tid == 0 && !(g.debug_skip & 4)) {
             tc_fence_after();
             const uint32_t tmem_acc = tmem_base + (uint32_t)(s * BN);
             const uint64_t da_hi = make_kmajor_sw128_desc(smem_u32(a_hi)), da_lo = make_kmajor_sw128_desc(smem_u32(a_lo));
@@ -656,10 +666,10 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
             }
             umma_commit(&bars[s]);
         }
-        if (kc >= 1) drain(kc - 1);
+        if (kc >= 1 && !(g.debug_skip & 12)) drain(kc - 1);
     }
     cp_async_wait<0>();
-    if (n_slices > 0) drain(n_slices - 1);
+    if (n_slices > 0 && !(g.debug_skip & 12)) drain(n_slices - 1);
 
     if (ROWSUM) {
         // fixed-order combination of the partial row sums
@@ -689,20 +699,57 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
 
     const int row = quarter * 32 + lane, m = m0 + row;
     const int nc0 = n0 + group * CPT;  // first output column of this thread
-    if (m < g.M && nc0 < g.N) {
+    const bool mine = m < g.M && nc0 < g.N;
+    bool finish = true;
+    float rs = ROWSUM ? s_rowsum[row] : 0.f;
+    if (gridDim.z > 1 && g.ws) {
+        __shared__ int s_last;
+        const size_t plane = (size_t)g.M * g.N;
+        if (mine) {
+            float* w = g.ws + (size_t)blockIdx.z * plane + (size_t)m * g.N + nc0;
+#pragma unroll
+            for (int j = 0; j < CPT; ++j)
+                if (nc0 + j < g.N) w[j] = acc[j];
+        }
+        if (ROWSUM && tid < kBM && m0 + tid < g.M) g.ws_rowsum[(size_t)blockIdx.z * g.M + m0 + tid] = s_rowsum[tid];
+        __threadfence();
+        __syncthreads();
+        const unsigned tile = blockIdx.y * ((g.M + kBM - 1) / kBM) + (unsigned)(m0 / kBM);
+        if (tid == 0) s_last = atomicAdd(&g.counters[tile], 1u) + 1u == gridDim.z ? 1 : 0;
+        __syncthreads();
+        finish = s_last != 0;
+        if (finish) {
+            __threadfence();
+            if (mine) {
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+                for (unsigned z = 0; z < gridDim.z; ++z) {  // split order, whoever came last
+                    const float* w = g.ws + (size_t)z * plane + (size_t)m * g.N + nc0;
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j)
+                        if (nc0 + j < g.N) acc[j] += __ldcg(w + j);
+                }
+                if (ROWSUM) {
+                    rs = 0.f;
+                    for (unsigned z = 0; z < gridDim.z; ++z) rs += __ldcg(g.ws_rowsum + (size_t)z * g.M + m);
+                }
+            }
+            if (tid == 0) g.counters[tile] = 0u;
+        }
+    }
+    if (finish && mine) {
         float* out_row;
         if (g.out_blocks) {
             const int blk = m / g.block_rows;
             out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
         } else {
-            out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
+            out_row = g.out + (g.ws ? 0 : (size_t)blockIdx.z * g.split_stride) + (size_t)m * g.ldc;
         }
         const uint8_t* x_row = nullptr;
         if (g.epilogue != EPI_STORE) {
             const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
             x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
         }
-        const float rs = ROWSUM ? s_rowsum[row] : 0.f;
         const bool vec_store = ((g.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_row) & 15) == 0);
 #pragma unroll
         for (int j = 0; j < CPT; ++j) {
@@ -757,8 +804,14 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
     bool fast = true;
     for (int i = 0; i < n_problems; ++i) fast = fast && rows_16_byte_aligned(problems[i].A) && rows_16_byte_aligned(problems[i].B);
     if (!fast) {
+        // the unpipelined kernel has no in-kernel split reduction: run each problem unsplit
         for (int i = 0; i < n_problems; ++i) {
-            cudaError_t err = launch<BN, A_EXACT, ROWSUM>(problems[i], splits, stream);
+            GemmArgs g = problems[i];
+            if (g.ws) {
+                g.k_per_split = (g.K + 31) / 32 * 32;
+                if (g.k_per_split == 0) g.k_per_split = 32;
+            }
+            cudaError_t err = launch<BN, A_EXACT, ROWSUM>(g, g.ws ? 1 : splits, stream);
             if (err != cudaSuccess) return err;
         }
         return cudaSuccess;

@@ -54,6 +54,20 @@ CASES = {
                                                entity_feature_size=0, batch_size=8, a2a_size=6, score_fn="TransE",
                                                distance_fn="L2", gamma=4.0, loss_type="logsigmoid",
                                                negative_adversarial_scale=1.5, weight_decay=0.01), seed=6),
+    # Long contraction axes: the tensor-core kernels split k over several blocks and reduce in-kernel.
+    # Sums of 256 to 768 terms whose rows cancel (softmax coefficients sum to zero) are beyond 1e-5
+    # in any float32 arithmetic: the float32 numpy oracle itself sits 1.0e-5 / 2.5e-5 from the float64
+    # one on these two cases, measured the same way.  Their bound is 5e-5, and they start from a warm
+    # optimiser state: Adam's first step from zero moments is lr * g / (|g| + eps'), a sign function
+    # that turns the rounding of an element whose gradient nearly cancels into a visible step.
+    "long_k_split": dict(cfg=StepConfig(n_shard=1, n_entity=1500, n_relation_type=7, embedding_size=64,
+                                        entity_feature_size=256, batch_size=128, a2a_size=256, score_fn="TransE",
+                                        distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
+                         seed=8, feature_dtype="float16", rtol=5e-5, warm_only=True),
+    "long_k_split_dot": dict(cfg=StepConfig(n_shard=2, n_entity=900, n_relation_type=6, embedding_size=128,
+                                            entity_feature_size=192, batch_size=128, a2a_size=96, score_fn="DistMult",
+                                            distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False),
+                             seed=9, rtol=5e-5, warm_only=True),
     "single_shard": dict(cfg=StepConfig(n_shard=1, n_entity=400, n_relation_type=5, embedding_size=64,
                                         entity_feature_size=32, batch_size=64, a2a_size=96, score_fn="TransE",
                                         distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
@@ -78,7 +92,7 @@ def _run_engine(engine, cfg, batch, lr):
     return loss
 
 
-def _compare_state(engine, cfg, oracle, what):
+def _compare_state(engine, cfg, oracle, what, RTOL=RTOL):
     got = read_state(engine, cfg, RW, cfg.n_shard)
     want = oracle.get_state()
     assert set(got) == set(want)
@@ -102,12 +116,16 @@ def test_single_step_matches_oracle(name, warm, tensor_cores):
     """Both forms of the contractions: on the tensor cores (3xTF32 split, the default) and on the
     FP32 pipe (always used for L1, which has no contraction form)."""
     case = CASES[name]
-    if not tensor_cores and warm:
+    if case.get("warm_only"):
+        if not warm:
+            pytest.skip("this case starts warm only")
+    elif not tensor_cores and warm:
         pytest.skip("the FP32-pipe form is covered by the cold start")
     cfg, state, engine, batch = _build(case, warm=warm, pad=3 if name != "config1_transe_l1" else 40,
                                        tensor_cores=tensor_cores)
     oracle = make_oracle(cfg, state)
     lr = 1e-3
+    RTOL = case.get("rtol", 1e-5)
     want_loss = oracle.train_step_loop(lr, batch)
     got_loss = _run_engine(engine, cfg, batch, lr)
     assert_close(got_loss, want_loss, RTOL, f"{name}: loss", atol_scale=0)
@@ -130,7 +148,7 @@ def test_single_step_matches_oracle(name, warm, tensor_cores):
     dense = engine.debug_fetch("dense_grad", 0, 1 << 24)
     n_rel = cfg.n_relation_type * D
     assert dense.size == n_rel + len(cfg.projection_names) * cfg.entity_feature_size * D * (cfg.entity_feature_size > 0)
-    _compare_state(engine, cfg, oracle, name)
+    _compare_state(engine, cfg, oracle, name, RTOL)
     engine.close()
 
 
