@@ -398,6 +398,15 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         const char* env_debug = std::getenv("KGE_TC_DEBUG");
         const int repeat = env_repeat ? std::atoi(env_repeat) : 0;
         g.debug_skip = env_debug ? std::atoi(env_debug) : 0;
+        // KGE_TC_WS=1: add the k splits with the reduction kernel (the engine's way); the sum lands in
+        // the first slice of out and the other slices stay zero
+        const bool in_kernel_reduce = std::getenv("KGE_TC_WS") && splits > 1 && tile_n == 64;
+        DeviceBuffer dws(in_kernel_reduce ? (size_t)splits * m * n * 4 : 16), dwr(in_kernel_reduce ? (size_t)splits * m * 4 : 16);
+        KGE_CUDA(cudaMemset(dout.p, 0, (size_t)splits * m * n * 4));
+        if (in_kernel_reduce) {
+            g.ws = dws.as<float>();
+            g.ws_rowsum = dwr.as<float>();
+        }
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         for (int it = 0; it <= repeat && err == cudaSuccess; ++it) {
             if (it == 1) {

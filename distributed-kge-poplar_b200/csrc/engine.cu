@@ -306,6 +306,7 @@ Engine::~Engine() {
     cudaSetDevice((int)cfg_.device_ordinal);
     if (stream_) cudaStreamSynchronize(stream_);
     if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    for (cudaEvent_t e : event_pool_) cudaEventDestroy(e);
     for (unsigned p = 0; p < peer_arena_.size(); ++p)
         if (p != cfg_.rank && peer_arena_[p]) cudaIpcCloseMemHandle(peer_arena_[p]);
     for (void* p : allocations_) cudaFree(p);
@@ -365,8 +366,6 @@ void Engine::allocate() {
         tc_ws_floats_ = per_problem * kTcMaxSplits;
         tc_ws_ = (float*)device_alloc(2 * tc_ws_floats_ * 4);
         tc_ws_rowsum_ = (float*)device_alloc(2 * (size_t)kTcMaxSplits * std::max(B, T) * 4);
-        tc_counters_ = (unsigned*)device_alloc(2 * 4096 * sizeof(unsigned));
-        KGE_CUDA(cudaMemset(tc_counters_, 0, 2 * 4096 * sizeof(unsigned)));
     }
     d_peer_flags_ = (unsigned**)device_alloc(sizeof(unsigned*) * cfg_.world);
     d_partials_ = (const float**)device_alloc(sizeof(float*) * cfg_.n_shard);
@@ -386,6 +385,8 @@ void Engine::allocate() {
     d_step_size_ = (float*)device_alloc(cfg_.n_step * 4);
     d_loss_total_ = (float*)device_alloc(n_local_ * 4);
     d_loss_last_ = (float*)device_alloc(n_local_ * 4);
+    d_loss_counter_ = (unsigned*)device_alloc(n_local_ * sizeof(unsigned));
+    KGE_CUDA(cudaMemset(d_loss_counter_, 0, n_local_ * sizeof(unsigned)));
 
     const size_t rw = (size_t)n_local_ * cfg_.rw_batch;
     d_rw_idx_ = (uint32_t*)device_alloc(std::max<size_t>(rw, (size_t)n_local_ * cfg_.predict_hr * 2) * 4);
@@ -615,6 +616,11 @@ void Engine::train_staged(float learning_rate, float* loss) {
         KGE_CUDA(cudaGraphLaunch(graph_exec_, stream_));
     } else {
         launch_counter_ = 0;
+        if (kernel_timing_) {
+            // hold the stream while the host queues the run, so the event pairs bracket kernels only
+            k_delay<<<1, 1, 0, stream_>>>(20ll * 1000 * 1000);
+            KGE_CUDA(cudaGetLastError());
+        }
         launch_steps();
         last_launches_ = launch_counter_;
     }
@@ -699,16 +705,20 @@ void Engine::launch_barrier() {
 }
 
 void Engine::timing_begin(const char* name) {
-    if (!kernel_timing_) return;
-    cudaEvent_t a = nullptr, b = nullptr;
-    KGE_CUDA(cudaEventCreate(&a));
-    KGE_CUDA(cudaEventCreate(&b));
-    timed_.push_back({name, a, b});
-    KGE_CUDA(cudaEventRecord(a, stream_));
+    if (!kernel_timing_ || timed_.size() >= kMaxTimedLaunches) return;
+    while (event_pool_.size() < 2 * (timed_.size() + 1)) {
+        cudaEvent_t e = nullptr;
+        KGE_CUDA(cudaEventCreate(&e));
+        event_pool_.push_back(e);
+    }
+    timed_.push_back({name, event_pool_[2 * timed_.size()], event_pool_[2 * timed_.size() + 1]});
+    timing_open_ = true;
+    KGE_CUDA(cudaEventRecord(timed_.back().start, stream_));
 }
 
 void Engine::timing_end() {
-    if (!kernel_timing_) return;
+    if (!timing_open_) return;
+    timing_open_ = false;
     KGE_CUDA(cudaEventRecord(timed_.back().stop, stream_));
 }
 
@@ -720,8 +730,6 @@ void Engine::timing_collect() {
             k.ms += ms;
             k.launches += 1;
         }
-        cudaEventDestroy(t.start);
-        cudaEventDestroy(t.stop);
     }
     timed_.clear();
 }
@@ -744,7 +752,6 @@ void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems,
             g.k_per_split = (int)round_up(ceil_div((unsigned)g.K, (unsigned)splits), 32);
             g.ws = tc_ws_ + (size_t)i * tc_ws_floats_;
             g.ws_rowsum = tc_ws_rowsum_ + (size_t)i * kTcMaxSplits * std::max(cfg_.batch_size, cfg_.n_tail());
-            g.counters = tc_counters_ + (size_t)i * 4096;
         } else {
             g.k_per_split = std::max(32, (int)round_up((unsigned)g.K, 32));
             g.ws = nullptr;
@@ -764,7 +771,7 @@ void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems,
     else err = rowsum ? tc::launch_pair<64, false, true>(problems, n_problems, splits, stream_)
                       : tc::launch_pair<64, false, false>(problems, n_problems, splits, stream_);
     timing_end();
-    ++launch_counter_;
+    launch_counter_ += problems[0].ws ? 2 : 1;
     KGE_CUDA(err);
 }
 
@@ -870,9 +877,8 @@ void Engine::launch_one_step(unsigned step) {
             case DIST_L2: KGE_LAUNCH("score", k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
             default: KGE_LAUNCH("score", k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
         }
-        KGE_LAUNCH("loss", k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp));
-        KGE_LAUNCH("loss_finish", k_loss_finish<<<1, 256, 0, stream_>>>(b.loss_rows, (int)B, 1.0f / normaliser,
-                                                                        d_loss_total_ + l, d_loss_last_ + l));
+        KGE_LAUNCH("loss", k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
+                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l));
         if (tc_bwd) {
             // Both input gradients are contractions with the coefficient matrix C [B, T]:
             //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
@@ -963,11 +969,17 @@ void Engine::launch_one_step(unsigned step) {
                                                  proj_rows_per_split_, b.proj_partial));
         }
         const size_t proj_total = (size_t)cfg_.n_net() * proj_elems_;
-        const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 255) / 256, 148 * 8) : 0;
-        KGE_LAUNCH("dense_partial", k_dense_partial<<<n_rel + proj_blocks, 32 * kRelationLanes, 0, stream_>>>(
-                                        b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                        (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
-                                        proj_elems_, b.dense_partial));
+        const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 511) / 512, 148 * 4) : 0;
+        if (vec)
+            KGE_LAUNCH("dense_partial", k_dense_partial<4><<<n_rel + proj_blocks, 64 * kRelationLanes, 0, stream_>>>(
+                                            b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                            (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
+                                            proj_elems_, b.dense_partial));
+        else
+            KGE_LAUNCH("dense_partial", k_dense_partial<1><<<n_rel + proj_blocks, 64 * kRelationLanes, 0, stream_>>>(
+                                            b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                            (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
+                                            proj_elems_, b.dense_partial));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();

@@ -155,7 +155,6 @@ class Engine {
     unsigned* d_tc_status_ = nullptr;
     // split-k workspace of the tensor-core contractions (shared by all of them: one stream)
     float *tc_ws_ = nullptr, *tc_ws_rowsum_ = nullptr;
-    unsigned* tc_counters_ = nullptr;
     size_t tc_ws_floats_ = 0;
     static constexpr int kTcMaxSplits = 8;
     int tc_splits(unsigned tiles, unsigned k) const;
@@ -179,6 +178,7 @@ class Engine {
     uint32_t *d_ent_perm_ = nullptr, *d_ent_off_ = nullptr, *d_rel_perm_ = nullptr,
              *d_rel_off_ = nullptr, *d_first_slot_ = nullptr;
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
+    unsigned* d_loss_counter_ = nullptr;
     uint8_t* pinned_ = nullptr;
     size_t pinned_bytes_ = 0;
     bool staged_ = false;
@@ -199,7 +199,9 @@ class Engine {
         float ms = 0.f;
         unsigned long long launches = 0;
     };
-    bool kernel_timing_ = false;
+    bool kernel_timing_ = false, timing_open_ = false;
+    static constexpr size_t kMaxTimedLaunches = 400;  // what the launch queue holds while the stream is held
+    std::vector<cudaEvent_t> event_pool_;
     std::vector<TimedLaunch> timed_;
     std::map<std::string, KernelTime> kernel_times_;
 

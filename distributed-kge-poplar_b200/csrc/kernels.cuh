@@ -86,6 +86,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return total;
 }
 
+// Holds the stream for about `cycles` clock ticks (bounded by the argument), so that the host can
+// queue the launches that follow before the first of them starts: per-kernel event timing then
+// measures kernels, not the host's launch rate.
+static __global__ void k_delay(long long cycles) {
+    const long long start = clock64();
+    while (clock64() - start < cycles) {
+    }
+}
+
 // ---------------------------------------------------------------------------
 // The step's row gather (fr::Buffer::read through getEntityData, src/fructose/fructose.cpp:790-798,
 // src/poplar_kge.cpp:405-410): the R rows named by `remote` are copied whole, with 128-bit
@@ -380,10 +389,35 @@ struct LossParams {
     float grad_scale;        // loss_scale / normaliser
 };
 
+// After its row, the block that finishes last adds the rows' loss terms in row order (a fixed
+// tree: the result does not depend on which block that is) and adds the step's loss to the running
+// total of the program run (src/poplar_kge.cpp:735-736).
+template <int THREADS>
+__device__ __forceinline__ void finish_step_loss(const float* loss_rows, int B, float inv_normaliser, float* loss_total,
+                                                 float* loss_last, unsigned* counter, float* scratch) {
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(counter, 1u) + 1u == gridDim.x ? 1 : 0;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float part = 0.f;
+    for (int i = threadIdx.x; i < B; i += THREADS) part += __ldcg(loss_rows + i);
+    part = block_sum<THREADS>(part, scratch);
+    if (threadIdx.x == 0) {
+        const float step_loss = part * inv_normaliser;
+        *loss_total += step_loss;
+        *loss_last = step_loss;
+        *counter = 0u;
+    }
+}
+
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float* __restrict__ coeff,
-       float* __restrict__ loss_rows, LossParams lp) {
+       float* __restrict__ loss_rows, LossParams lp, float inv_normaliser, float* __restrict__ loss_total,
+       float* __restrict__ loss_last, unsigned* __restrict__ counter) {
     __shared__ float scratch[THREADS / 32];
     const int i = blockIdx.x, T = lp.n_tail;
     const float* __restrict__ r = raw + (size_t)i * T;
@@ -415,6 +449,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
             c[j] = to_coeff(j, g);
             if (j == lab) loss_rows[i] = -logp;
         }
+        finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch);
         return;
     }
     // log-sigmoid, optionally with self-adversarial weights from a detached softmax
@@ -448,22 +483,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
     }
     part = block_sum<THREADS>(part, scratch);
     if (threadIdx.x == 0) loss_rows[i] = -part;
-}
-
-// Sums the rows' loss terms in a fixed order and adds the step's loss to the running total
-// of the program run (src/poplar_kge.cpp:735-736).
-static __global__ void __launch_bounds__(256)
-k_loss_finish(const float* __restrict__ loss_rows, int B, float inv_normaliser,
-              float* __restrict__ loss_total, float* __restrict__ loss_last) {
-    __shared__ float scratch[8];
-    float part = 0.f;
-    for (int i = threadIdx.x; i < B; i += 256) part += loss_rows[i];
-    part = block_sum<256>(part, scratch);
-    if (threadIdx.x == 0) {
-        const float step_loss = part * inv_normaliser;
-        *loss_total += step_loss;
-        *loss_last = step_loss;
-    }
+    finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch);
 }
 
 // ---------------------------------------------------------------------------
@@ -740,6 +760,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 const float* __restrict__ step_size, float lr_modifier, AdamParams ap) {
     // partial sums of the item lanes, [lane][head | tail][64 column threads][V]
     __shared__ float part[kSegmentLanes][2][64 * V];
+    __shared__ uint32_t s_perm[64 * kSegmentLanes];
     const int r = blockIdx.x, D = L.d;
     const int col = threadIdx.x & 63, lane = threadIdx.x >> 6;
     const uint32_t q0 = off[r], q1 = off[r + 1];
@@ -760,12 +781,18 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
         // Lane l sums the lookups q0 + l, q0 + l + lanes, ... in that order, four loads in flight;
         // the lanes' partial sums are then added in lane order: a fixed tree, whatever the timing.
-        if (c < D) {
-            for (uint32_t q = q0 + lane; q < q1; q += 4 * kSegmentLanes) {
+        for (uint32_t base = q0; base < q1; base += 64 * kSegmentLanes) {
+            // the segment's lookups go through shared memory, so the row loads do not wait on them
+            const int count = (int)min((uint32_t)(64 * kSegmentLanes), q1 - base);
+            __syncthreads();
+            if ((int)threadIdx.x < count) s_perm[threadIdx.x] = perm[base + threadIdx.x];
+            __syncthreads();
+            if (c >= D) continue;
+            for (int q = lane; q < count; q += 4 * kSegmentLanes) {
                 uint32_t e[4];
                 float4 g[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) e[u] = q + u * kSegmentLanes < q1 ? perm[q + u * kSegmentLanes] : 0xffffffffu;
+                for (int u = 0; u < 4; ++u) e[u] = q + u * kSegmentLanes < count ? s_perm[q + u * kSegmentLanes] : 0xffffffffu;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -937,46 +964,66 @@ k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t*
 // projection entries sum the split partials of k_projection_bwd in split order.
 constexpr int kRelationLanes = 8;
 
-static __global__ void __launch_bounds__(32 * kRelationLanes)
+template <int V>
+__global__ void __launch_bounds__(64 * kRelationLanes)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
                 float* __restrict__ dense_partial) {
-    __shared__ float part[kRelationLanes][32];
+    __shared__ float part[kRelationLanes][64 * V];
+    __shared__ uint32_t s_perm[64 * kRelationLanes];
     if ((int)blockIdx.x < n_rel) {
         // One relation row.  Relation popularity is skewed, so a few rows own most of the batch's
-        // triples: lane l sums triples q0 + l, q0 + l + lanes, ... (four loads in flight), and the
-        // lanes' partial sums are added in lane order.
-        const int rho = blockIdx.x, col = threadIdx.x & 31, lane = threadIdx.x >> 5;
+        // triples: the row's lookups are staged in shared memory, lane l sums triples l, l + lanes,
+        // ... (four loads in flight) and the lanes' partial sums are added in lane order.
+        const int rho = blockIdx.x, col = threadIdx.x & 63, lane = threadIdx.x >> 6;
         const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
         if (q0 == q1) {
             for (int c = threadIdx.x; c < D; c += blockDim.x) dense_partial[(size_t)rho * D + c] = 0.f;
             return;
         }
-        for (int c0 = 0; c0 < D; c0 += 32) {
-            const int c = c0 + col;
-            float g = 0.f;
-            if (c < D) {
-                for (uint32_t q = q0 + lane; q < q1; q += 4 * kRelationLanes) {
-                    float v[4];
+        for (int c0 = 0; c0 < D; c0 += 64 * V) {
+            const int c = c0 + col * V;
+            float g[V];
+#pragma unroll
+            for (int u = 0; u < V; ++u) g[u] = 0.f;
+            for (uint32_t base = q0; base < q1; base += 64 * kRelationLanes) {
+                const int count = (int)min((uint32_t)(64 * kRelationLanes), q1 - base);
+                __syncthreads();
+                if ((int)threadIdx.x < count) s_perm[threadIdx.x] = rel_perm[base + threadIdx.x];
+                __syncthreads();
+                if (c >= D) continue;
+                for (int i = lane; i < count; i += 4 * kRelationLanes) {
+                    float4 v[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        const uint32_t qq = q + u * kRelationLanes;
-                        v[u] = qq < q1 ? d_relrow[(size_t)rel_perm[qq] * D + c] : 0.f;
+                        const int ii = i + u * kRelationLanes;
+                        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (ii < count) {
+                            const float* src = d_relrow + (size_t)s_perm[ii] * D + c;
+                            if (V == 4) v[u] = load4(src); else v[u].x = src[0];
+                        }
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (q + u * kRelationLanes < q1) g += v[u];
+                    for (int u = 0; u < 4; ++u) {
+                        if (i + u * kRelationLanes >= count) continue;
+                        g[0] += v[u].x;
+                        if (V == 4) { g[1 % V] += v[u].y; g[2 % V] += v[u].z; g[3 % V] += v[u].w; }
+                    }
                 }
             }
             __syncthreads();
-            part[lane][col] = g;
+#pragma unroll
+            for (int u = 0; u < V; ++u) part[lane][col * V + u] = g[u];
             __syncthreads();
             if (lane == 0 && c < D) {
-                float total = part[0][col];
 #pragma unroll
-                for (int l = 1; l < kRelationLanes; ++l) total += part[l][col];
-                dense_partial[(size_t)rho * D + c] = total;
+                for (int u = 0; u < V; ++u) {
+                    float total = part[0][col * V + u];
+#pragma unroll
+                    for (int l = 1; l < kRelationLanes; ++l) total += part[l][col * V + u];
+                    dense_partial[(size_t)rho * D + c + u] = total;
+                }
             }
         }
         return;

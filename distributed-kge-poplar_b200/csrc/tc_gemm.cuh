@@ -72,13 +72,13 @@ struct GemmArgs {
     uint32_t x_row_base;
     int x_is_half;
     unsigned* status;           // device error word; non-zero = a bounded wait gave up
-    // In-kernel reduction of a k split (pipelined kernel only).  Every split writes its partial
-    // tile to ws [splits, M, N] (and its partial row sums to ws_rowsum [splits, M]); the block
-    // that arrives last at the tile's counter adds the partials in split order, applies the
-    // epilogue and resets the counter.  Null ws: each split writes its own output slice instead.
+    // k split with a deterministic reduction (pipelined kernel only).  Every split writes its raw
+    // partial tile to ws [splits, M, N] (and its partial row sums to ws_rowsum [splits, M]);
+    // k_tc_reduce then adds the partials in split order and applies the epilogue.  Null ws: each
+    // split applies the epilogue itself and writes its own output slice (out + z * split_stride).
     float* ws;
     float* ws_rowsum;
-    unsigned* counters;         // one per output tile, zero between launches
+    int splits;
     int debug_skip;             // developer aid: bit 0 no copies, 1 no split pass, 2 no MMAs, 3 no drain (timing only)
 };
 
@@ -701,41 +701,22 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
     const int nc0 = n0 + group * CPT;  // first output column of this thread
     const bool mine = m < g.M && nc0 < g.N;
     bool finish = true;
-    float rs = ROWSUM ? s_rowsum[row] : 0.f;
-    if (gridDim.z > 1 && g.ws) {
-        __shared__ int s_last;
-        const size_t plane = (size_t)g.M * g.N;
+    const float rs = ROWSUM ? s_rowsum[row] : 0.f;
+    if (g.ws) {
+        // split run: leave the raw partial tile (and partial row sums) for k_tc_reduce
         if (mine) {
-            float* w = g.ws + (size_t)blockIdx.z * plane + (size_t)m * g.N + nc0;
+            float* w = g.ws + ((size_t)blockIdx.z * g.M + m) * g.N + nc0;
+            if ((g.N & 3) == 0 && nc0 + CPT <= g.N) {
 #pragma unroll
-            for (int j = 0; j < CPT; ++j)
-                if (nc0 + j < g.N) w[j] = acc[j];
-        }
-        if (ROWSUM && tid < kBM && m0 + tid < g.M) g.ws_rowsum[(size_t)blockIdx.z * g.M + m0 + tid] = s_rowsum[tid];
-        __threadfence();
-        __syncthreads();
-        const unsigned tile = blockIdx.y * ((g.M + kBM - 1) / kBM) + (unsigned)(m0 / kBM);
-        if (tid == 0) s_last = atomicAdd(&g.counters[tile], 1u) + 1u == gridDim.z ? 1 : 0;
-        __syncthreads();
-        finish = s_last != 0;
-        if (finish) {
-            __threadfence();
-            if (mine) {
+                for (int j = 0; j < CPT; j += 4) *reinterpret_cast<float4*>(w + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            } else {
 #pragma unroll
-                for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
-                for (unsigned z = 0; z < gridDim.z; ++z) {  // split order, whoever came last
-                    const float* w = g.ws + (size_t)z * plane + (size_t)m * g.N + nc0;
-#pragma unroll
-                    for (int j = 0; j < CPT; ++j)
-                        if (nc0 + j < g.N) acc[j] += __ldcg(w + j);
-                }
-                if (ROWSUM) {
-                    rs = 0.f;
-                    for (unsigned z = 0; z < gridDim.z; ++z) rs += __ldcg(g.ws_rowsum + (size_t)z * g.M + m);
-                }
+                for (int j = 0; j < CPT; ++j)
+                    if (nc0 + j < g.N) w[j] = acc[j];
             }
-            if (tid == 0) g.counters[tile] = 0u;
         }
+        if (ROWSUM && blockIdx.y == 0 && tid < kBM && m0 + tid < g.M) g.ws_rowsum[(size_t)blockIdx.z * g.M + m0 + tid] = s_rowsum[tid];
+        finish = false;
     }
     if (finish && mine) {
         float* out_row;
@@ -743,7 +724,7 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
             const int blk = m / g.block_rows;
             out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
         } else {
-            out_row = g.out + (g.ws ? 0 : (size_t)blockIdx.z * g.split_stride) + (size_t)m * g.ldc;
+            out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
         }
         const uint8_t* x_row = nullptr;
         if (g.epilogue != EPI_STORE) {
@@ -777,6 +758,63 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, kStages * BN);
+}
+
+// Adds the partial tiles of a k split in split order and applies the epilogue of the contraction:
+// one thread per output row and group of four columns, 128-bit accesses.  blockIdx.y picks the
+// problem of a paired launch.
+static __global__ void __launch_bounds__(256) k_tc_reduce(const __grid_constant__ GemmPair gp) {
+    const GemmArgs& g = gp.p[blockIdx.y];
+    const int n4 = (g.N + 3) >> 2;
+    const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (unit >= (long long)g.M * n4) return;
+    const int m = (int)(unit / n4), n = (int)(unit - (long long)m * n4) * 4;
+    const size_t plane = (size_t)g.M * g.N;
+    const bool vec = (g.N & 3) == 0;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int z = 0; z < g.splits; ++z) {
+        const float* w = g.ws + (size_t)z * plane + (size_t)m * g.N + n;
+        if (vec) {
+            const float4 v = *reinterpret_cast<const float4*>(w);
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (n + j < g.N) acc[j] += w[j];
+        }
+    }
+    if (g.epilogue != EPI_STORE) {
+        const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
+        const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
+        float rs = 0.f;
+        if (g.epilogue == EPI_ROWSUM_X_MINUS)
+            for (int z = 0; z < g.splits; ++z) rs += g.ws_rowsum[(size_t)z * g.M + m];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (n + j >= g.N) continue;
+            if (g.epilogue == EPI_ADD_TABLE_VALUE) {
+                const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j])
+                                            : reinterpret_cast<const float*>(x_row)[n + j];
+                acc[j] = x + acc[j];
+            } else {
+                acc[j] = rs * reinterpret_cast<const float*>(x_row)[n + j] - acc[j];
+            }
+        }
+    }
+    float* out_row;
+    if (g.out_blocks) {
+        const int blk = m / g.block_rows;
+        out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+    } else {
+        out_row = g.out + (size_t)m * g.ldc;
+    }
+    if (vec && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(out_row) & 15) == 0) {
+        *reinterpret_cast<float4*>(out_row + n) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (n + j < g.N) out_row[n + j] = acc[j];
+    }
 }
 
 // Host side: grid = (ceil(M / 128), ceil(N / BN), splits).
@@ -835,6 +873,16 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
     }
     dim3 grid(tiles_m, tiles_n, splits);
     kernel<<<grid, 128 * CG, smem_bytes_async<BN>(), stream>>>(gp);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess || !problems[0].ws) return err;
+    gp.p[0].splits = gp.p[1].splits = splits;
+    long long units = 0;
+    for (int i = 0; i < n_problems; ++i) {
+        const long long u = (long long)problems[i].M * ((problems[i].N + 3) / 4);
+        units = u > units ? u : units;
+    }
+    dim3 rgrid((unsigned)((units + 255) / 256), n_problems);
+    k_tc_reduce<<<rgrid, 256, 0, stream>>>(gp);
     return cudaGetLastError();
 }
 
