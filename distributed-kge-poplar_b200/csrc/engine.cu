@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace kge {
@@ -687,6 +688,14 @@ void Engine::last_run_stats(float* ms, unsigned long long* launches) const {
         ++launch_counter_;               \
     } while (0)
 
+bool dependent_launch_enabled() {
+    static const bool enabled = [] {
+        const char* off = std::getenv("KGE_NO_DEPENDENT_LAUNCH");
+        return !(off && off[0] && off[0] != '0');
+    }();
+    return enabled;
+}
+
 void Engine::launch_steps() {
     for (unsigned step = 0; step < cfg_.n_step; ++step) launch_one_step(step);
 }
@@ -700,7 +709,7 @@ void Engine::launch_barrier() {
     a.rank = (int)cfg_.rank;
     a.world = (int)cfg_.world;
     a.max_spins = 2ull * 1000 * 1000;  // a second or two of 64 ns naps plus load latency
-    KGE_LAUNCH("barrier", k_barrier<<<1, 64, 0, stream_>>>(a));
+    KGE_LAUNCH("barrier", KGE_CUDA(launch_dependent(k_barrier, dim3(1), dim3(64), 0, stream_, a)));
     KGE_CUDA(cudaGetLastError());
 }
 
@@ -813,7 +822,7 @@ void Engine::launch_one_step(unsigned step) {
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
         const uint32_t* remote = step_ptr(d_remote_, l, R);
-        KGE_LAUNCH("gather", k_gather_step_rows<<<ceil_div(R, 8), 256, 0, stream_>>>(b.table, layout_.row_bytes, remote, (int)R, b.rows_c));
+        KGE_LAUNCH("gather", KGE_CUDA(launch_dependent(k_gather_step_rows, dim3(ceil_div(R, 8)), dim3(256), 0, stream_, b.table, layout_.row_bytes, remote, (int)R, b.rows_c)));
         if (cfg_.tensor_cores && F > 0) {
             // hidden = value + feature . W on the tensor cores: A = gathered feature rows, B = W stored [F, D]
             tc::GemmArgs nets[2] = {};
@@ -831,20 +840,20 @@ void Engine::launch_one_step(unsigned step) {
             launch_tc("hidden", nets, n_nets, tc_splits(n_nets * ceil_div(R, 128) * ceil_div(D, 64), F), cfg_.feature_type == ST_F16, false);
         } else {
             dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
-            KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
-                                                            b.rows_c, layout_, nullptr, 0u, (int)R, W0, W1, b.hid_h, b.hid_t)));
+            KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, KGE_CUDA(launch_dependent(k_hidden<ST, FT>, dim3(grid), dim3(256), 0, stream_, 
+                                                            b.rows_c, layout_, nullptr, 0u, (int)R, W0, W1, b.hid_h, b.hid_t))));
         }
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
         if (vec)
-            KGE_LAUNCH("route", k_route<4><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table,
+            KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn));
+                                                                      (int)B, (int)D, cfg_.score_fn)));
         else
-            KGE_LAUNCH("route", k_route<1><<<T + B, 64, 0, stream_>>>(b.hid_h, b.hid_t, a2a, head, relation, rel_table,
+            KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<1>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn));
+                                                                      (int)B, (int)D, cfg_.score_fn)));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -873,12 +882,12 @@ void Engine::launch_one_step(unsigned step) {
             launch_tc("score", &g, 1, tc_splits(ceil_div(B, 128) * ceil_div(T, 64), D), false, false);
         } else
         switch (cfg_.dist_fn) {
-            case DIST_L1: KGE_LAUNCH("score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
-            case DIST_L2: KGE_LAUNCH("score", k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
-            default: KGE_LAUNCH("score", k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(b.pred, b.tails, b.raw, (int)B, (int)T, (int)D)); break;
+            case DIST_L1: KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_score<DIST_L1>, dim3(sgrid), dim3(128), 0, stream_, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D))); break;
+            case DIST_L2: KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_score<DIST_L2>, dim3(sgrid), dim3(128), 0, stream_, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D))); break;
+            default: KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_score<DIST_DOT>, dim3(sgrid), dim3(128), 0, stream_, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D))); break;
         }
-        KGE_LAUNCH("loss", k_loss<256><<<B, 256, 0, stream_>>>(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
-                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l));
+        KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
+                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l)));
         if (tc_bwd) {
             // Both input gradients are contractions with the coefficient matrix C [B, T]:
             //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
@@ -904,13 +913,13 @@ void Engine::launch_one_step(unsigned step) {
             launch_tc("score_bwd", both, 2, tc_splits((ceil_div(B, 128) + ceil_div(T, 128)) * ceil_div(D, 64), std::min(B, T)), false, l2);
         } else
         switch (cfg_.dist_fn) {
-            case DIST_L1: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L1><<<bgrid, 128, 0, stream_>>>(pa)); break;
-            case DIST_L2: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_L2><<<bgrid, 128, 0, stream_>>>(pa)); break;
-            default: KGE_LAUNCH("score_bwd", k_pair_bwd<DIST_DOT><<<bgrid, 128, 0, stream_>>>(pa)); break;
+            case DIST_L1: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_L1>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
+            case DIST_L2: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_L2>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
+            default: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_DOT>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
         }
         if (cfg_.score_fn != SCORE_TRANSE)
-            KGE_LAUNCH("pred_bwd", k_pred_bwd<<<B, 64, 0, stream_>>>(b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
-                                                                     b.d_relrow, (int)D, cfg_.score_fn));
+            KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
+                                                                     b.d_relrow, (int)D, cfg_.score_fn)));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -926,22 +935,22 @@ void Engine::launch_one_step(unsigned step) {
         const float* alpha = d_step_size_ + step;
         if (cfg_.state_type == ST_F32) {
             if (vec)
-                KGE_LAUNCH("entity_update", k_entity_update<float, 4><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
             else
-                KGE_LAUNCH("entity_update", k_entity_update<float, 1><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
         } else {
             if (vec)
-                KGE_LAUNCH("entity_update", k_entity_update<__half, 4><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
             else
-                KGE_LAUNCH("entity_update", k_entity_update<__half, 1><<<R, 64 * kSegmentLanes, 0, stream_>>>(
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
         }
         if (F > 0 && cfg_.tensor_cores) {
             // d W = feature^T . d_hidden: the gathered rows are the k index of both operands
@@ -960,26 +969,26 @@ void Engine::launch_one_step(unsigned step) {
             dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
             if (cfg_.feature_type == ST_F32)
-                KGE_LAUNCH("projection_bwd", k_projection_bwd<float><<<grid, 256, 0, stream_>>>(
+                KGE_LAUNCH("projection_bwd", KGE_CUDA(launch_dependent(k_projection_bwd<float>, dim3(grid), dim3(256), 0, stream_, 
                                                  b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
-                                                 proj_rows_per_split_, b.proj_partial));
+                                                 proj_rows_per_split_, b.proj_partial)));
             else
-                KGE_LAUNCH("projection_bwd", k_projection_bwd<__half><<<grid, 256, 0, stream_>>>(
+                KGE_LAUNCH("projection_bwd", KGE_CUDA(launch_dependent(k_projection_bwd<__half>, dim3(grid), dim3(256), 0, stream_, 
                                                  b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
-                                                 proj_rows_per_split_, b.proj_partial));
+                                                 proj_rows_per_split_, b.proj_partial)));
         }
         const size_t proj_total = (size_t)cfg_.n_net() * proj_elems_;
         const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 511) / 512, 148 * 4) : 0;
         if (vec)
-            KGE_LAUNCH("dense_partial", k_dense_partial<4><<<n_rel + proj_blocks, 64 * kRelationLanes, 0, stream_>>>(
+            KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_, 
                                             b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                             (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
-                                            proj_elems_, b.dense_partial));
+                                            proj_elems_, b.dense_partial)));
         else
-            KGE_LAUNCH("dense_partial", k_dense_partial<1><<<n_rel + proj_blocks, 64 * kRelationLanes, 0, stream_>>>(
+            KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_, 
                                             b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                             (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
-                                            proj_elems_, b.dense_partial));
+                                            proj_elems_, b.dense_partial)));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();
@@ -1001,7 +1010,7 @@ void Engine::launch_one_step(unsigned step) {
         da.ap = adam_;
         // The parameter itself is read from this process's own replica (entry `rank`).
         const unsigned blocks = (unsigned)std::min<size_t>((own_hi_ - own_lo_ + 255) / 256, 148 * 8);
-        KGE_LAUNCH("dense_update", k_dense_update<<<std::max(1u, blocks), 256, 0, stream_>>>(da, (int)cfg_.rank));
+        KGE_LAUNCH("dense_update", KGE_CUDA(launch_dependent(k_dense_update, dim3(std::max(1u, blocks)), dim3(256), 0, stream_, da, (int)cfg_.rank)));
     }
     KGE_CUDA(cudaGetLastError());
     launch_barrier();

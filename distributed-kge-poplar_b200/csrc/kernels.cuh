@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace kge {
 
 enum ScoreFn : int { SCORE_TRANSE = 0, SCORE_DISTMULT = 1, SCORE_COMPLEX = 2 };
@@ -105,6 +107,7 @@ static __global__ void k_delay(long long cycles) {
 static __global__ void __launch_bounds__(256)
 k_gather_step_rows(const uint8_t* __restrict__ table, uint32_t row_bytes, const uint32_t* __restrict__ remote, int R,
                    uint8_t* __restrict__ rows_c) {
+    grid_dependency_sync();
     const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= R) return;
     const uint4* __restrict__ src = reinterpret_cast<const uint4*>(table + (size_t)remote[r] * row_bytes);
@@ -133,6 +136,7 @@ __global__ void __launch_bounds__(256)
 k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote,
          uint32_t row_base, int R, const float* __restrict__ W0, const float* __restrict__ W1,
          float* __restrict__ out0, float* __restrict__ out1) {
+    grid_dependency_sync();
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ __align__(16) float As[BK][BM + 4];
     __shared__ __align__(16) float Bs[BK][BN];
@@ -229,6 +233,7 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         const uint32_t* __restrict__ relation, const float* __restrict__ rel_table,
         float* const* __restrict__ send_dst, float* __restrict__ pred, int T, int a2a, int B, int D,
         int score_fn) {
+    grid_dependency_sync();
     const int b = blockIdx.x;
     if (b < T) {
         const int dst = b / a2a, j = b - dst * a2a;
@@ -279,6 +284,7 @@ template <int FN>
 __global__ void __launch_bounds__(128)
 k_score(const float* __restrict__ P, const float* __restrict__ Tl, float* __restrict__ raw, int B,
         int T, int D) {
+    grid_dependency_sync();
     constexpr int BM = 32, BN = 64, BK = 32;
     __shared__ __align__(16) float Ps[BK][BM];
     __shared__ __align__(16) float Ts[BK][BN];
@@ -418,6 +424,7 @@ __global__ void __launch_bounds__(THREADS)
 k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float* __restrict__ coeff,
        float* __restrict__ loss_rows, LossParams lp, float inv_normaliser, float* __restrict__ loss_total,
        float* __restrict__ loss_last, unsigned* __restrict__ counter) {
+    grid_dependency_sync();
     __shared__ float scratch[THREADS / 32];
     const int i = blockIdx.x, T = lp.n_tail;
     const float* __restrict__ r = raw + (size_t)i * T;
@@ -513,6 +520,7 @@ struct PairBwdArgs {
 
 template <int FN>
 __global__ void __launch_bounds__(128) k_pair_bwd(PairBwdArgs args) {
+    grid_dependency_sync();
     constexpr int BM = 32, BD = 64, BN = 32;
     __shared__ float Cs[BM][BN + 1];
     __shared__ __align__(16) float Ys[BN][BD];
@@ -618,6 +626,7 @@ k_pred_bwd(const float* __restrict__ d_pred, const float* __restrict__ hid_h,
            const uint32_t* __restrict__ head, const uint32_t* __restrict__ relation,
            const float* __restrict__ rel_table, float* __restrict__ d_head,
            float* __restrict__ d_relrow, int D, int score_fn) {
+    grid_dependency_sync();
     const int i = blockIdx.x;
     const float* __restrict__ dp = d_pred + (size_t)i * D;
     const float* __restrict__ h = hid_h + (size_t)head[i] * D;
@@ -758,6 +767,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 const float* __restrict__ grad_recv, int B,
                 float* __restrict__ d_hid_h, float* __restrict__ d_hid_t,
                 const float* __restrict__ step_size, float lr_modifier, AdamParams ap) {
+    grid_dependency_sync();
     // partial sums of the item lanes, [lane][head | tail][64 column threads][V]
     __shared__ float part[kSegmentLanes][2][64 * V];
     __shared__ uint32_t s_perm[64 * kSegmentLanes];
@@ -886,6 +896,7 @@ __global__ void __launch_bounds__(256)
 k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restrict__ remote,
                  int R, const float* __restrict__ dh0, const float* __restrict__ dh1, int splits,
                  int rows_per_split, float* __restrict__ partial) {
+    grid_dependency_sync();
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ __align__(16) float As[BK][BM];
     __shared__ __align__(16) float Bs[BK][BN];
@@ -970,6 +981,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
                 float* __restrict__ dense_partial) {
+    grid_dependency_sync();
     __shared__ float part[kRelationLanes][64 * V];
     __shared__ uint32_t s_perm[64 * kRelationLanes];
     if ((int)blockIdx.x < n_rel) {
@@ -1060,6 +1072,7 @@ struct DenseUpdateArgs {
 };
 
 static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, int self) {
+    grid_dependency_sync();
     const float base_alpha = *a.step_size;
     for (size_t e = a.lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < a.hi;
          e += (size_t)gridDim.x * blockDim.x) {
@@ -1090,6 +1103,7 @@ struct BarrierArgs {
 };
 
 static __global__ void k_barrier(BarrierArgs a) {
+    grid_dependency_sync();
     __shared__ unsigned epoch;
     if (threadIdx.x == 0) {
         epoch = *a.my_epoch + 1;

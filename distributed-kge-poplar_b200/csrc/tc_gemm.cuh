@@ -29,6 +29,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace kge {
 namespace tc {
 
@@ -280,6 +282,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    grid_dependency_sync();
     const uint32_t tmem_base = tmem_slot;
     constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
 
@@ -599,6 +602,7 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    grid_dependency_sync();
     const uint32_t tmem_base = tmem_slot;
     constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
 
@@ -764,6 +768,7 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
 // one thread per output row and group of four columns, 128-bit accesses.  blockIdx.y picks the
 // problem of a paired launch.
 static __global__ void __launch_bounds__(256) k_tc_reduce(const __grid_constant__ GemmPair gp) {
+    grid_dependency_sync();
     const GemmArgs& g = gp.p[blockIdx.y];
     const int n4 = (g.N + 3) >> 2;
     const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -828,8 +833,7 @@ inline cudaError_t launch(const GemmArgs& g, int splits, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid((g.M + kBM - 1) / kBM, (g.N + BN - 1) / BN, splits);
-    kernel<<<grid, kThreads, smem_bytes<BN>(), stream>>>(g);
-    return cudaGetLastError();
+    return launch_dependent(kernel, grid, dim3(kThreads), smem_bytes<BN>(), stream, g);
 }
 
 inline bool rows_16_byte_aligned(const Operand& op) {
@@ -872,8 +876,7 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         tiles_n = tiles_n > (problems[1].N + BN - 1) / BN ? tiles_n : (problems[1].N + BN - 1) / BN;
     }
     dim3 grid(tiles_m, tiles_n, splits);
-    kernel<<<grid, 128 * CG, smem_bytes_async<BN>(), stream>>>(gp);
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err = launch_dependent(kernel, grid, dim3(128 * CG), smem_bytes_async<BN>(), stream, gp);
     if (err != cudaSuccess || !problems[0].ws) return err;
     gp.p[0].splits = gp.p[1].splits = splits;
     long long units = 0;
@@ -882,8 +885,7 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         units = u > units ? u : units;
     }
     dim3 rgrid((unsigned)((units + 255) / 256), n_problems);
-    k_tc_reduce<<<rgrid, 256, 0, stream>>>(gp);
-    return cudaGetLastError();
+    return launch_dependent(k_tc_reduce, rgrid, dim3(256), 0, stream, gp);
 }
 
 inline Operand make_operand(const void* base, long long row_stride_bytes, bool is_half, bool transposed,
