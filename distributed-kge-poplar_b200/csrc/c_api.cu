@@ -214,11 +214,7 @@ int kge_op_pairwise(int fn, const float* a, const float* b, size_t m, size_t n, 
         DeviceBuffer da(m * k * 4), db(n * k * 4), dout(m * n * 4);
         to_device(da, a, m * k * 4);
         to_device(db, b, n * k * 4);
-        dim3 grid(blocks_for(n, 64), blocks_for(m, 32));
-        const int M = (int)m, N = (int)n, K = (int)k;
-        if (fn == DIST_L1) k_score<DIST_L1><<<grid, 128>>>(da.as<float>(), db.as<float>(), dout.as<float>(), M, N, K);
-        else if (fn == DIST_L2) k_score<DIST_L2><<<grid, 128>>>(da.as<float>(), db.as<float>(), dout.as<float>(), M, N, K);
-        else k_score<DIST_DOT><<<grid, 128>>>(da.as<float>(), db.as<float>(), dout.as<float>(), M, N, K);
+        KGE_CUDA(launch_score(fn, da.as<float>(), db.as<float>(), dout.as<float>(), (int)m, (int)n, (int)k, nullptr));
         finish_kernels();
         to_host(out, dout, m * n * 4);
     });
@@ -239,8 +235,7 @@ int kge_op_pairwise_grad(int fn, const float* a, const float* b, const float* gr
             // (src/poplar_extensions/l2distance.codelet.cpp:149-158): take the distance from
             // the forward kernel, then fold the division into the coefficient.
             DeviceBuffer ddist(m * n * 4);
-            dim3 grid(blocks_for(n, 64), blocks_for(m, 32));
-            k_score<DIST_L2><<<grid, 128>>>(da.as<float>(), db.as<float>(), ddist.as<float>(), (int)m, (int)n, (int)k);
+            KGE_CUDA(launch_score(DIST_L2, da.as<float>(), db.as<float>(), ddist.as<float>(), (int)m, (int)n, (int)k, nullptr));
             finish_kernels();
             std::vector<float> dist(m * n);
             to_host(dist.data(), ddist, m * n * 4);

@@ -864,7 +864,6 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
         const uint32_t* tail = step_ptr(d_tail_, l, B);
-        dim3 sgrid(ceil_div(T, 64), ceil_div(B, 32));
         PairBwdArgs pa{};
         pa.D = (int)D;
         pa.tiles_m0 = (int)ceil_div(B, 32);
@@ -880,11 +879,8 @@ void Engine::launch_one_step(unsigned step) {
             g.M = (int)B; g.N = (int)T; g.K = (int)D; g.k_per_split = (int)round_up(D, 32);
             g.epilogue = tc::EPI_STORE; g.out = b.raw; g.ldc = T; g.block_rows = 1;
             launch_tc("score", &g, 1, tc_splits(ceil_div(B, 128) * ceil_div(T, 64), D), false, false);
-        } else
-        switch (cfg_.dist_fn) {
-            case DIST_L1: KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_score<DIST_L1>, dim3(sgrid), dim3(128), 0, stream_, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D))); break;
-            case DIST_L2: KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_score<DIST_L2>, dim3(sgrid), dim3(128), 0, stream_, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D))); break;
-            default: KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_score<DIST_DOT>, dim3(sgrid), dim3(128), 0, stream_, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D))); break;
+        } else {
+            KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_)));
         }
         KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
                                                                d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l)));
@@ -1232,12 +1228,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
             KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<hgrid, 256, 0, stream_>>>(
                                                                     b.table, layout_, nullptr, start, (int)c, W_tail, nullptr,
                                                                     p_chunk_hidden_, nullptr)));
-            dim3 sgrid(ceil_div(c, 64), ceil_div((unsigned)Q, 32));
-            switch (cfg_.dist_fn) {
-                case DIST_L1: KGE_LAUNCH("predict_score", k_score<DIST_L1><<<sgrid, 128, 0, stream_>>>(queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D)); break;
-                case DIST_L2: KGE_LAUNCH("predict_score", k_score<DIST_L2><<<sgrid, 128, 0, stream_>>>(queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D)); break;
-                default: KGE_LAUNCH("predict_score", k_score<DIST_DOT><<<sgrid, 128, 0, stream_>>>(queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D)); break;
-            }
+            KGE_LAUNCH("predict_score", KGE_CUDA(launch_score(cfg_.dist_fn, queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D, stream_)));
             KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div((unsigned)Q, 4), 128, 0, stream_>>>(
                                            p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp));
         }

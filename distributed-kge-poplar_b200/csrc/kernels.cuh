@@ -375,6 +375,132 @@ k_score(const float* __restrict__ P, const float* __restrict__ Tl, float* __rest
     }
 }
 
+// The same scores for rows that allow 16-byte copies (D a multiple of 4, 16-byte aligned bases).
+// A block owns a 32x32 tile of outputs and its 8 warps divide the k range in chunks of 32: warp w
+// copies its own 32x32 chunk of both operands into its private part of shared memory (asynchronous
+// 16-byte copies, row-major with a stride of 36 floats, which keeps the 128-bit reads below free of
+// bank conflicts), accumulates a 4x8 register tile per lane over the chunk, and the 8 partial tiles
+// are added through shared memory at the end.  Splitting k, not the tile, is what gives every SM
+// several warps of independent work on a problem of only B x T = 512 x 768 outputs.
+constexpr int kScoreStride = 36;
+constexpr int kScoreWarps = 8;
+constexpr size_t kScoreWideSmem = (size_t)kScoreWarps * 2 * 32 * kScoreStride * sizeof(float);
+
+__device__ __forceinline__ void score_copy16(float* dst_smem, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+
+template <int FN>
+__global__ void __launch_bounds__(32 * kScoreWarps, 3)
+k_score_wide(const float* __restrict__ P, const float* __restrict__ Tl, float* __restrict__ raw, int B,
+             int T, int D) {
+    grid_dependency_sync();
+    extern __shared__ __align__(16) float score_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+    float* Ps = score_smem + (size_t)warp * 2 * 32 * kScoreStride;
+    float* Ts = Ps + 32 * kScoreStride;
+    const int ty = lane >> 2, tx = lane & 3;  // p rows ty + 8a, t rows tx + 4b
+    const int n_chunks = (D + 31) / 32;
+    float acc[4][8];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.f;
+
+    for (int chunk = warp; chunk < n_chunks; chunk += kScoreWarps) {
+        const int k0 = chunk * 32;
+        __syncwarp();
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+            const int row = it * 4 + (lane >> 3), k4 = (lane & 7) * 4;
+            float* pd = Ps + row * kScoreStride + k4;
+            float* td = Ts + row * kScoreStride + k4;
+            if (i0 + row < B && k0 + k4 < D) score_copy16(pd, P + (size_t)(i0 + row) * D + k0 + k4);
+            else *reinterpret_cast<float4*>(pd) = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j0 + row < T && k0 + k4 < D) score_copy16(td, Tl + (size_t)(j0 + row) * D + k0 + k4);
+            else *reinterpret_cast<float4*>(td) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncwarp();
+#pragma unroll 1
+        for (int k4 = 0; k4 < 32; k4 += 4) {
+            float4 pv[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) pv[a] = load4(Ps + (ty + 8 * a) * kScoreStride + k4);
+#pragma unroll
+            for (int half = 0; half < 4; ++half) {
+                float4 tv[2];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) tv[b] = load4(Ts + (tx + 4 * (half * 2 + b)) * kScoreStride + k4);
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const float pr[4] = {pv[a].x, pv[a].y, pv[a].z, pv[a].w};
+                        const float tr[4] = {tv[b].x, tv[b].y, tv[b].z, tv[b].w};
+                        float& sum = acc[a][half * 2 + b];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            if (FN == DIST_L1) {
+                                sum += fabsf(pr[c] - tr[c]);
+                            } else if (FN == DIST_L2) {
+                                const float d = pr[c] - tr[c];
+                                sum = fmaf(d, d, sum);
+                            } else {
+                                sum = fmaf(pr[c], tr[c], sum);
+                            }
+                        }
+                    }
+            }
+        }
+    }
+    // add the warps' partial tiles: red[warp][p row][t row], stride 33
+    __syncthreads();
+    float* red = score_smem;
+    const int n_active = n_chunks < kScoreWarps ? n_chunks : kScoreWarps;
+    if (warp < n_active) {
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 8; ++b) red[(warp * 32 + ty + 8 * a) * 33 + tx + 4 * b] = acc[a][b];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int o = threadIdx.x + it * 32 * kScoreWarps, prow = o >> 5, trow = o & 31;
+        float sum = 0.f;
+        for (int w = 0; w < n_active; ++w) sum += red[(w * 32 + prow) * 33 + trow];
+        const int i = i0 + prow, j = j0 + trow;
+        if (i < B && j < T) raw[(size_t)i * T + j] = FN == DIST_L2 ? sqrtf(sum) : sum;
+    }
+}
+
+// Picks the kernel: the 16-byte-copy form when the rows allow it, the general form otherwise.
+template <int FN>
+inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream) {
+    const bool aligned = (D % 4) == 0 && reinterpret_cast<uintptr_t>(P) % 16 == 0 && reinterpret_cast<uintptr_t>(Tl) % 16 == 0;
+    if (!aligned)
+        return launch_dependent(k_score<FN>, dim3((T + 63) / 64, (B + 31) / 32), dim3(128), 0, stream, P, Tl, raw, B, T, D);
+    static bool configured = false;  // one attribute call per instantiation and process is enough
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(k_score_wide<FN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreWideSmem);
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    return launch_dependent(k_score_wide<FN>, dim3((T + 31) / 32, (B + 31) / 32), dim3(32 * kScoreWarps), kScoreWideSmem, stream,
+                            P, Tl, raw, B, T, D);
+}
+
+inline cudaError_t launch_score(int dist_fn, const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream) {
+    switch (dist_fn) {
+        case DIST_L1: return launch_score<DIST_L1>(P, Tl, raw, B, T, D, stream);
+        case DIST_L2: return launch_score<DIST_L2>(P, Tl, raw, B, T, D, stream);
+        default: return launch_score<DIST_DOT>(P, Tl, raw, B, T, D, stream);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Loss forward and backward for one row of scores per block
 // (src/poplar_kge.cpp:615-660; guarded log-sigmoid src/pag/pag.cpp:888-910; log-softmax
