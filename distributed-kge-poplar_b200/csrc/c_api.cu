@@ -387,12 +387,9 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         g.status = dstatus.as<unsigned>();
         const bool exact = a_half != 0, rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
         cudaError_t err = cudaSuccess;
-        // Developer aid: KGE_TC_REPEAT=n launches the kernel n more times between two events and prints
-        // the mean time; KGE_TC_DEBUG=bits switches phases of the pipelined kernel off (results are then wrong).
+        // Developer aid: KGE_TC_REPEAT=n launches the kernel n more times between two events and prints the mean time.
         const char* env_repeat = std::getenv("KGE_TC_REPEAT");
-        const char* env_debug = std::getenv("KGE_TC_DEBUG");
         const int repeat = env_repeat ? std::atoi(env_repeat) : 0;
-        g.debug_skip = env_debug ? std::atoi(env_debug) : 0;
         // KGE_TC_WS=1: add the k splits with the reduction kernel (the engine's way); the sum lands in
         // the first slice of out and the other slices stay zero
         const bool in_kernel_reduce = std::getenv("KGE_TC_WS") && splits > 1 && tile_n == 64;
@@ -423,8 +420,7 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
             KGE_CUDA(cudaEventSynchronize(e1));
             float ms = 0.f;
             KGE_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-            std::fprintf(stderr, "kge_op_tc_gemm m=%zu n=%zu k=%zu splits=%d debug=%d: %.2f us per launch\n", m, n, k, splits,
-                         g.debug_skip, 1e3f * ms / repeat);
+            std::fprintf(stderr, "kge_op_tc_gemm m=%zu n=%zu k=%zu splits=%d: %.2f us per launch\n", m, n, k, splits, 1e3f * ms / repeat);
             cudaEventDestroy(e0);
             cudaEventDestroy(e1);
         }

@@ -747,7 +747,10 @@ void Engine::timing_collect() {
 int Engine::tc_splits(unsigned tiles, unsigned k) const {
     const unsigned by_sms = std::max(1u, 148u / std::max(1u, tiles));
     const unsigned by_k = std::max(1u, k / 64u);
-    return (int)std::min<unsigned>({by_sms, by_k, (unsigned)kTcMaxSplits});
+    int splits = (int)std::min<unsigned>({by_sms, by_k, (unsigned)kTcMaxSplits});
+    // the splits of a tile run as one cluster: all tiles' clusters should be resident together
+    while (splits > 1 && (unsigned)tc::max_resident_clusters(splits) < tiles) --splits;
+    return splits;
 }
 
 // One launch for one or two contractions of the same kind (see tc_gemm.cuh).  With splits > 1
@@ -775,12 +778,13 @@ void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems,
     }
     cudaError_t err;
     timing_begin(name);
-    if (a_exact) err = rowsum ? tc::launch_pair<64, true, true>(problems, n_problems, splits, stream_)
-                              : tc::launch_pair<64, true, false>(problems, n_problems, splits, stream_);
-    else err = rowsum ? tc::launch_pair<64, false, true>(problems, n_problems, splits, stream_)
-                      : tc::launch_pair<64, false, false>(problems, n_problems, splits, stream_);
+    int n_launches = 1;
+    if (a_exact) err = rowsum ? tc::launch_pair<64, true, true>(problems, n_problems, splits, stream_, &n_launches)
+                              : tc::launch_pair<64, true, false>(problems, n_problems, splits, stream_, &n_launches);
+    else err = rowsum ? tc::launch_pair<64, false, true>(problems, n_problems, splits, stream_, &n_launches)
+                      : tc::launch_pair<64, false, false>(problems, n_problems, splits, stream_, &n_launches);
     timing_end();
-    launch_counter_ += problems[0].ws ? 2 : 1;
+    launch_counter_ += (unsigned long long)n_launches;
     KGE_CUDA(err);
 }
 

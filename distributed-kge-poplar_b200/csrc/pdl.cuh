@@ -27,21 +27,39 @@ __device__ __forceinline__ void grid_dependency_sync() {
 // Process-wide switch (on by default; KGE_NO_DEPENDENT_LAUNCH=1 in the environment turns it off).
 bool dependent_launch_enabled();
 
-// kernel<<<grid, block, smem, stream>>>(args...) with the attribute when enabled.
+// kernel<<<grid, block, smem, stream>>>(args...) with the attribute when enabled; cluster_z > 1
+// also makes every cluster_z blocks that are neighbours in z one thread-block cluster.
 template <typename... Params, typename... Args>
-inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args&&... args) {
+inline cudaError_t launch_dependent_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                            unsigned cluster_z, Args&&... args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attribute[2];
+    unsigned n = 0;
+    if (dependent_launch_enabled()) {
+        attribute[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attribute[n].id = cudaLaunchAttributeClusterDimension;
+        attribute[n].val.clusterDim.x = 1;
+        attribute[n].val.clusterDim.y = 1;
+        attribute[n].val.clusterDim.z = cluster_z;
+        ++n;
+    }
     config.attrs = attribute;
-    config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+    config.numAttrs = n;
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    return launch_dependent_cluster(kernel, grid, block, smem, stream, 1u, static_cast<Args&&>(args)...);
 }
 
 }  // namespace kge

@@ -81,7 +81,9 @@ struct GemmArgs {
     float* ws;
     float* ws_rowsum;
     int splits;
-    int debug_skip;             // developer aid: bit 0 no copies, 1 no split pass, 2 no MMAs, 3 no drain (timing only)
+    // Set by launch_pair: the blocks of one output tile (one per split) form a thread-block cluster
+    // and reduce their partial tiles through distributed shared memory; 0 = not a cluster launch.
+    int cluster_splits;
 };
 
 // ---------------------------------------------------------------------------
@@ -412,17 +414,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
 // ---------------------------------------------------------------------------
 // Pipelined form.  Same arithmetic as k_tc_gemm, but the operand slices travel from global
 // memory to a ring of raw tiles in shared memory with cp.async (16 bytes per copy, zero-filled
-// outside the matrix), kRawStages - 1 slices ahead of their use, so the L2 latency is hidden
-// behind the split pass and the MMAs of earlier slices.  The split pass then reads the raw tile
-// from shared memory, splits (and, for mn-major operands, transposes) it into the swizzled
-// K-major hi / lo tiles.  The block has 4 * CG warps: the staging work is spread over all of
-// them, and warp w drains TMEM lanes 32 * (w % 4) .. (the quarter a warp may touch), columns of
-// group w / 4, so every thread keeps BN / CG accumulators.  Requires every operand row to start
-// on a 16-byte boundary; otherwise the launcher falls back to k_tc_gemm.  Two problems of the
-// same kind (the two gradients of the score, the two feature networks) can share one launch:
-// blockIdx.x picks the problem.
-
-constexpr int kRawStages = 3;
+// outside the matrix), three slices ahead of their use, so the L2 latency is hidden behind the
+// work on earlier slices, and the block's warps are specialised (staging, issuing, accumulating:
+// see the kernel).  The split pass reads the raw tile from shared memory and splits (and, for
+// mn-major operands, transposes) it into the swizzled K-major hi / lo tiles.  Requires every
+// operand row to start on a 16-byte boundary; otherwise the launcher falls back to k_tc_gemm.
+// Two problems of the same kind (the two gradients of the score, the two feature networks) can
+// share one launch: blockIdx.x picks the problem.  A k range divided over blockIdx.z is reduced
+// either through the distributed shared memory of a thread-block cluster (up to 8 splits) or by
+// k_tc_reduce over a workspace.
 
 struct GemmPair {
     GemmArgs p[2];
@@ -517,7 +517,7 @@ __device__ __forceinline__ void store_split(uint8_t* tile_hi, uint8_t* tile_lo, 
 //   mn-major: row tid % 128 for every i, the threads tid, tid + 128, ... share a row.
 template <int ROWS, int NT, bool WRITE_LO, bool ROWSUM>
 __device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw, uint8_t* tile_hi, uint8_t* tile_lo,
-                                          float (&rowsum)[2]) {
+                                          float (&rowsum)[4]) {
     const int tid = threadIdx.x;
     if (!op.transposed) {
         if (!op.is_half) {
@@ -527,7 +527,7 @@ __device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw,
                 const int row = u >> 3, ch = u & 7;
                 const float4 x = *reinterpret_cast<const float4*>(raw + row * 128 + ch * 16);
                 const float v[4] = {x.x, x.y, x.z, x.w};
-                if (ROWSUM) rowsum[i & 1] += (v[0] + v[1]) + (v[2] + v[3]);
+                if (ROWSUM) rowsum[i & 3] += (v[0] + v[1]) + (v[2] + v[3]);
                 store_split(tile_hi, tile_lo, row, ch, v, WRITE_LO);
             }
         } else {
@@ -564,29 +564,113 @@ __device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw,
     }
 }
 
-template <int BN>
-constexpr size_t smem_bytes_async() {
-    return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128) + (size_t)kRawStages * (kBM * 128 + BN * 128);
+// Epilogue and store of four neighbouring output columns (m, n .. n+3) whose k range is complete.
+__device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, int m, int n, float (&acc)[4], float rs) {
+    if (g.epilogue != EPI_STORE) {
+        const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
+        const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (n + j >= g.N) continue;
+            if (g.epilogue == EPI_ADD_TABLE_VALUE) {
+                const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j])
+                                            : reinterpret_cast<const float*>(x_row)[n + j];
+                acc[j] = x + acc[j];
+            } else {
+                acc[j] = rs * reinterpret_cast<const float*>(x_row)[n + j] - acc[j];
+            }
+        }
+    }
+    float* out_row;
+    if (g.out_blocks) {
+        const int blk = m / g.block_rows;
+        out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+    } else {
+        out_row = out_base + (size_t)m * g.ldc;
+    }
+    if ((g.N & 3) == 0 && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(out_row) & 15) == 0) {
+        *reinterpret_cast<float4*>(out_row + n) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (n + j < g.N) out_row[n + j] = acc[j];
+    }
 }
 
-template <int BN, int CG, bool A_EXACT, bool ROWSUM>
-__global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_constant__ GemmPair gp) {
-    constexpr int NT = 128 * CG;      // threads
-    constexpr int CPT = BN / CG;      // accumulator columns per thread
-    static_assert(CPT == 16 || CPT == 32, "a thread drains 16 or 32 columns");
-    static_assert(!ROWSUM || (NT == 512 || NT == 256 || NT == 128), "row sums assume at most two k-major rows per thread");
+// Thread-block cluster helpers: rank of this block, the cluster-wide barrier (a hardware barrier,
+// not a spin on memory) and 128-bit / 32-bit reads of another block's shared memory.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 cluster_load4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float cluster_load1(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+
+// Warp roles of the pipelined kernel: 8 staging warps, 8 accumulating warps, 1 issuing warp.
+constexpr int kStageWarps = 8, kAccWarps = 8;
+constexpr int kStageThreads = 32 * kStageWarps;
+constexpr int kPipeThreads = 32 * (kStageWarps + kAccWarps + 1);
+constexpr int kRawSlots = 4;   // raw slices in flight per block
+constexpr int kTmemSlots = 4;  // accumulator tiles: slices whose products may be pending or unread
+
+template <int BN>
+constexpr size_t smem_bytes_async() {
+    return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128) + (size_t)kRawSlots * (kBM * 128 + BN * 128);
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Barrier among the staging warps only (hardware barrier 1; barrier 0 is __syncthreads).
+__device__ __forceinline__ void stage_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStageThreads) : "memory"); }
+
+// The three groups of warps run their own loops over the k slices and meet only at mbarriers:
+//
+//   staging warps (0-7)   queue the 16-byte copies of slice j + 3 into the raw ring, wait for their
+//                         own copies of slice j, meet at their barrier (a thread splits what others
+//                         copied), wait until the MMAs that read stage j % 2 have completed
+//                         (`empty`), split / transpose slice j into that stage and arrive at `full`.
+//   issuing warp (16)     waits for `full` and for the accumulator tile j % 4 to have been read
+//                         (`acc_free`), issues the slice's tcgen05.mma instructions into it and
+//                         commits them to `empty` (the stage may be overwritten) and `acc_ready`.
+//   accumulating warps    wait for `acc_ready`, read their 32 lanes x 32 columns of the tile from
+//   (8-15)                TMEM, arrive at `acc_free` and add the values to registers.
+//
+// So the copies, the split pass, the tensor core and the TMEM reads of neighbouring slices
+// overlap, and no thread waits for a phase it has no part in.
+template <int BN, bool A_EXACT, bool ROWSUM>
+__global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_constant__ GemmPair gp) {
+    static_assert(BN == 64, "an accumulating warp reads 32 of the tile's 64 columns");
+    constexpr int CPT = 32;  // accumulator columns per accumulating thread
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[kStages];
+    __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_acc_ready[kTmemSlots], bar_acc_free[kTmemSlots];
     __shared__ uint32_t tmem_slot;
     __shared__ float s_rowsum[kBM];
-    __shared__ float s_part[CG][kBM];
+    __shared__ float s_part[kStageThreads / kBM][kBM];
 
     const int which = (int)blockIdx.x >= gp.tiles_m0 ? 1 : 0;
     const GemmArgs& g = gp.p[which];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quarter = warp & 3, group = warp >> 2;
     const int m0 = ((int)blockIdx.x - (which ? gp.tiles_m0 : 0)) * kBM, n0 = blockIdx.y * BN;
-    if (n0 >= g.N || m0 >= g.M) return;  // the two problems may differ in size
+    if (n0 >= g.N || m0 >= g.M) return;  // the two problems may differ in size (a whole cluster leaves together)
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128, kStage = 2 * kATile + 2 * kBTile, kRaw = kATile + kBTile;
@@ -595,120 +679,162 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
     const int n_slices = max(0, (k_end - k_begin + kBK - 1) / kBK);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bar_full[s], kStageWarps);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int t = 0; t < kTmemSlots; ++t) {
+            mbar_init(&bar_acc_ready[t], 1);
+            mbar_init(&bar_acc_free[t], kAccWarps);
+        }
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(&tmem_slot, kStages * BN);
+    if (warp == 0) tmem_alloc(&tmem_slot, kTmemSlots * BN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     grid_dependency_sync();
     const uint32_t tmem_base = tmem_slot;
-    constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
 
-    float rowsum[2] = {0.f, 0.f};
+    float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
     float acc[CPT];
 #pragma unroll
     for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 
-    auto issue = [&](int slice) {
-        if (slice < n_slices && !(g.debug_skip & 1)) {
-            uint8_t* raw = raw_ring + (size_t)(slice % kRawStages) * kRaw;
-            const int k0 = k_begin + slice * kBK;
-            issue_raw<kBM, NT>(g.A, m0, g.M, k0, k_end, raw);
-            issue_raw<BN, NT>(g.B, n0, g.N, k0, k_end, raw + kATile);
-        }
-        cp_async_commit();  // one group per slice, empty past the end, so the counting stays uniform
-    };
-    auto drain = [&](int slice) {
-        const int b = slice % kStages;
-        mbar_wait(&bars[b], (uint32_t)((slice / kStages) & 1), g.status, 1u);
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + group * CPT);
-        if (CPT == 32) {
-            uint32_t r[32];
-            tmem_ld32(taddr, r);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j % CPT] += __uint_as_float(r[j]);
-        } else {
-            uint32_t r[16];
-            tmem_ld16(taddr, r);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
-        }
-        tc_fence_before();
-    };
-
-#pragma unroll
-    for (int s = 0; s < kRawStages - 1; ++s) issue(s);
-    for (int kc = 0; kc < n_slices; ++kc) {
-        issue(kc + kRawStages - 1);
-        cp_async_wait<kRawStages - 1>();  // this thread's copies of slice kc have landed
-        __syncthreads();                  // ... and everybody else's
-        const int s = kc % kStages;
-        uint8_t* stage = smem + (size_t)s * kStage;
-        uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
-        const uint8_t* raw = raw_ring + (size_t)(kc % kRawStages) * kRaw;
-        float unused[2];
-        if (!(g.debug_skip & 2)) {
-            split_raw<kBM, NT, !A_EXACT, ROWSUM>(g.A, raw, a_hi, a_lo, rowsum);
-            split_raw<BN, NT, true, false>(g.B, raw + kATile, b_hi, b_lo, unused);
-        }
-        fence_async_shared();
-        __syncthreads();
-        if (tid == 0 && !(g.debug_skip & 4)) {
-            tc_fence_after();
-            const uint32_t tmem_acc = tmem_base + (uint32_t)(s * BN);
-            const uint64_t da_hi = make_kmajor_sw128_desc(smem_u32(a_hi)), da_lo = make_kmajor_sw128_desc(smem_u32(a_lo));
-            const uint64_t db_hi = make_kmajor_sw128_desc(smem_u32(b_hi)), db_lo = make_kmajor_sw128_desc(smem_u32(b_lo));
-#pragma unroll
-            for (int ks = 0; ks < kBK / 8; ++ks) {
-                const uint64_t adv = (uint64_t)(ks * 32 >> 4);
-                umma_tf32(tmem_acc, da_hi + adv, db_lo + adv, idesc, ks > 0 ? 1u : 0u);
-                if (!A_EXACT) umma_tf32(tmem_acc, da_lo + adv, db_hi + adv, idesc, 1u);
-                umma_tf32(tmem_acc, da_hi + adv, db_hi + adv, idesc, 1u);
+    if (warp < kStageWarps) {
+        auto issue = [&](int slice) {
+            if (slice < n_slices) {
+                uint8_t* raw = raw_ring + (size_t)(slice % kRawSlots) * kRaw;
+                const int k0 = k_begin + slice * kBK;
+                issue_raw<kBM, kStageThreads>(g.A, m0, g.M, k0, k_end, raw);
+                issue_raw<BN, kStageThreads>(g.B, n0, g.N, k0, k_end, raw + kATile);
             }
-            umma_commit(&bars[s]);
+            cp_async_commit();  // one group per slice, empty past the end, so the counting stays uniform
+        };
+#pragma unroll
+        for (int s = 0; s < kRawSlots - 1; ++s) issue(s);
+        for (int kc = 0; kc < n_slices; ++kc) {
+            cp_async_wait<kRawSlots - 2>();  // this thread's copies of slice kc have landed
+            stage_warps_sync();              // ... and every staging thread's; slice kc-1 has been split by all
+            issue(kc + kRawSlots - 1);       // into the slot of slice kc-1
+            const int s = kc % kStages;
+            if (kc >= kStages) mbar_wait(&bar_empty[s], (uint32_t)(((kc / kStages) - 1) & 1), g.status, 2u);
+            uint8_t* stage = smem + (size_t)s * kStage;
+            uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
+            const uint8_t* raw = raw_ring + (size_t)(kc % kRawSlots) * kRaw;
+            float unused[4];
+            split_raw<kBM, kStageThreads, !A_EXACT, ROWSUM>(g.A, raw, a_hi, a_lo, rowsum);
+            split_raw<BN, kStageThreads, true, false>(g.B, raw + kATile, b_hi, b_lo, unused);
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_full[s]);
         }
-        if (kc >= 1 && !(g.debug_skip & 12)) drain(kc - 1);
+        cp_async_wait<0>();
+    } else if (warp == kStageWarps + kAccWarps) {
+        constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
+        for (int kc = 0; kc < n_slices; ++kc) {
+            const int s = kc % kStages, t = kc % kTmemSlots;
+            mbar_wait(&bar_full[s], (uint32_t)((kc / kStages) & 1), g.status, 3u);
+            if (kc >= kTmemSlots) mbar_wait(&bar_acc_free[t], (uint32_t)(((kc / kTmemSlots) - 1) & 1), g.status, 4u);
+            tc_fence_after();
+            if (lane == 0) {
+                uint8_t* stage = smem + (size_t)s * kStage;
+                uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(t * BN);
+                const uint64_t da_hi = make_kmajor_sw128_desc(smem_u32(a_hi)), da_lo = make_kmajor_sw128_desc(smem_u32(a_lo));
+                const uint64_t db_hi = make_kmajor_sw128_desc(smem_u32(b_hi)), db_lo = make_kmajor_sw128_desc(smem_u32(b_lo));
+#pragma unroll
+                for (int ks = 0; ks < kBK / 8; ++ks) {
+                    const uint64_t adv = (uint64_t)(ks * 32 >> 4);
+                    umma_tf32(tmem_acc, da_hi + adv, db_lo + adv, idesc, ks > 0 ? 1u : 0u);
+                    if (!A_EXACT) umma_tf32(tmem_acc, da_lo + adv, db_hi + adv, idesc, 1u);
+                    umma_tf32(tmem_acc, da_hi + adv, db_hi + adv, idesc, 1u);
+                }
+                umma_commit(&bar_empty[s]);
+                umma_commit(&bar_acc_ready[t]);
+            }
+            __syncwarp();
+        }
+    } else {
+        // The tensor core truncates its fp32 accumulator once per instruction, so every slice is
+        // accumulated on its own in TMEM and the slices are added here with round-to-nearest.
+        const int quarter = warp & 3, half = (warp - kStageWarps) >> 2;
+        for (int kc = 0; kc < n_slices; ++kc) {
+            const int t = kc % kTmemSlots;
+            mbar_wait(&bar_acc_ready[t], (uint32_t)((kc / kTmemSlots) & 1), g.status, 1u);
+            tc_fence_after();
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * BN + half * CPT), r);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_acc_free[t]);
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) acc[j] += __uint_as_float(r[j]);
+        }
     }
-    cp_async_wait<0>();
-    if (n_slices > 0 && !(g.debug_skip & 12)) drain(n_slices - 1);
 
-    if (ROWSUM) {
-        // fixed-order combination of the partial row sums
+    if (ROWSUM && warp < kStageWarps) {
+        // fixed-order combination of the partial row sums of the staging threads
         if (!g.A.transposed) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < 4; ++i) {
                 float v = rowsum[i];
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
-                const int row = (tid >> 3) + i * (NT / 8);
-                if ((tid & 7) == 0 && row < kBM) s_rowsum[row] = v;
+                if ((tid & 7) == 0) s_rowsum[(tid >> 3) + i * (kStageThreads / 8)] = v;
             }
-            __syncthreads();
         } else {
             s_part[tid / kBM][tid % kBM] = rowsum[0];
-            __syncthreads();
-            if (tid < kBM) {
-                float v = 0.f;
-#pragma unroll
-                for (int c = 0; c < CG; ++c) v += s_part[c][tid];
-                s_rowsum[tid] = v;
-            }
-            __syncthreads();
         }
     }
+    __syncthreads();  // every slice has been read from TMEM: the operand stages are free
+    if (ROWSUM && g.A.transposed) {
+        if (tid < kBM) {
+            float v = 0.f;
+#pragma unroll
+            for (int c = 0; c < kStageThreads / kBM; ++c) v += s_part[c][tid];
+            s_rowsum[tid] = v;
+        }
+        __syncthreads();
+    }
 
-    const int row = quarter * 32 + lane, m = m0 + row;
-    const int nc0 = n0 + group * CPT;  // first output column of this thread
-    const bool mine = m < g.M && nc0 < g.N;
-    bool finish = true;
-    const float rs = ROWSUM ? s_rowsum[row] : 0.f;
-    if (g.ws) {
-        // split run: leave the raw partial tile (and partial row sums) for k_tc_reduce
-        if (mine) {
+    const bool acc_warp = warp >= kStageWarps && warp < kStageWarps + kAccWarps;
+    const int row = (warp & 3) * 32 + lane, m = m0 + row;
+    const int nc0 = n0 + ((warp - kStageWarps) >> 2) * CPT;  // first output column of an accumulating thread
+    if (g.cluster_splits > 1) {
+        // The splits of this tile are the blocks of one cluster.  Each leaves its partial tile in its
+        // own shared memory; after the cluster barrier block z adds rows z * rows_each ... of all
+        // partial tiles, in split order, and finishes them.
+        constexpr int kRedStride = BN + 4;  // floats; keeps the 128-bit writes below free of bank conflicts
+        static_assert((size_t)kBM * kRedStride * 4 <= (size_t)kStages * kStage, "the partial tile fits the operand stages");
+        float* red = reinterpret_cast<float*>(smem);
+        if (acc_warp) {
+#pragma unroll
+            for (int j = 0; j < CPT; j += 4)
+                *reinterpret_cast<float4*>(red + row * kRedStride + (nc0 - n0) + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        }
+        cluster_sync();
+        const int n_split = g.cluster_splits, rank = (int)cluster_rank();
+        const int rows_each = (kBM + n_split - 1) / n_split;
+        const int r_begin = rank * rows_each, r_end = min(kBM, r_begin + rows_each);
+        constexpr int kQuads = BN / 4;
+        const uint32_t red_addr = smem_u32(red), rowsum_addr = smem_u32(s_rowsum);
+        for (int u = tid; u < (r_end - r_begin) * kQuads; u += kPipeThreads) {
+            const int r = r_begin + u / kQuads, c = (u % kQuads) * 4;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            float row_total = 0.f;
+            for (int z = 0; z < n_split; ++z) {
+                const float4 v = cluster_load4(cluster_map(red_addr + (uint32_t)(r * kRedStride + c) * 4u, (uint32_t)z));
+                sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+                if (ROWSUM) row_total += cluster_load1(cluster_map(rowsum_addr + (uint32_t)r * 4u, (uint32_t)z));
+            }
+            if (m0 + r < g.M && n0 + c < g.N) finish_four(g, g.out, m0 + r, n0 + c, sum, row_total);
+        }
+        cluster_sync();  // nobody leaves while its shared memory may still be read
+    } else if (acc_warp && m < g.M && nc0 < g.N) {
+        if (g.ws) {
+            // split run without a cluster: leave the raw partial tile (and row sums) for k_tc_reduce
             float* w = g.ws + ((size_t)blockIdx.z * g.M + m) * g.N + nc0;
             if ((g.N & 3) == 0 && nc0 + CPT <= g.N) {
 #pragma unroll
@@ -718,50 +844,21 @@ __global__ void __launch_bounds__(128 * CG, 1) k_tc_gemm_async(const __grid_cons
                 for (int j = 0; j < CPT; ++j)
                     if (nc0 + j < g.N) w[j] = acc[j];
             }
-        }
-        if (ROWSUM && blockIdx.y == 0 && tid < kBM && m0 + tid < g.M) g.ws_rowsum[(size_t)blockIdx.z * g.M + m0 + tid] = s_rowsum[tid];
-        finish = false;
-    }
-    if (finish && mine) {
-        float* out_row;
-        if (g.out_blocks) {
-            const int blk = m / g.block_rows;
-            out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+            if (ROWSUM && blockIdx.y == 0 && nc0 == n0) g.ws_rowsum[(size_t)blockIdx.z * g.M + m] = s_rowsum[row];
         } else {
-            out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
-        }
-        const uint8_t* x_row = nullptr;
-        if (g.epilogue != EPI_STORE) {
-            const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
-            x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
-        }
-        const bool vec_store = ((g.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_row) & 15) == 0);
+            // each split finishes its own output slice
+            float* out_base = g.out_blocks ? nullptr : g.out + (size_t)blockIdx.z * g.split_stride;
+            const float rs = ROWSUM ? s_rowsum[row] : 0.f;
 #pragma unroll
-        for (int j = 0; j < CPT; ++j) {
-            const int n = nc0 + j;
-            if (n < g.N) {
-                if (g.epilogue == EPI_ADD_TABLE_VALUE) {
-                    const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n])
-                                                : reinterpret_cast<const float*>(x_row)[n];
-                    acc[j] = x + acc[j];
-                } else if (g.epilogue == EPI_ROWSUM_X_MINUS) {
-                    acc[j] = rs * reinterpret_cast<const float*>(x_row)[n] - acc[j];
-                }
+            for (int j = 0; j < CPT; j += 4) {
+                float four[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
+                if (nc0 + j < g.N) finish_four(g, out_base, m, nc0 + j, four, rs);
             }
-        }
-        if (vec_store && nc0 + CPT <= g.N) {
-#pragma unroll
-            for (int j = 0; j < CPT; j += 4)
-                *reinterpret_cast<float4*>(out_row + nc0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < CPT; ++j)
-                if (nc0 + j < g.N) out_row[nc0 + j] = acc[j];
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_base, kStages * BN);
+    if (warp == 0) tmem_dealloc(tmem_base, kTmemSlots * BN);
 }
 
 // Adds the partial tiles of a k split in split order and applies the epilogue of the contraction:
@@ -788,38 +885,10 @@ static __global__ void __launch_bounds__(256) k_tc_reduce(const __grid_constant_
                 if (n + j < g.N) acc[j] += w[j];
         }
     }
-    if (g.epilogue != EPI_STORE) {
-        const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
-        const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
-        float rs = 0.f;
-        if (g.epilogue == EPI_ROWSUM_X_MINUS)
-            for (int z = 0; z < g.splits; ++z) rs += g.ws_rowsum[(size_t)z * g.M + m];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (n + j >= g.N) continue;
-            if (g.epilogue == EPI_ADD_TABLE_VALUE) {
-                const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j])
-                                            : reinterpret_cast<const float*>(x_row)[n + j];
-                acc[j] = x + acc[j];
-            } else {
-                acc[j] = rs * reinterpret_cast<const float*>(x_row)[n + j] - acc[j];
-            }
-        }
-    }
-    float* out_row;
-    if (g.out_blocks) {
-        const int blk = m / g.block_rows;
-        out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
-    } else {
-        out_row = g.out + (size_t)m * g.ldc;
-    }
-    if (vec && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(out_row) & 15) == 0) {
-        *reinterpret_cast<float4*>(out_row + n) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (n + j < g.N) out_row[n + j] = acc[j];
-    }
+    float rs = 0.f;
+    if (g.epilogue == EPI_ROWSUM_X_MINUS)
+        for (int z = 0; z < g.splits; ++z) rs += g.ws_rowsum[(size_t)z * g.M + m];
+    finish_four(g, g.out, m, n, acc, rs);
 }
 
 // Host side: grid = (ceil(M / 128), ceil(N / BN), splits).
@@ -841,8 +910,42 @@ inline bool rows_16_byte_aligned(const Operand& op) {
 }
 
 // One or two problems in one launch, pipelined when every operand allows 16-byte copies.
+constexpr int kMaxClusterSplits = 8;  // the portable cluster size
+
+// How many clusters of `splits` blocks of the pipelined kernel the device can hold at once
+// (a cluster needs its blocks on SMs of one GPC, one block per SM).  0 when the query fails.
+inline int max_resident_clusters(int splits) {
+    static int cached[kMaxClusterSplits + 1] = {0};
+    static bool known[kMaxClusterSplits + 1] = {false};
+    if (splits < 1 || splits > kMaxClusterSplits) return 0;
+    if (known[splits]) return cached[splits];
+    auto kernel = k_tc_gemm_async<64, false, false>;
+    int n = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_async<64>()) == cudaSuccess) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(1, 1, splits);
+        config.blockDim = dim3(kPipeThreads);
+        config.dynamicSmemBytes = smem_bytes_async<64>();
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 1;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = (unsigned)splits;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &config) != cudaSuccess) {
+            n = 0;
+            (void)cudaGetLastError();
+        }
+    }
+    known[splits] = true;
+    cached[splits] = n;
+    return n;
+}
+
 template <int BN, bool A_EXACT, bool ROWSUM>
-inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int splits, cudaStream_t stream) {
+inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int splits, cudaStream_t stream, int* n_launches = nullptr) {
+    if (n_launches) *n_launches = n_problems;
     bool fast = true;
     for (int i = 0; i < n_problems; ++i) fast = fast && rows_16_byte_aligned(problems[i].A) && rows_16_byte_aligned(problems[i].B);
     if (!fast) {
@@ -859,8 +962,7 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         return cudaSuccess;
     }
     static bool configured = false;
-    constexpr int CG = 4;  // 16 warps
-    auto kernel = k_tc_gemm_async<BN, CG, A_EXACT, ROWSUM>;
+    auto kernel = k_tc_gemm_async<BN, A_EXACT, ROWSUM>;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_async<BN>());
         if (err != cudaSuccess) return err;
@@ -876,8 +978,16 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         tiles_n = tiles_n > (problems[1].N + BN - 1) / BN ? tiles_n : (problems[1].N + BN - 1) / BN;
     }
     dim3 grid(tiles_m, tiles_n, splits);
-    cudaError_t err = launch_dependent(kernel, grid, dim3(128 * CG), smem_bytes_async<BN>(), stream, gp);
+    if (n_launches) *n_launches = 1;
+    if (problems[0].ws && splits >= 2 && splits <= kMaxClusterSplits) {
+        // the splits of a tile as one cluster: no workspace, no second kernel
+        gp.p[0].ws = gp.p[1].ws = nullptr;
+        gp.p[0].cluster_splits = gp.p[1].cluster_splits = splits;
+        return launch_dependent_cluster(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, (unsigned)splits, gp);
+    }
+    cudaError_t err = launch_dependent(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, gp);
     if (err != cudaSuccess || !problems[0].ws) return err;
+    if (n_launches) *n_launches = 2;
     gp.p[0].splits = gp.p[1].splits = splits;
     long long units = 0;
     for (int i = 0; i < n_problems; ++i) {
