@@ -399,6 +399,11 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
             g.ws = dws.as<float>();
             g.ws_rowsum = dwr.as<float>();
         }
+#ifdef KGE_TC_TRACE
+        DeviceBuffer dtrace(64 * 8 * 8);
+        cudaMemset(dtrace.p, 0, 64 * 8 * 8);
+        g.trace = dtrace.as<long long>();
+#endif
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         for (int it = 0; it <= repeat && err == cudaSuccess; ++it) {
             if (it == 1) {
@@ -426,6 +431,18 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         }
         KGE_CUDA(err);
         finish_kernels();
+#ifdef KGE_TC_TRACE
+        {
+            long long h[64 * 8];
+            cudaMemcpy(h, dtrace.p, sizeof(h), cudaMemcpyDeviceToHost);
+            long long t0 = h[0];
+            for (int kc = 0; kc < 24 && kc * 32 < (int)k / splits + 31; ++kc) {
+                std::fprintf(stderr, "slice %2d:", kc);
+                for (int j = 0; j < 8; ++j) std::fprintf(stderr, " %7lld", h[kc * 8 + j] - t0);
+                std::fprintf(stderr, "\n");
+            }
+        }
+#endif
         unsigned status = 0;
         KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
         if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_gemm: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");

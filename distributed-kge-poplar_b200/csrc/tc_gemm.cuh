@@ -25,6 +25,7 @@
 // to its clean-up (TMEM is always released).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -84,6 +85,7 @@ struct GemmArgs {
     // Set by launch_pair: the blocks of one output tile (one per split) form a thread-block cluster
     // and reduce their partial tiles through distributed shared memory; 0 = not a cluster launch.
     int cluster_splits;
+    long long* trace;
 };
 
 // ---------------------------------------------------------------------------
@@ -624,10 +626,15 @@ __device__ __forceinline__ float cluster_load1(uint32_t addr) {
     return v;
 }
 
-// Warp roles of the pipelined kernel: 8 staging warps, 8 accumulating warps, 1 issuing warp.
+#ifdef KGE_TC_TRACE
+#define TRACE(slot) do { if (trace_on && kc < 64) g.trace[kc * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
+// Warp roles of the pipelined kernel: 8 staging warps, 8 accumulating warps, 1 issuing warp, 1 copying warp.
 constexpr int kStageWarps = 8, kAccWarps = 8;
 constexpr int kStageThreads = 32 * kStageWarps;
-constexpr int kPipeThreads = 32 * (kStageWarps + kAccWarps + 1);
+constexpr int kPipeThreads = 32 * (kStageWarps + kAccWarps + 2);
 constexpr int kRawSlots = 4;   // raw slices in flight per block
 constexpr int kTmemSlots = 4;  // accumulator tiles: slices whose products may be pending or unread
 
@@ -636,18 +643,34 @@ constexpr size_t smem_bytes_async() {
     return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128) + (size_t)kRawSlots * (kBM * 128 + BN * 128);
 }
 
+// Tensor maps of the operands of the (up to) two problems of a launch: the copying warp moves a
+// whole [rows x 32 k] (or [32 k x rows]) box per instruction with the TMA unit, which generates the
+// addresses, fills what lies outside the matrix with zeros and reports the bytes to an mbarrier.
+struct GemmMaps {
+    CUtensorMap a[2], b[2];
+};
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Barrier among the staging warps only (hardware barrier 1; barrier 0 is __syncthreads).
-__device__ __forceinline__ void stage_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStageThreads) : "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One box of a 2-d tensor map into this block's shared memory; x is the coordinate along the
+// contiguous dimension and x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint8_t* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
 
-// The three groups of warps run their own loops over the k slices and meet only at mbarriers:
+// The groups of warps run their own loops over the k slices and meet only at mbarriers:
 //
-//   staging warps (0-7)   queue the 16-byte copies of slice j + 3 into the raw ring, wait for their
-//                         own copies of slice j, meet at their barrier (a thread splits what others
-//                         copied), wait until the MMAs that read stage j % 2 have completed
-//                         (`empty`), split / transpose slice j into that stage and arrive at `full`.
+//   copying warp (17)     one thread waits until raw slot j % 4 has been read (`raw_empty`) and
+//                         starts the two TMA copies of slice j into it; their bytes complete `raw_full`.
+//   staging warps (0-7)   wait for `raw_full`, wait until the MMAs that read stage j % 2 have
+//                         completed (`empty`), split / transpose slice j into that stage and
+//                         arrive at `full` and `raw_empty`.
 //   issuing warp (16)     waits for `full` and for the accumulator tile j % 4 to have been read
 //                         (`acc_free`), issues the slice's tcgen05.mma instructions into it and
 //                         commits them to `empty` (the stage may be overwritten) and `acc_ready`.
@@ -657,11 +680,13 @@ __device__ __forceinline__ void stage_warps_sync() { asm volatile("bar.sync 1, %
 // So the copies, the split pass, the tensor core and the TMEM reads of neighbouring slices
 // overlap, and no thread waits for a phase it has no part in.
 template <int BN, bool A_EXACT, bool ROWSUM>
-__global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_constant__ GemmPair gp) {
+__global__ void __launch_bounds__(kPipeThreads, 1)
+k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ GemmMaps maps) {
     static_assert(BN == 64, "an accumulating warp reads 32 of the tile's 64 columns");
     constexpr int CPT = 32;  // accumulator columns per accumulating thread
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_acc_ready[kTmemSlots], bar_acc_free[kTmemSlots];
+    __shared__ uint64_t bar_raw_full[kRawSlots], bar_raw_empty[kRawSlots];
     __shared__ uint32_t tmem_slot;
     __shared__ float s_rowsum[kBM];
     __shared__ float s_part[kStageThreads / kBM][kBM];
@@ -687,6 +712,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_
             mbar_init(&bar_acc_ready[t], 1);
             mbar_init(&bar_acc_free[t], kAccWarps);
         }
+        for (int r = 0; r < kRawSlots; ++r) {
+            mbar_init(&bar_raw_full[r], 1);
+            mbar_init(&bar_raw_empty[r], kStageWarps);
+        }
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(&tmem_slot, kTmemSlots * BN);
@@ -696,47 +725,62 @@ __global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_
     grid_dependency_sync();
     const uint32_t tmem_base = tmem_slot;
 
+#ifdef KGE_TC_TRACE
+    const bool trace_on = g.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 256 || tid == 512);
+#endif
     float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
     float acc[CPT];
 #pragma unroll
     for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 
     if (warp < kStageWarps) {
-        auto issue = [&](int slice) {
-            if (slice < n_slices) {
-                uint8_t* raw = raw_ring + (size_t)(slice % kRawSlots) * kRaw;
-                const int k0 = k_begin + slice * kBK;
-                issue_raw<kBM, kStageThreads>(g.A, m0, g.M, k0, k_end, raw);
-                issue_raw<BN, kStageThreads>(g.B, n0, g.N, k0, k_end, raw + kATile);
-            }
-            cp_async_commit();  // one group per slice, empty past the end, so the counting stays uniform
-        };
-#pragma unroll
-        for (int s = 0; s < kRawSlots - 1; ++s) issue(s);
         for (int kc = 0; kc < n_slices; ++kc) {
-            cp_async_wait<kRawSlots - 2>();  // this thread's copies of slice kc have landed
-            stage_warps_sync();              // ... and every staging thread's; slice kc-1 has been split by all
-            issue(kc + kRawSlots - 1);       // into the slot of slice kc-1
-            const int s = kc % kStages;
+            const int s = kc % kStages, slot = kc % kRawSlots;
+            mbar_wait(&bar_raw_full[slot], (uint32_t)((kc / kRawSlots) & 1), g.status, 5u);
+            TRACE(0);
             if (kc >= kStages) mbar_wait(&bar_empty[s], (uint32_t)(((kc / kStages) - 1) & 1), g.status, 2u);
+            TRACE(1);
             uint8_t* stage = smem + (size_t)s * kStage;
             uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
-            const uint8_t* raw = raw_ring + (size_t)(kc % kRawSlots) * kRaw;
+            const uint8_t* raw = raw_ring + (size_t)slot * kRaw;
             float unused[4];
             split_raw<kBM, kStageThreads, !A_EXACT, ROWSUM>(g.A, raw, a_hi, a_lo, rowsum);
             split_raw<BN, kStageThreads, true, false>(g.B, raw + kATile, b_hi, b_lo, unused);
             fence_async_shared();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_full[s]);
+            if (lane == 0) {
+                mbar_arrive(&bar_full[s]);
+                mbar_arrive(&bar_raw_empty[slot]);
+            }
+            TRACE(2);
         }
-        cp_async_wait<0>();
+    } else if (warp == kStageWarps + kAccWarps + 1) {
+        const CUtensorMap* map_a = &maps.a[which];
+        const CUtensorMap* map_b = &maps.b[which];
+        const uint32_t bytes = (uint32_t)(kBM * kBK * (g.A.is_half ? 2 : 4) + BN * kBK * (g.B.is_half ? 2 : 4));
+        for (int kc = 0; kc < n_slices; ++kc) {
+            const int slot = kc % kRawSlots;
+            if (kc >= kRawSlots) mbar_wait(&bar_raw_empty[slot], (uint32_t)(((kc / kRawSlots) - 1) & 1), g.status, 6u);
+            if (lane == 0) {
+                uint8_t* raw = raw_ring + (size_t)slot * kRaw;
+                const int k0 = k_begin + kc * kBK;
+                mbar_arrive_expect(&bar_raw_full[slot], bytes);
+                if (g.A.transposed) tma_load_2d(raw, map_a, m0, k0, &bar_raw_full[slot]);
+                else tma_load_2d(raw, map_a, k0, m0, &bar_raw_full[slot]);
+                if (g.B.transposed) tma_load_2d(raw + kATile, map_b, n0, k0, &bar_raw_full[slot]);
+                else tma_load_2d(raw + kATile, map_b, k0, n0, &bar_raw_full[slot]);
+            }
+            __syncwarp();
+        }
     } else if (warp == kStageWarps + kAccWarps) {
         constexpr uint32_t idesc = make_idesc_tf32(kBM, BN);
         for (int kc = 0; kc < n_slices; ++kc) {
             const int s = kc % kStages, t = kc % kTmemSlots;
             mbar_wait(&bar_full[s], (uint32_t)((kc / kStages) & 1), g.status, 3u);
+            TRACE(3);
             if (kc >= kTmemSlots) mbar_wait(&bar_acc_free[t], (uint32_t)(((kc / kTmemSlots) - 1) & 1), g.status, 4u);
             tc_fence_after();
+            TRACE(4);
             if (lane == 0) {
                 uint8_t* stage = smem + (size_t)s * kStage;
                 uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
@@ -754,6 +798,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_
                 umma_commit(&bar_acc_ready[t]);
             }
             __syncwarp();
+            TRACE(5);
         }
     } else {
         // The tensor core truncates its fp32 accumulator once per instruction, so every slice is
@@ -762,6 +807,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_
         for (int kc = 0; kc < n_slices; ++kc) {
             const int t = kc % kTmemSlots;
             mbar_wait(&bar_acc_ready[t], (uint32_t)((kc / kTmemSlots) & 1), g.status, 1u);
+            TRACE(6);
             tc_fence_after();
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * BN + half * CPT), r);
@@ -770,6 +816,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) k_tc_gemm_async(const __grid_
             if (lane == 0) mbar_arrive(&bar_acc_free[t]);
 #pragma unroll
             for (int j = 0; j < CPT; ++j) acc[j] += __uint_as_float(r[j]);
+            TRACE(7);
         }
     }
 
@@ -912,6 +959,37 @@ inline bool rows_16_byte_aligned(const Operand& op) {
 // One or two problems in one launch, pipelined when every operand allows 16-byte copies.
 constexpr int kMaxClusterSplits = 8;  // the portable cluster size
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// The map of one operand: `mn` rows (or columns, for an mn-major operand) by `k`, boxes of
+// [rows x 32 k] (k-major) or [32 k x rows] (mn-major), dense in shared memory, zeros outside.
+inline cudaError_t make_operand_map(const Operand& op, int mn, int k, int rows, CUtensorMap* map) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)(op.transposed ? mn : k), (cuuint64_t)(op.transposed ? k : mn)};
+    const cuuint64_t strides[1] = {(cuuint64_t)op.row_stride_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(op.transposed ? rows : kBK), (cuuint32_t)(op.transposed ? kBK : rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, op.is_half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                              const_cast<uint8_t*>(op.base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 // How many clusters of `splits` blocks of the pipelined kernel the device can hold at once
 // (a cluster needs its blocks on SMs of one GPC, one block per SM).  0 when the query fails.
 inline int max_resident_clusters(int splits) {
@@ -947,7 +1025,8 @@ template <int BN, bool A_EXACT, bool ROWSUM>
 inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int splits, cudaStream_t stream, int* n_launches = nullptr) {
     if (n_launches) *n_launches = n_problems;
     bool fast = true;
-    for (int i = 0; i < n_problems; ++i) fast = fast && rows_16_byte_aligned(problems[i].A) && rows_16_byte_aligned(problems[i].B);
+    for (int i = 0; i < n_problems; ++i)
+        fast = fast && rows_16_byte_aligned(problems[i].A) && rows_16_byte_aligned(problems[i].B) && !problems[i].A.gather && !problems[i].B.gather;
     if (!fast) {
         // the unpipelined kernel has no in-kernel split reduction: run each problem unsplit
         for (int i = 0; i < n_problems; ++i) {
@@ -977,15 +1056,22 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         tiles_m += (problems[1].M + kBM - 1) / kBM;
         tiles_n = tiles_n > (problems[1].N + BN - 1) / BN ? tiles_n : (problems[1].N + BN - 1) / BN;
     }
+    GemmMaps maps;
+    for (int i = 0; i < 2; ++i) {
+        const GemmArgs& q = gp.p[i];
+        cudaError_t e = make_operand_map(q.A, q.M, q.K, kBM, &maps.a[i]);
+        if (e == cudaSuccess) e = make_operand_map(q.B, q.N, q.K, BN, &maps.b[i]);
+        if (e != cudaSuccess) return e;
+    }
     dim3 grid(tiles_m, tiles_n, splits);
     if (n_launches) *n_launches = 1;
     if (problems[0].ws && splits >= 2 && splits <= kMaxClusterSplits) {
         // the splits of a tile as one cluster: no workspace, no second kernel
         gp.p[0].ws = gp.p[1].ws = nullptr;
         gp.p[0].cluster_splits = gp.p[1].cluster_splits = splits;
-        return launch_dependent_cluster(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, (unsigned)splits, gp);
+        return launch_dependent_cluster(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, (unsigned)splits, gp, maps);
     }
-    cudaError_t err = launch_dependent(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, gp);
+    cudaError_t err = launch_dependent(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, gp, maps);
     if (err != cudaSuccess || !problems[0].ws) return err;
     if (n_launches) *n_launches = 2;
     gp.p[0].splits = gp.p[1].splits = splits;
