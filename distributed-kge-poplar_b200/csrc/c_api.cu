@@ -336,10 +336,10 @@ int kge_op_all_to_all(const float* in, size_t n_shard, size_t block, float* out)
             const float* rows = din.as<float>() + s * n_shard * block;
             if (block % 4 == 0)
                 k_route<4><<<(unsigned)n_shard, 64>>>(rows, rows, didx.as<uint32_t>(), nullptr, nullptr, nullptr,
-                                                      dtable.as<float*>(), nullptr, (int)n_shard, 1, 0, (int)block, SCORE_TRANSE);
+                                                      dtable.as<float*>(), nullptr, (int)n_shard, 1, 0, (int)block, SCORE_TRANSE, ExchangeSync{});
             else
                 k_route<1><<<(unsigned)n_shard, 64>>>(rows, rows, didx.as<uint32_t>(), nullptr, nullptr, nullptr,
-                                                      dtable.as<float*>(), nullptr, (int)n_shard, 1, 0, (int)block, SCORE_TRANSE);
+                                                      dtable.as<float*>(), nullptr, (int)n_shard, 1, 0, (int)block, SCORE_TRANSE, ExchangeSync{});
             finish_kernels();
         }
         to_host(out, dout, total * 4);
@@ -399,11 +399,6 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
             g.ws = dws.as<float>();
             g.ws_rowsum = dwr.as<float>();
         }
-#ifdef KGE_TC_TRACE
-        DeviceBuffer dtrace(64 * 8 * 8);
-        cudaMemset(dtrace.p, 0, 64 * 8 * 8);
-        g.trace = dtrace.as<long long>();
-#endif
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         for (int it = 0; it <= repeat && err == cudaSuccess; ++it) {
             if (it == 1) {
@@ -431,18 +426,6 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         }
         KGE_CUDA(err);
         finish_kernels();
-#ifdef KGE_TC_TRACE
-        {
-            long long h[64 * 8];
-            cudaMemcpy(h, dtrace.p, sizeof(h), cudaMemcpyDeviceToHost);
-            long long t0 = h[0];
-            for (int kc = 0; kc < 24 && kc * 32 < (int)k / splits + 31; ++kc) {
-                std::fprintf(stderr, "slice %2d:", kc);
-                for (int j = 0; j < 8; ++j) std::fprintf(stderr, " %7lld", h[kc * 8 + j] - t0);
-                std::fprintf(stderr, "\n");
-            }
-        }
-#endif
         unsigned status = 0;
         KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
         if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_gemm: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");

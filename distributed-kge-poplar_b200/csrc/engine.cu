@@ -203,7 +203,7 @@ void* Engine::device_alloc(size_t bytes) {
 }
 
 size_t Engine::arena_offset_dense(int which) const {
-    const size_t flags = round_up(sizeof(unsigned) * 64, 256);
+    const size_t flags = round_up(sizeof(unsigned) * kFlagWords, 256);
     return flags + (size_t)which * round_up(n_dense_ * sizeof(float), 256);
 }
 size_t Engine::arena_offset_shard(unsigned local, int which) const {
@@ -356,6 +356,8 @@ void Engine::allocate() {
         b.predict_index_dst = (uint32_t**)device_alloc(sizeof(uint32_t*) * cfg_.n_shard);
     }
     d_epoch_ = (unsigned*)device_alloc(sizeof(unsigned));
+    d_xchg_words_ = (unsigned*)device_alloc(2 * XCHG_KINDS * sizeof(unsigned));
+    KGE_CUDA(cudaMemset(d_xchg_words_, 0, 2 * XCHG_KINDS * sizeof(unsigned)));
     d_status_ = (unsigned*)device_alloc(sizeof(unsigned));
     KGE_CUDA(cudaMemset(d_epoch_, 0, sizeof(unsigned)));
     KGE_CUDA(cudaMemset(d_status_, 0, sizeof(unsigned)));
@@ -697,7 +699,21 @@ bool dependent_launch_enabled() {
 }
 
 void Engine::launch_steps() {
+    launch_gather(0);
     for (unsigned step = 0; step < cfg_.n_step; ++step) launch_one_step(step);
+}
+
+// The step's rows, gathered into the compact copy every later kernel of the step reads.  The
+// gather of step s + 1 is queued inside step s, behind the last reader of the copy and ahead of
+// the dense update, so that it runs while the partial dense gradients travel.
+void Engine::launch_gather(unsigned step) {
+    const unsigned R = cfg_.n_remote();
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        const uint32_t* remote = d_remote_ + ((size_t)l * cfg_.n_step + step) * R;
+        KGE_LAUNCH("gather", KGE_CUDA(launch_dependent(k_gather_step_rows, dim3(ceil_div(R, 8)), dim3(256), 0, stream_, b.table,
+                                                       layout_.row_bytes, remote, (int)R, b.rows_c)));
+    }
 }
 
 void Engine::launch_barrier() {
@@ -711,6 +727,30 @@ void Engine::launch_barrier() {
     a.max_spins = 2ull * 1000 * 1000;  // a second or two of 64 ns naps plus load latency
     KGE_LAUNCH("barrier", KGE_CUDA(launch_dependent(k_barrier, dim3(1), dim3(64), 0, stream_, a)));
     KGE_CUDA(cudaGetLastError());
+}
+
+// What the step's kernels need to publish and await the hand-overs between processes; with one
+// process the kernels skip both.
+ExchangeSync Engine::exchange_sync() const {
+    ExchangeSync s{};
+    s.peer_flags = d_peer_flags_;
+    s.epochs = d_xchg_words_;
+    s.counters = d_xchg_words_ + XCHG_KINDS;
+    s.status = d_status_;
+    s.rank = (int)cfg_.rank;
+    s.world = (int)cfg_.world;
+    s.max_spins = 8u * 1000u * 1000u;  // a second or two of 32 ns naps plus load latency
+    return s;
+}
+
+void Engine::launch_exchange_wait(int kind) {
+    if (cfg_.world == 1) return;
+    KGE_LAUNCH("exchange_wait", KGE_CUDA(launch_dependent(k_exchange_wait, dim3(1), dim3(kMaxProcesses), 0, stream_, exchange_sync(), kind)));
+}
+
+void Engine::launch_exchange_signal(int kind) {
+    if (cfg_.world == 1) return;
+    KGE_LAUNCH("exchange_signal", KGE_CUDA(launch_dependent(k_exchange_signal, dim3(1), dim3(kMaxProcesses), 0, stream_, exchange_sync(), kind)));
 }
 
 void Engine::timing_begin(const char* name) {
@@ -755,7 +795,8 @@ int Engine::tc_splits(unsigned tiles, unsigned k) const {
 
 // One launch for one or two contractions of the same kind (see tc_gemm.cuh).  With splits > 1
 // the k range is divided and the partial tiles are reduced inside the kernel, in split order.
-void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum) {
+void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum,
+                       int wait_kind, int signal_kind) {
     for (int i = 0; i < n_problems; ++i) {
         tc::GemmArgs& g = problems[i];
         g.status = d_tc_status_;
@@ -779,10 +820,11 @@ void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems,
     cudaError_t err;
     timing_begin(name);
     int n_launches = 1;
-    if (a_exact) err = rowsum ? tc::launch_pair<64, true, true>(problems, n_problems, splits, stream_, &n_launches)
-                              : tc::launch_pair<64, true, false>(problems, n_problems, splits, stream_, &n_launches);
-    else err = rowsum ? tc::launch_pair<64, false, true>(problems, n_problems, splits, stream_, &n_launches)
-                      : tc::launch_pair<64, false, false>(problems, n_problems, splits, stream_, &n_launches);
+    const ExchangeSync sync = exchange_sync();
+    if (a_exact) err = rowsum ? tc::launch_pair<64, true, true>(problems, n_problems, splits, stream_, &n_launches, sync, wait_kind, signal_kind)
+                              : tc::launch_pair<64, true, false>(problems, n_problems, splits, stream_, &n_launches, sync, wait_kind, signal_kind);
+    else err = rowsum ? tc::launch_pair<64, false, true>(problems, n_problems, splits, stream_, &n_launches, sync, wait_kind, signal_kind)
+                      : tc::launch_pair<64, false, false>(problems, n_problems, splits, stream_, &n_launches, sync, wait_kind, signal_kind);
     timing_end();
     launch_counter_ += (unsigned long long)n_launches;
     KGE_CUDA(err);
@@ -818,6 +860,8 @@ void Engine::launch_one_step(unsigned step) {
     }
     lp.grad_scale = cfg_.loss_scale / normaliser;
 
+    const ExchangeSync sync = exchange_sync();
+    const bool proj_direct = cfg_.tensor_cores && F > 0;  // the projection gradient lands in the partial dense vector directly
     auto step_ptr = [&](uint32_t* base, unsigned l, size_t per_step) {
         return base + ((size_t)l * cfg_.n_step + step) * per_step;
     };
@@ -825,8 +869,6 @@ void Engine::launch_one_step(unsigned step) {
     // 1./2. hidden rows, lookups, send half of the exchange
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
-        const uint32_t* remote = step_ptr(d_remote_, l, R);
-        KGE_LAUNCH("gather", KGE_CUDA(launch_dependent(k_gather_step_rows, dim3(ceil_div(R, 8)), dim3(256), 0, stream_, b.table, layout_.row_bytes, remote, (int)R, b.rows_c)));
         if (cfg_.tensor_cores && F > 0) {
             // hidden = value + feature . W on the tensor cores: A = gathered feature rows, B = W stored [F, D]
             tc::GemmArgs nets[2] = {};
@@ -841,8 +883,11 @@ void Engine::launch_one_step(unsigned step) {
                 g.x_base = b.rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = nullptr;
                 g.x_is_half = cfg_.state_type == ST_F16;
             }
-            launch_tc("hidden", nets, n_nets, tc_splits(n_nets * ceil_div(R, 128) * ceil_div(D, 64), F), cfg_.feature_type == ST_F16, false);
+            // the projection was updated by the processes that own its slices
+            launch_tc("hidden", nets, n_nets, tc_splits(n_nets * ceil_div(R, 128) * ceil_div(D, 64), F), cfg_.feature_type == ST_F16, false,
+                      XCHG_DENSE_PARAMS, -1);
         } else {
+            launch_exchange_wait(XCHG_DENSE_PARAMS);
             dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
             KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, KGE_CUDA(launch_dependent(k_hidden<ST, FT>, dim3(grid), dim3(256), 0, stream_, 
                                                             b.rows_c, layout_, nullptr, 0u, (int)R, W0, W1, b.hid_h, b.hid_t))));
@@ -853,14 +898,13 @@ void Engine::launch_one_step(unsigned step) {
         if (vec)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn)));
+                                                                      (int)B, (int)D, cfg_.score_fn, sync)));
         else
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<1>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn)));
+                                                                      (int)B, (int)D, cfg_.score_fn, sync)));
     }
     KGE_CUDA(cudaGetLastError());
-    launch_barrier();
 
     // 3./4./5a. scores, loss, score backward with the return half of the exchange
     for (unsigned l = 0; l < n_local_; ++l) {
@@ -882,9 +926,13 @@ void Engine::launch_one_step(unsigned step) {
             g.B = tc::make_operand(b.tails, (long long)D * 4, false, false);
             g.M = (int)B; g.N = (int)T; g.K = (int)D; g.k_per_split = (int)round_up(D, 32);
             g.epilogue = tc::EPI_STORE; g.out = b.raw; g.ldc = T; g.block_rows = 1;
-            launch_tc("score", &g, 1, tc_splits(ceil_div(B, 128) * ceil_div(T, 64), D), false, false);
+            launch_tc("score", &g, 1, tc_splits(ceil_div(B, 128) * ceil_div(T, 64), D), false, false, XCHG_TAILS, -1);
         } else {
-            KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_)));
+            // the tail rows come from the other processes: the 16-byte-copy kernel waits for them itself
+            const bool fused_wait = score_rows_aligned(b.pred, b.tails, (int)D);
+            if (!fused_wait) launch_exchange_wait(XCHG_TAILS);
+            KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_,
+                                                      fused_wait ? sync : ExchangeSync{})));
         }
         KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
                                                                d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l)));
@@ -910,19 +958,33 @@ void Engine::launch_one_step(unsigned step) {
             h.out = nullptr; h.out_blocks = b.grad_dst; h.block_rows = (int)cfg_.a2a_size; h.ldc = D;
             h.x_base = reinterpret_cast<const uint8_t*>(b.tails); h.x_row_stride_bytes = (long long)D * 4;
             g.k_per_split = h.k_per_split;
-            launch_tc("score_bwd", both, 2, tc_splits((ceil_div(B, 128) + ceil_div(T, 128)) * ceil_div(D, 64), std::min(B, T)), false, l2);
-        } else
+            launch_tc("score_bwd", both, 2, tc_splits((ceil_div(B, 128) + ceil_div(T, 128)) * ceil_div(D, 64), std::min(B, T)), false, l2,
+                      -1, XCHG_TAIL_GRADS);
+        } else {
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_L1>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
             case DIST_L2: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_L2>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
             default: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_DOT>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
         }
+        launch_exchange_signal(XCHG_TAIL_GRADS);
+        }
         if (cfg_.score_fn != SCORE_TRANSE)
             KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
                                                                      b.d_relrow, (int)D, cfg_.score_fn)));
+        if (proj_direct) {
+            // the relation gradients need nothing from other processes: they are summed while the tail gradients travel
+            const size_t sidx = (size_t)l * cfg_.n_step + step;
+            if (vec)
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
+                                                b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_partial, sync, -1)));
+            else
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
+                                                b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_partial, sync, -1)));
+        }
     }
     KGE_CUDA(cudaGetLastError());
-    launch_barrier();
 
     // 5b. segment sums + row-wise Adam; projection and relation gradients of this shard
     for (unsigned l = 0; l < n_local_; ++l) {
@@ -937,20 +999,20 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
         } else {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
                                                 b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
         }
         if (F > 0 && cfg_.tensor_cores) {
             // d W = feature^T . d_hidden: the gathered rows are the k index of both operands
@@ -961,10 +1023,12 @@ void Engine::launch_one_step(unsigned step) {
                 g.B = tc::make_operand(net ? b.d_hid_t : b.d_hid_h, (long long)D * 4, false, true);
                 g.M = (int)F; g.N = (int)D; g.K = (int)R; g.k_per_split = proj_rows_per_split_;
                 g.epilogue = tc::EPI_STORE;
-                g.out = b.proj_partial + (size_t)net * proj_elems_; g.ldc = D; g.block_rows = 1;
+                // straight into this shard's partial dense gradient, behind the relation rows
+                g.out = b.dense_partial + (size_t)n_rel * D + (size_t)net * proj_elems_; g.ldc = D; g.block_rows = 1;
             }
             launch_tc("projection_bwd", nets, (int)cfg_.n_net(),
-                      tc_splits(cfg_.n_net() * ceil_div(F, 128) * ceil_div(D, 64), R), cfg_.feature_type == ST_F16, false);
+                      tc_splits(cfg_.n_net() * ceil_div(F, 128) * ceil_div(D, 64), R), cfg_.feature_type == ST_F16, false,
+                      -1, XCHG_DENSE_PARTIALS);
         } else if (F > 0) {
             dim3 grid(ceil_div(F, 64), ceil_div(D, 64), cfg_.n_net() * proj_splits_);
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
@@ -977,25 +1041,30 @@ void Engine::launch_one_step(unsigned step) {
                                                  b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
                                                  proj_rows_per_split_, b.proj_partial)));
         }
-        const size_t proj_total = (size_t)cfg_.n_net() * proj_elems_;
-        const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 511) / 512, 148 * 4) : 0;
-        if (vec)
-            KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_, 
-                                            b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                            (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
-                                            proj_elems_, b.dense_partial)));
-        else
-            KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_, 
-                                            b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                            (int)D, b.proj_partial, (int)cfg_.n_net(), cfg_.tensor_cores ? 1 : proj_splits_,
-                                            proj_elems_, b.dense_partial)));
+        if (!proj_direct) {
+            // relation gradients and the sum of the projection gradient's row splits; completes the partial dense gradient
+            const size_t proj_total = (size_t)cfg_.n_net() * proj_elems_;
+            const unsigned proj_blocks = proj_total ? (unsigned)std::min<size_t>((proj_total + 511) / 512, 148 * 4) : 0;
+            if (vec)
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
+                                                b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                                (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
+                                                proj_elems_, b.dense_partial, sync, (int)XCHG_DENSE_PARTIALS)));
+            else
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
+                                                b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                                (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
+                                                proj_elems_, b.dense_partial, sync, (int)XCHG_DENSE_PARTIALS)));
+        }
     }
     KGE_CUDA(cudaGetLastError());
-    launch_barrier();
+    if (step + 1 < cfg_.n_step) launch_gather(step + 1);
 
-    // 5c. dense parameters: reduce over shards, Adam on the owned slice, publish
-    if (own_hi_ > own_lo_) {
+    // 5c. dense parameters: reduce over shards, Adam on the owned slice, publish.  Every process
+    // launches it, also one that owns nothing, since the kernel carries two hand-overs.
+    {
         DenseUpdateArgs da{};
+        da.sync = sync;
         da.partials = d_partials_;
         da.n_partial = (int)cfg_.n_shard;
         da.replicas = d_replicas_;
@@ -1013,7 +1082,6 @@ void Engine::launch_one_step(unsigned step) {
         KGE_LAUNCH("dense_update", KGE_CUDA(launch_dependent(k_dense_update, dim3(std::max(1u, blocks)), dim3(256), 0, stream_, da, (int)cfg_.rank)));
     }
     KGE_CUDA(cudaGetLastError());
-    launch_barrier();
 }
 
 // ---------------------------------------------------------------------------
@@ -1209,11 +1277,11 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
             if (vec)
                 KGE_LAUNCH("predict_query", k_route<4><<<(unsigned)hr, 64, 0, stream_>>>(
                                                 p_head_hidden_, p_head_hidden_, nullptr, d_iota_, d_rel + l * hr, dense_, nullptr,
-                                                dst, 0, 1, (int)hr, (int)D, cfg_.score_fn));
+                                                dst, 0, 1, (int)hr, (int)D, cfg_.score_fn, ExchangeSync{}));
             else
                 KGE_LAUNCH("predict_query", k_route<1><<<(unsigned)hr, 64, 0, stream_>>>(
                                                 p_head_hidden_, p_head_hidden_, nullptr, d_iota_, d_rel + l * hr, dense_, nullptr,
-                                                dst, 0, 1, (int)hr, (int)D, cfg_.score_fn));
+                                                dst, 0, 1, (int)hr, (int)D, cfg_.score_fn, ExchangeSync{}));
         }
     }
     KGE_CUDA(cudaGetLastError());

@@ -127,7 +127,12 @@ class Engine {
     void launch_steps();
     void launch_one_step(unsigned step);
     void launch_barrier();
-    void launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum);
+    ExchangeSync exchange_sync() const;
+    void launch_exchange_wait(int kind);
+    void launch_exchange_signal(int kind);
+    void launch_gather(unsigned step);
+    void launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum,
+                   int wait_kind = -1, int signal_kind = -1);
     void check_device_status();
     void timing_begin(const char* name);
     void timing_end();
@@ -152,6 +157,7 @@ class Engine {
     bool connected_ = false;
     unsigned* d_epoch_ = nullptr;
     unsigned* d_status_ = nullptr;
+    unsigned* d_xchg_words_ = nullptr;  // [XCHG_KINDS] published epochs, [XCHG_KINDS] finished-block counters
     unsigned* d_tc_status_ = nullptr;
     // split-k workspace of the tensor-core contractions (shared by all of them: one stream)
     float *tc_ws_ = nullptr, *tc_ws_rowsum_ = nullptr;

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "exchange.cuh"
 #include "pdl.cuh"
 
 namespace kge {
@@ -232,7 +233,7 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         const uint32_t* __restrict__ a2a_idx, const uint32_t* __restrict__ head,
         const uint32_t* __restrict__ relation, const float* __restrict__ rel_table,
         float* const* __restrict__ send_dst, float* __restrict__ pred, int T, int a2a, int B, int D,
-        int score_fn) {
+        int score_fn, ExchangeSync sync) {
     grid_dependency_sync();
     const int b = blockIdx.x;
     if (b < T) {
@@ -244,10 +245,14 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         } else {
             for (int c = threadIdx.x; c < D; c += blockDim.x) out[c] = src[c];
         }
+        exchange_signal(sync, XCHG_TAILS, gridDim.x);  // the tail rows are in their consumers' memory
         return;
     }
     const int i = b - T;
-    if (i >= B) return;
+    if (i >= B) {
+        exchange_signal(sync, XCHG_TAILS, gridDim.x);
+        return;
+    }
     const float* __restrict__ h = hid_h + (size_t)head[i] * D;
     const float* __restrict__ r = rel_table + (size_t)relation[i] * D;
     float* __restrict__ p = pred + (size_t)i * D;
@@ -273,6 +278,7 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         for (int c = threadIdx.x; c < D; c += blockDim.x)
             p[c] = score_fn == SCORE_TRANSE ? h[c] + r[c] : h[c] * r[c];
     }
+    exchange_signal(sync, XCHG_TAILS, gridDim.x);
 }
 
 // ---------------------------------------------------------------------------
@@ -394,8 +400,9 @@ __device__ __forceinline__ void score_copy16(float* dst_smem, const float* src) 
 template <int FN>
 __global__ void __launch_bounds__(32 * kScoreWarps, 3)
 k_score_wide(const float* __restrict__ P, const float* __restrict__ Tl, float* __restrict__ raw, int B,
-             int T, int D) {
+             int T, int D, ExchangeSync sync) {
     grid_dependency_sync();
+    exchange_wait(sync, XCHG_TAILS);  // the tail rows come from the other processes
     extern __shared__ __align__(16) float score_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
@@ -478,11 +485,16 @@ k_score_wide(const float* __restrict__ P, const float* __restrict__ Tl, float* _
 }
 
 // Picks the kernel: the 16-byte-copy form when the rows allow it, the general form otherwise.
+// `sync` with world > 1: the kernel waits for the tail rows of the other processes (only the
+// 16-byte-copy form can; returns cudaErrorNotSupported otherwise so that the caller waits first).
 template <int FN>
-inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream) {
+inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream,
+                                const ExchangeSync& sync = ExchangeSync{}) {
     const bool aligned = (D % 4) == 0 && reinterpret_cast<uintptr_t>(P) % 16 == 0 && reinterpret_cast<uintptr_t>(Tl) % 16 == 0;
-    if (!aligned)
+    if (!aligned) {
+        if (sync.world > 1) return cudaErrorNotSupported;
         return launch_dependent(k_score<FN>, dim3((T + 63) / 64, (B + 31) / 32), dim3(128), 0, stream, P, Tl, raw, B, T, D);
+    }
     static bool configured = false;  // one attribute call per instantiation and process is enough
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(k_score_wide<FN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreWideSmem);
@@ -490,14 +502,19 @@ inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int
         configured = true;
     }
     return launch_dependent(k_score_wide<FN>, dim3((T + 31) / 32, (B + 31) / 32), dim3(32 * kScoreWarps), kScoreWideSmem, stream,
-                            P, Tl, raw, B, T, D);
+                            P, Tl, raw, B, T, D, sync);
 }
 
-inline cudaError_t launch_score(int dist_fn, const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream) {
+inline bool score_rows_aligned(const float* P, const float* Tl, int D) {
+    return (D % 4) == 0 && reinterpret_cast<uintptr_t>(P) % 16 == 0 && reinterpret_cast<uintptr_t>(Tl) % 16 == 0;
+}
+
+inline cudaError_t launch_score(int dist_fn, const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream,
+                                const ExchangeSync& sync = ExchangeSync{}) {
     switch (dist_fn) {
-        case DIST_L1: return launch_score<DIST_L1>(P, Tl, raw, B, T, D, stream);
-        case DIST_L2: return launch_score<DIST_L2>(P, Tl, raw, B, T, D, stream);
-        default: return launch_score<DIST_DOT>(P, Tl, raw, B, T, D, stream);
+        case DIST_L1: return launch_score<DIST_L1>(P, Tl, raw, B, T, D, stream, sync);
+        case DIST_L2: return launch_score<DIST_L2>(P, Tl, raw, B, T, D, stream, sync);
+        default: return launch_score<DIST_DOT>(P, Tl, raw, B, T, D, stream, sync);
     }
 }
 
@@ -892,8 +909,9 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 const uint32_t* __restrict__ first_slot, const float* __restrict__ d_head,
                 const float* __restrict__ grad_recv, int B,
                 float* __restrict__ d_hid_h, float* __restrict__ d_hid_t,
-                const float* __restrict__ step_size, float lr_modifier, AdamParams ap) {
+                const float* __restrict__ step_size, float lr_modifier, AdamParams ap, ExchangeSync sync) {
     grid_dependency_sync();
+    exchange_wait(sync, XCHG_TAIL_GRADS);  // grad_recv is written by the other processes
     // partial sums of the item lanes, [lane][head | tail][64 column threads][V]
     __shared__ float part[kSegmentLanes][2][64 * V];
     __shared__ uint32_t s_perm[64 * kSegmentLanes];
@@ -1106,7 +1124,7 @@ __global__ void __launch_bounds__(64 * kRelationLanes)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
-                float* __restrict__ dense_partial) {
+                float* __restrict__ dense_partial, ExchangeSync sync, int signal_kind) {
     grid_dependency_sync();
     __shared__ float part[kRelationLanes][64 * V];
     __shared__ uint32_t s_perm[64 * kRelationLanes];
@@ -1118,6 +1136,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
         if (q0 == q1) {
             for (int c = threadIdx.x; c < D; c += blockDim.x) dense_partial[(size_t)rho * D + c] = 0.f;
+            exchange_signal(sync, signal_kind, gridDim.x);
             return;
         }
         for (int c0 = 0; c0 < D; c0 += 64 * V) {
@@ -1164,6 +1183,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
                 }
             }
         }
+        exchange_signal(sync, signal_kind, gridDim.x);
         return;
     }
     const size_t rel_elems = (size_t)n_rel * D;
@@ -1176,6 +1196,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         for (int z = 0; z < splits; ++z) g += proj_partial[(net * splits + z) * proj_elems + idx];
         dense_partial[rel_elems + pe] = g;
     }
+    exchange_signal(sync, signal_kind, gridDim.x);
 }
 
 // Sum of the shards' dense contributions in shard order (the reduce-scatter of
@@ -1195,25 +1216,59 @@ struct DenseUpdateArgs {
     float lr_modifier[3];
     const float* step_size;
     AdamParams ap;
+    ExchangeSync sync;
 };
 
+__device__ __forceinline__ float dense_adam(float x, float g, float& m, float& v, float alpha, const AdamParams& ap) {
+    m = ap.beta_m * m + ap.one_minus_beta_m * g;
+    v = ap.beta_v * v + ap.one_minus_beta_v * g * g;
+    return x - alpha * (m / (sqrtf(v) + ap.epsilon) + ap.weight_decay * x);
+}
+
+// With more than one process the partial gradients are read from, and the new values written to,
+// the other processes' memory: four elements per access, and the reads of all partials of an
+// element group are issued before the first is used.
 static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, int self) {
     grid_dependency_sync();
+    exchange_wait(a.sync, XCHG_DENSE_PARTIALS);  // every process's partial gradients are complete
     const float base_alpha = *a.step_size;
-    for (size_t e = a.lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < a.hi;
-         e += (size_t)gridDim.x * blockDim.x) {
-        float g = 0.f;
-        for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][e];
-        const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
-        const float alpha = base_alpha * a.lr_modifier[p];
-        float x = a.replicas[self][e], m = a.adam_m[e], v = a.adam_v[e];
-        m = a.ap.beta_m * m + a.ap.one_minus_beta_m * g;
-        v = a.ap.beta_v * v + a.ap.one_minus_beta_v * g * g;
-        x = x - alpha * (m / (sqrtf(v) + a.ap.epsilon) + a.ap.weight_decay * x);
-        a.adam_m[e] = m;
-        a.adam_v[e] = v;
-        for (int rep = 0; rep < a.n_replica; ++rep) a.replicas[rep][e] = x;
+    const bool vec = ((a.lo | a.hi | a.bounds[1] | a.bounds[2]) & 3) == 0;
+    if (vec) {
+        for (size_t e = a.lo + 4 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x); e < a.hi;
+             e += 4 * (size_t)gridDim.x * blockDim.x) {
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int s = 0; s < a.n_partial; ++s) {
+                const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + e);
+                g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+            }
+            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
+            const float alpha = base_alpha * a.lr_modifier[p];
+            float4 x = *reinterpret_cast<const float4*>(a.replicas[self] + e);
+            float4 m = *reinterpret_cast<const float4*>(a.adam_m + e), v = *reinterpret_cast<const float4*>(a.adam_v + e);
+            x.x = dense_adam(x.x, g.x, m.x, v.x, alpha, a.ap);
+            x.y = dense_adam(x.y, g.y, m.y, v.y, alpha, a.ap);
+            x.z = dense_adam(x.z, g.z, m.z, v.z, alpha, a.ap);
+            x.w = dense_adam(x.w, g.w, m.w, v.w, alpha, a.ap);
+            *reinterpret_cast<float4*>(a.adam_m + e) = m;
+            *reinterpret_cast<float4*>(a.adam_v + e) = v;
+            for (int rep = 0; rep < a.n_replica; ++rep) *reinterpret_cast<float4*>(a.replicas[rep] + e) = x;
+        }
+    } else {
+        for (size_t e = a.lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < a.hi;
+             e += (size_t)gridDim.x * blockDim.x) {
+            float g = 0.f;
+            for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][e];
+            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
+            const float alpha = base_alpha * a.lr_modifier[p];
+            float m = a.adam_m[e], v = a.adam_v[e];
+            const float x = dense_adam(a.replicas[self][e], g, m, v, alpha, a.ap);
+            a.adam_m[e] = m;
+            a.adam_v[e] = v;
+            for (int rep = 0; rep < a.n_replica; ++rep) a.replicas[rep][e] = x;
+        }
     }
+    exchange_signal(a.sync, XCHG_DENSE_PARAMS, gridDim.x);  // the new values are in every process's copy
 }
 
 // ---------------------------------------------------------------------------

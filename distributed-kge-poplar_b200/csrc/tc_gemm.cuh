@@ -30,6 +30,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "exchange.cuh"
 #include "pdl.cuh"
 
 namespace kge {
@@ -85,7 +86,6 @@ struct GemmArgs {
     // Set by launch_pair: the blocks of one output tile (one per split) form a thread-block cluster
     // and reduce their partial tiles through distributed shared memory; 0 = not a cluster launch.
     int cluster_splits;
-    long long* trace;
 };
 
 // ---------------------------------------------------------------------------
@@ -429,6 +429,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
 struct GemmPair {
     GemmArgs p[2];
     int tiles_m0;  // blocks with blockIdx.x < tiles_m0 work on p[0], the others on p[1]
+    // hand-overs between processes folded into the launch (-1 = none): what the blocks wait for
+    // before they read their operands, and what the last block to finish publishes
+    ExchangeSync sync;
+    int wait_kind, signal_kind;
 };
 
 __device__ __forceinline__ void cp_async16(uint8_t* dst_smem, const void* src, int src_bytes) {
@@ -566,22 +570,34 @@ __device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw,
     }
 }
 
-// Epilogue and store of four neighbouring output columns (m, n .. n+3) whose k range is complete.
-__device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, int m, int n, float (&acc)[4], float rs) {
-    if (g.epilogue != EPI_STORE) {
-        const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
-        const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
+// The epilogue's second operand for four neighbouring output columns (m, n .. n+3): the value part
+// of the table row (EPI_ADD_TABLE_VALUE) or X[m, n ..] (EPI_ROWSUM_X_MINUS); zeros for EPI_STORE.
+__device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, float (&x)[4]) {
+    x[0] = x[1] = x[2] = x[3] = 0.f;
+    if (g.epilogue == EPI_STORE) return;
+    const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
+    const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
+    const bool half = g.epilogue == EPI_ADD_TABLE_VALUE && g.x_is_half;
+    if (!half && n + 3 < g.N && ((reinterpret_cast<uintptr_t>(x_row) + (size_t)n * 4) & 15) == 0) {
+        const float4 v = *reinterpret_cast<const float4*>(x_row + (size_t)n * 4);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        return;
+    }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (n + j >= g.N) continue;
-            if (g.epilogue == EPI_ADD_TABLE_VALUE) {
-                const float x = g.x_is_half ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j])
-                                            : reinterpret_cast<const float*>(x_row)[n + j];
-                acc[j] = x + acc[j];
-            } else {
-                acc[j] = rs * reinterpret_cast<const float*>(x_row)[n + j] - acc[j];
-            }
-        }
+    for (int j = 0; j < 4; ++j)
+        if (n + j < g.N)
+            x[j] = half ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j]) : reinterpret_cast<const float*>(x_row)[n + j];
+}
+
+// Epilogue and store of four neighbouring output columns whose k range is complete.
+__device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, int m, int n, float (&acc)[4],
+                                            const float (&x)[4], float rs) {
+    if (g.epilogue == EPI_ADD_TABLE_VALUE) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = x[j] + acc[j];
+    } else if (g.epilogue == EPI_ROWSUM_X_MINUS) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = rs * x[j] - acc[j];
     }
     float* out_row;
     if (g.out_blocks) {
@@ -620,27 +636,35 @@ __device__ __forceinline__ float4 cluster_load4(uint32_t addr) {
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ void cluster_store4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void cluster_store1(uint32_t addr, float a) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
 __device__ __forceinline__ float cluster_load1(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
 }
 
-#ifdef KGE_TC_TRACE
-#define TRACE(slot) do { if (trace_on && kc < 64) g.trace[kc * 8 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot) do {} while (0)
-#endif
 // Warp roles of the pipelined kernel: 8 staging warps, 8 accumulating warps, 1 issuing warp, 1 copying warp.
 constexpr int kStageWarps = 8, kAccWarps = 8;
 constexpr int kStageThreads = 32 * kStageWarps;
 constexpr int kPipeThreads = 32 * (kStageWarps + kAccWarps + 2);
-constexpr int kRawSlots = 4;   // raw slices in flight per block
+constexpr int kRawSlots = 3;   // raw slices in flight per block
 constexpr int kTmemSlots = 4;  // accumulator tiles: slices whose products may be pending or unread
 
+constexpr int kMaxClusterRows = 8;  // rows_each * splits exceeds 128 by less than the number of splits
+// Rows received from the other splits of a cluster: [splits][rows_each][BN + 4] floats and their row sums.
+template <int BN>
+constexpr size_t cluster_receive_bytes() {
+    return (size_t)(kBM + kMaxClusterRows) * (BN + 4 + 1) * 4;
+}
 template <int BN>
 constexpr size_t smem_bytes_async() {
-    return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128) + (size_t)kRawSlots * (kBM * 128 + BN * 128);
+    return 1024 + (size_t)kStages * (2 * kBM * 128 + 2 * BN * 128) + (size_t)kRawSlots * (kBM * 128 + BN * 128) +
+           cluster_receive_bytes<BN>();
 }
 
 // Tensor maps of the operands of the (up to) two problems of a launch: the copying warp moves a
@@ -695,7 +719,12 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
     const GemmArgs& g = gp.p[which];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = ((int)blockIdx.x - (which ? gp.tiles_m0 : 0)) * kBM, n0 = blockIdx.y * BN;
-    if (n0 >= g.N || m0 >= g.M) return;  // the two problems may differ in size (a whole cluster leaves together)
+    const unsigned total_blocks = gridDim.x * gridDim.y * gridDim.z;
+    if (n0 >= g.N || m0 >= g.M) {  // the two problems may differ in size (a whole cluster leaves together)
+        grid_dependency_sync();
+        exchange_signal(gp.sync, gp.signal_kind, total_blocks);
+        return;
+    }
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128, kStage = 2 * kATile + 2 * kBTile, kRaw = kATile + kBTile;
@@ -723,11 +752,9 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
     __syncthreads();
     tc_fence_after();
     grid_dependency_sync();
+    exchange_wait(gp.sync, gp.wait_kind);
     const uint32_t tmem_base = tmem_slot;
 
-#ifdef KGE_TC_TRACE
-    const bool trace_on = g.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 256 || tid == 512);
-#endif
     float rowsum[4] = {0.f, 0.f, 0.f, 0.f};
     float acc[CPT];
 #pragma unroll
@@ -737,9 +764,7 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
         for (int kc = 0; kc < n_slices; ++kc) {
             const int s = kc % kStages, slot = kc % kRawSlots;
             mbar_wait(&bar_raw_full[slot], (uint32_t)((kc / kRawSlots) & 1), g.status, 5u);
-            TRACE(0);
             if (kc >= kStages) mbar_wait(&bar_empty[s], (uint32_t)(((kc / kStages) - 1) & 1), g.status, 2u);
-            TRACE(1);
             uint8_t* stage = smem + (size_t)s * kStage;
             uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
             const uint8_t* raw = raw_ring + (size_t)slot * kRaw;
@@ -752,7 +777,6 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
                 mbar_arrive(&bar_full[s]);
                 mbar_arrive(&bar_raw_empty[slot]);
             }
-            TRACE(2);
         }
     } else if (warp == kStageWarps + kAccWarps + 1) {
         const CUtensorMap* map_a = &maps.a[which];
@@ -777,10 +801,8 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
         for (int kc = 0; kc < n_slices; ++kc) {
             const int s = kc % kStages, t = kc % kTmemSlots;
             mbar_wait(&bar_full[s], (uint32_t)((kc / kStages) & 1), g.status, 3u);
-            TRACE(3);
             if (kc >= kTmemSlots) mbar_wait(&bar_acc_free[t], (uint32_t)(((kc / kTmemSlots) - 1) & 1), g.status, 4u);
             tc_fence_after();
-            TRACE(4);
             if (lane == 0) {
                 uint8_t* stage = smem + (size_t)s * kStage;
                 uint8_t *a_hi = stage, *a_lo = stage + kATile, *b_hi = stage + 2 * kATile, *b_lo = b_hi + kBTile;
@@ -798,7 +820,6 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
                 umma_commit(&bar_acc_ready[t]);
             }
             __syncwarp();
-            TRACE(5);
         }
     } else {
         // The tensor core truncates its fp32 accumulator once per instruction, so every slice is
@@ -807,7 +828,6 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
         for (int kc = 0; kc < n_slices; ++kc) {
             const int t = kc % kTmemSlots;
             mbar_wait(&bar_acc_ready[t], (uint32_t)((kc / kTmemSlots) & 1), g.status, 1u);
-            TRACE(6);
             tc_fence_after();
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * BN + half * CPT), r);
@@ -816,7 +836,6 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
             if (lane == 0) mbar_arrive(&bar_acc_free[t]);
 #pragma unroll
             for (int j = 0; j < CPT; ++j) acc[j] += __uint_as_float(r[j]);
-            TRACE(7);
         }
     }
 
@@ -850,35 +869,53 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
     const int row = (warp & 3) * 32 + lane, m = m0 + row;
     const int nc0 = n0 + ((warp - kStageWarps) >> 2) * CPT;  // first output column of an accumulating thread
     if (g.cluster_splits > 1) {
-        // The splits of this tile are the blocks of one cluster.  Each leaves its partial tile in its
-        // own shared memory; after the cluster barrier block z adds rows z * rows_each ... of all
-        // partial tiles, in split order, and finishes them.
-        constexpr int kRedStride = BN + 4;  // floats; keeps the 128-bit writes below free of bank conflicts
-        static_assert((size_t)kBM * kRedStride * 4 <= (size_t)kStages * kStage, "the partial tile fits the operand stages");
-        float* red = reinterpret_cast<float*>(smem);
-        if (acc_warp) {
-#pragma unroll
-            for (int j = 0; j < CPT; j += 4)
-                *reinterpret_cast<float4*>(red + row * kRedStride + (nc0 - n0) + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-        }
-        cluster_sync();
+        // The splits of this tile are the blocks of one cluster, and block z finishes rows
+        // z * rows_each ... of the tile.  Every block sends each of its partial rows to the shared
+        // memory of the row's owner (remote stores, nobody waits for them); after one cluster
+        // barrier the owner adds what it received, in split order, and nobody reads remote memory
+        // any more, so a block may leave as soon as it has stored its rows.
+        constexpr int kRedStride = BN + 4;  // floats; keeps the 128-bit accesses free of bank conflicts
         const int n_split = g.cluster_splits, rank = (int)cluster_rank();
         const int rows_each = (kBM + n_split - 1) / n_split;
+        // (a region of its own: a faster block may send while this one still reads its operand stages)
+        float* red = reinterpret_cast<float*>(raw_ring + (size_t)kRawSlots * kRaw);  // [source block][row of mine][BN]
+        float* red_rowsum = red + (size_t)n_split * rows_each * kRedStride;  // [source block][row of mine]
+        if (acc_warp) {
+            const int owner = row / rows_each, local = row - owner * rows_each;
+            const uint32_t dst = cluster_map(smem_u32(red + ((size_t)rank * rows_each + local) * kRedStride + (nc0 - n0)), (uint32_t)owner);
+#pragma unroll
+            for (int j = 0; j < CPT; j += 4) cluster_store4(dst + (uint32_t)j * 4u, acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            if (ROWSUM && nc0 == n0)
+                cluster_store1(cluster_map(smem_u32(red_rowsum + rank * rows_each + local), (uint32_t)owner), s_rowsum[row]);
+        }
+        // the epilogue's second operand is fetched while the partial rows travel
         const int r_begin = rank * rows_each, r_end = min(kBM, r_begin + rows_each);
         constexpr int kQuads = BN / 4;
-        const uint32_t red_addr = smem_u32(red), rowsum_addr = smem_u32(s_rowsum);
-        for (int u = tid; u < (r_end - r_begin) * kQuads; u += kPipeThreads) {
-            const int r = r_begin + u / kQuads, c = (u % kQuads) * 4;
+        const int n_units = max(0, r_end - r_begin) * kQuads;  // at most 64 rows x 16 = 2 per thread
+        float xv[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int u = tid + i * kPipeThreads;
+            const int mm = m0 + r_begin + u / kQuads, nn = n0 + (u % kQuads) * 4;
+            xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
+            if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i]);
+        }
+        cluster_sync();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int u = tid + i * kPipeThreads;
+            if (u >= n_units) continue;
+            const int local = u / kQuads, c = (u % kQuads) * 4;
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
             float row_total = 0.f;
             for (int z = 0; z < n_split; ++z) {
-                const float4 v = cluster_load4(cluster_map(red_addr + (uint32_t)(r * kRedStride + c) * 4u, (uint32_t)z));
+                const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)z * rows_each + local) * kRedStride + c);
                 sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
-                if (ROWSUM) row_total += cluster_load1(cluster_map(rowsum_addr + (uint32_t)r * 4u, (uint32_t)z));
+                if (ROWSUM) row_total += red_rowsum[z * rows_each + local];
             }
-            if (m0 + r < g.M && n0 + c < g.N) finish_four(g, g.out, m0 + r, n0 + c, sum, row_total);
+            const int mm = m0 + r_begin + local, nn = n0 + c;
+            if (mm < g.M && nn < g.N) finish_four(g, g.out, mm, nn, sum, xv[i], row_total);
         }
-        cluster_sync();  // nobody leaves while its shared memory may still be read
     } else if (acc_warp && m < g.M && nc0 < g.N) {
         if (g.ws) {
             // split run without a cluster: leave the raw partial tile (and row sums) for k_tc_reduce
@@ -899,13 +936,18 @@ k_tc_gemm_async(const __grid_constant__ GemmPair gp, const __grid_constant__ Gem
 #pragma unroll
             for (int j = 0; j < CPT; j += 4) {
                 float four[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
-                if (nc0 + j < g.N) finish_four(g, out_base, m, nc0 + j, four, rs);
+                float x[4];
+                if (nc0 + j < g.N) {
+                    load_x_four(g, m, nc0 + j, x);
+                    finish_four(g, out_base, m, nc0 + j, four, x, rs);
+                }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, kTmemSlots * BN);
+    exchange_signal(gp.sync, gp.signal_kind, total_blocks);
 }
 
 // Adds the partial tiles of a k split in split order and applies the epilogue of the contraction:
@@ -935,7 +977,9 @@ static __global__ void __launch_bounds__(256) k_tc_reduce(const __grid_constant_
     float rs = 0.f;
     if (g.epilogue == EPI_ROWSUM_X_MINUS)
         for (int z = 0; z < g.splits; ++z) rs += g.ws_rowsum[(size_t)z * g.M + m];
-    finish_four(g, g.out, m, n, acc, rs);
+    float x[4];
+    load_x_four(g, m, n, x);
+    finish_four(g, g.out, m, n, acc, x, rs);
 }
 
 // Host side: grid = (ceil(M / 128), ceil(N / BN), splits).
@@ -1022,13 +1066,21 @@ inline int max_resident_clusters(int splits) {
 }
 
 template <int BN, bool A_EXACT, bool ROWSUM>
-inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int splits, cudaStream_t stream, int* n_launches = nullptr) {
+inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int splits, cudaStream_t stream, int* n_launches = nullptr,
+                               const ExchangeSync& sync = ExchangeSync{}, int wait_kind = -1, int signal_kind = -1) {
     if (n_launches) *n_launches = n_problems;
     bool fast = true;
     for (int i = 0; i < n_problems; ++i)
         fast = fast && rows_16_byte_aligned(problems[i].A) && rows_16_byte_aligned(problems[i].B) && !problems[i].A.gather && !problems[i].B.gather;
+    const bool synced = sync.world > 1;
     if (!fast) {
-        // the unpipelined kernel has no in-kernel split reduction: run each problem unsplit
+        // the unpipelined kernel has no in-kernel split reduction: run each problem unsplit; the
+        // hand-overs between processes become kernels of their own around it
+        if (synced && wait_kind >= 0) {
+            cudaError_t err = launch_dependent(k_exchange_wait, dim3(1), dim3(kMaxProcesses), 0, stream, sync, wait_kind);
+            if (err != cudaSuccess) return err;
+            if (n_launches) ++*n_launches;
+        }
         for (int i = 0; i < n_problems; ++i) {
             GemmArgs g = problems[i];
             if (g.ws) {
@@ -1037,6 +1089,10 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
             }
             cudaError_t err = launch<BN, A_EXACT, ROWSUM>(g, g.ws ? 1 : splits, stream);
             if (err != cudaSuccess) return err;
+        }
+        if (synced && signal_kind >= 0) {
+            if (n_launches) ++*n_launches;
+            return launch_dependent(k_exchange_signal, dim3(1), dim3(kMaxProcesses), 0, stream, sync, signal_kind);
         }
         return cudaSuccess;
     }
@@ -1051,6 +1107,9 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
     gp.p[0] = problems[0];
     gp.p[1] = problems[n_problems > 1 ? 1 : 0];
     gp.tiles_m0 = (problems[0].M + kBM - 1) / kBM;
+    gp.sync = sync;
+    gp.wait_kind = wait_kind;
+    gp.signal_kind = signal_kind;
     int tiles_m = gp.tiles_m0, tiles_n = (problems[0].N + BN - 1) / BN;
     if (n_problems > 1) {
         tiles_m += (problems[1].M + kBM - 1) / kBM;
@@ -1071,8 +1130,11 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         gp.p[0].cluster_splits = gp.p[1].cluster_splits = splits;
         return launch_dependent_cluster(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, (unsigned)splits, gp, maps);
     }
+    // with a workspace the reduction kernel writes the result, so the publishing moves behind it
+    const bool reduce_after = problems[0].ws != nullptr;
+    if (reduce_after) gp.signal_kind = -1;
     cudaError_t err = launch_dependent(kernel, grid, dim3(kPipeThreads), smem_bytes_async<BN>(), stream, gp, maps);
-    if (err != cudaSuccess || !problems[0].ws) return err;
+    if (err != cudaSuccess || !reduce_after) return err;
     if (n_launches) *n_launches = 2;
     gp.p[0].splits = gp.p[1].splits = splits;
     long long units = 0;
@@ -1081,7 +1143,10 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         units = u > units ? u : units;
     }
     dim3 rgrid((unsigned)((units + 255) / 256), n_problems);
-    return launch_dependent(k_tc_reduce, rgrid, dim3(256), 0, stream, gp);
+    err = launch_dependent(k_tc_reduce, rgrid, dim3(256), 0, stream, gp);
+    if (err != cudaSuccess || !synced || signal_kind < 0) return err;
+    if (n_launches) *n_launches = 3;
+    return launch_dependent(k_exchange_signal, dim3(1), dim3(kMaxProcesses), 0, stream, sync, signal_kind);
 }
 
 inline Operand make_operand(const void* base, long long row_stride_bytes, bool is_half, bool transposed,
