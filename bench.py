@@ -236,6 +236,27 @@ def step_traffic(n_shard: int) -> dict:
     }
 
 
+def summarise_exchange_trace(flat: np.ndarray) -> dict:
+    """Mean timeline of one step from the engine's optional hand-over stamps (KGE_EXCHANGE_TRACE=1),
+    in microseconds after the end of the wait for the dense parameters (the start of `hidden`)."""
+    t = np.asarray(flat, np.float64).reshape(256, 4, 3)
+    kinds = ["tails", "tail_grads", "dense_partials", "dense_params"]
+    rows = []
+    for e in range(256):
+        prev = t[(e - 1) % 256]
+        if (t[e] > 0).all() and (prev > 0).all() and t[e, 0, 0] > prev[3, 2]:
+            origin = prev[3, 2]  # the previous step's parameters have arrived: hidden begins
+            if t[e, 3, 2] - origin < 1e4:
+                rows.append((t[e] - origin).reshape(-1))
+    if not rows:
+        return {"steps": 0}
+    mean = np.mean(rows, axis=0).reshape(4, 3)
+    out = {"steps": len(rows)}
+    for k, name in enumerate(kinds):
+        out[name] = {"published": round(mean[k, 0], 2), "wait_began": round(mean[k, 1], 2), "wait_ended": round(mean[k, 2], 2)}
+    return out
+
+
 # ---------------------------------------------------------------------------
 # Arms
 
@@ -386,6 +407,10 @@ def run_ours(args) -> None:
     wall_value = time.perf_counter() - t0
     device_s = max_over_ranks(device_ms / 1e3)
     value = triples_per_call * args.steps / device_s
+
+    if os.environ.get("KGE_EXCHANGE_TRACE") and world > 1 and rank == 0:
+        print(json.dumps({"exchange_trace_us": summarise_exchange_trace(engine.debug_fetch("exchange_trace", 0, 256 * 4 * 3))}),
+              file=sys.stderr, flush=True)
 
     # -- e2e: the public command with host arrays ----------------------------
     for i in range(args.warmup):

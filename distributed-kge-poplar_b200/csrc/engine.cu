@@ -358,6 +358,11 @@ void Engine::allocate() {
     d_epoch_ = (unsigned*)device_alloc(sizeof(unsigned));
     d_xchg_words_ = (unsigned*)device_alloc(2 * XCHG_KINDS * sizeof(unsigned));
     KGE_CUDA(cudaMemset(d_xchg_words_, 0, 2 * XCHG_KINDS * sizeof(unsigned)));
+    if (const char* on = std::getenv("KGE_EXCHANGE_TRACE"); on && on[0] && on[0] != '0') {
+        const size_t bytes = (size_t)kTraceSlots * XCHG_KINDS * 3 * sizeof(unsigned long long);
+        d_xchg_trace_ = (unsigned long long*)device_alloc(bytes);
+        KGE_CUDA(cudaMemset(d_xchg_trace_, 0, bytes));
+    }
     d_status_ = (unsigned*)device_alloc(sizeof(unsigned));
     KGE_CUDA(cudaMemset(d_epoch_, 0, sizeof(unsigned)));
     KGE_CUDA(cudaMemset(d_status_, 0, sizeof(unsigned)));
@@ -740,6 +745,7 @@ ExchangeSync Engine::exchange_sync() const {
     s.rank = (int)cfg_.rank;
     s.world = (int)cfg_.world;
     s.max_spins = 8u * 1000u * 1000u;  // a second or two of 32 ns naps plus load latency
+    s.trace = d_xchg_trace_;
     return s;
 }
 
@@ -1336,6 +1342,19 @@ size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, si
     else if (what == "grad_recv") { src = b.grad_recv; count = T * D; }
     else if (what == "dense_grad") { src = b.dense_partial; count = n_dense_; }
     else if (what == "loss_last") { src = d_loss_last_ + shard; count = 1; }
+    else if (what == "exchange_trace") {
+        // microseconds since the earliest stamp, [kTraceSlots][XCHG_KINDS][published | wait began | wait ended]; 0 = no stamp
+        const size_t n = (size_t)kTraceSlots * XCHG_KINDS * 3;
+        if (!d_xchg_trace_) fail(KGE_INVALID_ARGUMENT, "kge_debug_fetch: exchange_trace needs KGE_EXCHANGE_TRACE=1 in the environment");
+        if (n > capacity) fail(KGE_INVALID_ARGUMENT, msg() << "kge_debug_fetch: 'exchange_trace' needs room for " << n << " floats");
+        KGE_CUDA(cudaStreamSynchronize(stream_));
+        std::vector<unsigned long long> stamps(n);
+        KGE_CUDA(cudaMemcpy(stamps.data(), d_xchg_trace_, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        unsigned long long base = ~0ull;
+        for (unsigned long long v : stamps) if (v && v < base) base = v;
+        for (size_t i = 0; i < n; ++i) out[i] = stamps[i] ? (float)((double)(stamps[i] - base) * 1e-3) + 1e-3f : 0.f;
+        return n;
+    }
     else fail(KGE_INVALID_ARGUMENT, msg() << "kge_debug_fetch: unknown buffer '" << what << "'");
     if (count > capacity) fail(KGE_INVALID_ARGUMENT, msg() << "kge_debug_fetch: '" << what << "' needs room for " << count << " floats");
     KGE_CUDA(cudaStreamSynchronize(stream_));

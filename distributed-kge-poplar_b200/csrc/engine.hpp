@@ -157,6 +157,7 @@ class Engine {
     bool connected_ = false;
     unsigned* d_epoch_ = nullptr;
     unsigned* d_status_ = nullptr;
+    unsigned long long* d_xchg_trace_ = nullptr;  // optional time stamps of the hand-overs (KGE_EXCHANGE_TRACE=1)
     unsigned* d_xchg_words_ = nullptr;  // [XCHG_KINDS] published epochs, [XCHG_KINDS] finished-block counters
     unsigned* d_tc_status_ = nullptr;
     // split-k workspace of the tensor-core contractions (shared by all of them: one stream)

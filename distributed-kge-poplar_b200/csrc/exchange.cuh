@@ -34,9 +34,20 @@ struct ExchangeSync {
     unsigned* status;             // device error word
     int rank, world;
     unsigned max_spins;
+    // Optional time stamps (nanoseconds of the GPU's global timer), [kTraceSlots][XCHG_KINDS][3]:
+    // when this process published an epoch, and when its first consuming block began and ended
+    // its wait for that epoch; slot = epoch % kTraceSlots.  Null: no stamps.
+    unsigned long long* trace;
 };
+constexpr int kTraceSlots = 256;
 
 #ifdef __CUDACC__
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 // Called by every thread of every block of the producing kernel once the block's writes have been
 // issued (contains __syncthreads).  `total_blocks` = blocks of the grid.
 __device__ __forceinline__ void exchange_signal(const ExchangeSync& s, int kind, unsigned total_blocks) {
@@ -52,29 +63,39 @@ __device__ __forceinline__ void exchange_signal(const ExchangeSync& s, int kind,
             *reinterpret_cast<volatile unsigned*>(&s.epochs[kind]) = epoch;
             for (int p = 0; p < s.world; ++p)
                 *reinterpret_cast<volatile unsigned*>(s.peer_flags[p] + (size_t)(1 + kind) * kMaxProcesses + s.rank) = epoch;
+            if (s.trace) s.trace[((size_t)(epoch % kTraceSlots) * XCHG_KINDS + kind) * 3 + 0] = global_timer_ns();
         }
     }
 }
 
+__device__ __forceinline__ unsigned load_acquire_system(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // Called by every thread of every block of the consuming kernel before it reads exchanged data
-// (contains __syncthreads; the block needs at least `world` threads).
+// (contains __syncthreads; the block needs at least `world` threads).  Thread t reads process t's
+// flag with acquire semantics at system scope; the barrier passes that on to the block.
 __device__ __forceinline__ void exchange_wait(const ExchangeSync& s, int kind) {
     if (s.world <= 1 || kind < 0) return;
     const int t = threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z);
     if (t < s.world) {
-        const unsigned want = *reinterpret_cast<volatile unsigned*>(&s.epochs[kind]);
-        volatile unsigned* flag = s.peer_flags[s.rank] + (size_t)(1 + kind) * kMaxProcesses + t;
-        if (*reinterpret_cast<volatile unsigned*>(s.status) == 0) {
+        const unsigned want = __ldcg(&s.epochs[kind]);
+        const bool stamp = s.trace && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        if (stamp) s.trace[((size_t)(want % kTraceSlots) * XCHG_KINDS + kind) * 3 + 1] = global_timer_ns();
+        const unsigned* flag = s.peer_flags[s.rank] + (size_t)(1 + kind) * kMaxProcesses + t;
+        if ((int)(load_acquire_system(flag) - want) < 0 && __ldcg(s.status) == 0) {
             unsigned spins = 0;
-            while ((int)(*flag - want) < 0) {
+            while ((int)(load_acquire_system(flag) - want) < 0) {
                 if (++spins > s.max_spins) {
                     atomicExch(s.status, 1u + (unsigned)t);
                     break;
                 }
-                __nanosleep(32);
+                __nanosleep(20);
             }
         }
-        __threadfence_system();
+        if (stamp) s.trace[((size_t)(want % kTraceSlots) * XCHG_KINDS + kind) * 3 + 2] = global_timer_ns();
     }
     __syncthreads();
 }
