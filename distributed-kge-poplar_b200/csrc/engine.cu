@@ -208,11 +208,12 @@ size_t Engine::arena_offset_dense(int which) const {
 }
 size_t Engine::arena_offset_shard(unsigned local, int which) const {
     const size_t row_block = round_up((size_t)cfg_.n_tail() * cfg_.d * sizeof(float), 256);
-    const size_t dense_block = round_up(n_dense_ * sizeof(float), 256);
-    const size_t per_shard = 2 * row_block + dense_block;
+    const size_t per_shard = 2 * row_block;
     const size_t base = arena_offset_dense(3) + (size_t)local * per_shard;
-    return base + (which == 0 ? 0 : which == 1 ? row_block : 2 * row_block);
+    return base + (which == 0 ? 0 : row_block);
 }
+// Receive buffer of the partial dense gradients: one slot of `dense_chunk_` floats per shard of the job.
+size_t Engine::arena_offset_dense_recv() const { return arena_offset_predict(3); }
 size_t Engine::arena_offset_predict(int which) const {
     // gathered queries [n_shard, hr, D] | result scores | result rows, each [n_local, n_shard, hr, n_best]
     const size_t queries = round_up((size_t)cfg_.n_shard * cfg_.predict_hr * cfg_.d * sizeof(float), 256);
@@ -220,7 +221,9 @@ size_t Engine::arena_offset_predict(int which) const {
     const size_t base = arena_offset_shard(n_local_, 0);
     return base + (which == 0 ? 0 : which == 1 ? queries : which == 2 ? queries + results : queries + 2 * results);
 }
-size_t Engine::arena_size() const { return arena_offset_predict(3); }
+size_t Engine::arena_size() const {
+    return arena_offset_dense_recv() + round_up((size_t)cfg_.n_shard * dense_chunk_ * sizeof(float), 256);
+}
 
 Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     int count = 0;
@@ -283,9 +286,12 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
         add_variable(proj_names[i], cfg_.f, cfg_.d, cfg_.f ? dense_bounds_[1 + i] : n_dense_);
     variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3});
 
-    const size_t chunk = round_up((n_dense_ + cfg_.world - 1) / cfg_.world, 4);
-    own_lo_ = std::min(n_dense_, chunk * cfg_.rank);
-    own_hi_ = std::min(n_dense_, own_lo_ + chunk);
+    // every process owns (reduces and updates) a slice of whole rows of the dense vector
+    const size_t dense_rows = cfg_.n_relation_type + (size_t)cfg_.n_net() * cfg_.f;
+    dense_chunk_rows_ = std::max<size_t>(1, (dense_rows + cfg_.world - 1) / cfg_.world);
+    dense_chunk_ = dense_chunk_rows_ * cfg_.d;
+    own_lo_ = std::min(n_dense_, dense_chunk_ * cfg_.rank);
+    own_hi_ = std::min(n_dense_, own_lo_ + dense_chunk_);
 
     const unsigned tiles = ceil_div(cfg_.f, 64) * ceil_div(cfg_.d, 64) * std::max(1u, cfg_.n_net());
     proj_splits_ = (int)std::min(8u, std::max(1u, ceil_div(148, std::max(1u, tiles))));
@@ -349,7 +355,8 @@ void Engine::allocate() {
         b.loss_rows = (float*)device_alloc((size_t)B * 4);
         b.tails = (float*)(arena_ + arena_offset_shard(l, 0));
         b.grad_recv = (float*)(arena_ + arena_offset_shard(l, 1));
-        b.dense_partial = (float*)(arena_ + arena_offset_shard(l, 2));
+        b.dense_partial = (float*)(arena_ + arena_offset_dense_recv()) + (size_t)(shard0_ + l) * dense_chunk_;
+        b.dense_dst = (float**)device_alloc(sizeof(float*) * cfg_.world);
         b.send_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.grad_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.predict_score_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
@@ -432,8 +439,15 @@ void Engine::build_pointer_tables() {
         KGE_CUDA(cudaMemcpy(shards_[l].predict_score_dst, pscore.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
         KGE_CUDA(cudaMemcpy(shards_[l].predict_index_dst, pindex.data(), sizeof(uint32_t*) * cfg_.n_shard, cudaMemcpyHostToDevice));
     }
+    for (unsigned l = 0; l < n_local_; ++l) {
+        // where shard shard0_ + l writes its partial dense gradient: its slot in every owner's receive buffer
+        std::vector<float*> dst(cfg_.world);
+        for (unsigned p = 0; p < cfg_.world; ++p)
+            dst[p] = (float*)(peer_arena_[p] + arena_offset_dense_recv()) + (size_t)(shard0_ + l) * dense_chunk_;
+        KGE_CUDA(cudaMemcpy(shards_[l].dense_dst, dst.data(), sizeof(float*) * cfg_.world, cudaMemcpyHostToDevice));
+    }
     for (unsigned d = 0; d < cfg_.n_shard; ++d)
-        partials[d] = (const float*)(peer_arena_[d / n_local_] + arena_offset_shard(d % n_local_, 2));
+        partials[d] = (const float*)(arena_ + arena_offset_dense_recv()) + (size_t)d * dense_chunk_;
     KGE_CUDA(cudaMemcpy(d_partials_, partials.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
     std::vector<float*> replicas(cfg_.world);
     std::vector<unsigned*> flags(cfg_.world);
@@ -983,11 +997,11 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_partial, sync, -1)));
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
             else
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_partial, sync, -1)));
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
         }
     }
     KGE_CUDA(cudaGetLastError());
@@ -1029,8 +1043,10 @@ void Engine::launch_one_step(unsigned step) {
                 g.B = tc::make_operand(net ? b.d_hid_t : b.d_hid_h, (long long)D * 4, false, true);
                 g.M = (int)F; g.N = (int)D; g.K = (int)R; g.k_per_split = proj_rows_per_split_;
                 g.epilogue = tc::EPI_STORE;
-                // straight into this shard's partial dense gradient, behind the relation rows
-                g.out = b.dense_partial + (size_t)n_rel * D + (size_t)net * proj_elems_; g.ldc = D; g.block_rows = 1;
+                // straight into this shard's partial dense gradient, behind the relation rows: row m of
+                // the projection is row n_rel + net * F + m of the dense vector, and goes to its owner
+                g.out = nullptr; g.out_blocks = b.dense_dst; g.block_rows = (int)dense_chunk_rows_;
+                g.block_row_offset = (int)(n_rel + net * F); g.ldc = D;
             }
             launch_tc("projection_bwd", nets, (int)cfg_.n_net(),
                       tc_splits(cfg_.n_net() * ceil_div(F, 128) * ceil_div(D, 64), R), cfg_.feature_type == ST_F16, false,
@@ -1055,12 +1071,12 @@ void Engine::launch_one_step(unsigned step) {
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
-                                                proj_elems_, b.dense_partial, sync, (int)XCHG_DENSE_PARTIALS)));
+                                                proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, (int)XCHG_DENSE_PARTIALS)));
             else
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
-                                                proj_elems_, b.dense_partial, sync, (int)XCHG_DENSE_PARTIALS)));
+                                                proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, (int)XCHG_DENSE_PARTIALS)));
         }
     }
     KGE_CUDA(cudaGetLastError());
@@ -1205,7 +1221,7 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
     }
     // Optimiser state lives with the process that owns the slice (src/poplar_kge.cpp:329-339):
     // collect each owner's part through its mapped arena.
-    const size_t chunk = round_up((n_dense_ + cfg_.world - 1) / cfg_.world, 4);
+    const size_t chunk = dense_chunk_;  // the slice each process owns
     for (unsigned p = 0; p < cfg_.world; ++p) {
         const size_t lo = std::max(var->offset, std::min(n_dense_, chunk * p));
         const size_t hi = std::min(var->offset + count, std::min(n_dense_, chunk * (p + 1)));
@@ -1340,7 +1356,10 @@ size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, si
     else if (what == "d_pred") { src = b.d_pred; count = B * D; }
     else if (what == "d_hidden") { src = b.d_hid_h; count = R * D; }
     else if (what == "grad_recv") { src = b.grad_recv; count = T * D; }
-    else if (what == "dense_grad") { src = b.dense_partial; count = n_dense_; }
+    else if (what == "dense_grad") {
+        if (cfg_.world > 1) fail(KGE_INVALID_ARGUMENT, "kge_debug_fetch: 'dense_grad' is spread over the processes; fetch it with one process");
+        src = b.dense_partial; count = n_dense_;
+    }
     else if (what == "loss_last") { src = d_loss_last_ + shard; count = 1; }
     else if (what == "exchange_trace") {
         // microseconds since the earliest stamp, [kTraceSlots][XCHG_KINDS][published | wait began | wait ended]; 0 = no stamp

@@ -100,6 +100,7 @@ class Engine {
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
         float** grad_dst = nullptr;  // device table [n_shard]
+        float** dense_dst = nullptr;  // device table [world]: this shard's slot in each owner's receive buffer
         float** predict_score_dst = nullptr;     // device table [n_shard]: where each asking shard's results go
         uint32_t** predict_index_dst = nullptr;  // device table [n_shard]
         unsigned long long* topk_state = nullptr;
@@ -113,6 +114,7 @@ class Engine {
     size_t arena_offset_dense(int which) const;
     size_t arena_offset_shard(unsigned local, int which) const;
     size_t arena_offset_predict(int which) const;
+    size_t arena_offset_dense_recv() const;
     size_t arena_size() const;
 
     // commands
@@ -174,7 +176,7 @@ class Engine {
     float dense_lr_mod_[3] = {1.f, 1.f, 1.f};
     float entity_lr_mod_ = 1.f;
     float *dense_ = nullptr, *dense_m_ = nullptr, *dense_v_ = nullptr;
-    size_t own_lo_ = 0, own_hi_ = 0;
+    size_t own_lo_ = 0, own_hi_ = 0, dense_chunk_ = 0, dense_chunk_rows_ = 1;
     std::vector<Variable> variables_;
     unsigned long long step_ = 0;
     int proj_splits_ = 1, proj_rows_per_split_ = 0;

@@ -1114,7 +1114,9 @@ k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t*
 }
 
 // This shard's contribution to the dense gradients, laid out like the dense parameter
-// vector: relation table | projection(s).  Relation rows are the segment sums of the
+// vector: relation table | projection(s), and written slice by slice into the memory of the
+// process that owns (reduces and updates) each slice of `chunk_rows` rows: dense_dst[owner] is
+// this shard's slot in that process's receive buffer.  Relation rows are the segment sums of the
 // per-triple relation gradients (backward of the gather at src/poplar_kge.cpp:489);
 // projection entries sum the split partials of k_projection_bwd in split order.
 constexpr int kRelationLanes = 8;
@@ -1124,7 +1126,7 @@ __global__ void __launch_bounds__(64 * kRelationLanes)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
-                float* __restrict__ dense_partial, ExchangeSync sync, int signal_kind) {
+                float* const* __restrict__ dense_dst, int chunk_rows, ExchangeSync sync, int signal_kind) {
     grid_dependency_sync();
     __shared__ float part[kRelationLanes][64 * V];
     __shared__ uint32_t s_perm[64 * kRelationLanes];
@@ -1134,8 +1136,11 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         // ... (four loads in flight) and the lanes' partial sums are added in lane order.
         const int rho = blockIdx.x, col = threadIdx.x & 63, lane = threadIdx.x >> 6;
         const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
+        // the row goes to the process that owns this slice of the dense vector
+        const int owner = rho / chunk_rows;
+        float* __restrict__ dst_row = dense_dst[owner] + (size_t)(rho - owner * chunk_rows) * D;
         if (q0 == q1) {
-            for (int c = threadIdx.x; c < D; c += blockDim.x) dense_partial[(size_t)rho * D + c] = 0.f;
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dst_row[c] = 0.f;
             exchange_signal(sync, signal_kind, gridDim.x);
             return;
         }
@@ -1179,14 +1184,14 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
                     float total = part[0][col * V + u];
 #pragma unroll
                     for (int l = 1; l < kRelationLanes; ++l) total += part[l][col * V + u];
-                    dense_partial[(size_t)rho * D + c + u] = total;
+                    dst_row[c + u] = total;
                 }
             }
         }
         exchange_signal(sync, signal_kind, gridDim.x);
         return;
     }
-    const size_t rel_elems = (size_t)n_rel * D;
+    const size_t rel_elems = (size_t)n_rel * D, chunk = (size_t)chunk_rows * D;
     const size_t total = (size_t)n_net * proj_elems;
     const size_t first = ((size_t)blockIdx.x - n_rel) * blockDim.x + threadIdx.x;
     const size_t stride = ((size_t)gridDim.x - n_rel) * blockDim.x;
@@ -1194,7 +1199,8 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         const size_t net = pe / proj_elems, idx = pe - net * proj_elems;
         float g = 0.f;
         for (int z = 0; z < splits; ++z) g += proj_partial[(net * splits + z) * proj_elems + idx];
-        dense_partial[rel_elems + pe] = g;
+        const size_t e = rel_elems + pe, owner = e / chunk;
+        dense_dst[owner][e - owner * chunk] = g;
     }
     exchange_signal(sync, signal_kind, gridDim.x);
 }
@@ -1205,7 +1211,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
 // (the all-gather on next use, :341-348).  Pointer tables live in device memory; entries
 // may point into peers' memory.
 struct DenseUpdateArgs {
-    const float* const* partials;  // [n_partial]
+    const float* const* partials;  // [n_partial] the shards' slots in this process's receive buffer, element lo first
     int n_partial;
     float* const* replicas;  // [n_replica] dense parameter vectors
     int n_replica;
@@ -1225,9 +1231,9 @@ __device__ __forceinline__ float dense_adam(float x, float g, float& m, float& v
     return x - alpha * (m / (sqrtf(v) + ap.epsilon) + ap.weight_decay * x);
 }
 
-// With more than one process the partial gradients are read from, and the new values written to,
-// the other processes' memory: four elements per access, and the reads of all partials of an
-// element group are issued before the first is used.
+// The shards' partial gradients of the owned slice have been written into this process's
+// receive buffer by their producers; the new values are written to every process's copy of the
+// parameters (posted stores over NVLink).  Four elements per access.
 static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, int self) {
     grid_dependency_sync();
     exchange_wait(a.sync, XCHG_DENSE_PARTIALS);  // every process's partial gradients are complete
@@ -1239,7 +1245,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
             float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
             for (int s = 0; s < a.n_partial; ++s) {
-                const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + e);
+                const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + (e - a.lo));
                 g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
             }
             const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
@@ -1258,7 +1264,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
         for (size_t e = a.lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < a.hi;
              e += (size_t)gridDim.x * blockDim.x) {
             float g = 0.f;
-            for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][e];
+            for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][e - a.lo];
             const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
             const float alpha = base_alpha * a.lr_modifier[p];
             float m = a.adam_m[e], v = a.adam_v[e];

@@ -62,10 +62,11 @@ struct GemmArgs {
     int k_per_split;            // k range of blockIdx.z is [z * k_per_split, min(K, (z + 1) * k_per_split))
     int epilogue;
     // output: row m at out + m * ldc (+ blockIdx.z * split_stride), or, when out_blocks is set, at
-    // out_blocks[m / block_rows] + (m % block_rows) * ldc (rows routed to their owning shard)
+    // out_blocks[(m + block_row_offset) / block_rows] + ((m + block_row_offset) % block_rows) * ldc (rows routed to their owners)
     float* out;
     float* const* out_blocks;
     int block_rows;
+    int block_row_offset;  // with out_blocks: row m belongs to block (m + offset) / block_rows
     long long ldc;
     long long split_stride;
     // EPI_ADD_TABLE_VALUE: value row of output row m is x_base + (x_gather ? x_gather[m] : m) * x_row_stride_bytes
@@ -373,8 +374,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
     if (m < g.M) {
         float* out_row;
         if (g.out_blocks) {
-            const int blk = m / g.block_rows;
-            out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+            const int blk = (m + g.block_row_offset) / g.block_rows;
+            out_row = g.out_blocks[blk] + (size_t)(m + g.block_row_offset - blk * g.block_rows) * g.ldc;
         } else {
             out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
         }
@@ -601,8 +602,8 @@ __device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, 
     }
     float* out_row;
     if (g.out_blocks) {
-        const int blk = m / g.block_rows;
-        out_row = g.out_blocks[blk] + (size_t)(m - blk * g.block_rows) * g.ldc;
+        const int blk = (m + g.block_row_offset) / g.block_rows;
+        out_row = g.out_blocks[blk] + (size_t)(m + g.block_row_offset - blk * g.block_rows) * g.ldc;
     } else {
         out_row = out_base + (size_t)m * g.ldc;
     }
