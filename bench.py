@@ -213,6 +213,7 @@ class ClockSampler:
 
 
 def step_traffic(n_shard: int) -> dict:
+    """Algorithmic bytes per launch, by the name the engine times the kernel under."""
     B, T = BATCH, BATCH + NEGATIVES
     R = B + T
     n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
@@ -229,11 +230,36 @@ def step_traffic(n_shard: int) -> dict:
         # reads the lookup gradients and value/m/sqrt(v) of R rows, writes them back + hidden grads
         "entity_update": (B + T) * D * 4 + 2 * R * row_state + R * D * 4,
         "projection_bwd": R * row_feat + R * D * 4 + F * D * 4,
-        "dense_partial": (n_rel + F) * D * 4 + B * D * 4,
+        "dense_partial": n_rel * D * 4 + B * D * 4,
         "dense_update": 5 * (n_rel + F) * D * 4,
         # the step as the reference's host sees it: gather R whole rows, scatter their state back
         "step": R * (row_state + row_feat) + R * row_state,
     }
+
+
+def step_flops() -> dict:
+    """Algorithmic floating-point operations per launch of the kernels that are bound by arithmetic:
+    2 per multiply-add of the contraction as the reference states it (the three TF32 products that
+    make up one fp32 product on the tensor cores count once), 3 per pair-element of the L2 distance."""
+    B, T = BATCH, BATCH + NEGATIVES
+    R = B + T
+    return {
+        "hidden": 2 * R * F * D,
+        "projection_bwd": 2 * R * F * D,
+        "score_bwd": 2 * (2 * B * T * D),
+        "score": 3 * B * T * D,
+    }
+
+
+# Which unit bounds each kernel (the rest move bytes): the contractions run on the tensor cores,
+# the direct L2 distance on the FP32 pipe.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
+# (small-table case; the step's kernels touch the same rows whatever the table size).
+NCU_TRAFFIC: dict = {}
+
+TENSOR_KERNELS = ("hidden", "projection_bwd", "score_bwd")
+FP32_KERNELS = ("score",)
+FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # FMA lanes x 2 x the maximum SM clock: nominal, not measured
 
 
 def summarise_exchange_trace(flat: np.ndarray) -> dict:
@@ -261,11 +287,14 @@ def summarise_exchange_trace(flat: np.ndarray) -> dict:
 # Arms
 
 
-def measured_peak_gbs() -> tuple:
+def measured_peaks() -> dict:
+    """HBM copy bandwidth and dense bf16 tensor throughput measured on this pool's B200s (the sustained
+    figure: the kernels here are timed inside a long step), or the stated fallbacks."""
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
-        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        peaks = json.loads(path.read_text())
+        return {"hbm_gbs": float(peaks["hbm_gbs"]), "tensor_tflops": float(peaks["bf16_tflops_sustained"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tensor_tflops": 1400.0, "source": "fallback"}
 
 
 def cpu_baseline(seconds_target: float = 12.0, n_shard: int = 1, rows: int = 200_001) -> dict:
@@ -437,8 +466,10 @@ def run_ours(args) -> None:
         if world > 1:
             dist.destroy_process_group()
         return
-    peak, peak_kind = measured_peak_gbs()
+    peaks = measured_peaks()
+    peak = peaks["hbm_gbs"]
     traffic = step_traffic(n_shard)
+    flops = step_flops()
     total_kernel_ms = sum(ms for ms, _ in times.values())
     kernels = {}
     for name, (ms, count) in sorted(times.items(), key=lambda kv: -kv[1][0]):
@@ -447,10 +478,26 @@ def run_ours(args) -> None:
         if name in traffic:
             entry["algorithmic_bytes"] = traffic[name]
             entry["gb_per_s"] = traffic[name] / (per_launch_us * 1e-6) / 1e9
+        if name in flops:
+            entry["algorithmic_flops"] = flops[name]
+            entry["tflop_per_s"] = flops[name] / (per_launch_us * 1e-6) / 1e12
         kernels[name] = entry
     dominant = next(iter(kernels))
     dom = kernels[dominant]
-    achieved = dom.get("gb_per_s", 0.0)
+    if dominant in TENSOR_KERNELS:
+        roofline = {"bound": "tensor", "kernel": dominant, "achieved": dom["tflop_per_s"], "peak": peaks["tensor_tflops"],
+                    "unit": "TFLOP/s", "frac": dom["tflop_per_s"] / peaks["tensor_tflops"], "peak_source": peaks["source"],
+                    "peak_note": "dense bf16 sustained; the kernel computes fp32 products as three TF32 products",
+                    "algorithmic_flops_per_launch": dom["algorithmic_flops"]}
+    elif dominant in FP32_KERNELS:
+        roofline = {"bound": "fp32", "kernel": dominant, "achieved": dom["tflop_per_s"], "peak": FP32_PEAK_TFLOPS,
+                    "unit": "TFLOP/s", "frac": dom["tflop_per_s"] / FP32_PEAK_TFLOPS, "peak_source": "nominal",
+                    "algorithmic_flops_per_launch": dom["algorithmic_flops"]}
+    else:
+        achieved = dom.get("gb_per_s", 0.0)
+        roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_source": peaks["source"],
+                    "algorithmic_bytes_per_launch": dom.get("algorithmic_bytes")}
     step_us = 1e6 * device_s / (args.steps * device_steps)
     line = {
         "metric": "train_triples_per_sec", "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
@@ -460,9 +507,7 @@ def run_ours(args) -> None:
         "e2e": {"value": triples_per_call * args.steps / e2e_s, "unit": "triples/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": loss.nbytes, "ms_per_step": 1e3 * e2e_s / args.steps},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": peak_kind, "traffic": None,
-                     "algorithmic_bytes_per_launch": dom.get("algorithmic_bytes"), "us_per_launch": dom["us_per_launch"],
+        "roofline": {**roofline, "traffic": NCU_TRAFFIC.get(dominant), "us_per_launch": dom["us_per_launch"],
                      "step_us": step_us, "step_hbm_gb_per_s": traffic["step"] / (step_us * 1e-6) / 1e9,
                      "step_frac_of_hbm": traffic["step"] / (step_us * 1e-6) / 1e9 / peak},
         "kernels": kernels,

@@ -95,9 +95,10 @@ __device__ __forceinline__ void exchange_wait(const ExchangeSync& s, int kind) {
                 __nanosleep(20);
             }
         }
-        if (stamp) s.trace[((size_t)(want % kTraceSlots) * XCHG_KINDS + kind) * 3 + 2] = global_timer_ns();
     }
     __syncthreads();
+    if (s.trace && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)  // all processes' flags have arrived
+        s.trace[((size_t)(__ldcg(&s.epochs[kind]) % kTraceSlots) * XCHG_KINDS + kind) * 3 + 2] = global_timer_ns();
 }
 
 // The two halves as kernels of their own, for producers and consumers that have no fused form.
