@@ -298,6 +298,9 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     proj_rows_per_split_ = (int)round_up(ceil_div(cfg_.n_remote(), proj_splits_), 32);
 
     KGE_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    KGE_CUDA(cudaStreamCreateWithFlags(&side_stream_, cudaStreamNonBlocking));
+    KGE_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
+    for (cudaEvent_t& e : ev_join_) KGE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     KGE_CUDA(cudaEventCreate(&ev_begin_));
     KGE_CUDA(cudaEventCreate(&ev_end_));
     allocate();
@@ -320,6 +323,9 @@ Engine::~Engine() {
     if (pinned_) cudaFreeHost(pinned_);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
     if (ev_end_) cudaEventDestroy(ev_end_);
+    if (ev_fork_) cudaEventDestroy(ev_fork_);
+    for (cudaEvent_t e : ev_join_) if (e) cudaEventDestroy(e);
+    if (side_stream_) cudaStreamDestroy(side_stream_);
     if (stream_) cudaStreamDestroy(stream_);
 }
 
@@ -340,7 +346,7 @@ void Engine::allocate() {
         ShardBuffers& b = shards_[l];
         b.table = (uint8_t*)device_alloc(table_bytes);
         KGE_CUDA(cudaMemset(b.table, 0, table_bytes));
-        b.rows_c = (uint8_t*)device_alloc((size_t)R * layout_.row_bytes);
+        for (uint8_t*& rows : b.rows_c2) rows = (uint8_t*)device_alloc((size_t)R * layout_.row_bytes);
         b.hid_h = (float*)device_alloc((size_t)R * D * 4);
         b.hid_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : b.hid_h;
         b.pred = (float*)device_alloc((size_t)B * D * 4);
@@ -718,21 +724,40 @@ bool dependent_launch_enabled() {
 }
 
 void Engine::launch_steps() {
-    launch_gather(0);
+    launch_gather(0, stream_);
     for (unsigned step = 0; step < cfg_.n_step; ++step) launch_one_step(step);
 }
 
-// The step's rows, gathered into the compact copy every later kernel of the step reads.  The
-// gather of step s + 1 is queued inside step s, behind the last reader of the copy and ahead of
-// the dense update, so that it runs while the partial dense gradients travel.
-void Engine::launch_gather(unsigned step) {
+// The step's rows, gathered into the compact copy every later kernel of the step reads (two
+// copies, for even and odd steps).  The gather of step s + 1 needs only the rows step s has
+// updated, so it runs beside the projection gradient and the dense update of step s.
+void Engine::launch_gather(unsigned step, cudaStream_t stream) {
     const unsigned R = cfg_.n_remote();
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
         const uint32_t* remote = d_remote_ + ((size_t)l * cfg_.n_step + step) * R;
-        KGE_LAUNCH("gather", KGE_CUDA(launch_dependent(k_gather_step_rows, dim3(ceil_div(R, 8)), dim3(256), 0, stream_, b.table,
-                                                       layout_.row_bytes, remote, (int)R, b.rows_c)));
+        KGE_LAUNCH("gather", KGE_CUDA(launch_dependent(k_gather_step_rows, dim3(ceil_div(R, 8)), dim3(256), 0, stream, b.table,
+                                                       layout_.row_bytes, remote, (int)R, b.rows_c2[step & 1])));
     }
+}
+
+// Fork: what is launched on the returned stream starts after everything queued on the main stream
+// so far.  While per-kernel timing is on, everything stays on the main stream.
+cudaStream_t Engine::side_begin() {
+    if (kernel_timing_) return stream_;
+    KGE_CUDA(cudaEventRecord(ev_fork_, stream_));
+    KGE_CUDA(cudaStreamWaitEvent(side_stream_, ev_fork_, 0));
+    return side_stream_;
+}
+// ... the side work is complete here ...
+void Engine::side_end(int which) {
+    if (kernel_timing_) return;
+    KGE_CUDA(cudaEventRecord(ev_join_[which], side_stream_));
+}
+// ... and the main stream waits for it here.
+void Engine::side_join(int which) {
+    if (kernel_timing_) return;
+    KGE_CUDA(cudaStreamWaitEvent(stream_, ev_join_[which], 0));
 }
 
 void Engine::launch_barrier() {
@@ -889,18 +914,19 @@ void Engine::launch_one_step(unsigned step) {
     // 1./2. hidden rows, lookups, send half of the exchange
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
+        uint8_t* rows_c = b.rows_c2[step & 1];
         if (cfg_.tensor_cores && F > 0) {
             // hidden = value + feature . W on the tensor cores: A = gathered feature rows, B = W stored [F, D]
             tc::GemmArgs nets[2] = {};
             const int n_nets = two_nets ? 2 : 1;
             for (int net = 0; net < n_nets; ++net) {
                 tc::GemmArgs& g = nets[net];
-                g.A = tc::make_operand(b.rows_c + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, false);
+                g.A = tc::make_operand(rows_c + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, false);
                 g.B = tc::make_operand(net ? W1 : W0, (long long)D * 4, false, true);
                 g.M = (int)R; g.N = (int)D; g.K = (int)F; g.k_per_split = (int)round_up(F, 32);
                 g.epilogue = tc::EPI_ADD_TABLE_VALUE;
                 g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
-                g.x_base = b.rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = nullptr;
+                g.x_base = rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = nullptr;
                 g.x_is_half = cfg_.state_type == ST_F16;
             }
             // the projection was updated by the processes that own its slices
@@ -910,7 +936,7 @@ void Engine::launch_one_step(unsigned step) {
             launch_exchange_wait(XCHG_DENSE_PARAMS);
             dim3 grid(ceil_div(R, 64), ceil_div(D, 64), two_nets ? 2 : 1);
             KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, KGE_CUDA(launch_dependent(k_hidden<ST, FT>, dim3(grid), dim3(256), 0, stream_, 
-                                                            b.rows_c, layout_, nullptr, 0u, (int)R, W0, W1, b.hid_h, b.hid_t))));
+                                                            rows_c, layout_, nullptr, 0u, (int)R, W0, W1, b.hid_h, b.hid_t))));
         }
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
@@ -991,24 +1017,31 @@ void Engine::launch_one_step(unsigned step) {
         if (cfg_.score_fn != SCORE_TRANSE)
             KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
                                                                      b.d_relrow, (int)D, cfg_.score_fn)));
-        if (proj_direct) {
-            // the relation gradients need nothing from other processes: they are summed while the tail gradients travel
+    }
+    KGE_CUDA(cudaGetLastError());
+
+    if (proj_direct) {
+        // The relation gradients depend on the score backward only: they are summed beside the entity update.
+        cudaStream_t side = side_begin();
+        for (unsigned l = 0; l < n_local_; ++l) {
+            ShardBuffers& b = shards_[l];
             const size_t sidx = (size_t)l * cfg_.n_step + step;
             if (vec)
-                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, side,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
             else
-                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, side,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
         }
+        side_end(0);
     }
-    KGE_CUDA(cudaGetLastError());
 
     // 5b. segment sums + row-wise Adam; projection and relation gradients of this shard
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
+        uint8_t* rows_c = b.rows_c2[step & 1];
         const size_t sidx = (size_t)l * cfg_.n_step + step;
         const uint32_t* remote = step_ptr(d_remote_, l, R);
         const uint32_t* perm = d_ent_perm_ + sidx * (B + T);
@@ -1018,28 +1051,42 @@ void Engine::launch_one_step(unsigned step) {
         if (cfg_.state_type == ST_F32) {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
-                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
-                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
         } else {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
-                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
-                                                b.table, b.rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
+                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
         }
+    }
+    KGE_CUDA(cudaGetLastError());
+    if (proj_direct) side_join(0);  // the relation rows of the partial dense gradient are in place
+    const bool gather_ahead = step + 1 < cfg_.n_step;
+    if (gather_ahead) {
+        // the next step's rows: needs only the rows just updated, runs beside the rest of this step
+        cudaStream_t side = side_begin();
+        launch_gather(step + 1, side);
+        side_end(1);
+    }
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        uint8_t* rows_c = b.rows_c2[step & 1];
+        const size_t sidx = (size_t)l * cfg_.n_step + step;
         if (F > 0 && cfg_.tensor_cores) {
             // d W = feature^T . d_hidden: the gathered rows are the k index of both operands
             tc::GemmArgs nets[2] = {};
             for (unsigned net = 0; net < cfg_.n_net(); ++net) {
                 tc::GemmArgs& g = nets[net];
-                g.A = tc::make_operand(b.rows_c + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, true);
+                g.A = tc::make_operand(rows_c + layout_.off_feat, layout_.row_bytes, cfg_.feature_type == ST_F16, true);
                 g.B = tc::make_operand(net ? b.d_hid_t : b.d_hid_h, (long long)D * 4, false, true);
                 g.M = (int)F; g.N = (int)D; g.K = (int)R; g.k_per_split = proj_rows_per_split_;
                 g.epilogue = tc::EPI_STORE;
@@ -1056,11 +1103,11 @@ void Engine::launch_one_step(unsigned step) {
             const float* dh1 = two_nets ? b.d_hid_t : b.d_hid_h;
             if (cfg_.feature_type == ST_F32)
                 KGE_LAUNCH("projection_bwd", KGE_CUDA(launch_dependent(k_projection_bwd<float>, dim3(grid), dim3(256), 0, stream_, 
-                                                 b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
+                                                 rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
                                                  proj_rows_per_split_, b.proj_partial)));
             else
                 KGE_LAUNCH("projection_bwd", KGE_CUDA(launch_dependent(k_projection_bwd<__half>, dim3(grid), dim3(256), 0, stream_, 
-                                                 b.rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
+                                                 rows_c, layout_, nullptr, (int)R, b.d_hid_h, dh1, proj_splits_,
                                                  proj_rows_per_split_, b.proj_partial)));
         }
         if (!proj_direct) {
@@ -1080,7 +1127,6 @@ void Engine::launch_one_step(unsigned step) {
         }
     }
     KGE_CUDA(cudaGetLastError());
-    if (step + 1 < cfg_.n_step) launch_gather(step + 1);
 
     // 5c. dense parameters: reduce over shards, Adam on the owned slice, publish.  Every process
     // launches it, also one that owns nothing, since the kernel carries two hand-overs.
@@ -1104,6 +1150,7 @@ void Engine::launch_one_step(unsigned step) {
         KGE_LAUNCH("dense_update", KGE_CUDA(launch_dependent(k_dense_update, dim3(std::max(1u, blocks)), dim3(256), 0, stream_, da, (int)cfg_.rank)));
     }
     KGE_CUDA(cudaGetLastError());
+    if (gather_ahead) side_join(1);
 }
 
 // ---------------------------------------------------------------------------

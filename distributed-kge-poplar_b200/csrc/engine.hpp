@@ -93,7 +93,7 @@ class Engine {
    private:
     struct ShardBuffers {
         uint8_t* table = nullptr;
-        uint8_t* rows_c = nullptr;  // the step's gathered rows, table row layout, [R]
+        uint8_t* rows_c2[2] = {nullptr, nullptr};  // the gathered rows of even / odd steps, table row layout, [R]
         float *hid_h = nullptr, *hid_t = nullptr, *pred = nullptr, *raw = nullptr, *coeff = nullptr;
         float *d_pred = nullptr, *d_head = nullptr, *d_relrow = nullptr;
         float *d_hid_h = nullptr, *d_hid_t = nullptr, *proj_partial = nullptr, *loss_rows = nullptr;
@@ -132,7 +132,7 @@ class Engine {
     ExchangeSync exchange_sync() const;
     void launch_exchange_wait(int kind);
     void launch_exchange_signal(int kind);
-    void launch_gather(unsigned step);
+    void launch_gather(unsigned step, cudaStream_t stream);
     void launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum,
                    int wait_kind = -1, int signal_kind = -1);
     void check_device_status();
@@ -149,6 +149,13 @@ class Engine {
     AdamParams adam_{};
     unsigned n_local_ = 0, shard0_ = 0;
     cudaStream_t stream_ = nullptr;
+    // Work that does not lie on the step's chain of dependent kernels runs beside it: forked from and
+    // joined to the main stream with events (graph edges under capture).
+    cudaStream_t side_stream_ = nullptr;
+    cudaEvent_t ev_fork_ = nullptr, ev_join_[2] = {nullptr, nullptr};
+    cudaStream_t side_begin();
+    void side_end(int which);
+    void side_join(int which);
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
     std::vector<void*> allocations_;
     std::vector<ShardBuffers> shards_;
