@@ -255,7 +255,8 @@ def step_flops() -> dict:
 # the direct L2 distance on the FP32 pipe.
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
 # (small-table case; the step's kernels touch the same rows whatever the table size).
-NCU_TRAFFIC: dict = {}
+NCU_TRAFFIC: dict = {"hidden": 4_133_632, "projection_bwd": 3_347_200, "score_bwd": 2_953_728, "score": 1_329_408,
+                     "entity_update": 3_810_560, "loss": 1_611_776}
 
 TENSOR_KERNELS = ("hidden", "projection_bwd", "score_bwd")
 FP32_KERNELS = ("score",)
