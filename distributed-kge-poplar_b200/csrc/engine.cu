@@ -783,7 +783,8 @@ ExchangeSync Engine::exchange_sync() const {
     s.status = d_status_;
     s.rank = (int)cfg_.rank;
     s.world = (int)cfg_.world;
-    s.max_spins = 8u * 1000u * 1000u;  // a second or two of 32 ns naps plus load latency
+    s.max_spins = 1u << 28;
+    s.timeout_ns = 2000ull * 1000ull * 1000ull;  // two seconds
     s.trace = d_xchg_trace_;
     return s;
 }

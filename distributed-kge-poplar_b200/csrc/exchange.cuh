@@ -33,7 +33,8 @@ struct ExchangeSync {
     unsigned* counters;           // [XCHG_KINDS] blocks of the publishing kernel that have finished
     unsigned* status;             // device error word
     int rank, world;
-    unsigned max_spins;
+    unsigned max_spins;            // a wait gives up after this many polls ...
+    unsigned long long timeout_ns; // ... or this long, whichever comes first
     // Optional time stamps (nanoseconds of the GPU's global timer), [kTraceSlots][XCHG_KINDS][3]:
     // when this process published an epoch, and when its first consuming block began and ended
     // its wait for that epoch; slot = epoch % kTraceSlots.  Null: no stamps.
@@ -86,9 +87,11 @@ __device__ __forceinline__ void exchange_wait(const ExchangeSync& s, int kind) {
         if (stamp) s.trace[((size_t)(want % kTraceSlots) * XCHG_KINDS + kind) * 3 + 1] = global_timer_ns();
         const unsigned* flag = s.peer_flags[s.rank] + (size_t)(1 + kind) * kMaxProcesses + t;
         if ((int)(load_acquire_system(flag) - want) < 0 && __ldcg(s.status) == 0) {
+            // bounded by the GPU's global timer (and by a count, should the timer not advance)
+            const unsigned long long deadline = global_timer_ns() + s.timeout_ns;
             unsigned spins = 0;
             while ((int)(load_acquire_system(flag) - want) < 0) {
-                if (++spins > s.max_spins) {
+                if (++spins > s.max_spins || ((spins & 63u) == 0 && global_timer_ns() > deadline)) {
                     atomicExch(s.status, 1u + (unsigned)t);
                     break;
                 }
