@@ -299,6 +299,9 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
 
     KGE_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     KGE_CUDA(cudaStreamCreateWithFlags(&side_stream_, cudaStreamNonBlocking));
+    // Which work runs beside the step's chain: bit 0 the relation gradients, bit 1 the next step's gather.
+    side_streams_ = cfg_.world == 1 ? 3u : 0u;
+    if (const char* v = std::getenv("KGE_SIDE_STREAMS")) side_streams_ = (unsigned)std::atoi(v) & 3u;
     KGE_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
     for (cudaEvent_t& e : ev_join_) KGE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     KGE_CUDA(cudaEventCreate(&ev_begin_));
@@ -744,19 +747,19 @@ void Engine::launch_gather(unsigned step, cudaStream_t stream) {
 // Fork: what is launched on the returned stream starts after everything queued on the main stream
 // so far.  While per-kernel timing is on, everything stays on the main stream.
 cudaStream_t Engine::side_begin() {
-    if (kernel_timing_) return stream_;
+    if (kernel_timing_ || !side_streams_) return stream_;
     KGE_CUDA(cudaEventRecord(ev_fork_, stream_));
     KGE_CUDA(cudaStreamWaitEvent(side_stream_, ev_fork_, 0));
     return side_stream_;
 }
 // ... the side work is complete here ...
 void Engine::side_end(int which) {
-    if (kernel_timing_) return;
+    if (kernel_timing_ || !side_streams_) return;
     KGE_CUDA(cudaEventRecord(ev_join_[which], side_stream_));
 }
 // ... and the main stream waits for it here.
 void Engine::side_join(int which) {
-    if (kernel_timing_) return;
+    if (kernel_timing_ || !side_streams_) return;
     KGE_CUDA(cudaStreamWaitEvent(stream_, ev_join_[which], 0));
 }
 
@@ -1023,6 +1026,8 @@ void Engine::launch_one_step(unsigned step) {
 
     if (proj_direct) {
         // The relation gradients depend on the score backward only: they are summed beside the entity update.
+        const unsigned saved = side_streams_;
+        side_streams_ = saved & 1u;
         cudaStream_t side = side_begin();
         for (unsigned l = 0; l < n_local_; ++l) {
             ShardBuffers& b = shards_[l];
@@ -1037,6 +1042,7 @@ void Engine::launch_one_step(unsigned step) {
                                                 (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
         }
         side_end(0);
+        side_streams_ = saved;
     }
 
     // 5b. segment sums + row-wise Adam; projection and relation gradients of this shard
@@ -1051,28 +1057,29 @@ void Engine::launch_one_step(unsigned step) {
         const float* alpha = d_step_size_ + step;
         if (cfg_.state_type == ST_F32) {
             if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
             else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
         } else {
             if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
             else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_, 
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
         }
     }
     KGE_CUDA(cudaGetLastError());
-    if (proj_direct) side_join(0);  // the relation rows of the partial dense gradient are in place
+    if (proj_direct && (side_streams_ & 1u)) side_join(0);  // the relation rows of the partial dense gradient are in place
     const bool gather_ahead = step + 1 < cfg_.n_step;
-    if (gather_ahead) {
+    const bool gather_beside = gather_ahead && (side_streams_ & 2u);
+    if (gather_beside) {
         // the next step's rows: needs only the rows just updated, runs beside the rest of this step
         cudaStream_t side = side_begin();
         launch_gather(step + 1, side);
@@ -1128,6 +1135,7 @@ void Engine::launch_one_step(unsigned step) {
         }
     }
     KGE_CUDA(cudaGetLastError());
+    if (gather_ahead && !gather_beside) launch_gather(step + 1, stream_);  // runs while the partial dense gradients travel
 
     // 5c. dense parameters: reduce over shards, Adam on the owned slice, publish.  Every process
     // launches it, also one that owns nothing, since the kernel carries two hand-overs.
@@ -1151,7 +1159,7 @@ void Engine::launch_one_step(unsigned step) {
         KGE_LAUNCH("dense_update", KGE_CUDA(launch_dependent(k_dense_update, dim3(std::max(1u, blocks)), dim3(256), 0, stream_, da, (int)cfg_.rank)));
     }
     KGE_CUDA(cudaGetLastError());
-    if (gather_ahead) side_join(1);
+    if (gather_beside) side_join(1);
 }
 
 // ---------------------------------------------------------------------------

@@ -152,6 +152,7 @@ class Engine {
     // Work that does not lie on the step's chain of dependent kernels runs beside it: forked from and
     // joined to the main stream with events (graph edges under capture).
     cudaStream_t side_stream_ = nullptr;
+    unsigned side_streams_ = 0;
     cudaEvent_t ev_fork_ = nullptr, ev_join_[2] = {nullptr, nullptr};
     cudaStream_t side_begin();
     void side_end(int which);

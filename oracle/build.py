@@ -5,8 +5,8 @@
   oracle/_build/libbess_oracle.so   the C++ / OpenMP restatement of the step (csrc/bess_step.cpp)
   oracle/_ref/libref_distance.so    the reference's own portable L1 / L2 distance code, compiled
                                     from its codelet sources where they lie; built only when a
-                                    checkout of the reference is present (REFERENCE_ROOT, default
-                                    /root/reference).  The stand-in Poplar headers under
+                                    checkout of the reference is present (environment variable
+                                    REFERENCE_ROOT).  The stand-in Poplar headers under
                                     oracle/stubs/ let those two files compile on the host.
 """
 

@@ -305,3 +305,39 @@ def test_argument_errors_match_the_reference():
     engine.run("train_step_loop", dict(learning_rate=lr, loss=loss, **batch))
     assert np.all(np.isfinite(loss))
     engine.close()
+
+
+def test_metric_step_shapes_match_the_cpp_port():
+    """The per-step shapes of the metric configuration (512 positives + 256 shared negatives per
+    shard, d = 256, 768 fp16 features, TransE-L2, sampled softmax with the log-count correction)
+    on two shards with small tables, three steps, against the C++ restatement of the step.  That
+    restatement computes in float32 like the engine, so the bound is the one of the long-k cases:
+    5e-5 relative (sums of 768 and 1280 cancelling terms)."""
+    from oracle import build as oracle_build
+    from oracle.cpp_oracle import CppOracle
+
+    oracle_build.build()
+    cfg = StepConfig(n_shard=2, n_entity=4001, n_relation_type=1388, embedding_size=256, entity_feature_size=768,
+                     batch_size=512, a2a_size=384, score_fn="TransE", distance_fn="L2", gamma=10.0,
+                     loss_type="softmax", correction_weight=1.0)
+    rw, n_step, lr = 512, 3, 1e-3
+    state = random_state(cfg, 21, fp16_features=True, warm=True)
+    engine = capi.CEngine(engine_settings(cfg, n_step=n_step, feature_dtype="float16", rw_batch=rw))
+    write_state(engine, cfg, state, rw)
+    batch = random_batch(cfg, n_step, 121, pad=7)
+    oracle = CppOracle(cfg)
+    oracle.set_state(state)
+    want_loss = oracle.train_step_loop(lr, batch)
+    loss = np.zeros(cfg.n_shard, np.float32)
+    engine.run("train_step_loop", dict(learning_rate=np.full(cfg.n_shard, lr, np.float32), loss=loss, **batch))
+    assert_close(loss, want_loss, 5e-5, "metric shapes: loss", atol_scale=0)
+    got, want = read_state(engine, cfg, rw, cfg.n_shard), oracle.get_state()
+    d = cfg.embedding_size
+    for name, sl in (("value", slice(0, d)), ("adam_m", slice(d, 2 * d)), ("sqrt_adam_v", slice(2 * d, 3 * d))):
+        assert_close(got["entity_data"][..., sl], want["entity_data"][..., sl], 5e-5, f"metric shapes: entity {name}")
+    np.testing.assert_array_equal(got["entity_data"][..., 3 * d :], want["entity_data"][..., 3 * d :])
+    for key in sorted(want):
+        if key not in ("entity_data", "step"):
+            assert_close(got[key], want[key], 5e-5, f"metric shapes: {key}")
+    np.testing.assert_array_equal(got["step"], want["step"])
+    engine.close()
