@@ -286,12 +286,12 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
         add_variable(proj_names[i], cfg_.f, cfg_.d, cfg_.f ? dense_bounds_[1 + i] : n_dense_);
     variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3});
 
-    // every process owns (reduces and updates) a slice of whole rows of the dense vector
+    // Every process owns (reduces and updates) an equal share of the rows of the dense vector, dealt
+    // out in turn: row r belongs to process r % world, as its row r / world.
     const size_t dense_rows = cfg_.n_relation_type + (size_t)cfg_.n_net() * cfg_.f;
     dense_chunk_rows_ = std::max<size_t>(1, (dense_rows + cfg_.world - 1) / cfg_.world);
     dense_chunk_ = dense_chunk_rows_ * cfg_.d;
-    own_lo_ = std::min(n_dense_, dense_chunk_ * cfg_.rank);
-    own_hi_ = std::min(n_dense_, own_lo_ + dense_chunk_);
+    own_rows_ = dense_rows > cfg_.rank ? (dense_rows - cfg_.rank + cfg_.world - 1) / cfg_.world : 0;
 
     const unsigned tiles = ceil_div(cfg_.f, 64) * ceil_div(cfg_.d, 64) * std::max(1u, cfg_.n_net());
     proj_splits_ = (int)std::min(8u, std::max(1u, ceil_div(148, std::max(1u, tiles))));
@@ -300,7 +300,7 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     KGE_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     KGE_CUDA(cudaStreamCreateWithFlags(&side_stream_, cudaStreamNonBlocking));
     // Which work runs beside the step's chain: bit 0 the relation gradients, bit 1 the next step's gather.
-    side_streams_ = cfg_.world == 1 ? 3u : 0u;
+    side_streams_ = 3u;
     if (const char* v = std::getenv("KGE_SIDE_STREAMS")) side_streams_ = (unsigned)std::atoi(v) & 3u;
     KGE_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
     for (cudaEvent_t& e : ev_join_) KGE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -1035,11 +1035,11 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, side,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1)));
             else
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, side,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, -1)));
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1)));
         }
         side_end(0);
         side_streams_ = saved;
@@ -1100,7 +1100,7 @@ void Engine::launch_one_step(unsigned step) {
                 g.epilogue = tc::EPI_STORE;
                 // straight into this shard's partial dense gradient, behind the relation rows: row m of
                 // the projection is row n_rel + net * F + m of the dense vector, and goes to its owner
-                g.out = nullptr; g.out_blocks = b.dense_dst; g.block_rows = (int)dense_chunk_rows_;
+                g.out = nullptr; g.out_blocks = b.dense_dst; g.block_rows = 1; g.block_cyclic = (int)cfg_.world;
                 g.block_row_offset = (int)(n_rel + net * F); g.ldc = D;
             }
             launch_tc("projection_bwd", nets, (int)cfg_.n_net(),
@@ -1126,12 +1126,12 @@ void Engine::launch_one_step(unsigned step) {
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
-                                                proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, (int)XCHG_DENSE_PARTIALS)));
+                                                proj_elems_, b.dense_dst, (int)cfg_.world, sync, (int)XCHG_DENSE_PARTIALS)));
             else
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
-                                                proj_elems_, b.dense_dst, (int)dense_chunk_rows_, sync, (int)XCHG_DENSE_PARTIALS)));
+                                                proj_elems_, b.dense_dst, (int)cfg_.world, sync, (int)XCHG_DENSE_PARTIALS)));
         }
     }
     KGE_CUDA(cudaGetLastError());
@@ -1148,14 +1148,14 @@ void Engine::launch_one_step(unsigned step) {
         da.n_replica = (int)cfg_.world;
         da.adam_m = dense_m_;
         da.adam_v = dense_v_;
-        da.lo = own_lo_;
-        da.hi = own_hi_;
+        da.n_own = own_rows_;
+        da.row_width = D;
         for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
         for (int i = 0; i < 3; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
         da.step_size = d_step_size_ + step;
         da.ap = adam_;
         // The parameter itself is read from this process's own replica (entry `rank`).
-        const unsigned blocks = (unsigned)std::min<size_t>((own_hi_ - own_lo_ + 255) / 256, 148 * 8);
+        const unsigned blocks = (unsigned)std::min<size_t>((own_rows_ * D / (vec ? 4 : 1) + 255) / 256, 148 * 8);
         KGE_LAUNCH("dense_update", KGE_CUDA(launch_dependent(k_dense_update, dim3(std::max(1u, blocks)), dim3(256), 0, stream_, da, (int)cfg_.rank)));
     }
     KGE_CUDA(cudaGetLastError());
@@ -1275,15 +1275,16 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
         KGE_CUDA(cudaMemcpy(value.data, base + var->offset, count * 4, cudaMemcpyDeviceToHost));
         return;
     }
-    // Optimiser state lives with the process that owns the slice (src/poplar_kge.cpp:329-339):
-    // collect each owner's part through its mapped arena.
-    const size_t chunk = dense_chunk_;  // the slice each process owns
-    for (unsigned p = 0; p < cfg_.world; ++p) {
-        const size_t lo = std::max(var->offset, std::min(n_dense_, chunk * p));
-        const size_t hi = std::min(var->offset + count, std::min(n_dense_, chunk * (p + 1)));
-        if (hi <= lo) continue;
-        const float* src = (const float*)(peer_arena_[p] + arena_offset_dense(var->kind)) + lo;
-        KGE_CUDA(cudaMemcpy(static_cast<float*>(value.data) + (lo - var->offset), src, (hi - lo) * 4, cudaMemcpyDeviceToHost));
+    // Optimiser state lives with the process that owns the row (src/poplar_kge.cpp:329-339): row r of
+    // the dense vector with process r % world.  Collect each owner's rows through its mapped arena.
+    const size_t D = cfg_.d, row0 = var->offset / D, n_rows = count / D, W = cfg_.world;
+    for (size_t p = 0; p < W; ++p) {
+        const size_t first = row0 + (p + W - row0 % W) % W;
+        if (first >= row0 + n_rows) continue;
+        const size_t rows = (row0 + n_rows - first + W - 1) / W;
+        const float* src = (const float*)(peer_arena_[p] + arena_offset_dense(var->kind)) + first * D;
+        KGE_CUDA(cudaMemcpy2D(static_cast<float*>(value.data) + (first - row0) * D, W * D * 4, src, W * D * 4, D * 4, rows,
+                              cudaMemcpyDeviceToHost));
     }
 }
 

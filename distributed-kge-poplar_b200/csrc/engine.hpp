@@ -184,7 +184,7 @@ class Engine {
     float dense_lr_mod_[3] = {1.f, 1.f, 1.f};
     float entity_lr_mod_ = 1.f;
     float *dense_ = nullptr, *dense_m_ = nullptr, *dense_v_ = nullptr;
-    size_t own_lo_ = 0, own_hi_ = 0, dense_chunk_ = 0, dense_chunk_rows_ = 1;
+    size_t own_rows_ = 0, dense_chunk_ = 0, dense_chunk_rows_ = 1;
     std::vector<Variable> variables_;
     unsigned long long step_ = 0;
     int proj_splits_ = 1, proj_rows_per_split_ = 0;

@@ -933,6 +933,20 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         float gh[V], gt[V];
 #pragma unroll
         for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
+        // the row's state does not depend on the lookups: requested first, used after the sums
+        float x[V], m[V], qq[V];
+#pragma unroll
+        for (int u = 0; u < V; ++u) x[u] = m[u] = qq[u] = 0.f;
+        if (lane == 0 && writes_row && c < D) {
+            if (V == 4) {
+                const float4 a = load4(xs + c), b = load4(ms + c), d = load4(qs + c);
+                x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
+                m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
+                qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
+            } else {
+                x[0] = load_as_float(xs + c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
+            }
+        }
         // Lane l sums the lookups q0 + l, q0 + l + lanes, ... in that order, four loads in flight;
         // the lanes' partial sums are then added in lane order: a fixed tree, whatever the timing.
         for (uint32_t base = q0; base < q1; base += 64 * kSegmentLanes) {
@@ -1000,15 +1014,6 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             if (d_hid_t) d_hid_t[o] = gt[0];
         }
         if (!writes_row) continue;
-        float x[V], m[V], qq[V];
-        if (V == 4) {
-            const float4 a = load4(xs + c), b = load4(ms + c), d = load4(qs + c);
-            x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
-            m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
-            qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
-        } else {
-            x[0] = load_as_float(xs + c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
-        }
 #pragma unroll
         for (int u = 0; u < V; ++u) {
             const float g = gh[u] + gt[u];
@@ -1115,8 +1120,10 @@ k_projection_bwd(const uint8_t* __restrict__ table, RowLayout L, const uint32_t*
 
 // This shard's contribution to the dense gradients, laid out like the dense parameter
 // vector: relation table | projection(s), and written slice by slice into the memory of the
-// process that owns (reduces and updates) each slice of `chunk_rows` rows: dense_dst[owner] is
-// this shard's slot in that process's receive buffer.  Relation rows are the segment sums of the
+// process that owns (reduces and updates) each row: the rows are dealt out in turn, row r to
+// process r % n_owner as its row r / n_owner, so that every process receives and updates an
+// equal share of every parameter; dense_dst[owner] is this shard's slot in that process's
+// receive buffer.  Relation rows are the segment sums of the
 // per-triple relation gradients (backward of the gather at src/poplar_kge.cpp:489);
 // projection entries sum the split partials of k_projection_bwd in split order.
 constexpr int kRelationLanes = 8;
@@ -1126,7 +1133,7 @@ __global__ void __launch_bounds__(64 * kRelationLanes)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
-                float* const* __restrict__ dense_dst, int chunk_rows, ExchangeSync sync, int signal_kind) {
+                float* const* __restrict__ dense_dst, int n_owner, ExchangeSync sync, int signal_kind) {
     grid_dependency_sync();
     __shared__ float part[kRelationLanes][64 * V];
     __shared__ uint32_t s_perm[64 * kRelationLanes];
@@ -1137,8 +1144,8 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         const int rho = blockIdx.x, col = threadIdx.x & 63, lane = threadIdx.x >> 6;
         const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
         // the row goes to the process that owns this slice of the dense vector
-        const int owner = rho / chunk_rows;
-        float* __restrict__ dst_row = dense_dst[owner] + (size_t)(rho - owner * chunk_rows) * D;
+        const int owner = rho % n_owner;
+        float* __restrict__ dst_row = dense_dst[owner] + (size_t)(rho / n_owner) * D;
         if (q0 == q1) {
             for (int c = threadIdx.x; c < D; c += blockDim.x) dst_row[c] = 0.f;
             exchange_signal(sync, signal_kind, gridDim.x);
@@ -1191,7 +1198,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         exchange_signal(sync, signal_kind, gridDim.x);
         return;
     }
-    const size_t rel_elems = (size_t)n_rel * D, chunk = (size_t)chunk_rows * D;
+    const size_t rel_elems = (size_t)n_rel * D;
     const size_t total = (size_t)n_net * proj_elems;
     const size_t first = ((size_t)blockIdx.x - n_rel) * blockDim.x + threadIdx.x;
     const size_t stride = ((size_t)gridDim.x - n_rel) * blockDim.x;
@@ -1199,8 +1206,8 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         const size_t net = pe / proj_elems, idx = pe - net * proj_elems;
         float g = 0.f;
         for (int z = 0; z < splits; ++z) g += proj_partial[(net * splits + z) * proj_elems + idx];
-        const size_t e = rel_elems + pe, owner = e / chunk;
-        dense_dst[owner][e - owner * chunk] = g;
+        const size_t e = rel_elems + pe, row = e / D;
+        dense_dst[row % n_owner][(row / n_owner) * D + (e - row * D)] = g;
     }
     exchange_signal(sync, signal_kind, gridDim.x);
 }
@@ -1211,14 +1218,16 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
 // (the all-gather on next use, :341-348).  Pointer tables live in device memory; entries
 // may point into peers' memory.
 struct DenseUpdateArgs {
-    const float* const* partials;  // [n_partial] the shards' slots in this process's receive buffer, element lo first
+    const float* const* partials;  // [n_partial] the shards' slots in this process's receive buffer
     int n_partial;
     float* const* replicas;  // [n_replica] dense parameter vectors
     int n_replica;
     float* adam_m;
     float* adam_v;
-    size_t lo, hi;          // owned element range
-    size_t bounds[4];       // parameter p covers [bounds[p], bounds[p+1])
+    // This process owns the rows self, self + n_replica, ... of the dense vector: n_own of them,
+    // row_width elements each; its j-th row is row j of every slot.
+    size_t n_own, row_width;
+    size_t bounds[4];       // parameter p covers the elements [bounds[p], bounds[p+1])
     float lr_modifier[3];
     const float* step_size;
     AdamParams ap;
@@ -1238,14 +1247,15 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
     grid_dependency_sync();
     exchange_wait(a.sync, XCHG_DENSE_PARTIALS);  // every process's partial gradients are complete
     const float base_alpha = *a.step_size;
-    const bool vec = ((a.lo | a.hi | a.bounds[1] | a.bounds[2]) & 3) == 0;
+    const size_t W = a.row_width, total = a.n_own * W;
+    const bool vec = ((W | a.bounds[1] | a.bounds[2]) & 3) == 0;
     if (vec) {
-        for (size_t e = a.lo + 4 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x); e < a.hi;
-             e += 4 * (size_t)gridDim.x * blockDim.x) {
+        for (size_t le = 4 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x); le < total; le += 4 * (size_t)gridDim.x * blockDim.x) {
+            const size_t j = le / W, e = (j * a.n_replica + self) * W + (le - j * W);  // slot index -> dense index
             float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
             for (int s = 0; s < a.n_partial; ++s) {
-                const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + (e - a.lo));
+                const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + le);
                 g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
             }
             const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
@@ -1261,10 +1271,10 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
             for (int rep = 0; rep < a.n_replica; ++rep) *reinterpret_cast<float4*>(a.replicas[rep] + e) = x;
         }
     } else {
-        for (size_t e = a.lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < a.hi;
-             e += (size_t)gridDim.x * blockDim.x) {
+        for (size_t le = (size_t)blockIdx.x * blockDim.x + threadIdx.x; le < total; le += (size_t)gridDim.x * blockDim.x) {
+            const size_t j = le / W, e = (j * a.n_replica + self) * W + (le - j * W);
             float g = 0.f;
-            for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][e - a.lo];
+            for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][le];
             const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
             const float alpha = base_alpha * a.lr_modifier[p];
             float m = a.adam_m[e], v = a.adam_v[e];

@@ -67,6 +67,7 @@ struct GemmArgs {
     float* const* out_blocks;
     int block_rows;
     int block_row_offset;  // with out_blocks: row m belongs to block (m + offset) / block_rows
+    int block_cyclic;      // > 0: rows are dealt out in turn instead, row m + offset to block (m + offset) % block_cyclic, as its row (m + offset) / block_cyclic
     long long ldc;
     long long split_stride;
     // EPI_ADD_TABLE_VALUE: value row of output row m is x_base + (x_gather ? x_gather[m] : m) * x_row_stride_bytes
@@ -374,8 +375,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(GemmArgs g) {
     if (m < g.M) {
         float* out_row;
         if (g.out_blocks) {
-            const int blk = (m + g.block_row_offset) / g.block_rows;
-            out_row = g.out_blocks[blk] + (size_t)(m + g.block_row_offset - blk * g.block_rows) * g.ldc;
+            const int gr = m + g.block_row_offset;
+            const int blk = g.block_cyclic > 0 ? gr % g.block_cyclic : gr / g.block_rows;
+            const int local = g.block_cyclic > 0 ? gr / g.block_cyclic : gr - blk * g.block_rows;
+            out_row = g.out_blocks[blk] + (size_t)local * g.ldc;
         } else {
             out_row = g.out + (size_t)blockIdx.z * g.split_stride + (size_t)m * g.ldc;
         }
@@ -602,8 +605,10 @@ __device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, 
     }
     float* out_row;
     if (g.out_blocks) {
-        const int blk = (m + g.block_row_offset) / g.block_rows;
-        out_row = g.out_blocks[blk] + (size_t)(m + g.block_row_offset - blk * g.block_rows) * g.ldc;
+        const int gr = m + g.block_row_offset;
+        const int blk = g.block_cyclic > 0 ? gr % g.block_cyclic : gr / g.block_rows;
+        const int local = g.block_cyclic > 0 ? gr / g.block_cyclic : gr - blk * g.block_rows;
+        out_row = g.out_blocks[blk] + (size_t)local * g.ldc;
     } else {
         out_row = out_base + (size_t)m * g.ldc;
     }
