@@ -136,3 +136,18 @@ def test_benchmark_batches_obey_the_stream_contract():
                 assert (s, int(row[head[s, step, i]]), int(rel[s, step, i]), col // a2a, int(received[s, col])) in triples
     sliced = bench.local_slice(b, rank=1, world=2)
     np.testing.assert_array_equal(sliced["remote"], b["remote"][2:4])
+
+
+def test_exchange_trace_summary():
+    """bench.summarise_exchange_trace: mean step timeline from the engine's hand-over stamps."""
+    import bench
+
+    t = np.zeros((256, 4, 3))
+    for e in range(1, 200):  # epoch e: a step of 100 us that starts at 100 * e
+        start = 100.0 * e
+        t[e % 256] = [[start + 20, start + 21, start + 22], [start + 60, start + 61, start + 62],
+                      [start + 90, start + 91, start + 92], [start + 99, start + 99.5, start + 100]]
+    out = bench.summarise_exchange_trace(t.reshape(-1))
+    assert out["steps"] >= 190
+    assert abs(out["tails"]["published"] - 20) < 1e-6 and abs(out["dense_params"]["wait_ended"] - 100) < 1e-6
+    assert bench.summarise_exchange_trace(np.zeros(256 * 4 * 3)) == {"steps": 0}
