@@ -289,7 +289,7 @@ int kge_op_scatter_add_rows(const float* grad_rows, const uint32_t* indices, siz
         // relation part (fed the same indices, with zero relation types) is not used.
         k_prepare_segments<<<1, 512>>>(di.as<uint32_t>(), di.as<uint32_t>(), di.as<uint32_t>(), nullptr, (int)n, 0,
                                        (int)rows, 0, dperm.as<uint32_t>(), doff.as<uint32_t>(),
-                                       unused_perm.as<uint32_t>(), unused_off.as<uint32_t>(), nullptr);
+                                       unused_perm.as<uint32_t>(), unused_off.as<uint32_t>(), nullptr, nullptr, nullptr);
         k_segment_sum_rows<<<(unsigned)rows, 128>>>(dg.as<float>(), dperm.as<uint32_t>(), doff.as<uint32_t>(), width,
                                                     dout.as<float>());
         finish_kernels();
@@ -493,7 +493,7 @@ int kge_op_scatter_add_rows_noalloc(const float* grad_rows, const uint32_t* indi
         // Every entry the second kernel reads (perm[0, n) and offsets[0, rows]) is rewritten by the
         // first, so nothing left by an earlier call is ever read and nothing needs clearing.
         k_prepare_segments<<<1, 512, 0, stream>>>(indices, indices, indices, nullptr, (int)n, 0, (int)rows, 0, scratch->perm,
-                                                  scratch->offsets, scratch->spare_perm, scratch->spare_offsets, nullptr);
+                                                  scratch->offsets, scratch->spare_perm, scratch->spare_offsets, nullptr, nullptr, nullptr);
         k_segment_sum_rows<<<(unsigned)rows, 128, 0, stream>>>(grad_rows, scratch->perm, scratch->offsets, width, grad_table);
         KGE_CUDA(cudaGetLastError());
     });

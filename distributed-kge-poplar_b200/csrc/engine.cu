@@ -299,6 +299,7 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
 
     KGE_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     KGE_CUDA(cudaStreamCreateWithFlags(&side_stream_, cudaStreamNonBlocking));
+    if (const char* v = std::getenv("KGE_SPLIT_POPULAR_ROWS")) split_popular_rows_ = std::atoi(v) != 0;
     // Which work runs beside the step's chain: bit 0 the relation gradients, bit 1 the next step's gather.
     side_streams_ = 3u;
     if (const char* v = std::getenv("KGE_SIDE_STREAMS")) side_streams_ = (unsigned)std::atoi(v) & 3u;
@@ -366,6 +367,9 @@ void Engine::allocate() {
         b.grad_recv = (float*)(arena_ + arena_offset_shard(l, 1));
         b.dense_partial = (float*)(arena_ + arena_offset_dense_recv()) + (size_t)(shard0_ + l) * dense_chunk_;
         b.dense_dst = (float**)device_alloc(sizeof(float*) * cfg_.world);
+        b.heavy_partial = (float*)device_alloc((size_t)kHeavySlots * 2 * D * 4);
+        b.heavy_counter = (unsigned*)device_alloc(kHeavySlots * sizeof(unsigned));
+        KGE_CUDA(cudaMemset(b.heavy_counter, 0, kHeavySlots * sizeof(unsigned)));
         b.send_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.grad_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.predict_score_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
@@ -406,6 +410,9 @@ void Engine::allocate() {
     d_rel_perm_ = (uint32_t*)device_alloc(steps * B * 4);
     d_rel_off_ = (uint32_t*)device_alloc(steps * (cfg_.n_relation_type + 1) * 4);
     d_first_slot_ = (uint32_t*)device_alloc(steps * R * 4);
+    d_heavy_parts_ = (uint4*)device_alloc(steps * kHeavySlots * sizeof(uint4));
+    d_heavy_count_ = (uint32_t*)device_alloc(steps * 4);
+    KGE_CUDA(cudaMemset(d_heavy_count_, 0, steps * 4));
     d_step_size_ = (float*)device_alloc(cfg_.n_step * 4);
     d_loss_total_ = (float*)device_alloc(n_local_ * 4);
     d_loss_last_ = (float*)device_alloc(n_local_ * 4);
@@ -608,7 +615,7 @@ void Engine::stage_batch(std::vector<HostArray>& arrays) {
     upload(tail, d_tail_);
     k_prepare_segments<<<(unsigned)(n * S), 512, 0, stream_>>>(
         d_head_, d_a2a_, d_relation_, d_remote_, (int)B, (int)T, (int)R, (int)cfg_.n_relation_type, d_ent_perm_,
-        d_ent_off_, d_rel_perm_, d_rel_off_, d_first_slot_);
+        d_ent_off_, d_rel_perm_, d_rel_off_, d_first_slot_, split_popular_rows_ ? d_heavy_parts_ : nullptr, d_heavy_count_);
     KGE_CUDA(cudaGetLastError());
     staged_ = true;
 }
@@ -1055,24 +1062,25 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* off = d_ent_off_ + sidx * (R + 1);
         const uint32_t* first = d_first_slot_ + sidx * R;
         const float* alpha = d_step_size_ + step;
+        const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
         if (cfg_.state_type == ST_F32) {
             if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
             else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
         } else {
             if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
             else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
         }
     }
     KGE_CUDA(cudaGetLastError());

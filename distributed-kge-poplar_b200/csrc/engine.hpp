@@ -100,6 +100,8 @@ class Engine {
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
         float** grad_dst = nullptr;  // device table [n_shard]
+        float* heavy_partial = nullptr;   // [kHeavySlots][2][D] sums of the parts of popular rows
+        unsigned* heavy_counter = nullptr;  // [kHeavySlots]
         float** dense_dst = nullptr;  // device table [world]: this shard's slot in each owner's receive buffer
         float** predict_score_dst = nullptr;     // device table [n_shard]: where each asking shard's results go
         uint32_t** predict_index_dst = nullptr;  // device table [n_shard]
@@ -153,6 +155,7 @@ class Engine {
     // joined to the main stream with events (graph edges under capture).
     cudaStream_t side_stream_ = nullptr;
     unsigned side_streams_ = 0;
+    bool split_popular_rows_ = true;  // rows with many lookups are summed in parts by several blocks
     cudaEvent_t ev_fork_ = nullptr, ev_join_[2] = {nullptr, nullptr};
     cudaStream_t side_begin();
     void side_end(int which);
@@ -193,7 +196,8 @@ class Engine {
     uint32_t *d_remote_ = nullptr, *d_a2a_ = nullptr, *d_head_ = nullptr, *d_relation_ = nullptr,
              *d_tail_ = nullptr;
     uint32_t *d_ent_perm_ = nullptr, *d_ent_off_ = nullptr, *d_rel_perm_ = nullptr,
-             *d_rel_off_ = nullptr, *d_first_slot_ = nullptr;
+             *d_rel_off_ = nullptr, *d_first_slot_ = nullptr, *d_heavy_count_ = nullptr;
+    uint4* d_heavy_parts_ = nullptr;
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
     unsigned* d_loss_counter_ = nullptr;
     uint8_t* pinned_ = nullptr;

@@ -833,12 +833,19 @@ __device__ __forceinline__ int lower_bound_key(const unsigned long long* keys, i
     return lo;
 }
 
+// Rows with more than kHeavyMin lookups are cut into parts of kHeavyPart lookups, at most kHeavySlots
+// parts per shard and step (see k_entity_update).
+constexpr int kHeavySlots = 48;
+constexpr int kHeavyMin = 64;
+constexpr int kHeavyPart = 32;
+
 static __global__ void __launch_bounds__(512)
 k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict__ a2a_idx,
                    const uint32_t* __restrict__ relation, const uint32_t* __restrict__ remote, int B,
                    int T, int R, int n_rel, uint32_t* __restrict__ ent_perm,
                    uint32_t* __restrict__ ent_off, uint32_t* __restrict__ rel_perm,
-                   uint32_t* __restrict__ rel_off, uint32_t* __restrict__ first_slot) {
+                   uint32_t* __restrict__ rel_off, uint32_t* __restrict__ first_slot,
+                   uint4* __restrict__ heavy_parts, uint32_t* __restrict__ heavy_count) {
     __shared__ unsigned long long keys[kMaxSortItems];
     const int s = blockIdx.x;
     head += (size_t)s * B;
@@ -891,6 +898,26 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
         const bool first = i == 0 || (keys[i - 1] >> 32) != (keys[i] >> 32);
         first_slot[(uint32_t)keys[i]] = first ? 1u : 0u;
     }
+    if (!heavy_parts) return;
+    __syncthreads();
+    // Rows with many lookups are cut into parts for k_entity_update (bit 1 of first_slot marks them).
+    if (threadIdx.x == 0) {
+        heavy_parts += (size_t)s * kHeavySlots;
+        int used = 0;
+        for (int r = 0; r < R; ++r) {
+            const uint32_t q0 = ent_off[r], q1 = ent_off[r + 1];
+            if (q1 - q0 <= (uint32_t)kHeavyMin) continue;
+            const int parts = (int)((q1 - q0 + kHeavyPart - 1) / kHeavyPart);
+            if (used + parts > kHeavySlots || parts > 255) continue;  // stays with its own block
+            for (int p = 0; p < parts; ++p)
+                heavy_parts[used + p] = make_uint4((uint32_t)r, q0 + (uint32_t)(p * kHeavyPart),
+                                                   min(q1, q0 + (uint32_t)((p + 1) * kHeavyPart)),
+                                                   ((uint32_t)used << 16) | ((uint32_t)parts << 8) | (uint32_t)p);
+            first_slot[r] |= 2u;
+            used += parts;
+        }
+        heavy_count[s] = (uint32_t)used;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -899,7 +926,22 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
 // src/fructose/frnn.cpp:61-90).  One block per gathered row.  Every gathered row is
 // updated, rows with a zero gradient and the padding row included, as in the reference.
 // d_hid_h / d_hid_t keep the hidden-row gradients for the projection backward.
+//
+// Entity popularity is skewed: the shard that holds a step's most popular entity sees one row
+// with hundreds of lookups, and a single block would add them sixteen at a time while the rest of
+// the GPU idles.  k_prepare_segments therefore cuts every row with more than kHeavyMin lookups
+// into parts of kHeavyPart lookups (at most kHeavySlots parts per shard and step).  The first
+// kHeavySlots blocks of the grid take one part each, leave its sums in `heavy_partial`, and the
+// block that arrives last at the row's counter adds the parts in part order and finishes the
+// row; the row's own block skips it.  Nothing waits, and the order of the additions is fixed.
 constexpr int kSegmentLanes = 4;  // threads groups that share one segment's lookups
+
+struct HeavyRows {
+    const uint4* parts;      // [kHeavySlots] {gathered row, first lookup, end lookup, (first part's slot << 16) | (parts << 8) | part}
+    const uint32_t* count;   // parts in use
+    float* partial;          // [kHeavySlots][2][D] sums of a part: head lookups | tail lookups
+    unsigned* counter;       // [kHeavySlots] parts of a row that have arrived (indexed by the row's first slot)
+};
 
 template <class ST, int V>
 __global__ void __launch_bounds__(64 * kSegmentLanes)
@@ -909,15 +951,27 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 const uint32_t* __restrict__ first_slot, const float* __restrict__ d_head,
                 const float* __restrict__ grad_recv, int B,
                 float* __restrict__ d_hid_h, float* __restrict__ d_hid_t,
-                const float* __restrict__ step_size, float lr_modifier, AdamParams ap, ExchangeSync sync) {
+                const float* __restrict__ step_size, float lr_modifier, AdamParams ap, ExchangeSync sync, HeavyRows heavy) {
     grid_dependency_sync();
     exchange_wait(sync, XCHG_TAIL_GRADS);  // grad_recv is written by the other processes
     // partial sums of the item lanes, [lane][head | tail][64 column threads][V]
     __shared__ float part[kSegmentLanes][2][64 * V];
     __shared__ uint32_t s_perm[64 * kSegmentLanes];
-    const int r = blockIdx.x, D = L.d;
+    __shared__ int s_last;
+    const int D = L.d;
     const int col = threadIdx.x & 63, lane = threadIdx.x >> 6;
-    const uint32_t q0 = off[r], q1 = off[r + 1];
+    const bool helper = (int)blockIdx.x < kHeavySlots;
+    int r;
+    uint32_t q0, q1, info = 0;
+    if (helper) {
+        if (blockIdx.x >= *heavy.count) return;
+        const uint4 h = heavy.parts[blockIdx.x];
+        r = (int)h.x; q0 = h.y; q1 = h.z; info = h.w;
+    } else {
+        r = (int)blockIdx.x - kHeavySlots;
+        if (first_slot[r] & 2u) return;  // its lookups are summed part by part by the first blocks
+        q0 = off[r]; q1 = off[r + 1];
+    }
     const size_t row = remote[r];
     ST* __restrict__ xv = reinterpret_cast<ST*>(table + row * L.row_bytes);
     ST* __restrict__ mv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_m);
@@ -927,28 +981,15 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
     const ST* __restrict__ ms = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes + L.off_m);
     const ST* __restrict__ qs = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes + L.off_q);
     const float alpha = *step_size * lr_modifier;
-    const bool writes_row = first_slot[r] != 0;
-    for (int c0 = 0; c0 < D; c0 += 64 * V) {
-        const int c = c0 + col * V;
-        float gh[V], gt[V];
+    const bool writes_row = (first_slot[r] & 1u) != 0;
+
+    // Sums of the lookups [q0, q1) for the columns c .. c+V-1, separately for head and tail lookups;
+    // complete in the threads of lane 0.  Lane l sums the lookups q0 + l, q0 + l + lanes, ... in
+    // that order, four loads in flight; the lanes' partial sums are then added in lane order: a
+    // fixed tree, whatever the timing.  Called by all threads of the block.
+    auto segment_sums = [&](int c, float (&gh)[V], float (&gt)[V]) {
 #pragma unroll
         for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
-        // the row's state does not depend on the lookups: requested first, used after the sums
-        float x[V], m[V], qq[V];
-#pragma unroll
-        for (int u = 0; u < V; ++u) x[u] = m[u] = qq[u] = 0.f;
-        if (lane == 0 && writes_row && c < D) {
-            if (V == 4) {
-                const float4 a = load4(xs + c), b = load4(ms + c), d = load4(qs + c);
-                x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
-                m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
-                qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
-            } else {
-                x[0] = load_as_float(xs + c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
-            }
-        }
-        // Lane l sums the lookups q0 + l, q0 + l + lanes, ... in that order, four loads in flight;
-        // the lanes' partial sums are then added in lane order: a fixed tree, whatever the timing.
         for (uint32_t base = q0; base < q1; base += 64 * kSegmentLanes) {
             // the segment's lookups go through shared memory, so the row loads do not wait on them
             const int count = (int)min((uint32_t)(64 * kSegmentLanes), q1 - base);
@@ -989,7 +1030,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             part[lane][1][col * V + u] = gt[u];
         }
         __syncthreads();
-        if (lane != 0 || c >= D) continue;
+        if (lane != 0) return;
 #pragma unroll
         for (int u = 0; u < V; ++u) {
             gh[u] = part[0][0][col * V + u];
@@ -1000,6 +1041,10 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 gt[u] += part[l][1][col * V + u];
             }
         }
+    };
+
+    // The row's hidden gradients and its Adam step for the columns c .. c+V-1 (one thread).
+    auto finish = [&](int c, float (&gh)[V], float (&gt)[V]) {
         const size_t o = (size_t)r * D + c;
         if (V == 4) {
             if (d_hid_t) {
@@ -1013,7 +1058,16 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             d_hid_h[o] = d_hid_t ? gh[0] : gh[0] + gt[0];
             if (d_hid_t) d_hid_t[o] = gt[0];
         }
-        if (!writes_row) continue;
+        if (!writes_row) return;
+        float x[V], m[V], qq[V];
+        if (V == 4) {
+            const float4 a = load4(xs + c), b = load4(ms + c), d = load4(qs + c);
+            x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
+            m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
+            qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
+        } else {
+            x[0] = load_as_float(xs + c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
+        }
 #pragma unroll
         for (int u = 0; u < V; ++u) {
             const float g = gh[u] + gt[u];
@@ -1032,6 +1086,54 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             store_from_float(mv + c, m[0]);
             store_from_float(qv + c, qq[0]);
         }
+    };
+
+    float gh[V], gt[V];
+    if (!helper) {
+        for (int c0 = 0; c0 < D; c0 += 64 * V) {
+            const int c = c0 + col * V;
+            segment_sums(c, gh, gt);
+            if (lane == 0 && c < D) finish(c, gh, gt);
+        }
+        return;
+    }
+    // one part of a popular row: leave its sums; the part that arrives last adds all of them
+    const int first = (int)(info >> 16), parts = (int)((info >> 8) & 255u), me = (int)(info & 255u);
+    for (int c0 = 0; c0 < D; c0 += 64 * V) {
+        const int c = c0 + col * V;
+        segment_sums(c, gh, gt);
+        if (lane == 0 && c < D) {
+            float* mine = heavy.partial + (size_t)(first + me) * 2 * D;
+#pragma unroll
+            for (int u = 0; u < V; ++u) {
+                mine[c + u] = gh[u];
+                mine[D + c + u] = gt[u];
+            }
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned arrived = atomicAdd(&heavy.counter[first], 1u) + 1u;
+        s_last = arrived == (unsigned)parts;
+        if (s_last) heavy.counter[first] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (lane != 0) return;
+    for (int c = col * V; c < D; c += 64 * V) {
+#pragma unroll
+        for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
+        for (int p = 0; p < parts; ++p) {
+            const float* theirs = heavy.partial + (size_t)(first + p) * 2 * D;
+#pragma unroll
+            for (int u = 0; u < V; ++u) {
+                gh[u] += __ldcg(theirs + c + u);
+                gt[u] += __ldcg(theirs + D + c + u);
+            }
+        }
+        finish(c, gh, gt);
     }
 }
 

@@ -341,3 +341,34 @@ def test_metric_step_shapes_match_the_cpp_port():
             assert_close(got[key], want[key], 5e-5, f"metric shapes: {key}")
     np.testing.assert_array_equal(got["step"], want["step"])
     engine.close()
+
+
+@pytest.mark.parametrize("separate", [False, True], ids=["shared_net", "two_nets"])
+def test_popular_rows_are_summed_in_parts(separate):
+    """Skewed lookups: one gathered row is named by most heads and tails of a shard, a second one by
+    about a hundred (entity popularity in real graphs is Zipf-like).  Rows with more than 64 lookups
+    are cut into parts that separate blocks sum; the result must match the oracle like any other."""
+    cfg = StepConfig(n_shard=2, n_entity=700, n_relation_type=6, embedding_size=64, entity_feature_size=32,
+                     batch_size=256, a2a_size=160, score_fn="TransE", distance_fn="L2", gamma=8.0,
+                     loss_type="softmax", correction_weight=1.0, share_feature_networks=not separate)
+    case = dict(cfg=cfg, seed=12, feature_dtype="float16")
+    n_step = 2
+    cfg, state, engine, batch = _build(case, n_step=n_step, warm=True, pad=5)
+    rng = np.random.RandomState(5)
+    for key in ("head", "a2a"):
+        idx = batch[key]
+        hot = rng.uniform(size=idx.shape)
+        idx[hot < 0.55] = 7      # several hundred lookups of one row per shard and step
+        idx[(hot >= 0.55) & (hot < 0.7)] = 11
+    oracle = make_oracle(cfg, state)
+    want_loss = oracle.train_step_loop(1e-3, batch)
+    got_loss = _run_engine(engine, cfg, batch, 1e-3)
+    assert_close(got_loss, want_loss, 2e-5, "popular rows: loss", atol_scale=0)
+    for s in range(cfg.n_shard):
+        d_hidden = engine.debug_fetch("d_hidden", s, cfg.n_remote * cfg.embedding_size).reshape(cfg.n_remote, -1)
+        if not separate:
+            # the popular row's gradient is a sum of several hundred terms of size ~1e2 that cancel to ~1e1:
+            # float32 addition in any order is good to about 1e-4 of the tensor's scale there
+            assert_close(d_hidden, oracle.last["d_value"][s], 1e-4, f"popular rows: d hidden[{s}]")
+    _compare_state(engine, cfg, oracle, "popular rows", RTOL=2e-5)
+    engine.close()
