@@ -899,14 +899,33 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
         first_slot[(uint32_t)keys[i]] = first ? 1u : 0u;
     }
     if (!heavy_parts) return;
-    __syncthreads();
     // Rows with many lookups are cut into parts for k_entity_update (bit 1 of first_slot marks them).
+    // All threads look for such rows (there are at most (B + T) / kHeavyMin of them); one thread
+    // then orders them by row, so that the slots do not depend on the timing, and hands out the parts.
+    constexpr int kMaxHeavyRows = 64;
+    __shared__ int s_heavy_rows[kMaxHeavyRows];
+    __shared__ int s_heavy_n;
+    if (threadIdx.x == 0) s_heavy_n = 0;
+    __syncthreads();
+    for (int r = threadIdx.x; r < R; r += blockDim.x)
+        if (ent_off[r + 1] - ent_off[r] > (uint32_t)kHeavyMin) {
+            const int i = atomicAdd(&s_heavy_n, 1);
+            if (i < kMaxHeavyRows) s_heavy_rows[i] = r;
+        }
+    __syncthreads();
     if (threadIdx.x == 0) {
         heavy_parts += (size_t)s * kHeavySlots;
+        const int n_rows = min(s_heavy_n, kMaxHeavyRows);
+        for (int i = 1; i < n_rows; ++i) {  // insertion sort, a handful of entries
+            const int r = s_heavy_rows[i];
+            int j = i - 1;
+            for (; j >= 0 && s_heavy_rows[j] > r; --j) s_heavy_rows[j + 1] = s_heavy_rows[j];
+            s_heavy_rows[j + 1] = r;
+        }
         int used = 0;
-        for (int r = 0; r < R; ++r) {
+        for (int i = 0; i < n_rows; ++i) {
+            const int r = s_heavy_rows[i];
             const uint32_t q0 = ent_off[r], q1 = ent_off[r + 1];
-            if (q1 - q0 <= (uint32_t)kHeavyMin) continue;
             const int parts = (int)((q1 - q0 + kHeavyPart - 1) / kHeavyPart);
             if (used + parts > kHeavySlots || parts > 255) continue;  // stays with its own block
             for (int p = 0; p < parts; ++p)
