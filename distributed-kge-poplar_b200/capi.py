@@ -29,7 +29,7 @@ SYMBOLS = (
     "kge_stage_batch", "kge_train_staged", "kge_last_run_stats", "kge_set_kernel_timing",
     "kge_kernel_time_count", "kge_kernel_time", "kge_debug_fetch",
     "kge_op_pairwise", "kge_op_pairwise_grad", "kge_op_gather_rows", "kge_op_scatter_add_rows",
-    "kge_op_scatter_add_rows_noalloc", "kge_op_tc_gemm",
+    "kge_op_scatter_add_rows_noalloc", "kge_op_tc_gemm", "kge_op_tc_planes",
     "kge_op_activation", "kge_op_all_to_all",
 )
 
@@ -84,6 +84,8 @@ def load_library() -> C.CDLL:
     lib.kge_op_scatter_add_rows_noalloc.argtypes = [vp, vp, sz, sz, sz, vp, vp]
     lib.kge_op_tc_gemm.argtypes = [vp, C.c_int, C.c_int, u32p, sz, sz, fp, C.c_int, sz, sz, sz, sz, sz, C.c_int, fp,
                                    C.c_int, C.c_int, fp]
+    lib.kge_op_tc_planes.argtypes = [fp, C.c_int, C.c_int, sz, sz, fp, C.c_int, sz, sz, sz, sz, sz, C.c_int, fp, C.c_int,
+                                     C.c_int, C.c_int, C.c_int, fp, fp]
     lib.kge_op_activation.argtypes = [C.c_int, fp, fp, sz, sz, fp, fp]
     lib.kge_op_all_to_all.argtypes = [fp, sz, sz, fp]
     _lib = lib
@@ -306,6 +308,20 @@ def op_tc_gemm(a, b, m: int, n: int, k: int, a_transposed: bool = False, b_trans
         _fp(b), int(b_transposed), b.shape[0], b.shape[1], m, n, k, epilogue, _fp(xx) if xx is not None else None,
         splits, tile_n, _fp(out)))
     return out
+
+
+def op_tc_planes(a, b, m: int, n: int, k: int, a_mn_major: bool = False, b_mn_major: bool = False, a_exact: bool = False,
+                 epilogue: int = 0, x=None, splits: int = 1, tile_n: int = 128, hi_is_cleared: bool = False, repeat: int = 0):
+    """Plane-fed tensor-core contraction out[m, n] (see kge_op_tc_planes); returns (out, mean_us)."""
+    a, b = _f32(a), _f32(b)
+    xx = _f32(x) if x is not None else None
+    out = np.empty((m, n), np.float32)
+    mean_us = C.c_float(0.0)
+    _op_check(load_library().kge_op_tc_planes(
+        _fp(a), int(a_mn_major), int(a_exact), a.shape[0], a.shape[1], _fp(b), int(b_mn_major), b.shape[0], b.shape[1],
+        m, n, k, epilogue, _fp(xx) if xx is not None else None, splits, tile_n, int(hi_is_cleared), repeat,
+        C.byref(mean_us), _fp(out)))
+    return out, float(mean_us.value)
 
 
 def op_activation(kind: int, x, grad_out) -> Tuple[np.ndarray, np.ndarray]:

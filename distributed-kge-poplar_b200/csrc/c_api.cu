@@ -8,6 +8,7 @@
 
 #include "engine.hpp"
 #include "tc_gemm.cuh"
+#include "tc_planes.cuh"
 
 using namespace kge;
 
@@ -282,14 +283,12 @@ int kge_op_scatter_add_rows(const float* grad_rows, const uint32_t* indices, siz
             if (indices[i] >= rows) fail(KGE_INVALID_ARGUMENT, msg() << "kge_op_scatter_add_rows: index " << indices[i] << " is not below " << rows);
         if (rows == 0 || width == 0) return;
         DeviceBuffer dg(n * width * 4), di(n * 4), dperm(n * 4), doff((rows + 1) * 4), dout(rows * width * 4);
-        DeviceBuffer unused_perm(n * 4), unused_off(16);
         to_device(dg, grad_rows, n * width * 4);
         to_device(di, indices, n * 4);
-        // All n lookups are passed as "head" lookups; there are no tail lookups, and the
-        // relation part (fed the same indices, with zero relation types) is not used.
-        k_prepare_segments<<<1, 512>>>(di.as<uint32_t>(), di.as<uint32_t>(), di.as<uint32_t>(), nullptr, (int)n, 0,
+        // All n lookups are passed as "head" lookups; there are no tail and no relation lookups.
+        k_prepare_segments<<<1, 512>>>(di.as<uint32_t>(), di.as<uint32_t>(), nullptr, nullptr, (int)n, 0,
                                        (int)rows, 0, dperm.as<uint32_t>(), doff.as<uint32_t>(),
-                                       unused_perm.as<uint32_t>(), unused_off.as<uint32_t>(), nullptr, nullptr, nullptr);
+                                       nullptr, nullptr, nullptr, nullptr, nullptr);
         k_segment_sum_rows<<<(unsigned)rows, 128>>>(dg.as<float>(), dperm.as<uint32_t>(), doff.as<uint32_t>(), width,
                                                     dout.as<float>());
         finish_kernels();
@@ -387,42 +386,14 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         g.status = dstatus.as<unsigned>();
         const bool exact = a_half != 0, rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
         cudaError_t err = cudaSuccess;
-        // Developer aid: KGE_TC_REPEAT=n launches the kernel n more times between two events and prints the mean time.
-        const char* env_repeat = std::getenv("KGE_TC_REPEAT");
-        const int repeat = env_repeat ? std::atoi(env_repeat) : 0;
-        // KGE_TC_WS=1: add the k splits with the reduction kernel (the engine's way); the sum lands in
-        // the first slice of out and the other slices stay zero
-        const bool in_kernel_reduce = std::getenv("KGE_TC_WS") && splits > 1 && tile_n == 64;
-        DeviceBuffer dws(in_kernel_reduce ? (size_t)splits * m * n * 4 : 16), dwr(in_kernel_reduce ? (size_t)splits * m * 4 : 16);
         KGE_CUDA(cudaMemset(dout.p, 0, (size_t)splits * m * n * 4));
-        if (in_kernel_reduce) {
-            g.ws = dws.as<float>();
-            g.ws_rowsum = dwr.as<float>();
-        }
-        cudaEvent_t e0 = nullptr, e1 = nullptr;
-        for (int it = 0; it <= repeat && err == cudaSuccess; ++it) {
-            if (it == 1) {
-                KGE_CUDA(cudaEventCreate(&e0));
-                KGE_CUDA(cudaEventCreate(&e1));
-                KGE_CUDA(cudaEventRecord(e0, nullptr));
-            }
-            if (tile_n == 64) {
-                if (exact) err = rowsum ? tc::launch_pair<64, true, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, true, false>(&g, 1, splits, nullptr);
-                else err = rowsum ? tc::launch_pair<64, false, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, false, false>(&g, 1, splits, nullptr);
-            } else {
-                // the 128-column tile exists only in the unpipelined form
-                if (exact) err = rowsum ? tc::launch<128, true, true>(g, splits, nullptr) : tc::launch<128, true, false>(g, splits, nullptr);
-                else err = rowsum ? tc::launch<128, false, true>(g, splits, nullptr) : tc::launch<128, false, false>(g, splits, nullptr);
-            }
-        }
-        if (repeat > 0 && err == cudaSuccess) {
-            KGE_CUDA(cudaEventRecord(e1, nullptr));
-            KGE_CUDA(cudaEventSynchronize(e1));
-            float ms = 0.f;
-            KGE_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-            std::fprintf(stderr, "kge_op_tc_gemm m=%zu n=%zu k=%zu splits=%d: %.2f us per launch\n", m, n, k, splits, 1e3f * ms / repeat);
-            cudaEventDestroy(e0);
-            cudaEventDestroy(e1);
+        if (tile_n == 64) {
+            if (exact) err = rowsum ? tc::launch_pair<64, true, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, true, false>(&g, 1, splits, nullptr);
+            else err = rowsum ? tc::launch_pair<64, false, true>(&g, 1, splits, nullptr) : tc::launch_pair<64, false, false>(&g, 1, splits, nullptr);
+        } else {
+            // the 128-column tile exists only in the unpipelined form
+            if (exact) err = rowsum ? tc::launch<128, true, true>(g, splits, nullptr) : tc::launch<128, true, false>(g, splits, nullptr);
+            else err = rowsum ? tc::launch<128, false, true>(g, splits, nullptr) : tc::launch<128, false, false>(g, splits, nullptr);
         }
         KGE_CUDA(err);
         finish_kernels();
@@ -430,6 +401,78 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
         KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
         if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_gemm: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");
         to_host(out, dout, (size_t)splits * m * n * 4);
+    });
+}
+
+// Operator form of the plane-fed contraction (tc_planes.cuh) on host buffers.  The stored matrices
+// are split into their TF32-exact planes on the device, as the producing kernels of the training
+// step do, and the k splits (a thread-block cluster) are reduced inside the kernel.
+//   out[m, n] = epilogue( sum_k A[m, k] * B[n, k] )
+// a: stored [a_rows, a_cols] fp32; A[m, k] = a[m, k], or a[k, m] when a_mn_major.  a_exact: the
+// values are exact in TF32 (they came from fp16), one plane.  b likewise.  The upper plane is the
+// stored array itself (the tensor core ignores the low 13 bits of a TF32 operand);
+// hi_is_cleared: a copy with those bits cleared is used instead, which must give the same bits.
+// repeat > 0: the launch is repeated that many times between two events and *mean_us receives the
+// mean device time per launch.
+int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows, size_t a_cols, const float* b, int b_mn_major,
+                     size_t b_rows, size_t b_cols, size_t m, size_t n, size_t k, int epilogue, const float* x, int splits,
+                     int tile_n, int hi_is_cleared, int repeat, float* mean_us, float* out) {
+    return guarded(g_error, [&] {
+        require(a && b && out, "kge_op_tc_planes: null argument");
+        require(epilogue >= 0 && epilogue <= 2 && (epilogue == 0 || x), "kge_op_tc_planes: bad epilogue or missing x");
+        require(splits >= 1 && splits <= tc::kMaxClusterSplits, "kge_op_tc_planes: splits must be between 1 and 8");
+        require(tile_n == 64 || tile_n == 128, "kge_op_tc_planes: tile_n must be 64 or 128");
+        require(m > 0 && n > 0 && k > 0, "kge_op_tc_planes: empty problem");
+        require(a_rows >= (a_mn_major ? k : m) && a_cols >= (a_mn_major ? m : k), "kge_op_tc_planes: a is too small");
+        require(b_rows >= (b_mn_major ? k : n) && b_cols >= (b_mn_major ? n : k), "kge_op_tc_planes: b is too small");
+        require(a_cols % 4 == 0 && b_cols % 4 == 0, "kge_op_tc_planes: stored rows must be a multiple of 16 bytes");
+        const size_t na = a_rows * a_cols, nb = b_rows * b_cols;
+        DeviceBuffer da(na * 4), da_hi(na * 4), da_lo(na * 4), db(nb * 4), db_hi(nb * 4), db_lo(nb * 4);
+        DeviceBuffer dout(m * n * 4), dx(m * n * 4), dstatus(4);
+        to_device(da, a, na * 4);
+        to_device(db, b, nb * 4);
+        if (x) to_device(dx, x, m * n * 4);
+        KGE_CUDA(cudaMemset(dstatus.p, 0, 4));
+        tc::k_split_planes<<<std::min(blocks_for(na, 256), 1184u), 256>>>(da.as<float>(), na, da_hi.as<float>(), da_lo.as<float>());
+        tc::k_split_planes<<<std::min(blocks_for(nb, 256), 1184u), 256>>>(db.as<float>(), nb, db_hi.as<float>(), db_lo.as<float>());
+        KGE_CUDA(cudaGetLastError());
+        tc::PlaneProblem p{};
+        p.A = {hi_is_cleared ? da_hi.as<float>() : da.as<float>(), a_exact ? nullptr : da_lo.as<float>(), (long long)(a_cols * 4), a_mn_major ? 1 : 0};
+        p.B = {hi_is_cleared ? db_hi.as<float>() : db.as<float>(), db_lo.as<float>(), (long long)(b_cols * 4), b_mn_major ? 1 : 0};
+        tc::GemmArgs& g = p.g;
+        g.M = (int)m; g.N = (int)n; g.K = (int)k;
+        g.k_per_split = std::max(32, (int)(((k + splits - 1) / splits + 31) / 32 * 32));
+        g.epilogue = epilogue;
+        g.out = dout.as<float>(); g.out_blocks = nullptr; g.block_rows = 1;
+        g.ldc = (long long)n; g.split_stride = 0;
+        g.x_base = static_cast<const uint8_t*>(dx.p); g.x_row_stride_bytes = (long long)(n * 4);
+        g.status = dstatus.as<unsigned>();
+        const bool rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
+        tc::PlaneLaunch prepared;
+        KGE_CUDA(tc::prepare_planes(&p, 1, splits, tile_n, &prepared));
+        auto run = [&] { return rowsum ? tc::launch_prepared<true>(prepared, nullptr) : tc::launch_prepared<false>(prepared, nullptr); };
+        KGE_CUDA(run());
+        finish_kernels();
+        if (repeat > 0) {
+            cudaEvent_t e0 = nullptr, e1 = nullptr;
+            KGE_CUDA(cudaEventCreate(&e0));
+            KGE_CUDA(cudaEventCreate(&e1));
+            KGE_CUDA(cudaEventRecord(e0, nullptr));
+            cudaError_t err = cudaSuccess;
+            for (int it = 0; it < repeat && err == cudaSuccess; ++it) err = run();
+            KGE_CUDA(cudaEventRecord(e1, nullptr));
+            KGE_CUDA(cudaEventSynchronize(e1));
+            float ms = 0.f;
+            KGE_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            KGE_CUDA(err);
+            if (mean_us) *mean_us = 1e3f * ms / (float)repeat;
+        }
+        unsigned status = 0;
+        KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
+        if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_planes: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");
+        to_host(out, dout, m * n * 4);
     });
 }
 
@@ -442,7 +485,7 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
 // pool, where a raw cudaMalloc fragments or exceeds the pool's budget; a service with a fixed
 // device-memory reservation; code on a latency path where the implicit device synchronisation
 // of cudaMalloc / cudaFree is not acceptable.  For them the working memory is this fixed array
-// in the library's own device image.  Every GPU that loads the library holds it (about 290 KB)
+// in the library's own device image.  Every GPU that loads the library holds it (about 272 KB)
 // until the process exits.
 constexpr size_t kNoAllocMaxLookups = kMaxSortItems;  // 4096
 constexpr size_t kNoAllocMaxRows = 65536;
@@ -450,8 +493,6 @@ constexpr size_t kNoAllocMaxRows = 65536;
 struct NoAllocScratch {
     uint32_t perm[kNoAllocMaxLookups];      // lookups ordered by (row, position)
     uint32_t offsets[kNoAllocMaxRows + 1];  // segment start of each table row
-    uint32_t spare_perm[kNoAllocMaxLookups];
-    uint32_t spare_offsets[4];
 };
 
 static __device__ __align__(256) unsigned char g_no_alloc_scratch[sizeof(NoAllocScratch)];
@@ -492,8 +533,8 @@ int kge_op_scatter_add_rows_noalloc(const float* grad_rows, const uint32_t* indi
         cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
         // Every entry the second kernel reads (perm[0, n) and offsets[0, rows]) is rewritten by the
         // first, so nothing left by an earlier call is ever read and nothing needs clearing.
-        k_prepare_segments<<<1, 512, 0, stream>>>(indices, indices, indices, nullptr, (int)n, 0, (int)rows, 0, scratch->perm,
-                                                  scratch->offsets, scratch->spare_perm, scratch->spare_offsets, nullptr, nullptr, nullptr);
+        k_prepare_segments<<<1, 512, 0, stream>>>(indices, indices, nullptr, nullptr, (int)n, 0, (int)rows, 0, scratch->perm,
+                                                  scratch->offsets, nullptr, nullptr, nullptr, nullptr, nullptr);
         k_segment_sum_rows<<<(unsigned)rows, 128, 0, stream>>>(grad_rows, scratch->perm, scratch->offsets, width, grad_table);
         KGE_CUDA(cudaGetLastError());
     });

@@ -870,15 +870,17 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
         ent_off[r] = (uint32_t)lower_bound_key(keys, n, (unsigned long long)r << 32);
     __syncthreads();
 
-    n = B;
-    padded = 1;
-    while (padded < n) padded <<= 1;
-    for (int i = threadIdx.x; i < padded; i += blockDim.x)
-        keys[i] = i < n ? (((unsigned long long)relation[i] << 32) | (unsigned)i) : ~0ull;
-    bitonic_sort(keys, padded);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) rel_perm[i] = (uint32_t)keys[i];
-    for (int r = threadIdx.x; r <= n_rel; r += blockDim.x)
-        rel_off[r] = (uint32_t)lower_bound_key(keys, n, (unsigned long long)r << 32);
+    if (rel_perm) {  // null: the caller has no relation lookups (the operator form of the scatter-add)
+        n = B;
+        padded = 1;
+        while (padded < n) padded <<= 1;
+        for (int i = threadIdx.x; i < padded; i += blockDim.x)
+            keys[i] = i < n ? (((unsigned long long)relation[i] << 32) | (unsigned)i) : ~0ull;
+        bitonic_sort(keys, padded);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) rel_perm[i] = (uint32_t)keys[i];
+        for (int r = threadIdx.x; r <= n_rel; r += blockDim.x)
+            rel_off[r] = (uint32_t)lower_bound_key(keys, n, (unsigned long long)r << 32);
+    }
     if (!remote) return;
     __syncthreads();
 

@@ -1,0 +1,584 @@
+// The tensor-core contraction fed straight by the TMA unit (tcgen05, sm_100a).
+//
+//   acc[m, n] = sum_k A[m, k] * B[n, k]          fp32 operands as TF32-exact planes, fp32 result
+//
+// Same arithmetic as tc_gemm.cuh (three TF32 products of the hi / lo parts of each operand, every
+// 32-deep k slice accumulated alone in TMEM and added in registers with round-to-nearest), but
+// nobody in the block touches the operands: the kernels that PRODUCE an operand write its two
+// TF32-exact parts to global memory once ("planes": hi = x with the low 13 significand bits
+// cleared, lo = x - hi cut likewise; an operand that came from fp16 storage is one plane), and one
+// thread moves [rows x 32 k] boxes of those planes into shared memory with cp.async.bulk.tensor
+// under the 128-byte swizzle, which is exactly the layout the UMMA shared-memory descriptors read:
+//
+//   k-major operand  (stored [mn][k]):  one box of `rows` 128-byte rows, CU_TENSOR_MAP_SWIZZLE_128B;
+//                                        descriptor "K-major, SWIZZLE_128B", 8-row groups 1024 B
+//                                        apart, 32 B per 8-deep k step;
+//   mn-major operand (stored [k][mn]):  rows / 32 boxes of 32 k-rows x 32 mn (4 KB each, 4096 B
+//                                        apart), CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B: 32-bit
+//                                        operands are transposed by the tensor core only from the
+//                                        layout that swizzles 32-byte chunks; descriptor "MN-major,
+//                                        SWIZZLE_128B_BASE32B", leading offset 4096 B between the
+//                                        boxes, 512 B between groups of 4 k-rows, 1024 B per k step.
+//
+// The tensor core reads the upper 19 bits of a 32-bit TF32 operand and ignores the rest (checked
+// bit for bit on the B200 against planes with those bits cleared), so the unmodified fp32 array
+// serves as the hi plane and a producer only adds the lo plane.
+//
+// Warp roles (10 warps): warp 0 one thread issues the copies of slice j into ring stage j % 3 once
+// the MMAs that read it have completed; warp 1 one thread issues the slice's tcgen05.mma
+// instructions into TMEM tile j % 4 and commits them; warps 2-9 read the tile (32 lanes x 32
+// columns each) and add it to registers.  With ROWSUM they also add up the rows of A from the
+// staged tile (the L2 backward needs rowsum(A) . X).  The groups meet only at mbarriers; every wait
+// is bounded.  The k range may be split over the blocks of a thread-block cluster, reduced through
+// distributed shared memory in split order, as in tc_gemm.cuh.
+#pragma once
+
+#include <algorithm>
+
+#include "tc_gemm.cuh"
+
+namespace kge {
+namespace tc {
+
+struct PlaneOperand {
+    const float* hi;             // TF32-exact upper part (or the value itself when it is exact in TF32)
+    const float* lo;             // TF32-exact remainder; null = the operand has one plane
+    long long row_stride_bytes;  // multiple of 16
+    int mn_major;                // 0: stored [mn][k], k contiguous; 1: stored [k][mn], mn contiguous
+};
+
+// One contraction: the planes of both operands and, in `g`, sizes, k split, epilogue and output
+// (g.A and g.B are not used).
+struct PlaneProblem {
+    PlaneOperand A, B;
+    GemmArgs g;
+};
+
+// Folded into the epilogue of hidden = value + feature . W: the lookups of the step
+// (src/poplar_kge.cpp:676-684).  `perm` lists the lookups ordered by the hidden row they read,
+// `off[r]` is where row r's begin.  Lookup e < B is head lookup e: pred[e] = f(row, relation row);
+// lookup e >= B is tail lookup e - B: the row goes to slot (e - B) % a2a of the destination shard
+// (e - B) / a2a.  Null `perm`: no routing.
+struct RouteArgs {
+    const uint32_t* perm;
+    const uint32_t* off;
+    const uint32_t* relation;
+    const float* rel_table;
+    float* const* send_dst;
+    float* pred;
+    int B, a2a, score_fn;
+};
+
+struct PlanePair {
+    PlaneProblem p[2];
+    int tiles_m0;  // blocks with blockIdx.x < tiles_m0 work on p[0], the others on p[1]
+    ExchangeSync sync;
+    int wait_kind, signal_kind;
+    RouteArgs route;
+    int n_stages[2];  // ring stages of each problem (2 to kPlMaxStages), as many as the shared memory holds
+};
+
+struct PlaneMaps {
+    CUtensorMap a_hi[2], a_lo[2], b_hi[2], b_lo[2];
+};
+
+constexpr int kPlMaxStages = 4;
+constexpr int kPlAccWarps = 8;
+constexpr int kPlThreads = 32 * (2 + kPlAccWarps);
+constexpr int kPlTmemSlots = 4;
+
+// Dynamic shared memory of a block: the operand ring (the partial rows of a cluster's k split land
+// in the same memory once the ring is idle), after alignment to 1024 bytes.
+constexpr size_t kPlRingBytes = 220 * 1024;
+constexpr size_t plane_smem_bytes() { return 1024 + kPlRingBytes; }
+static_assert(2 * (size_t)(kBM + kMaxClusterRows) * (128 + 1) * 4 <= kPlRingBytes, "the sent and the received rows fit the ring");
+
+// MN-major tile of 32-bit elements: atoms of 4 k-rows x 128 B (32 fp32 along mn) whose 32-byte
+// chunks are XOR-ed with the k-row index modulo 4; the next 32 mn are 4096 B further (leading byte
+// offset), the next 4 k 512 B further (stride byte offset).  Layout type 1 = SWIZZLE_128B_BASE32B.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(4096 >> 4) << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
+
+// The copies of one [ROWS x 32 k] slice of one plane.
+template <int ROWS>
+__device__ __forceinline__ void tma_plane_tile(uint8_t* dst, const CUtensorMap* map, int mn_major, int mn0, int k0, uint64_t* bar) {
+    if (!mn_major) {
+        tma_load_2d(dst, map, k0, mn0, bar);
+    } else {
+#pragma unroll
+        for (int j = 0; j < ROWS / 32; ++j) tma_load_2d(dst + j * 4096, map, mn0 + 32 * j, k0, bar);
+    }
+}
+
+// The sum of 16 of the 32 k of row `row` of a staged A tile, added in k order.  The upper plane
+// holds the operand's values themselves (the tensor core ignores their low bits), so it alone is read.
+__device__ __forceinline__ float staged_row_sum(const uint8_t* tile, int mn_major, int row, int half) {
+    float s = 0.f;
+    if (!mn_major) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t off = (uint32_t)row * 128u + ((((uint32_t)(half * 4 + c)) ^ ((uint32_t)row & 7u)) << 4);
+            const float4 v = *reinterpret_cast<const float4*>(tile + off);
+            s += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+        const uint32_t base = (uint32_t)(row >> 5) * 4096u, r = (uint32_t)row & 31u;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t kk = (uint32_t)(half * 16 + i);
+            s += *reinterpret_cast<const float*>(tile + base + kk * 128u + (((r >> 3) ^ (kk & 3u)) << 5) + ((r & 7u) << 2));
+        }
+    }
+    return s;
+}
+
+// The lookups that read hidden row m, for the four columns n .. n+3 whose values are `h`.
+__device__ __forceinline__ void route_four(const RouteArgs& rt, int m, int n, int D, const float (&h)[4]) {
+    const uint32_t q0 = rt.off[m], q1 = rt.off[m + 1];
+    for (uint32_t q = q0; q < q1; ++q) {
+        const uint32_t e = rt.perm[q];
+        if (e >= (uint32_t)rt.B) {
+            const uint32_t j = e - (uint32_t)rt.B, dst = j / (uint32_t)rt.a2a, slot = j - dst * (uint32_t)rt.a2a;
+            *reinterpret_cast<float4*>(rt.send_dst[dst] + (size_t)slot * D + n) = make_float4(h[0], h[1], h[2], h[3]);
+        } else {
+            // TransE / DistMult: elementwise with the relation row (ComplEx mixes the two halves of
+            // the row and keeps its own kernel)
+            const float4 r = *reinterpret_cast<const float4*>(rt.rel_table + (size_t)rt.relation[e] * D + n);
+            float4 o;
+            if (rt.score_fn == 0) o = make_float4(h[0] + r.x, h[1] + r.y, h[2] + r.z, h[3] + r.w);
+            else o = make_float4(h[0] * r.x, h[1] * r.y, h[2] * r.z, h[3] * r.w);
+            *reinterpret_cast<float4*>(rt.pred + (size_t)e * D + n) = o;
+        }
+    }
+}
+
+// Epilogue and store of four neighbouring output columns, then the lookups that read them.
+__device__ __forceinline__ void finish_four_routed(const GemmArgs& g, const RouteArgs& rt, float* out_base, int m, int n,
+                                                   float (&acc)[4], const float (&x)[4], float rs) {
+    finish_four(g, out_base, m, n, acc, x, rs);
+    if (rt.perm) route_four(rt, m, n, g.N, acc);
+}
+
+// 32 consecutive accumulator columns of this thread's TMEM lane, without waiting for them.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+template <int BN, bool ROWSUM>
+__global__ void __launch_bounds__(kPlThreads, 1)
+k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneMaps maps) {
+    static_assert(BN == 64 || BN == 128, "tile widths: 64 or 128 columns");
+    constexpr int CPT = BN / 2;  // accumulator columns per accumulating thread: a warp reads one half of its 32 lanes' columns
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[kPlMaxStages], bar_empty[kPlMaxStages], bar_acc_ready[kPlTmemSlots], bar_acc_free[kPlTmemSlots];
+    __shared__ uint64_t bar_reduce;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float s_rowsum[2][kBM];
+
+    const int which = (int)blockIdx.x >= gp.tiles_m0 ? 1 : 0;
+    const PlaneProblem& pp = gp.p[which];
+    const GemmArgs& g = pp.g;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = ((int)blockIdx.x - (which ? gp.tiles_m0 : 0)) * kBM, n0 = blockIdx.y * BN;
+    const unsigned total_blocks = gridDim.x * gridDim.y * gridDim.z;
+    if (n0 >= g.N || m0 >= g.M) {  // the two problems may differ in size (a whole cluster leaves together)
+        grid_dependency_sync();
+        exchange_signal(gp.sync, gp.signal_kind, total_blocks);
+        return;
+    }
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128;
+    const int k_begin = blockIdx.z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
+    const int n_slices = max(0, (k_end - k_begin + kBK - 1) / kBK);
+    const bool a_two = pp.A.lo != nullptr, b_two = pp.B.lo != nullptr;
+    // a ring stage: A hi [| A lo] | B hi [| B lo]
+    const uint32_t off_b = (a_two ? 2u : 1u) * kATile, stage_bytes = off_b + (b_two ? 2u : 1u) * kBTile;
+    const int n_stages = gp.n_stages[which];
+
+    if (tid == 0) {
+        for (int s = 0; s < kPlMaxStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], ROWSUM ? 1 + kPlAccWarps : 1);
+        }
+        for (int t = 0; t < kPlTmemSlots; ++t) {
+            mbar_init(&bar_acc_ready[t], 1);
+            mbar_init(&bar_acc_free[t], kPlAccWarps);
+        }
+        mbar_init(&bar_reduce, 1);
+        mbar_fence_init();
+        // the TMA unit fetches the descriptors while the predecessor kernel still runs
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.a_hi[which])) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.b_hi[which])) : "memory");
+        if (a_two) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.a_lo[which])) : "memory");
+        if (b_two) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.b_lo[which])) : "memory");
+    }
+    constexpr int n_slots = kPlTmemSlots;
+    if (warp == 0) tmem_alloc(&tmem_slot, (uint32_t)(n_slots * BN));
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    grid_dependency_sync();
+    exchange_wait(gp.sync, gp.wait_kind);
+    const uint32_t tmem_base = tmem_slot;
+
+    float acc[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+    float row_part = 0.f;
+
+    if (warp == 0) {
+        for (int kc = 0; kc < n_slices; ++kc) {
+            const int s = kc % n_stages, use = kc / n_stages;
+            if (use >= 1) mbar_wait(&bar_empty[s], (uint32_t)((use - 1) & 1), g.status, 6u);
+            if (lane == 0) {
+                uint8_t* stage = smem + (size_t)s * stage_bytes;
+                const int k0 = k_begin + kc * kBK;
+                mbar_arrive_expect(&bar_full[s], stage_bytes);
+                tma_plane_tile<kBM>(stage, &maps.a_hi[which], pp.A.mn_major, m0, k0, &bar_full[s]);
+                if (a_two) tma_plane_tile<kBM>(stage + kATile, &maps.a_lo[which], pp.A.mn_major, m0, k0, &bar_full[s]);
+                tma_plane_tile<BN>(stage + off_b, &maps.b_hi[which], pp.B.mn_major, n0, k0, &bar_full[s]);
+                if (b_two) tma_plane_tile<BN>(stage + off_b + kBTile, &maps.b_lo[which], pp.B.mn_major, n0, k0, &bar_full[s]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        const uint32_t idesc = make_idesc_tf32(kBM, BN) | (pp.A.mn_major ? (1u << 15) : 0u) | (pp.B.mn_major ? (1u << 16) : 0u);
+        const uint64_t a_step = pp.A.mn_major ? (1024 >> 4) : (32 >> 4), b_step = pp.B.mn_major ? (1024 >> 4) : (32 >> 4);
+        for (int kc = 0; kc < n_slices; ++kc) {
+            const int s = kc % n_stages, t = kc % n_slots;
+            mbar_wait(&bar_full[s], (uint32_t)((kc / n_stages) & 1), g.status, 3u);
+            if (kc >= n_slots) mbar_wait(&bar_acc_free[t], (uint32_t)(((kc / n_slots) - 1) & 1), g.status, 4u);
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t a_hi = smem_u32(smem + (size_t)s * stage_bytes), a_lo = a_hi + kATile, b_hi = a_hi + off_b, b_lo = b_hi + kBTile;
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(t * BN);
+                const uint64_t da_hi = pp.A.mn_major ? make_mnmajor_sw128_desc(a_hi) : make_kmajor_sw128_desc(a_hi);
+                const uint64_t da_lo = pp.A.mn_major ? make_mnmajor_sw128_desc(a_lo) : make_kmajor_sw128_desc(a_lo);
+                const uint64_t db_hi = pp.B.mn_major ? make_mnmajor_sw128_desc(b_hi) : make_kmajor_sw128_desc(b_hi);
+                const uint64_t db_lo = pp.B.mn_major ? make_mnmajor_sw128_desc(b_lo) : make_kmajor_sw128_desc(b_lo);
+                uint32_t accumulate = 0u;
+#pragma unroll
+                for (int ks = 0; ks < kBK / 8; ++ks) {
+                    const uint64_t ka = (uint64_t)ks * a_step, kb = (uint64_t)ks * b_step;
+                    // small cross terms first, the large hi*hi term last
+                    if (b_two) { umma_tf32(tmem_acc, da_hi + ka, db_lo + kb, idesc, accumulate); accumulate = 1u; }
+                    if (a_two) { umma_tf32(tmem_acc, da_lo + ka, db_hi + kb, idesc, accumulate); accumulate = 1u; }
+                    umma_tf32(tmem_acc, da_hi + ka, db_hi + kb, idesc, accumulate);
+                    accumulate = 1u;
+                }
+                umma_commit(&bar_empty[s]);
+                umma_commit(&bar_acc_ready[t]);
+            }
+            __syncwarp();
+        }
+    } else {
+        const int quarter = warp & 3, half = (warp - 2) >> 2, row = quarter * 32 + lane;
+        auto add_rows = [&](int kc) {
+            const int s = kc % n_stages;
+            mbar_wait(&bar_full[s], (uint32_t)((kc / n_stages) & 1), g.status, 7u);
+            const uint8_t* stage = smem + (size_t)s * stage_bytes;
+            row_part += staged_row_sum(stage, pp.A.mn_major, row, half);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_empty[s]);
+        };
+        if (ROWSUM && n_slices > 0) add_rows(0);
+        for (int kc = 0; kc < n_slices; ++kc) {
+            if (ROWSUM && kc + 1 < n_slices) add_rows(kc + 1);  // one slice ahead of the drain: the stage is not held back
+            const int t = kc % n_slots;
+            mbar_wait(&bar_acc_ready[t], (uint32_t)((kc / n_slots) & 1), g.status, 1u);
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * BN + half * CPT);
+            uint32_t r[CPT / 32][32];
+#pragma unroll
+            for (int c = 0; c < CPT / 32; ++c) tmem_ld32_issue(taddr + (uint32_t)(c * 32), r[c]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_acc_free[t]);
+#pragma unroll
+            for (int c = 0; c < CPT / 32; ++c)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(r[c][j]);
+        }
+        if (ROWSUM) s_rowsum[half][row] = row_part;
+    }
+    __syncthreads();  // every slice has been read from TMEM (so the ring is idle); the row sums are in place
+
+    const bool acc_warp = warp >= 2;
+    const int row = (warp & 3) * 32 + lane, m = m0 + row;
+    const int nc0 = n0 + (acc_warp ? ((warp - 2) >> 2) * CPT : 0);  // first output column of an accumulating thread
+    if (g.cluster_splits > 1) {
+        // Block z of the cluster finishes rows z * rows_each ... of the tile.  Every block lays its
+        // partial tile out in its own (now idle) operand ring, one slot per owner, and hands each
+        // slot to the copy engine (cp.async.bulk from its shared memory into the owner's), which
+        // reports the bytes to the owner's mbarrier; the owner then adds the slots in split order.
+        // A block may be written to only after it has left its k loop: that is the first cluster
+        // barrier (arrive here, wait before the copies are issued).
+        cluster_arrive_relaxed();
+        const int n_split = g.cluster_splits, rank = (int)cluster_rank();
+        const int rows_each = (kBM + n_split - 1) / n_split;
+        const uint32_t slot_floats = (uint32_t)rows_each * BN + (uint32_t)((rows_each + 3) & ~3);  // rows | row sums
+        const uint32_t slot_bytes = slot_floats * 4u;
+        float* staging = reinterpret_cast<float*>(smem);                   // [owner][rows_each][BN] + row sums, what I send
+        float* receive = staging + (size_t)n_split * slot_floats;         // [source][rows_each][BN] + row sums, what I own
+        if (tid == 0) mbar_arrive_expect(&bar_reduce, (uint32_t)(n_split - 1) * slot_bytes);
+        if (acc_warp) {
+            // 16-byte chunk c of tile row `row` lies at chunk c ^ (row & 7): the lanes of a warp hold
+            // 32 different rows, and this spreads their stores over all banks
+            const int owner = row / rows_each, local = row - owner * rows_each;
+            float* mine = staging + (size_t)owner * slot_floats + (size_t)local * BN;
+            const int c0 = (nc0 - n0) >> 2;
+#pragma unroll
+            for (int j = 0; j < CPT; j += 4)
+                *reinterpret_cast<float4*>(mine + (((c0 + (j >> 2)) ^ (row & 7)) << 2)) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            if (ROWSUM && nc0 == n0) staging[(size_t)owner * slot_floats + (size_t)rows_each * BN + local] = s_rowsum[0][row] + s_rowsum[1][row];
+        }
+        fence_async_shared();  // the copy engine reads what the threads have just written
+        const int r_begin = rank * rows_each, r_end = min(kBM, r_begin + rows_each);
+        constexpr int kQuads = BN / 4;
+        constexpr int kUnits = (64 * kQuads + kPlThreads - 1) / kPlThreads;  // at most 64 rows x BN / 4 quads per block
+        const int n_units = max(0, r_end - r_begin) * kQuads;
+        float xv[kUnits][4];
+#pragma unroll
+        for (int i = 0; i < kUnits; ++i) {  // the epilogue's second operand is fetched while the rows travel
+            const int u = tid + i * kPlThreads;
+            const int mm = m0 + r_begin + u / kQuads, nn = n0 + (u % kQuads) * 4;
+            xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
+            if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i]);
+        }
+        __syncthreads();
+        cluster_wait();
+        if (warp == 0 && lane < n_split && lane != rank) {
+            const uint32_t dst = cluster_map(smem_u32(receive + (size_t)rank * slot_floats), (uint32_t)lane);
+            const uint32_t bar = cluster_map(smem_u32(&bar_reduce), (uint32_t)lane);
+            asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dst), "r"(smem_u32(staging + (size_t)lane * slot_floats)), "r"(slot_bytes), "r"(bar) : "memory");
+        }
+        mbar_wait(&bar_reduce, 0u, g.status, 8u);
+        // Nobody may leave while the copy engine can still read its slots.  Every block reports here
+        // that all of its bytes have arrived and checks before it exits that all blocks have.
+        cluster_arrive_relaxed();
+#pragma unroll
+        for (int i = 0; i < kUnits; ++i) {
+            const int u = tid + i * kPlThreads;
+            if (u >= n_units) continue;
+            const int local = u / kQuads, q = u % kQuads, trow = r_begin + local;
+            const int chunk = (q ^ (trow & 7)) << 2;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            float row_total = 0.f;
+            for (int z = 0; z < n_split; ++z) {
+                const float* slot = z == rank ? staging + (size_t)rank * slot_floats : receive + (size_t)z * slot_floats;
+                const float4 v = *reinterpret_cast<const float4*>(slot + (size_t)local * BN + chunk);
+                sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+                if (ROWSUM) row_total += slot[(size_t)rows_each * BN + local];
+            }
+            const int mm = m0 + trow, nn = n0 + q * 4;
+            if (mm < g.M && nn < g.N) finish_four_routed(g, gp.route, g.out, mm, nn, sum, xv[i], row_total);
+        }
+        cluster_wait();
+    } else if (acc_warp && m < g.M && nc0 < g.N) {
+        float* out_base = g.out_blocks ? nullptr : g.out + (size_t)blockIdx.z * g.split_stride;
+        const float rs = ROWSUM ? s_rowsum[0][row] + s_rowsum[1][row] : 0.f;
+#pragma unroll
+        for (int j = 0; j < CPT; j += 4) {
+            float four[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
+            float x[4];
+            if (nc0 + j < g.N) {
+                load_x_four(g, m, nc0 + j, x);
+                finish_four_routed(g, gp.route, out_base, m, nc0 + j, four, x, rs);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, (uint32_t)(n_slots * BN));
+    exchange_signal(gp.sync, gp.signal_kind, total_blocks);
+}
+
+// Splits fp32 values into the two planes the contraction reads (for operands that no kernel of the
+// step produces: parameters written by the host, operator inputs).
+static __global__ void __launch_bounds__(256) k_split_planes(const float* __restrict__ x, size_t n, float* __restrict__ hi, float* __restrict__ lo) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[e], h = tf32_hi(v);
+        hi[e] = h;
+        lo[e] = tf32_hi(v - h);
+    }
+}
+
+// What a producing kernel stores for four neighbouring values.
+__device__ __forceinline__ void store_planes4(float* hi, float* lo, size_t e, float a, float b, float c, float d) {
+    const float4 h = make_float4(tf32_hi(a), tf32_hi(b), tf32_hi(c), tf32_hi(d));
+    *reinterpret_cast<float4*>(hi + e) = h;
+    *reinterpret_cast<float4*>(lo + e) = make_float4(tf32_hi(a - h.x), tf32_hi(b - h.y), tf32_hi(c - h.z), tf32_hi(d - h.w));
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+
+// State that CUDA keeps per device (function attributes, occupancy answers) is cached per device.
+constexpr int kMaxDeviceOrdinals = 64;
+inline int current_device_slot() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDeviceOrdinals) return -1;
+    return device;
+}
+
+// The map of one plane: boxes of [rows x 32 k] (k-major) or [32 k x 32 mn] (mn-major) under the
+// 128-byte swizzle, zeros outside the matrix.
+inline cudaError_t make_plane_map(const float* base, const PlaneOperand& op, int mn, int k, int rows, CUtensorMap* map) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return cudaErrorNotSupported;
+    if (reinterpret_cast<uintptr_t>(base) % 16 || op.row_stride_bytes % 16) return cudaErrorInvalidValue;
+    const cuuint64_t dims[2] = {(cuuint64_t)(op.mn_major ? mn : k), (cuuint64_t)(op.mn_major ? k : mn)};
+    const cuuint64_t strides[1] = {(cuuint64_t)op.row_stride_bytes};
+    const cuuint32_t box[2] = {32u, (cuuint32_t)(op.mn_major ? kBK : rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+inline bool planes_aligned(const PlaneOperand& op) {
+    return reinterpret_cast<uintptr_t>(op.hi) % 16 == 0 && reinterpret_cast<uintptr_t>(op.lo) % 16 == 0 && op.row_stride_bytes % 16 == 0;
+}
+
+template <int BN, bool ROWSUM>
+inline cudaError_t configure_planes() {
+    static bool configured[kMaxDeviceOrdinals] = {};
+    const int slot = current_device_slot();
+    if (slot >= 0 && configured[slot]) return cudaSuccess;
+    cudaError_t err = cudaFuncSetAttribute(k_tc_planes<BN, ROWSUM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plane_smem_bytes());
+    if (err == cudaSuccess && slot >= 0) configured[slot] = true;
+    return err;
+}
+
+// How many clusters of `splits` blocks of k_tc_planes the current device holds at once (one block
+// per SM whatever the tile width, so one instantiation answers for all).
+inline int max_resident_plane_clusters(int splits) {
+    static int cached[kMaxDeviceOrdinals][kMaxClusterSplits + 1] = {};
+    static bool known[kMaxDeviceOrdinals][kMaxClusterSplits + 1] = {};
+    if (splits < 1 || splits > kMaxClusterSplits) return 0;
+    const int slot = current_device_slot();
+    if (slot >= 0 && known[slot][splits]) return cached[slot][splits];
+    int n = 0;
+    if (configure_planes<128, false>() == cudaSuccess) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(1, 1, splits);
+        config.blockDim = dim3(kPlThreads);
+        config.dynamicSmemBytes = plane_smem_bytes();
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 1;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = (unsigned)splits;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, k_tc_planes<128, false>, &config) != cudaSuccess) {
+            n = 0;
+            (void)cudaGetLastError();
+        }
+    }
+    if (slot >= 0) {
+        known[slot][splits] = true;
+        cached[slot][splits] = n;
+    }
+    return n;
+}
+
+// A launch with its tensor maps encoded (encoding costs the host a few microseconds per map; a
+// launch that is repeated, or captured into a graph, pays it once).
+struct PlaneLaunch {
+    PlanePair gp;
+    PlaneMaps maps;
+    dim3 grid;
+    int splits, tile_n;
+};
+
+// One or two contractions of the same kind in one launch, tiles of 128 x tile_n (64 or 128).
+// splits > 1: the blocks of a tile form a cluster (at most kMaxClusterSplits) and g.k_per_split
+// must be set accordingly by the caller.
+inline cudaError_t prepare_planes(const PlaneProblem* problems, int n_problems, int splits, int tile_n, PlaneLaunch* out,
+                                  const ExchangeSync& sync = ExchangeSync{}, int wait_kind = -1, int signal_kind = -1,
+                                  const RouteArgs* route = nullptr) {
+    if (splits < 1 || splits > kMaxClusterSplits || (tile_n != 64 && tile_n != 128)) return cudaErrorInvalidValue;
+    PlanePair& gp = out->gp;
+    gp = PlanePair{};
+    gp.p[0] = problems[0];
+    gp.p[1] = problems[n_problems > 1 ? 1 : 0];
+    gp.tiles_m0 = (problems[0].g.M + kBM - 1) / kBM;
+    gp.sync = sync;
+    gp.wait_kind = wait_kind;
+    gp.signal_kind = signal_kind;
+    if (route) gp.route = *route;
+    int tiles_m = gp.tiles_m0, tiles_n = (problems[0].g.N + tile_n - 1) / tile_n;
+    if (n_problems > 1) {
+        tiles_m += (problems[1].g.M + kBM - 1) / kBM;
+        tiles_n = std::max(tiles_n, (problems[1].g.N + tile_n - 1) / tile_n);
+    }
+    for (int i = 0; i < 2; ++i) {
+        PlaneProblem& q = gp.p[i];
+        q.g.ws = nullptr;
+        q.g.cluster_splits = splits > 1 ? splits : 0;
+        if (!planes_aligned(q.A) || !planes_aligned(q.B)) return cudaErrorInvalidValue;
+        cudaError_t err = make_plane_map(q.A.hi, q.A, q.g.M, q.g.K, kBM, &out->maps.a_hi[i]);
+        if (err == cudaSuccess) err = make_plane_map(q.A.lo ? q.A.lo : q.A.hi, q.A, q.g.M, q.g.K, kBM, &out->maps.a_lo[i]);
+        if (err == cudaSuccess) err = make_plane_map(q.B.hi, q.B, q.g.N, q.g.K, tile_n, &out->maps.b_hi[i]);
+        if (err == cudaSuccess) err = make_plane_map(q.B.lo ? q.B.lo : q.B.hi, q.B, q.g.N, q.g.K, tile_n, &out->maps.b_lo[i]);
+        if (err != cudaSuccess) return err;
+        const size_t stage = (size_t)(q.A.lo ? 2 : 1) * kBM * 128 + (size_t)(q.B.lo ? 2 : 1) * tile_n * 128;
+        gp.n_stages[i] = (int)std::min<size_t>(kPlMaxStages, kPlRingBytes / stage);
+    }
+    out->grid = dim3(tiles_m, tiles_n, splits);
+    out->splits = splits;
+    out->tile_n = tile_n;
+    return cudaSuccess;
+}
+
+template <bool ROWSUM>
+inline cudaError_t launch_prepared(const PlaneLaunch& l, cudaStream_t stream) {
+    if (l.tile_n == 128) {
+        cudaError_t err = configure_planes<128, ROWSUM>();
+        if (err != cudaSuccess) return err;
+        return launch_dependent_cluster(k_tc_planes<128, ROWSUM>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
+                                        (unsigned)l.splits, l.gp, l.maps);
+    }
+    cudaError_t err = configure_planes<64, ROWSUM>();
+    if (err != cudaSuccess) return err;
+    return launch_dependent_cluster(k_tc_planes<64, ROWSUM>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
+                                    (unsigned)l.splits, l.gp, l.maps);
+}
+
+template <bool ROWSUM>
+inline cudaError_t launch_planes(const PlaneProblem* problems, int n_problems, int splits, int tile_n, cudaStream_t stream,
+                                 const ExchangeSync& sync = ExchangeSync{}, int wait_kind = -1, int signal_kind = -1,
+                                 const RouteArgs* route = nullptr) {
+    PlaneLaunch l;
+    cudaError_t err = prepare_planes(problems, n_problems, splits, tile_n, &l, sync, wait_kind, signal_kind, route);
+    if (err != cudaSuccess) return err;
+    return launch_prepared<ROWSUM>(l, stream);
+}
+
+}  // namespace tc
+}  // namespace kge

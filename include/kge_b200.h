@@ -179,6 +179,23 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
                    size_t n, size_t k, int epilogue, const float* x, int splits, int tile_n, float* out);
 
 /*
+ * The same contraction in the form the training step runs: both operands are given to the kernel
+ * as TF32-exact planes in device memory (made here from the host arrays; in the step the producing
+ * kernels write them) and the TMA unit feeds the tensor core directly.  a: stored [a_rows, a_cols]
+ * fp32, A[m, k] = a[m, k] or a[k, m] when a_mn_major; a_exact: every value is exact in TF32 (e.g. it
+ * came from fp16 storage).  b likewise.  Stored rows must be multiples of 16 bytes.  splits (1-8)
+ * blocks share a tile's k range as one thread-block cluster; tile_n (64 or 128) is the tile's width;
+ * out is [m, n].  The upper plane is the stored array itself, since the tensor core ignores the low
+ * 13 bits of a TF32 operand; hi_is_cleared uses a copy with those bits cleared instead (same
+ * result, bit for bit).  repeat > 0: *mean_us receives the mean device time of `repeat` further
+ * launches (for the microbench; mean_us may be NULL).
+ */
+int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows, size_t a_cols, const float* b,
+                     int b_mn_major, size_t b_rows, size_t b_cols, size_t m, size_t n, size_t k, int epilogue,
+                     const float* x, int splits, int tile_n, int hi_is_cleared, int repeat, float* mean_us,
+                     float* out);
+
+/*
  * kge_op_scatter_add_rows for callers that cannot allocate device memory.  It has no counterpart
  * in the reference.  The operator's working memory (the sorted lookups and the per-row segment
  * starts) lives in a fixed array inside the library's device image instead of coming from
@@ -190,7 +207,7 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
  *     the caller; the work is queued on `cuda_stream` (a cudaStream_t, or NULL for the default
  *     stream) and the call returns without waiting for it.
  *   - Limits: n <= 4096 lookups, rows <= 65536; larger sizes are refused with KGE_INVALID_ARGUMENT.
- *     The array costs about 290 KB on every GPU that loads the library, until the process exits.
+ *     The array costs about 272 KB on every GPU that loads the library, until the process exits.
  *   - An index >= rows cannot be refused here (the indices are on the device): it is ignored.
  *   - The first call on a device looks up the array's address on that device (the device must be
  *     current); make that first call before starting any stream capture.

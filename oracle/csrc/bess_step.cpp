@@ -1,7 +1,8 @@
 // CPU restatement of the reference's sharded training step in C++ / OpenMP, float32.
 //
 // TEST INFRASTRUCTURE ONLY: the timed CPU baseline of bench.py and a second checker beside
-// oracle/step_oracle.py (which pins it: tests compare the two).  It follows the reference's
+// oracle/step_oracle.py, which pins it: tests/test_oracle_cpu.py compares the two on every
+// score / loss variant (test_compiled_restatement_agrees_with_the_pinned_oracle).  It follows the reference's
 // Model::trainStep (src/poplar_kge.cpp:664-707): gather rows (:405-410), hidden = value +
 // feature.W (:439-467), lookups and exchange (:676-681, src/pag/pag.cpp:915-935), predicted
 // tail and score (:488-613; distances as in src/poplar_extensions/l{1,2}distance.codelet.cpp),

@@ -238,3 +238,44 @@ def test_reference_distance_code_agrees_with_the_oracle():
     a64, b64, g64 = a.astype(np.float64), b.astype(np.float64), g.astype(np.float64)
     np.testing.assert_allclose(g1, so.l1_distance_grad(a64, b64, g64), rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(g2, so.l2_distance_grad(a64, b64, so.l2_distance(a64, b64), g64), rtol=1e-4, atol=1e-5)
+
+
+CPP_VARIANTS = [
+    dict(score_fn="TransE", distance_fn="L1", loss_type="logsigmoid"),
+    dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", correction_weight=1.0),
+    dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid"),
+    dict(score_fn="ComplEx", distance_fn="MatMul", loss_type="softmax", correction_weight=0.5, share_feature_networks=False),
+]
+
+
+@pytest.mark.parametrize("variant", CPP_VARIANTS, ids=lambda v: f"{v['score_fn']}-{v['distance_fn']}-{v['loss_type']}")
+def test_compiled_restatement_agrees_with_the_pinned_oracle(variant):
+    """oracle/csrc/bess_step.cpp (float32, C++/OpenMP: the timed CPU baseline and the checker of the
+    full-size GPU cases) against the float64 numpy oracle that the reference's fixtures pin: two
+    steps from a warm state, losses and every state tensor.  Bound 5e-6 of the tensor's rms (the
+    two agree to about 1e-6; float32 rounding of one step is 1e-7 per operation)."""
+    from helpers import random_batch, random_state
+    from oracle.cpp_oracle import LIB_PATH, CppOracle
+
+    if not LIB_PATH.exists():
+        pytest.skip("oracle/_build/libbess_oracle.so has not been built (python oracle/build.py)")
+    cfg = so.StepConfig(n_shard=3, n_entity=200, n_relation_type=6, embedding_size=16, entity_feature_size=12,
+                        batch_size=12, a2a_size=7, gamma=4.0, **variant)
+    state = random_state(cfg, 3, warm=True)
+    batch = random_batch(cfg, 2, 4, pad=3)
+    pinned = so.Oracle(cfg, np.float64)
+    pinned.set_state(state)
+    compiled = CppOracle(cfg)
+    compiled.set_state(state)
+    want_loss = pinned.train_step_loop(1e-3, batch)
+    got_loss = compiled.train_step_loop(1e-3, batch)
+    np.testing.assert_allclose(got_loss, want_loss, rtol=2e-6)
+    want, got = pinned.get_state(), compiled.get_state()
+    assert set(want) == set(got)
+    for name in want:
+        if name == "step":
+            np.testing.assert_array_equal(got[name], want[name])
+            continue
+        rms = float(np.sqrt(np.mean(np.asarray(want[name], np.float64) ** 2)))
+        worst = float(np.max(np.abs(np.asarray(got[name], np.float64) - want[name])))
+        assert worst <= 5e-6 * rms, f"{name}: {worst / rms:.2e} of the tensor's rms"
