@@ -207,10 +207,11 @@ size_t Engine::arena_offset_dense(int which) const {
     return flags + (size_t)which * round_up(n_dense_ * sizeof(float), 256);
 }
 size_t Engine::arena_offset_shard(unsigned local, int which) const {
+    // per local shard: tails | grad_recv | lower plane of tails
     const size_t row_block = round_up((size_t)cfg_.n_tail() * cfg_.d * sizeof(float), 256);
-    const size_t per_shard = 2 * row_block;
-    const size_t base = arena_offset_dense(3) + (size_t)local * per_shard;
-    return base + (which == 0 ? 0 : row_block);
+    const size_t per_shard = 3 * row_block;
+    const size_t base = arena_offset_dense(4) + (size_t)local * per_shard;
+    return base + (size_t)which * row_block;
 }
 // Receive buffer of the partial dense gradients: one slot of `dense_chunk_` floats per shard of the job.
 size_t Engine::arena_offset_dense_recv() const { return arena_offset_predict(3); }
@@ -307,6 +308,15 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     for (cudaEvent_t& e : ev_join_) KGE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     KGE_CUDA(cudaEventCreate(&ev_begin_));
     KGE_CUDA(cudaEventCreate(&ev_end_));
+    for (cudaEvent_t& e : ev_stage_) KGE_CUDA(cudaEventCreate(&e));
+    // The plane-fed contraction needs 16-byte rows in every operand and the lookups of a block of
+    // hidden rows to fit its staging area.
+    planes_ = cfg_.tensor_cores && cfg_.d % 4 == 0 && cfg_.batch_size % 4 == 0 && cfg_.n_tail() % 4 == 0 &&
+              cfg_.n_remote() <= (unsigned)tc::kRouteMaxLookups;
+    if (const char* v = std::getenv("KGE_PLANE_CONTRACTIONS")) planes_ = planes_ && std::atoi(v) != 0;
+    // fp16 features are widened into rows of their own; the lower plane of fp32 features keeps the
+    // stride of the rows whose feature part is its upper plane (one stride per operand)
+    feat_stride_ = cfg_.feature_type == ST_F16 ? (uint32_t)round_up(cfg_.f, 4) : layout_.row_bytes / 4;
     allocate();
     peer_arena_.assign(cfg_.world, nullptr);
     peer_arena_[cfg_.rank] = arena_;
@@ -327,6 +337,7 @@ Engine::~Engine() {
     if (pinned_) cudaFreeHost(pinned_);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
     if (ev_end_) cudaEventDestroy(ev_end_);
+    for (cudaEvent_t e : ev_stage_) if (e) cudaEventDestroy(e);
     if (ev_fork_) cudaEventDestroy(ev_fork_);
     for (cudaEvent_t e : ev_join_) if (e) cudaEventDestroy(e);
     if (side_stream_) cudaStreamDestroy(side_stream_);
@@ -343,6 +354,7 @@ void Engine::allocate() {
     dense_ = (float*)(arena_ + arena_offset_dense(0));
     dense_m_ = (float*)(arena_ + arena_offset_dense(1));
     dense_v_ = (float*)(arena_ + arena_offset_dense(2));
+    dense_lo_ = (float*)(arena_ + arena_offset_dense(3));
 
     shards_.resize(n_local_);
     const size_t table_bytes = (size_t)cfg_.n_entity * layout_.row_bytes;
@@ -372,6 +384,18 @@ void Engine::allocate() {
         KGE_CUDA(cudaMemset(b.heavy_counter, 0, kHeavySlots * sizeof(unsigned)));
         b.send_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.grad_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+        b.send_lo_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
+        b.tails_lo = (float*)(arena_ + arena_offset_shard(l, 2));
+        if (planes_) {
+            for (int par = 0; par < 2; ++par) {
+                if (cfg_.feature_type == ST_F16) b.feat_wide2[par] = (float*)device_alloc((size_t)R * feat_stride_ * 4);
+                else b.feat_lo2[par] = (float*)device_alloc((size_t)R * feat_stride_ * 4);
+            }
+            b.pred_lo = (float*)device_alloc((size_t)B * D * 4);
+            b.coeff_lo = (float*)device_alloc((size_t)B * T * 4);
+            b.d_hid_h_lo = (float*)device_alloc((size_t)R * D * 4);
+            b.d_hid_t_lo = two_nets ? (float*)device_alloc((size_t)R * D * 4) : nullptr;
+        }
         b.predict_score_dst = (float**)device_alloc(sizeof(float*) * cfg_.n_shard);
         b.predict_index_dst = (uint32_t**)device_alloc(sizeof(uint32_t*) * cfg_.n_shard);
     }
@@ -383,11 +407,10 @@ void Engine::allocate() {
         d_xchg_trace_ = (unsigned long long*)device_alloc(bytes);
         KGE_CUDA(cudaMemset(d_xchg_trace_, 0, bytes));
     }
-    d_status_ = (unsigned*)device_alloc(sizeof(unsigned));
+    d_tc_status_ = (unsigned*)device_alloc(2 * sizeof(unsigned));  // read back together after every run
+    d_status_ = d_tc_status_ + 1;
     KGE_CUDA(cudaMemset(d_epoch_, 0, sizeof(unsigned)));
-    KGE_CUDA(cudaMemset(d_status_, 0, sizeof(unsigned)));
-    d_tc_status_ = (unsigned*)device_alloc(sizeof(unsigned));
-    KGE_CUDA(cudaMemset(d_tc_status_, 0, sizeof(unsigned)));
+    KGE_CUDA(cudaMemset(d_tc_status_, 0, 2 * sizeof(unsigned)));
     {
         // room for the two problems of the largest paired launch, kTcMaxSplits partial tiles each
         const size_t per_problem = std::max<size_t>({(size_t)R * D, (size_t)(std::max(B, T)) * D, (size_t)cfg_.f * D, (size_t)B * T});
@@ -398,6 +421,7 @@ void Engine::allocate() {
     d_peer_flags_ = (unsigned**)device_alloc(sizeof(unsigned*) * cfg_.world);
     d_partials_ = (const float**)device_alloc(sizeof(float*) * cfg_.n_shard);
     d_replicas_ = (float**)device_alloc(sizeof(float*) * cfg_.world);
+    d_replicas_lo_ = (float**)device_alloc(sizeof(float*) * cfg_.world);
 
     const size_t steps = (size_t)n_local_ * cfg_.n_step;
     d_remote_ = (uint32_t*)device_alloc(steps * R * 4);
@@ -430,7 +454,7 @@ void Engine::allocate() {
 
 void Engine::build_pointer_tables() {
     const size_t block = (size_t)cfg_.a2a_size * cfg_.d;  // floats per (src, dst) block
-    std::vector<float*> send(cfg_.n_shard), grad(cfg_.n_shard);
+    std::vector<float*> send(cfg_.n_shard), grad(cfg_.n_shard), send_lo(cfg_.n_shard);
     std::vector<const float*> partials(cfg_.n_shard);
     for (unsigned l = 0; l < n_local_; ++l) {
         const unsigned me = shard0_ + l;
@@ -439,7 +463,9 @@ void Engine::build_pointer_tables() {
             uint8_t* base = peer_arena_[owner];
             send[d] = (float*)(base + arena_offset_shard(dl, 0)) + (size_t)me * block;
             grad[d] = (float*)(base + arena_offset_shard(dl, 1)) + (size_t)me * block;
+            send_lo[d] = (float*)(base + arena_offset_shard(dl, 2)) + (size_t)me * block;
         }
+        KGE_CUDA(cudaMemcpy(shards_[l].send_lo_dst, send_lo.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
         KGE_CUDA(cudaMemcpy(shards_[l].send_dst, send.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
         KGE_CUDA(cudaMemcpy(shards_[l].grad_dst, grad.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
         // predict: results of tail shard `me` for the queries of shard d land in d's [d_local][me] block
@@ -465,13 +491,15 @@ void Engine::build_pointer_tables() {
     for (unsigned d = 0; d < cfg_.n_shard; ++d)
         partials[d] = (const float*)(arena_ + arena_offset_dense_recv()) + (size_t)d * dense_chunk_;
     KGE_CUDA(cudaMemcpy(d_partials_, partials.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
-    std::vector<float*> replicas(cfg_.world);
+    std::vector<float*> replicas(cfg_.world), replicas_lo(cfg_.world);
     std::vector<unsigned*> flags(cfg_.world);
     for (unsigned p = 0; p < cfg_.world; ++p) {
         replicas[p] = (float*)(peer_arena_[p] + arena_offset_dense(0));
+        replicas_lo[p] = (float*)(peer_arena_[p] + arena_offset_dense(3));
         flags[p] = (unsigned*)(peer_arena_[p] + arena_offset_flags());
     }
     KGE_CUDA(cudaMemcpy(d_replicas_, replicas.data(), sizeof(float*) * cfg_.world, cudaMemcpyHostToDevice));
+    KGE_CUDA(cudaMemcpy(d_replicas_lo_, replicas_lo.data(), sizeof(float*) * cfg_.world, cudaMemcpyHostToDevice));
     KGE_CUDA(cudaMemcpy(d_peer_flags_, flags.data(), sizeof(unsigned*) * cfg_.world, cudaMemcpyHostToDevice));
 }
 
@@ -613,15 +641,19 @@ void Engine::stage_batch(std::vector<HostArray>& arrays) {
     upload(head, d_head_);
     upload(relation, d_relation_);
     upload(tail, d_tail_);
+    KGE_CUDA(cudaEventRecord(ev_stage_[0], stream_));
     k_prepare_segments<<<(unsigned)(n * S), 512, 0, stream_>>>(
         d_head_, d_a2a_, d_relation_, d_remote_, (int)B, (int)T, (int)R, (int)cfg_.n_relation_type, d_ent_perm_,
         d_ent_off_, d_rel_perm_, d_rel_off_, d_first_slot_, split_popular_rows_ ? d_heavy_parts_ : nullptr, d_heavy_count_);
     KGE_CUDA(cudaGetLastError());
+    KGE_CUDA(cudaEventRecord(ev_stage_[1], stream_));
     staged_ = true;
+    stage_fresh_ = true;
 }
 
 void Engine::train_staged(float learning_rate, float* loss) {
     KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    require_usable();
     if (!staged_) fail(KGE_LOGIC_ERROR, "kge_train_staged called before kge_stage_batch");
     if (!connected_) fail(KGE_LOGIC_ERROR, "world_size > 1 but kge_comm_connect has not been called");
     // Adam step sizes of the staged steps (src/fructose/frnn.cpp:42-59), in fp32.
@@ -668,6 +700,14 @@ void Engine::train_staged(float learning_rate, float* loss) {
         KGE_CUDA(cudaMemcpyAsync(host_loss, d_loss_total_, n_local_ * 4, cudaMemcpyDeviceToHost, stream_));
     KGE_CUDA(cudaStreamSynchronize(stream_));
     KGE_CUDA(cudaEventElapsedTime(&last_ms_, ev_begin_, ev_end_));
+    if (stage_fresh_) {
+        // the sort-and-segment preparation belongs to the step (it is the backward of the row
+        // gather): its device time counts towards the first run of a staged batch
+        float stage_ms = 0.f;
+        KGE_CUDA(cudaEventElapsedTime(&stage_ms, ev_stage_[0], ev_stage_[1]));
+        last_ms_ += stage_ms;
+        stage_fresh_ = false;
+    }
     timing_collect();
     step_ += cfg_.n_step;
     check_device_status();
@@ -675,23 +715,25 @@ void Engine::train_staged(float learning_rate, float* loss) {
         for (unsigned l = 0; l < n_local_; ++l) loss[l] = host_loss[l] / (float)cfg_.n_step;
 }
 
+// Both status words come back in one copy (they are neighbours in device memory).  A wait that gave
+// up leaves this engine's kernels out of step with the other processes' (their hand-over epochs
+// disagree from then on), so the engine refuses further device commands: it must be rebuilt.
 void Engine::check_device_status() {
-    if (cfg_.tensor_cores) {
-        unsigned tc_status = 0;
-        KGE_CUDA(cudaMemcpy(&tc_status, d_tc_status_, sizeof(tc_status), cudaMemcpyDeviceToHost));
-        if (tc_status) {
-            KGE_CUDA(cudaMemset(d_tc_status_, 0, sizeof(tc_status)));
-            fail(KGE_DEVICE_STATUS, msg() << "a bounded wait on the tensor-core pipeline gave up (code " << tc_status << ")");
-        }
-    }
-    if (cfg_.world == 1) return;
-    unsigned status = 0;
-    KGE_CUDA(cudaMemcpy(&status, d_status_, sizeof(status), cudaMemcpyDeviceToHost));
-    if (status) {
-        KGE_CUDA(cudaMemset(d_status_, 0, sizeof(status)));
-        fail(KGE_DEVICE_STATUS, msg() << "a device-side wait for rank " << (status - 1)
-                                      << " gave up: that process did not reach the same step");
-    }
+    unsigned status[2] = {0, 0};  // [0] the tensor-core pipeline, [1] the hand-overs between processes
+    KGE_CUDA(cudaMemcpyAsync(status, d_tc_status_, sizeof(status), cudaMemcpyDeviceToHost, stream_));
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    if (!status[0] && !status[1]) return;
+    poisoned_ = true;
+    KGE_CUDA(cudaMemset(d_tc_status_, 0, sizeof(status)));
+    if (status[0]) fail(KGE_DEVICE_STATUS, msg() << "a bounded wait on the tensor-core pipeline gave up (code " << status[0] << ")");
+    fail(KGE_DEVICE_STATUS, msg() << "a device-side wait for rank " << (status[1] - 1)
+                                  << " gave up: that process did not reach the same step");
+}
+
+void Engine::require_usable() const {
+    if (poisoned_)
+        fail(KGE_LOGIC_ERROR, "a device-side wait of an earlier command gave up: this engine is out of step with the other "
+                              "processes and must be rebuilt");
 }
 
 void Engine::set_kernel_timing(bool on) {
@@ -736,6 +778,10 @@ bool dependent_launch_enabled() {
 void Engine::launch_steps() {
     launch_gather(0, stream_);
     for (unsigned step = 0; step < cfg_.n_step; ++step) launch_one_step(step);
+    // The last kernel of a step only publishes its dense parameters.  The run ends when every
+    // process's share has arrived in this process's copy (values and optimiser state), so that a
+    // "read" or "predict" issued straight after the run sees the finished step without a host barrier.
+    launch_exchange_wait(XCHG_DENSE_PARAMS);
 }
 
 // The step's rows, gathered into the compact copy every later kernel of the step reads (two
@@ -747,8 +793,17 @@ void Engine::launch_gather(unsigned step, cudaStream_t stream) {
         ShardBuffers& b = shards_[l];
         const uint32_t* remote = d_remote_ + ((size_t)l * cfg_.n_step + step) * R;
         KGE_LAUNCH("gather", KGE_CUDA(launch_dependent(k_gather_step_rows, dim3(ceil_div(R, 8)), dim3(256), 0, stream, b.table,
-                                                       layout_.row_bytes, remote, (int)R, b.rows_c2[step & 1])));
+                                                       layout_.row_bytes, remote, (int)R, b.rows_c2[step & 1], feature_planes(b, step & 1))));
     }
+}
+
+FeaturePlanes Engine::feature_planes(const ShardBuffers& b, unsigned parity) const {
+    FeaturePlanes fp{};
+    fp.wide = b.feat_wide2[parity];
+    fp.lo = b.feat_lo2[parity];
+    fp.stride = feat_stride_;
+    fp.off_feat = layout_.off_feat;
+    return fp;
 }
 
 // Fork: what is launched on the returned stream starts after everything queued on the main stream
@@ -886,6 +941,231 @@ void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems,
     KGE_CUDA(err);
 }
 
+// One launch of the plane-fed contraction for one or two problems of the same shape class.  Tiles
+// are 128 x 128 (128 x 64 for narrow outputs); the k range is split over the blocks of a cluster so
+// that about one block per SM is busy and every split keeps at least two 32-deep slices.
+void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_problems, bool rowsum, int wait_kind, int signal_kind,
+                           const tc::RouteArgs* route) {
+    int max_n = 0, max_k = 0;
+    unsigned tiles = 0;
+    for (int i = 0; i < n_problems; ++i) max_n = std::max(max_n, problems[i].g.N);
+    const int tile_n = max_n > 64 ? 128 : 64;
+    for (int i = 0; i < n_problems; ++i) {
+        tiles += ceil_div((unsigned)problems[i].g.M, 128) * ceil_div((unsigned)max_n, (unsigned)tile_n);
+        max_k = std::max(max_k, problems[i].g.K);
+    }
+    int splits = (int)std::min<unsigned>({std::max(1u, 148u / std::max(1u, tiles)), std::max(1u, (unsigned)max_k / 64u),
+                                          (unsigned)tc::kMaxClusterSplits});
+    while (splits > 1 && (unsigned)tc::max_resident_plane_clusters(splits) < tiles) --splits;
+    for (int i = 0; i < n_problems; ++i) {
+        tc::GemmArgs& g = problems[i].g;
+        g.status = d_tc_status_;
+        g.k_per_split = std::max(32, (int)round_up(ceil_div((unsigned)g.K, (unsigned)splits), 32));
+    }
+    timing_begin(name);
+    const cudaError_t err = rowsum ? tc::launch_planes<true>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route)
+                                   : tc::launch_planes<false>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route);
+    timing_end();
+    ++launch_counter_;
+    KGE_CUDA(err);
+}
+
+// The training step with its contractions on the plane-fed kernel: seven launches on the step's
+// chain (hidden + lookups + send, scores, loss, score gradients + return, segment sums + Adam +
+// relation gradients, projection gradient, dense update) and the next step's gather beside the
+// last two.  Every operand of a contraction is the fp32 array its producer wrote (the upper TF32
+// plane) plus a lower plane the same producer wrote next to it.
+void Engine::launch_step_planes(unsigned step, const LossParams& lp, float normaliser) {
+    const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d, F = cfg_.f;
+    const unsigned n_rel = cfg_.n_relation_type, parity = step & 1;
+    const bool two_nets = cfg_.n_net() == 2, l2 = cfg_.dist_fn == DIST_L2, l1 = cfg_.dist_fn == DIST_L1;
+    const bool half_features = cfg_.feature_type == ST_F16;
+    const float* rel_table = dense_;
+    const ExchangeSync sync = exchange_sync();
+    auto step_ptr = [&](uint32_t* base, unsigned l, size_t per_step) { return base + ((size_t)l * cfg_.n_step + step) * per_step; };
+    auto plane = [](const float* hi, const float* lo, long long stride_bytes, bool mn_major) {
+        return tc::PlaneOperand{hi, lo, stride_bytes, mn_major ? 1 : 0};
+    };
+    auto features = [&](const ShardBuffers& b, bool mn_major) {
+        if (half_features) return plane(b.feat_wide2[parity], nullptr, (long long)feat_stride_ * 4, mn_major);
+        return plane(reinterpret_cast<const float*>(b.rows_c2[parity] + layout_.off_feat), b.feat_lo2[parity], (long long)layout_.row_bytes, mn_major);
+    };
+
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        uint8_t* rows_c = b.rows_c2[parity];
+        const size_t sidx = (size_t)l * cfg_.n_step + step;
+        const uint32_t* a2a = step_ptr(d_a2a_, l, T);
+        const uint32_t* head = step_ptr(d_head_, l, B);
+        const uint32_t* relation = step_ptr(d_relation_, l, B);
+        // 1. hidden = value + feature . W, and from its epilogue the lookups and the send half of the exchange
+        const bool fused_route = F > 0 && cfg_.score_fn != SCORE_COMPLEX;
+        if (F > 0) {
+            tc::PlaneProblem nets[2] = {};
+            const int n_nets = two_nets ? 2 : 1;
+            for (int net = 0; net < n_nets; ++net) {
+                tc::PlaneProblem& p = nets[net];
+                const size_t w = dense_bounds_[1 + net];
+                p.A = features(b, false);
+                p.B = plane(dense_ + w, dense_lo_ + w, (long long)D * 4, true);
+                tc::GemmArgs& g = p.g;
+                g.M = (int)R; g.N = (int)D; g.K = (int)F;
+                g.epilogue = tc::EPI_ADD_TABLE_VALUE;
+                g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
+                g.x_base = rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_is_half = cfg_.state_type == ST_F16;
+            }
+            tc::RouteArgs route{};
+            route.perm = d_ent_perm_ + sidx * (B + T);
+            route.off = d_ent_off_ + sidx * (R + 1);
+            route.relation = relation;
+            route.rel_table = rel_table;
+            route.send_dst = b.send_dst;
+            route.send_lo_dst = b.send_lo_dst;
+            route.pred = b.pred;
+            route.pred_lo = b.pred_lo;
+            route.B = (int)B; route.a2a = (int)cfg_.a2a_size; route.n_shard = (int)cfg_.n_shard; route.score_fn = cfg_.score_fn;
+            route.mode[0] = two_nets ? 1 : 3;
+            route.mode[1] = two_nets ? 2 : 0;
+            launch_planes("hidden", nets, n_nets, false, XCHG_DENSE_PARAMS, fused_route ? XCHG_TAILS : -1, fused_route ? &route : nullptr);
+        } else {
+            // no features: the hidden rows are the gathered values
+            launch_exchange_wait(XCHG_DENSE_PARAMS);
+            dim3 grid(ceil_div(R, 64), ceil_div(D, 64), 1);
+            KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, KGE_CUDA(launch_dependent(k_hidden<ST, FT>, dim3(grid), dim3(256), 0, stream_, rows_c, layout_,
+                                                                                  nullptr, 0u, (int)R, nullptr, nullptr, b.hid_h, b.hid_t))));
+        }
+        if (!fused_route)
+            KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
+                                                          b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn, sync,
+                                                          b.send_lo_dst, b.pred_lo)));
+    }
+    KGE_CUDA(cudaGetLastError());
+
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        const uint32_t* head = step_ptr(d_head_, l, B);
+        const uint32_t* relation = step_ptr(d_relation_, l, B);
+        const uint32_t* tail = step_ptr(d_tail_, l, B);
+        // 2. scores
+        if (cfg_.dist_fn == DIST_DOT) {
+            tc::PlaneProblem p{};
+            p.A = plane(b.pred, b.pred_lo, (long long)D * 4, false);
+            p.B = plane(b.tails, b.tails_lo, (long long)D * 4, false);
+            p.g.M = (int)B; p.g.N = (int)T; p.g.K = (int)D;
+            p.g.epilogue = tc::EPI_STORE; p.g.out = b.raw; p.g.ldc = T; p.g.block_rows = 1;
+            launch_planes("score", &p, 1, false, XCHG_TAILS, -1);
+        } else {
+            KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_, sync)));
+        }
+        // 3. loss and the coefficients of the score gradients
+        KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
+                                                     d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo)));
+        // 4. score gradients; the tails' rows go straight to the shards that own them
+        if (l1) {
+            PairBwdArgs pa{};
+            pa.D = (int)D;
+            pa.tiles_m0 = (int)ceil_div(B, 32);
+            pa.p[0] = {b.pred, b.tails, b.coeff, (int)B, (int)T, (int)T, 1, b.d_pred, nullptr, 1};
+            pa.p[1] = {b.tails, b.pred, b.coeff, (int)T, (int)B, 1, (int)T, nullptr, b.grad_dst, (int)cfg_.a2a_size};
+            dim3 bgrid(ceil_div(B, 32) + ceil_div(T, 32), ceil_div(D, 64));
+            KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_L1>, dim3(bgrid), dim3(128), 0, stream_, pa)));
+            launch_exchange_signal(XCHG_TAIL_GRADS);
+        } else {
+            //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
+            //   L2:   d_pred = rowsum(C) * pred - C . tails,       d_tails = colsum(C) * tails - C^T . pred
+            tc::PlaneProblem both[2] = {};
+            tc::PlaneProblem& g = both[0];
+            g.A = plane(b.coeff, b.coeff_lo, (long long)T * 4, false);
+            g.B = plane(b.tails, b.tails_lo, (long long)D * 4, true);
+            g.g.M = (int)B; g.g.N = (int)D; g.g.K = (int)T;
+            g.g.epilogue = l2 ? tc::EPI_ROWSUM_X_MINUS : tc::EPI_STORE;
+            g.g.out = b.d_pred; g.g.ldc = D; g.g.block_rows = 1;
+            g.g.x_base = reinterpret_cast<const uint8_t*>(b.pred); g.g.x_row_stride_bytes = (long long)D * 4;
+            tc::PlaneProblem& h = both[1];
+            h.A = plane(b.coeff, b.coeff_lo, (long long)T * 4, true);
+            h.B = plane(b.pred, b.pred_lo, (long long)D * 4, true);
+            h.g.M = (int)T; h.g.N = (int)D; h.g.K = (int)B;
+            h.g.epilogue = g.g.epilogue;
+            h.g.out = nullptr; h.g.out_blocks = b.grad_dst; h.g.block_rows = (int)cfg_.a2a_size; h.g.ldc = D;
+            h.g.x_base = reinterpret_cast<const uint8_t*>(b.tails); h.g.x_row_stride_bytes = (long long)D * 4;
+            launch_planes("score_bwd", both, 2, l2, -1, XCHG_TAIL_GRADS);
+        }
+        if (cfg_.score_fn != SCORE_TRANSE)
+            KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
+                                                             b.d_relrow, (int)D, cfg_.score_fn)));
+    }
+    KGE_CUDA(cudaGetLastError());
+
+    // 5. segment sums + row-wise Adam, and the relation rows of the partial dense gradient
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        const size_t sidx = (size_t)l * cfg_.n_step + step;
+        const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
+        const RelationRows rr{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst, (int)n_rel, (int)cfg_.world,
+                              b.d_hid_h_lo, b.d_hid_t_lo};
+        const dim3 grid(kHeavySlots + R + n_rel), block(64 * kSegmentLanes);
+        if (cfg_.state_type == ST_F32)
+            KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
+                                                 step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,
+                                                 b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step, entity_lr_mod_, adam_, sync, heavy,
+                                                 (int)R, rr)));
+        else
+            KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
+                                                 step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,
+                                                 b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step, entity_lr_mod_, adam_, sync, heavy,
+                                                 (int)R, rr)));
+    }
+    KGE_CUDA(cudaGetLastError());
+    const bool gather_ahead = step + 1 < cfg_.n_step;
+    const bool gather_beside = gather_ahead && (side_streams_ & 2u);
+    if (gather_beside) {
+        cudaStream_t side = side_begin();
+        launch_gather(step + 1, side);
+        side_end(1);
+    }
+    // 6. d W = feature^T . d_hidden, straight into the owners' slices of the partial dense gradient
+    for (unsigned l = 0; l < n_local_; ++l) {
+        ShardBuffers& b = shards_[l];
+        tc::PlaneProblem nets[2] = {};
+        for (unsigned net = 0; net < cfg_.n_net(); ++net) {
+            tc::PlaneProblem& p = nets[net];
+            p.A = features(b, true);
+            p.B = plane(net ? b.d_hid_t : b.d_hid_h, net ? b.d_hid_t_lo : b.d_hid_h_lo, (long long)D * 4, true);
+            tc::GemmArgs& g = p.g;
+            g.M = (int)F; g.N = (int)D; g.K = (int)R;
+            g.epilogue = tc::EPI_STORE;
+            g.out = nullptr; g.out_blocks = b.dense_dst; g.block_rows = 1; g.block_cyclic = (int)cfg_.world;
+            g.block_row_offset = (int)(n_rel + net * F); g.ldc = D;
+        }
+        if (F > 0) launch_planes("projection_bwd", nets, (int)cfg_.n_net(), false, -1, XCHG_DENSE_PARTIALS);
+        else launch_exchange_signal(XCHG_DENSE_PARTIALS);  // the relation rows of the entity update are all there is
+    }
+    KGE_CUDA(cudaGetLastError());
+    if (gather_ahead && !gather_beside) launch_gather(step + 1, stream_);
+    // 7. dense parameters: reduce over shards, Adam on the owned rows, new values and their lower planes into every replica
+    {
+        DenseUpdateArgs da{};
+        da.sync = sync;
+        da.partials = d_partials_;
+        da.n_partial = (int)cfg_.n_shard;
+        da.replicas = d_replicas_;
+        da.replicas_lo = d_replicas_lo_;
+        da.n_replica = (int)cfg_.world;
+        da.adam_m = dense_m_;
+        da.adam_v = dense_v_;
+        da.n_own = own_rows_;
+        da.row_width = D;
+        for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
+        for (int i = 0; i < 3; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
+        da.step_size = d_step_size_ + step;
+        da.ap = adam_;
+        const unsigned blocks = (unsigned)std::min<size_t>((own_rows_ * D / 4 + 255) / 256, 148 * 8);
+        KGE_LAUNCH("dense_update", KGE_CUDA(launch_dependent(k_dense_update, dim3(std::max(1u, blocks)), dim3(256), 0, stream_, da, (int)cfg_.rank)));
+    }
+    KGE_CUDA(cudaGetLastError());
+    if (gather_beside) side_join(1);
+}
+
 void Engine::launch_one_step(unsigned step) {
     const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d, F = cfg_.f;
     const unsigned n_rel = cfg_.n_relation_type;
@@ -916,6 +1196,7 @@ void Engine::launch_one_step(unsigned step) {
     }
     lp.grad_scale = cfg_.loss_scale / normaliser;
 
+    if (planes_) return launch_step_planes(step, lp, normaliser);
     const ExchangeSync sync = exchange_sync();
     const bool proj_direct = cfg_.tensor_cores && F > 0;  // the projection gradient lands in the partial dense vector directly
     auto step_ptr = [&](uint32_t* base, unsigned l, size_t per_step) {
@@ -955,11 +1236,11 @@ void Engine::launch_one_step(unsigned step) {
         if (vec)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn, sync)));
+                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr)));
         else
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<1>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn, sync)));
+                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr)));
     }
     KGE_CUDA(cudaGetLastError());
 
@@ -992,7 +1273,7 @@ void Engine::launch_one_step(unsigned step) {
                                                       fused_wait ? sync : ExchangeSync{})));
         }
         KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
-                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l)));
+                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, (float*)nullptr)));
         if (tc_bwd) {
             // Both input gradients are contractions with the coefficient matrix C [B, T]:
             //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
@@ -1067,20 +1348,20 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
         } else {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy)));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
         }
     }
     KGE_CUDA(cudaGetLastError());
@@ -1276,7 +1557,10 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
     if (count == 0) return;
     float* base = var->kind == 0 ? dense_ : var->kind == 1 ? dense_m_ : dense_v_;
     if (write) {
-        KGE_CUDA(cudaMemcpy(base + var->offset, value.data, count * 4, cudaMemcpyHostToDevice));
+        // on the engine's stream, so that the kernel that derives the lower plane is ordered behind the copy
+        KGE_CUDA(cudaMemcpyAsync(base + var->offset, value.data, count * 4, cudaMemcpyHostToDevice, stream_));
+        if (var->kind == 0) refresh_lower_plane(var->offset, count);
+        KGE_CUDA(cudaStreamSynchronize(stream_));
         return;
     }
     if (var->kind == 0 || cfg_.world == 1) {
@@ -1294,6 +1578,14 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
         KGE_CUDA(cudaMemcpy2D(static_cast<float*>(value.data) + (first - row0) * D, W * D * 4, src, W * D * 4, D * 4, rows,
                               cudaMemcpyDeviceToHost));
     }
+}
+
+// The projections are tensor-core operands: their lower TF32 plane follows every change of the values.
+void Engine::refresh_lower_plane(size_t offset, size_t count) {
+    if (!planes_ || count == 0) return;
+    k_lower_plane<<<(unsigned)std::min<size_t>((count + 255) / 256, 148 * 8), 256, 0, stream_>>>(dense_ + offset, count, dense_lo_ + offset);
+    KGE_CUDA(cudaGetLastError());
+    KGE_CUDA(cudaStreamSynchronize(stream_));
 }
 
 void Engine::ensure_predict_buffers() {
@@ -1328,6 +1620,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
     if (nb == 0 || nb > kTopkCapacity / 2)
         fail(KGE_INVALID_ARGUMENT, msg() << "'execution.predict_n_best' must be between 1 and " << kTopkCapacity / 2);
     if (!connected_) fail(KGE_LOGIC_ERROR, "world_size > 1 but kge_comm_connect has not been called");
+    require_usable();
     const uint32_t* h_head = static_cast<const uint32_t*>(head.data);
     const uint32_t* h_rel = static_cast<const uint32_t*>(relation.data);
     const uint32_t* h_count = static_cast<const uint32_t*>(count.data);
@@ -1414,6 +1707,7 @@ size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, si
     const float* src = nullptr;
     size_t count = 0;
     if (what == "hidden") { src = b.hid_h; count = R * D; }
+    else if (what == "hidden_tail") { src = b.hid_t; count = R * D; }
     else if (what == "tails") { src = b.tails; count = T * D; }
     else if (what == "pred") { src = b.pred; count = B * D; }
     else if (what == "raw_score") { src = b.raw; count = B * T; }

@@ -11,6 +11,7 @@
 #include "common.hpp"
 #include "kernels.cuh"
 #include "tc_gemm.cuh"
+#include "tc_planes.cuh"
 
 namespace kge {
 
@@ -100,6 +101,13 @@ class Engine {
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
         float** grad_dst = nullptr;  // device table [n_shard]
+        // Lower TF32 planes of the tensor-core operands that this shard's kernels produce (the upper
+        // plane is the fp32 array itself), and the widened features of the gathered rows.
+        float* feat_wide2[2] = {nullptr, nullptr};  // fp16 features as fp32, [R, feat_stride], even / odd steps
+        float* feat_lo2[2] = {nullptr, nullptr};    // lower plane of fp32 features
+        float *pred_lo = nullptr, *coeff_lo = nullptr, *d_hid_h_lo = nullptr, *d_hid_t_lo = nullptr;
+        float* tails_lo = nullptr;       // inside the arena, beside `tails`
+        float** send_lo_dst = nullptr;   // device table [n_shard]
         float* heavy_partial = nullptr;   // [kHeavySlots][2][D] sums of the parts of popular rows
         unsigned* heavy_counter = nullptr;  // [kHeavySlots]
         float** dense_dst = nullptr;  // device table [world]: this shard's slot in each owner's receive buffer
@@ -137,7 +145,14 @@ class Engine {
     void launch_gather(unsigned step, cudaStream_t stream);
     void launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum,
                    int wait_kind = -1, int signal_kind = -1);
+    // the plane-fed contraction: tile width and k splits chosen here
+    void launch_planes(const char* name, tc::PlaneProblem* problems, int n_problems, bool rowsum, int wait_kind, int signal_kind,
+                       const tc::RouteArgs* route = nullptr);
+    void launch_step_planes(unsigned step, const LossParams& lp, float normaliser);
+    void refresh_lower_plane(size_t offset, size_t count);
+    FeaturePlanes feature_planes(const ShardBuffers& b, unsigned parity) const;
     void check_device_status();
+    void require_usable() const;
     void timing_begin(const char* name);
     void timing_end();
     void timing_collect();
@@ -156,11 +171,16 @@ class Engine {
     cudaStream_t side_stream_ = nullptr;
     unsigned side_streams_ = 0;
     bool split_popular_rows_ = true;  // rows with many lookups are summed in parts by several blocks
+    bool planes_ = false;             // the step's contractions run on the plane-fed tensor-core kernel
+    uint32_t feat_stride_ = 0;        // floats per row of the widened / lower feature planes
     cudaEvent_t ev_fork_ = nullptr, ev_join_[2] = {nullptr, nullptr};
     cudaStream_t side_begin();
     void side_end(int which);
     void side_join(int which);
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+    cudaEvent_t ev_stage_[2] = {nullptr, nullptr};  // around the segment preparation of a staged batch
+    bool stage_fresh_ = false;                      // its time has not been counted towards a run yet
+    bool poisoned_ = false;                         // a device-side wait gave up: the engine must be rebuilt
     std::vector<void*> allocations_;
     std::vector<ShardBuffers> shards_;
 
@@ -187,6 +207,8 @@ class Engine {
     float dense_lr_mod_[3] = {1.f, 1.f, 1.f};
     float entity_lr_mod_ = 1.f;
     float *dense_ = nullptr, *dense_m_ = nullptr, *dense_v_ = nullptr;
+    float* dense_lo_ = nullptr;      // lower TF32 plane of the dense vector (same layout, inside the arena)
+    float** d_replicas_lo_ = nullptr;  // [world]
     size_t own_rows_ = 0, dense_chunk_ = 0, dense_chunk_rows_ = 1;
     std::vector<Variable> variables_;
     unsigned long long step_ = 0;

@@ -105,23 +105,55 @@ static __global__ void k_delay(long long cycles) {
 // compact buffer with the same row layout.  One warp per row with all of its loads in flight
 // before the first store; everything after this kernel in the step reads the compact,
 // L2-resident copy.
+// What the tensor-core contractions read of a gathered row's features: fp16 features are widened
+// to fp32 (exact, one TF32 plane) into feat_wide [R, feat_stride]; fp32 features are read in place
+// (the compact copy is their upper plane) and only their lower plane feat_lo is written.  Both null:
+// nothing extra.
+struct FeaturePlanes {
+    float* wide;   // fp16 features as fp32
+    float* lo;     // lower TF32 plane of fp32 features
+    uint32_t stride;    // floats per row of either
+    uint32_t off_feat;  // byte offset of the features in a table row (multiple of 16)
+};
+
+__device__ __forceinline__ float tf32_upper(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
+__device__ __forceinline__ float tf32_lower(float x) { return tf32_upper(x - tf32_upper(x)); }
+__device__ __forceinline__ float4 tf32_lower4(float4 v) { return make_float4(tf32_lower(v.x), tf32_lower(v.y), tf32_lower(v.z), tf32_lower(v.w)); }
+
 static __global__ void __launch_bounds__(256)
 k_gather_step_rows(const uint8_t* __restrict__ table, uint32_t row_bytes, const uint32_t* __restrict__ remote, int R,
-                   uint8_t* __restrict__ rows_c) {
+                   uint8_t* __restrict__ rows_c, FeaturePlanes fp) {
     grid_dependency_sync();
     const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= R) return;
     const uint4* __restrict__ src = reinterpret_cast<const uint4*>(table + (size_t)remote[r] * row_bytes);
     uint4* __restrict__ dst = reinterpret_cast<uint4*>(rows_c + (size_t)r * row_bytes);
-    const int chunks = (int)(row_bytes >> 4);
+    const int chunks = (int)(row_bytes >> 4), feat_chunk0 = (int)(fp.off_feat >> 4);
     for (int c0 = lane; c0 < chunks; c0 += 32 * 8) {
         uint4 v[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u)
             if (c0 + 32 * u < chunks) v[u] = src[c0 + 32 * u];
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-            if (c0 + 32 * u < chunks) dst[c0 + 32 * u] = v[u];
+        for (int u = 0; u < 8; ++u) {
+            const int c = c0 + 32 * u;
+            if (c >= chunks) continue;
+            dst[c] = v[u];
+            if (c < feat_chunk0) continue;
+            if (fp.wide) {  // 8 fp16 values
+                const int f = (c - feat_chunk0) * 8;
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v[u].x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v[u].y));
+                const float2 cc = __half22float2(*reinterpret_cast<const __half2*>(&v[u].z)), d = __half22float2(*reinterpret_cast<const __half2*>(&v[u].w));
+                float* o = fp.wide + (size_t)r * fp.stride + f;
+                if (f < (int)fp.stride) *reinterpret_cast<float4*>(o) = make_float4(a.x, a.y, b.x, b.y);
+                if (f + 4 < (int)fp.stride) *reinterpret_cast<float4*>(o + 4) = make_float4(cc.x, cc.y, d.x, d.y);
+            } else if (fp.lo) {  // 4 fp32 values
+                const int f = (c - feat_chunk0) * 4;
+                if (f < (int)fp.stride)
+                    *reinterpret_cast<float4*>(fp.lo + (size_t)r * fp.stride + f) =
+                        tf32_lower4(make_float4(__uint_as_float(v[u].x), __uint_as_float(v[u].y), __uint_as_float(v[u].z), __uint_as_float(v[u].w)));
+            }
+        }
     }
 }
 
@@ -233,7 +265,7 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         const uint32_t* __restrict__ a2a_idx, const uint32_t* __restrict__ head,
         const uint32_t* __restrict__ relation, const float* __restrict__ rel_table,
         float* const* __restrict__ send_dst, float* __restrict__ pred, int T, int a2a, int B, int D,
-        int score_fn, ExchangeSync sync) {
+        int score_fn, ExchangeSync sync, float* const* __restrict__ send_lo_dst = nullptr, float* __restrict__ pred_lo = nullptr) {
     grid_dependency_sync();
     const int b = blockIdx.x;
     if (b < T) {
@@ -241,7 +273,11 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         const float* __restrict__ src = hid_t + (size_t)a2a_idx[b] * D;
         float* __restrict__ out = send_dst[dst] + (size_t)j * D;
         if (V == 4) {
-            for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) store4(out + c, load4(src + c));
+            for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
+                const float4 v = load4(src + c);
+                store4(out + c, v);
+                if (send_lo_dst) store4(send_lo_dst[dst] + (size_t)j * D + c, tf32_lower4(v));  // lower plane for the tensor-core gradients
+            }
         } else {
             for (int c = threadIdx.x; c < D; c += blockDim.x) out[c] = src[c];
         }
@@ -262,6 +298,10 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
             const float hr = h[c], hi = h[c + half], rr = r[c], ri = r[c + half];
             p[c] = hr * rr - hi * ri;
             p[c + half] = hr * ri + hi * rr;
+            if (pred_lo) {
+                pred_lo[(size_t)i * D + c] = tf32_lower(p[c]);
+                pred_lo[(size_t)i * D + c + half] = tf32_lower(p[c + half]);
+            }
         }
     } else if (V == 4) {
         for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
@@ -273,6 +313,7 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
                 o = make_float4(a.x * q.x, a.y * q.y, a.z * q.z, a.w * q.w);
             }
             store4(p + c, o);
+            if (pred_lo) store4(pred_lo + (size_t)i * D + c, tf32_lower4(o));
         }
     } else {
         for (int c = threadIdx.x; c < D; c += blockDim.x)
@@ -566,12 +607,13 @@ template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float* __restrict__ coeff,
        float* __restrict__ loss_rows, LossParams lp, float inv_normaliser, float* __restrict__ loss_total,
-       float* __restrict__ loss_last, unsigned* __restrict__ counter) {
+       float* __restrict__ loss_last, unsigned* __restrict__ counter, float* __restrict__ coeff_lo = nullptr) {
     grid_dependency_sync();
     __shared__ float scratch[THREADS / 32];
     const int i = blockIdx.x, T = lp.n_tail;
     const float* __restrict__ r = raw + (size_t)i * T;
     float* __restrict__ c = coeff + (size_t)i * T;
+    float* __restrict__ c_lo = coeff_lo ? coeff_lo + (size_t)i * T : nullptr;  // lower TF32 plane for the tensor-core gradients
     const int lab = (int)label[i];
     const bool transe = lp.score_fn == SCORE_TRANSE;
     auto score_of = [&](int j) { return transe ? lp.gamma - r[j] : r[j]; };
@@ -596,7 +638,9 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
         for (int j = threadIdx.x; j < T; j += THREADS) {
             const float logp = score_of(j) + (j == lab ? 0.f : lp.softmax_shift) - mx - log_z;
             const float g = lp.grad_scale * (expf(logp) - (j == lab ? 1.f : 0.f));
-            c[j] = to_coeff(j, g);
+            const float cj = to_coeff(j, g);
+            c[j] = cj;
+            if (c_lo) c_lo[j] = tf32_lower(cj);
             if (j == lab) loss_rows[i] = -logp;
         }
         finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch);
@@ -629,7 +673,9 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
         const float ls = x > -11.f ? -log1pf(expf(-fmaxf(x, -11.f))) : x;
         part += w * ls;
         const float dx = (-w * lp.grad_scale) / (1.f + expf(fminf(x, 11.f)));
-        c[j] = to_coeff(j, pos ? dx : -dx);
+        const float cj = to_coeff(j, pos ? dx : -dx);
+        c[j] = cj;
+        if (c_lo) c_lo[j] = tf32_lower(cj);
     }
     part = block_sum<THREADS>(part, scratch);
     if (threadIdx.x == 0) loss_rows[i] = -part;
@@ -964,6 +1010,76 @@ struct HeavyRows {
     unsigned* counter;       // [kHeavySlots] parts of a row that have arrived (indexed by the row's first slot)
 };
 
+// The relation part of a shard's dense gradient, summed by blocks appended to the entity update's
+// grid (both depend only on the score gradients): row rho = the sum of the per-triple relation
+// gradients of the triples of relation rho, in position order (backward of the gather at
+// src/poplar_kge.cpp:489), stored into the memory of the process that owns that row of the dense
+// vector (row r to process r % n_owner as its row r / n_owner).  Null d_relrow: no such blocks.
+struct RelationRows {
+    const float* d_relrow;       // [B, D] per-triple gradients
+    const uint32_t* perm;        // triples ordered by relation
+    const uint32_t* off;         // [n_rel + 1]
+    float* const* dense_dst;     // [n_owner] this shard's slot in each owner's receive buffer
+    int n_rel, n_owner;
+    float* d_hid_h_lo;           // lower TF32 planes of the hidden-row gradients (null: not needed)
+    float* d_hid_t_lo;
+};
+
+template <int V, int LANES>
+__device__ __forceinline__ void relation_row_sum(const RelationRows& rr, int rho, int D, float (*part)[64 * V], uint32_t* s_perm) {
+    const int col = threadIdx.x & 63, lane = threadIdx.x >> 6;
+    const uint32_t q0 = rr.off[rho], q1 = rr.off[rho + 1];
+    float* __restrict__ dst_row = rr.dense_dst[rho % rr.n_owner] + (size_t)(rho / rr.n_owner) * D;
+    if (q0 == q1) {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) dst_row[c] = 0.f;
+        return;
+    }
+    for (int c0 = 0; c0 < D; c0 += 64 * V) {
+        const int c = c0 + col * V;
+        float g[V];
+#pragma unroll
+        for (int u = 0; u < V; ++u) g[u] = 0.f;
+        for (uint32_t base = q0; base < q1; base += 64 * LANES) {
+            const int count = (int)min((uint32_t)(64 * LANES), q1 - base);
+            __syncthreads();
+            if ((int)threadIdx.x < count) s_perm[threadIdx.x] = rr.perm[base + threadIdx.x];
+            __syncthreads();
+            if (c >= D) continue;
+            for (int i = lane; i < count; i += 4 * LANES) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int ii = i + u * LANES;
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (ii < count) {
+                        const float* src = rr.d_relrow + (size_t)s_perm[ii] * D + c;
+                        if (V == 4) v[u] = load4(src); else v[u].x = src[0];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (i + u * LANES >= count) continue;
+                    g[0] += v[u].x;
+                    if (V == 4) { g[1 % V] += v[u].y; g[2 % V] += v[u].z; g[3 % V] += v[u].w; }
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < V; ++u) part[lane][col * V + u] = g[u];
+        __syncthreads();
+        if (lane == 0 && c < D) {
+#pragma unroll
+            for (int u = 0; u < V; ++u) {
+                float total = part[0][col * V + u];
+#pragma unroll
+                for (int l = 1; l < LANES; ++l) total += part[l][col * V + u];
+                dst_row[c + u] = total;
+            }
+        }
+    }
+}
+
 template <class ST, int V>
 __global__ void __launch_bounds__(64 * kSegmentLanes)
 k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c, RowLayout L,
@@ -972,8 +1088,15 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 const uint32_t* __restrict__ first_slot, const float* __restrict__ d_head,
                 const float* __restrict__ grad_recv, int B,
                 float* __restrict__ d_hid_h, float* __restrict__ d_hid_t,
-                const float* __restrict__ step_size, float lr_modifier, AdamParams ap, ExchangeSync sync, HeavyRows heavy) {
+                const float* __restrict__ step_size, float lr_modifier, AdamParams ap, ExchangeSync sync, HeavyRows heavy,
+                int R, RelationRows rr) {
     grid_dependency_sync();
+    if ((int)blockIdx.x >= kHeavySlots + R) {  // a relation row: needs nothing from the other processes
+        __shared__ float rel_part[kSegmentLanes][64 * V];
+        __shared__ uint32_t rel_perm[64 * kSegmentLanes];
+        relation_row_sum<V, kSegmentLanes>(rr, (int)blockIdx.x - kHeavySlots - R, (int)L.d, rel_part, rel_perm);
+        return;
+    }
     exchange_wait(sync, XCHG_TAIL_GRADS);  // grad_recv is written by the other processes
     // partial sums of the item lanes, [lane][head | tail][64 column threads][V]
     __shared__ float part[kSegmentLanes][2][64 * V];
@@ -1069,11 +1192,15 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         const size_t o = (size_t)r * D + c;
         if (V == 4) {
             if (d_hid_t) {
-                store4(d_hid_h + o, make_float4(gh[0], gh[1 % V], gh[2 % V], gh[3 % V]));
-                store4(d_hid_t + o, make_float4(gt[0], gt[1 % V], gt[2 % V], gt[3 % V]));
+                const float4 a = make_float4(gh[0], gh[1 % V], gh[2 % V], gh[3 % V]), b = make_float4(gt[0], gt[1 % V], gt[2 % V], gt[3 % V]);
+                store4(d_hid_h + o, a);
+                store4(d_hid_t + o, b);
+                if (rr.d_hid_h_lo) store4(rr.d_hid_h_lo + o, tf32_lower4(a));
+                if (rr.d_hid_t_lo) store4(rr.d_hid_t_lo + o, tf32_lower4(b));
             } else {
-                store4(d_hid_h + o, make_float4(gh[0] + gt[0], gh[1 % V] + gt[1 % V], gh[2 % V] + gt[2 % V],
-                                                gh[3 % V] + gt[3 % V]));
+                const float4 a = make_float4(gh[0] + gt[0], gh[1 % V] + gt[1 % V], gh[2 % V] + gt[2 % V], gh[3 % V] + gt[3 % V]);
+                store4(d_hid_h + o, a);
+                if (rr.d_hid_h_lo) store4(rr.d_hid_h_lo + o, tf32_lower4(a));  // lower plane for the projection gradient
             }
         } else {
             d_hid_h[o] = d_hid_t ? gh[0] : gh[0] + gt[0];
@@ -1344,6 +1471,7 @@ struct DenseUpdateArgs {
     const float* const* partials;  // [n_partial] the shards' slots in this process's receive buffer
     int n_partial;
     float* const* replicas;  // [n_replica] dense parameter vectors
+    float* const* replicas_lo;  // [n_replica] their lower TF32 planes (the projections are tensor-core operands); null: none
     int n_replica;
     float* adam_m;
     float* adam_v;
@@ -1392,6 +1520,10 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
             *reinterpret_cast<float4*>(a.adam_m + e) = m;
             *reinterpret_cast<float4*>(a.adam_v + e) = v;
             for (int rep = 0; rep < a.n_replica; ++rep) *reinterpret_cast<float4*>(a.replicas[rep] + e) = x;
+            if (a.replicas_lo && p > 0) {
+                const float4 lo = tf32_lower4(x);
+                for (int rep = 0; rep < a.n_replica; ++rep) *reinterpret_cast<float4*>(a.replicas_lo[rep] + e) = lo;
+            }
         }
     } else {
         for (size_t le = (size_t)blockIdx.x * blockDim.x + threadIdx.x; le < total; le += (size_t)gridDim.x * blockDim.x) {
@@ -1405,6 +1537,8 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
             a.adam_m[e] = m;
             a.adam_v[e] = v;
             for (int rep = 0; rep < a.n_replica; ++rep) a.replicas[rep][e] = x;
+            if (a.replicas_lo && p > 0)
+                for (int rep = 0; rep < a.n_replica; ++rep) a.replicas_lo[rep][e] = tf32_lower(x);
         }
     }
     exchange_signal(a.sync, XCHG_DENSE_PARAMS, gridDim.x);  // the new values are in every process's copy
@@ -1728,6 +1862,11 @@ k_gather_rows(const float* __restrict__ table, size_t width, const uint32_t* __r
     } else {
         for (size_t c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
     }
+}
+
+// lo[e] = the lower TF32 plane of x[e] (for parameters that the host writes).
+static __global__ void __launch_bounds__(256) k_lower_plane(const float* __restrict__ x, size_t n, float* __restrict__ lo) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) lo[e] = tf32_lower(x[e]);
 }
 
 // Operator form of the duplicate-combining scatter-add: one block per table row, summing

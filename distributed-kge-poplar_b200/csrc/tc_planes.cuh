@@ -54,20 +54,27 @@ struct PlaneProblem {
     GemmArgs g;
 };
 
-// Folded into the epilogue of hidden = value + feature . W: the lookups of the step
-// (src/poplar_kge.cpp:676-684).  `perm` lists the lookups ordered by the hidden row they read,
-// `off[r]` is where row r's begin.  Lookup e < B is head lookup e: pred[e] = f(row, relation row);
-// lookup e >= B is tail lookup e - B: the row goes to slot (e - B) % a2a of the destination shard
-// (e - B) / a2a.  Null `perm`: no routing.
+// Folded into the epilogue of hidden = value + feature . W: the lookups of the step and the send
+// half of the exchange (src/poplar_kge.cpp:676-684).  `perm` lists the lookups ordered by the hidden
+// row they read, `off[r]` is where row r's begin (k_prepare_segments).  Lookup e < B is head lookup
+// e: pred[e] = row (+|*) relation row; lookup e >= B is tail lookup e - B: the row goes to slot
+// (e - B) % a2a of destination shard (e - B) / a2a, whose buffer may be a peer's memory.  Both also
+// get their lo plane (the score gradients read them as tensor-core operands).  mode[p]: what
+// problem p of the launch routes (bit 0 heads, bit 1 tails; separate head / tail networks are two
+// problems).  Null `perm`: no routing.
 struct RouteArgs {
     const uint32_t* perm;
     const uint32_t* off;
     const uint32_t* relation;
     const float* rel_table;
-    float* const* send_dst;
+    float* const* send_dst;     // [n_shard] this shard's slot in every shard's tail buffer
+    float* const* send_lo_dst;  // [n_shard] the same in the lo plane
     float* pred;
-    int B, a2a, score_fn;
+    float* pred_lo;
+    int B, a2a, n_shard, score_fn;
+    int mode[2];
 };
+constexpr int kRouteMaxLookups = 4096;  // lookups one block may have to route (batch_size + n_shard * a2a_size)
 
 struct PlanePair {
     PlaneProblem p[2];
@@ -91,7 +98,8 @@ constexpr int kPlTmemSlots = 4;
 // in the same memory once the ring is idle), after alignment to 1024 bytes.
 constexpr size_t kPlRingBytes = 220 * 1024;
 constexpr size_t plane_smem_bytes() { return 1024 + kPlRingBytes; }
-static_assert(2 * (size_t)(kBM + kMaxClusterRows) * (128 + 1) * 4 <= kPlRingBytes, "the sent and the received rows fit the ring");
+static_assert(2 * (size_t)(kBM + kMaxClusterRows) * (128 + 1) * 4 <= 140 * 1024, "the sent and the received rows of a k split");
+static_assert(140 * 1024 + 64 * 128 * 4 <= 176 * 1024 && 176 * 1024 + (2 * 4096 + kBM + 1) * 4 <= kPlRingBytes, "finished rows and staged lookups behind them");
 
 // MN-major tile of 32-bit elements: atoms of 4 k-rows x 128 B (32 fp32 along mn) whose 32-byte
 // chunks are XOR-ed with the k-row index modulo 4; the next 32 mn are 4096 B further (leading byte
@@ -139,31 +147,79 @@ __device__ __forceinline__ float staged_row_sum(const uint8_t* tile, int mn_majo
     return s;
 }
 
-// The lookups that read hidden row m, for the four columns n .. n+3 whose values are `h`.
-__device__ __forceinline__ void route_four(const RouteArgs& rt, int m, int n, int D, const float (&h)[4]) {
-    const uint32_t q0 = rt.off[m], q1 = rt.off[m + 1];
-    for (uint32_t q = q0; q < q1; ++q) {
-        const uint32_t e = rt.perm[q];
-        if (e >= (uint32_t)rt.B) {
-            const uint32_t j = e - (uint32_t)rt.B, dst = j / (uint32_t)rt.a2a, slot = j - dst * (uint32_t)rt.a2a;
-            *reinterpret_cast<float4*>(rt.send_dst[dst] + (size_t)slot * D + n) = make_float4(h[0], h[1], h[2], h[3]);
-        } else {
-            // TransE / DistMult: elementwise with the relation row (ComplEx mixes the two halves of
-            // the row and keeps its own kernel)
-            const float4 r = *reinterpret_cast<const float4*>(rt.rel_table + (size_t)rt.relation[e] * D + n);
-            float4 o;
-            if (rt.score_fn == 0) o = make_float4(h[0] + r.x, h[1] + r.y, h[2] + r.z, h[3] + r.w);
-            else o = make_float4(h[0] * r.x, h[1] * r.y, h[2] * r.z, h[3] * r.w);
-            *reinterpret_cast<float4*>(rt.pred + (size_t)e * D + n) = o;
+__device__ __forceinline__ float tf32_lo(float v) { return tf32_hi(v - tf32_hi(v)); }
+
+// The routing phase of a block that has finished the hidden rows [row0, row0 + n_rows) x [n0, n0 + BN)
+// and left them in `fin` ([n_rows][BN], shared memory): every (lookup, 4 columns) pair is one unit
+// of work, spread over all threads, so a row that hundreds of lookups name costs no thread more
+// than any other.  s_look[i] = lookup | local row << 16 and s_rel[i] = relation of a head lookup
+// were staged by route_stage.
+template <int BN>
+__device__ __forceinline__ void route_rows(const RouteArgs& rt, int mode, const float* fin, const uint32_t* s_look, const uint32_t* s_rel,
+                                           int n_look, int n0, int D, int n_threads) {
+    constexpr int kQuads = BN / 4;
+    const int n_units = n_look * kQuads;
+    for (int u0 = threadIdx.x; u0 < n_units; u0 += 4 * n_threads) {
+        uint32_t look[4];
+        float4 h[4], r[4];
+        bool head[4], live[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int u = u0 + b * n_threads;
+            live[b] = u < n_units;
+            const int i = live[b] ? u / kQuads : 0, q = u % kQuads;
+            look[b] = s_look[i];
+            const uint32_t e = look[b] & 0xffffu;
+            head[b] = e < (uint32_t)rt.B;
+            live[b] = live[b] && n0 + q * 4 < D && ((head[b] ? mode & 1 : mode & 2) != 0);
+            h[b] = *reinterpret_cast<const float4*>(fin + (size_t)(look[b] >> 16) * BN + q * 4);
+            r[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live[b] && head[b]) r[b] = *reinterpret_cast<const float4*>(rt.rel_table + (size_t)s_rel[i] * D + n0 + q * 4);
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (!live[b]) continue;
+            const int q = (u0 + b * n_threads) % kQuads;
+            const uint32_t e = look[b] & 0xffffu;
+            float4 o = h[b];
+            float *dst, *dst_lo;
+            if (head[b]) {
+                // TransE / DistMult: elementwise with the relation row (ComplEx mixes the halves of a row: k_route)
+                if (rt.score_fn == 0) o = make_float4(o.x + r[b].x, o.y + r[b].y, o.z + r[b].z, o.w + r[b].w);
+                else o = make_float4(o.x * r[b].x, o.y * r[b].y, o.z * r[b].z, o.w * r[b].w);
+                dst = rt.pred + (size_t)e * D;
+                dst_lo = rt.pred_lo + (size_t)e * D;
+            } else {
+                const uint32_t j = e - (uint32_t)rt.B, shard = j / (uint32_t)rt.a2a, slot = j - shard * (uint32_t)rt.a2a;
+                dst = rt.send_dst[shard] + (size_t)slot * D;
+                dst_lo = rt.send_lo_dst[shard] + (size_t)slot * D;
+            }
+            *reinterpret_cast<float4*>(dst + n0 + q * 4) = o;
+            *reinterpret_cast<float4*>(dst_lo + n0 + q * 4) = make_float4(tf32_lo(o.x), tf32_lo(o.y), tf32_lo(o.z), tf32_lo(o.w));
         }
     }
 }
 
-// Epilogue and store of four neighbouring output columns, then the lookups that read them.
-__device__ __forceinline__ void finish_four_routed(const GemmArgs& g, const RouteArgs& rt, float* out_base, int m, int n,
-                                                   float (&acc)[4], const float (&x)[4], float rs) {
-    finish_four(g, out_base, m, n, acc, x, rs);
-    if (rt.perm) route_four(rt, m, n, g.N, acc);
+// Stages the lookups of the hidden rows [row0, row0 + n_rows) in shared memory and returns their
+// number (at most kRouteMaxLookups: the launcher refuses larger batches).  Called by all threads.
+__device__ __forceinline__ int route_stage(const RouteArgs& rt, int row0, int n_rows, uint32_t* s_off, uint32_t* s_look, uint32_t* s_rel,
+                                           int n_threads) {
+    if (n_rows <= 0) return 0;
+    for (int r = threadIdx.x; r <= n_rows; r += n_threads) s_off[r] = rt.off[row0 + r];
+    __syncthreads();
+    const uint32_t q_lo = s_off[0];
+    const int n_look = min((int)(s_off[n_rows] - q_lo), kRouteMaxLookups);
+    for (int i = threadIdx.x; i < n_look; i += n_threads) {
+        const uint32_t q = q_lo + (uint32_t)i, e = rt.perm[q];
+        int lo = 0, hi = n_rows;  // the row r with s_off[r] <= q < s_off[r + 1]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_off[mid] <= q) lo = mid; else hi = mid;
+        }
+        s_look[i] = e | ((uint32_t)lo << 16);
+        s_rel[i] = e < (uint32_t)rt.B ? rt.relation[e] : 0u;
+    }
+    return n_look;
 }
 
 // 32 consecutive accumulator columns of this thread's TMEM lane, without waiting for them.
@@ -324,6 +380,14 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     }
     __syncthreads();  // every slice has been read from TMEM (so the ring is idle); the row sums are in place
 
+    // Routing (hidden rows to their lookups): the finished rows and the staged lookups live in the
+    // idle ring, behind what the k-split exchange uses.
+    const bool routing = gp.route.perm != nullptr && gp.route.mode[which] != 0;
+    float* fin = reinterpret_cast<float*>(smem + 140 * 1024);                              // [<= 64 rows][BN], or [128][BN] at offset 0 without a k split
+    uint32_t* s_look = reinterpret_cast<uint32_t*>(smem + 176 * 1024);                      // [kRouteMaxLookups]
+    uint32_t* s_rel = s_look + kRouteMaxLookups;                                            // [kRouteMaxLookups]
+    uint32_t* s_off = s_rel + kRouteMaxLookups;                                             // [kBM + 1]
+    int route_n = 0;
     const bool acc_warp = warp >= 2;
     const int row = (warp & 3) * 32 + lane, m = m0 + row;
     const int nc0 = n0 + (acc_warp ? ((warp - 2) >> 2) * CPT : 0);  // first output column of an accumulating thread
@@ -366,6 +430,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
             if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i]);
         }
+        if (routing) route_n = route_stage(gp.route, m0 + r_begin, max(0, min(r_end, g.M - m0) - r_begin), s_off, s_look, s_rel, kPlThreads);
         __syncthreads();
         cluster_wait();
         if (warp == 0 && lane < n_split && lane != rank) {
@@ -393,10 +458,18 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                 if (ROWSUM) row_total += slot[(size_t)rows_each * BN + local];
             }
             const int mm = m0 + trow, nn = n0 + q * 4;
-            if (mm < g.M && nn < g.N) finish_four_routed(g, gp.route, g.out, mm, nn, sum, xv[i], row_total);
+            if (mm < g.M && nn < g.N) {
+                finish_four(g, g.out, mm, nn, sum, xv[i], row_total);
+                if (routing) *reinterpret_cast<float4*>(fin + (size_t)local * BN + q * 4) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+            }
         }
         cluster_wait();
-    } else if (acc_warp && m < g.M && nc0 < g.N) {
+    } else {
+        if (routing) {
+            fin = reinterpret_cast<float*>(smem);
+            route_n = route_stage(gp.route, m0, min(kBM, g.M - m0), s_off, s_look, s_rel, kPlThreads);
+        }
+        if (acc_warp && m < g.M && nc0 < g.N) {
         float* out_base = g.out_blocks ? nullptr : g.out + (size_t)blockIdx.z * g.split_stride;
         const float rs = ROWSUM ? s_rowsum[0][row] + s_rowsum[1][row] : 0.f;
 #pragma unroll
@@ -405,9 +478,15 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             float x[4];
             if (nc0 + j < g.N) {
                 load_x_four(g, m, nc0 + j, x);
-                finish_four_routed(g, gp.route, out_base, m, nc0 + j, four, x, rs);
+                finish_four(g, out_base, m, nc0 + j, four, x, rs);
+                if (routing) *reinterpret_cast<float4*>(fin + (size_t)row * BN + (nc0 - n0) + j) = make_float4(four[0], four[1], four[2], four[3]);
             }
         }
+        }
+    }
+    if (routing) {
+        __syncthreads();  // the finished rows are in `fin`
+        route_rows<BN>(gp.route, gp.route.mode[which], fin, s_look, s_rel, route_n, n0, g.N, kPlThreads);
     }
     tc_fence_before();
     __syncthreads();

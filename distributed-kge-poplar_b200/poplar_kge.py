@@ -595,11 +595,20 @@ class Engine:
             score=scores.transpose(0, 2, 1, 3).reshape(self.n_local, e.predict_hr_batch_size, -1))
         return merged.topk(e.predict_n_best).sort()
 
+    def predict_chunks(self, query_shards: np.ndarray) -> int:
+        """Engine "predict" calls needed for queries whose head shards are ``query_shards``: the
+        same on every process, whatever shards it holds."""
+        counts = np.bincount(np.asarray(query_shards, np.int64), minlength=self.settings.model.n_shard)
+        hr = self.settings.execution.predict_hr_batch_size
+        return int(-(-int(counts.max(initial=0)) // hr))
+
     def predict(self, shard_idx_relation: np.ndarray) -> Predictions:
         """Rank all entities as tails of (head shard, head row, relation) queries ``[q, 3]``.
 
-        Queries whose head lives on a shard of another process are left as zeros; with
-        world_size > 1 every process must call this the same number of times."""
+        Queries whose head lives on a shard of another process are left as zeros.  With
+        world_size > 1 every process passes the same query list: the number of engine calls is taken
+        from the longest per-shard list over ALL shards, so that every process makes the same number
+        of calls (each engine call synchronises the processes twice), padding with empty chunks."""
         q = np.asarray(shard_idx_relation)
         if q.ndim != 2 or q.shape[1] != 3:
             raise ValueError("shard_idx_relation should be of shape (n, 3)")
@@ -608,8 +617,7 @@ class Engine:
         per_shard = [np.flatnonzero(q[:, 0] == s) for s in local]
         out = Predictions(shard_idx=np.zeros((q.shape[0], e.predict_n_best, 2), np.uint32),
                           score=np.zeros((q.shape[0], e.predict_n_best), np.float32))
-        longest = max((len(x) for x in per_shard), default=0)
-        for lo in range(0, longest, e.predict_hr_batch_size):
+        for lo in range(0, self.predict_chunks(q[:, 0]) * e.predict_hr_batch_size, e.predict_hr_batch_size):
             chunk = np.zeros((self.n_local, e.predict_hr_batch_size, 2), dtype=np.uint32)
             picks = [x[lo : lo + e.predict_hr_batch_size] for x in per_shard]
             for l, rows in enumerate(picks):

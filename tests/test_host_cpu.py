@@ -151,3 +151,29 @@ def test_exchange_trace_summary():
     assert out["steps"] >= 190
     assert abs(out["tails"]["published"] - 20) < 1e-6 and abs(out["dense_params"]["wait_ended"] - 100) < 1e-6
     assert bench.summarise_exchange_trace(np.zeros(256 * 4 * 3)) == {"steps": 0}
+
+
+def test_predict_chunk_count_is_the_same_on_every_process():
+    """Each engine "predict" call synchronises the processes, so the number of calls must not
+    depend on which shards a process holds: it follows the longest per-shard query list over all
+    shards (uneven counts: shard 3 has 70 queries, shard 0 has 2, shard 1 none)."""
+    from distributed_kge_poplar_b200 import poplar_kge
+
+    settings = poplar_kge.Settings.create_demo().prepare()
+    settings.model.n_shard = 4
+    settings.execution.predict_hr_batch_size = 30
+    shards = np.array([0] * 2 + [2] * 31 + [3] * 70)
+
+    class Holder:  # predict_chunks reads nothing but the settings
+        pass
+
+    counts = []
+    for rank in range(4):
+        holder = Holder()
+        holder.settings = settings
+        counts.append(poplar_kge.Engine.predict_chunks(holder, shards))
+    assert counts == [3, 3, 3, 3]
+    holder = Holder()
+    holder.settings = settings
+    assert poplar_kge.Engine.predict_chunks(holder, np.zeros(0, np.int64)) == 0
+    assert poplar_kge.Engine.predict_chunks(holder, np.array([1] * 30)) == 1

@@ -95,36 +95,3 @@ def test_rowsum_epilogue(a_t):
     C = c.astype(np.float64).T if a_t else c.astype(np.float64)
     ref = C.sum(1, keepdims=True) * x - C @ y.astype(np.float64)
     assert_close(out, ref, RTOL, f"rowsum epilogue a_t={a_t}")
-
-
-@pytest.mark.parametrize("splits", [2, 3, 5, 8])
-@pytest.mark.parametrize("case", ["hidden", "l2_backward", "projection"])
-def test_split_reduced_through_cluster(case, splits, monkeypatch):
-    """The engine's form of a k split: the blocks of one output tile form a thread-block cluster,
-    send their partial rows to the block that finishes them and that block applies the epilogue.
-    The sum lands in the first slice of the result; the result must not depend on the split count
-    beyond rounding."""
-    monkeypatch.setenv("KGE_TC_WS", "1")
-    rng = np.random.RandomState(11)
-    if case == "hidden":  # fp16 rows times W stored [k, n], plus the value
-        m, n, k = 300, 256, 768
-        a = rng.normal(size=(m, k)).astype(np.float16)
-        b = rng.normal(size=(k, n)).astype(np.float32)
-        x = rng.normal(size=(m, n)).astype(np.float32)
-        out = capi.op_tc_gemm(a, b, m, n, k, b_transposed=True, epilogue=1, x=x, splits=splits, tile_n=64)[0]
-        ref = a.astype(np.float64) @ b.astype(np.float64) + x
-    elif case == "l2_backward":  # rowsum(A) * X - A . B with B stored [k, n]
-        m, n, k = 512, 192, 640
-        a = rng.normal(size=(m, k)).astype(np.float32)
-        b = rng.normal(size=(k, n)).astype(np.float32)
-        x = rng.normal(size=(m, n)).astype(np.float32)
-        out = capi.op_tc_gemm(a, b, m, n, k, b_transposed=True, epilogue=2, x=x, splits=splits, tile_n=64)[0]
-        a64 = a.astype(np.float64)
-        ref = a64.sum(1, keepdims=True) * x - a64 @ b.astype(np.float64)
-    else:  # both operands stored [k, .]: the projection gradient
-        m, n, k = 200, 128, 1280
-        a = rng.normal(size=(k, m)).astype(np.float16)
-        b = rng.normal(size=(k, n)).astype(np.float32)
-        out = capi.op_tc_gemm(a, b, m, n, k, a_transposed=True, b_transposed=True, splits=splits, tile_n=64)[0]
-        ref = a.astype(np.float64).T @ b.astype(np.float64)
-    assert_close(out, ref, RTOL, f"{case} splits={splits}")
