@@ -521,7 +521,7 @@ NoAllocScratch* no_alloc_scratch_for_current_device() {
 int kge_op_scatter_add_rows_noalloc(const float* grad_rows, const uint32_t* indices, size_t n, size_t rows, size_t width,
                                     float* grad_table, void* cuda_stream) {
     return guarded(g_error, [&] {
-        require(grad_rows && indices && grad_table, "kge_op_scatter_add_rows_noalloc: null argument");
+        require(grad_table && (n == 0 || (grad_rows && indices)), "kge_op_scatter_add_rows_noalloc: null argument");
         if (n > kNoAllocMaxLookups)
             fail(KGE_INVALID_ARGUMENT, msg() << "kge_op_scatter_add_rows_noalloc: " << n << " lookups exceed the fixed working memory ("
                                              << kNoAllocMaxLookups << " lookups)");

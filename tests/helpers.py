@@ -164,3 +164,38 @@ def assert_close(actual, expected, rtol: float, what: str, atol_scale: float = 1
     assert np.all(err <= bound), (
         f"{what}: max violation at {worst}: actual {actual[worst]!r} expected {expected[worst]!r} "
         f"(rtol {rtol}, tensor rms {scale:.3g})")
+
+
+def philox_normal4(seed: int, stream: int, row: np.ndarray, col4: np.ndarray) -> np.ndarray:
+    """Numpy restatement of the engine's counter-based normal generator (csrc/kernels.cuh,
+    philox_normal4): Philox-4x32-10 keyed by (seed, stream), counted by (row, column / 4), then two
+    Box-Muller pairs.  Returns [..., 4] float64 for broadcast ``row`` / ``col4`` arrays."""
+    row, col4 = np.broadcast_arrays(np.asarray(row, np.uint64), np.asarray(col4, np.uint64))
+    mask = np.uint64(0xFFFFFFFF)
+    c = [row & mask, col4 & mask, np.full(row.shape, stream, np.uint64), np.full(row.shape, 0x6B676562, np.uint64)]
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64((0x9E3779B9 ^ stream) & 0xFFFFFFFF)
+    m0, m1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+    for _ in range(10):
+        p0, p1 = m0 * c[0], m1 * c[2]  # 32 x 32 -> 64 bit products
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0 = (k0 + np.uint64(0x9E3779B9)) & mask
+        k1 = (k1 + np.uint64(0xBB67AE85)) & mask
+    u = [((x >> np.uint64(8)).astype(np.float64) + 0.5) / 16777216.0 for x in c]
+    r0, r1 = np.sqrt(-2.0 * np.log(u[0])), np.sqrt(-2.0 * np.log(u[2]))
+    a0, a1 = 2.0 * np.pi * u[1], 2.0 * np.pi * u[3]
+    return np.stack([r0 * np.cos(a0), r0 * np.sin(a0), r1 * np.cos(a1), r1 * np.sin(a1)], axis=-1)
+
+
+def expected_initial_table(seed: int, shard: int, n_rows: int, d: int, f: int, stddev: float) -> np.ndarray:
+    """What "initialise_entities" leaves in a shard: [n_rows, 3d + f] float64 (value ~ N(0, stddev),
+    zero optimiser state, features ~ N(0, 1) from a second stream, zero features in row 0)."""
+    rows = np.arange(n_rows)[:, None]
+    out = np.zeros((n_rows, 3 * d + f))
+    value = philox_normal4(seed, shard, rows, np.arange((d + 3) // 4)[None, :]).reshape(n_rows, -1)[:, :d]
+    out[:, :d] = stddev * value
+    if f:
+        feat = philox_normal4(seed ^ 0x5BD1E995, shard, rows, np.arange((f + 3) // 4)[None, :]).reshape(n_rows, -1)[:, :f]
+        feat[0] = 0
+        out[:, 3 * d:] = feat
+    return out

@@ -13,8 +13,8 @@ import numpy as np
 import pytest
 
 from distributed_kge_poplar_b200 import capi
-from helpers import (BATCH_KEYS, assert_close, engine_settings, make_oracle, random_batch, random_state,
-                     read_state, write_state)
+from helpers import (BATCH_KEYS, assert_close, engine_settings, expected_initial_table, make_oracle, random_batch,
+                     random_state, read_rows, read_state, write_state)
 from oracle.step_oracle import StepConfig
 
 pytestmark = pytest.mark.gpu
@@ -341,6 +341,91 @@ def test_metric_step_shapes_match_the_cpp_port():
             assert_close(got[key], want[key], 5e-5, f"metric shapes: {key}")
     np.testing.assert_array_equal(got["step"], want["step"])
     engine.close()
+
+
+def _err(x, ref):
+    ref = np.asarray(ref, np.float64)
+    return float(np.max(np.abs(np.asarray(x, np.float64) - ref)) / (np.sqrt(np.mean(ref**2)) + 1e-300))
+
+
+def test_metric_step_shapes_against_the_float64_oracle():
+    """The same per-step shapes against the float64 numpy oracle (the one the reference's fixtures
+    pin).  First step: loss, hidden rows and scores within plain 1e-5.  After three steps the updated
+    state is a sum of 768 to 1280 cancelling float32 terms per element, which no float32 arithmetic
+    holds to 1e-5; instead of asserting a looser constant, the engine's distance from float64 is
+    measured against that of the same oracle run in float32, and must be no more than twice it."""
+    from oracle.step_oracle import Oracle
+
+    cfg = StepConfig(n_shard=2, n_entity=4001, n_relation_type=1388, embedding_size=256, entity_feature_size=768,
+                     batch_size=512, a2a_size=384, score_fn="TransE", distance_fn="L2", gamma=10.0,
+                     loss_type="softmax", correction_weight=1.0)
+    rw, lr = 512, 1e-3
+    state = random_state(cfg, 21, fp16_features=True, warm=True)
+    engine = capi.CEngine(engine_settings(cfg, n_step=1, feature_dtype="float16", rw_batch=rw))
+    write_state(engine, cfg, state, rw)
+    exact, single = Oracle(cfg, np.float64), Oracle(cfg, np.float32)
+    exact.set_state(state)
+    single.set_state(state)
+    B, T, R, D = cfg.batch_size, cfg.n_tail, cfg.n_remote, cfg.embedding_size
+    for i in range(3):
+        batch = random_batch(cfg, 1, 121 + i, pad=7)
+        want = exact.train_step_loop(lr, batch)
+        single.train_step_loop(lr, batch)
+        got = _run_engine(engine, cfg, batch, lr)
+        if i == 0:
+            assert_close(got, want, 1e-5, "metric shapes: loss of the first step", atol_scale=0)
+            for s in range(cfg.n_shard):
+                hidden = engine.debug_fetch("hidden", s, R * D).reshape(R, D)
+                assert_close(hidden, exact.last["hidden"][s], 1e-5, f"metric shapes: hidden[{s}]")
+                scores = cfg.gamma - engine.debug_fetch("raw_score", s, B * T).reshape(B, T)
+                assert_close(scores, exact.last["scores"][s], 1e-5, f"metric shapes: scores[{s}]")
+        else:
+            np.testing.assert_allclose(got, want, rtol=2e-5)
+    got, want, f32 = read_state(engine, cfg, rw, cfg.n_shard), exact.get_state(), single.get_state()
+    report = {}
+    for key in sorted(want):
+        if key == "step":
+            np.testing.assert_array_equal(got[key], want[key])
+            continue
+        parts = {key: slice(None)} if key != "entity_data" else {"value": slice(0, D), "adam_m": slice(D, 2 * D), "sqrt_adam_v": slice(2 * D, 3 * D)}
+        for name, sl in parts.items():
+            mine, theirs = _err(got[key][..., sl], want[key][..., sl]), _err(f32[key][..., sl], want[key][..., sl])
+            report[name] = (mine, theirs)
+            assert mine <= 2.0 * theirs + 2e-6, f"{name}: engine {mine:.2e} from float64, float32 numpy {theirs:.2e}"
+    print("distance from float64 (engine, float32 numpy):", {k: (f"{a:.1e}", f"{b:.1e}") for k, (a, b) in report.items()})
+    np.testing.assert_array_equal(got["entity_data"][..., 3 * D :], want["entity_data"][..., 3 * D :].astype(np.float32))
+    engine.close()
+
+
+def test_initialise_entities_fills_the_table_from_the_counter_based_generator():
+    """"initialise_entities" (the on-device stand-in for streaming a dataset through write_entity):
+    values ~ N(0, init_scale / d) and features ~ N(0, 1) that depend only on (seed, shard, row,
+    column), zero optimiser state, zero features in the padding row; checked against a numpy
+    restatement of the generator, for determinism across engines, and for its moments."""
+    cfg = StepConfig(n_shard=2, n_entity=300, n_relation_type=4, embedding_size=20, entity_feature_size=10, batch_size=8, a2a_size=6)
+    d, f = cfg.embedding_size, cfg.entity_feature_size
+    tables = {}
+    for seed in (5, 6):
+        for dtype in ("float32", "float16"):
+            engine = capi.CEngine(engine_settings(cfg, rw_batch=RW, seed=seed, dtype=dtype))
+            engine.run("initialise_entities", {})
+            tables[seed, dtype] = read_rows(engine, cfg, RW, cfg.n_shard, np.float32 if dtype == "float32" else np.float16).astype(np.float64)
+            if seed == 5 and dtype == "float32":
+                again = capi.CEngine(engine_settings(cfg, rw_batch=RW, seed=seed))
+                again.run("initialise_entities", {})
+                np.testing.assert_array_equal(read_rows(again, cfg, RW, cfg.n_shard), tables[seed, dtype])
+                again.close()
+            engine.close()
+    table = tables[5, "float32"]
+    for shard in range(cfg.n_shard):
+        want = expected_initial_table(5, shard, cfg.n_entity, d, f, 1.0 / d)
+        np.testing.assert_allclose(table[shard], want, rtol=2e-5, atol=2e-6)
+        np.testing.assert_allclose(tables[5, "float16"][shard], want, rtol=2e-3, atol=1e-4)  # the same numbers, stored in half
+    assert not np.any(table[..., d : 3 * d]) and not np.any(table[:, 0, 3 * d :])
+    assert not np.allclose(table[0], table[1]) and not np.allclose(table, tables[6, "float32"])  # shard and seed both matter
+    value, feat = table[..., :d], table[:, 1:, 3 * d :]
+    assert abs(value.mean()) < 0.1 / d and 0.95 / d < value.std() < 1.05 / d
+    assert abs(feat.mean()) < 0.05 and 0.95 < feat.std() < 1.05
 
 
 @pytest.mark.parametrize("separate", [False, True], ids=["shared_net", "two_nets"])

@@ -88,6 +88,40 @@ def test_predict_ties_are_broken_by_row():
     engine.close()
 
 
+def test_predict_ties_across_table_passes_and_shards():
+    """Ties between rows that different passes over the table score (a pass covers 4096 rows, so
+    rows 4096 and 4097 meet only in the running top-k) and between rows of different shards: the
+    best candidates are returned in ascending (shard, row) order.  Every tied row equals the
+    predicted tail exactly, so its distance is an exact zero on any arithmetic."""
+    cfg = StepConfig(n_shard=2, n_entity=4300, n_relation_type=2, embedding_size=8, entity_feature_size=0,
+                     batch_size=4, a2a_size=4, score_fn="TransE", distance_fn="L2", gamma=3.0)
+    state = random_state(cfg, 8)
+    state["relation_embedding"][1] = 0.0          # relation 1: predicted tail = the head row itself
+    tied = {0: [4094, 4095, 4096, 4097, 4098, 4200], 1: [2, 4096, 4097]}
+    head_row = 7
+    for shard, rows in tied.items():
+        state["entity_data"][shard, rows, :8] = state["entity_data"][0, head_row, :8]
+    engine = capi.CEngine(engine_settings(cfg, rw_batch=RW))
+    write_state(engine, cfg, state, RW)
+    n_best = 5
+    idx, score = _predict(engine, cfg, np.array([[0, head_row, 1]]), np.array([4299, 4299]), 8, n_best)
+    np.testing.assert_array_equal(score[0], np.full(n_best, 3.0, np.float32))   # gamma - 0
+    np.testing.assert_array_equal(idx[0, :, 0], [0, 0, 0, 0, 0])
+    np.testing.assert_array_equal(idx[0, :, 1], [7, 4094, 4095, 4096, 4097])
+    # per-shard lists before the merge: shard 1's candidates across its own pass boundary
+    scores = np.zeros((2, 2, 8, 5), np.float32)
+    indices = np.zeros((2, 2, 8, 5), np.uint32)
+    head = np.zeros((2, 8), np.uint32)
+    head[0, 0] = head_row
+    rel = np.ones((2, 8), np.uint32)
+    engine.run("predict", dict(predict_head=head, predict_relation=rel, predict_entity_count=np.array([4299, 4299], np.uint32),
+                               predict_scores=scores, predict_indices=indices))
+    np.testing.assert_array_equal(indices[0, 1, 0, :3], [2, 4096, 4097])
+    np.testing.assert_array_equal(scores[0, 1, 0, :3], [3.0, 3.0, 3.0])
+    assert np.all(scores[0, 1, 0, 3:] < 3.0)
+    engine.close()
+
+
 @pytest.mark.parametrize("case", ["demo", "mid"])
 def test_predict_matches_reference_model(case):
     g, s, cfg = _golden(case)

@@ -38,6 +38,26 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         np.testing.assert_allclose(got, want, rtol=1e-5)
 
 
+def test_against_numpy_and_indices_past_the_table_are_ignored():
+    """The operator's own definition, np.add.at into a zeroed table (the duplicate-combining
+    scatter-add of src/pag/pag.cpp:706-746), including what the header promises for indices that
+    are not below `rows`: their gradient rows are dropped.  Lookups of one row are added in
+    position order, which is the order np.add.at uses, so the sums agree to the last bit."""
+    rng = np.random.RandomState(9)
+    n, rows, width = 3000, 500, 48
+    grad = rng.normal(size=(n, width)).astype(np.float32)
+    idx = rng.randint(rows + 60, size=n).astype(np.uint32)   # about a tenth of them past the table
+    idx[:5] = [0, rows - 1, rows, rows + 59, 2**31 + 5]
+    assert np.any(idx >= rows)
+    want = np.zeros((rows, width), np.float32)
+    keep = idx < rows
+    np.add.at(want, idx[keep], grad[keep])
+    got = _device_call(grad, idx, rows)
+    np.testing.assert_array_equal(got, want)
+    empty = _device_call(grad[:0], idx[:0], rows)   # no lookups at all: a zeroed table
+    np.testing.assert_array_equal(empty, np.zeros_like(want))
+
+
 def test_sizes_beyond_the_fixed_array_are_refused():
     import torch
 
