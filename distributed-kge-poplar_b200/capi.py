@@ -30,6 +30,7 @@ SYMBOLS = (
     "kge_kernel_time_count", "kge_kernel_time", "kge_debug_fetch",
     "kge_op_pairwise", "kge_op_pairwise_grad", "kge_op_gather_rows", "kge_op_scatter_add_rows",
     "kge_op_scatter_add_rows_noalloc", "kge_op_tc_gemm", "kge_op_tc_planes",
+    "kge_microbench_rows", "kge_microbench_scores",
     "kge_op_activation", "kge_op_all_to_all",
 )
 
@@ -86,6 +87,8 @@ def load_library() -> C.CDLL:
                                    C.c_int, C.c_int, fp]
     lib.kge_op_tc_planes.argtypes = [fp, C.c_int, C.c_int, sz, sz, fp, C.c_int, sz, sz, sz, sz, sz, C.c_int, fp, C.c_int,
                                      C.c_int, C.c_int, C.c_int, fp, fp]
+    lib.kge_microbench_rows.argtypes = [C.c_int, sz, sz, u32p, sz, C.c_int, fp]
+    lib.kge_microbench_scores.argtypes = [C.c_int, sz, sz, sz, C.c_int, fp]
     lib.kge_op_activation.argtypes = [C.c_int, fp, fp, sz, sz, fp, fp]
     lib.kge_op_all_to_all.argtypes = [fp, sz, sz, fp]
     _lib = lib
@@ -322,6 +325,21 @@ def op_tc_planes(a, b, m: int, n: int, k: int, a_mn_major: bool = False, b_mn_ma
         m, n, k, epilogue, _fp(xx) if xx is not None else None, splits, tile_n, int(hi_is_cleared), repeat,
         C.byref(mean_us), _fp(out)))
     return out, float(mean_us.value)
+
+
+def microbench_rows(kind: int, table_rows: int, d: int, indices, repeat: int = 20) -> float:
+    """Mean device microseconds of the step's row gather (kind 0) or row-wise Adam scatter (kind 1)."""
+    idx = np.ascontiguousarray(indices, dtype=np.uint32)
+    us = C.c_float(0.0)
+    _op_check(load_library().kge_microbench_rows(kind, table_rows, d, idx.ctypes.data_as(C.POINTER(C.c_uint32)), idx.size, repeat, C.byref(us)))
+    return float(us.value)
+
+
+def microbench_scores(fn: int, m: int, n: int, k: int, repeat: int = 50) -> float:
+    """Mean device microseconds of m x n scores, k deep (fn: 0 L1, 1 L2, 2 dot, 3 L2 on the tensor cores)."""
+    us = C.c_float(0.0)
+    _op_check(load_library().kge_microbench_scores(fn, m, n, k, repeat, C.byref(us)))
+    return float(us.value)
 
 
 def op_activation(kind: int, x, grad_out) -> Tuple[np.ndarray, np.ndarray]:

@@ -419,7 +419,8 @@ int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows,
                      int tile_n, int hi_is_cleared, int repeat, float* mean_us, float* out) {
     return guarded(g_error, [&] {
         require(a && b && out, "kge_op_tc_planes: null argument");
-        require(epilogue >= 0 && epilogue <= 2 && (epilogue == 0 || x), "kge_op_tc_planes: bad epilogue or missing x");
+        require(epilogue >= 0 && epilogue <= 3 && (epilogue == 0 || epilogue == 3 || x), "kge_op_tc_planes: bad epilogue or missing x");
+        require(epilogue != 3 || (!a_mn_major && !b_mn_major), "kge_op_tc_planes: the distance epilogue needs both operands stored [mn][k]");
         require(splits >= 1 && splits <= tc::kMaxClusterSplits, "kge_op_tc_planes: splits must be between 1 and 8");
         require(tile_n == 64 || tile_n == 128, "kge_op_tc_planes: tile_n must be 64 or 128");
         require(m > 0 && n > 0 && k > 0, "kge_op_tc_planes: empty problem");
@@ -447,10 +448,13 @@ int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows,
         g.ldc = (long long)n; g.split_stride = 0;
         g.x_base = static_cast<const uint8_t*>(dx.p); g.x_row_stride_bytes = (long long)(n * 4);
         g.status = dstatus.as<unsigned>();
-        const bool rowsum = epilogue == tc::EPI_ROWSUM_X_MINUS;
         tc::PlaneLaunch prepared;
         KGE_CUDA(tc::prepare_planes(&p, 1, splits, tile_n, &prepared));
-        auto run = [&] { return rowsum ? tc::launch_prepared<true>(prepared, nullptr) : tc::launch_prepared<false>(prepared, nullptr); };
+        auto run = [&] {
+            if (epilogue == tc::EPI_ROWSUM_X_MINUS) return tc::launch_prepared<tc::SIDE_ROWSUM>(prepared, nullptr);
+            if (epilogue == tc::EPI_L2_DISTANCE) return tc::launch_prepared<tc::SIDE_NORMS>(prepared, nullptr);
+            return tc::launch_prepared<tc::SIDE_NONE>(prepared, nullptr);
+        };
         KGE_CUDA(run());
         finish_kernels();
         if (repeat > 0) {
@@ -473,6 +477,132 @@ int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows,
         KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
         if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_planes: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");
         to_host(out, dout, m * n * 4);
+    });
+}
+
+// ---------------------------------------------------------------------------
+// Device-timed single kernels for the microbenchmark (the reference's only kernel benchmark is
+// tests/pag/testPag.cpp:321-332; its whole-program profile is scripts/run_profile.py).  Inputs are
+// made on the device, the kernel under test is the one the training step launches, and the mean of
+// `repeat` back-to-back launches between two CUDA events is returned.
+
+}  // extern "C"
+
+namespace {
+static __global__ void k_fill_pattern(float* p, size_t n, uint32_t seed) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        uint32_t h = (uint32_t)e * 2654435761u + seed;
+        h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+        p[e] = ((float)(h >> 8) * (1.0f / 16777216.0f) - 0.5f) * 0.25f;
+    }
+}
+template <class Launch>
+float timed_launches(int repeat, Launch&& launch) {
+    KGE_CUDA(launch());
+    finish_kernels();
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    KGE_CUDA(cudaEventCreate(&e0));
+    KGE_CUDA(cudaEventCreate(&e1));
+    KGE_CUDA(cudaEventRecord(e0, nullptr));
+    cudaError_t err = cudaSuccess;
+    for (int it = 0; it < repeat && err == cudaSuccess; ++it) err = launch();
+    KGE_CUDA(cudaEventRecord(e1, nullptr));
+    KGE_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    KGE_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    KGE_CUDA(err);
+    return 1e3f * ms / (float)repeat;
+}
+}  // namespace
+
+extern "C" {
+
+// kind 0: the step's row gather (k_gather_step_rows) of `n` rows of [value | adam_m | sqrt(adam_v)]
+//         (3 * d fp32 per row) out of a table of `table_rows` rows into a compact copy;
+// kind 1: the row-wise Adam scatter (k_entity_update with one lookup per row) on the same rows:
+//         reads a gradient row and the gathered state, writes value / m / sqrt(v) back to the table.
+// indices [n] are table rows (host array; for kind 1 they must be distinct).
+int kge_microbench_rows(int kind, size_t table_rows, size_t d, const uint32_t* indices, size_t n, int repeat, float* mean_us) {
+    return guarded(g_error, [&] {
+        require(kind == 0 || kind == 1, "kge_microbench_rows: kind must be 0 (gather) or 1 (Adam scatter)");
+        require(indices && mean_us && repeat > 0 && n > 0 && d > 0 && d % 4 == 0, "kge_microbench_rows: bad argument");
+        for (size_t i = 0; i < n; ++i)
+            if (indices[i] >= table_rows) fail(KGE_INVALID_ARGUMENT, "kge_microbench_rows: index out of range");
+        RowLayout L{};
+        L.d = (uint32_t)d; L.f = 0;
+        L.off_m = (uint32_t)(d * 4); L.off_q = 2 * L.off_m; L.off_feat = 3 * L.off_m; L.row_bytes = L.off_feat;
+        DeviceBuffer table(table_rows * L.row_bytes), rows_c(n * L.row_bytes), idx(n * 4);
+        k_fill_pattern<<<1184, 256>>>(table.as<float>(), table_rows * 3 * d, 1u);
+        KGE_CUDA(cudaGetLastError());
+        to_device(idx, indices, n * 4);
+        const FeaturePlanes no_planes{nullptr, nullptr, 0u, L.off_feat};
+        auto gather = [&] {
+            return launch_dependent(k_gather_step_rows, dim3(blocks_for(n, 8)), dim3(256), 0, nullptr, table.as<uint8_t>(), L.row_bytes,
+                                    idx.as<uint32_t>(), (int)n, rows_c.as<uint8_t>(), no_planes);
+        };
+        if (kind == 0) {
+            *mean_us = timed_launches(repeat, gather);
+            return;
+        }
+        // one "head" lookup per gathered row: lookup i reads gradient row i and belongs to row i
+        std::vector<uint32_t> iota(n + 1), ones(n, 1u);
+        for (size_t i = 0; i <= n; ++i) iota[i] = (uint32_t)i;
+        DeviceBuffer perm(n * 4), off((n + 1) * 4), first(n * 4), grads(n * d * 4), d_hid(n * d * 4), step_size(4), heavy_count(4);
+        to_device(perm, iota.data(), n * 4);
+        to_device(off, iota.data(), (n + 1) * 4);
+        to_device(first, ones.data(), n * 4);
+        const float alpha = 1e-3f;
+        to_device(step_size, &alpha, 4);
+        KGE_CUDA(cudaMemset(heavy_count.p, 0, 4));
+        k_fill_pattern<<<1184, 256>>>(grads.as<float>(), n * d, 7u);
+        KGE_CUDA(gather());
+        finish_kernels();
+        const AdamParams ap{0.9f, 0.999f, 0.1f, 0.001f, 1e-8f, 0.f};
+        const HeavyRows heavy{nullptr, heavy_count.as<uint32_t>(), nullptr, nullptr};
+        *mean_us = timed_launches(repeat, [&] {
+            return launch_dependent(k_entity_update<float, 4>, dim3((unsigned)(kHeavySlots + n)), dim3(64 * kSegmentLanes), 0, nullptr, table.as<uint8_t>(),
+                                    rows_c.as<uint8_t>(), L, idx.as<uint32_t>(), perm.as<uint32_t>(), off.as<uint32_t>(), first.as<uint32_t>(),
+                                    grads.as<float>(), grads.as<float>(), (int)n, d_hid.as<float>(), (float*)nullptr, step_size.as<float>(), 1.0f, ap,
+                                    ExchangeSync{}, heavy, (int)n, RelationRows{});
+        });
+    });
+}
+
+// Scores of m queries against n shared tails, k deep, device-resident: fn 0 = L1 and 1 = L2 on the
+// FP32 pipe (k_score_wide), 2 = dot product and 3 = L2 in the form |a|^2 + |b|^2 - 2 a.b on the tensor
+// cores (k_tc_planes, 3xTF32).
+int kge_microbench_scores(int fn, size_t m, size_t n, size_t k, int repeat, float* mean_us) {
+    return guarded(g_error, [&] {
+        require(fn >= 0 && fn <= 3 && mean_us && repeat > 0 && m > 0 && n > 0 && k > 0 && k % 4 == 0, "kge_microbench_scores: bad argument");
+        DeviceBuffer a(m * k * 4), b(n * k * 4), a_lo(m * k * 4), b_lo(n * k * 4), out(m * n * 4), status(4);
+        k_fill_pattern<<<1184, 256>>>(a.as<float>(), m * k, 3u);
+        k_fill_pattern<<<1184, 256>>>(b.as<float>(), n * k, 5u);
+        k_lower_plane<<<1184, 256>>>(a.as<float>(), m * k, a_lo.as<float>());
+        k_lower_plane<<<1184, 256>>>(b.as<float>(), n * k, b_lo.as<float>());
+        KGE_CUDA(cudaMemset(status.p, 0, 4));
+        KGE_CUDA(cudaGetLastError());
+        if (fn <= 1) {
+            *mean_us = timed_launches(repeat, [&] { return launch_score(fn, a.as<float>(), b.as<float>(), out.as<float>(), (int)m, (int)n, (int)k, nullptr); });
+            return;
+        }
+        tc::PlaneProblem p{};
+        p.A = {a.as<float>(), a_lo.as<float>(), (long long)(k * 4), 0};
+        p.B = {b.as<float>(), b_lo.as<float>(), (long long)(k * 4), 0};
+        p.g.M = (int)m; p.g.N = (int)n; p.g.K = (int)k;
+        p.g.epilogue = fn == 3 ? tc::EPI_L2_DISTANCE : tc::EPI_STORE;
+        p.g.out = out.as<float>(); p.g.ldc = (long long)n; p.g.block_rows = 1;
+        p.g.status = status.as<unsigned>();
+        const unsigned tiles = blocks_for(m, 128) * blocks_for(n, 128);
+        int splits = (int)std::min<unsigned>({std::max(1u, 148u / tiles), std::max(1u, (unsigned)k / 64u), (unsigned)tc::kMaxClusterSplits});
+        while (splits > 1 && (unsigned)tc::max_resident_plane_clusters(splits) < tiles) --splits;
+        p.g.k_per_split = std::max(32, (int)(((k + splits - 1) / splits + 31) / 32 * 32));
+        tc::PlaneLaunch prepared;
+        KGE_CUDA(tc::prepare_planes(&p, 1, splits, 128, &prepared));
+        *mean_us = timed_launches(repeat, [&] {
+            return fn == 3 ? tc::launch_prepared<tc::SIDE_NORMS>(prepared, nullptr) : tc::launch_prepared<tc::SIDE_NONE>(prepared, nullptr);
+        });
     });
 }
 

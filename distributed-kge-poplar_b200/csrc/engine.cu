@@ -115,6 +115,7 @@ Config parse_config(const SettingMap& s) {
     c.world = get_or<unsigned>(s, "execution.world_size", get_unsigned, 1u);
     c.cuda_graph = get_or<bool>(s, "execution.cuda_graph", get_bool, true);
     c.tensor_cores = get_or<bool>(s, "execution.tensor_cores", get_bool, true);
+    c.l2_contraction = get_or<bool>(s, "execution.l2_contraction", get_bool, true);
 
     if (score_fn == "TransE") c.score_fn = SCORE_TRANSE;
     else if (score_fn == "DistMult") c.score_fn = SCORE_DISTMULT;
@@ -944,7 +945,7 @@ void Engine::launch_tc(const char* name, tc::GemmArgs* problems, int n_problems,
 // One launch of the plane-fed contraction for one or two problems of the same shape class.  Tiles
 // are 128 x 128 (128 x 64 for narrow outputs); the k range is split over the blocks of a cluster so
 // that about one block per SM is busy and every split keeps at least two 32-deep slices.
-void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_problems, bool rowsum, int wait_kind, int signal_kind,
+void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_problems, int side, int wait_kind, int signal_kind,
                            const tc::RouteArgs* route) {
     int max_n = 0, max_k = 0;
     unsigned tiles = 0;
@@ -963,8 +964,10 @@ void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_p
         g.k_per_split = std::max(32, (int)round_up(ceil_div((unsigned)g.K, (unsigned)splits), 32));
     }
     timing_begin(name);
-    const cudaError_t err = rowsum ? tc::launch_planes<true>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route)
-                                   : tc::launch_planes<false>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route);
+    cudaError_t err;
+    if (side == tc::SIDE_ROWSUM) err = tc::launch_planes<tc::SIDE_ROWSUM>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route);
+    else if (side == tc::SIDE_NORMS) err = tc::launch_planes<tc::SIDE_NORMS>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route);
+    else err = tc::launch_planes<tc::SIDE_NONE>(problems, n_problems, splits, tile_n, stream_, exchange_sync(), wait_kind, signal_kind, route);
     timing_end();
     ++launch_counter_;
     KGE_CUDA(err);
@@ -1026,7 +1029,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             route.B = (int)B; route.a2a = (int)cfg_.a2a_size; route.n_shard = (int)cfg_.n_shard; route.score_fn = cfg_.score_fn;
             route.mode[0] = two_nets ? 1 : 3;
             route.mode[1] = two_nets ? 2 : 0;
-            launch_planes("hidden", nets, n_nets, false, XCHG_DENSE_PARAMS, fused_route ? XCHG_TAILS : -1, fused_route ? &route : nullptr);
+            launch_planes("hidden", nets, n_nets, tc::SIDE_NONE, XCHG_DENSE_PARAMS, fused_route ? XCHG_TAILS : -1, fused_route ? &route : nullptr);
         } else {
             // no features: the hidden rows are the gathered values
             launch_exchange_wait(XCHG_DENSE_PARAMS);
@@ -1053,7 +1056,15 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             p.B = plane(b.tails, b.tails_lo, (long long)D * 4, false);
             p.g.M = (int)B; p.g.N = (int)T; p.g.K = (int)D;
             p.g.epilogue = tc::EPI_STORE; p.g.out = b.raw; p.g.ldc = T; p.g.block_rows = 1;
-            launch_planes("score", &p, 1, false, XCHG_TAILS, -1);
+            launch_planes("score", &p, 1, tc::SIDE_NONE, XCHG_TAILS, -1);
+        } else if (l2 && cfg_.l2_contraction) {
+            // the L2 distance as |p|^2 + |t|^2 - 2 p.t on the tensor cores (direct form where that cancels)
+            tc::PlaneProblem p{};
+            p.A = plane(b.pred, b.pred_lo, (long long)D * 4, false);
+            p.B = plane(b.tails, b.tails_lo, (long long)D * 4, false);
+            p.g.M = (int)B; p.g.N = (int)T; p.g.K = (int)D;
+            p.g.epilogue = tc::EPI_L2_DISTANCE; p.g.out = b.raw; p.g.ldc = T; p.g.block_rows = 1;
+            launch_planes("score", &p, 1, tc::SIDE_NORMS, XCHG_TAILS, -1);
         } else {
             KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_, sync)));
         }
@@ -1088,7 +1099,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             h.g.epilogue = g.g.epilogue;
             h.g.out = nullptr; h.g.out_blocks = b.grad_dst; h.g.block_rows = (int)cfg_.a2a_size; h.g.ldc = D;
             h.g.x_base = reinterpret_cast<const uint8_t*>(b.tails); h.g.x_row_stride_bytes = (long long)D * 4;
-            launch_planes("score_bwd", both, 2, l2, -1, XCHG_TAIL_GRADS);
+            launch_planes("score_bwd", both, 2, l2 ? tc::SIDE_ROWSUM : tc::SIDE_NONE, -1, XCHG_TAIL_GRADS);
         }
         if (cfg_.score_fn != SCORE_TRANSE)
             KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
@@ -1137,7 +1148,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             g.out = nullptr; g.out_blocks = b.dense_dst; g.block_rows = 1; g.block_cyclic = (int)cfg_.world;
             g.block_row_offset = (int)(n_rel + net * F); g.ldc = D;
         }
-        if (F > 0) launch_planes("projection_bwd", nets, (int)cfg_.n_net(), false, -1, XCHG_DENSE_PARTIALS);
+        if (F > 0) launch_planes("projection_bwd", nets, (int)cfg_.n_net(), tc::SIDE_NONE, -1, XCHG_DENSE_PARTIALS);
         else launch_exchange_signal(XCHG_DENSE_PARTIALS);  // the relation rows of the entity update are all there is
     }
     KGE_CUDA(cudaGetLastError());

@@ -38,6 +38,7 @@ struct Config {
     unsigned device_ordinal, rank, world;
     bool cuda_graph;
     bool tensor_cores;  // dense contractions on tcgen05 (3xTF32) instead of the FP32 pipe
+    bool l2_contraction;  // the L2 distance as |a|^2 + |b|^2 - 2 a.b on the tensor cores (direct form where it cancels)
 
     unsigned n_tail() const { return n_shard * a2a_size; }
     unsigned n_remote() const { return batch_size + n_tail(); }
@@ -146,7 +147,7 @@ class Engine {
     void launch_tc(const char* name, tc::GemmArgs* problems, int n_problems, int splits, bool a_exact, bool rowsum,
                    int wait_kind = -1, int signal_kind = -1);
     // the plane-fed contraction: tile width and k splits chosen here
-    void launch_planes(const char* name, tc::PlaneProblem* problems, int n_problems, bool rowsum, int wait_kind, int signal_kind,
+    void launch_planes(const char* name, tc::PlaneProblem* problems, int n_problems, int side, int wait_kind, int signal_kind,
                        const tc::RouteArgs* route = nullptr);
     void launch_step_planes(unsigned step, const LossParams& lp, float normaliser);
     void refresh_lower_plane(size_t offset, size_t count);

@@ -98,8 +98,8 @@ constexpr int kPlTmemSlots = 4;
 // in the same memory once the ring is idle), after alignment to 1024 bytes.
 constexpr size_t kPlRingBytes = 220 * 1024;
 constexpr size_t plane_smem_bytes() { return 1024 + kPlRingBytes; }
-static_assert(2 * (size_t)(kBM + kMaxClusterRows) * (128 + 1) * 4 <= 140 * 1024, "the sent and the received rows of a k split");
-static_assert(140 * 1024 + 64 * 128 * 4 <= 176 * 1024 && 176 * 1024 + (2 * 4096 + kBM + 1) * 4 <= kPlRingBytes, "finished rows and staged lookups behind them");
+static_assert(2 * ((size_t)(kBM + kMaxClusterRows) * (128 + 1) + 8 * 128) * 4 <= 150 * 1024, "the sent and the received rows of a k split");
+static_assert(150 * 1024 + 64 * 128 * 4 <= 184 * 1024 && 184 * 1024 + (2 * 4096 + kBM + 1) * 4 <= kPlRingBytes, "finished rows and staged lookups behind them");
 
 // MN-major tile of 32-bit elements: atoms of 4 k-rows x 128 B (32 fp32 along mn) whose 32-byte
 // chunks are XOR-ed with the k-row index modulo 4; the next 32 mn are 4096 B further (leading byte
@@ -125,8 +125,15 @@ __device__ __forceinline__ void tma_plane_tile(uint8_t* dst, const CUtensorMap* 
     }
 }
 
+// What the accumulating warps add up from the staged operand tiles while the slices pass:
+//   SIDE_ROWSUM  the row sums of A (the L2 backward needs rowsum(A) . X);
+//   SIDE_NORMS   the squared norms of the rows of A and of B (the L2 distance in contraction form).
+enum Side : int { SIDE_NONE = 0, SIDE_ROWSUM = 1, SIDE_NORMS = 2 };
+constexpr int EPI_L2_DISTANCE = 3;  // out = sqrt(|a|^2 + |b|^2 - 2 a.b), recomputed directly where that cancels
+
 // The sum of 16 of the 32 k of row `row` of a staged A tile, added in k order.  The upper plane
 // holds the operand's values themselves (the tensor core ignores their low bits), so it alone is read.
+template <bool SQUARE = false>
 __device__ __forceinline__ float staged_row_sum(const uint8_t* tile, int mn_major, int row, int half) {
     float s = 0.f;
     if (!mn_major) {
@@ -134,7 +141,8 @@ __device__ __forceinline__ float staged_row_sum(const uint8_t* tile, int mn_majo
         for (int c = 0; c < 4; ++c) {
             const uint32_t off = (uint32_t)row * 128u + ((((uint32_t)(half * 4 + c)) ^ ((uint32_t)row & 7u)) << 4);
             const float4 v = *reinterpret_cast<const float4*>(tile + off);
-            s += (v.x + v.y) + (v.z + v.w);
+            if (SQUARE) s += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+            else s += (v.x + v.y) + (v.z + v.w);
         }
     } else {
         const uint32_t base = (uint32_t)(row >> 5) * 4096u, r = (uint32_t)row & 31u;
@@ -222,6 +230,51 @@ __device__ __forceinline__ int route_stage(const RouteArgs& rt, int row0, int n_
     return n_look;
 }
 
+// Distances of A row m to the B rows n .. n+3 from the contraction: d^2 = |a|^2 + |b|^2 - 2 a.b
+// (src/poplar_extensions/distance.cpp:151-185 computes sqrt(sum (a - b)^2); the reference's own
+// comment at src/poplar_kge.cpp:376-396 names this expansion).  The expansion loses the distance
+// when the rows are close: where d^2 comes out below a fifth of |a|^2 + |b|^2 its relative error
+// could pass 5e-6, so it is recomputed there in the direct form from the rows themselves, which
+// also returns the exact zero for identical rows that the gradient rule tests for
+// (l2distance.codelet.cpp:149-158).  Both operands are k-major; `acc` = a.b, an = |a|^2, bn = |b|^2.
+__device__ __forceinline__ void finish_l2_four(const PlaneProblem& pp, int m, int n, float (&acc)[4], float an, const float (&bn)[4]) {
+    const GemmArgs& g = pp.g;
+    const float* a = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.A.hi) + (size_t)m * pp.A.row_stride_bytes);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (n + j >= g.N) continue;
+        float d2 = an + bn[j] - 2.f * acc[j];
+        if (d2 < 0.2f * (an + bn[j])) {
+            const float* b = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.B.hi) + (size_t)(n + j) * pp.B.row_stride_bytes);
+            float s0 = 0.f, s1 = 0.f;
+            int k = 0;
+            for (; k + 7 < g.K; k += 8) {
+                const float4 x0 = *reinterpret_cast<const float4*>(a + k), y0 = *reinterpret_cast<const float4*>(b + k);
+                const float4 x1 = *reinterpret_cast<const float4*>(a + k + 4), y1 = *reinterpret_cast<const float4*>(b + k + 4);
+                float d;
+                d = x0.x - y0.x; s0 = fmaf(d, d, s0); d = x0.y - y0.y; s0 = fmaf(d, d, s0);
+                d = x0.z - y0.z; s0 = fmaf(d, d, s0); d = x0.w - y0.w; s0 = fmaf(d, d, s0);
+                d = x1.x - y1.x; s1 = fmaf(d, d, s1); d = x1.y - y1.y; s1 = fmaf(d, d, s1);
+                d = x1.z - y1.z; s1 = fmaf(d, d, s1); d = x1.w - y1.w; s1 = fmaf(d, d, s1);
+            }
+            for (; k < g.K; ++k) {
+                const float d = a[k] - b[k];
+                s0 = fmaf(d, d, s0);
+            }
+            d2 = s0 + s1;
+        }
+        acc[j] = sqrtf(fmaxf(d2, 0.f));
+    }
+    float* out_row = g.out + (size_t)m * g.ldc;
+    if ((g.N & 3) == 0 && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(out_row) & 15) == 0) {
+        *reinterpret_cast<float4*>(out_row + n) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (n + j < g.N) out_row[n + j] = acc[j];
+    }
+}
+
 // 32 consecutive accumulator columns of this thread's TMEM lane, without waiting for them.
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -239,7 +292,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-template <int BN, bool ROWSUM>
+template <int BN, int SIDE>
 __global__ void __launch_bounds__(kPlThreads, 1)
 k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneMaps maps) {
     static_assert(BN == 64 || BN == 128, "tile widths: 64 or 128 columns");
@@ -249,6 +302,8 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     __shared__ uint64_t bar_reduce;
     __shared__ uint32_t tmem_slot;
     __shared__ float s_rowsum[2][kBM];
+    __shared__ float s_colsum[2][BN];
+    constexpr bool ROWSUM = SIDE != SIDE_NONE;
 
     const int which = (int)blockIdx.x >= gp.tiles_m0 ? 1 : 0;
     const PlaneProblem& pp = gp.p[which];
@@ -300,7 +355,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     float acc[CPT];
 #pragma unroll
     for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
-    float row_part = 0.f;
+    float row_part = 0.f, col_part = 0.f;
 
     if (warp == 0) {
         for (int kc = 0; kc < n_slices; ++kc) {
@@ -353,7 +408,12 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             const int s = kc % n_stages;
             mbar_wait(&bar_full[s], (uint32_t)((kc / n_stages) & 1), g.status, 7u);
             const uint8_t* stage = smem + (size_t)s * stage_bytes;
-            row_part += staged_row_sum(stage, pp.A.mn_major, row, half);
+            if (SIDE == SIDE_NORMS) {  // both operands k-major
+                row_part += staged_row_sum<true>(stage, 0, row, half);
+                if (row < BN) col_part += staged_row_sum<true>(stage + off_b, 0, row, half);
+            } else {
+                row_part += staged_row_sum(stage, pp.A.mn_major, row, half);
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_empty[s]);
         };
@@ -377,14 +437,15 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                 for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(r[c][j]);
         }
         if (ROWSUM) s_rowsum[half][row] = row_part;
+        if (SIDE == SIDE_NORMS && row < BN) s_colsum[half][row] = col_part;
     }
     __syncthreads();  // every slice has been read from TMEM (so the ring is idle); the row sums are in place
 
     // Routing (hidden rows to their lookups): the finished rows and the staged lookups live in the
     // idle ring, behind what the k-split exchange uses.
     const bool routing = gp.route.perm != nullptr && gp.route.mode[which] != 0;
-    float* fin = reinterpret_cast<float*>(smem + 140 * 1024);                              // [<= 64 rows][BN], or [128][BN] at offset 0 without a k split
-    uint32_t* s_look = reinterpret_cast<uint32_t*>(smem + 176 * 1024);                      // [kRouteMaxLookups]
+    float* fin = reinterpret_cast<float*>(smem + 150 * 1024);                              // [<= 64 rows][BN], or [128][BN] at offset 0 without a k split
+    uint32_t* s_look = reinterpret_cast<uint32_t*>(smem + 184 * 1024);                      // [kRouteMaxLookups]
     uint32_t* s_rel = s_look + kRouteMaxLookups;                                            // [kRouteMaxLookups]
     uint32_t* s_off = s_rel + kRouteMaxLookups;                                             // [kBM + 1]
     int route_n = 0;
@@ -401,7 +462,8 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
         cluster_arrive_relaxed();
         const int n_split = g.cluster_splits, rank = (int)cluster_rank();
         const int rows_each = (kBM + n_split - 1) / n_split;
-        const uint32_t slot_floats = (uint32_t)rows_each * BN + (uint32_t)((rows_each + 3) & ~3);  // rows | row sums
+        const uint32_t off_rowsum = (uint32_t)rows_each * BN, off_colsum = off_rowsum + (uint32_t)((rows_each + 3) & ~3);
+        const uint32_t slot_floats = off_colsum + (SIDE == SIDE_NORMS ? BN : 0);  // rows | row sums | column sums
         const uint32_t slot_bytes = slot_floats * 4u;
         float* staging = reinterpret_cast<float*>(smem);                   // [owner][rows_each][BN] + row sums, what I send
         float* receive = staging + (size_t)n_split * slot_floats;         // [source][rows_each][BN] + row sums, what I own
@@ -415,8 +477,11 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
 #pragma unroll
             for (int j = 0; j < CPT; j += 4)
                 *reinterpret_cast<float4*>(mine + (((c0 + (j >> 2)) ^ (row & 7)) << 2)) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-            if (ROWSUM && nc0 == n0) staging[(size_t)owner * slot_floats + (size_t)rows_each * BN + local] = s_rowsum[0][row] + s_rowsum[1][row];
+            if (ROWSUM && nc0 == n0) staging[(size_t)owner * slot_floats + off_rowsum + local] = s_rowsum[0][row] + s_rowsum[1][row];
         }
+        if (SIDE == SIDE_NORMS)  // every owner gets this split's part of the column norms
+            for (int u = tid; u < n_split * BN; u += kPlThreads)
+                staging[(size_t)(u / BN) * slot_floats + off_colsum + (u % BN)] = s_colsum[0][u % BN] + s_colsum[1][u % BN];
         fence_async_shared();  // the copy engine reads what the threads have just written
         const int r_begin = rank * rows_each, r_end = min(kBM, r_begin + rows_each);
         constexpr int kQuads = BN / 4;
@@ -449,17 +514,22 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             if (u >= n_units) continue;
             const int local = u / kQuads, q = u % kQuads, trow = r_begin + local;
             const int chunk = (q ^ (trow & 7)) << 2;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            float sum[4] = {0.f, 0.f, 0.f, 0.f}, col_total[4] = {0.f, 0.f, 0.f, 0.f};
             float row_total = 0.f;
             for (int z = 0; z < n_split; ++z) {
                 const float* slot = z == rank ? staging + (size_t)rank * slot_floats : receive + (size_t)z * slot_floats;
                 const float4 v = *reinterpret_cast<const float4*>(slot + (size_t)local * BN + chunk);
                 sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
-                if (ROWSUM) row_total += slot[(size_t)rows_each * BN + local];
+                if (ROWSUM) row_total += slot[off_rowsum + local];
+                if (SIDE == SIDE_NORMS) {
+                    const float4 c = *reinterpret_cast<const float4*>(slot + off_colsum + q * 4);
+                    col_total[0] += c.x; col_total[1] += c.y; col_total[2] += c.z; col_total[3] += c.w;
+                }
             }
             const int mm = m0 + trow, nn = n0 + q * 4;
             if (mm < g.M && nn < g.N) {
-                finish_four(g, g.out, mm, nn, sum, xv[i], row_total);
+                if (SIDE == SIDE_NORMS) finish_l2_four(pp, mm, nn, sum, row_total, col_total);
+                else finish_four(g, g.out, mm, nn, sum, xv[i], row_total);
                 if (routing) *reinterpret_cast<float4*>(fin + (size_t)local * BN + q * 4) = make_float4(sum[0], sum[1], sum[2], sum[3]);
             }
         }
@@ -477,8 +547,15 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             float four[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
             float x[4];
             if (nc0 + j < g.N) {
-                load_x_four(g, m, nc0 + j, x);
-                finish_four(g, out_base, m, nc0 + j, four, x, rs);
+                if (SIDE == SIDE_NORMS) {
+                    float cs[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) cs[u] = s_colsum[0][nc0 - n0 + j + u] + s_colsum[1][nc0 - n0 + j + u];
+                    finish_l2_four(pp, m, nc0 + j, four, rs, cs);
+                } else {
+                    load_x_four(g, m, nc0 + j, x);
+                    finish_four(g, out_base, m, nc0 + j, four, x, rs);
+                }
                 if (routing) *reinterpret_cast<float4*>(fin + (size_t)row * BN + (nc0 - n0) + j) = make_float4(four[0], four[1], four[2], four[3]);
             }
         }
@@ -543,12 +620,12 @@ inline bool planes_aligned(const PlaneOperand& op) {
     return reinterpret_cast<uintptr_t>(op.hi) % 16 == 0 && reinterpret_cast<uintptr_t>(op.lo) % 16 == 0 && op.row_stride_bytes % 16 == 0;
 }
 
-template <int BN, bool ROWSUM>
+template <int BN, int SIDE>
 inline cudaError_t configure_planes() {
     static bool configured[kMaxDeviceOrdinals] = {};
     const int slot = current_device_slot();
     if (slot >= 0 && configured[slot]) return cudaSuccess;
-    cudaError_t err = cudaFuncSetAttribute(k_tc_planes<BN, ROWSUM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plane_smem_bytes());
+    cudaError_t err = cudaFuncSetAttribute(k_tc_planes<BN, SIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plane_smem_bytes());
     if (err == cudaSuccess && slot >= 0) configured[slot] = true;
     return err;
 }
@@ -562,7 +639,7 @@ inline int max_resident_plane_clusters(int splits) {
     const int slot = current_device_slot();
     if (slot >= 0 && known[slot][splits]) return cached[slot][splits];
     int n = 0;
-    if (configure_planes<128, false>() == cudaSuccess) {
+    if (configure_planes<128, SIDE_NONE>() == cudaSuccess) {
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(1, 1, splits);
         config.blockDim = dim3(kPlThreads);
@@ -574,7 +651,7 @@ inline int max_resident_plane_clusters(int splits) {
         attribute[0].val.clusterDim.z = (unsigned)splits;
         config.attrs = attribute;
         config.numAttrs = 1;
-        if (cudaOccupancyMaxActiveClusters(&n, k_tc_planes<128, false>, &config) != cudaSuccess) {
+        if (cudaOccupancyMaxActiveClusters(&n, k_tc_planes<128, SIDE_NONE>, &config) != cudaSuccess) {
             n = 0;
             (void)cudaGetLastError();
         }
@@ -635,28 +712,31 @@ inline cudaError_t prepare_planes(const PlaneProblem* problems, int n_problems, 
     return cudaSuccess;
 }
 
-template <bool ROWSUM>
+template <int SIDE>
 inline cudaError_t launch_prepared(const PlaneLaunch& l, cudaStream_t stream) {
+    if (SIDE == SIDE_NORMS)
+        for (int i = 0; i < 2; ++i)
+            if (l.gp.p[i].A.mn_major || l.gp.p[i].B.mn_major || l.gp.p[i].g.out_blocks) return cudaErrorInvalidValue;
     if (l.tile_n == 128) {
-        cudaError_t err = configure_planes<128, ROWSUM>();
+        cudaError_t err = configure_planes<128, SIDE>();
         if (err != cudaSuccess) return err;
-        return launch_dependent_cluster(k_tc_planes<128, ROWSUM>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
+        return launch_dependent_cluster(k_tc_planes<128, SIDE>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
                                         (unsigned)l.splits, l.gp, l.maps);
     }
-    cudaError_t err = configure_planes<64, ROWSUM>();
+    cudaError_t err = configure_planes<64, SIDE>();
     if (err != cudaSuccess) return err;
-    return launch_dependent_cluster(k_tc_planes<64, ROWSUM>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
+    return launch_dependent_cluster(k_tc_planes<64, SIDE>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
                                     (unsigned)l.splits, l.gp, l.maps);
 }
 
-template <bool ROWSUM>
+template <int SIDE>
 inline cudaError_t launch_planes(const PlaneProblem* problems, int n_problems, int splits, int tile_n, cudaStream_t stream,
                                  const ExchangeSync& sync = ExchangeSync{}, int wait_kind = -1, int signal_kind = -1,
                                  const RouteArgs* route = nullptr) {
     PlaneLaunch l;
     cudaError_t err = prepare_planes(problems, n_problems, splits, tile_n, &l, sync, wait_kind, signal_kind, route);
     if (err != cudaSuccess) return err;
-    return launch_prepared<ROWSUM>(l, stream);
+    return launch_prepared<SIDE>(l, stream);
 }
 
 }  // namespace tc

@@ -183,7 +183,10 @@ int kge_op_tc_gemm(const void* a, int a_half, int a_transposed, const uint32_t* 
  * as TF32-exact planes in device memory (made here from the host arrays; in the step the producing
  * kernels write them) and the TMA unit feeds the tensor core directly.  a: stored [a_rows, a_cols]
  * fp32, A[m, k] = a[m, k] or a[k, m] when a_mn_major; a_exact: every value is exact in TF32 (e.g. it
- * came from fp16 storage).  b likewise.  Stored rows must be multiples of 16 bytes.  splits (1-8)
+ * came from fp16 storage).  b likewise.  Stored rows must be multiples of 16 bytes.  epilogue 0-2 as
+ * for kge_op_tc_gemm; 3: out[m, n] = the L2 distance of row m of A and row n of B in the form
+ * sqrt(|a|^2 + |b|^2 - 2 a.b) (src/poplar_extensions/distance.cpp:151-185), recomputed directly
+ * where the expansion cancels (both operands stored [mn][k]).  splits (1-8)
  * blocks share a tile's k range as one thread-block cluster; tile_n (64 or 128) is the tile's width;
  * out is [m, n].  The upper plane is the stored array itself, since the tensor core ignores the low
  * 13 bits of a TF32 operand; hi_is_cleared uses a copy with those bits cleared instead (same
@@ -194,6 +197,19 @@ int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows,
                      int b_mn_major, size_t b_rows, size_t b_cols, size_t m, size_t n, size_t k, int epilogue,
                      const float* x, int splits, int tile_n, int hi_is_cleared, int repeat, float* mean_us,
                      float* out);
+
+/*
+ * Device-timed kernels for the microbenchmark (BASELINE configuration 2; the reference's counterpart
+ * is its operator benchmark tests/pag/testPag.cpp:321-332 and scripts/run_profile.py:43-51).  Inputs
+ * are made on the device; *mean_us receives the mean device time of `repeat` back-to-back launches.
+ * kge_microbench_rows: kind 0 = the step's gather of n whole rows [value | adam_m | sqrt(adam_v)]
+ * (3 * d fp32) out of a table of table_rows rows; kind 1 = the row-wise Adam scatter on the same rows
+ * (one lookup per row; indices distinct).  kge_microbench_scores: m queries against n shared tails,
+ * k deep; fn 0 = L1, 1 = L2 (FP32 pipe), 2 = dot product, 3 = L2 as |a|^2 + |b|^2 - 2 a.b (tensor cores).
+ */
+int kge_microbench_rows(int kind, size_t table_rows, size_t d, const uint32_t* indices, size_t n, int repeat,
+                        float* mean_us);
+int kge_microbench_scores(int fn, size_t m, size_t n, size_t k, int repeat, float* mean_us);
 
 /*
  * kge_op_scatter_add_rows for callers that cannot allocate device memory.  It has no counterpart

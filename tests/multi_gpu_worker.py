@@ -50,7 +50,8 @@ def main() -> None:
         engine.run("train_step_loop", dict(learning_rate=np.full(n_local, lr, np.float32), loss=loss,
                                            **bench.local_slice(batch, rank, world)))
         assert_close(loss, want[mine], 1e-4, f"rank {rank} call {call}: loss", atol_scale=0)
-    dist.barrier()
+    # No host barrier here on purpose: a run ends only when every process's share of the dense
+    # update has arrived in this process's memory, so the state can be read straight away.
     got, ref = read_state(engine, cfg, rw, n_local), oracle.get_state()
     d = cfg.embedding_size
     assert_close(got["entity_data"][..., : 3 * d], ref["entity_data"][mine][..., : 3 * d], 1e-4, f"rank {rank}: rows")
@@ -59,7 +60,7 @@ def main() -> None:
             assert_close(got[key], ref[key], 1e-4, f"rank {rank}: {key}")
     np.testing.assert_array_equal(got["step"], ref["step"])
 
-    # ranking across processes
+    # ranking across processes, again with no host barrier since the training call
     hr, n_best = 8, 5
     rng = np.random.RandomState(9)
     head = (1 + rng.randint(cfg.n_entity - 1, size=(cfg.n_shard, hr))).astype(np.uint32)
@@ -90,6 +91,13 @@ def main() -> None:
             except RuntimeError as e:
                 assert "gave up" in str(e), str(e)
             assert time.time() - t0 < 60
+            # this engine's hand-over epochs now disagree with its peer's: it refuses further work
+            try:
+                engine.run("train_step_loop", dict(learning_rate=np.full(n_local, lr, np.float32),
+                                                   loss=np.zeros(n_local, np.float32), **batch))
+                raise AssertionError("an engine whose wait gave up should refuse further steps")
+            except RuntimeError as e:
+                assert "must be rebuilt" in str(e), str(e)
         dist.barrier()
     engine.close()
     dist.barrier()

@@ -102,3 +102,24 @@ def test_argument_errors():
     b = np.zeros((8, 8), np.float32)
     with pytest.raises(ValueError):
         capi.op_tc_planes(b, b, 8, 8, 8, splits=9)
+
+
+@pytest.mark.parametrize("tile_n", [64, 128])
+@pytest.mark.parametrize("splits", [1, 2, 4])
+def test_l2_distance_in_contraction_form(splits, tile_n):
+    """sqrt(|a|^2 + |b|^2 - 2 a.b) with the direct form where the expansion cancels: rows of b that
+    equal a row of a give an exact zero, near rows keep 1e-5 relative, and the rest agree with the
+    float64 distance to 1e-5 of the matrix's scale."""
+    rng = np.random.RandomState(3 + splits)
+    m, n, k = 200, 300, 256
+    a = rng.normal(size=(m, k)).astype(np.float32)
+    b = rng.normal(size=(n, k)).astype(np.float32)
+    b[5] = a[17]                                   # identical rows: distance exactly 0
+    b[6] = a[18] + np.float32(1e-3) * rng.normal(size=k).astype(np.float32)   # near rows: the expansion alone would lose these
+    b[7] = 10 * a[19]
+    out, _ = capi.op_tc_planes(a, b, m, n, k, epilogue=3, splits=splits, tile_n=tile_n)
+    ref = np.sqrt(((a.astype(np.float64)[:, None, :] - b.astype(np.float64)[None, :, :]) ** 2).sum(-1))
+    assert out[17, 5] == 0.0
+    np.testing.assert_allclose(out[18, 6], ref[18, 6], rtol=1e-5)
+    assert_close(out, ref, RTOL, f"L2 distance splits={splits} tile {tile_n}")
+    np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-30)
