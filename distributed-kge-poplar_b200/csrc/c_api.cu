@@ -562,7 +562,7 @@ int kge_microbench_rows(int kind, size_t table_rows, size_t d, const uint32_t* i
         const AdamParams ap{0.9f, 0.999f, 0.1f, 0.001f, 1e-8f, 0.f};
         const HeavyRows heavy{nullptr, heavy_count.as<uint32_t>(), nullptr, nullptr};
         *mean_us = timed_launches(repeat, [&] {
-            return launch_dependent(k_entity_update<float, 4>, dim3((unsigned)(kHeavySlots + n)), dim3(64 * kSegmentLanes), 0, nullptr, table.as<uint8_t>(),
+            return launch_dependent(k_entity_update<float, 4>, dim3((unsigned)(kHeavySlots + blocks_for(n, kRowsPerBlock))), dim3(64 * kSegmentLanes), 0, nullptr, table.as<uint8_t>(),
                                     rows_c.as<uint8_t>(), L, idx.as<uint32_t>(), perm.as<uint32_t>(), off.as<uint32_t>(), first.as<uint32_t>(),
                                     grads.as<float>(), grads.as<float>(), (int)n, d_hid.as<float>(), (float*)nullptr, step_size.as<float>(), 1.0f, ap,
                                     ExchangeSync{}, heavy, (int)n, RelationRows{});

@@ -1114,7 +1114,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
         const RelationRows rr{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst, (int)n_rel, (int)cfg_.world,
                               b.d_hid_h_lo, b.d_hid_t_lo};
-        const dim3 grid(kHeavySlots + R + n_rel), block(64 * kSegmentLanes);
+        const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
         if (cfg_.state_type == ST_F32)
             KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
                                                  step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,
@@ -1357,20 +1357,20 @@ void Engine::launch_one_step(unsigned step) {
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
         if (cfg_.state_type == ST_F32) {
             if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
             else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
         } else {
             if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
             else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(R + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
+                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
                                                 b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
         }

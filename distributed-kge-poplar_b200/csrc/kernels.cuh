@@ -1001,7 +1001,8 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
 // kHeavySlots blocks of the grid take one part each, leave its sums in `heavy_partial`, and the
 // block that arrives last at the row's counter adds the parts in part order and finishes the
 // row; the row's own block skips it.  Nothing waits, and the order of the additions is fixed.
-constexpr int kSegmentLanes = 4;  // threads groups that share one segment's lookups
+constexpr int kSegmentLanes = 4;  // threads groups that share the lookups of one part of a popular row
+constexpr int kRowsPerBlock = 8;  // gathered rows per block of k_entity_update: one warp each
 
 struct HeavyRows {
     const uint4* parts;      // [kHeavySlots] {gathered row, first lookup, end lookup, (first part's slot << 16) | (parts << 8) | part}
@@ -1091,10 +1092,11 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 const float* __restrict__ step_size, float lr_modifier, AdamParams ap, ExchangeSync sync, HeavyRows heavy,
                 int R, RelationRows rr) {
     grid_dependency_sync();
-    if ((int)blockIdx.x >= kHeavySlots + R) {  // a relation row: needs nothing from the other processes
+    const int row_blocks = (R + kRowsPerBlock - 1) / kRowsPerBlock;
+    if ((int)blockIdx.x >= kHeavySlots + row_blocks) {  // a relation row: needs nothing from the other processes
         __shared__ float rel_part[kSegmentLanes][64 * V];
         __shared__ uint32_t rel_perm[64 * kSegmentLanes];
-        relation_row_sum<V, kSegmentLanes>(rr, (int)blockIdx.x - kHeavySlots - R, (int)L.d, rel_part, rel_perm);
+        relation_row_sum<V, kSegmentLanes>(rr, (int)blockIdx.x - kHeavySlots - row_blocks, (int)L.d, rel_part, rel_perm);
         return;
     }
     exchange_wait(sync, XCHG_TAIL_GRADS);  // grad_recv is written by the other processes
@@ -1112,7 +1114,10 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         const uint4 h = heavy.parts[blockIdx.x];
         r = (int)h.x; q0 = h.y; q1 = h.z; info = h.w;
     } else {
-        r = (int)blockIdx.x - kHeavySlots;
+        // one warp per gathered row: nothing in a row's update needs more than a warp, and a block of
+        // eight independent warps keeps eight rows' loads in flight
+        r = ((int)blockIdx.x - kHeavySlots) * kRowsPerBlock + (int)(threadIdx.x >> 5);
+        if (r >= R) return;
         if (first_slot[r] & 2u) return;  // its lookups are summed part by part by the first blocks
         q0 = off[r]; q1 = off[r + 1];
     }
@@ -1238,10 +1243,38 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
 
     float gh[V], gt[V];
     if (!helper) {
-        for (int c0 = 0; c0 < D; c0 += 64 * V) {
-            const int c = c0 + col * V;
-            segment_sums(c, gh, gt);
-            if (lane == 0 && c < D) finish(c, gh, gt);
+        // the row's lookups in position order, four loads in flight; head and tail lookups apart
+        const int wl = threadIdx.x & 31;
+        for (int c0 = 0; c0 < D; c0 += 32 * V) {
+            const int c = c0 + wl * V;
+            if (c >= D) continue;
+#pragma unroll
+            for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
+            for (uint32_t q = q0; q < q1; q += 4) {
+                uint32_t e[4];
+                float4 g[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) e[u] = q + u < q1 ? perm[q + u] : 0xffffffffu;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (e[u] == 0xffffffffu) continue;
+                    const float* src = e[u] < (uint32_t)B ? d_head + (size_t)e[u] * D + c : grad_recv + (size_t)(e[u] - B) * D + c;
+                    if (V == 4) g[u] = load4(src); else g[u].x = src[0];
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (e[u] == 0xffffffffu) continue;
+                    if (e[u] < (uint32_t)B) {
+                        gh[0] += g[u].x;
+                        if (V == 4) { gh[1 % V] += g[u].y; gh[2 % V] += g[u].z; gh[3 % V] += g[u].w; }
+                    } else {
+                        gt[0] += g[u].x;
+                        if (V == 4) { gt[1 % V] += g[u].y; gt[2 % V] += g[u].z; gt[3 % V] += g[u].w; }
+                    }
+                }
+            }
+            finish(c, gh, gt);
         }
         return;
     }

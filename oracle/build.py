@@ -5,8 +5,9 @@
   oracle/_build/libbess_oracle.so   the C++ / OpenMP restatement of the step (csrc/bess_step.cpp)
   oracle/_ref/libref_distance.so    the reference's own portable L1 / L2 distance code, compiled
                                     from its codelet sources where they lie; built only when a
-                                    checkout of the reference is present (environment variable
-                                    REFERENCE_ROOT).  The stand-in Poplar headers under
+                                    checkout of the reference is present: the directory named by
+                                    the environment variable REFERENCE_ROOT, or a directory
+                                    `reference` beside this repository.  The stand-in Poplar headers under
                                     oracle/stubs/ let those two files compile on the host.
 """
 
@@ -18,7 +19,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE_ROOT = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REFERENCE_ROOT = Path(os.environ.get("REFERENCE_ROOT") or HERE.parent.parent / "reference")
 ORACLE_LIB = HERE / "_build" / "libbess_oracle.so"
 REF_LIB = HERE / "_ref" / "libref_distance.so"
 

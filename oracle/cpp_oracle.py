@@ -36,7 +36,24 @@ def load():
     lib.bess_oracle_step.argtypes = [C.POINTER(_Config), fp, fp, fp, fp, fp, fp, fp, C.POINTER(C.c_uint), C.c_float,
                                      up, up, up, up, up, fp]
     lib.bess_oracle_threads.restype = C.c_int
+    lib.bess_oracle_set_threads.argtypes = [C.c_int]
+    lib.bess_oracle_set_threads.restype = None
     return lib
+
+
+def _no_huge_pages(array: np.ndarray) -> None:
+    """A table of many gigabytes is mapped untouched and only the rows a run names are ever written.
+    With transparent huge pages every first touch would zero two megabytes; ordinary pages keep the
+    cost of a touched row at a few kilobytes.  Best effort: ignored where madvise is not available."""
+    try:
+        libc = C.CDLL("libc.so.6", use_errno=True)
+        page = 4096
+        start = (array.ctypes.data + page - 1) // page * page
+        length = (array.ctypes.data + array.nbytes - start) // page * page
+        if length > 0:
+            libc.madvise(C.c_void_p(start), C.c_size_t(length), 14 + 1)  # MADV_NOHUGEPAGE
+    except OSError:
+        pass
 
 
 class CppOracle:
@@ -51,6 +68,7 @@ class CppOracle:
         d, f = cfg.embedding_size, cfg.entity_feature_size
         n_net = len(cfg.projection_names) if f else 0
         self.entity_data = np.zeros((cfg.n_shard, cfg.n_entity, cfg.row_size), np.float32)
+        _no_huge_pages(self.entity_data)
         self.rel = [np.zeros((cfg.n_relation_type, d), np.float32) for _ in range(3)]
         self.proj = [np.zeros((max(n_net, 1), f, d), np.float32) for _ in range(3)]
         self.step = C.c_uint(0)
@@ -58,6 +76,9 @@ class CppOracle:
     @property
     def threads(self) -> int:
         return int(self.lib.bess_oracle_threads())
+
+    def set_threads(self, n: int) -> None:
+        self.lib.bess_oracle_set_threads(int(n))
 
     def set_state(self, state: Dict[str, np.ndarray]) -> None:
         self.entity_data[...] = state["entity_data"]

@@ -40,6 +40,16 @@ int bess_oracle_threads(void) {
 #endif
 }
 
+// The number of OpenMP threads of later steps (a launcher may have set OMP_NUM_THREADS=1 for its
+// worker processes; the timed CPU baseline uses all host cores whatever the environment says).
+void bess_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 }  // extern "C"
 
 namespace {

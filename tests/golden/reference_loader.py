@@ -5,7 +5,8 @@ The reference's ``poplar_kge.py`` imports two Poplar SDK modules (``libpvti``,
 installed.  Empty stand-ins are placed in ``sys.modules`` so the files import
 as they are; nothing of the SDK is emulated.  Only fixture generation and the
 CPU tests that validate the oracle use this, and only where a checkout of the
-reference is present (``REFERENCE_ROOT`` or the default path).
+reference is present: the directory named by ``REFERENCE_ROOT``, or a directory
+``reference`` beside this repository.
 """
 
 from __future__ import annotations
@@ -15,7 +16,7 @@ import sys
 import types
 from pathlib import Path
 
-REFERENCE_ROOT = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REFERENCE_ROOT = Path(os.environ.get("REFERENCE_ROOT") or Path(__file__).resolve().parents[3] / "reference")
 
 
 def available() -> bool:
