@@ -30,7 +30,7 @@ SYMBOLS = (
     "kge_kernel_time_count", "kge_kernel_time", "kge_debug_fetch",
     "kge_op_pairwise", "kge_op_pairwise_grad", "kge_op_gather_rows", "kge_op_scatter_add_rows",
     "kge_op_scatter_add_rows_noalloc", "kge_op_tc_gemm", "kge_op_tc_planes",
-    "kge_microbench_rows", "kge_microbench_scores",
+    "kge_microbench_rows", "kge_microbench_scores", "kge_op_tc_planes_bf16",
     "kge_op_activation", "kge_op_all_to_all",
 )
 
@@ -87,6 +87,7 @@ def load_library() -> C.CDLL:
                                    C.c_int, C.c_int, fp]
     lib.kge_op_tc_planes.argtypes = [fp, C.c_int, C.c_int, sz, sz, fp, C.c_int, sz, sz, sz, sz, sz, C.c_int, fp, C.c_int,
                                      C.c_int, C.c_int, C.c_int, fp, fp]
+    lib.kge_op_tc_planes_bf16.argtypes = [fp, C.c_int, sz, sz, fp, C.c_int, sz, sz, sz, sz, sz, C.c_int, C.c_int, C.c_int, fp, fp]
     lib.kge_microbench_rows.argtypes = [C.c_int, sz, sz, u32p, sz, C.c_int, fp]
     lib.kge_microbench_scores.argtypes = [C.c_int, sz, sz, sz, C.c_int, fp]
     lib.kge_op_activation.argtypes = [C.c_int, fp, fp, sz, sz, fp, fp]
@@ -324,6 +325,17 @@ def op_tc_planes(a, b, m: int, n: int, k: int, a_mn_major: bool = False, b_mn_ma
         _fp(a), int(a_mn_major), int(a_exact), a.shape[0], a.shape[1], _fp(b), int(b_mn_major), b.shape[0], b.shape[1],
         m, n, k, epilogue, _fp(xx) if xx is not None else None, splits, tile_n, int(hi_is_cleared), repeat,
         C.byref(mean_us), _fp(out)))
+    return out, float(mean_us.value)
+
+
+def op_tc_planes_bf16(a, b, m: int, n: int, k: int, a_mn_major: bool = False, b_mn_major: bool = False, splits: int = 1,
+                      tile_n: int = 128, repeat: int = 0):
+    """bf16 tensor-core contraction out[m, n] (see kge_op_tc_planes_bf16); returns (out, mean_us)."""
+    a, b = _f32(a), _f32(b)
+    out = np.empty((m, n), np.float32)
+    mean_us = C.c_float(0.0)
+    _op_check(load_library().kge_op_tc_planes_bf16(_fp(a), int(a_mn_major), a.shape[0], a.shape[1], _fp(b), int(b_mn_major),
+                                                   b.shape[0], b.shape[1], m, n, k, splits, tile_n, repeat, C.byref(mean_us), _fp(out)))
     return out, float(mean_us.value)
 
 

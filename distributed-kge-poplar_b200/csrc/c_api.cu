@@ -10,6 +10,8 @@
 #include "tc_gemm.cuh"
 #include "tc_planes.cuh"
 
+#include <cuda_bf16.h>
+
 using namespace kge;
 
 struct kge_engine {
@@ -518,6 +520,50 @@ float timed_launches(int repeat, Launch&& launch) {
 }  // namespace
 
 extern "C" {
+
+// The same contraction on bfloat16 operands (tcgen05.mma.kind::f16, fp32 accumulation): the form of
+// the 2e-2 tier (bf16 embeddings).  The host arrays are fp32; they are rounded to bf16 on the device.
+int kge_op_tc_planes_bf16(const float* a, int a_mn_major, size_t a_rows, size_t a_cols, const float* b, int b_mn_major, size_t b_rows,
+                          size_t b_cols, size_t m, size_t n, size_t k, int splits, int tile_n, int repeat, float* mean_us, float* out) {
+    return guarded(g_error, [&] {
+        require(a && b && out, "kge_op_tc_planes_bf16: null argument");
+        require(splits >= 1 && splits <= tc::kMaxClusterSplits, "kge_op_tc_planes_bf16: splits must be between 1 and 8");
+        require(tile_n == 64 || tile_n == 128, "kge_op_tc_planes_bf16: tile_n must be 64 or 128");
+        require(m > 0 && n > 0 && k > 0, "kge_op_tc_planes_bf16: empty problem");
+        require(a_rows >= (a_mn_major ? k : m) && a_cols >= (a_mn_major ? m : k), "kge_op_tc_planes_bf16: a is too small");
+        require(b_rows >= (b_mn_major ? k : n) && b_cols >= (b_mn_major ? n : k), "kge_op_tc_planes_bf16: b is too small");
+        require(a_cols % 8 == 0 && b_cols % 8 == 0, "kge_op_tc_planes_bf16: stored rows must be a multiple of 16 bytes");
+        const size_t na = a_rows * a_cols, nb = b_rows * b_cols;
+        DeviceBuffer da(na * 4), db(nb * 4), da16(na * 2), db16(nb * 2), dout(m * n * 4), dstatus(4);
+        to_device(da, a, na * 4);
+        to_device(db, b, nb * 4);
+        KGE_CUDA(cudaMemset(dstatus.p, 0, 4));
+        k_to_bf16<<<std::min(blocks_for(na, 256), 1184u), 256>>>(da.as<float>(), na, da16.as<__nv_bfloat16>());
+        k_to_bf16<<<std::min(blocks_for(nb, 256), 1184u), 256>>>(db.as<float>(), nb, db16.as<__nv_bfloat16>());
+        KGE_CUDA(cudaGetLastError());
+        tc::PlaneProblem p{};
+        p.A = {da16.as<float>(), nullptr, (long long)(a_cols * 2), a_mn_major ? 1 : 0, 2};
+        p.B = {db16.as<float>(), nullptr, (long long)(b_cols * 2), b_mn_major ? 1 : 0, 2};
+        tc::GemmArgs& g = p.g;
+        g.M = (int)m; g.N = (int)n; g.K = (int)k;
+        g.k_per_split = std::max(64, (int)(((k + splits - 1) / splits + 63) / 64 * 64));
+        g.epilogue = tc::EPI_STORE;
+        g.out = dout.as<float>(); g.block_rows = 1; g.ldc = (long long)n;
+        g.status = dstatus.as<unsigned>();
+        tc::PlaneLaunch prepared;
+        KGE_CUDA(tc::prepare_planes(&p, 1, splits, tile_n, &prepared));
+        auto run = [&] { return tc::launch_prepared<tc::SIDE_NONE>(prepared, nullptr); };
+        if (repeat > 0 && mean_us) *mean_us = timed_launches(repeat, run);
+        else {
+            KGE_CUDA(run());
+            finish_kernels();
+        }
+        unsigned status = 0;
+        KGE_CUDA(cudaMemcpy(&status, dstatus.p, 4, cudaMemcpyDeviceToHost));
+        if (status) fail(KGE_DEVICE_STATUS, msg() << "kge_op_tc_planes_bf16: a bounded wait on the tensor-core pipeline gave up (code " << status << ")");
+        to_host(out, dout, m * n * 4);
+    });
+}
 
 // kind 0: the step's row gather (k_gather_step_rows) of `n` rows of [value | adam_m | sqrt(adam_v)]
 //         (3 * d fp32 per row) out of a table of `table_rows` rows into a compact copy;

@@ -115,7 +115,7 @@ Config parse_config(const SettingMap& s) {
     c.world = get_or<unsigned>(s, "execution.world_size", get_unsigned, 1u);
     c.cuda_graph = get_or<bool>(s, "execution.cuda_graph", get_bool, true);
     c.tensor_cores = get_or<bool>(s, "execution.tensor_cores", get_bool, true);
-    c.l2_contraction = get_or<bool>(s, "execution.l2_contraction", get_bool, true);
+    c.l2_contraction = get_or<bool>(s, "execution.l2_contraction", get_bool, false);
 
     if (score_fn == "TransE") c.score_fn = SCORE_TRANSE;
     else if (score_fn == "DistMult") c.score_fn = SCORE_DISTMULT;

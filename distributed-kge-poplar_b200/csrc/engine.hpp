@@ -38,7 +38,11 @@ struct Config {
     unsigned device_ordinal, rank, world;
     bool cuda_graph;
     bool tensor_cores;  // dense contractions on tcgen05 (3xTF32) instead of the FP32 pipe
-    bool l2_contraction;  // the L2 distance as |a|^2 + |b|^2 - 2 a.b on the tensor cores (direct form where it cancels)
+    // The training step's L2 distance as |a|^2 + |b|^2 - 2 a.b on the tensor cores, with the direct form
+    // wherever the expansion cancels.  Off by default: with skewed entity popularity a quarter of a
+    // batch's (head, tail) pairs name the same popular entity, whose distance is the small relation
+    // vector, so the direct form is needed for too many pairs and the FP32-pipe kernel is faster.
+    bool l2_contraction;
 
     unsigned n_tail() const { return n_shard * a2a_size; }
     unsigned n_remote() const { return batch_size + n_tail(); }

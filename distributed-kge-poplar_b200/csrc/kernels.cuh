@@ -6,6 +6,7 @@
 // back the same way into a row-wise Adam update.  All arithmetic is fp32.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -881,9 +882,9 @@ __device__ __forceinline__ int lower_bound_key(const unsigned long long* keys, i
 
 // Rows with more than kHeavyMin lookups are cut into parts of kHeavyPart lookups, at most kHeavySlots
 // parts per shard and step (see k_entity_update).
-constexpr int kHeavySlots = 48;
-constexpr int kHeavyMin = 64;
-constexpr int kHeavyPart = 32;
+constexpr int kHeavySlots = 112;
+constexpr int kHeavyMin = 12;
+constexpr int kHeavyPart = 16;
 
 static __global__ void __launch_bounds__(512)
 k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict__ a2a_idx,
@@ -950,7 +951,7 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
     // Rows with many lookups are cut into parts for k_entity_update (bit 1 of first_slot marks them).
     // All threads look for such rows (there are at most (B + T) / kHeavyMin of them); one thread
     // then orders them by row, so that the slots do not depend on the timing, and hands out the parts.
-    constexpr int kMaxHeavyRows = 64;
+    constexpr int kMaxHeavyRows = 128;
     __shared__ int s_heavy_rows[kMaxHeavyRows];
     __shared__ int s_heavy_n;
     if (threadIdx.x == 0) s_heavy_n = 0;
@@ -1243,38 +1244,54 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
 
     float gh[V], gt[V];
     if (!helper) {
-        // the row's lookups in position order, four loads in flight; head and tail lookups apart
+        // the row's lookups in position order, four lookups and two column chunks (eight loads) in
+        // flight; head and tail lookups apart
         const int wl = threadIdx.x & 31;
-        for (int c0 = 0; c0 < D; c0 += 32 * V) {
-            const int c = c0 + wl * V;
-            if (c >= D) continue;
+        for (int c0 = 0; c0 < D; c0 += 64 * V) {
+            const int ca = c0 + wl * V, cb = ca + 32 * V;
+            if (ca >= D) continue;
+            const bool two = cb < D;
+            float hb[V], tb[V];
 #pragma unroll
-            for (int u = 0; u < V; ++u) gh[u] = gt[u] = 0.f;
+            for (int u = 0; u < V; ++u) gh[u] = gt[u] = hb[u] = tb[u] = 0.f;
             for (uint32_t q = q0; q < q1; q += 4) {
                 uint32_t e[4];
-                float4 g[4];
+                float4 ga[4], gb[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) e[u] = q + u < q1 ? perm[q + u] : 0xffffffffu;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    ga[u] = gb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (e[u] == 0xffffffffu) continue;
-                    const float* src = e[u] < (uint32_t)B ? d_head + (size_t)e[u] * D + c : grad_recv + (size_t)(e[u] - B) * D + c;
-                    if (V == 4) g[u] = load4(src); else g[u].x = src[0];
+                    const float* src = e[u] < (uint32_t)B ? d_head + (size_t)e[u] * D : grad_recv + (size_t)(e[u] - B) * D;
+                    if (V == 4) {
+                        ga[u] = load4(src + ca);
+                        if (two) gb[u] = load4(src + cb);
+                    } else {
+                        ga[u].x = src[ca];
+                        if (two) gb[u].x = src[cb];
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     if (e[u] == 0xffffffffu) continue;
                     if (e[u] < (uint32_t)B) {
-                        gh[0] += g[u].x;
-                        if (V == 4) { gh[1 % V] += g[u].y; gh[2 % V] += g[u].z; gh[3 % V] += g[u].w; }
+                        gh[0] += ga[u].x; hb[0] += gb[u].x;
+                        if (V == 4) {
+                            gh[1 % V] += ga[u].y; gh[2 % V] += ga[u].z; gh[3 % V] += ga[u].w;
+                            hb[1 % V] += gb[u].y; hb[2 % V] += gb[u].z; hb[3 % V] += gb[u].w;
+                        }
                     } else {
-                        gt[0] += g[u].x;
-                        if (V == 4) { gt[1 % V] += g[u].y; gt[2 % V] += g[u].z; gt[3 % V] += g[u].w; }
+                        gt[0] += ga[u].x; tb[0] += gb[u].x;
+                        if (V == 4) {
+                            gt[1 % V] += ga[u].y; gt[2 % V] += ga[u].z; gt[3 % V] += ga[u].w;
+                            tb[1 % V] += gb[u].y; tb[2 % V] += gb[u].z; tb[3 % V] += gb[u].w;
+                        }
                     }
                 }
             }
-            finish(c, gh, gt);
+            finish(ca, gh, gt);
+            if (two) finish(cb, hb, tb);
         }
         return;
     }
@@ -1895,6 +1912,11 @@ k_gather_rows(const float* __restrict__ table, size_t width, const uint32_t* __r
     } else {
         for (size_t c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
     }
+}
+
+// y[e] = x[e] rounded to bfloat16 (operands of the bf16 contractions that the host provides).
+static __global__ void __launch_bounds__(256) k_to_bf16(const float* __restrict__ x, size_t n, __nv_bfloat16* __restrict__ y) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) y[e] = __float2bfloat16_rn(x[e]);
 }
 
 // lo[e] = the lower TF32 plane of x[e] (for parameters that the host writes).

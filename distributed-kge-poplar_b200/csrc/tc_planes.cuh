@@ -45,6 +45,9 @@ struct PlaneOperand {
     const float* lo;             // TF32-exact remainder; null = the operand has one plane
     long long row_stride_bytes;  // multiple of 16
     int mn_major;                // 0: stored [mn][k], k contiguous; 1: stored [k][mn], mn contiguous
+    // 2: `hi` points at bfloat16 values, one plane, multiplied by tcgen05.mma.kind::f16 (the 2e-2 tier:
+    // bf16 embeddings with fp32 accumulation); 0 or 4: fp32 values as above.  One kind per launch.
+    int elem_bytes;
 };
 
 // One contraction: the planes of both operands and, in `g`, sizes, k split, epilogue and output
@@ -83,6 +86,7 @@ struct PlanePair {
     int wait_kind, signal_kind;
     RouteArgs route;
     int n_stages[2];  // ring stages of each problem (2 to kPlMaxStages), as many as the shared memory holds
+    int bf16;         // the operands are bfloat16 planes: 64-deep slices, kind::f16 products
 };
 
 struct PlaneMaps {
@@ -114,14 +118,43 @@ __device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr) 
     return d;
 }
 
-// The copies of one [ROWS x 32 k] slice of one plane.
+// MN-major tile of 16-bit elements under the ordinary 128-byte swizzle: atoms of 8 k-rows x 128 B
+// (64 elements along mn); a box holds 64 k-rows (8 KB), the next 64 mn are 8192 B further, the
+// next 8 k 1024 B further.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc16(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(8192 >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, fp32 accumulate, K = 16 per instruction.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Instruction descriptor for bf16 inputs (format 1 at bits 7-9 and 10-12), fp32 accumulator.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// The copies of one slice of one plane: [ROWS x 32 k] fp32 or [ROWS x 64 k] bf16 (16 KB for 128 rows either way).
 template <int ROWS>
-__device__ __forceinline__ void tma_plane_tile(uint8_t* dst, const CUtensorMap* map, int mn_major, int mn0, int k0, uint64_t* bar) {
+__device__ __forceinline__ void tma_plane_tile(uint8_t* dst, const CUtensorMap* map, int mn_major, int bf16, int mn0, int k0, uint64_t* bar) {
     if (!mn_major) {
         tma_load_2d(dst, map, k0, mn0, bar);
-    } else {
+    } else if (!bf16) {
 #pragma unroll
         for (int j = 0; j < ROWS / 32; ++j) tma_load_2d(dst + j * 4096, map, mn0 + 32 * j, k0, bar);
+    } else {
+#pragma unroll
+        for (int j = 0; j < ROWS / 64; ++j) tma_load_2d(dst + j * 8192, map, mn0 + 64 * j, k0, bar);
     }
 }
 
@@ -320,7 +353,8 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128;
     const int k_begin = blockIdx.z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
-    const int n_slices = max(0, (k_end - k_begin + kBK - 1) / kBK);
+    const int bf16 = gp.bf16, slice_k = bf16 ? 64 : kBK;
+    const int n_slices = max(0, (k_end - k_begin + slice_k - 1) / slice_k);
     const bool a_two = pp.A.lo != nullptr, b_two = pp.B.lo != nullptr;
     // a ring stage: A hi [| A lo] | B hi [| B lo]
     const uint32_t off_b = (a_two ? 2u : 1u) * kATile, stage_bytes = off_b + (b_two ? 2u : 1u) * kBTile;
@@ -363,12 +397,12 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             if (use >= 1) mbar_wait(&bar_empty[s], (uint32_t)((use - 1) & 1), g.status, 6u);
             if (lane == 0) {
                 uint8_t* stage = smem + (size_t)s * stage_bytes;
-                const int k0 = k_begin + kc * kBK;
+                const int k0 = k_begin + kc * slice_k;
                 mbar_arrive_expect(&bar_full[s], stage_bytes);
-                tma_plane_tile<kBM>(stage, &maps.a_hi[which], pp.A.mn_major, m0, k0, &bar_full[s]);
-                if (a_two) tma_plane_tile<kBM>(stage + kATile, &maps.a_lo[which], pp.A.mn_major, m0, k0, &bar_full[s]);
-                tma_plane_tile<BN>(stage + off_b, &maps.b_hi[which], pp.B.mn_major, n0, k0, &bar_full[s]);
-                if (b_two) tma_plane_tile<BN>(stage + off_b + kBTile, &maps.b_lo[which], pp.B.mn_major, n0, k0, &bar_full[s]);
+                tma_plane_tile<kBM>(stage, &maps.a_hi[which], pp.A.mn_major, bf16, m0, k0, &bar_full[s]);
+                if (a_two) tma_plane_tile<kBM>(stage + kATile, &maps.a_lo[which], pp.A.mn_major, bf16, m0, k0, &bar_full[s]);
+                tma_plane_tile<BN>(stage + off_b, &maps.b_hi[which], pp.B.mn_major, bf16, n0, k0, &bar_full[s]);
+                if (b_two) tma_plane_tile<BN>(stage + off_b + kBTile, &maps.b_lo[which], pp.B.mn_major, bf16, n0, k0, &bar_full[s]);
             }
             __syncwarp();
         }
@@ -388,6 +422,18 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                 const uint64_t db_hi = pp.B.mn_major ? make_mnmajor_sw128_desc(b_hi) : make_kmajor_sw128_desc(b_hi);
                 const uint64_t db_lo = pp.B.mn_major ? make_mnmajor_sw128_desc(b_lo) : make_kmajor_sw128_desc(b_lo);
                 uint32_t accumulate = 0u;
+                if (bf16) {
+                    // one bf16 plane per operand, four 16-deep products per 64-deep slice
+                    const uint32_t idesc16 = make_idesc_bf16(kBM, BN) | (pp.A.mn_major ? (1u << 15) : 0u) | (pp.B.mn_major ? (1u << 16) : 0u);
+                    const uint64_t da = pp.A.mn_major ? make_mnmajor_sw128_desc16(a_hi) : make_kmajor_sw128_desc(a_hi);
+                    const uint64_t db = pp.B.mn_major ? make_mnmajor_sw128_desc16(b_hi) : make_kmajor_sw128_desc(b_hi);
+                    const uint64_t sa = pp.A.mn_major ? (2048 >> 4) : (32 >> 4), sb = pp.B.mn_major ? (2048 >> 4) : (32 >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        umma_bf16(tmem_acc, da + (uint64_t)ks * sa, db + (uint64_t)ks * sb, idesc16, accumulate);
+                        accumulate = 1u;
+                    }
+                } else {
 #pragma unroll
                 for (int ks = 0; ks < kBK / 8; ++ks) {
                     const uint64_t ka = (uint64_t)ks * a_step, kb = (uint64_t)ks * b_step;
@@ -396,6 +442,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                     if (a_two) { umma_tf32(tmem_acc, da_lo + ka, db_hi + kb, idesc, accumulate); accumulate = 1u; }
                     umma_tf32(tmem_acc, da_hi + ka, db_hi + kb, idesc, accumulate);
                     accumulate = 1u;
+                }
                 }
                 umma_commit(&bar_empty[s]);
                 umma_commit(&bar_acc_ready[t]);
@@ -605,13 +652,16 @@ inline cudaError_t make_plane_map(const float* base, const PlaneOperand& op, int
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return cudaErrorNotSupported;
     if (reinterpret_cast<uintptr_t>(base) % 16 || op.row_stride_bytes % 16) return cudaErrorInvalidValue;
+    const bool bf16 = op.elem_bytes == 2;
     const cuuint64_t dims[2] = {(cuuint64_t)(op.mn_major ? mn : k), (cuuint64_t)(op.mn_major ? k : mn)};
     const cuuint64_t strides[1] = {(cuuint64_t)op.row_stride_bytes};
-    const cuuint32_t box[2] = {32u, (cuuint32_t)(op.mn_major ? kBK : rows)};
+    // 128 bytes along the contiguous dimension; a slice is 32 k deep in fp32 and 64 k deep in bf16
+    const cuuint32_t inner = bf16 ? 64u : 32u;
+    const cuuint32_t box[2] = {inner, (cuuint32_t)(op.mn_major ? inner : rows)};
     const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+    const CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims,
+                              strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              op.mn_major && !bf16 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
@@ -693,8 +743,11 @@ inline cudaError_t prepare_planes(const PlaneProblem* problems, int n_problems, 
         tiles_m += (problems[1].g.M + kBM - 1) / kBM;
         tiles_n = std::max(tiles_n, (problems[1].g.N + tile_n - 1) / tile_n);
     }
+    gp.bf16 = problems[0].A.elem_bytes == 2 ? 1 : 0;
     for (int i = 0; i < 2; ++i) {
         PlaneProblem& q = gp.p[i];
+        if ((q.A.elem_bytes == 2) != (gp.bf16 != 0) || (q.B.elem_bytes == 2) != (gp.bf16 != 0)) return cudaErrorInvalidValue;
+        if (gp.bf16 && (q.A.lo || q.B.lo || q.g.k_per_split % 64)) return cudaErrorInvalidValue;
         q.g.ws = nullptr;
         q.g.cluster_splits = splits > 1 ? splits : 0;
         if (!planes_aligned(q.A) || !planes_aligned(q.B)) return cudaErrorInvalidValue;
@@ -714,6 +767,7 @@ inline cudaError_t prepare_planes(const PlaneProblem* problems, int n_problems, 
 
 template <int SIDE>
 inline cudaError_t launch_prepared(const PlaneLaunch& l, cudaStream_t stream) {
+    if (SIDE != SIDE_NONE && l.gp.bf16) return cudaErrorInvalidValue;  // the side sums read fp32 tiles
     if (SIDE == SIDE_NORMS)
         for (int i = 0; i < 2; ++i)
             if (l.gp.p[i].A.mn_major || l.gp.p[i].B.mn_major || l.gp.p[i].g.out_blocks) return cudaErrorInvalidValue;

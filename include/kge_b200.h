@@ -199,6 +199,17 @@ int kge_op_tc_planes(const float* a, int a_mn_major, int a_exact, size_t a_rows,
                      float* out);
 
 /*
+ * The contraction on bfloat16 operands with fp32 accumulation (tcgen05.mma.kind::f16): the form in
+ * which DistMult / ComplEx scores and their gradients run when the embeddings are stored in bf16
+ * (`matMul`, src/poplar_kge.cpp:512-514, 571-573; the reference's reduced-precision tier is fp16
+ * rows, src/poplar_kge.cpp:405-417).  Host arrays are fp32 and are rounded to bf16 on the device;
+ * stored rows must be multiples of 8 elements.  Otherwise as kge_op_tc_planes with epilogue 0.
+ */
+int kge_op_tc_planes_bf16(const float* a, int a_mn_major, size_t a_rows, size_t a_cols, const float* b, int b_mn_major,
+                          size_t b_rows, size_t b_cols, size_t m, size_t n, size_t k, int splits, int tile_n, int repeat,
+                          float* mean_us, float* out);
+
+/*
  * Device-timed kernels for the microbenchmark (BASELINE configuration 2; the reference's counterpart
  * is its operator benchmark tests/pag/testPag.cpp:321-332 and scripts/run_profile.py:43-51).  Inputs
  * are made on the device; *mean_us receives the mean device time of `repeat` back-to-back launches.

@@ -123,3 +123,29 @@ def test_l2_distance_in_contraction_form(splits, tile_n):
     np.testing.assert_allclose(out[18, 6], ref[18, 6], rtol=1e-5)
     assert_close(out, ref, RTOL, f"L2 distance splits={splits} tile {tile_n}")
     np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-30)
+
+
+def _bf16_round(x):
+    """Round-to-nearest-even to bfloat16, returned as float32."""
+    bits = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32)
+
+
+@pytest.mark.parametrize("tile_n", [64, 128])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape,splits", [((128, 128, 64), 1), ((1024, 2048, 512), 1), ((1024, 512, 2048), 4), ((300, 264, 200), 2), ((5, 3, 9), 1)])
+def test_bf16_operands(shape, splits, a_mn, b_mn, tile_n):
+    """bfloat16 operands, fp32 accumulation (the 2e-2 tier's contraction): products of bf16 values
+    are exact in fp32, so against the float64 product of the rounded inputs only the order of the
+    fp32 additions shows."""
+    m, n, k = shape
+    rng = np.random.RandomState(m + n + k)
+    def stored(rows, cols):
+        return rng.normal(size=(rows, (cols + 7) // 8 * 8)).astype(np.float32)
+    a = stored(k, m) if a_mn else stored(m, k)
+    b = stored(k, n) if b_mn else stored(n, k)
+    A = _bf16_round(a.T if a_mn else a)[:m, :k].astype(np.float64)
+    B = _bf16_round(b.T if b_mn else b)[:n, :k].astype(np.float64)
+    out, _ = capi.op_tc_planes_bf16(a, b, m, n, k, a_mn_major=a_mn, b_mn_major=b_mn, splits=splits, tile_n=tile_n)
+    assert_close(out, A @ B.T, RTOL, f"bf16 {shape} a_mn={a_mn} b_mn={b_mn} tile {tile_n}")
