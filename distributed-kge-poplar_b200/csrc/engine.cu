@@ -110,6 +110,15 @@ Config parse_config(const SettingMap& s) {
     c.feature_type = s.count("execution.feature_dtype")
                          ? parse_storage("execution.feature_dtype", get_string(s, "execution.feature_dtype"))
                          : c.state_type;
+    c.value_bf16 = false;
+    if (s.count("execution.value_dtype")) {
+        const std::string v = get_string(s, "execution.value_dtype");
+        if (v == "bfloat16") c.value_bf16 = true;
+        else if (v != "float32" && v != "float16")
+            fail(KGE_INVALID_ARGUMENT, msg() << "'execution.value_dtype' must be 'bfloat16' or the row type, not '" << v << "'");
+        if (c.value_bf16 && c.state_type != ST_F32)
+            fail(KGE_INVALID_ARGUMENT, "'execution.value_dtype' 'bfloat16' needs 'execution.dtype' 'float32' (the optimiser state stays float32)");
+    }
     c.device_ordinal = get_or<unsigned>(s, "execution.device_ordinal", get_unsigned, 0u);
     c.rank = get_or<unsigned>(s, "execution.rank", get_unsigned, 0u);
     c.world = get_or<unsigned>(s, "execution.world_size", get_unsigned, 1u);
@@ -239,11 +248,12 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     shard0_ = cfg_.rank * n_local_;
 
     const size_t sb = type_bytes(cfg_.state_type), fb = type_bytes(cfg_.feature_type);
-    const uint32_t seg = (uint32_t)round_up(cfg_.d * sb, 16);
-    layout_.off_m = seg;
-    layout_.off_q = 2 * seg;
-    layout_.off_feat = 3 * seg;
-    layout_.row_bytes = 3 * seg + (uint32_t)round_up(cfg_.f * fb, 16);
+    const uint32_t seg = (uint32_t)round_up(cfg_.d * sb, 16), value_seg = cfg_.value_bf16 ? (uint32_t)round_up(cfg_.d * 2, 16) : seg;
+    layout_.off_m = value_seg;
+    layout_.off_q = value_seg + seg;
+    layout_.off_feat = value_seg + 2 * seg;
+    layout_.row_bytes = layout_.off_feat + (uint32_t)round_up(cfg_.f * fb, 16);
+    layout_.value_bf16 = cfg_.value_bf16 ? 1u : 0u;
     layout_.d = cfg_.d;
     layout_.f = cfg_.f;
 
@@ -317,6 +327,8 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     if (const char* v = std::getenv("KGE_PLANE_CONTRACTIONS")) planes_ = planes_ && std::atoi(v) != 0;
     // fp16 features are widened into rows of their own; the lower plane of fp32 features keeps the
     // stride of the rows whose feature part is its upper plane (one stride per operand)
+    bf16_planes_ = planes_ && cfg_.value_bf16 && cfg_.dist_fn == DIST_DOT && cfg_.d % 8 == 0 && cfg_.n_tail() % 8 == 0 && cfg_.batch_size % 8 == 0 &&
+                   (cfg_.a2a_size * cfg_.d) % 2 == 0;
     feat_stride_ = cfg_.feature_type == ST_F16 ? (uint32_t)round_up(cfg_.f, 4) : layout_.row_bytes / 4;
     allocate();
     peer_arena_.assign(cfg_.world, nullptr);
@@ -464,7 +476,8 @@ void Engine::build_pointer_tables() {
             uint8_t* base = peer_arena_[owner];
             send[d] = (float*)(base + arena_offset_shard(dl, 0)) + (size_t)me * block;
             grad[d] = (float*)(base + arena_offset_shard(dl, 1)) + (size_t)me * block;
-            send_lo[d] = (float*)(base + arena_offset_shard(dl, 2)) + (size_t)me * block;
+            // the companion plane holds rows of D bf16 values (half a float each) in the bf16 tier
+            send_lo[d] = (float*)(base + arena_offset_shard(dl, 2)) + (size_t)me * block / (bf16_planes_ ? 2 : 1);
         }
         KGE_CUDA(cudaMemcpy(shards_[l].send_lo_dst, send_lo.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
         KGE_CUDA(cudaMemcpy(shards_[l].send_dst, send.data(), sizeof(float*) * cfg_.n_shard, cudaMemcpyHostToDevice));
@@ -961,7 +974,8 @@ void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_p
     for (int i = 0; i < n_problems; ++i) {
         tc::GemmArgs& g = problems[i].g;
         g.status = d_tc_status_;
-        g.k_per_split = std::max(32, (int)round_up(ceil_div((unsigned)g.K, (unsigned)splits), 32));
+        const unsigned slice = problems[i].A.elem_bytes == 2 ? 64u : 32u;  // bf16 slices are 64 deep
+        g.k_per_split = (int)std::max<size_t>(slice, round_up(ceil_div((unsigned)g.K, (unsigned)splits), slice));
     }
     timing_begin(name);
     cudaError_t err;
@@ -982,6 +996,12 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
     const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d, F = cfg_.f;
     const unsigned n_rel = cfg_.n_relation_type, parity = step & 1;
     const bool two_nets = cfg_.n_net() == 2, l2 = cfg_.dist_fn == DIST_L2, l1 = cfg_.dist_fn == DIST_L1;
+    // bf16 embeddings: the dot-product scores and their gradients multiply bfloat16 copies of pred,
+    // tails and the coefficients (written by their producers into the companion planes)
+    const bool bf16 = bf16_planes_;
+    auto plane16 = [](const float* values, long long row_elems, bool mn_major) {
+        return tc::PlaneOperand{values, nullptr, row_elems * 2, mn_major ? 1 : 0, 2};
+    };
     const bool half_features = cfg_.feature_type == ST_F16;
     const float* rel_table = dense_;
     const ExchangeSync sync = exchange_sync();
@@ -1015,7 +1035,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
                 g.M = (int)R; g.N = (int)D; g.K = (int)F;
                 g.epilogue = tc::EPI_ADD_TABLE_VALUE;
                 g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
-                g.x_base = rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_is_half = cfg_.state_type == ST_F16;
+                g.x_base = rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_is_half = cfg_.value_bf16 ? 2 : (cfg_.state_type == ST_F16 ? 1 : 0);
             }
             tc::RouteArgs route{};
             route.perm = d_ent_perm_ + sidx * (B + T);
@@ -1029,6 +1049,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             route.B = (int)B; route.a2a = (int)cfg_.a2a_size; route.n_shard = (int)cfg_.n_shard; route.score_fn = cfg_.score_fn;
             route.mode[0] = two_nets ? 1 : 3;
             route.mode[1] = two_nets ? 2 : 0;
+            route.lo_bf16 = bf16 ? 1 : 0;
             launch_planes("hidden", nets, n_nets, tc::SIDE_NONE, XCHG_DENSE_PARAMS, fused_route ? XCHG_TAILS : -1, fused_route ? &route : nullptr);
         } else {
             // no features: the hidden rows are the gathered values
@@ -1040,7 +1061,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         if (!fused_route)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                           b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn, sync,
-                                                          b.send_lo_dst, b.pred_lo)));
+                                                          b.send_lo_dst, b.pred_lo, bf16 ? 1 : 0)));
     }
     KGE_CUDA(cudaGetLastError());
 
@@ -1052,8 +1073,8 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         // 2. scores
         if (cfg_.dist_fn == DIST_DOT) {
             tc::PlaneProblem p{};
-            p.A = plane(b.pred, b.pred_lo, (long long)D * 4, false);
-            p.B = plane(b.tails, b.tails_lo, (long long)D * 4, false);
+            p.A = bf16 ? plane16(b.pred_lo, D, false) : plane(b.pred, b.pred_lo, (long long)D * 4, false);
+            p.B = bf16 ? plane16(b.tails_lo, D, false) : plane(b.tails, b.tails_lo, (long long)D * 4, false);
             p.g.M = (int)B; p.g.N = (int)T; p.g.K = (int)D;
             p.g.epilogue = tc::EPI_STORE; p.g.out = b.raw; p.g.ldc = T; p.g.block_rows = 1;
             launch_planes("score", &p, 1, tc::SIDE_NONE, XCHG_TAILS, -1);
@@ -1070,7 +1091,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         }
         // 3. loss and the coefficients of the score gradients
         KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
-                                                     d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo)));
+                                                     d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0)));
         // 4. score gradients; the tails' rows go straight to the shards that own them
         if (l1) {
             PairBwdArgs pa{};
@@ -1086,15 +1107,15 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             //   L2:   d_pred = rowsum(C) * pred - C . tails,       d_tails = colsum(C) * tails - C^T . pred
             tc::PlaneProblem both[2] = {};
             tc::PlaneProblem& g = both[0];
-            g.A = plane(b.coeff, b.coeff_lo, (long long)T * 4, false);
-            g.B = plane(b.tails, b.tails_lo, (long long)D * 4, true);
+            g.A = bf16 ? plane16(b.coeff_lo, T, false) : plane(b.coeff, b.coeff_lo, (long long)T * 4, false);
+            g.B = bf16 ? plane16(b.tails_lo, D, true) : plane(b.tails, b.tails_lo, (long long)D * 4, true);
             g.g.M = (int)B; g.g.N = (int)D; g.g.K = (int)T;
             g.g.epilogue = l2 ? tc::EPI_ROWSUM_X_MINUS : tc::EPI_STORE;
             g.g.out = b.d_pred; g.g.ldc = D; g.g.block_rows = 1;
             g.g.x_base = reinterpret_cast<const uint8_t*>(b.pred); g.g.x_row_stride_bytes = (long long)D * 4;
             tc::PlaneProblem& h = both[1];
-            h.A = plane(b.coeff, b.coeff_lo, (long long)T * 4, true);
-            h.B = plane(b.pred, b.pred_lo, (long long)D * 4, true);
+            h.A = bf16 ? plane16(b.coeff_lo, T, true) : plane(b.coeff, b.coeff_lo, (long long)T * 4, true);
+            h.B = bf16 ? plane16(b.pred_lo, D, true) : plane(b.pred, b.pred_lo, (long long)D * 4, true);
             h.g.M = (int)T; h.g.N = (int)D; h.g.K = (int)B;
             h.g.epilogue = g.g.epilogue;
             h.g.out = nullptr; h.g.out_blocks = b.grad_dst; h.g.block_rows = (int)cfg_.a2a_size; h.g.ldc = D;
@@ -1230,7 +1251,7 @@ void Engine::launch_one_step(unsigned step) {
                 g.epilogue = tc::EPI_ADD_TABLE_VALUE;
                 g.out = net ? b.hid_t : b.hid_h; g.ldc = D; g.block_rows = 1;
                 g.x_base = rows_c; g.x_row_stride_bytes = layout_.row_bytes; g.x_gather = nullptr;
-                g.x_is_half = cfg_.state_type == ST_F16;
+                g.x_is_half = cfg_.value_bf16 ? 2 : (cfg_.state_type == ST_F16 ? 1 : 0);
             }
             // the projection was updated by the processes that own its slices
             launch_tc("hidden", nets, n_nets, tc_splits(n_nets * ceil_div(R, 128) * ceil_div(D, 64), F), cfg_.feature_type == ST_F16, false,
@@ -1247,11 +1268,11 @@ void Engine::launch_one_step(unsigned step) {
         if (vec)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr)));
+                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
         else
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<1>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr)));
+                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
     }
     KGE_CUDA(cudaGetLastError());
 
@@ -1284,7 +1305,7 @@ void Engine::launch_one_step(unsigned step) {
                                                       fused_wait ? sync : ExchangeSync{})));
         }
         KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
-                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, (float*)nullptr)));
+                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, (float*)nullptr, 0)));
         if (tc_bwd) {
             // Both input gradients are contractions with the coefficient matrix C [B, T]:
             //   dot:  d_pred = C . tails,                          d_tails = C^T . pred

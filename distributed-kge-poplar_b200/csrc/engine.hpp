@@ -35,6 +35,10 @@ struct Config {
     float beta_m, beta_v, epsilon, weight_decay;
     std::map<std::string, float> lr_modifiers;
     int state_type, feature_type;
+    // "execution.value_dtype": "bfloat16" stores the embedding values in bf16 while adam_m and
+    // sqrt(adam_v) stay float32, and runs the dot-product scores and their gradients on bf16
+    // tensor-core products with fp32 accumulation (results agree with fp32 to about 1e-2).
+    bool value_bf16;
     unsigned device_ordinal, rank, world;
     bool cuda_graph;
     bool tensor_cores;  // dense contractions on tcgen05 (3xTF32) instead of the FP32 pipe
@@ -177,6 +181,7 @@ class Engine {
     unsigned side_streams_ = 0;
     bool split_popular_rows_ = true;  // rows with many lookups are summed in parts by several blocks
     bool planes_ = false;             // the step's contractions run on the plane-fed tensor-core kernel
+    bool bf16_planes_ = false;        // scores and their gradients multiply bfloat16 copies of their operands
     uint32_t feat_stride_ = 0;        // floats per row of the widened / lower feature planes
     cudaEvent_t ev_fork_ = nullptr, ev_join_[2] = {nullptr, nullptr};
     cudaStream_t side_begin();

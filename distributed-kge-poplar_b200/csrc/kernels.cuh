@@ -30,6 +30,9 @@ struct RowLayout {
     uint32_t off_feat;
     uint32_t d;
     uint32_t f;
+    // 1: the value segment holds bfloat16 while adam_m and sqrt(adam_v) keep the state type (bf16
+    // embeddings with fp32 optimiser state; the reference has one type per row, src/poplar_kge.cpp:405-417)
+    uint32_t value_bf16;
 };
 
 struct AdamParams {
@@ -45,6 +48,32 @@ __device__ __forceinline__ float load_as_float(const float* p) { return *p; }
 __device__ __forceinline__ float load_as_float(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ void store_from_float(float* p, float v) { *p = v; }
 __device__ __forceinline__ void store_from_float(__half* p, float v) { *p = __float2half_rn(v); }
+
+__device__ __forceinline__ float load_as_float(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void store_from_float(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+// Element c of a row's value segment, whose type the layout names.
+template <class ST>
+__device__ __forceinline__ float load_value(const RowLayout& L, const uint8_t* row, int c) {
+    return L.value_bf16 ? load_as_float(reinterpret_cast<const __nv_bfloat16*>(row) + c) : load_as_float(reinterpret_cast<const ST*>(row) + c);
+}
+template <class ST>
+__device__ __forceinline__ void store_value(const RowLayout& L, uint8_t* row, int c, float v) {
+    if (L.value_bf16) store_from_float(reinterpret_cast<__nv_bfloat16*>(row) + c, v);
+    else store_from_float(reinterpret_cast<ST*>(row) + c, v);
+}
 
 // Four consecutive elements starting at an element index that is a multiple of 4.
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -245,11 +274,11 @@ k_hidden(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restr
         const int m = m0 + ty * 4 + i;
         if (m >= R) continue;
         const size_t row = remote ? remote[m] : row_base + (uint32_t)m;
-        const ST* vp = reinterpret_cast<const ST*>(table + row * L.row_bytes);
+        const uint8_t* vp = table + row * L.row_bytes;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < D) out[(size_t)m * D + n] = load_as_float(vp + n) + acc[i][j];
+            if (n < D) out[(size_t)m * D + n] = load_value<ST>(L, vp, n) + acc[i][j];
         }
     }
 }
@@ -266,7 +295,8 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
         const uint32_t* __restrict__ a2a_idx, const uint32_t* __restrict__ head,
         const uint32_t* __restrict__ relation, const float* __restrict__ rel_table,
         float* const* __restrict__ send_dst, float* __restrict__ pred, int T, int a2a, int B, int D,
-        int score_fn, ExchangeSync sync, float* const* __restrict__ send_lo_dst = nullptr, float* __restrict__ pred_lo = nullptr) {
+        int score_fn, ExchangeSync sync, float* const* __restrict__ send_lo_dst = nullptr, float* __restrict__ pred_lo = nullptr,
+        int lo_bf16 = 0) {
     grid_dependency_sync();
     const int b = blockIdx.x;
     if (b < T) {
@@ -277,7 +307,10 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
             for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
                 const float4 v = load4(src + c);
                 store4(out + c, v);
-                if (send_lo_dst) store4(send_lo_dst[dst] + (size_t)j * D + c, tf32_lower4(v));  // lower plane for the tensor-core gradients
+                if (send_lo_dst) {  // the companion plane of the tensor-core operands: lower TF32 part, or the bf16 rounding
+                    if (lo_bf16) store4(reinterpret_cast<__nv_bfloat16*>(send_lo_dst[dst]) + (size_t)j * D + c, v);
+                    else store4(send_lo_dst[dst] + (size_t)j * D + c, tf32_lower4(v));
+                }
             }
         } else {
             for (int c = threadIdx.x; c < D; c += blockDim.x) out[c] = src[c];
@@ -299,7 +332,11 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
             const float hr = h[c], hi = h[c + half], rr = r[c], ri = r[c + half];
             p[c] = hr * rr - hi * ri;
             p[c + half] = hr * ri + hi * rr;
-            if (pred_lo) {
+            if (pred_lo && lo_bf16) {
+                __nv_bfloat16* p16 = reinterpret_cast<__nv_bfloat16*>(pred_lo) + (size_t)i * D;
+                p16[c] = __float2bfloat16_rn(p[c]);
+                p16[c + half] = __float2bfloat16_rn(p[c + half]);
+            } else if (pred_lo) {
                 pred_lo[(size_t)i * D + c] = tf32_lower(p[c]);
                 pred_lo[(size_t)i * D + c + half] = tf32_lower(p[c + half]);
             }
@@ -314,7 +351,8 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
                 o = make_float4(a.x * q.x, a.y * q.y, a.z * q.z, a.w * q.w);
             }
             store4(p + c, o);
-            if (pred_lo) store4(pred_lo + (size_t)i * D + c, tf32_lower4(o));
+            if (pred_lo && lo_bf16) store4(reinterpret_cast<__nv_bfloat16*>(pred_lo) + (size_t)i * D + c, o);
+            else if (pred_lo) store4(pred_lo + (size_t)i * D + c, tf32_lower4(o));
         }
     } else {
         for (int c = threadIdx.x; c < D; c += blockDim.x)
@@ -608,13 +646,15 @@ template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float* __restrict__ coeff,
        float* __restrict__ loss_rows, LossParams lp, float inv_normaliser, float* __restrict__ loss_total,
-       float* __restrict__ loss_last, unsigned* __restrict__ counter, float* __restrict__ coeff_lo = nullptr) {
+       float* __restrict__ loss_last, unsigned* __restrict__ counter, float* __restrict__ coeff_lo = nullptr, int lo_bf16 = 0) {
     grid_dependency_sync();
     __shared__ float scratch[THREADS / 32];
     const int i = blockIdx.x, T = lp.n_tail;
     const float* __restrict__ r = raw + (size_t)i * T;
     float* __restrict__ c = coeff + (size_t)i * T;
-    float* __restrict__ c_lo = coeff_lo ? coeff_lo + (size_t)i * T : nullptr;  // lower TF32 plane for the tensor-core gradients
+    // the companion plane for the tensor-core gradients: lower TF32 part, or the bf16 rounding (rows of T bf16)
+    float* __restrict__ c_lo = coeff_lo && !lo_bf16 ? coeff_lo + (size_t)i * T : nullptr;
+    __nv_bfloat16* __restrict__ c16 = coeff_lo && lo_bf16 ? reinterpret_cast<__nv_bfloat16*>(coeff_lo) + (size_t)i * T : nullptr;
     const int lab = (int)label[i];
     const bool transe = lp.score_fn == SCORE_TRANSE;
     auto score_of = [&](int j) { return transe ? lp.gamma - r[j] : r[j]; };
@@ -642,6 +682,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
             const float cj = to_coeff(j, g);
             c[j] = cj;
             if (c_lo) c_lo[j] = tf32_lower(cj);
+            if (c16) c16[j] = __float2bfloat16_rn(cj);
             if (j == lab) loss_rows[i] = -logp;
         }
         finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch);
@@ -677,6 +718,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
         const float cj = to_coeff(j, pos ? dx : -dx);
         c[j] = cj;
         if (c_lo) c_lo[j] = tf32_lower(cj);
+        if (c16) c16[j] = __float2bfloat16_rn(cj);
     }
     part = block_sum<THREADS>(part, scratch);
     if (threadIdx.x == 0) loss_rows[i] = -part;
@@ -1215,12 +1257,12 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         if (!writes_row) return;
         float x[V], m[V], qq[V];
         if (V == 4) {
-            const float4 a = load4(xs + c), b = load4(ms + c), d = load4(qs + c);
+            const float4 a = L.value_bf16 ? load4(reinterpret_cast<const __nv_bfloat16*>(xs) + c) : load4(xs + c), b = load4(ms + c), d = load4(qs + c);
             x[0] = a.x; x[1 % V] = a.y; x[2 % V] = a.z; x[3 % V] = a.w;
             m[0] = b.x; m[1 % V] = b.y; m[2 % V] = b.z; m[3 % V] = b.w;
             qq[0] = d.x; qq[1 % V] = d.y; qq[2 % V] = d.z; qq[3 % V] = d.w;
         } else {
-            x[0] = load_as_float(xs + c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
+            x[0] = load_value<ST>(L, reinterpret_cast<const uint8_t*>(xs), c); m[0] = load_as_float(ms + c); qq[0] = load_as_float(qs + c);
         }
 #pragma unroll
         for (int u = 0; u < V; ++u) {
@@ -1232,11 +1274,12 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             qq[u] = sqrtf(v);
         }
         if (V == 4) {
-            store4(xv + c, make_float4(x[0], x[1 % V], x[2 % V], x[3 % V]));
+            if (L.value_bf16) store4(reinterpret_cast<__nv_bfloat16*>(xv) + c, make_float4(x[0], x[1 % V], x[2 % V], x[3 % V]));
+            else store4(xv + c, make_float4(x[0], x[1 % V], x[2 % V], x[3 % V]));
             store4(mv + c, make_float4(m[0], m[1 % V], m[2 % V], m[3 % V]));
             store4(qv + c, make_float4(qq[0], qq[1 % V], qq[2 % V], qq[3 % V]));
         } else {
-            store_from_float(xv + c, x[0]);
+            store_value<ST>(L, reinterpret_cast<uint8_t*>(xv), c, x[0]);
             store_from_float(mv + c, m[0]);
             store_from_float(qv + c, qq[0]);
         }
@@ -1812,7 +1855,7 @@ k_write_entity(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restr
         const float4 z = philox_normal4(seed, shard, (uint32_t)row, (uint32_t)c4);
         const float zz[4] = {z.x, z.y, z.z, z.w};
         for (int u = 0; u < 4 && c4 * 4 + u < D; ++u) {
-            store_from_float(xv + c4 * 4 + u, stddev * zz[u]);
+            store_value<ST>(L, reinterpret_cast<uint8_t*>(xv), c4 * 4 + u, stddev * zz[u]);
             store_from_float(mv + c4 * 4 + u, 0.f);
             store_from_float(qv + c4 * 4 + u, 0.f);
         }
@@ -1841,7 +1884,7 @@ k_init_table(uint8_t* __restrict__ table, RowLayout L, size_t n_rows, uint32_t s
             const float4 z = philox_normal4(seed, shard, (uint32_t)row, (uint32_t)q);
             const float zz[4] = {z.x, z.y, z.z, z.w};
             for (int u = 0; u < 4 && q * 4 + u < D; ++u) {
-                store_from_float(reinterpret_cast<ST*>(base) + q * 4 + u, stddev * zz[u]);
+                store_value<ST>(L, base, q * 4 + u, stddev * zz[u]);
                 store_from_float(reinterpret_cast<ST*>(base + L.off_m) + q * 4 + u, 0.f);
                 store_from_float(reinterpret_cast<ST*>(base + L.off_q) + q * 4 + u, 0.f);
             }
@@ -1871,7 +1914,7 @@ k_write_rows(uint8_t* __restrict__ table, RowLayout L, const uint32_t* __restric
     uint8_t* base = table + row * L.row_bytes;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         const float v = load_as_float(src + c);
-        if (c < D) store_from_float(reinterpret_cast<ST*>(base) + c, v);
+        if (c < D) store_value<ST>(L, base, c, v);
         else if (c < 2 * D) store_from_float(reinterpret_cast<ST*>(base + L.off_m) + (c - D), v);
         else if (c < 3 * D) store_from_float(reinterpret_cast<ST*>(base + L.off_q) + (c - 2 * D), v);
         else store_from_float(reinterpret_cast<FT*>(base + L.off_feat) + (c - 3 * D), v);
@@ -1890,7 +1933,7 @@ k_read_rows(const uint8_t* __restrict__ table, RowLayout L, const uint32_t* __re
     OT* __restrict__ dst = out + (size_t)j * W;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float v;
-        if (c < D) v = load_as_float(reinterpret_cast<const ST*>(base) + c);
+        if (c < D) v = load_value<ST>(L, base, c);
         else if (c < 2 * D) v = load_as_float(reinterpret_cast<const ST*>(base + L.off_m) + (c - D));
         else if (c < 3 * D) v = load_as_float(reinterpret_cast<const ST*>(base + L.off_q) + (c - 2 * D));
         else v = load_as_float(reinterpret_cast<const FT*>(base + L.off_feat) + (c - 3 * D));

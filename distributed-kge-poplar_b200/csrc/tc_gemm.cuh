@@ -76,7 +76,7 @@ struct GemmArgs {
     long long x_row_stride_bytes;
     const uint32_t* x_gather;
     uint32_t x_row_base;
-    int x_is_half;
+    int x_is_half;              // EPI_ADD_TABLE_VALUE: 0 fp32 values, 1 fp16, 2 bfloat16
     unsigned* status;           // device error word; non-zero = a bounded wait gave up
     // k split with a deterministic reduction (pipelined kernel only).  Every split writes its raw
     // partial tile to ws [splits, M, N] (and its partial row sums to ws_rowsum [splits, M]);
@@ -581,8 +581,8 @@ __device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, flo
     if (g.epilogue == EPI_STORE) return;
     const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
     const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
-    const bool half = g.epilogue == EPI_ADD_TABLE_VALUE && g.x_is_half;
-    if (!half && n + 3 < g.N && ((reinterpret_cast<uintptr_t>(x_row) + (size_t)n * 4) & 15) == 0) {
+    const int narrow = g.epilogue == EPI_ADD_TABLE_VALUE ? g.x_is_half : 0;  // 1: fp16 values, 2: bf16 values
+    if (!narrow && n + 3 < g.N && ((reinterpret_cast<uintptr_t>(x_row) + (size_t)n * 4) & 15) == 0) {
         const float4 v = *reinterpret_cast<const float4*>(x_row + (size_t)n * 4);
         x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
         return;
@@ -590,7 +590,9 @@ __device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, flo
 #pragma unroll
     for (int j = 0; j < 4; ++j)
         if (n + j < g.N)
-            x[j] = half ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j]) : reinterpret_cast<const float*>(x_row)[n + j];
+            x[j] = narrow == 1   ? __half2float(reinterpret_cast<const __half*>(x_row)[n + j])
+                   : narrow == 2 ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(x_row)[n + j] << 16)
+                                 : reinterpret_cast<const float*>(x_row)[n + j];
 }
 
 // Epilogue and store of four neighbouring output columns whose k range is complete.

@@ -35,6 +35,7 @@
 
 #include <algorithm>
 
+#include "kernels.cuh"
 #include "tc_gemm.cuh"
 
 namespace kge {
@@ -76,6 +77,7 @@ struct RouteArgs {
     float* pred_lo;
     int B, a2a, n_shard, score_fn;
     int mode[2];
+    int lo_bf16;  // the companion planes hold the bfloat16 rounding of the rows instead of the lower TF32 part
 };
 constexpr int kRouteMaxLookups = 4096;  // lookups one block may have to route (batch_size + n_shard * a2a_size)
 
@@ -229,14 +231,15 @@ __device__ __forceinline__ void route_rows(const RouteArgs& rt, int mode, const 
                 if (rt.score_fn == 0) o = make_float4(o.x + r[b].x, o.y + r[b].y, o.z + r[b].z, o.w + r[b].w);
                 else o = make_float4(o.x * r[b].x, o.y * r[b].y, o.z * r[b].z, o.w * r[b].w);
                 dst = rt.pred + (size_t)e * D;
-                dst_lo = rt.pred_lo + (size_t)e * D;
+                dst_lo = rt.lo_bf16 ? rt.pred_lo + (size_t)e * D / 2 : rt.pred_lo + (size_t)e * D;  // rows of D bf16 = D / 2 floats
             } else {
                 const uint32_t j = e - (uint32_t)rt.B, shard = j / (uint32_t)rt.a2a, slot = j - shard * (uint32_t)rt.a2a;
                 dst = rt.send_dst[shard] + (size_t)slot * D;
-                dst_lo = rt.send_lo_dst[shard] + (size_t)slot * D;
+                dst_lo = rt.lo_bf16 ? rt.send_lo_dst[shard] + (size_t)slot * D / 2 : rt.send_lo_dst[shard] + (size_t)slot * D;
             }
             *reinterpret_cast<float4*>(dst + n0 + q * 4) = o;
-            *reinterpret_cast<float4*>(dst_lo + n0 + q * 4) = make_float4(tf32_lo(o.x), tf32_lo(o.y), tf32_lo(o.z), tf32_lo(o.w));
+            if (rt.lo_bf16) store4(reinterpret_cast<__nv_bfloat16*>(dst_lo) + n0 + q * 4, o);
+            else *reinterpret_cast<float4*>(dst_lo + n0 + q * 4) = make_float4(tf32_lo(o.x), tf32_lo(o.y), tf32_lo(o.z), tf32_lo(o.w));
         }
     }
 }

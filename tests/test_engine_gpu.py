@@ -457,3 +457,55 @@ def test_popular_rows_are_summed_in_parts(separate):
             assert_close(d_hidden, oracle.last["d_value"][s], 1e-4, f"popular rows: d hidden[{s}]")
     _compare_state(engine, cfg, oracle, "popular rows", RTOL=2e-5)
     engine.close()
+
+
+def _bf16_round(x):
+    bits = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32)
+
+
+BF16_CASES = {
+    "distmult_small": dict(score_fn="DistMult", n_shard=2, n_entity=600, n_relation_type=8, d=64, batch=32, a2a=24, loss="logsigmoid"),
+    "complex_small": dict(score_fn="ComplEx", n_shard=2, n_entity=600, n_relation_type=8, d=64, batch=32, a2a=24, loss="softmax"),
+    # BASELINE configuration 4 per shard-step: d = 512, 1024 positives and 1024 shared negatives per
+    # shard (a2a = 2048 / n_shard), on two emulated shards with small tables
+    "config4_distmult": dict(score_fn="DistMult", n_shard=2, n_entity=5000, n_relation_type=1000, d=512, batch=1024, a2a=1024, loss="logsigmoid"),
+    "config4_complex": dict(score_fn="ComplEx", n_shard=2, n_entity=5000, n_relation_type=1000, d=512, batch=1024, a2a=1024, loss="softmax"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(BF16_CASES))
+def test_bf16_values_with_float32_optimiser_state(name):
+    """bfloat16 embedding values with float32 adam_m / sqrt(adam_v) ("execution.value_dtype"), scores
+    and their gradients as bf16 tensor-core products with fp32 accumulation.  Against the float64
+    oracle started from the same bf16-rounded values: 2e-2 on the loss, the scores and the updated
+    state (the tolerance of the reduced-precision tier)."""
+    c = BF16_CASES[name]
+    cfg = StepConfig(n_shard=c["n_shard"], n_entity=c["n_entity"], n_relation_type=c["n_relation_type"], embedding_size=c["d"],
+                     entity_feature_size=0, batch_size=c["batch"], a2a_size=c["a2a"], score_fn=c["score_fn"], distance_fn="MatMul",
+                     loss_type=c["loss"], correction_weight=1.0 if c["loss"] == "softmax" else 0.0)
+    rw, d = 512, cfg.embedding_size
+    state = random_state(cfg, 33, warm=True)
+    state["entity_data"][..., :d] = _bf16_round(state["entity_data"][..., :d])
+    engine = capi.CEngine(engine_settings(cfg, rw_batch=rw, **{"execution.value_dtype": "bfloat16"}))
+    write_state(engine, cfg, state, rw)
+    back = read_rows(engine, cfg, rw, cfg.n_shard)
+    np.testing.assert_array_equal(back, state["entity_data"])  # bf16 values and fp32 moments survive the round trip
+    batch = random_batch(cfg, 1, 34, pad=5)
+    oracle = make_oracle(cfg, state)
+    want = oracle.train_step_loop(1e-3, batch)
+    got = _run_engine(engine, cfg, batch, 1e-3)
+    np.testing.assert_allclose(got, want, rtol=2e-2)
+    B, T = cfg.batch_size, cfg.n_tail
+    for s in range(cfg.n_shard):
+        raw = engine.debug_fetch("raw_score", s, B * T).reshape(B, T)
+        assert_close(raw, oracle.last["scores"][s], 2e-2, f"{name}: scores[{s}]")
+    got_state, want_state = read_state(engine, cfg, rw, cfg.n_shard), oracle.get_state()
+    for part, sl in (("value", slice(0, d)), ("adam_m", slice(d, 2 * d)), ("sqrt_adam_v", slice(2 * d, 3 * d))):
+        assert_close(got_state["entity_data"][..., sl], want_state["entity_data"][..., sl], 2e-2, f"{name}: entity {part}")
+    assert_close(got_state["relation_embedding"], want_state["relation_embedding"], 2e-2, f"{name}: relations")
+    # the values are stored in bf16: they are exactly representable
+    values = got_state["entity_data"][..., :d]
+    np.testing.assert_array_equal(values, _bf16_round(values))
+    engine.close()
