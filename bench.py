@@ -39,6 +39,26 @@ ROWS_PER_SHARD = 11_375_001  # ceil(91 000 000 / 8) + the padding row
 N_RELATION = 1387
 BATCH, NEGATIVES, D, F = 512, 256, 256, 768
 DEVICE_STEPS = 100
+ENTITY_ALPHA, RELATION_ALPHA = 1.1, 1.3  # Zipf exponents of the synthetic ids; None = uniform
+MODEL = {"score_fn": "TransE", "distance_fn": "L2", "loss": "softmax", "value_dtype": None, "feature_dtype": "float16",
+         "title": "BESS TransE-L2 training", "precision": "d=256 fp32 + 768 fp16 features"}
+
+# The training workloads of bench.py: "train" is the metric configuration (BASELINE configuration 3);
+# "config4" is BASELINE configuration 4 (DistMult, d = 512, bf16 embedding values with fp32 Adam
+# state, 1024 positives + 1024 shared negatives per shard, 30 M entities over 8 shards, 1000
+# relations, uniform ids, no entity features), whose scores are bf16 tensor-core contractions.
+WORKLOADS = {
+    "train": {},
+    "config4": dict(ROWS_PER_SHARD=3_750_001, N_RELATION=1000, BATCH=1024, NEGATIVES=1024, D=512, F=0, ENTITY_ALPHA=None,
+                    RELATION_ALPHA=None,
+                    MODEL={"score_fn": "DistMult", "distance_fn": "MatMul", "loss": "logsigmoid", "value_dtype": "bfloat16",
+                           "feature_dtype": None, "title": "BESS DistMult training",
+                           "precision": "d=512 bf16 values + fp32 Adam state, no features"}),
+}
+
+
+def select_workload(name: str) -> None:
+    globals().update(WORKLOADS[name])
 
 
 # ---------------------------------------------------------------------------
@@ -49,8 +69,8 @@ def workload_settings(n_shard: int, rows_per_shard: int, device_steps: int, rank
                       cuda_graph: bool = True) -> dict:
     n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
     a2a = (BATCH + NEGATIVES) // n_shard
-    return {
-        "model.seed": 2, "model.score_fn": "TransE", "model.distance_fn": "L2", "model.n_shard": n_shard,
+    settings = {
+        "model.seed": 2, "model.score_fn": MODEL["score_fn"], "model.distance_fn": MODEL["distance_fn"], "model.n_shard": n_shard,
         "model.n_entity": rows_per_shard, "model.n_relation_type": n_rel, "model.embedding_size": D,
         "model.entity_feature_size": F, "model.feature_mlp_size": 0, "model.feature_dropout": 0.0,
         "model.share_feature_networks": True, "model.gamma": 10.0, "model.init_scale": 1.0,
@@ -58,17 +78,22 @@ def workload_settings(n_shard: int, rows_per_shard: int, device_steps: int, rank
         "training.adam_beta_m": 0.9, "training.adam_beta_v": 0.999, "training.adam_epsilon": 1e-8,
         "training.weight_decay": 0.0, "training.learning_rate_modifiers": {},
         "data.batch_size": BATCH, "data.a2a_size": a2a,
-        "training.loss.type": "softmax", "training.loss.correction_weight": 1.0,
+        "training.loss.type": MODEL["loss"], "training.loss.correction_weight": 1.0,
         "training.loss_scale": float(BATCH * n_shard * a2a),
         "training.embedding_regularisation.power": 3.0, "training.embedding_regularisation.weight": 0.0,
         "training.feature_regularisation.power": 3.0, "training.feature_regularisation.weight": 0.0,
         "training.hidden_regularisation.power": 3.0, "training.hidden_regularisation.weight": 0.0,
-        "execution.device": "cuda", "execution.dtype": "float32", "execution.feature_dtype": "float16",
+        "execution.device": "cuda", "execution.dtype": "float32",
         "execution.train_steps_per_program_run": device_steps, "execution.rw_batch_size": 512,
         "execution.predict_hr_batch_size": 128, "execution.predict_tail_batch_size": 1024,
         "execution.predict_n_best": 100, "execution.cuda_graph": cuda_graph,
         "execution.rank": rank, "execution.world_size": world, "execution.device_ordinal": rank if world > 1 else 0,
     }
+    if MODEL["feature_dtype"]:
+        settings["execution.feature_dtype"] = MODEL["feature_dtype"]
+    if MODEL["value_dtype"]:
+        settings["execution.value_dtype"] = MODEL["value_dtype"]
+    return settings
 
 
 def _bounded_zipf(rng: np.random.RandomState, alpha: float, limit: int, size: int) -> np.ndarray:
@@ -97,9 +122,11 @@ class TriplePool:
         while np.gcd(mult, n_entity) != 1:
             mult += 1
         permute = lambda k: (k * mult + 12_345) % n_entity  # noqa: E731
-        head = permute(_bounded_zipf(rng, 1.1, n_entity, pool_size))
-        tail = permute(_bounded_zipf(rng, 1.1, n_entity, pool_size))
-        rel = _bounded_zipf(rng, 1.3, n_relation, pool_size)
+        draw = lambda alpha, limit: (_bounded_zipf(rng, alpha, limit, pool_size) if alpha else  # noqa: E731
+                                     rng.randint(limit, size=pool_size).astype(np.int64))
+        head = permute(draw(ENTITY_ALPHA, n_entity))
+        tail = permute(draw(ENTITY_ALPHA, n_entity))
+        rel = draw(RELATION_ALPHA, n_relation)
         pair = (head % n_shard) * n_shard + (tail % n_shard)
         order = np.argsort(pair, kind="stable")
         self.h = (head[order] // n_shard + 1).astype(np.uint32)
@@ -217,7 +244,7 @@ def step_traffic(n_shard: int) -> dict:
     B, T = BATCH, BATCH + NEGATIVES
     R = B + T
     n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
-    row_state, row_feat = 3 * D * 4, F * 2
+    row_state, row_feat = (D * 2 if MODEL["value_dtype"] == "bfloat16" else D * 4) + 2 * D * 4, F * 2
     return {
         # the row gather: R whole rows out of the table, written once to the compact copy
         "gather": 2 * R * (row_state + row_feat),
@@ -247,7 +274,7 @@ def step_flops() -> dict:
         "hidden": 2 * R * F * D,
         "projection_bwd": 2 * R * F * D,
         "score_bwd": 2 * (2 * B * T * D),
-        "score": 3 * B * T * D,
+        "score": (2 if MODEL["distance_fn"] == "MatMul" else 3) * B * T * D,
     }
 
 
@@ -346,8 +373,8 @@ class CpuArm:
         n_rel = int(n_shard * np.ceil(N_RELATION / n_shard))
         while True:
             cfg = StepConfig(n_shard=n_shard, n_entity=rows, n_relation_type=n_rel, embedding_size=D, entity_feature_size=F,
-                             batch_size=BATCH, a2a_size=self.a2a, score_fn="TransE", distance_fn="L2", gamma=10.0,
-                             loss_type="softmax", correction_weight=1.0)
+                             batch_size=BATCH, a2a_size=self.a2a, score_fn=MODEL["score_fn"], distance_fn=MODEL["distance_fn"],
+                             gamma=10.0, loss_type=MODEL["loss"], correction_weight=1.0 if MODEL["loss"] == "softmax" else 0.0)
             try:
                 self.oracle = CppOracle(cfg)
                 break
@@ -358,14 +385,16 @@ class CpuArm:
         self.oracle.set_threads(os.cpu_count() or 1)
         rng = np.random.RandomState(0)
         self.oracle.rel[0][...] = rng.normal(size=self.oracle.rel[0].shape) / D
-        self.oracle.proj[0][...] = rng.normal(size=self.oracle.proj[0].shape) / D / np.sqrt(F)
+        if F:
+            self.oracle.proj[0][...] = rng.normal(size=self.oracle.proj[0].shape) / D / np.sqrt(F)
         pool = TriplePool(n_shard, rows, n_rel, max(200_000, 100_000 * n_shard * n_shard))
         self.batch = pool.sample(4, BATCH, self.a2a, seed=1)
         for s in range(n_shard):
             touched = np.unique(self.batch["remote"][s])
             block = np.zeros((touched.size, self.oracle.entity_data.shape[2]), np.float32)
             block[:, :D] = rng.normal(size=(touched.size, D)) / D
-            block[:, 3 * D:] = rng.normal(size=(touched.size, F)).astype(np.float16)
+            if F:
+                block[:, 3 * D:] = rng.normal(size=(touched.size, F)).astype(np.float16)
             self.oracle.entity_data[s, touched] = block
         self.steps_done = 0
 
@@ -421,8 +450,8 @@ def run_reference_arm(args) -> None:
 
 def workload_config(n_shard: int, rows: int, device_steps: int, note: str = "") -> dict:
     cfg = {
-        "workload": f"BESS TransE-L2 training, {n_shard} shard(s) x {rows} rows (d=256 fp32 + 768 fp16 features), "
-                    f"512 positives + 256 shared negatives per shard, softmax loss, {device_steps} steps per program run",
+        "workload": f"{MODEL['title']}, {n_shard} shard(s) x {rows} rows ({MODEL['precision']}), "
+                    f"{BATCH} positives + {NEGATIVES} shared negatives per shard, {MODEL['loss']} loss, {device_steps} steps per program run",
         "n_shard": n_shard, "rows_per_shard": rows, "per_shard_batch": BATCH, "shared_negatives": NEGATIVES,
         "embedding_size": D, "feature_size": F, "steps_per_program_run": device_steps,
         "cache": "inputs larger than L2: one program run touches about 0.5 GB of distinct table rows",
@@ -475,7 +504,8 @@ def run_ours(args) -> None:
     rng = np.random.RandomState(2)
     n_rel = settings["model.n_relation_type"]
     engine.run("write", {"value": (rng.normal(size=(n_rel, D)) / D).astype(np.float32)}, name="relation_embedding")
-    engine.run("write", {"value": (rng.normal(size=(F, D)) / D / np.sqrt(F)).astype(np.float32)}, name="feature_projection")
+    if F:
+        engine.run("write", {"value": (rng.normal(size=(F, D)) / D / np.sqrt(F)).astype(np.float32)}, name="feature_projection")
 
     a2a = settings["data.a2a_size"]
     pool = TriplePool(n_shard, rows, n_rel, pool_size=max(400_000, 200_000 * n_shard * n_shard))
@@ -556,12 +586,14 @@ def run_ours(args) -> None:
         kernels[name] = entry
     dominant = next(iter(kernels))
     dom = kernels[dominant]
-    if dominant in TENSOR_KERNELS:
+    tensor_kernels = TENSOR_KERNELS + (("score",) if MODEL["distance_fn"] == "MatMul" else ())
+    if dominant in tensor_kernels:
         roofline = {"bound": "tensor", "kernel": dominant, "achieved": dom["tflop_per_s"], "peak": peaks["tensor_tflops"],
                     "unit": "TFLOP/s", "frac": dom["tflop_per_s"] / peaks["tensor_tflops"], "peak_source": peaks["source"],
-                    "peak_note": "dense bf16 sustained; the kernel computes fp32 products as three TF32 products",
+                    "peak_note": "dense bf16 sustained; " + ("bf16 products, fp32 accumulation" if MODEL["value_dtype"] == "bfloat16" and dominant in ("score", "score_bwd")
+                                                             else "the kernel computes fp32 products as three TF32 products"),
                     "algorithmic_flops_per_launch": dom["algorithmic_flops"]}
-    elif dominant in FP32_KERNELS:
+    elif dominant in FP32_KERNELS and dominant not in tensor_kernels:
         roofline = {"bound": "fp32", "kernel": dominant, "achieved": dom["tflop_per_s"], "peak": FP32_PEAK_TFLOPS,
                     "unit": "TFLOP/s", "frac": dom["tflop_per_s"] / FP32_PEAK_TFLOPS, "peak_source": "nominal",
                     "algorithmic_flops_per_launch": dom["algorithmic_flops"]}
@@ -574,7 +606,7 @@ def run_ours(args) -> None:
     line = {
         "metric": "train_triples_per_sec", "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * device_s / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": "bf16" if MODEL["value_dtype"] == "bfloat16" else "f32", "data": "synthetic",
         "config": workload_config(n_shard, rows, device_steps),
         "e2e": {"value": triples_per_call * args.steps / e2e_s, "unit": "triples/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": loss.nbytes, "ms_per_step": 1e3 * e2e_s / args.steps},
@@ -596,17 +628,99 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_micro(args) -> None:
+    """BASELINE configuration 2: single kernels on one GPU, device-timed through the C ABI's microbenchmark
+    entry points.  Row gather and row-wise Adam scatter over R unique rows of a 2 000 000-row table of
+    [value | adam_m | sqrt(adam_v)] (3 x 256 fp32 per row), ids Zipf(1.1) over a random permutation,
+    seed 1; scores of 4096 (h, r) queries against 256 shared negative tails, d = 256, as L1, L2 (FP32
+    pipe), dot product and L2 in contraction form (tensor cores).  CPU baseline: the reference's own
+    l1dist / l2dist (oracle/_ref, compiled from its codelet sources) where built, on a bounded sample."""
+    import ctypes
+
+    import torch
+
+    from distributed_kge_poplar_b200 import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    rows, d, queries, tails = 2_000_000, 256, 4096, 256
+    rng = np.random.RandomState(1)
+    perm = rng.permutation(rows)
+    peaks = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    gathers, scatters = [], []
+    for n in (4096, 16384, 65536, 262144, 1048576):
+        ranks = _bounded_zipf(rng, 1.1, rows, n)
+        idx = np.unique(perm[ranks]).astype(np.uint32)   # what the sampler's unique_pad leaves of n draws
+        state_bytes = idx.size * 3 * d * 4
+        g_us = capi.microbench_rows(0, rows, d, idx, max(args.steps, 5))
+        s_us = capi.microbench_rows(1, rows, d, idx, max(args.steps, 5))
+        scatter_bytes = 2 * state_bytes + 2 * idx.size * d * 4   # state in and out, gradient row in, hidden gradient out
+        gathers.append({"draws": n, "rows": int(idx.size), "us": g_us, "gb_per_s": 2 * state_bytes / g_us / 1e3,
+                        "frac_of_hbm": 2 * state_bytes / g_us / 1e3 / peaks["hbm_gbs"]})
+        scatters.append({"draws": n, "rows": int(idx.size), "us": s_us, "gb_per_s": scatter_bytes / s_us / 1e3,
+                         "frac_of_hbm": scatter_bytes / s_us / 1e3 / peaks["hbm_gbs"]})
+    scores = {}
+    for fn, name, flop in ((0, "l1_fp32_pipe", 3), (1, "l2_fp32_pipe", 3), (2, "dot_tensor_3xtf32", 2), (3, "l2_tensor_3xtf32", 2)):
+        us = capi.microbench_scores(fn, queries, tails, d, max(10 * args.steps, 50))
+        tf = flop * queries * tails * d / us / 1e6
+        peak = peaks["tensor_tflops"] if fn >= 2 else FP32_PEAK_TFLOPS
+        scores[name] = {"us": us, "pairs_per_s": queries * tails / us * 1e6, "tflop_per_s": tf, "peak_tflops": peak, "frac": tf / peak}
+    clocks = sampler.stop()
+    best = max(gathers, key=lambda g: g["gb_per_s"])
+    line = {
+        "metric": "microbench_gather_gb_per_s", "value": best["gb_per_s"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"single kernels: gather / Adam scatter of R rows out of {rows} x (3 x {d} fp32), ids Zipf(1.1) seed 1; "
+                               f"{queries} x {tails} scores, d = {d}"},
+        "roofline": {"bound": "hbm", "kernel": "k_gather_step_rows", "achieved": best["gb_per_s"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": best["gb_per_s"] / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_launch": 2 * best["rows"] * 3 * d * 4, "traffic": None},
+        "gather": gathers, "adam_scatter": scatters, "scores": scores, "clocks": clocks,
+    }
+    # the reference's own distance code on the host cores (one pair per call, as its vertex computes them)
+    ref_path = ROOT / "oracle" / "_ref" / "libref_distance.so"
+    if ref_path.exists() and not args.no_cpu_baseline:
+        lib = ctypes.CDLL(str(ref_path))
+        fp = ctypes.POINTER(ctypes.c_float)
+        a = rng.normal(size=(64, d)).astype(np.float32)
+        b = rng.normal(size=(tails, d)).astype(np.float32)
+        base = {}
+        for name in ("ref_l1dist", "ref_l2dist"):
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = ctypes.c_float, [fp, fp, ctypes.c_size_t]
+            pa = [row.ctypes.data_as(fp) for row in a]
+            pb = [row.ctypes.data_as(fp) for row in b]
+            t0 = time.perf_counter()
+            for x in pa:
+                for y in pb:
+                    fn(x, y, d)
+            base[name] = len(pa) * len(pb) / (time.perf_counter() - t0)
+        line["cpu_baseline"] = {"value": base["ref_l2dist"], "unit": "pairs/s", "cores": 1, "kind": "reference",
+                                "sample": f"64 x {tails} pairs, d = {d}, of the reference's l2dist (and l1dist: {base['ref_l1dist']:.3g} pairs/s) "
+                                          "compiled from its codelet sources, one call per pair through ctypes"}
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--rows-per-shard", type=int, default=ROWS_PER_SHARD, help="smaller tables for profiler captures")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["micro"], default="train",
+                    help="train: the metric configuration; config4: DistMult with bf16 values; micro: single kernels (configuration 2)")
+    ap.add_argument("--rows-per-shard", type=int, default=None, help="smaller tables for profiler captures")
     ap.add_argument("--device-steps", type=int, default=DEVICE_STEPS, help="training steps per program run")
     ap.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload == "micro":
+        return run_micro(args)
+    select_workload(args.workload)
+    if args.rows_per_shard is None:
+        args.rows_per_shard = ROWS_PER_SHARD
     if args.warmup < 3 and args.impl == "ours" and args.rows_per_shard == ROWS_PER_SHARD:
         args.warmup = 3
     if args.impl == "reference":

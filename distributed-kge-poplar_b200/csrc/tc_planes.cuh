@@ -105,7 +105,7 @@ constexpr int kPlTmemSlots = 4;
 constexpr size_t kPlRingBytes = 220 * 1024;
 constexpr size_t plane_smem_bytes() { return 1024 + kPlRingBytes; }
 static_assert(2 * ((size_t)(kBM + kMaxClusterRows) * (128 + 1) + 8 * 128) * 4 <= 150 * 1024, "the sent and the received rows of a k split");
-static_assert(150 * 1024 + 64 * 128 * 4 <= 184 * 1024 && 184 * 1024 + (2 * 4096 + kBM + 1) * 4 <= kPlRingBytes, "finished rows and staged lookups behind them");
+static_assert(150 * 1024 + 64 * 128 * 4 <= 184 * 1024 && (128 * 128 + 128 + 128) * 4 <= 72 * 1024 && 72 * 1024 + 128 * 128 * 4 <= 184 * 1024 && 184 * 1024 + (2 * 4096 + kBM + 1) * 4 <= kPlRingBytes, "finished rows and staged lookups behind them");
 
 // MN-major tile of 32-bit elements: atoms of 4 k-rows x 128 B (32 fp32 along mn) whose 32-byte
 // chunks are XOR-ed with the k-row index modulo 4; the next 32 mn are 4096 B further (leading byte
@@ -502,22 +502,26 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     const bool acc_warp = warp >= 2;
     const int row = (warp & 3) * 32 + lane, m = m0 + row;
     const int nc0 = n0 + (acc_warp ? ((warp - 2) >> 2) * CPT : 0);  // first output column of an accumulating thread
-    if (g.cluster_splits > 1) {
+    {
         // Block z of the cluster finishes rows z * rows_each ... of the tile.  Every block lays its
         // partial tile out in its own (now idle) operand ring, one slot per owner, and hands each
         // slot to the copy engine (cp.async.bulk from its shared memory into the owner's), which
         // reports the bytes to the owner's mbarrier; the owner then adds the slots in split order.
         // A block may be written to only after it has left its k loop: that is the first cluster
-        // barrier (arrive here, wait before the copies are issued).
-        cluster_arrive_relaxed();
-        const int n_split = g.cluster_splits, rank = (int)cluster_rank();
+        // barrier (arrive here, wait before the copies are issued).  Without a k split the block is
+        // the only owner: its rows take the same way through shared memory, which turns one thread's
+        // row of the accumulator into whole rows stored by neighbouring threads.
+        const bool clustered = g.cluster_splits > 1;
+        if (clustered) cluster_arrive_relaxed();
+        const int n_split = clustered ? g.cluster_splits : 1, rank = clustered ? (int)cluster_rank() : 0;
         const int rows_each = (kBM + n_split - 1) / n_split;
         const uint32_t off_rowsum = (uint32_t)rows_each * BN, off_colsum = off_rowsum + (uint32_t)((rows_each + 3) & ~3);
         const uint32_t slot_floats = off_colsum + (SIDE == SIDE_NORMS ? BN : 0);  // rows | row sums | column sums
         const uint32_t slot_bytes = slot_floats * 4u;
-        float* staging = reinterpret_cast<float*>(smem);                   // [owner][rows_each][BN] + row sums, what I send
-        float* receive = staging + (size_t)n_split * slot_floats;         // [source][rows_each][BN] + row sums, what I own
-        if (tid == 0) mbar_arrive_expect(&bar_reduce, (uint32_t)(n_split - 1) * slot_bytes);
+        float* staging = reinterpret_cast<float*>(smem);                   // [owner][rows_each][BN] + sums, what I send
+        float* receive = staging + (size_t)n_split * slot_floats;         // [source][rows_each][BN] + sums, what I own
+        if (!clustered) fin = reinterpret_cast<float*>(smem + 72 * 1024);  // one slot of 67 KB only: the finished rows follow it
+        if (clustered && tid == 0) mbar_arrive_expect(&bar_reduce, (uint32_t)(n_split - 1) * slot_bytes);
         if (acc_warp) {
             // 16-byte chunk c of tile row `row` lies at chunk c ^ (row & 7): the lanes of a warp hold
             // 32 different rows, and this spreads their stores over all banks
@@ -532,36 +536,37 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
         if (SIDE == SIDE_NORMS)  // every owner gets this split's part of the column norms
             for (int u = tid; u < n_split * BN; u += kPlThreads)
                 staging[(size_t)(u / BN) * slot_floats + off_colsum + (u % BN)] = s_colsum[0][u % BN] + s_colsum[1][u % BN];
-        fence_async_shared();  // the copy engine reads what the threads have just written
+        if (clustered) fence_async_shared();  // the copy engine reads what the threads have just written
         const int r_begin = rank * rows_each, r_end = min(kBM, r_begin + rows_each);
         constexpr int kQuads = BN / 4;
-        constexpr int kUnits = (64 * kQuads + kPlThreads - 1) / kPlThreads;  // at most 64 rows x BN / 4 quads per block
+        constexpr int kUnits = (64 * kQuads + kPlThreads - 1) / kPlThreads;  // a split owns at most 64 rows x BN / 4 quads
         const int n_units = max(0, r_end - r_begin) * kQuads;
         float xv[kUnits][4];
+        if (clustered) {
 #pragma unroll
-        for (int i = 0; i < kUnits; ++i) {  // the epilogue's second operand is fetched while the rows travel
-            const int u = tid + i * kPlThreads;
-            const int mm = m0 + r_begin + u / kQuads, nn = n0 + (u % kQuads) * 4;
-            xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
-            if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i]);
+            for (int i = 0; i < kUnits; ++i) {  // the epilogue's second operand is fetched while the rows travel
+                const int u = tid + i * kPlThreads;
+                const int mm = m0 + r_begin + u / kQuads, nn = n0 + (u % kQuads) * 4;
+                xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
+                if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i]);
+            }
         }
         if (routing) route_n = route_stage(gp.route, m0 + r_begin, max(0, min(r_end, g.M - m0) - r_begin), s_off, s_look, s_rel, kPlThreads);
         __syncthreads();
-        cluster_wait();
-        if (warp == 0 && lane < n_split && lane != rank) {
-            const uint32_t dst = cluster_map(smem_u32(receive + (size_t)rank * slot_floats), (uint32_t)lane);
-            const uint32_t bar = cluster_map(smem_u32(&bar_reduce), (uint32_t)lane);
-            asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(dst), "r"(smem_u32(staging + (size_t)lane * slot_floats)), "r"(slot_bytes), "r"(bar) : "memory");
+        if (clustered) {
+            cluster_wait();
+            if (warp == 0 && lane < n_split && lane != rank) {
+                const uint32_t dst = cluster_map(smem_u32(receive + (size_t)rank * slot_floats), (uint32_t)lane);
+                const uint32_t bar = cluster_map(smem_u32(&bar_reduce), (uint32_t)lane);
+                asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(dst), "r"(smem_u32(staging + (size_t)lane * slot_floats)), "r"(slot_bytes), "r"(bar) : "memory");
+            }
+            mbar_wait(&bar_reduce, 0u, g.status, 8u);
+            // Nobody may leave while the copy engine can still read its slots.  Every block reports here
+            // that all of its bytes have arrived and checks before it exits that all blocks have.
+            cluster_arrive_relaxed();
         }
-        mbar_wait(&bar_reduce, 0u, g.status, 8u);
-        // Nobody may leave while the copy engine can still read its slots.  Every block reports here
-        // that all of its bytes have arrived and checks before it exits that all blocks have.
-        cluster_arrive_relaxed();
-#pragma unroll
-        for (int i = 0; i < kUnits; ++i) {
-            const int u = tid + i * kPlThreads;
-            if (u >= n_units) continue;
+        auto finish_unit = [&](int u, const float* x_ready) {
             const int local = u / kQuads, q = u % kQuads, trow = r_begin + local;
             const int chunk = (q ^ (trow & 7)) << 2;
             float sum[4] = {0.f, 0.f, 0.f, 0.f}, col_total[4] = {0.f, 0.f, 0.f, 0.f};
@@ -577,39 +582,29 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                 }
             }
             const int mm = m0 + trow, nn = n0 + q * 4;
-            if (mm < g.M && nn < g.N) {
-                if (SIDE == SIDE_NORMS) finish_l2_four(pp, mm, nn, sum, row_total, col_total);
-                else finish_four(g, g.out, mm, nn, sum, xv[i], row_total);
-                if (routing) *reinterpret_cast<float4*>(fin + (size_t)local * BN + q * 4) = make_float4(sum[0], sum[1], sum[2], sum[3]);
-            }
-        }
-        cluster_wait();
-    } else {
-        if (routing) {
-            fin = reinterpret_cast<float*>(smem);
-            route_n = route_stage(gp.route, m0, min(kBM, g.M - m0), s_off, s_look, s_rel, kPlThreads);
-        }
-        if (acc_warp && m < g.M && nc0 < g.N) {
-        float* out_base = g.out_blocks ? nullptr : g.out + (size_t)blockIdx.z * g.split_stride;
-        const float rs = ROWSUM ? s_rowsum[0][row] + s_rowsum[1][row] : 0.f;
+            if (mm >= g.M || nn >= g.N) return;
+            if (SIDE == SIDE_NORMS) {
+                finish_l2_four(pp, mm, nn, sum, row_total, col_total);
+            } else {
+                float x[4];
+                if (x_ready) {
 #pragma unroll
-        for (int j = 0; j < CPT; j += 4) {
-            float four[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
-            float x[4];
-            if (nc0 + j < g.N) {
-                if (SIDE == SIDE_NORMS) {
-                    float cs[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) cs[u] = s_colsum[0][nc0 - n0 + j + u] + s_colsum[1][nc0 - n0 + j + u];
-                    finish_l2_four(pp, m, nc0 + j, four, rs, cs);
+                    for (int j = 0; j < 4; ++j) x[j] = x_ready[j];
                 } else {
-                    load_x_four(g, m, nc0 + j, x);
-                    finish_four(g, out_base, m, nc0 + j, four, x, rs);
+                    load_x_four(g, mm, nn, x);
                 }
-                if (routing) *reinterpret_cast<float4*>(fin + (size_t)row * BN + (nc0 - n0) + j) = make_float4(four[0], four[1], four[2], four[3]);
+                finish_four(g, g.out, mm, nn, sum, x, row_total);
             }
+            if (routing) *reinterpret_cast<float4*>(fin + (size_t)local * BN + q * 4) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+        };
+        if (clustered) {
+#pragma unroll
+            for (int i = 0; i < kUnits; ++i)
+                if (tid + i * kPlThreads < n_units) finish_unit(tid + i * kPlThreads, xv[i]);
+        } else {
+            for (int u = tid; u < n_units; u += kPlThreads) finish_unit(u, nullptr);
         }
-        }
+        if (clustered) cluster_wait();
     }
     if (routing) {
         __syncthreads();  // the finished rows are in `fin`
