@@ -129,7 +129,8 @@ Config parse_config(const SettingMap& s) {
     if (score_fn == "TransE") c.score_fn = SCORE_TRANSE;
     else if (score_fn == "DistMult") c.score_fn = SCORE_DISTMULT;
     else if (score_fn == "ComplEx") c.score_fn = SCORE_COMPLEX;
-    else if (score_fn == "RotatE" || score_fn == "TransH")
+    else if (score_fn == "RotatE") c.score_fn = SCORE_ROTATE;
+    else if (score_fn == "TransH")
         fail(KGE_INVALID_ARGUMENT, msg() << "'model.score_fn' '" << score_fn << "' is not supported by this engine");
     else
         fail(KGE_INVALID_ARGUMENT, msg() << "'model.score_fn' must be one of 'TransE', 'ComplEx', 'RotatE', "
@@ -174,8 +175,10 @@ Config parse_config(const SettingMap& s) {
     if (c.d == 0 || c.batch_size == 0 || c.a2a_size == 0 || c.n_step == 0 || c.n_entity == 0)
         fail(KGE_INVALID_ARGUMENT, "embedding_size, batch_size, a2a_size, n_entity and "
                                    "train_steps_per_program_run must be positive");
-    if (c.score_fn == SCORE_COMPLEX && (c.d & 1))
-        fail(KGE_INVALID_ARGUMENT, "ComplEx needs an even 'model.embedding_size'");
+    if ((c.score_fn == SCORE_COMPLEX || c.score_fn == SCORE_ROTATE) && (c.d & 1))
+        fail(KGE_INVALID_ARGUMENT, "ComplEx and RotatE need an even 'model.embedding_size'");
+    if (c.score_fn == SCORE_ROTATE && c.dist_fn == DIST_DOT)
+        fail(KGE_INVALID_ARGUMENT, "RotatE scores by a distance: 'model.distance_fn' must be 'L1' or 'L2'");
     if (c.n_tail() < 2) fail(KGE_INVALID_ARGUMENT, "n_shard * a2a_size must be at least 2");
     if ((size_t)c.batch_size + c.n_tail() > (size_t)kMaxSortItems)
         fail(KGE_INVALID_ARGUMENT, msg() << "batch_size + n_shard * a2a_size (" << c.n_remote()
@@ -293,7 +296,9 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
         for (int k = 0; k < 3; ++k)
             variables_.push_back({name + suffix[k], KGE_F32, {rows, cols}, offset, k});
     };
-    add_variable("relation_embedding", cfg_.n_relation_type, cfg_.d, 0);
+    // RotatE's relations are angles, one per complex pair (src/poplar_kge.cpp:248-251); the table keeps
+    // rows of d floats all the same and uses their first half
+    add_variable("relation_embedding", cfg_.n_relation_type, cfg_.score_fn == SCORE_ROTATE ? cfg_.d / 2 : cfg_.d, 0);
     for (size_t i = 0; i < proj_names.size(); ++i)
         add_variable(proj_names[i], cfg_.f, cfg_.d, cfg_.f ? dense_bounds_[1 + i] : n_dense_);
     variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3});
@@ -1022,7 +1027,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
         // 1. hidden = value + feature . W, and from its epilogue the lookups and the send half of the exchange
-        const bool fused_route = F > 0 && cfg_.score_fn != SCORE_COMPLEX;
+        const bool fused_route = F > 0 && cfg_.score_fn != SCORE_COMPLEX && cfg_.score_fn != SCORE_ROTATE;
         if (F > 0) {
             tc::PlaneProblem nets[2] = {};
             const int n_nets = two_nets ? 2 : 1;
@@ -1588,27 +1593,29 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
     const size_t count = value.count();
     if (count == 0) return;
     float* base = var->kind == 0 ? dense_ : var->kind == 1 ? dense_m_ : dense_v_;
+    // Rows of the dense vector are d floats wide; a variable may show fewer columns of them to the
+    // host (RotatE's angles are the first half of their rows).
+    const size_t D = cfg_.d, cols = var->shape[1], n_rows = var->shape[0], row0 = var->offset / D, W = cfg_.world;
+    float* host = static_cast<float*>(value.data);
     if (write) {
         // on the engine's stream, so that the kernel that derives the lower plane is ordered behind the copy
-        KGE_CUDA(cudaMemcpyAsync(base + var->offset, value.data, count * 4, cudaMemcpyHostToDevice, stream_));
-        if (var->kind == 0) refresh_lower_plane(var->offset, count);
+        KGE_CUDA(cudaMemcpy2DAsync(base + var->offset, D * 4, host, cols * 4, cols * 4, n_rows, cudaMemcpyHostToDevice, stream_));
+        if (var->kind == 0) refresh_lower_plane(var->offset, n_rows * D);
         KGE_CUDA(cudaStreamSynchronize(stream_));
         return;
     }
     if (var->kind == 0 || cfg_.world == 1) {
-        KGE_CUDA(cudaMemcpy(value.data, base + var->offset, count * 4, cudaMemcpyDeviceToHost));
+        KGE_CUDA(cudaMemcpy2D(host, cols * 4, base + var->offset, D * 4, cols * 4, n_rows, cudaMemcpyDeviceToHost));
         return;
     }
     // Optimiser state lives with the process that owns the row (src/poplar_kge.cpp:329-339): row r of
     // the dense vector with process r % world.  Collect each owner's rows through its mapped arena.
-    const size_t D = cfg_.d, row0 = var->offset / D, n_rows = count / D, W = cfg_.world;
     for (size_t p = 0; p < W; ++p) {
         const size_t first = row0 + (p + W - row0 % W) % W;
         if (first >= row0 + n_rows) continue;
         const size_t rows = (row0 + n_rows - first + W - 1) / W;
         const float* src = (const float*)(peer_arena_[p] + arena_offset_dense(var->kind)) + first * D;
-        KGE_CUDA(cudaMemcpy2D(static_cast<float*>(value.data) + (first - row0) * D, W * D * 4, src, W * D * 4, D * 4, rows,
-                              cudaMemcpyDeviceToHost));
+        KGE_CUDA(cudaMemcpy2D(host + (first - row0) * cols, W * cols * 4, src, W * D * 4, cols * 4, rows, cudaMemcpyDeviceToHost));
     }
 }
 
@@ -1701,7 +1708,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
 
     // 2. stream each local shard's rows past all queries
     const float* queries = (const float*)(arena_ + arena_offset_predict(0));
-    TopkParams tp{(int)Q, (int)nb, cfg_.score_fn == SCORE_TRANSE ? 1 : 0, cfg_.gamma};
+    TopkParams tp{(int)Q, (int)nb, score_is_gamma_minus_distance(cfg_.score_fn) ? 1 : 0, cfg_.gamma};
     for (unsigned l = 0; l < n; ++l) {
         ShardBuffers& b = shards_[l];
         KGE_CUDA(cudaMemsetAsync(b.topk_count, 0, Q * sizeof(int), stream_));

@@ -16,7 +16,19 @@
 
 namespace kge {
 
-enum ScoreFn : int { SCORE_TRANSE = 0, SCORE_DISTMULT = 1, SCORE_COMPLEX = 2 };
+enum ScoreFn : int { SCORE_TRANSE = 0, SCORE_DISTMULT = 1, SCORE_COMPLEX = 2, SCORE_ROTATE = 3 };
+// TransE and RotatE score by gamma - distance (src/poplar_kge.cpp:492-499, 532-537); the others by the raw product.
+__host__ __device__ inline bool score_is_gamma_minus_distance(int score_fn) { return score_fn == SCORE_TRANSE || score_fn == SCORE_ROTATE; }
+
+// RotatE's relation row holds one angle per complex pair.  The reference casts the angles to
+// float16 and takes sine and cosine in float16 (src/poplar_kge.cpp:522-525): restated as the
+// correctly rounded float16 of the exact value (double-precision sin / cos of the rounded angle).
+__device__ __forceinline__ void rotate_sin_cos(float angle, float& s, float& c) {
+    const double theta = (double)__half2float(__float2half_rn(angle));
+    s = __half2float(__double2half(sin(theta)));
+    c = __half2float(__double2half(cos(theta)));
+}
+__device__ __forceinline__ float round_to_half(float x) { return __half2float(__float2half_rn(x)); }
 enum DistFn : int { DIST_L1 = 0, DIST_L2 = 1, DIST_DOT = 2 };
 enum LossFn : int { LOSS_LOGSIGMOID = 0, LOSS_SOFTMAX = 1 };
 
@@ -326,10 +338,13 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
     const float* __restrict__ h = hid_h + (size_t)head[i] * D;
     const float* __restrict__ r = rel_table + (size_t)relation[i] * D;
     float* __restrict__ p = pred + (size_t)i * D;
-    if (score_fn == SCORE_COMPLEX) {
+    if (score_fn == SCORE_COMPLEX || score_fn == SCORE_ROTATE) {
         const int half = D / 2;
         for (int c = threadIdx.x; c < half; c += blockDim.x) {
-            const float hr = h[c], hi = h[c + half], rr = r[c], ri = r[c + half];
+            const float hr = h[c], hi = h[c + half];
+            float rr, ri;  // the relation as a complex number: stored (ComplEx) or the unit rotation by the stored angle (RotatE)
+            if (score_fn == SCORE_ROTATE) rotate_sin_cos(r[c], ri, rr);
+            else { rr = r[c]; ri = r[c + half]; }
             p[c] = hr * rr - hi * ri;
             p[c + half] = hr * ri + hi * rr;
             if (pred_lo && lo_bf16) {
@@ -656,7 +671,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
     float* __restrict__ c_lo = coeff_lo && !lo_bf16 ? coeff_lo + (size_t)i * T : nullptr;
     __nv_bfloat16* __restrict__ c16 = coeff_lo && lo_bf16 ? reinterpret_cast<__nv_bfloat16*>(coeff_lo) + (size_t)i * T : nullptr;
     const int lab = (int)label[i];
-    const bool transe = lp.score_fn == SCORE_TRANSE;
+    const bool transe = score_is_gamma_minus_distance(lp.score_fn);
     auto score_of = [&](int j) { return transe ? lp.gamma - r[j] : r[j]; };
     auto to_coeff = [&](int j, float g_score) {
         float g = transe ? -g_score : g_score;  // d score / d raw
@@ -869,6 +884,23 @@ k_pred_bwd(const float* __restrict__ d_pred, const float* __restrict__ hid_h,
         for (int c = threadIdx.x; c < D; c += blockDim.x) {
             dh[c] = dp[c] * r[c];
             dr[c] = dp[c] * h[c];
+        }
+    } else if (score_fn == SCORE_ROTATE) {
+        // Backward of src/poplar_kge.cpp:516-530.  The gradients of sine and cosine pass back through
+        // the float16 casts and the float16 sin / cos (src/pag/pag.cpp:552-595, 619-633): rounded to
+        // float16 at each of those points, the angle's gradient is their float16 sum.
+        const int half = D / 2;
+        for (int c = threadIdx.x; c < half; c += blockDim.x) {
+            const float hr = h[c], hi = h[c + half];
+            float s, co;
+            rotate_sin_cos(r[c], s, co);
+            const float gr = dp[c], gi = dp[c + half];
+            dh[c] = gr * co + gi * s;
+            dh[c + half] = -gr * s + gi * co;
+            const float d_sin = round_to_half(-gr * hi + gi * hr), d_cos = round_to_half(gr * hr + gi * hi);
+            const float via_sin = round_to_half(d_sin * co), via_cos = round_to_half(-d_cos * s);
+            dr[c] = round_to_half(via_sin + via_cos);
+            dr[c + half] = 0.f;  // the table keeps rows of D floats; the upper half of an angle row is unused
         }
     } else {
         const int half = D / 2;

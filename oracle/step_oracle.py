@@ -30,7 +30,7 @@ class StepConfig:
     entity_feature_size: int
     batch_size: int  # positives per shard
     a2a_size: int  # tails sent to each peer
-    score_fn: str = "TransE"  # TransE | DistMult | ComplEx
+    score_fn: str = "TransE"  # TransE | DistMult | ComplEx | RotatE
     distance_fn: str = "L1"  # L1 | L2 | MatMul
     gamma: float = 10.0
     loss_type: str = "logsigmoid"  # logsigmoid | softmax
@@ -209,7 +209,20 @@ def predict_tail(cfg: StepConfig, h: np.ndarray, r: np.ndarray) -> np.ndarray:
         half = h.shape[-1] // 2
         hr, hi, rr, ri = h[..., :half], h[..., half:], r[..., :half], r[..., half:]
         return np.concatenate([hr * rr - hi * ri, hr * ri + hi * rr], axis=-1)
+    if cfg.score_fn == "RotatE":  # :516-530: the angles go through float16, and so do their sine and cosine
+        half = h.shape[-1] // 2
+        re, im = h[..., :half], h[..., half:]
+        sin, cos = _rotate_sin_cos(r, h.dtype)
+        return np.concatenate([re * cos - im * sin, im * cos + re * sin], axis=-1)
     raise ValueError(f"score_fn {cfg.score_fn!r} is not covered by the oracle")
+
+
+def _rotate_sin_cos(r: np.ndarray, dtype) -> Tuple[np.ndarray, np.ndarray]:
+    """sin and cos of the relation angles as src/poplar_kge.cpp:522-525 computes them: the angles are
+    cast to float16, sine and cosine are taken in float16 (restated as the correctly rounded
+    float16 of the exact value), and the results are cast back."""
+    theta = r.astype(np.float16).astype(np.float64)
+    return np.sin(theta).astype(np.float16).astype(dtype), np.cos(theta).astype(np.float16).astype(dtype)
 
 
 def predict_tail_grad(cfg: StepConfig, h, r, dp) -> Tuple[np.ndarray, np.ndarray]:
@@ -224,6 +237,23 @@ def predict_tail_grad(cfg: StepConfig, h, r, dp) -> Tuple[np.ndarray, np.ndarray
         dh = np.concatenate([dpr * rr + dpi * ri, -dpr * ri + dpi * rr], axis=-1)
         dr = np.concatenate([dpr * hr + dpi * hi, -dpr * hi + dpi * hr], axis=-1)
         return dh, dr
+    if cfg.score_fn == "RotatE":
+        # The gradients of sine and cosine pass through the float16 casts (src/pag/pag.cpp:619-633:
+        # the gradient of a cast is cast to the input's type), and the backward of sin / cos runs in
+        # float16 (:552-595: grad * cos(x), -grad * sin(x) on the float16 tensor); the two are added
+        # in float16 and cast back to float32 for the relation table.
+        half = h.shape[-1] // 2
+        re, im = h[..., :half], h[..., half:]
+        sin, cos = _rotate_sin_cos(r, h.dtype)
+        dpr, dpi = dp[..., :half], dp[..., half:]
+        dh = np.concatenate([dpr * cos + dpi * sin, -dpr * sin + dpi * cos], axis=-1)
+        d_sin = (-dpr * im + dpi * re).astype(np.float16)
+        d_cos = (dpr * re + dpi * im).astype(np.float16)
+        f16 = lambda x: x.astype(np.float16)  # noqa: E731
+        via_sin = f16(d_sin.astype(np.float64) * f16(cos).astype(np.float64))
+        via_cos = f16(-d_cos.astype(np.float64) * f16(sin).astype(np.float64))
+        d_theta = f16(via_sin.astype(np.float64) + via_cos.astype(np.float64)).astype(h.dtype)
+        return dh, d_theta
     raise ValueError(cfg.score_fn)
 
 
@@ -252,13 +282,13 @@ def score(cfg: StepConfig, p: np.ndarray, tails: np.ndarray):
     as is (:512-514, :571-573), normally with distance_fn "MatMul".
     """
     dist = _distance(cfg, p, tails)
-    if cfg.score_fn == "TransE":
+    if cfg.score_fn in ("TransE", "RotatE"):  # :492-499, :532-537
         return p.dtype.type(_f32(cfg.gamma)) - dist, dist
     return dist, dist
 
 
 def score_grad(cfg: StepConfig, p, tails, dist, g):
-    if cfg.score_fn == "TransE":
+    if cfg.score_fn in ("TransE", "RotatE"):
         g = -g
     return _distance_grad(cfg, p, tails, dist, g)
 
@@ -341,7 +371,8 @@ class Oracle:
         d, f = cfg.embedding_size, cfg.entity_feature_size
         self.entity_data = np.zeros((cfg.n_shard, cfg.n_entity, cfg.row_size), dtype)
         self.variables: Dict[str, np.ndarray] = {}
-        shapes = {"relation_embedding": (cfg.n_relation_type, d)}
+        # RotatE's relations are angles, one per complex pair (src/poplar_kge.cpp:248-251)
+        shapes = {"relation_embedding": (cfg.n_relation_type, d // 2 if cfg.score_fn == "RotatE" else d)}
         for name in cfg.projection_names:
             shapes[name] = (f, d)
         for name, shape in shapes.items():

@@ -60,7 +60,10 @@ def random_state(cfg: StepConfig, seed: int, fp16_features: bool = False, warm: 
         rows[..., 3 * d :] = feat.astype(np.float32)
         rows[:, 0, 3 * d :] = 0
     state = {"entity_data": rows, "step": np.zeros(cfg.n_shard, np.uint32)}
-    state["relation_embedding"] = (rng.normal(size=(cfg.n_relation_type, d)) / np.sqrt(d)).astype(np.float32)
+    if cfg.score_fn == "RotatE":  # one angle per complex pair
+        state["relation_embedding"] = rng.uniform(-np.pi, np.pi, size=(cfg.n_relation_type, d // 2)).astype(np.float32)
+    else:
+        state["relation_embedding"] = (rng.normal(size=(cfg.n_relation_type, d)) / np.sqrt(d)).astype(np.float32)
     for name in cfg.projection_names:
         state[name] = (rng.normal(size=(f, d)) / np.sqrt(max(f, 1)) / np.sqrt(d)).astype(np.float32)
     for name in ("relation_embedding",) + cfg.projection_names:

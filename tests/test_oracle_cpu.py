@@ -279,3 +279,25 @@ def test_compiled_restatement_agrees_with_the_pinned_oracle(variant):
         rms = float(np.sqrt(np.mean(np.asarray(want[name], np.float64) ** 2)))
         worst = float(np.max(np.abs(np.asarray(got[name], np.float64) - want[name])))
         assert worst <= 5e-6 * rms, f"{name}: {worst / rms:.2e} of the tensor's rms"
+
+
+def test_rotate_follows_the_float16_points_of_the_reference():
+    """RotatE in the oracle (src/poplar_kge.cpp:516-530): angles, sine and cosine go through
+    float16, so the predicted tail is a rotation by the float16-rounded sine / cosine exactly, and
+    the angle's gradient (computed in float16 in the reference) agrees with the analytic float64
+    gradient to float16 accuracy."""
+    cfg = so.StepConfig(n_shard=1, n_entity=10, n_relation_type=3, embedding_size=8, entity_feature_size=0, batch_size=4,
+                        a2a_size=4, score_fn="RotatE", distance_fn="L2")
+    rng = np.random.RandomState(0)
+    h, theta, dp = rng.normal(size=(5, 8)), rng.uniform(-3, 3, size=(5, 4)), rng.normal(size=(5, 8))
+    p = so.predict_tail(cfg, h, theta)
+    t16 = theta.astype(np.float16).astype(np.float64)
+    s, c = np.sin(t16).astype(np.float16).astype(np.float64), np.cos(t16).astype(np.float16).astype(np.float64)
+    np.testing.assert_array_equal(p, np.concatenate([h[:, :4] * c - h[:, 4:] * s, h[:, 4:] * c + h[:, :4] * s], axis=1))
+    # a rotation keeps the modulus of every complex pair, up to the float16 rounding of sine and cosine
+    np.testing.assert_allclose(p[:, :4] ** 2 + p[:, 4:] ** 2, h[:, :4] ** 2 + h[:, 4:] ** 2, rtol=2e-3)
+    dh, dtheta = so.predict_tail_grad(cfg, h, theta, dp)
+    np.testing.assert_allclose(dh, np.concatenate([dp[:, :4] * c + dp[:, 4:] * s, -dp[:, :4] * s + dp[:, 4:] * c], axis=1), rtol=1e-12)
+    analytic = dp[:, :4] * (-h[:, :4] * np.sin(theta) - h[:, 4:] * np.cos(theta)) + dp[:, 4:] * (-h[:, 4:] * np.sin(theta) + h[:, :4] * np.cos(theta))
+    np.testing.assert_allclose(dtheta, analytic, rtol=0, atol=4e-3 * np.abs(analytic).max())
+    assert dtheta.shape == theta.shape
