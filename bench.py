@@ -555,6 +555,20 @@ def run_ours(args) -> None:
     clocks = sampler.stop() if rank == 0 else None
     final_loss = float(loss[0])
 
+    # -- e2e with the batch sampler on the device: no index stream crosses the host ----------
+    engine.run("load_triples", dict(triples=np.ascontiguousarray(np.stack([pool.h, pool.r, pool.t])),
+                                    bucket_offset=pool.offset.astype(np.uint32), bucket_count=pool.count.astype(np.uint32),
+                                    shard_to_count=np.full(n_shard, rows - 1, np.uint32)))
+    seed = np.array([7], np.uint32)
+    for i in range(args.warmup):
+        engine.run("train_step_loop_sampled", dict(sample_seed=seed, learning_rate=lr, loss=loss))
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        engine.run("train_step_loop_sampled", dict(sample_seed=seed, learning_rate=lr, loss=loss))
+    barrier()
+    sampled_s = max_over_ranks(time.perf_counter() - t0)
+
     # -- per-kernel times (plain launches bracketed by events), for the roofline ----
     engine.set_kernel_timing(True)
     engine.stage_batch(batches[0])
@@ -610,6 +624,9 @@ def run_ours(args) -> None:
         "config": workload_config(n_shard, rows, device_steps),
         "e2e": {"value": triples_per_call * args.steps / e2e_s, "unit": "triples/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": loss.nbytes, "ms_per_step": 1e3 * e2e_s / args.steps},
+        "e2e_device_sampler": {"value": triples_per_call * args.steps / sampled_s, "unit": "triples/s", "h2d_bytes_per_step": int(lr.nbytes + 4),
+                               "d2h_bytes_per_step": loss.nbytes, "ms_per_step": 1e3 * sampled_s / args.steps,
+                               "note": "\"train_step_loop_sampled\": positives, negatives, unique rows and routing indices are drawn on the GPU"},
         "gpu_launches": int(launches),
         "roofline": {**roofline, "traffic": NCU_TRAFFIC.get(dominant), "us_per_launch": dom["us_per_launch"],
                      "step_us": step_us, "step_hbm_gb_per_s": traffic["step"] / (step_us * 1e-6) / 1e9,

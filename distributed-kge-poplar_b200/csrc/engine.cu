@@ -613,6 +613,9 @@ void Engine::run(const std::string& command, std::vector<HostArray>& arrays, con
     if (command == "write_entity") return cmd_write_entity(arrays, false);
     if (command == "write_entity_rows") return cmd_write_entity(arrays, true);
     if (command == "initialise_entities") return cmd_initialise_entities();
+    if (command == "load_triples") return cmd_load_triples(arrays);
+    if (command == "sample_batch") return cmd_sample_batch(arrays, false);
+    if (command == "train_step_loop_sampled") return cmd_sample_batch(arrays, true);
     if (command == "read" || command == "write") return cmd_read_write_variable(arrays, variable, command == "write");
     fail(KGE_INVALID_ARGUMENT, msg() << "Unknown command '" << command << "'");
 }
@@ -660,6 +663,12 @@ void Engine::stage_batch(std::vector<HostArray>& arrays) {
     upload(head, d_head_);
     upload(relation, d_relation_);
     upload(tail, d_tail_);
+    prepare_staged();
+}
+
+// The sort-and-segment tables of the staged index streams (the backward of the row gather).
+void Engine::prepare_staged() {
+    const size_t n = n_local_, S = cfg_.n_step, B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote();
     KGE_CUDA(cudaEventRecord(ev_stage_[0], stream_));
     k_prepare_segments<<<(unsigned)(n * S), 512, 0, stream_>>>(
         d_head_, d_a2a_, d_relation_, d_remote_, (int)B, (int)T, (int)R, (int)cfg_.n_relation_type, d_ent_perm_,
@@ -669,6 +678,89 @@ void Engine::stage_batch(std::vector<HostArray>& arrays) {
     staged_ = true;
     stage_fresh_ = true;
 }
+
+// ---------------------------------------------------------------------------
+// The batch sampler on the device (src/python/poplar_kge_dataset.py:199-263, 310-393)
+
+// "load_triples": the training triples as local rows, sorted by (head shard, tail shard) bucket:
+// `triples` u32 [3, n] (head row, relation, tail row), `bucket_offset` / `bucket_count` u32
+// [n_shard, n_shard], `shard_to_count` u32 [n_shard] (real rows per shard).  All shards of the job,
+// on every process: a shard's batch names positives that other shards' heads drew.
+void Engine::cmd_load_triples(std::vector<HostArray>& arrays) {
+    const size_t n = cfg_.n_shard;
+    HostArray* triples = nullptr;
+    for (HostArray& a : arrays)
+        if (a.name == "triples") triples = &a;
+    if (!triples) fail(KGE_INVALID_ARGUMENT, "Key not found 'triples'");
+    if (triples->dtype != KGE_U32 || triples->shape.size() != 2 || triples->shape[0] != 3 || triples->shape[1] == 0)
+        fail(KGE_INVALID_ARGUMENT, "'triples' expected an unsigned int array of shape (3, n_triples)");
+    const size_t n_triples = triples->shape[1];
+    HostArray& offset = find_array(arrays, "bucket_offset", KGE_U32, {n, n});
+    HostArray& count = find_array(arrays, "bucket_count", KGE_U32, {n, n});
+    HostArray& rows = find_array(arrays, "shard_to_count", KGE_U32, {n});
+    const uint32_t *h_off = static_cast<const uint32_t*>(offset.data), *h_cnt = static_cast<const uint32_t*>(count.data);
+    const uint32_t *h_rows = static_cast<const uint32_t*>(rows.data), *h_tri = static_cast<const uint32_t*>(triples->data);
+    if (cfg_.batch_size % cfg_.n_shard || cfg_.a2a_size <= cfg_.batch_size / cfg_.n_shard)
+        fail(KGE_INVALID_ARGUMENT, msg() << "Expected batch_size (" << cfg_.batch_size << ") to be a multiple of n_shard and a2a_size ("
+                                         << cfg_.a2a_size << ") to be >= batch_size/n_shard");
+    for (size_t b = 0; b < n * n; ++b) {
+        if (h_cnt[b] == 0) fail(KGE_INVALID_ARGUMENT, msg() << "'bucket_count' has an empty (head shard, tail shard) bucket " << b);
+        if ((size_t)h_off[b] + h_cnt[b] > n_triples) fail(KGE_INVALID_ARGUMENT, "'bucket_offset' + 'bucket_count' passes the end of 'triples'");
+    }
+    for (size_t s = 0; s < n; ++s)
+        if (h_rows[s] == 0 || h_rows[s] >= cfg_.n_entity)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'shard_to_count' (" << h_rows[s] << ") must be between 1 and model.n_entity - 1");
+    for (size_t i = 0; i < n_triples; ++i) {
+        if (h_tri[i] >= cfg_.n_entity || h_tri[2 * n_triples + i] >= cfg_.n_entity || h_tri[i] == 0 || h_tri[2 * n_triples + i] == 0)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'triples' names a row outside [1, model.n_entity) at triple " << i);
+        if (h_tri[n_triples + i] >= cfg_.n_relation_type)
+            fail(KGE_INVALID_ARGUMENT, msg() << "'triples' names relation " << h_tri[n_triples + i] << " at triple " << i);
+    }
+    uint32_t* d_triples = (uint32_t*)device_alloc(3 * n_triples * 4);
+    uint32_t* d_meta = (uint32_t*)device_alloc((2 * n * n + n) * 4);
+    KGE_CUDA(cudaMemcpy(d_triples, h_tri, 3 * n_triples * 4, cudaMemcpyHostToDevice));
+    KGE_CUDA(cudaMemcpy(d_meta, h_off, n * n * 4, cudaMemcpyHostToDevice));
+    KGE_CUDA(cudaMemcpy(d_meta + n * n, h_cnt, n * n * 4, cudaMemcpyHostToDevice));
+    KGE_CUDA(cudaMemcpy(d_meta + 2 * n * n, h_rows, n * 4, cudaMemcpyHostToDevice));
+    sampler_ = SamplerData{d_triples, n_triples, d_meta, d_meta + n * n, d_meta + 2 * n * n};
+}
+
+void Engine::sample_and_stage(uint32_t seed) {
+    if (!sampler_.triples) fail(KGE_LOGIC_ERROR, "no training triples: run \"load_triples\" first");
+    k_sample_batch<<<(unsigned)(n_local_ * cfg_.n_step), 512, 0, stream_>>>(sampler_, seed, sample_run_++, (int)cfg_.n_shard, (int)shard0_,
+                                                                             (int)cfg_.n_step, (int)cfg_.batch_size, (int)cfg_.a2a_size,
+                                                                             d_remote_, d_a2a_, d_head_, d_relation_, d_tail_);
+    KGE_CUDA(cudaGetLastError());
+    prepare_staged();
+}
+
+// "sample_batch": draws one program run's index streams on the device (`sample_seed` u32 [1]) and
+// stages them; any of remote / a2a / head / relation / tail given (local shapes of
+// "train_step_loop") receives a copy.  "train_step_loop_sampled": the same, then the steps:
+// `learning_rate`, `loss` as for "train_step_loop"; no index array crosses the host.
+void Engine::cmd_sample_batch(std::vector<HostArray>& arrays, bool train) {
+    const size_t n = n_local_, S = cfg_.n_step, B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote();
+    HostArray& seed = find_array(arrays, "sample_seed", KGE_U32, {1});
+    HostArray *lr = nullptr, *loss = nullptr;
+    if (train) {
+        lr = &find_array(arrays, "learning_rate", KGE_F32, {n});
+        loss = &find_array(arrays, "loss", KGE_F32, {n});
+    }
+    KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));
+    sample_and_stage(static_cast<const uint32_t*>(seed.data)[0]);
+    struct Stream { const char* name; uint32_t* device; std::vector<size_t> shape; };
+    const Stream streams[5] = {{"remote", d_remote_, {n, S, R}}, {"a2a", d_a2a_, {n, S, cfg_.n_shard, cfg_.a2a_size}},
+                               {"head", d_head_, {n, S, B}}, {"relation", d_relation_, {n, S, B}}, {"tail", d_tail_, {n, S, B}}};
+    for (const Stream& st : streams)
+        for (HostArray& a : arrays)
+            if (a.name == st.name) {
+                HostArray& out = find_array(arrays, st.name, KGE_U32, st.shape);
+                KGE_CUDA(cudaMemcpyAsync(out.data, st.device, out.count() * 4, cudaMemcpyDeviceToHost, stream_));
+            }
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+    if (train) train_staged(static_cast<const float*>(lr->data)[0], static_cast<float*>(loss->data));
+}
+
 
 void Engine::train_staged(float learning_rate, float* loss) {
     KGE_CUDA(cudaSetDevice((int)cfg_.device_ordinal));

@@ -143,6 +143,10 @@ class Engine {
     void cmd_read_write_variable(std::vector<HostArray>& arrays, const std::string& name, bool write);
     void cmd_predict(std::vector<HostArray>& arrays);
     void cmd_initialise_entities();
+    void cmd_load_triples(std::vector<HostArray>& arrays);
+    void cmd_sample_batch(std::vector<HostArray>& arrays, bool train);
+    void sample_and_stage(uint32_t seed);
+    void prepare_staged();
 
     // the step
     void launch_steps();
@@ -235,6 +239,9 @@ class Engine {
     uint8_t* pinned_ = nullptr;
     size_t pinned_bytes_ = 0;
     bool staged_ = false;
+    // the training triples for the on-device sampler ("load_triples"), bucketed by (head shard, tail shard)
+    SamplerData sampler_{};
+    uint32_t sample_run_ = 0;  // program runs sampled so far: part of the generator's key
     // predict: buffers made on first use
     void ensure_predict_buffers();
     float *p_head_hidden_ = nullptr, *p_chunk_hidden_ = nullptr, *p_raw_ = nullptr;

@@ -1825,6 +1825,112 @@ k_topk_finish(const unsigned long long* __restrict__ state, const int* __restric
 }
 
 // ---------------------------------------------------------------------------
+// The BESS batch sampler on the device (src/python/poplar_kge_dataset.py:310-393, `sample_batch`,
+// with its uniform strategy; `unique_pad` :161-164).  The training triples lie in device memory
+// sorted by (head shard, tail shard) bucket, as local rows: triples[0] head rows, [1] relations,
+// [2] tail rows (:199-241).  One block draws everything shard s needs for step i:
+//   positions [0, B)       its own positives, B / n per tail shard: head rows (and the relations);
+//   positions [B, 2B)      the positives of every head shard whose tail lives on s: tail rows;
+//   positions [2B, 2B + n * neg)  the negatives every head shard asks s for: uniform rows of s;
+// then sorts them, keeps each row once (`remote`, zero-padded) and gives every position the slot
+// of its row (`head`, `a2a`).  Draws are counter-based (Philox keyed by seed and run, counted by
+// head shard, step, tail shard and slot), so the block of shard s and the block of the head
+// shard that owns a positive compute the same triple without talking to each other, on any GPU.
+struct SamplerData {
+    const uint32_t* triples;        // [3][n_triples]
+    size_t n_triples;
+    const uint32_t* bucket_offset;  // [n_shard][n_shard]
+    const uint32_t* bucket_count;   // [n_shard][n_shard], none empty
+    const uint32_t* shard_count;    // [n_shard] real rows per shard (rows 1 .. count)
+};
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1);
+
+__device__ __forceinline__ unsigned long long sampler_draw(uint32_t seed, uint32_t run, uint32_t head_shard, uint32_t step,
+                                                           uint32_t tail_shard, uint32_t slot) {
+    uint32_t c[4] = {head_shard, step, tail_shard, slot};
+    uint32_t k0 = seed, k1 = run ^ 0x243F6A88u;
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        philox_round(c, k0, k1);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return ((unsigned long long)c[0] << 32) | c[1];
+}
+
+constexpr uint32_t kNegativeSlot = 0x80000000u;  // slot numbers of negatives, apart from those of positives
+
+static __global__ void __launch_bounds__(512)
+k_sample_batch(SamplerData sd, uint32_t seed, uint32_t run, int n_shard, int shard0, int n_step, int B, int a2a,
+               uint32_t* __restrict__ remote, uint32_t* __restrict__ a2a_out, uint32_t* __restrict__ head,
+               uint32_t* __restrict__ relation, uint32_t* __restrict__ tail) {
+    __shared__ unsigned long long keys[kMaxSortItems];
+    __shared__ uint32_t s_scan[512];
+    const int l = blockIdx.x / n_step, step = blockIdx.x % n_step, s = shard0 + l;
+    const int pos = B / n_shard, neg = a2a - pos, T = n_shard * a2a, R = B + T;
+    const size_t sidx = (size_t)l * n_step + step;
+    remote += sidx * R;
+    a2a_out += sidx * T;
+    head += sidx * B;
+    relation += sidx * B;
+    tail += sidx * B;
+    int padded = 1;
+    while (padded < R) padded <<= 1;
+    for (int p = threadIdx.x; p < padded; p += blockDim.x) {
+        unsigned long long key = ~0ull;
+        if (p < B) {
+            const int ts = p / pos, k = p - ts * pos;
+            const uint32_t bucket = (uint32_t)(s * n_shard + ts);
+            const size_t idx = sd.bucket_offset[bucket] + sampler_draw(seed, run, (uint32_t)s, (uint32_t)step, (uint32_t)ts, (uint32_t)k) % sd.bucket_count[bucket];
+            key = ((unsigned long long)sd.triples[idx] << 32) | (unsigned)p;
+            relation[p] = sd.triples[sd.n_triples + idx];
+            tail[p] = (uint32_t)(ts * a2a + k);  // where the exchange puts this positive's tail (:257-263)
+        } else if (p < 2 * B) {
+            const int q = p - B, hs = q / pos, k = q - hs * pos;
+            const uint32_t bucket = (uint32_t)(hs * n_shard + s);
+            const size_t idx = sd.bucket_offset[bucket] + sampler_draw(seed, run, (uint32_t)hs, (uint32_t)step, (uint32_t)s, (uint32_t)k) % sd.bucket_count[bucket];
+            key = ((unsigned long long)sd.triples[2 * sd.n_triples + idx] << 32) | (unsigned)p;
+        } else if (p < R) {
+            const int q = p - 2 * B, hs = q / neg, k = q - hs * neg;
+            const uint32_t row = 1u + (uint32_t)(sampler_draw(seed, run, (uint32_t)hs, (uint32_t)step, (uint32_t)s, kNegativeSlot | (uint32_t)k) % sd.shard_count[s]);
+            key = ((unsigned long long)row << 32) | (unsigned)p;
+        }
+        keys[p] = key;
+    }
+    bitonic_sort(keys, padded);
+    // rank of every sorted entry among the distinct rows: an exclusive scan of "starts a new row"
+    const int per_thread = (padded + (int)blockDim.x - 1) / (int)blockDim.x, first = threadIdx.x * per_thread;
+    uint32_t mine = 0;
+    for (int i = first; i < first + per_thread && i < R; ++i) mine += (i == 0 || (keys[i] >> 32) != (keys[i - 1] >> 32)) ? 1u : 0u;
+    s_scan[threadIdx.x] = mine;
+    __syncthreads();
+    for (int o = 1; o < (int)blockDim.x; o <<= 1) {  // Hillis-Steele inclusive scan over the threads' counts
+        const uint32_t v = (int)threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0u;
+        __syncthreads();
+        s_scan[threadIdx.x] += v;
+        __syncthreads();
+    }
+    uint32_t rank = s_scan[threadIdx.x] - mine;  // distinct rows before this thread's first entry
+    const uint32_t n_unique = s_scan[blockDim.x - 1];
+    for (int i = first; i < first + per_thread && i < R; ++i) {
+        const bool starts = i == 0 || (keys[i] >> 32) != (keys[i - 1] >> 32);
+        if (starts) remote[rank++] = (uint32_t)(keys[i] >> 32);
+        const uint32_t p = (uint32_t)keys[i], slot = rank - 1;
+        if (p < (uint32_t)B) {
+            head[p] = slot;
+        } else if (p < (uint32_t)(2 * B)) {
+            const uint32_t q = p - (uint32_t)B, hs = q / (uint32_t)pos;
+            a2a_out[hs * a2a + (q - hs * pos)] = slot;
+        } else {
+            const uint32_t q = p - (uint32_t)(2 * B), hs = q / (uint32_t)neg;
+            a2a_out[hs * a2a + pos + (q - hs * neg)] = slot;
+        }
+    }
+    for (int i = (int)n_unique + (int)threadIdx.x; i < R; i += blockDim.x) remote[i] = 0u;  // unique_pad's zeros
+}
+
+// ---------------------------------------------------------------------------
 // Table I/O (src/poplar_kge.cpp:857-871).
 
 // Counter-based normal numbers (Philox-4x32-10 + Box-Muller), keyed by (seed, shard) and

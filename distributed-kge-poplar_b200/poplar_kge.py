@@ -576,6 +576,55 @@ class Engine:
             learning_rate=np.full(self.n_local, self.current_learning_rate, dtype=np.float32), loss=loss, **streams))
         return float(np.sum(loss)), self.current_learning_rate
 
+    # -- sampling on the device ----------------------------------------------
+
+    @staticmethod
+    def bucket_triples(train_hrt: np.ndarray, entity_to_shard: np.ndarray, entity_to_idx: np.ndarray,
+                       n_shard: int) -> Dict[str, np.ndarray]:
+        """The training triples as the device sampler wants them: local rows sorted by
+        (head shard, tail shard) bucket with each bucket's offset and size, the index that the
+        reference's ``Dataset`` builds for ``sample_batch`` (src/python/poplar_kge_dataset.py:199-241)."""
+        hrt = np.asarray(train_hrt)
+        head_shard, tail_shard = entity_to_shard[hrt[:, 0]], entity_to_shard[hrt[:, 2]]
+        pair = n_shard * head_shard.astype(np.int64) + tail_shard
+        order = np.argsort(pair, kind="stable")
+        count = np.bincount(pair, minlength=n_shard * n_shard)
+        offset = np.concatenate([[0], np.cumsum(count)[:-1]])
+        ordered = hrt[order]
+        triples = np.stack([entity_to_idx[ordered[:, 0]], ordered[:, 1], entity_to_idx[ordered[:, 2]]]).astype(np.uint32)
+        return dict(triples=np.ascontiguousarray(triples), bucket_offset=offset.reshape(n_shard, n_shard).astype(np.uint32),
+                    bucket_count=count.reshape(n_shard, n_shard).astype(np.uint32))
+
+    def load_triples(self, train_hrt: np.ndarray, entity_to_shard: np.ndarray, entity_to_idx: np.ndarray) -> None:
+        """Put the training set on the device for ``sample_batch`` / ``train_step_loop_sampled``."""
+        n = self.settings.model.n_shard
+        self.engine.run("load_triples", dict(
+            shard_to_count=np.ascontiguousarray(self.shard_to_entity_count, dtype=np.uint32),
+            **self.bucket_triples(train_hrt, np.asarray(entity_to_shard), np.asarray(entity_to_idx), n)))
+
+    def sample_batch(self, seed: int) -> Batch:
+        """One program run's index streams of the local shards, drawn on the device (and left staged
+        there): the device counterpart of ``Dataset.sample_batch`` (src/python/poplar_kge_dataset.py:310-393)."""
+        d, e, n = self.settings.data, self.settings.execution, self.settings.model.n_shard
+        S, B, R = e.train_steps_per_program_run, d.batch_size, d.batch_size + n * d.a2a_size
+        out = dict(remote=np.zeros((self.n_local, S, R), np.uint32), a2a=np.zeros((self.n_local, S, n, d.a2a_size), np.uint32),
+                   head=np.zeros((self.n_local, S, B), np.uint32), relation=np.zeros((self.n_local, S, B), np.uint32),
+                   tail=np.zeros((self.n_local, S, B), np.uint32))
+        self.engine.run("sample_batch", dict(sample_seed=np.array([seed], np.uint32), **out))
+        return Batch(**out)
+
+    def train_step_loop_sampled(self, seed: int) -> Tuple[float, float]:
+        """``train_step_loop`` on a batch that the device draws itself: no index array crosses the host."""
+        if self.uninitialized_variables:
+            raise ValueError(f"Calling train_step() with uninitialised variables {sorted(self.uninitialized_variables)}")
+        self._update_learning_rate()
+        self.step += self.settings.execution.train_steps_per_program_run
+        loss = np.full(self.n_local, np.nan, dtype=np.float32)
+        self.engine.run("train_step_loop_sampled", dict(
+            sample_seed=np.array([seed], np.uint32), loss=loss,
+            learning_rate=np.full(self.n_local, self.current_learning_rate, dtype=np.float32)))
+        return float(np.sum(loss)), self.current_learning_rate
+
     # -- prediction ----------------------------------------------------------
 
     def _predict_hr_chunk(self, idx_relation: np.ndarray) -> Predictions:

@@ -202,3 +202,31 @@ def expected_initial_table(seed: int, shard: int, n_rows: int, d: int, f: int, s
         feat[0] = 0
         out[:, 3 * d:] = feat
     return out
+
+
+def check_batch_decodes_to_training_triples(batch: Dict[str, np.ndarray], n_shard: int, batch_size: int, train_hrt, entity_to_shard,
+                                            entity_to_idx) -> None:
+    """The invariants of the reference's sampler tests (tests/python/test_poplar_kge_dataset.py:48-138)
+    on index streams [n_shard, steps, ...]: following remote -> a2a -> exchange -> tail recovers an
+    (h, r, t) of the training set for every positive, and `remote` is sorted, unique, zero-padded."""
+    from oracle.step_oracle import all_to_all
+
+    train = {tuple(t) for t in np.asarray(train_hrt).tolist()}
+    lookup = {(int(s), int(i)): e for e, (s, i) in enumerate(zip(entity_to_shard, entity_to_idx))}
+    remote, a2a, head, rel, tail = (np.asarray(batch[k]).astype(np.int64) for k in BATCH_KEYS)
+    n = n_shard
+    assert remote.shape[0] == n
+    for step in range(remote.shape[1]):
+        sent = np.stack([remote[s, step][a2a[s, step]] for s in range(n)])  # [src, dst, a2a]
+        received = all_to_all(sent)  # [dst, src, a2a]
+        for s in range(n):
+            tails_local = received[s].reshape(-1)
+            tail_shard = np.repeat(np.arange(n), a2a.shape[-1])
+            for i in range(batch_size):
+                h = lookup[(s, int(remote[s, step][head[s, step, i]]))]
+                col = tail[s, step, i]
+                t = lookup[(int(tail_shard[col]), int(tails_local[col]))]
+                assert (h, int(rel[s, step, i]), t) in train
+            row = remote[s, step]
+            used = row[row > 0]
+            assert np.all(np.diff(used) > 0) and np.all(row[len(used):] == 0)

@@ -9,7 +9,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from helpers import BATCH_KEYS, random_batch, random_state
+from helpers import BATCH_KEYS, check_batch_decodes_to_training_triples, random_batch, random_state
 from oracle import step_oracle as so
 from oracle.step_oracle import Oracle, StepConfig
 
@@ -69,28 +69,10 @@ def test_sampler_fixture_decodes_to_training_triples():
     (tests/python/test_poplar_kge_dataset.py:48-80)."""
     for case in ("demo", "mid"):
         f = np.load(GOLDEN / f"sampler_{case}.npz")
-        n, B = int(f["n_shard"]), int(f["batch_size"])
-        train = {tuple(t) for t in f["train_hrt"].tolist()}
-        lookup = {}
-        for e, (s, i) in enumerate(zip(f["entity_to_shard"], f["entity_to_idx"])):
-            lookup[(int(s), int(i))] = e
         for b in range(2):
-            remote, a2a, head, rel, tail = (f[f"batch{b}/{k}"].astype(np.int64) for k in BATCH_KEYS)
-            steps = remote.shape[1]
-            for step in range(steps):
-                sent = np.stack([remote[s, step][a2a[s, step]] for s in range(n)])  # [src, dst, a2a]
-                received = so.all_to_all(sent)  # [dst, src, a2a]
-                for s in range(n):
-                    tails_local = received[s].reshape(-1)
-                    tail_shard = np.repeat(np.arange(n), a2a.shape[-1])
-                    for i in range(B):
-                        h = lookup[(s, int(remote[s, step][head[s, step, i]]))]
-                        col = tail[s, step, i]
-                        t = lookup[(int(tail_shard[col]), int(tails_local[col]))]
-                        assert (h, int(rel[s, step, i]), t) in train
-                    row = remote[s, step]
-                    used = row[row > 0]
-                    assert np.all(np.diff(used) > 0) and np.all(row[len(used) :] == 0)
+            batch = {k: f[f"batch{b}/{k}"] for k in BATCH_KEYS}
+            check_batch_decodes_to_training_triples(batch, int(f["n_shard"]), int(f["batch_size"]), f["train_hrt"],
+                                                    f["entity_to_shard"], f["entity_to_idx"])
 
 
 def test_operator_known_answers():
