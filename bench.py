@@ -720,14 +720,111 @@ def run_micro(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_predict(args) -> None:
+    """BASELINE configuration 5: sharded ranking.  1250 (h, r) queries per GPU (10 000 over 8) are
+    scored by TransE-L2, d = 256 fp32, against every row of every shard (11 375 001 rows per GPU, fp16
+    features through the learned projection), each shard keeps its 100 best per query and the lists go
+    back to the asking shard's process; the host merges them to a global top 10.  One bench step =
+    one such ranking of 1250 queries per GPU."""
+    import torch
+    import torch.distributed as dist
+
+    from distributed_kge_poplar_b200 import capi
+
+    rank, world, local_rank = (int(os.environ.get(k, "0")) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    world = max(world, 1)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run for N > 1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    rows = args.rows_per_shard or ROWS_PER_SHARD
+    hr, n_best, queries_per_gpu = 1250, 100, 1250   # one pass over the table serves all of a GPU's queries
+    settings = workload_settings(world, rows, 1, rank, world)
+    settings.update({"execution.predict_hr_batch_size": hr, "execution.predict_n_best": n_best, "execution.device_ordinal": local_rank})
+    engine = capi.CEngine(settings)
+    if world > 1:
+        engine.comm_connect(exchange_handles(engine.comm_export(), world), world)
+    engine.run("initialise_entities", {})
+    rng = np.random.RandomState(4)
+    n_rel = settings["model.n_relation_type"]
+    engine.run("write", {"value": (rng.normal(size=(n_rel, D)) / D).astype(np.float32)}, name="relation_embedding")
+    engine.run("write", {"value": (rng.normal(size=(F, D)) / D / np.sqrt(F)).astype(np.float32)}, name="feature_projection")
+    mult = 2_654_435_761 % (rows - 1)
+    heads = (1 + (_bounded_zipf(rng, 1.1, rows - 1, queries_per_gpu) * mult + 12_345) % (rows - 1)).astype(np.uint32)
+    rels = _bounded_zipf(rng, 1.3, N_RELATION, queries_per_gpu).astype(np.uint32)
+    count = np.full(1, rows - 1, np.uint32)
+    scores = np.zeros((1, world, hr, n_best), np.float32)
+    indices = np.zeros((1, world, hr, n_best), np.uint32)
+
+    def rank_all():
+        best = np.zeros((queries_per_gpu, 10), np.float32)
+        for lo in range(0, queries_per_gpu, hr):
+            engine.run("predict", dict(predict_head=np.ascontiguousarray(heads[None, lo:lo + hr]), predict_relation=np.ascontiguousarray(rels[None, lo:lo + hr]),
+                                       predict_entity_count=count, predict_scores=scores, predict_indices=indices))
+            merged = scores[0].transpose(1, 0, 2).reshape(hr, -1)   # [query, shard * n_best]: the global top 10 on the host
+            best[lo:lo + hr] = -np.sort(-merged, axis=1)[:, :10]
+        return best
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(1, args.warmup // 3)):
+        rank_all()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t0 = time.perf_counter()
+    launches = 0
+    for _ in range(args.steps):
+        best = rank_all()
+        launches += engine.last_run_stats()[1] * (queries_per_gpu // hr)
+    barrier()
+    seconds = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        seconds = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    engine.close()
+    if rank == 0:
+        per_step = seconds / args.steps
+        pairs = queries_per_gpu * world * (rows - 1) * world   # every query against every row of every shard
+        flop = pairs * (2 * D) + (rows - 1) * world * 2 * F * D * (queries_per_gpu // hr)  # scores + hidden rows of every pass
+        peaks = measured_peaks()
+        print(json.dumps({
+            "metric": "ranked_queries_per_sec", "value": queries_per_gpu * world / per_step, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"sharded ranking: {queries_per_gpu} queries per GPU against {world} x {rows - 1} rows, TransE-L2 d={D}, "
+                                   f"{F} fp16 features, per-shard top {n_best} in passes of {hr} queries, global top 10 on the host"},
+            "e2e": {"value": queries_per_gpu * world / per_step, "unit": "queries/s", "h2d_bytes_per_step": int(2 * 4 * queries_per_gpu),
+                    "d2h_bytes_per_step": int(2 * scores.nbytes * (queries_per_gpu // hr))},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "k_tc_planes (hidden rows and L2 scores of a pass)", "achieved": flop / per_step / world / 1e12,
+                         "peak": peaks["tensor_tflops"], "unit": "TFLOP/s", "frac": flop / per_step / world / 1e12 / peaks["tensor_tflops"],
+                         "peak_source": peaks["source"], "traffic": None,
+                         "algorithmic_flops_per_step": flop, "peak_note": "dense bf16 sustained; fp32 products run as three TF32 products"},
+            "clocks": clocks, "best_score_of_first_query": float(best[0, 0]),
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["micro"], default="train",
-                    help="train: the metric configuration; config4: DistMult with bf16 values; micro: single kernels (configuration 2)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["micro", "predict"], default="train",
+                    help="train: the metric configuration; config4: DistMult with bf16 values; micro: single kernels (configuration 2); "
+                         "predict: sharded ranking (configuration 5)")
     ap.add_argument("--rows-per-shard", type=int, default=None, help="smaller tables for profiler captures")
     ap.add_argument("--device-steps", type=int, default=DEVICE_STEPS, help="training steps per program run")
     ap.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a CUDA graph")
@@ -735,6 +832,8 @@ def main() -> None:
     args = ap.parse_args()
     if args.workload == "micro":
         return run_micro(args)
+    if args.workload == "predict":
+        return run_predict(args)
     select_workload(args.workload)
     if args.rows_per_shard is None:
         args.rows_per_shard = ROWS_PER_SHARD

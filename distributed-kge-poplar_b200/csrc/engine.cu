@@ -1723,8 +1723,16 @@ void Engine::ensure_predict_buffers() {
     if (p_raw_) return;
     const size_t Q = (size_t)cfg_.n_shard * cfg_.predict_hr, D = cfg_.d;
     p_head_hidden_ = (float*)device_alloc((size_t)cfg_.predict_hr * D * 4);
-    p_chunk_hidden_ = (float*)device_alloc((size_t)kPredictChunk * D * 4);
-    p_raw_ = (float*)device_alloc(Q * kPredictChunk * 4);
+    // L1 has no contraction form; everything else ranks with the plane-fed tensor-core kernel
+    predict_planes_ = planes_ && cfg_.dist_fn != DIST_L1;
+    predict_chunk_ = predict_planes_ ? 16384u : 4096u;
+    p_chunk_hidden_ = (float*)device_alloc((size_t)predict_chunk_ * D * 4);
+    p_raw_ = (float*)device_alloc(Q * predict_chunk_ * 4);
+    if (predict_planes_) {
+        p_chunk_lo_ = (float*)device_alloc((size_t)predict_chunk_ * D * 4);
+        p_query_lo_ = (float*)device_alloc(Q * D * 4);
+        if (cfg_.f) p_feat_ = (float*)device_alloc((size_t)predict_chunk_ * feat_stride_ * 4);
+    }
     d_iota_ = (uint32_t*)device_alloc((size_t)cfg_.predict_hr * 4);
     std::vector<uint32_t> iota(cfg_.predict_hr);
     for (unsigned i = 0; i < cfg_.predict_hr; ++i) iota[i] = i;
@@ -1800,13 +1808,22 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
 
     // 2. stream each local shard's rows past all queries
     const float* queries = (const float*)(arena_ + arena_offset_predict(0));
+    if (predict_planes_) {
+        KGE_LAUNCH("predict_planes", k_lower_plane<<<(unsigned)std::min<size_t>((Q * D + 255) / 256, 148 * 8), 256, 0, stream_>>>(queries, Q * D, p_query_lo_));
+    }
     TopkParams tp{(int)Q, (int)nb, score_is_gamma_minus_distance(cfg_.score_fn) ? 1 : 0, cfg_.gamma};
     for (unsigned l = 0; l < n; ++l) {
         ShardBuffers& b = shards_[l];
         KGE_CUDA(cudaMemsetAsync(b.topk_count, 0, Q * sizeof(int), stream_));
         const uint32_t last = h_count[l];
-        for (uint32_t start = 1; start <= last; start += kPredictChunk) {
-            const unsigned c = std::min<uint32_t>(kPredictChunk, last - start + 1);
+        for (uint32_t start = 1; start <= last; start += predict_chunk_) {
+            const unsigned c = std::min<uint32_t>(predict_chunk_, last - start + 1);
+            if (predict_planes_) {
+                predict_pass_planes(b, start, c, queries, (unsigned)Q, W_tail == W_head ? 0 : 1);
+                KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div((unsigned)Q, 4), 128, 0, stream_>>>(
+                                               p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp));
+                continue;
+            }
             dim3 hgrid(ceil_div(c, 64), dtiles, 1);
             KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<hgrid, 256, 0, stream_>>>(
                                                                     b.table, layout_, nullptr, start, (int)c, W_tail, nullptr,
@@ -1828,6 +1845,52 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
     timing_collect();
     last_launches_ = launch_counter_;
     check_device_status();
+}
+
+// One pass of predict on the tensor cores: hidden rows of the table rows [start, start + c) as the
+// contraction feature . W + value, then their scores against all Q queries: the dot product, or
+// the L2 distance as |q|^2 + |t|^2 - 2 q.t with the direct form where that cancels, so identical
+// rows still score identically and an exact match still scores gamma
+// (src/poplar_kge.cpp:812-855; src/poplar_extensions/distance.cpp:151-185).
+void Engine::predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, const float* queries, unsigned Q, int net) {
+    const unsigned D = cfg_.d, F = cfg_.f;
+    const uint8_t* rows = b.table + (size_t)start * layout_.row_bytes;
+    if (F > 0) {
+        FeaturePlanes fp{};
+        const bool half_features = cfg_.feature_type == ST_F16;
+        (half_features ? fp.wide : fp.lo) = p_feat_;
+        fp.stride = feat_stride_;
+        fp.off_feat = layout_.off_feat;
+        const size_t units = (size_t)c * ((layout_.row_bytes - layout_.off_feat) >> 4);
+        KGE_LAUNCH("predict_planes", k_table_feature_planes<<<(unsigned)std::min<size_t>((units + 255) / 256, 148 * 16), 256, 0, stream_>>>(
+                                         b.table, layout_, start, (int)c, fp));
+        tc::PlaneProblem p{};
+        p.A = half_features ? tc::PlaneOperand{p_feat_, nullptr, (long long)feat_stride_ * 4, 0, 0}
+                            : tc::PlaneOperand{reinterpret_cast<const float*>(rows + layout_.off_feat), p_feat_, (long long)layout_.row_bytes, 0, 0};
+        const size_t w = dense_bounds_[1 + net];
+        p.B = tc::PlaneOperand{dense_ + w, dense_lo_ + w, (long long)D * 4, 1, 0};
+        p.g.M = (int)c; p.g.N = (int)D; p.g.K = (int)F;
+        p.g.epilogue = tc::EPI_ADD_TABLE_VALUE;
+        p.g.out = p_chunk_hidden_; p.g.ldc = D; p.g.block_rows = 1;
+        p.g.x_base = rows; p.g.x_row_stride_bytes = layout_.row_bytes;
+        p.g.x_is_half = cfg_.value_bf16 ? 2 : (cfg_.state_type == ST_F16 ? 1 : 0);
+        launch_planes("predict_hidden", &p, 1, tc::SIDE_NONE, -1, -1);
+    } else {
+        dim3 hgrid(ceil_div(c, 64), ceil_div(D, 64), 1);
+        KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<hgrid, 256, 0, stream_>>>(
+                                                                b.table, layout_, nullptr, start, (int)c, nullptr, nullptr, p_chunk_hidden_, nullptr)));
+    }
+    KGE_LAUNCH("predict_planes", k_lower_plane<<<(unsigned)std::min<size_t>(((size_t)c * D + 255) / 256, 148 * 16), 256, 0, stream_>>>(
+                                     p_chunk_hidden_, (size_t)c * D, p_chunk_lo_));
+    tc::PlaneProblem s{};
+    s.A = tc::PlaneOperand{queries, p_query_lo_, (long long)D * 4, 0, 0};
+    s.B = tc::PlaneOperand{p_chunk_hidden_, p_chunk_lo_, (long long)D * 4, 0, 0};
+    s.g.M = (int)Q; s.g.N = (int)c; s.g.K = (int)D;
+    const bool l2 = cfg_.dist_fn == DIST_L2;
+    s.g.epilogue = l2 ? tc::EPI_L2_DISTANCE : tc::EPI_STORE;
+    s.g.out = p_raw_; s.g.ldc = c; s.g.block_rows = 1;
+    launch_planes("predict_score", &s, 1, l2 ? tc::SIDE_NORMS : tc::SIDE_NONE, -1, -1);
+    KGE_CUDA(cudaGetLastError());
 }
 
 size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, size_t capacity) {

@@ -244,9 +244,13 @@ class Engine {
     uint32_t sample_run_ = 0;  // program runs sampled so far: part of the generator's key
     // predict: buffers made on first use
     void ensure_predict_buffers();
+    void predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, const float* queries, unsigned Q, int net);
     float *p_head_hidden_ = nullptr, *p_chunk_hidden_ = nullptr, *p_raw_ = nullptr;
     uint32_t* d_iota_ = nullptr;
-    static constexpr unsigned kPredictChunk = 4096;  // table rows scored per pass
+    // table rows scored per pass: 4096 on the FP32 pipe, 16384 when hidden rows and scores are tensor-core contractions
+    unsigned predict_chunk_ = 4096;
+    bool predict_planes_ = false;
+    float *p_feat_ = nullptr, *p_chunk_lo_ = nullptr, *p_query_lo_ = nullptr;  // planes of a pass: widened / lower features, lower hidden rows, lower queries
 
     uint32_t* d_rw_idx_ = nullptr;
     uint8_t* d_rw_data_ = nullptr;

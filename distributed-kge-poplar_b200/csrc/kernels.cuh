@@ -1775,11 +1775,22 @@ k_topk_update(const float* __restrict__ raw, int n_cols, uint32_t first_row, uin
     __syncwarp();
     unsigned long long cutoff = count >= tp.n_best ? buf[tp.n_best - 1] : 0ull;
     const float* __restrict__ row = raw + (size_t)q * n_cols;
-    for (int base = 0; base < n_cols; base += 32) {
+    constexpr int kAhead = 8;  // scores fetched before the first of them is looked at: the loads overlap
+    for (int base0 = 0; base0 < n_cols; base0 += 32 * kAhead) {
+    float ahead[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+        const int j = base0 + 32 * u + lane;
+        ahead[u] = j < n_cols ? row[j] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+        const int base = base0 + 32 * u;
+        if (base >= n_cols) break;
         const int j = base + lane;
         unsigned long long key = 0ull;
         if (j < n_cols && first_row + (uint32_t)j <= last_valid_row) {
-            const float v = row[j];
+            const float v = ahead[u];
             key = topk_key(tp.score_is_gamma_minus ? tp.gamma - v : v, first_row + (uint32_t)j);
         }
         const bool pass = key > cutoff;
@@ -1797,6 +1808,7 @@ k_topk_update(const float* __restrict__ raw, int n_cols, uint32_t first_row, uin
         if (still) buf[count + __popc(mask2 & ((1u << lane) - 1))] = key;
         count += __popc(mask2);
         __syncwarp();
+    }
     }
     warp_sort_desc(buf);
     count = min(count, tp.n_best);
@@ -2098,6 +2110,31 @@ k_gather_rows(const float* __restrict__ table, size_t width, const uint32_t* __r
 // y[e] = x[e] rounded to bfloat16 (operands of the bf16 contractions that the host provides).
 static __global__ void __launch_bounds__(256) k_to_bf16(const float* __restrict__ x, size_t n, __nv_bfloat16* __restrict__ y) {
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) y[e] = __float2bfloat16_rn(x[e]);
+}
+
+// The feature planes of `count` consecutive table rows from `first_row` on (a pass of predict over
+// the table), as k_gather_step_rows makes them for the gathered rows of a training step: fp16
+// features widened to fp32 into planes.wide, or the lower TF32 plane of fp32 features into planes.lo.
+static __global__ void __launch_bounds__(256)
+k_table_feature_planes(const uint8_t* __restrict__ table, RowLayout L, uint32_t first_row, int count, FeaturePlanes planes) {
+    const int per_row = (int)((L.row_bytes - L.off_feat) >> 4);  // 16-byte chunks of a row's feature segment
+    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < (size_t)count * per_row; u += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(u / per_row), c = (int)(u - (size_t)r * per_row);
+        const uint4 v = *reinterpret_cast<const uint4*>(table + ((size_t)first_row + r) * L.row_bytes + L.off_feat + (size_t)c * 16);
+        if (planes.wide) {
+            const int f = c * 8;
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+            const float2 cc = __half22float2(*reinterpret_cast<const __half2*>(&v.z)), d = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+            float* o = planes.wide + (size_t)r * planes.stride + f;
+            if (f < (int)planes.stride) *reinterpret_cast<float4*>(o) = make_float4(a.x, a.y, b.x, b.y);
+            if (f + 4 < (int)planes.stride) *reinterpret_cast<float4*>(o + 4) = make_float4(cc.x, cc.y, d.x, d.y);
+        } else if (planes.lo) {
+            const int f = c * 4;
+            if (f < (int)planes.stride)
+                *reinterpret_cast<float4*>(planes.lo + (size_t)r * planes.stride + f) =
+                    tf32_lower4(make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)));
+        }
+    }
 }
 
 // lo[e] = the lower TF32 plane of x[e] (for parameters that the host writes).
