@@ -282,8 +282,8 @@ def step_flops() -> dict:
 # the direct L2 distance on the FP32 pipe.
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture of the same kernels on a
 # small table (the step's kernels touch the same rows whatever the table size).
-NCU_TRAFFIC: dict = {"hidden": 4_133_632, "projection_bwd": 3_347_200, "score_bwd": 2_953_728, "score": 1_329_408,
-                     "entity_update": 3_810_560, "loss": 1_611_776}
+NCU_TRAFFIC: dict = {"hidden": 7_063_808, "projection_bwd": 6_648_320, "score_bwd": 5_864_960, "score": 1_329_408,
+                     "loss": 1_611_776}
 
 TENSOR_KERNELS = ("hidden", "projection_bwd", "score_bwd")
 FP32_KERNELS = ("score",)

@@ -1187,8 +1187,8 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_, sync)));
         }
         // 3. loss and the coefficients of the score gradients
-        KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
-                                                     d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0)));
+        KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,
+                                                d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0, (int)B, stream_)));
         // 4. score gradients; the tails' rows go straight to the shards that own them
         if (l1) {
             PairBwdArgs pa{};
@@ -1401,8 +1401,8 @@ void Engine::launch_one_step(unsigned step) {
             KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_,
                                                       fused_wait ? sync : ExchangeSync{})));
         }
-        KGE_LAUNCH("loss", KGE_CUDA(launch_dependent(k_loss<256>, dim3(B), dim3(256), 0, stream_, b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser,
-                                                               d_loss_total_ + l, d_loss_last_ + l, d_loss_counter_ + l, (float*)nullptr, 0)));
+        KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,
+                                                d_loss_counter_ + l, nullptr, 0, (int)B, stream_)));
         if (tc_bwd) {
             // Both input gradients are contractions with the coefficient matrix C [B, T]:
             //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
