@@ -613,6 +613,15 @@ void Engine::run(const std::string& command, std::vector<HostArray>& arrays, con
     if (command == "write_entity") return cmd_write_entity(arrays, false);
     if (command == "write_entity_rows") return cmd_write_entity(arrays, true);
     if (command == "initialise_entities") return cmd_initialise_entities();
+    if (command == "entity_layout") {
+        // `layout` u32 [4]: bytes of a stored row, rows per shard, local shards, the first local shard
+        HostArray& out = find_array(arrays, "layout", KGE_U32, {4});
+        uint32_t* o = static_cast<uint32_t*>(out.data);
+        o[0] = layout_.row_bytes, o[1] = (uint32_t)cfg_.n_entity, o[2] = (uint32_t)n_local_, o[3] = (uint32_t)(cfg_.rank * n_local_);
+        return;
+    }
+    if (command == "dump_entity_rows") return cmd_copy_entity_range(arrays, true);
+    if (command == "restore_entity_rows") return cmd_copy_entity_range(arrays, false);
     if (command == "load_triples") return cmd_load_triples(arrays);
     if (command == "sample_batch") return cmd_sample_batch(arrays, false);
     if (command == "train_step_loop_sampled") return cmd_sample_batch(arrays, true);
@@ -1608,6 +1617,31 @@ void Engine::cmd_read_entity(std::vector<HostArray>& arrays) {
     }
     KGE_CUDA(cudaGetLastError());
     KGE_CUDA(cudaMemcpyAsync(out.data, d_rw_data_, n * rw * W * elem, cudaMemcpyDeviceToHost, stream_));
+    KGE_CUDA(cudaStreamSynchronize(stream_));
+}
+
+// "dump_entity_rows" / "restore_entity_rows": a contiguous range of one local shard's table as it
+// is stored (no type conversion, optimiser state included), for checkpoints of tables too large
+// to pass through host arrays of the state type at once.  `shard_range` u32 [3] = (local shard,
+// first row, row count); `rows` u32 [row count, row bytes / 4].  The reference reads and writes
+// the table only through indexed chunks of rw_batch_size rows (src/poplar_kge.cpp:857-871;
+// read_entity_all, src/python/poplar_kge.py:583-598); a stored range is one plain copy.
+void Engine::cmd_copy_entity_range(std::vector<HostArray>& arrays, bool to_host) {
+    HostArray& range = find_array(arrays, "shard_range", KGE_U32, {3});
+    const uint32_t* r = static_cast<const uint32_t*>(range.data);
+    const size_t shard = r[0], first = r[1], count = r[2];
+    if (shard >= n_local_) fail(KGE_INVALID_ARGUMENT, msg() << "'shard_range' names local shard " << shard << " of " << n_local_);
+    if (first + count > cfg_.n_entity)
+        fail(KGE_INVALID_ARGUMENT, msg() << "'shard_range' covers rows [" << first << ", " << first + count
+                                         << "), not within model.n_entity (" << cfg_.n_entity << ")");
+    HostArray& rows = find_array(arrays, "rows", KGE_U32, {count, (size_t)layout_.row_bytes / 4});
+    if (!count) return;
+    unsigned char* table = shards_[shard].table + first * (size_t)layout_.row_bytes;
+    const size_t bytes = count * (size_t)layout_.row_bytes;
+    if (to_host)
+        KGE_CUDA(cudaMemcpyAsync(rows.data, table, bytes, cudaMemcpyDeviceToHost, stream_));
+    else
+        KGE_CUDA(cudaMemcpyAsync(table, rows.data, bytes, cudaMemcpyHostToDevice, stream_));
     KGE_CUDA(cudaStreamSynchronize(stream_));
 }
 

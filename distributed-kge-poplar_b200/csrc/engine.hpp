@@ -139,6 +139,7 @@ class Engine {
     // commands
     void cmd_train_step_loop(std::vector<HostArray>& arrays);
     void cmd_read_entity(std::vector<HostArray>& arrays);
+    void cmd_copy_entity_range(std::vector<HostArray>& arrays, bool to_host);
     void cmd_write_entity(std::vector<HostArray>& arrays, bool whole_rows);
     void cmd_read_write_variable(std::vector<HostArray>& arrays, const std::string& name, bool write);
     void cmd_predict(std::vector<HostArray>& arrays);

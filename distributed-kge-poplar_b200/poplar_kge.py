@@ -15,12 +15,15 @@ Differences a caller can see:
     world_size > 1, an ``exchange`` callable that all-gathers a bytes object
     across the processes (one process per GPU).
   * ``Engine.write_entity_rows`` writes whole rows, optimiser state included.
+  * ``Engine.dump`` / ``Engine.restore`` write and load a checkpoint with one file per shard.
+  * ``Engine.load_triples`` / ``sample_batch`` / ``train_step_loop_sampled`` draw batches on the device.
 """
 
 from __future__ import annotations
 
 import dataclasses
 import importlib.util
+import json
 import sys
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -545,6 +548,80 @@ class Engine:
         state = {name: self.read_variable(name) for name in self.variable_to_shape}
         state["entity_data"] = self.read_entity_all()
         return state
+
+    # -- sharded checkpoints --------------------------------------------------
+
+    DUMP_CHUNK_BYTES = 256 << 20
+
+    def _entity_layout(self) -> Tuple[int, int, int, int]:
+        layout = np.zeros(4, np.uint32)
+        self.engine.run("entity_layout", dict(layout=layout))
+        return tuple(int(x) for x in layout)
+
+    def _dump_manifest(self) -> Dict[str, Any]:
+        row_bytes, n_entity, _, _ = self._entity_layout()
+        m, e = self.settings.model, self.settings.execution
+        return dict(format=1, row_bytes=row_bytes, n_entity=n_entity, n_shard=m.n_shard, embedding_size=m.embedding_size,
+                    entity_feature_size=m.entity_feature_size, score_fn=m.score_fn, dtype=str(e.dtype),
+                    variables={k: list(v) for k, v in self.variable_to_shape.items()})
+
+    def dump(self, folder: Union[str, Path]) -> None:
+        """Write a checkpoint: one file per local shard holding the table exactly as it is stored
+        (``entity_shard<global index>.npy``, uint32 words ``[n_entity, row_bytes / 4]``, streamed in
+        chunks so that host memory holds one chunk at a time), and, from rank 0, the dense variables
+        with their optimiser state and the host-side schedule (``variables.npz``, ``manifest.json``).
+        With one process per GPU every process calls this with the same folder and writes only its
+        own shards, so a table of any size is dumped in parallel and never gathered in one place.
+        The reference offers read_entity_all / read_all, which build the whole table in host memory
+        (src/python/poplar_kge.py:583-598, 707-716)."""
+        folder = Path(folder)
+        folder.mkdir(parents=True, exist_ok=True)
+        row_bytes, n_entity, n_local, first_shard = self._entity_layout()
+        words = row_bytes // 4
+        chunk_rows = max(1, self.DUMP_CHUNK_BYTES // row_bytes)
+        for local in range(n_local):
+            out = np.lib.format.open_memmap(folder / f"entity_shard{first_shard + local:03d}.npy", mode="w+",
+                                            dtype=np.uint32, shape=(n_entity, words))
+            buffer = np.empty((chunk_rows, words), np.uint32)
+            for first in range(0, n_entity, chunk_rows):
+                count = min(chunk_rows, n_entity - first)
+                self.engine.run("dump_entity_rows", dict(shard_range=np.array([local, first, count], np.uint32), rows=buffer[:count]))
+                out[first : first + count] = buffer[:count]
+            out.flush()
+            del out
+        state = {name: self.read_variable(name) for name in self.variable_to_shape}  # every process: reads may be collective
+        if self.rank == 0:
+            np.savez(folder / "variables.npz", **{name.replace("/", "__"): value for name, value in state.items()})
+            manifest = self._dump_manifest()
+            manifest["host"] = dict(step=self.step, current_learning_rate=self.current_learning_rate, decay_step=self.decay_step)
+            (folder / "manifest.json").write_text(json.dumps(manifest, indent=1))
+
+    def restore(self, folder: Union[str, Path]) -> None:
+        """Load a checkpoint written by :meth:`dump` into an engine built with the same settings
+        (any number of processes: each reads the files of its own shards)."""
+        folder = Path(folder)
+        manifest = json.loads((folder / "manifest.json").read_text())
+        mine = self._dump_manifest()
+        for key, value in mine.items():
+            if manifest.get(key) != value:
+                raise ValueError(f"checkpoint {folder} was written with {key}={manifest.get(key)!r}, this engine has {value!r}")
+        row_bytes, n_entity, n_local, first_shard = self._entity_layout()
+        chunk_rows = max(1, self.DUMP_CHUNK_BYTES // row_bytes)
+        for local in range(n_local):
+            path = folder / f"entity_shard{first_shard + local:03d}.npy"
+            rows = np.load(path, mmap_mode="r")
+            if rows.shape != (n_entity, row_bytes // 4) or rows.dtype != np.uint32:
+                raise ValueError(f"{path} holds {rows.dtype}{rows.shape}, expected uint32{(n_entity, row_bytes // 4)}")
+            for first in range(0, n_entity, chunk_rows):
+                count = min(chunk_rows, n_entity - first)
+                self.engine.run("restore_entity_rows", dict(shard_range=np.array([local, first, count], np.uint32),
+                                                            rows=np.ascontiguousarray(rows[first : first + count])))
+        with np.load(folder / "variables.npz") as state:
+            for name in self.variable_to_shape:
+                self.write_variable(name, state[name.replace("/", "__")])
+        host = manifest["host"]
+        self.step, self.current_learning_rate, self.decay_step = host["step"], host["current_learning_rate"], host["decay_step"]
+        self.uninitialized_entity_data[:] = False
 
     # -- training ------------------------------------------------------------
 

@@ -89,13 +89,23 @@ const char* kge_last_error(const kge_engine* engine);
  * 814-819,853-854,858-860,868-869, with the leading axis equal to the number of shards
  * this process holds (all of them when world_size is 1, as in the reference).  For
  * "read"/"write" the variable is named by `variable_name` and the array is called "value"
- * (src/poplar_kge.cpp:977-991).  One command is added: "write_entity_rows"
- * (write_indices u32 [n, rw], write_data [n, rw, 3D+F]) writes whole rows, embedding and
- * optimiser state included, which the reference cannot do from the host; and
- * "initialise_entities" (no arrays) fills every row on the device: embeddings as
- * "write_entity" draws them, features ~ N(0, 1), optimiser state zero.  It stands in for
- * the reference's host loop that streams all features through "write_entity"
- * (src/python/poplar_kge.py:690-705) when the data is synthetic.
+ * (src/poplar_kge.cpp:977-991).  Commands added to the reference's:
+ *   "write_entity_rows" (write_indices u32 [n, rw], write_data [n, rw, 3D+F]) writes whole
+ *     rows, embedding and optimiser state included, which the reference cannot do from the host.
+ *   "initialise_entities" (no arrays) fills every row on the device: embeddings as
+ *     "write_entity" draws them, features ~ N(0, 1), optimiser state zero.  It stands in for
+ *     the reference's host loop that streams all features through "write_entity"
+ *     (src/python/poplar_kge.py:690-705) when the data is synthetic.
+ *   "entity_layout" (layout u32 [4]: bytes of a stored row, rows per shard, local shards, first
+ *     local shard), "dump_entity_rows" and "restore_entity_rows" (shard_range u32 [3] = local
+ *     shard, first row, row count; rows u32 [count, row bytes / 4]) copy a contiguous range of a
+ *     shard's table as stored, for per-shard checkpoints; the reference reads the table only
+ *     through read_entity chunks gathered into one host array (src/python/poplar_kge.py:583-598).
+ *   "load_triples" (triples u32 [3, n_triples] sorted by bucket, bucket_offset and bucket_count
+ *     u32 [n_shard, n_shard], shard_to_count u32 [n_shard]), "sample_batch" (sample_seed u32 [1];
+ *     returns the five index streams of "train_step_loop") and "train_step_loop_sampled"
+ *     (learning_rate, loss, sample_seed) are the reference's host-side batch sampler
+ *     (src/python/poplar_kge_dataset.py:199-263, 310-393) on the device.
  */
 int kge_run(kge_engine* engine, const char* command, const kge_array* arrays, size_t n_arrays,
             const char* variable_name);
