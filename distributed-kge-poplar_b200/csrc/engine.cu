@@ -53,11 +53,13 @@ int parse_storage(const std::string& key, const std::string& value) {
                                      << value << "'");
 }
 
-void reject_regulariser(const SettingMap& s, const std::string& prefix) {
-    get_float(s, prefix + ".power");
-    if (get_float(s, prefix + ".weight") > 0.f) {
-        fail(KGE_INVALID_ARGUMENT, msg() << "'" << prefix << ".weight' > 0 is not supported by this engine");
-    }
+// src/poplar_kge.cpp:144-152.  A power below 1 is no norm, and pow of a negative base needs an integer power.
+void read_regulariser(const SettingMap& s, const std::string& prefix, float& power, float& weight) {
+    power = get_float(s, prefix + ".power");
+    weight = get_float(s, prefix + ".weight");
+    if (weight < 0.f) fail(KGE_INVALID_ARGUMENT, msg() << "'" << prefix << ".weight' must not be negative");
+    if (weight > 0.f && !(power >= 1.f))
+        fail(KGE_INVALID_ARGUMENT, msg() << "'" << prefix << ".power' must be at least 1, actual: " << power);
 }
 
 }  // namespace
@@ -96,9 +98,9 @@ Config parse_config(const SettingMap& s) {
     c.a2a_size = get_unsigned(s, "data.a2a_size");
     c.adversarial_scale = get_float(s, "model.negative_adversarial_scale");
     const std::string loss = get_string(s, "training.loss.type");
-    reject_regulariser(s, "training.embedding_regularisation");
-    reject_regulariser(s, "training.feature_regularisation");
-    reject_regulariser(s, "training.hidden_regularisation");
+    read_regulariser(s, "training.embedding_regularisation", c.reg_power[0], c.reg_weight[0]);
+    read_regulariser(s, "training.feature_regularisation", c.reg_power[1], c.reg_weight[1]);
+    read_regulariser(s, "training.hidden_regularisation", c.reg_power[2], c.reg_weight[2]);
     c.correction_weight = loss == "softmax" ? get_float(s, "training.loss.correction_weight") : 0.f;
     c.loss_scale = get_float(s, "training.loss_scale");
     c.n_step = get_unsigned(s, "execution.train_steps_per_program_run");
@@ -389,6 +391,12 @@ void Engine::allocate() {
         b.d_pred = (float*)device_alloc((size_t)B * D * 4);
         b.d_head = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
         b.d_relrow = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
+        if (cfg_.regularised()) {
+            b.reg_val = (float*)device_alloc((size_t)R * D * 4);
+            b.reg_h = (float*)device_alloc((size_t)R * D * 4);
+            b.reg_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : nullptr;
+            b.reg_loss_rows = (float*)device_alloc((size_t)R * 4);
+        }
         b.d_hid_h = (float*)device_alloc((size_t)R * D * 4);
         b.d_hid_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : nullptr;
         b.proj_partial = (float*)device_alloc(std::max<size_t>(1, cfg_.n_net()) * proj_splits_ * proj_elems_ * 4);
@@ -460,6 +468,12 @@ void Engine::allocate() {
     d_loss_last_ = (float*)device_alloc(n_local_ * 4);
     d_loss_counter_ = (unsigned*)device_alloc(n_local_ * sizeof(unsigned));
     KGE_CUDA(cudaMemset(d_loss_counter_, 0, n_local_ * sizeof(unsigned)));
+    if (cfg_.regularised()) {
+        d_reg_loss_ = (float*)device_alloc(n_local_ * 2 * sizeof(float));
+        KGE_CUDA(cudaMemset(d_reg_loss_, 0, n_local_ * 2 * sizeof(float)));
+        d_reg_counter_ = (unsigned*)device_alloc(n_local_ * sizeof(unsigned));
+        KGE_CUDA(cudaMemset(d_reg_counter_, 0, n_local_ * sizeof(unsigned)));
+    }
 
     const size_t rw = (size_t)n_local_ * cfg_.rw_batch;
     d_rw_idx_ = (uint32_t*)device_alloc(std::max<size_t>(rw, (size_t)n_local_ * cfg_.predict_hr * 2) * 4);
@@ -1093,6 +1107,32 @@ void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_p
     KGE_CUDA(err);
 }
 
+// The norm regularisers of local shard l's gathered rows (k_regularise): after the hidden rows,
+// before the loss (which adds their loss term) and the entity update (which adds their gradients).
+void Engine::launch_regularise(unsigned l, const uint8_t* rows_c) {
+    ShardBuffers& b = shards_[l];
+    const size_t R = cfg_.n_remote();
+    RegParams rp{};
+    for (int i = 0; i < 3; ++i) rp.power[i] = cfg_.reg_power[i], rp.weight[i] = cfg_.reg_weight[i];
+    rp.loss_scale = cfg_.loss_scale;
+    rp.shared = cfg_.n_net() == 2 ? 0 : 1;
+    float* loss = d_reg_loss_ + 2 * l;
+    if (cfg_.state_type == ST_F32)
+        KGE_LAUNCH("regularise", KGE_CUDA(launch_dependent(k_regularise<float>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, stream_, rows_c, layout_, b.hid_h,
+                                                           b.hid_t, (int)R, rp, b.reg_val, b.reg_h, b.reg_t, b.reg_loss_rows, loss, loss + 1, d_reg_counter_ + l)));
+    else
+        KGE_LAUNCH("regularise", KGE_CUDA(launch_dependent(k_regularise<__half>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, stream_, rows_c, layout_, b.hid_h,
+                                                           b.hid_t, (int)R, rp, b.reg_val, b.reg_h, b.reg_t, b.reg_loss_rows, loss, loss + 1, d_reg_counter_ + l)));
+}
+
+RelationRows Engine::with_regularisers(RelationRows rr, unsigned l) const {
+    const ShardBuffers& b = shards_[l];
+    rr.reg_val = b.reg_val;
+    rr.reg_h = b.reg_h;
+    rr.reg_t = b.reg_t;
+    return rr;
+}
+
 // The training step with its contractions on the plane-fed kernel: seven launches on the step's
 // chain (hidden + lookups + send, scores, loss, score gradients + return, segment sums + Adam +
 // relation gradients, projection gradient, dense update) and the next step's gather beside the
@@ -1168,6 +1208,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                           b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn, sync,
                                                           b.send_lo_dst, b.pred_lo, bf16 ? 1 : 0)));
+        if (cfg_.regularised()) launch_regularise(l, rows_c);
     }
     KGE_CUDA(cudaGetLastError());
 
@@ -1197,7 +1238,8 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         }
         // 3. loss and the coefficients of the score gradients
         KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,
-                                                d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0, (int)B, stream_)));
+                                                d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0, (int)B, stream_,
+                                                d_reg_loss_ ? d_reg_loss_ + 2 * l : nullptr)));
         // 4. score gradients; the tails' rows go straight to the shards that own them
         if (l1) {
             PairBwdArgs pa{};
@@ -1239,8 +1281,8 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         ShardBuffers& b = shards_[l];
         const size_t sidx = (size_t)l * cfg_.n_step + step;
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
-        const RelationRows rr{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst, (int)n_rel, (int)cfg_.world,
-                              b.d_hid_h_lo, b.d_hid_t_lo};
+        const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
+                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr}, l);
         const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
         if (cfg_.state_type == ST_F32)
             KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
@@ -1379,6 +1421,7 @@ void Engine::launch_one_step(unsigned step) {
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<1>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
                                                                       (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
+        if (cfg_.regularised()) launch_regularise(l, rows_c);
     }
     KGE_CUDA(cudaGetLastError());
 
@@ -1411,7 +1454,7 @@ void Engine::launch_one_step(unsigned step) {
                                                       fused_wait ? sync : ExchangeSync{})));
         }
         KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,
-                                                d_loss_counter_ + l, nullptr, 0, (int)B, stream_)));
+                                                d_loss_counter_ + l, nullptr, 0, (int)B, stream_, d_reg_loss_ ? d_reg_loss_ + 2 * l : nullptr)));
         if (tc_bwd) {
             // Both input gradients are contractions with the coefficient matrix C [B, T]:
             //   dot:  d_pred = C . tails,                          d_tails = C^T . pred
@@ -1486,20 +1529,20 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
         } else {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, RelationRows{})));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
         }
     }
     KGE_CUDA(cudaGetLastError());

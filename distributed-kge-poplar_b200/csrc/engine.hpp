@@ -32,6 +32,10 @@ struct Config {
     int score_fn, dist_fn, loss_fn;
     bool share_networks;
     float gamma, init_scale, adversarial_scale, correction_weight, loss_scale;
+    // Norm regularisers of the gathered rows' values, feature-network outputs and hidden rows
+    // (training.embedding_regularisation, .feature_regularisation, .hidden_regularisation): power and weight.
+    float reg_power[3], reg_weight[3];
+    bool regularised() const { return reg_weight[0] > 0.f || reg_weight[1] > 0.f || reg_weight[2] > 0.f; }
     float beta_m, beta_v, epsilon, weight_decay;
     std::map<std::string, float> lr_modifiers;
     int state_type, feature_type;
@@ -107,6 +111,7 @@ class Engine {
         float *hid_h = nullptr, *hid_t = nullptr, *pred = nullptr, *raw = nullptr, *coeff = nullptr;
         float *d_pred = nullptr, *d_head = nullptr, *d_relrow = nullptr;
         float *d_hid_h = nullptr, *d_hid_t = nullptr, *proj_partial = nullptr, *loss_rows = nullptr;
+        float *reg_val = nullptr, *reg_h = nullptr, *reg_t = nullptr, *reg_loss_rows = nullptr;  // regularisers' terms, [R, D] and [R]
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
         float** grad_dst = nullptr;  // device table [n_shard]
@@ -237,6 +242,10 @@ class Engine {
     uint4* d_heavy_parts_ = nullptr;
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
     unsigned* d_loss_counter_ = nullptr;
+    float* d_reg_loss_ = nullptr;      // [n_local][2]: the step's regularisation loss, and a sink for its running sum
+    unsigned* d_reg_counter_ = nullptr;
+    void launch_regularise(unsigned l, const uint8_t* rows_c);
+    RelationRows with_regularisers(RelationRows rr, unsigned l) const;
     uint8_t* pinned_ = nullptr;
     size_t pinned_bytes_ = 0;
     bool staged_ = false;

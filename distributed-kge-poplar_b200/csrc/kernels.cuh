@@ -636,9 +636,10 @@ struct LossParams {
 // After its row, the block that finishes last adds the rows' loss terms in row order (a fixed
 // tree: the result does not depend on which block that is) and adds the step's loss to the running
 // total of the program run (src/poplar_kge.cpp:735-736).
+// `extra` (may be null): a term of the step's loss that another kernel has already summed (the regularisers).
 template <int THREADS>
 __device__ __forceinline__ void finish_step_loss(const float* loss_rows, int B, float inv_normaliser, float* loss_total,
-                                                 float* loss_last, unsigned* counter, float* scratch) {
+                                                 float* loss_last, unsigned* counter, float* scratch, const float* extra) {
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
@@ -650,7 +651,7 @@ __device__ __forceinline__ void finish_step_loss(const float* loss_rows, int B, 
     for (int i = threadIdx.x; i < B; i += THREADS) part += __ldcg(loss_rows + i);
     part = block_sum<THREADS>(part, scratch);
     if (threadIdx.x == 0) {
-        const float step_loss = part * inv_normaliser;
+        const float step_loss = part * inv_normaliser + (extra ? *extra : 0.f);
         *loss_total += step_loss;
         *loss_last = step_loss;
         *counter = 0u;
@@ -661,7 +662,8 @@ template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float* __restrict__ coeff,
        float* __restrict__ loss_rows, LossParams lp, float inv_normaliser, float* __restrict__ loss_total,
-       float* __restrict__ loss_last, unsigned* __restrict__ counter, float* __restrict__ coeff_lo = nullptr, int lo_bf16 = 0) {
+       float* __restrict__ loss_last, unsigned* __restrict__ counter, float* __restrict__ coeff_lo, int lo_bf16,
+       const float* __restrict__ extra_loss) {
     grid_dependency_sync();
     __shared__ float scratch[THREADS / 32];
     const int i = blockIdx.x, T = lp.n_tail;
@@ -700,7 +702,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
             if (c16) c16[j] = __float2bfloat16_rn(cj);
             if (j == lab) loss_rows[i] = -logp;
         }
-        finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch);
+        finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch, extra_loss);
         return;
     }
     // log-sigmoid, optionally with self-adversarial weights from a detached softmax
@@ -737,15 +739,16 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
     }
     part = block_sum<THREADS>(part, scratch);
     if (threadIdx.x == 0) loss_rows[i] = -part;
-    finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch);
+    finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch, extra_loss);
 }
 
 inline cudaError_t launch_loss(const float* raw, const uint32_t* label, float* coeff, float* loss_rows, const LossParams& lp, float inv_normaliser,
-                               float* loss_total, float* loss_last, unsigned* counter, float* coeff_lo, int lo_bf16, int B, cudaStream_t stream) {
+                               float* loss_total, float* loss_last, unsigned* counter, float* coeff_lo, int lo_bf16, int B, cudaStream_t stream,
+                               const float* extra_loss = nullptr) {
     // One block per row keeps about 130 thousand threads in flight for the metric's 512 x 768 scores; a warp
     // per row (a sixth as many threads, each with a serial chain of exponentials) measured 4 us slower.
     return launch_dependent(k_loss<256>, dim3((unsigned)B), dim3(256), 0, stream, raw, label, coeff, loss_rows, lp, inv_normaliser, loss_total,
-                            loss_last, counter, coeff_lo, lo_bf16);
+                            loss_last, counter, coeff_lo, lo_bf16, extra_loss);
 }
 
 // ---------------------------------------------------------------------------
@@ -1087,6 +1090,84 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
 constexpr int kSegmentLanes = 4;  // threads groups that share the lookups of one part of a popular row
 constexpr int kRowsPerBlock = 8;  // gathered rows per block of k_entity_update: one warp each
 
+// Norm regularisers of the gathered rows (src/poplar_kge.cpp:430-437, 463-465): each of the two
+// entityHidden calls of a step (head part, tail part) adds
+//   w_e * sum_r N(value_r) + w_f * sum_r N(feature_hidden_r) + w_h * sum_r N(hidden_r),
+// N(a) = (sum_k |a_k^p|)^(1/p) per row (lpnorm, :389-391), over all R gathered rows, to the shard's
+// loss, not normalised.  The backward is the reference's tape: pow gives g * p * out / a with 0 where
+// a is 0 (src/pag/pag.cpp:493-503), abs gives sign (:449-456), so
+//   dN/da_k = N / s * |a_k|^p / a_k   (s = sum_k |a_k|^p; 0 where a_k or s is 0),
+// times the weight and the loss scale (the root gradient, :691).  |a|^p stands for |a^p|: the same
+// wherever a^p is defined.  The feature network's output is taken as hidden - value.
+// One warp per row; writes the three gradient terms k_entity_update adds and the row's loss term;
+// the last block adds the rows' terms in row order into *loss_out.
+struct RegParams {
+    float power[3], weight[3];  // embedding, feature, hidden
+    float loss_scale;
+    int shared;                 // one feature network: both calls see the same rows
+};
+
+__device__ __forceinline__ float abs_pow(float a, float p) {
+    a = fabsf(a);
+    return p == 2.f ? a * a : (p == 1.f ? a : powf(a, p));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <class ST>
+__global__ void __launch_bounds__(256)
+k_regularise(const uint8_t* __restrict__ rows_c, RowLayout L, const float* __restrict__ hid_h, const float* __restrict__ hid_t, int R,
+             RegParams rp, float* __restrict__ reg_val, float* __restrict__ reg_h, float* __restrict__ reg_t,
+             float* __restrict__ loss_rows, float* __restrict__ loss_out, float* __restrict__ loss_sink, unsigned* __restrict__ counter) {
+    grid_dependency_sync();
+    __shared__ float scratch[8];
+    const int lane = threadIdx.x & 31, r = (int)blockIdx.x * 8 + (int)(threadIdx.x >> 5), D = (int)L.d;
+    if (r < R) {
+        const uint8_t* __restrict__ row = rows_c + (size_t)r * L.row_bytes;
+        const float* __restrict__ hid[2] = {hid_h + (size_t)r * D, hid_t + (size_t)r * D};
+        float* __restrict__ out[2] = {reg_h + (size_t)r * D, rp.shared ? nullptr : reg_t + (size_t)r * D};
+        const int parts = rp.shared ? 1 : 2;
+        const float calls = rp.shared ? 2.f : 1.f;  // how many of the two calls a part stands for
+        float s_e = 0.f, s_f[2] = {0.f, 0.f}, s_h[2] = {0.f, 0.f};
+        for (int c = lane; c < D; c += 32) {
+            const float v = load_value<ST>(L, row, c);
+            s_e += abs_pow(v, rp.power[0]);
+            for (int q = 0; q < parts; ++q) {
+                const float h = hid[q][c];
+                s_f[q] += abs_pow(h - v, rp.power[1]);
+                s_h[q] += abs_pow(h, rp.power[2]);
+            }
+        }
+        // norm and the factor weight * loss_scale * N / s of a row's gradient
+        auto norm = [&](float s, int which, float& fac) {
+            s = warp_sum(s);
+            const float n = s > 0.f ? powf(s, 1.f / rp.power[which]) : 0.f;
+            fac = s > 0.f && rp.weight[which] > 0.f ? rp.weight[which] * rp.loss_scale * n / s : 0.f;
+            return rp.weight[which] > 0.f ? rp.weight[which] * n : 0.f;
+        };
+        auto term = [&](float a, int which, float fac) { return a == 0.f || fac == 0.f ? 0.f : fac * abs_pow(a, rp.power[which]) / a; };
+        float fac_e, fac_f[2] = {0.f, 0.f}, fac_h[2] = {0.f, 0.f};
+        float loss = 2.f * norm(s_e, 0, fac_e);
+        for (int q = 0; q < parts; ++q) loss += calls * (norm(s_f[q], 1, fac_f[q]) + norm(s_h[q], 2, fac_h[q]));
+        for (int c = lane; c < D; c += 32) {
+            const float v = load_value<ST>(L, row, c);
+            float gv = 2.f * term(v, 0, fac_e);
+            for (int q = 0; q < parts; ++q) {
+                const float h = hid[q][c];
+                const float g_h = calls * term(h, 2, fac_h[q]);
+                gv += g_h;
+                out[q][c] = g_h + calls * term(h - v, 1, fac_f[q]);
+            }
+            reg_val[(size_t)r * D + c] = gv;
+        }
+        if (lane == 0) loss_rows[r] = loss;
+    }
+    finish_step_loss<256>(loss_rows, R, 1.f, loss_sink, loss_out, counter, scratch, nullptr);
+}
+
 struct HeavyRows {
     const uint4* parts;      // [kHeavySlots] {gathered row, first lookup, end lookup, (first part's slot << 16) | (parts << 8) | part}
     const uint32_t* count;   // parts in use
@@ -1107,6 +1188,12 @@ struct RelationRows {
     int n_rel, n_owner;
     float* d_hid_h_lo;           // lower TF32 planes of the hidden-row gradients (null: not needed)
     float* d_hid_t_lo;
+    // Gradients of the norm regularisers (k_regularise), [R, D] each, null when all weights are 0:
+    // reg_val joins the value's gradient, reg_h / reg_t the gradient of the feature network's output
+    // (reg_t null with a shared network, whose reg_h then holds both calls' terms).
+    const float* reg_val;
+    const float* reg_h;
+    const float* reg_t;
 };
 
 template <int V, int LANES>
@@ -1278,6 +1365,18 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
     // The row's hidden gradients and its Adam step for the columns c .. c+V-1 (one thread).
     auto finish = [&](int c, float (&gh)[V], float (&gt)[V]) {
         const size_t o = (size_t)r * D + c;
+        float gv[V];  // the value's gradient: the lookups' sums (+ the regularisers' terms for the value)
+#pragma unroll
+        for (int u = 0; u < V; ++u) gv[u] = gh[u] + gt[u];
+        if (rr.reg_val) {
+            // gh / gt become the gradients of the feature network's output
+#pragma unroll
+            for (int u = 0; u < V; ++u) {
+                gv[u] += rr.reg_val[o + u];
+                gh[u] += rr.reg_h[o + u];
+                if (rr.reg_t) gt[u] += rr.reg_t[o + u];
+            }
+        }
         if (V == 4) {
             if (d_hid_t) {
                 const float4 a = make_float4(gh[0], gh[1 % V], gh[2 % V], gh[3 % V]), b = make_float4(gt[0], gt[1 % V], gt[2 % V], gt[3 % V]);
@@ -1306,7 +1405,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         }
 #pragma unroll
         for (int u = 0; u < V; ++u) {
-            const float g = gh[u] + gt[u];
+            const float g = gv[u];
             float v = qq[u] * qq[u];
             m[u] = ap.beta_m * m[u] + ap.one_minus_beta_m * g;
             v = ap.beta_v * v + ap.one_minus_beta_v * g * g;

@@ -43,6 +43,10 @@ class StepConfig:
     weight_decay: float = 0.0
     loss_scale: Optional[float] = None
     learning_rate_modifiers: Dict[str, float] = dataclasses.field(default_factory=dict)
+    # (power, weight) of the norm regularisers (src/poplar_kge.cpp:144-152, 175-177)
+    embedding_regularisation: Tuple[float, float] = (2.0, 0.0)
+    feature_regularisation: Tuple[float, float] = (2.0, 0.0)
+    hidden_regularisation: Tuple[float, float] = (2.0, 0.0)
 
     def __post_init__(self) -> None:
         if self.loss_scale is None:
@@ -157,6 +161,23 @@ def scatter_add_rows(n_rows: int, indices: np.ndarray, rows: np.ndarray) -> np.n
     out = np.zeros((n_rows,) + rows.shape[1:], dtype=rows.dtype)
     np.add.at(out, indices, rows)
     return out
+
+
+def lp_norm(a: np.ndarray, p: float) -> np.ndarray:
+    """Rows' (sum_k |a_k^p|)^(1/p) (lpnorm, src/poplar_kge.cpp:389-391).  |a|^p stands for |a^p|:
+    the same wherever a^p is defined (integer p, or a >= 0)."""
+    return np.sum(np.abs(a) ** p, axis=-1) ** (1.0 / p)
+
+
+def lp_norm_grad(a: np.ndarray, p: float, grad_out: np.ndarray) -> np.ndarray:
+    """Backward of lp_norm as the reference's tape replays it: pow gives g * exponent * out / base
+    with 0 where the base is 0 (src/pag/pag.cpp:493-503), abs gives sign(x) * g (:449-456), the
+    sum broadcasts."""
+    u = np.abs(a) ** p
+    s = np.sum(u, axis=-1, keepdims=True)
+    norm = s ** (1.0 / p)
+    d_s = grad_out[..., None] * (1.0 / p) * norm / (s + (s == 0))  # outer pow
+    return d_s * p * u / (a + (a == 0))  # abs, then the inner pow: sign(a^p) * p * a^p / a
 
 
 def all_to_all(blocks: np.ndarray) -> np.ndarray:
@@ -431,6 +452,25 @@ class Oracle:
         heads = np.stack([hid_h[s, head[s]] for s in range(n)])
         send = np.stack([hid_t[s, a2a[s]] for s in range(n)])  # [src, dst, a2a, D]
         tails = all_to_all(send).reshape(n, cfg.n_tail, d)  # [dst, src*a2a, D]
+        # norm regularisers: every entityHidden call (head part, tail part) adds its three terms to
+        # the shard's loss, not normalised (:430-437, 463-465, 673-688); root gradient loss_scale (:691)
+        reg_loss = np.zeros(n, self.entity_data.dtype)
+        reg_value = np.zeros_like(value)                      # gradient of the gathered values
+        reg_fh = [np.zeros_like(value), np.zeros_like(value)]  # gradient of each call's feature-network output
+        ls = dt(_f32(cfg.loss_scale))
+        for call, (hid, w) in enumerate(((hid_h, w_head), (hid_t, w_tail))):
+            terms = ((cfg.embedding_regularisation, value, "value"), (cfg.feature_regularisation, feat @ w, "fh"),
+                     (cfg.hidden_regularisation, hid, "hidden"))
+            for (power, weight), tensor, kind in terms:
+                if weight <= 0:
+                    continue
+                wt = dt(_f32(weight))
+                reg_loss += wt * np.sum(lp_norm(tensor, power), axis=-1)
+                g = lp_norm_grad(tensor, power, np.full(tensor.shape[:-1], wt * ls, tensor.dtype))
+                if kind in ("value", "hidden"):
+                    reg_value += g
+                if kind in ("fh", "hidden"):
+                    reg_fh[call] += g
         # 3./4. scores and loss (:684-688)
         losses = np.zeros(n, self.entity_data.dtype)
         d_hid_h = np.zeros_like(hid_h)
@@ -458,14 +498,18 @@ class Oracle:
                 for s in range(n)
             ]
         )
-        d_value = d_hid_h + d_hid_t
+        d_value = d_hid_h + d_hid_t + reg_value
+        d_fh_h, d_fh_t = d_hid_h + reg_fh[0], d_hid_t + reg_fh[1]
+        losses = losses + reg_loss
         grads = {"relation_embedding": d_rel}
         if cfg.share_feature_networks:
-            grads["feature_projection"] = np.einsum("srf,srd->fd", feat, d_value)
+            grads["feature_projection"] = np.einsum("srf,srd->fd", feat, d_fh_h + d_fh_t)
         else:
-            grads["head_feature_projection"] = np.einsum("srf,srd->fd", feat, d_hid_h)
-            grads["tail_feature_projection"] = np.einsum("srf,srd->fd", feat, d_hid_t)
-        keep.update(d_value=d_value, grads=grads, d_tails=d_tails)
+            grads["head_feature_projection"] = np.einsum("srf,srd->fd", feat, d_fh_h)
+            grads["tail_feature_projection"] = np.einsum("srf,srd->fd", feat, d_fh_t)
+        one_net = cfg.share_feature_networks or cfg.entity_feature_size == 0
+        keep.update(d_value=d_value, grads=grads, d_tails=d_tails, reg_loss=reg_loss,
+                    d_feature_hidden=d_fh_h + d_fh_t if one_net else d_fh_h)
         self.last = keep
         # update (:692-704)
         self.step += 1

@@ -28,9 +28,12 @@ def engine_settings(cfg: StepConfig, n_step: int = 1, dtype: str = "float32",
         "training.learning_rate_modifiers": dict(cfg.learning_rate_modifiers),
         "data.batch_size": cfg.batch_size, "data.a2a_size": cfg.a2a_size,
         "training.loss.type": cfg.loss_type, "training.loss_scale": float(cfg.loss_scale),
-        "training.embedding_regularisation.power": 3.0, "training.embedding_regularisation.weight": 0.0,
-        "training.feature_regularisation.power": 3.0, "training.feature_regularisation.weight": 0.0,
-        "training.hidden_regularisation.power": 3.0, "training.hidden_regularisation.weight": 0.0,
+        "training.embedding_regularisation.power": float(cfg.embedding_regularisation[0]),
+        "training.embedding_regularisation.weight": float(cfg.embedding_regularisation[1]),
+        "training.feature_regularisation.power": float(cfg.feature_regularisation[0]),
+        "training.feature_regularisation.weight": float(cfg.feature_regularisation[1]),
+        "training.hidden_regularisation.power": float(cfg.hidden_regularisation[0]),
+        "training.hidden_regularisation.weight": float(cfg.hidden_regularisation[1]),
         "execution.device": "cuda", "execution.dtype": dtype,
         "execution.train_steps_per_program_run": n_step, "execution.rw_batch_size": rw_batch,
         "execution.predict_hr_batch_size": 8, "execution.predict_tail_batch_size": 64,

@@ -78,6 +78,26 @@ CASES = {
                                             entity_feature_size=192, batch_size=128, a2a_size=96, score_fn="DistMult",
                                             distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False),
                              seed=9, rtol=5e-5, warm_only=True),
+    # Norm regularisers of the gathered values, the feature network's outputs and the hidden rows
+    # (src/poplar_kge.cpp:430-437, 463-465): with one shared network, whose two calls double every
+    # term, and with separate networks and no features
+    "regularised_shared": dict(cfg=StepConfig(n_shard=2, n_entity=300, n_relation_type=4, embedding_size=32,
+                                              entity_feature_size=24, batch_size=16, a2a_size=12, score_fn="TransE",
+                                              distance_fn="L2", gamma=6.0, loss_type="softmax", correction_weight=1.0,
+                                              embedding_regularisation=(3.0, 0.02), feature_regularisation=(2.0, 0.03),
+                                              hidden_regularisation=(2.0, 0.01)),
+                               seed=21, feature_dtype="float16"),
+    "regularised_separate": dict(cfg=StepConfig(n_shard=2, n_entity=200, n_relation_type=4, embedding_size=16,
+                                                entity_feature_size=12, batch_size=8, a2a_size=6, score_fn="DistMult",
+                                                distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
+                                                embedding_regularisation=(2.0, 0.05), feature_regularisation=(1.0, 0.01),
+                                                hidden_regularisation=(3.0, 0.02)),
+                                 seed=22),
+    "regularised_no_features": dict(cfg=StepConfig(n_shard=3, n_entity=101, n_relation_type=6, embedding_size=10,
+                                                   entity_feature_size=0, batch_size=9, a2a_size=5, score_fn="TransE",
+                                                   distance_fn="L1", gamma=3.0, loss_type="logsigmoid",
+                                                   embedding_regularisation=(2.5, 0.02), hidden_regularisation=(2.0, 0.04)),
+                                    seed=23),
     "single_shard": dict(cfg=StepConfig(n_shard=1, n_entity=400, n_relation_type=5, embedding_size=64,
                                         entity_feature_size=32, batch_size=64, a2a_size=96, score_fn="TransE",
                                         distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
@@ -155,7 +175,7 @@ def test_single_step_matches_oracle(name, warm, tensor_cores):
         assert_close(scores, last["scores"][s], RTOL, f"{name}: scores[{s}]")
         d_hidden = engine.debug_fetch("d_hidden", s, R * D).reshape(R, D)
         if cfg.share_feature_networks or cfg.entity_feature_size == 0:
-            assert_close(d_hidden, last["d_value"][s], RTOL, f"{name}: d hidden[{s}]")
+            assert_close(d_hidden, last["d_feature_hidden"][s], RTOL, f"{name}: d hidden[{s}]")
     dense = engine.debug_fetch("dense_grad", 0, 1 << 24)
     n_rel = cfg.n_relation_type * D
     assert dense.size == n_rel + len(cfg.projection_names) * cfg.entity_feature_size * D * (cfg.entity_feature_size > 0)

@@ -104,6 +104,10 @@ def test_operator_known_answers():
     blocks = np.array([[[1011, 1012, 1013], [1021, 1022, 1023]], [[2011, 2012, 2013], [2021, 2022, 2023]]], np.float64)
     np.testing.assert_array_equal(so.all_to_all(blocks).reshape(-1),
                                   [1011, 1012, 1013, 2011, 2012, 2013, 1021, 1022, 1023, 2021, 2022, 2023])
+    # lpnorm (src/poplar_kge.cpp:389-391) and the reference's pow backward, which gives 0 where the base is 0
+    np.testing.assert_allclose(so.lp_norm(np.array([[3.0, -4.0], [0.0, 0.0]]), 2.0), [5.0, 0.0])
+    np.testing.assert_allclose(so.lp_norm_grad(np.array([[3.0, -4.0], [0.0, 0.0]]), 2.0, np.array([10.0, 10.0])), [[6.0, -8.0], [0.0, 0.0]])
+    np.testing.assert_allclose(so.lp_norm_grad(np.array([[1.0, -2.0, 0.0]]), 1.0, np.array([2.0])), [[2.0, -2.0, 0.0]])
     # softmax cross-entropy of uniform logits over 4 classes is log 4
     cfg = StepConfig(n_shard=1, n_entity=10, n_relation_type=1, embedding_size=2, entity_feature_size=0,
                      batch_size=1, a2a_size=4, loss_type="softmax")
@@ -118,6 +122,10 @@ VARIANTS = [
     dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid"),
     dict(score_fn="ComplEx", distance_fn="MatMul", loss_type="softmax", correction_weight=0.3),
     dict(score_fn="TransE", distance_fn="L1", loss_type="softmax", share_feature_networks=False),
+    dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", embedding_regularisation=(3.0, 0.02),
+         feature_regularisation=(2.0, 0.03), hidden_regularisation=(1.0, 0.01)),
+    dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
+         embedding_regularisation=(2.0, 0.05), feature_regularisation=(2.5, 0.01), hidden_regularisation=(3.0, 0.02)),
 ]
 
 
@@ -148,6 +156,20 @@ def test_hand_derived_backward_matches_autograd(variant):
     heads = torch.stack([hid_h[s, idx["head"][s]] for s in range(n)])
     send = torch.stack([hid_t[s, idx["a2a"][s]] for s in range(n)])
     tails = send.transpose(0, 1).reshape(n, cfg.n_tail, d)
+
+    def norm_sum(x, power):  # rows' (sum |x|^p)^(1/p), summed; a zero row has zero gradient (the reference's pow rule)
+        s_ = (x.abs() ** power).sum(-1)
+        return (torch.where(s_ > 0, s_, torch.ones_like(s_)) ** (1.0 / power) * (s_ > 0)).sum()
+
+    def regularisers(s):  # both entityHidden calls add their three terms (src/poplar_kge.cpp:463-465)
+        out = 0
+        for hid, w_part in ((hid_h, w_h), (hid_t, w_t)):
+            for (power, weight), x in ((cfg.embedding_regularisation, value[s]), (cfg.feature_regularisation, feat[s] @ w_part),
+                                       (cfg.hidden_regularisation, hid[s])):
+                if weight > 0:
+                    out = out + float(np.float32(weight)) * norm_sum(x, power)
+        return out
+
     total = 0
     for s in range(n):
         r = rel[idx["relation"][s]]
@@ -177,6 +199,7 @@ def test_hand_derived_backward_matches_autograd(variant):
                 soft = torch.softmax(float(np.float32(cfg.negative_adversarial_scale)) * scores.detach() - 10000.0 * onehot, dim=1)
                 weight = weight * (onehot + (T - 1) * soft)
             loss = -(weight * torch.nn.functional.logsigmoid((2 * onehot - 1) * scores)).sum() / (n * cfg.batch_size * cfg.a2a_size * n)
+        loss = loss + regularisers(s)
         np.testing.assert_allclose(float(loss.detach()), losses[s], rtol=1e-10)
         total = total + loss
     total.backward(torch.tensor(float(cfg.loss_scale), dtype=torch.float64))
