@@ -149,7 +149,8 @@ Config parse_config(const SettingMap& s) {
         fail(KGE_INVALID_ARGUMENT, msg() << "'training.loss.type' must be one of 'logsigmoid' or 'softmax', not '"
                                          << loss << "'");
     if (mlp > 0) fail(KGE_INVALID_ARGUMENT, "'model.feature_mlp_size' > 0 is not supported by this engine");
-    if (dropout > 0.f) fail(KGE_INVALID_ARGUMENT, "'model.feature_dropout' > 0 is not supported by this engine");
+    if (!(dropout >= 0.f && dropout < 1.f)) fail(KGE_INVALID_ARGUMENT, msg() << "'model.feature_dropout' must be in [0, 1), actual: " << dropout);
+    c.dropout = dropout;
     if (c.state_type == ST_F16 && c.feature_type != ST_F16)
         fail(KGE_INVALID_ARGUMENT, "'execution.feature_dtype' must be 'float16' when 'execution.dtype' is 'float16'");
 
@@ -384,7 +385,7 @@ void Engine::allocate() {
         KGE_CUDA(cudaMemset(b.table, 0, table_bytes));
         for (uint8_t*& rows : b.rows_c2) rows = (uint8_t*)device_alloc((size_t)R * layout_.row_bytes);
         b.hid_h = (float*)device_alloc((size_t)R * D * 4);
-        b.hid_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : b.hid_h;
+        b.hid_t = two_nets || dropout_on() ? (float*)device_alloc((size_t)R * D * 4) : b.hid_h;  // dropout: each call has its own mask
         b.pred = (float*)device_alloc((size_t)B * D * 4);
         b.raw = (float*)device_alloc((size_t)B * T * 4);
         b.coeff = (float*)device_alloc((size_t)B * T * 4);
@@ -394,7 +395,7 @@ void Engine::allocate() {
         if (cfg_.regularised()) {
             b.reg_val = (float*)device_alloc((size_t)R * D * 4);
             b.reg_h = (float*)device_alloc((size_t)R * D * 4);
-            b.reg_t = two_nets ? (float*)device_alloc((size_t)R * D * 4) : nullptr;
+            b.reg_t = two_nets || dropout_on() ? (float*)device_alloc((size_t)R * D * 4) : nullptr;
             b.reg_loss_rows = (float*)device_alloc((size_t)R * 4);
         }
         b.d_hid_h = (float*)device_alloc((size_t)R * D * 4);
@@ -464,6 +465,7 @@ void Engine::allocate() {
     d_heavy_count_ = (uint32_t*)device_alloc(steps * 4);
     KGE_CUDA(cudaMemset(d_heavy_count_, 0, steps * 4));
     d_step_size_ = (float*)device_alloc(cfg_.n_step * 4);
+    d_step_key_ = (uint32_t*)device_alloc(cfg_.n_step * 4);
     d_loss_total_ = (float*)device_alloc(n_local_ * 4);
     d_loss_last_ = (float*)device_alloc(n_local_ * 4);
     d_loss_counter_ = (unsigned*)device_alloc(n_local_ * sizeof(unsigned));
@@ -479,7 +481,7 @@ void Engine::allocate() {
     d_rw_idx_ = (uint32_t*)device_alloc(std::max<size_t>(rw, (size_t)n_local_ * cfg_.predict_hr * 2) * 4);
     d_rw_data_ = (uint8_t*)device_alloc(rw * cfg_.row_width() * 4);
 
-    pinned_bytes_ = steps * ((size_t)R + T + 3 * B) * 4 + cfg_.n_step * 4 + 256;
+    pinned_bytes_ = steps * ((size_t)R + T + 3 * B) * 4 + 2 * cfg_.n_step * 4 + 256;  // index streams | step keys | step sizes | loss
     KGE_CUDA(cudaMallocHost((void**)&pinned_, pinned_bytes_));
     KGE_CUDA(cudaDeviceSynchronize());
 }
@@ -797,6 +799,11 @@ void Engine::train_staged(float learning_rate, float* loss) {
         sizes[i] = (std::sqrt(1.0f - std::pow(cfg_.beta_v, t)) / (1.0f - std::pow(cfg_.beta_m, t))) * learning_rate;
     }
     KGE_CUDA(cudaMemcpyAsync(d_step_size_, sizes, (size_t)cfg_.n_step * 4, cudaMemcpyHostToDevice, stream_));
+    if (dropout_on()) {
+        uint32_t* keys = reinterpret_cast<uint32_t*>(sizes) - cfg_.n_step;
+        for (unsigned i = 0; i < cfg_.n_step; ++i) keys[i] = (uint32_t)(step_ + 1 + i);
+        KGE_CUDA(cudaMemcpyAsync(d_step_key_, keys, (size_t)cfg_.n_step * 4, cudaMemcpyHostToDevice, stream_));
+    }
     KGE_CUDA(cudaMemsetAsync(d_loss_total_, 0, n_local_ * 4, stream_));
     KGE_CUDA(cudaEventRecord(ev_begin_, stream_));
     if (cfg_.cuda_graph && !kernel_timing_) {
@@ -1115,7 +1122,7 @@ void Engine::launch_regularise(unsigned l, const uint8_t* rows_c) {
     RegParams rp{};
     for (int i = 0; i < 3; ++i) rp.power[i] = cfg_.reg_power[i], rp.weight[i] = cfg_.reg_weight[i];
     rp.loss_scale = cfg_.loss_scale;
-    rp.shared = cfg_.n_net() == 2 ? 0 : 1;
+    rp.shared = b.hid_t == b.hid_h ? 1 : 0;
     float* loss = d_reg_loss_ + 2 * l;
     if (cfg_.state_type == ST_F32)
         KGE_LAUNCH("regularise", KGE_CUDA(launch_dependent(k_regularise<float>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, stream_, rows_c, layout_, b.hid_h,
@@ -1125,12 +1132,38 @@ void Engine::launch_regularise(unsigned l, const uint8_t* rows_c) {
                                                            b.hid_t, (int)R, rp, b.reg_val, b.reg_h, b.reg_t, b.reg_loss_rows, loss, loss + 1, d_reg_counter_ + l)));
 }
 
-RelationRows Engine::with_regularisers(RelationRows rr, unsigned l) const {
+RelationRows Engine::with_regularisers(RelationRows rr, unsigned l, unsigned step) const {
     const ShardBuffers& b = shards_[l];
     rr.reg_val = b.reg_val;
     rr.reg_h = b.reg_h;
     rr.reg_t = b.reg_t;
+    rr.drop = dropout_params(l, step);
     return rr;
+}
+
+DropoutParams Engine::dropout_params(unsigned l, unsigned step) const {
+    DropoutParams dp{};
+    if (!dropout_on()) return dp;
+    dp.threshold = (uint32_t)std::lround((1.0 - (double)cfg_.dropout) * 16777216.0);
+    dp.seed = cfg_.seed;
+    dp.step_key = d_step_key_ + step;
+    dp.shard = (uint32_t)(shard0_ + l);
+    dp.scale = 1.0f / (1.0f - cfg_.dropout);
+    return dp;
+}
+
+// hidden = value + dropout(hidden - value) for both calls of local shard l (k_dropout_hidden).
+void Engine::launch_dropout(unsigned l, unsigned step, const uint8_t* rows_c) {
+    ShardBuffers& b = shards_[l];
+    const size_t R = cfg_.n_remote(), quads = ceil_div(cfg_.d, 4);
+    const float* tail_in = cfg_.n_net() == 2 ? b.hid_t : b.hid_h;
+    const dim3 grid((unsigned)ceil_div(R * quads, 256));
+    if (cfg_.state_type == ST_F32)
+        KGE_LAUNCH("dropout", KGE_CUDA(launch_dependent(k_dropout_hidden<float>, grid, dim3(256), 0, stream_, rows_c, layout_, b.hid_h, tail_in, b.hid_t,
+                                                        (int)R, dropout_params(l, step))));
+    else
+        KGE_LAUNCH("dropout", KGE_CUDA(launch_dependent(k_dropout_hidden<__half>, grid, dim3(256), 0, stream_, rows_c, layout_, b.hid_h, tail_in, b.hid_t,
+                                                        (int)R, dropout_params(l, step))));
 }
 
 // The training step with its contractions on the plane-fed kernel: seven launches on the step's
@@ -1168,7 +1201,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
         // 1. hidden = value + feature . W, and from its epilogue the lookups and the send half of the exchange
-        const bool fused_route = F > 0 && cfg_.score_fn != SCORE_COMPLEX && cfg_.score_fn != SCORE_ROTATE;
+        const bool fused_route = F > 0 && cfg_.score_fn != SCORE_COMPLEX && cfg_.score_fn != SCORE_ROTATE && !dropout_on();
         if (F > 0) {
             tc::PlaneProblem nets[2] = {};
             const int n_nets = two_nets ? 2 : 1;
@@ -1204,6 +1237,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             KGE_LAUNCH("hidden", KGE_DISPATCH_ROW(cfg_, KGE_CUDA(launch_dependent(k_hidden<ST, FT>, dim3(grid), dim3(256), 0, stream_, rows_c, layout_,
                                                                                   nullptr, 0u, (int)R, nullptr, nullptr, b.hid_h, b.hid_t))));
         }
+        if (dropout_on()) launch_dropout(l, step, rows_c);
         if (!fused_route)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                           b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn, sync,
@@ -1282,7 +1316,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const size_t sidx = (size_t)l * cfg_.n_step + step;
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
         const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
-                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr}, l);
+                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}}, l, step);
         const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
         if (cfg_.state_type == ST_F32)
             KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
@@ -1413,6 +1447,7 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
+        if (dropout_on()) launch_dropout(l, step, rows_c);
         if (vec)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
@@ -1529,20 +1564,20 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
         } else {
             if (vec)
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
             else
                 KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
                                                 b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l))));
+                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
         }
     }
     KGE_CUDA(cudaGetLastError());

@@ -35,6 +35,7 @@ struct Config {
     // Norm regularisers of the gathered rows' values, feature-network outputs and hidden rows
     // (training.embedding_regularisation, .feature_regularisation, .hidden_regularisation): power and weight.
     float reg_power[3], reg_weight[3];
+    float dropout;  // model.feature_dropout: drop probability of the feature network's output while training
     bool regularised() const { return reg_weight[0] > 0.f || reg_weight[1] > 0.f || reg_weight[2] > 0.f; }
     float beta_m, beta_v, epsilon, weight_decay;
     std::map<std::string, float> lr_modifiers;
@@ -242,10 +243,14 @@ class Engine {
     uint4* d_heavy_parts_ = nullptr;
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
     unsigned* d_loss_counter_ = nullptr;
+    uint32_t* d_step_key_ = nullptr;   // [n_step] numbers of the staged training steps (keys of the dropout masks)
+    bool dropout_on() const { return cfg_.dropout > 0.f && cfg_.f > 0; }
+    DropoutParams dropout_params(unsigned l, unsigned step) const;
+    void launch_dropout(unsigned l, unsigned step, const uint8_t* rows_c);
     float* d_reg_loss_ = nullptr;      // [n_local][2]: the step's regularisation loss, and a sink for its running sum
     unsigned* d_reg_counter_ = nullptr;
     void launch_regularise(unsigned l, const uint8_t* rows_c);
-    RelationRows with_regularisers(RelationRows rr, unsigned l) const;
+    RelationRows with_regularisers(RelationRows rr, unsigned l, unsigned step) const;
     uint8_t* pinned_ = nullptr;
     size_t pinned_bytes_ = 0;
     bool staged_ = false;

@@ -1090,6 +1090,64 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
 constexpr int kSegmentLanes = 4;  // threads groups that share the lookups of one part of a popular row
 constexpr int kRowsPerBlock = 8;  // gathered rows per block of k_entity_update: one warp each
 
+// Dropout of the feature network's output (src/poplar_kge.cpp:459-461; frnn::dropout,
+// src/pag/pag.cpp:596-617): an element is kept with probability 1 - p and scaled by 1 / (1 - p);
+// the backward passes g / (1 - p) through the kept elements.  (The reference tests output != 0
+// instead of the mask; the two differ only where a kept element is exactly zero, which is a row
+// without features, whose gradient reaches no parameter.)  The reference draws from the IPU's
+// generator; here the mask is a pure function of (seed, training step, shard, call, row, column):
+// Philox-4x32-10 keyed by (seed, step), one word per element, kept when word >> 8 is below
+// `threshold` = round((1 - p) * 2^24).  Forward and backward recompute it, nothing is stored.
+struct DropoutParams {
+    uint32_t threshold;        // 0: no dropout
+    uint32_t seed;
+    const uint32_t* step_key;  // the training step's number, on the device (a graph replays with fixed arguments)
+    uint32_t shard;            // global shard index
+    float scale;               // 1 / (1 - p)
+};
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1);
+
+// Keep bits of columns 4 * col4 .. 4 * col4 + 3 of gathered row r in call `part` (0 head, 1 tail).
+__device__ __forceinline__ uint32_t dropout_keep4(const DropoutParams& dp, uint32_t part, uint32_t r, uint32_t col4) {
+    uint32_t c[4] = {r, col4, (dp.shard << 1) | part, 0x64726f70u};
+    uint32_t k0 = dp.seed, k1 = *dp.step_key;
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        philox_round(c, k0, k1);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    uint32_t bits = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) bits |= ((c[i] >> 8) < dp.threshold ? 1u : 0u) << i;
+    return bits;
+}
+
+// hidden = value + dropout(hidden - value), in place on the hidden rows of each call.  With one
+// feature network both calls start from the same rows (hid_t_in == hid_h) and get their own masks.
+template <class ST>
+__global__ void __launch_bounds__(256)
+k_dropout_hidden(const uint8_t* __restrict__ rows_c, RowLayout L, float* __restrict__ hid_h, const float* __restrict__ hid_t_in,
+                 float* __restrict__ hid_t, int R, DropoutParams dp) {
+    grid_dependency_sync();
+    const int D = (int)L.d, quads = (D + 3) / 4;
+    const int i = (int)(blockIdx.x * blockDim.x + threadIdx.x);
+    if (i >= R * quads) return;
+    const int r = i / quads, q = i - r * quads;
+    const uint8_t* __restrict__ row = rows_c + (size_t)r * L.row_bytes;
+    const uint32_t keep_h = dropout_keep4(dp, 0u, (uint32_t)r, (uint32_t)q), keep_t = dropout_keep4(dp, 1u, (uint32_t)r, (uint32_t)q);
+    for (int u = 0; u < 4; ++u) {
+        const int c = 4 * q + u;
+        if (c >= D) break;
+        const size_t o = (size_t)r * D + c;
+        const float v = load_value<ST>(L, row, c);
+        const float fh_h = hid_h[o] - v, fh_t = hid_t_in[o] - v;
+        hid_h[o] = (keep_h >> u) & 1u ? v + fh_h * dp.scale : v;
+        hid_t[o] = (keep_t >> u) & 1u ? v + fh_t * dp.scale : v;
+    }
+}
+
 // Norm regularisers of the gathered rows (src/poplar_kge.cpp:430-437, 463-465): each of the two
 // entityHidden calls of a step (head part, tail part) adds
 //   w_e * sum_r N(value_r) + w_f * sum_r N(feature_hidden_r) + w_h * sum_r N(hidden_r),
@@ -1194,6 +1252,7 @@ struct RelationRows {
     const float* reg_val;
     const float* reg_h;
     const float* reg_t;
+    DropoutParams drop;  // threshold 0: none.  Masks the gradients of the feature network's outputs.
 };
 
 template <int V, int LANES>
@@ -1375,6 +1434,16 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 gv[u] += rr.reg_val[o + u];
                 gh[u] += rr.reg_h[o + u];
                 if (rr.reg_t) gt[u] += rr.reg_t[o + u];
+            }
+        }
+        if (rr.drop.threshold) {
+            // through the dropout of each call: kept elements pass g / (1 - p)
+            const uint32_t keep_h = dropout_keep4(rr.drop, 0u, (uint32_t)r, (uint32_t)c >> 2), keep_t = dropout_keep4(rr.drop, 1u, (uint32_t)r, (uint32_t)c >> 2);
+#pragma unroll
+            for (int u = 0; u < V; ++u) {
+                const int bit = (c & 3) + u;
+                gh[u] = (keep_h >> bit) & 1u ? gh[u] * rr.drop.scale : 0.f;
+                gt[u] = (keep_t >> bit) & 1u ? gt[u] * rr.drop.scale : 0.f;
             }
         }
         if (V == 4) {

@@ -47,6 +47,7 @@ class StepConfig:
     embedding_regularisation: Tuple[float, float] = (2.0, 0.0)
     feature_regularisation: Tuple[float, float] = (2.0, 0.0)
     hidden_regularisation: Tuple[float, float] = (2.0, 0.0)
+    feature_dropout: float = 0.0  # src/poplar_kge.cpp:459-461
 
     def __post_init__(self) -> None:
         if self.loss_scale is None:
@@ -400,6 +401,7 @@ class Oracle:
             for suffix in ("", "/adam_m", "/adam_v"):
                 self.variables[name + suffix] = np.zeros(shape, dtype)
         self.step = 0
+        self.dropout_mask = None  # callable (training step number, call 0 head / 1 tail) -> bool [n_shard, R, D]
         self.last = {}  # intermediates of the most recent step, for kernel-level checks
 
     # -- state I/O ---------------------------------------------------------
@@ -447,8 +449,18 @@ class Oracle:
         )
         value = value.copy()
         # 2. hidden, lookups, exchange (:676-681, :439-467)
-        hid_h = value + feat @ w_head
-        hid_t = hid_h if cfg.share_feature_networks else value + feat @ w_tail
+        fh_h, fh_t = feat @ w_head, feat @ w_tail
+        keep_h = keep_t = None
+        if cfg.feature_dropout > 0 and cfg.entity_feature_size > 0:
+            # frnn::dropout (src/pag/pag.cpp:596-617): kept with probability 1 - p, scaled by 1 / (1 - p);
+            # each entityHidden call draws its own mask.  The masks come from `dropout_mask(step, part)`
+            # -> bool [n_shard, R, D] (the reference draws them from the IPU's generator).
+            scale = dt(1.0) / (dt(1.0) - dt(_f32(cfg.feature_dropout)))
+            keep_h = self.dropout_mask(self.step + 1, 0) * scale
+            keep_t = self.dropout_mask(self.step + 1, 1) * scale
+            fh_h, fh_t = fh_h * keep_h, fh_t * keep_t
+        hid_h = value + fh_h
+        hid_t = hid_h if cfg.share_feature_networks and keep_h is None else value + fh_t
         heads = np.stack([hid_h[s, head[s]] for s in range(n)])
         send = np.stack([hid_t[s, a2a[s]] for s in range(n)])  # [src, dst, a2a, D]
         tails = all_to_all(send).reshape(n, cfg.n_tail, d)  # [dst, src*a2a, D]
@@ -458,8 +470,8 @@ class Oracle:
         reg_value = np.zeros_like(value)                      # gradient of the gathered values
         reg_fh = [np.zeros_like(value), np.zeros_like(value)]  # gradient of each call's feature-network output
         ls = dt(_f32(cfg.loss_scale))
-        for call, (hid, w) in enumerate(((hid_h, w_head), (hid_t, w_tail))):
-            terms = ((cfg.embedding_regularisation, value, "value"), (cfg.feature_regularisation, feat @ w, "fh"),
+        for call, (hid, fh) in enumerate(((hid_h, fh_h), (hid_t, fh_t))):
+            terms = ((cfg.embedding_regularisation, value, "value"), (cfg.feature_regularisation, fh, "fh"),
                      (cfg.hidden_regularisation, hid, "hidden"))
             for (power, weight), tensor, kind in terms:
                 if weight <= 0:
@@ -500,6 +512,8 @@ class Oracle:
         )
         d_value = d_hid_h + d_hid_t + reg_value
         d_fh_h, d_fh_t = d_hid_h + reg_fh[0], d_hid_t + reg_fh[1]
+        if keep_h is not None:  # backward of the dropout: g / (1 - p) where the output is not zero
+            d_fh_h, d_fh_t = d_fh_h * keep_h * (fh_h != 0), d_fh_t * keep_t * (fh_t != 0)
         losses = losses + reg_loss
         grads = {"relation_embedding": d_rel}
         if cfg.share_feature_networks:

@@ -20,7 +20,7 @@ def engine_settings(cfg: StepConfig, n_step: int = 1, dtype: str = "float32",
         "model.n_shard": cfg.n_shard, "model.n_entity": cfg.n_entity,
         "model.n_relation_type": cfg.n_relation_type, "model.embedding_size": cfg.embedding_size,
         "model.entity_feature_size": cfg.entity_feature_size, "model.feature_mlp_size": 0,
-        "model.feature_dropout": 0.0, "model.share_feature_networks": cfg.share_feature_networks,
+        "model.feature_dropout": float(cfg.feature_dropout), "model.share_feature_networks": cfg.share_feature_networks,
         "model.gamma": float(cfg.gamma), "model.init_scale": 1.0,
         "model.negative_adversarial_scale": float(cfg.negative_adversarial_scale),
         "training.adam_beta_m": cfg.adam_beta_m, "training.adam_beta_v": cfg.adam_beta_v,
@@ -150,9 +150,13 @@ def read_state(engine, cfg: StepConfig, rw_batch: int, n_local: int) -> Dict[str
     return state
 
 
-def make_oracle(cfg: StepConfig, state: Dict[str, np.ndarray], dtype=np.float64) -> Oracle:
+def make_oracle(cfg: StepConfig, state: Dict[str, np.ndarray], dtype=np.float64, seed: int = 1) -> Oracle:
+    """`seed` is the engine's model.seed: with dropout on, the oracle is handed the engine's masks."""
     oracle = Oracle(cfg, dtype)
     oracle.set_state(state)
+    if cfg.feature_dropout > 0:
+        oracle.dropout_mask = lambda step, part: dropout_keep_mask(seed, step, part, cfg.n_shard, cfg.n_remote,
+                                                                   cfg.embedding_size, cfg.feature_dropout)
     return oracle
 
 
@@ -172,14 +176,11 @@ def assert_close(actual, expected, rtol: float, what: str, atol_scale: float = 1
         f"(rtol {rtol}, tensor rms {scale:.3g})")
 
 
-def philox_normal4(seed: int, stream: int, row: np.ndarray, col4: np.ndarray) -> np.ndarray:
-    """Numpy restatement of the engine's counter-based normal generator (csrc/kernels.cuh,
-    philox_normal4): Philox-4x32-10 keyed by (seed, stream), counted by (row, column / 4), then two
-    Box-Muller pairs.  Returns [..., 4] float64 for broadcast ``row`` / ``col4`` arrays."""
-    row, col4 = np.broadcast_arrays(np.asarray(row, np.uint64), np.asarray(col4, np.uint64))
+def philox_4x32_10(counter, key0: int, key1: int):
+    """Philox-4x32 with ten rounds on four uint64 arrays holding 32-bit counters; returns the four words."""
     mask = np.uint64(0xFFFFFFFF)
-    c = [row & mask, col4 & mask, np.full(row.shape, stream, np.uint64), np.full(row.shape, 0x6B676562, np.uint64)]
-    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64((0x9E3779B9 ^ stream) & 0xFFFFFFFF)
+    c = [np.asarray(x, np.uint64) & mask for x in counter]
+    k0, k1 = np.uint64(key0 & 0xFFFFFFFF), np.uint64(key1 & 0xFFFFFFFF)
     m0, m1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
     for _ in range(10):
         p0, p1 = m0 * c[0], m1 * c[2]  # 32 x 32 -> 64 bit products
@@ -187,6 +188,32 @@ def philox_normal4(seed: int, stream: int, row: np.ndarray, col4: np.ndarray) ->
         c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
         k0 = (k0 + np.uint64(0x9E3779B9)) & mask
         k1 = (k1 + np.uint64(0xBB67AE85)) & mask
+    return c
+
+
+def dropout_keep_mask(seed: int, step: int, part: int, n_shard: int, n_rows: int, d: int, p: float) -> np.ndarray:
+    """Numpy restatement of the engine's dropout mask (csrc/kernels.cuh, dropout_keep4): bool
+    [n_shard, n_rows, d], True where the element of gathered row r, column c is kept in training
+    step `step` (counted from 1) by call `part` (0 head, 1 tail)."""
+    threshold = int(round((1.0 - p) * 16777216.0))
+    quads = (d + 3) // 4
+    shard = np.arange(n_shard, dtype=np.uint64)[:, None, None]
+    r = np.arange(n_rows, dtype=np.uint64)[None, :, None]
+    q = np.arange(quads, dtype=np.uint64)[None, None, :]
+    shape = (n_shard, n_rows, quads)
+    words = philox_4x32_10([np.broadcast_to(r, shape), np.broadcast_to(q, shape), np.broadcast_to((shard << np.uint64(1)) | np.uint64(part), shape),
+                            np.full(shape, 0x64726F70, np.uint64)], seed, step)
+    keep = np.stack([(w >> np.uint64(8)) < threshold for w in words], axis=-1)  # [n, R, quads, 4]
+    return keep.reshape(n_shard, n_rows, quads * 4)[:, :, :d]
+
+
+def philox_normal4(seed: int, stream: int, row: np.ndarray, col4: np.ndarray) -> np.ndarray:
+    """Numpy restatement of the engine's counter-based normal generator (csrc/kernels.cuh,
+    philox_normal4): Philox-4x32-10 keyed by (seed, stream), counted by (row, column / 4), then two
+    Box-Muller pairs.  Returns [..., 4] float64 for broadcast ``row`` / ``col4`` arrays."""
+    row, col4 = np.broadcast_arrays(np.asarray(row, np.uint64), np.asarray(col4, np.uint64))
+    c = philox_4x32_10([row, col4, np.full(row.shape, stream, np.uint64), np.full(row.shape, 0x6B676562, np.uint64)],
+                       seed, 0x9E3779B9 ^ stream)
     u = [((x >> np.uint64(8)).astype(np.float64) + 0.5) / 16777216.0 for x in c]
     r0, r1 = np.sqrt(-2.0 * np.log(u[0])), np.sqrt(-2.0 * np.log(u[2]))
     a0, a1 = 2.0 * np.pi * u[1], 2.0 * np.pi * u[3]

@@ -98,6 +98,18 @@ CASES = {
                                                    distance_fn="L1", gamma=3.0, loss_type="logsigmoid",
                                                    embedding_regularisation=(2.5, 0.02), hidden_regularisation=(2.0, 0.04)),
                                     seed=23),
+    # Dropout of the feature network's output: each of the two calls draws its own mask, so the head
+    # and tail rows differ even with one shared network; the oracle is given the engine's masks
+    "dropout_shared": dict(cfg=StepConfig(n_shard=2, n_entity=300, n_relation_type=4, embedding_size=32,
+                                          entity_feature_size=24, batch_size=16, a2a_size=12, score_fn="TransE",
+                                          distance_fn="L2", gamma=6.0, loss_type="softmax", correction_weight=1.0,
+                                          feature_dropout=0.25, feature_regularisation=(2.0, 0.03)),
+                           seed=24, feature_dtype="float16"),
+    "dropout_separate": dict(cfg=StepConfig(n_shard=2, n_entity=200, n_relation_type=4, embedding_size=18,
+                                            entity_feature_size=12, batch_size=8, a2a_size=6, score_fn="DistMult",
+                                            distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
+                                            feature_dropout=0.5),
+                             seed=25),
     "single_shard": dict(cfg=StepConfig(n_shard=1, n_entity=400, n_relation_type=5, embedding_size=64,
                                         entity_feature_size=32, batch_size=64, a2a_size=96, score_fn="TransE",
                                         distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
@@ -200,7 +212,7 @@ def test_exchange_routing_is_bit_exact():
     engine.close()
 
 
-@pytest.mark.parametrize("name", ["config1_transe_l1", "transe_l2_softmax_features", "complex_softmax"])
+@pytest.mark.parametrize("name", ["config1_transe_l1", "transe_l2_softmax_features", "complex_softmax", "dropout_shared"])
 def test_step_loop_and_graph_replay(name):
     """Several steps per call, twice: replaying the captured graph gives bit-identical results to
     plain launches, and both follow the oracle."""

@@ -126,6 +126,7 @@ VARIANTS = [
          feature_regularisation=(2.0, 0.03), hidden_regularisation=(1.0, 0.01)),
     dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
          embedding_regularisation=(2.0, 0.05), feature_regularisation=(2.5, 0.01), hidden_regularisation=(3.0, 0.02)),
+    dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", feature_dropout=0.3, feature_regularisation=(2.0, 0.03)),
 ]
 
 
@@ -140,6 +141,8 @@ def test_hand_derived_backward_matches_autograd(variant):
     batch = random_batch(cfg, 1, 6)
     oracle = Oracle(cfg, np.float64)
     oracle.set_state(state)
+    masks = np.random.RandomState(11).uniform(size=(2, cfg.n_shard, cfg.n_remote, cfg.embedding_size)) >= cfg.feature_dropout
+    oracle.dropout_mask = lambda step, part: masks[part]
     losses = oracle.train_step(1e-3, *(batch[k][:, 0] for k in BATCH_KEYS))
 
     n, d = cfg.n_shard, cfg.embedding_size
@@ -152,7 +155,11 @@ def test_hand_derived_backward_matches_autograd(variant):
     w = {name: t(state[name]).requires_grad_(True) for name in cfg.projection_names}
     w_h = w[cfg.projection_names[0]]
     w_t = w[cfg.projection_names[-1]]
-    hid_h, hid_t = value + feat @ w_h, value + feat @ w_t
+    fh_h, fh_t = feat @ w_h, feat @ w_t
+    if cfg.feature_dropout > 0:  # kept with probability 1 - p, scaled by 1 / (1 - p); a mask per call
+        scale = 1.0 / (1.0 - float(np.float32(cfg.feature_dropout)))
+        fh_h, fh_t = fh_h * t(masks[0]) * scale, fh_t * t(masks[1]) * scale
+    hid_h, hid_t = value + fh_h, value + fh_t
     heads = torch.stack([hid_h[s, idx["head"][s]] for s in range(n)])
     send = torch.stack([hid_t[s, idx["a2a"][s]] for s in range(n)])
     tails = send.transpose(0, 1).reshape(n, cfg.n_tail, d)
@@ -163,8 +170,8 @@ def test_hand_derived_backward_matches_autograd(variant):
 
     def regularisers(s):  # both entityHidden calls add their three terms (src/poplar_kge.cpp:463-465)
         out = 0
-        for hid, w_part in ((hid_h, w_h), (hid_t, w_t)):
-            for (power, weight), x in ((cfg.embedding_regularisation, value[s]), (cfg.feature_regularisation, feat[s] @ w_part),
+        for hid, fh in ((hid_h, fh_h), (hid_t, fh_t)):
+            for (power, weight), x in ((cfg.embedding_regularisation, value[s]), (cfg.feature_regularisation, fh[s]),
                                        (cfg.hidden_regularisation, hid[s])):
                 if weight > 0:
                     out = out + float(np.float32(weight)) * norm_sum(x, power)
