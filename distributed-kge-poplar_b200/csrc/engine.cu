@@ -132,8 +132,7 @@ Config parse_config(const SettingMap& s) {
     else if (score_fn == "DistMult") c.score_fn = SCORE_DISTMULT;
     else if (score_fn == "ComplEx") c.score_fn = SCORE_COMPLEX;
     else if (score_fn == "RotatE") c.score_fn = SCORE_ROTATE;
-    else if (score_fn == "TransH")
-        fail(KGE_INVALID_ARGUMENT, msg() << "'model.score_fn' '" << score_fn << "' is not supported by this engine");
+    else if (score_fn == "TransH") c.score_fn = SCORE_TRANSH;
     else
         fail(KGE_INVALID_ARGUMENT, msg() << "'model.score_fn' must be one of 'TransE', 'ComplEx', 'RotatE', "
                                             "'TransH', or 'DistMult', not '" << score_fn << "'");
@@ -143,6 +142,8 @@ Config parse_config(const SettingMap& s) {
     else
         fail(KGE_INVALID_ARGUMENT, msg() << "'model.distance_fn' must be one of 'L1', 'L1_old', 'L2', 'L2_old' "
                                             "or 'MatMul', not '" << distance_fn << "'");
+    // TransH's score is the L1 form whatever the setting says (src/poplar_kge.cpp:552-565)
+    if (c.score_fn == SCORE_TRANSH) c.dist_fn = DIST_L1;
     if (loss == "logsigmoid") c.loss_fn = LOSS_LOGSIGMOID;
     else if (loss == "softmax") c.loss_fn = LOSS_SOFTMAX;
     else
@@ -168,6 +169,7 @@ Config parse_config(const SettingMap& s) {
     if (c.f) divisible(c.share_networks ? "feature_projection" : "head_feature_projection", c.f, c.d);
     for (auto& kv : c.lr_modifiers) {
         const bool known = kv.first == "entity_embedding" || kv.first == "relation_embedding" ||
+                           (c.score_fn == SCORE_TRANSH && kv.first == "relation_normal") ||
                            (c.share_networks ? kv.first == "feature_projection"
                                              : (kv.first == "head_feature_projection" ||
                                                 kv.first == "tail_feature_projection"));
@@ -233,7 +235,8 @@ size_t Engine::arena_offset_shard(unsigned local, int which) const {
 size_t Engine::arena_offset_dense_recv() const { return arena_offset_predict(3); }
 size_t Engine::arena_offset_predict(int which) const {
     // gathered queries [n_shard, hr, D] | result scores | result rows, each [n_local, n_shard, hr, n_best]
-    const size_t queries = round_up((size_t)cfg_.n_shard * cfg_.predict_hr * cfg_.d * sizeof(float), 256);
+    // (TransH: the predicted tails, then the unit normals, src/poplar_kge.cpp:823-828)
+    const size_t queries = round_up((size_t)(cfg_.score_fn == SCORE_TRANSH ? 2 : 1) * cfg_.n_shard * cfg_.predict_hr * cfg_.d * sizeof(float), 256);
     const size_t results = round_up((size_t)n_local_ * cfg_.n_shard * cfg_.predict_hr * cfg_.predict_n_best * 4, 256);
     const size_t base = arena_offset_shard(n_local_, 0);
     return base + (which == 0 ? 0 : which == 1 ? queries : which == 2 ? queries + results : queries + 2 * results);
@@ -276,7 +279,8 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     dense_bounds_[1] = (size_t)cfg_.n_relation_type * cfg_.d;
     dense_bounds_[2] = dense_bounds_[1] + (cfg_.n_net() >= 1 ? proj_elems_ : 0);
     dense_bounds_[3] = dense_bounds_[2] + (cfg_.n_net() >= 2 ? proj_elems_ : 0);
-    n_dense_ = dense_bounds_[3];
+    dense_bounds_[4] = dense_bounds_[3] + (cfg_.score_fn == SCORE_TRANSH ? (size_t)cfg_.n_relation_type * cfg_.d : 0);
+    n_dense_ = dense_bounds_[4];
     auto modifier = [&](const std::string& name) {
         auto it = cfg_.lr_modifiers.find(name);
         return it == cfg_.lr_modifiers.end() ? 1.0f : it->second;
@@ -304,11 +308,15 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     add_variable("relation_embedding", cfg_.n_relation_type, cfg_.score_fn == SCORE_ROTATE ? cfg_.d / 2 : cfg_.d, 0);
     for (size_t i = 0; i < proj_names.size(); ++i)
         add_variable(proj_names[i], cfg_.f, cfg_.d, cfg_.f ? dense_bounds_[1 + i] : n_dense_);
+    if (cfg_.score_fn == SCORE_TRANSH) {  // src/poplar_kge.cpp:252-255
+        add_variable("relation_normal", cfg_.n_relation_type, cfg_.d, dense_bounds_[3]);
+        dense_lr_mod_[3] = modifier("relation_normal");
+    }
     variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3});
 
     // Every process owns (reduces and updates) an equal share of the rows of the dense vector, dealt
     // out in turn: row r belongs to process r % world, as its row r / world.
-    const size_t dense_rows = cfg_.n_relation_type + (size_t)cfg_.n_net() * cfg_.f;
+    const size_t dense_rows = cfg_.n_relation_type + (size_t)cfg_.n_net() * cfg_.f + (cfg_.score_fn == SCORE_TRANSH ? cfg_.n_relation_type : 0);
     dense_chunk_rows_ = std::max<size_t>(1, (dense_rows + cfg_.world - 1) / cfg_.world);
     dense_chunk_ = dense_chunk_rows_ * cfg_.d;
     own_rows_ = dense_rows > cfg_.rank ? (dense_rows - cfg_.rank + cfg_.world - 1) / cfg_.world : 0;
@@ -333,6 +341,11 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     planes_ = cfg_.tensor_cores && cfg_.d % 4 == 0 && cfg_.batch_size % 4 == 0 && cfg_.n_tail() % 4 == 0 &&
               cfg_.n_remote() <= (unsigned)tc::kRouteMaxLookups;
     if (const char* v = std::getenv("KGE_PLANE_CONTRACTIONS")) planes_ = planes_ && std::atoi(v) != 0;
+    if (cfg_.score_fn == SCORE_TRANSH) {
+        planes_ = false;  // its score has no contraction form: the step of separate kernels
+        if (transh_score_smem() > 200 * 1024) fail(KGE_INVALID_ARGUMENT, "TransH: model.embedding_size is limited to 1600");
+        KGE_CUDA(cudaFuncSetAttribute(k_transh_score, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)transh_score_smem()));
+    }
     // fp16 features are widened into rows of their own; the lower plane of fp32 features keeps the
     // stride of the rows whose feature part is its upper plane (one stride per operand)
     bf16_planes_ = planes_ && cfg_.value_bf16 && cfg_.dist_fn == DIST_DOT && cfg_.d % 8 == 0 && cfg_.n_tail() % 8 == 0 && cfg_.batch_size % 8 == 0 &&
@@ -392,6 +405,13 @@ void Engine::allocate() {
         b.d_pred = (float*)device_alloc((size_t)B * D * 4);
         b.d_head = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
         b.d_relrow = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
+        if (cfg_.score_fn == SCORE_TRANSH) {
+            b.nrm = (float*)device_alloc((size_t)B * D * 4);
+            b.d_nrm = (float*)device_alloc((size_t)B * D * 4);
+            b.d_normrow = (float*)device_alloc((size_t)B * D * 4);
+            b.pair_s = (float*)device_alloc((size_t)B * T * 4);
+            b.pair_u = (float*)device_alloc((size_t)B * T * 4);
+        }
         if (cfg_.regularised()) {
             b.reg_val = (float*)device_alloc((size_t)R * D * 4);
             b.reg_h = (float*)device_alloc((size_t)R * D * 4);
@@ -1370,7 +1390,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         da.n_own = own_rows_;
         da.row_width = D;
         for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
-        for (int i = 0; i < 3; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
+        for (int i = 0; i < 4; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
         da.step_size = d_step_size_ + step;
         da.ap = adam_;
         const unsigned blocks = (unsigned)std::min<size_t>((own_rows_ * D / 4 + 255) / 256, 148 * 8);
@@ -1388,6 +1408,8 @@ void Engine::launch_one_step(unsigned step) {
     const float* rel_table = dense_;
     const float* W0 = cfg_.n_net() >= 1 ? dense_ + dense_bounds_[1] : nullptr;
     const float* W1 = two_nets ? dense_ + dense_bounds_[2] : W0;
+    const bool transh = cfg_.score_fn == SCORE_TRANSH;
+    const float* normal_table = dense_ + dense_bounds_[3];
 
     LossParams lp{};
     lp.loss_fn = cfg_.loss_fn;
@@ -1448,14 +1470,18 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
         if (dropout_on()) launch_dropout(l, step, rows_c);
+        const int route_fn = transh ? SCORE_TRANSE : cfg_.score_fn;  // TransH: the tails are routed, the prediction follows
         if (vec)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
+                                                                      (int)B, (int)D, route_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
         else
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<1>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                                       b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size,
-                                                                      (int)B, (int)D, cfg_.score_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
+                                                                      (int)B, (int)D, route_fn, sync, (float* const*)nullptr, (float*)nullptr, 0)));
+        if (transh)
+            KGE_LAUNCH("transh_predict", KGE_CUDA(launch_dependent(k_transh_predict, dim3(B), dim3(64), 0, stream_, b.hid_h, head, relation, rel_table,
+                                                                   normal_table, b.pred, b.nrm, (int)D)));
         if (cfg_.regularised()) launch_regularise(l, rows_c);
     }
     KGE_CUDA(cudaGetLastError());
@@ -1474,7 +1500,11 @@ void Engine::launch_one_step(unsigned step) {
         dim3 bgrid(ceil_div(B, 32) + ceil_div(T, 32), ceil_div(D, 64));
         const bool tc_score = cfg_.tensor_cores && cfg_.dist_fn == DIST_DOT;
         const bool tc_bwd = cfg_.tensor_cores && cfg_.dist_fn != DIST_L1;
-        if (tc_score) {
+        if (transh) {
+            const dim3 grid(ceil_div(B, kTranshRows), std::max(1u, std::min(ceil_div(T, 8), 2 * 148 / std::max(1u, ceil_div(B, kTranshRows)))));
+            KGE_LAUNCH("score", KGE_CUDA(launch_dependent(k_transh_score, grid, dim3(256), transh_score_smem(), stream_, b.pred, b.nrm, b.tails, b.raw,
+                                                          b.pair_s, b.pair_u, (int)B, (int)T, (int)D, sync)));
+        } else if (tc_score) {
             tc::GemmArgs g{};
             g.A = tc::make_operand(b.pred, (long long)D * 4, false, false);
             g.B = tc::make_operand(b.tails, (long long)D * 4, false, false);
@@ -1514,6 +1544,10 @@ void Engine::launch_one_step(unsigned step) {
             g.k_per_split = h.k_per_split;
             launch_tc("score_bwd", both, 2, tc_splits((ceil_div(B, 128) + ceil_div(T, 128)) * ceil_div(D, 64), std::min(B, T)), false, l2,
                       -1, XCHG_TAIL_GRADS);
+        } else if (transh) {
+            KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_transh_bwd, dim3(B + T), dim3(128), 0, stream_, b.pred, b.nrm, b.tails, b.coeff, b.pair_s,
+                                                              b.pair_u, b.d_pred, b.d_nrm, b.grad_dst, (int)cfg_.a2a_size, (int)B, (int)T, (int)D)));
+            launch_exchange_signal(XCHG_TAIL_GRADS);
         } else {
         switch (cfg_.dist_fn) {
             case DIST_L1: KGE_LAUNCH("score_bwd", KGE_CUDA(launch_dependent(k_pair_bwd<DIST_L1>, dim3(bgrid), dim3(128), 0, stream_, pa))); break;
@@ -1522,7 +1556,21 @@ void Engine::launch_one_step(unsigned step) {
         }
         launch_exchange_signal(XCHG_TAIL_GRADS);
         }
-        if (cfg_.score_fn != SCORE_TRANSE)
+        if (transh) {
+            KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_transh_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.d_nrm, b.hid_h, head, relation,
+                                                             normal_table, b.nrm, b.d_head, b.d_relrow, b.d_normrow, (int)D)));
+            // the normals' rows of the partial dense gradient, behind the relation table and the projections
+            const size_t sidx = (size_t)l * cfg_.n_step + step;
+            const int normal_row0 = (int)(n_rel + cfg_.n_net() * F);
+            if (vec)
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
+                                                b.d_normrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1, normal_row0)));
+            else
+                KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, stream_,
+                                                b.d_normrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1, normal_row0)));
+        } else if (cfg_.score_fn != SCORE_TRANSE)
             KGE_LAUNCH("pred_bwd", KGE_CUDA(launch_dependent(k_pred_bwd, dim3(B), dim3(64), 0, stream_, b.d_pred, b.hid_h, head, relation, rel_table, b.d_head,
                                                                      b.d_relrow, (int)D, cfg_.score_fn)));
     }
@@ -1539,11 +1587,11 @@ void Engine::launch_one_step(unsigned step) {
             if (vec)
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel), dim3(64 * kRelationLanes), 0, side,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1)));
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1, 0)));
             else
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel), dim3(64 * kRelationLanes), 0, side,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
-                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1)));
+                                                (int)D, b.proj_partial, 0, 1, proj_elems_, b.dense_dst, (int)cfg_.world, sync, -1, 0)));
         }
         side_end(0);
         side_streams_ = saved;
@@ -1631,12 +1679,12 @@ void Engine::launch_one_step(unsigned step) {
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<4>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
-                                                proj_elems_, b.dense_dst, (int)cfg_.world, sync, (int)XCHG_DENSE_PARTIALS)));
+                                                proj_elems_, b.dense_dst, (int)cfg_.world, sync, (int)XCHG_DENSE_PARTIALS, 0)));
             else
                 KGE_LAUNCH("dense_partial", KGE_CUDA(launch_dependent(k_dense_partial<1>, dim3(n_rel + proj_blocks), dim3(64 * kRelationLanes), 0, stream_,
                                                 b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), (int)n_rel,
                                                 (int)D, b.proj_partial, (int)cfg_.n_net(), proj_splits_,
-                                                proj_elems_, b.dense_dst, (int)cfg_.world, sync, (int)XCHG_DENSE_PARTIALS)));
+                                                proj_elems_, b.dense_dst, (int)cfg_.world, sync, (int)XCHG_DENSE_PARTIALS, 0)));
         }
     }
     KGE_CUDA(cudaGetLastError());
@@ -1656,7 +1704,7 @@ void Engine::launch_one_step(unsigned step) {
         da.n_own = own_rows_;
         da.row_width = D;
         for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
-        for (int i = 0; i < 3; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
+        for (int i = 0; i < 4; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
         da.step_size = d_step_size_ + step;
         da.ap = adam_;
         // The parameter itself is read from this process's own replica (entry `rank`).
@@ -1905,6 +1953,11 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
                                                                 nullptr, p_head_hidden_, nullptr)));
         for (unsigned p = 0; p < cfg_.world; ++p) {
             float* dst = (float*)(peer_arena_[p] + arena_offset_predict(0)) + (size_t)(shard0_ + l) * hr * D;
+            if (cfg_.score_fn == SCORE_TRANSH) {
+                KGE_LAUNCH("predict_query", k_transh_predict<<<(unsigned)hr, 64, 0, stream_>>>(
+                                                p_head_hidden_, d_iota_, d_rel + l * hr, dense_, dense_ + dense_bounds_[3], dst, dst + Q * D, (int)D));
+                continue;
+            }
             if (vec)
                 KGE_LAUNCH("predict_query", k_route<4><<<(unsigned)hr, 64, 0, stream_>>>(
                                                 p_head_hidden_, p_head_hidden_, nullptr, d_iota_, d_rel + l * hr, dense_, nullptr,
@@ -1940,6 +1993,11 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
             KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<hgrid, 256, 0, stream_>>>(
                                                                     b.table, layout_, nullptr, start, (int)c, W_tail, nullptr,
                                                                     p_chunk_hidden_, nullptr)));
+            if (cfg_.score_fn == SCORE_TRANSH) {
+                const dim3 grid(ceil_div((unsigned)Q, kTranshRows), std::max(1u, std::min(ceil_div(c, 8u), 2 * 148 / std::max(1u, ceil_div((unsigned)Q, kTranshRows)))));
+                KGE_LAUNCH("predict_score", k_transh_score<<<grid, 256, transh_score_smem(), stream_>>>(
+                                                queries, queries + Q * D, p_chunk_hidden_, p_raw_, nullptr, nullptr, (int)Q, (int)c, (int)D, ExchangeSync{}));
+            } else
             KGE_LAUNCH("predict_score", KGE_CUDA(launch_score(cfg_.dist_fn, queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D, stream_)));
             KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div((unsigned)Q, 4), 128, 0, stream_>>>(
                                            p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp));

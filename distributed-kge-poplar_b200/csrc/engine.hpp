@@ -12,6 +12,7 @@
 #include "kernels.cuh"
 #include "tc_gemm.cuh"
 #include "tc_planes.cuh"
+#include "transh.cuh"
 
 namespace kge {
 
@@ -112,6 +113,9 @@ class Engine {
         float *hid_h = nullptr, *hid_t = nullptr, *pred = nullptr, *raw = nullptr, *coeff = nullptr;
         float *d_pred = nullptr, *d_head = nullptr, *d_relrow = nullptr;
         float *d_hid_h = nullptr, *d_hid_t = nullptr, *proj_partial = nullptr, *loss_rows = nullptr;
+        // TransH: unit normals of the batch's relations, n_i . t_j and the signs' sums along the normal
+        // ([B, T]), gradients of the normals from the scores, per-triple gradients of the raw normals
+        float *nrm = nullptr, *pair_s = nullptr, *pair_u = nullptr, *d_nrm = nullptr, *d_normrow = nullptr;
         float *reg_val = nullptr, *reg_h = nullptr, *reg_t = nullptr, *reg_loss_rows = nullptr;  // regularisers' terms, [R, D] and [R]
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
@@ -224,8 +228,8 @@ class Engine {
     float** d_replicas_ = nullptr;        // [world]
 
     // dense parameters: relation table | projection(s)
-    size_t n_dense_ = 0, proj_elems_ = 0, dense_bounds_[4] = {0, 0, 0, 0};
-    float dense_lr_mod_[3] = {1.f, 1.f, 1.f};
+    size_t n_dense_ = 0, proj_elems_ = 0, dense_bounds_[5] = {0, 0, 0, 0, 0};  // relation table | projection(s) | TransH normals
+    float dense_lr_mod_[4] = {1.f, 1.f, 1.f, 1.f};
     float entity_lr_mod_ = 1.f;
     float *dense_ = nullptr, *dense_m_ = nullptr, *dense_v_ = nullptr;
     float* dense_lo_ = nullptr;      // lower TF32 plane of the dense vector (same layout, inside the arena)
@@ -243,6 +247,7 @@ class Engine {
     uint4* d_heavy_parts_ = nullptr;
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
     unsigned* d_loss_counter_ = nullptr;
+    size_t transh_score_smem() const { return (size_t)2 * kTranshRows * cfg_.d * sizeof(float); }
     uint32_t* d_step_key_ = nullptr;   // [n_step] numbers of the staged training steps (keys of the dropout masks)
     bool dropout_on() const { return cfg_.dropout > 0.f && cfg_.f > 0; }
     DropoutParams dropout_params(unsigned l, unsigned step) const;

@@ -16,9 +16,9 @@
 
 namespace kge {
 
-enum ScoreFn : int { SCORE_TRANSE = 0, SCORE_DISTMULT = 1, SCORE_COMPLEX = 2, SCORE_ROTATE = 3 };
-// TransE and RotatE score by gamma - distance (src/poplar_kge.cpp:492-499, 532-537); the others by the raw product.
-__host__ __device__ inline bool score_is_gamma_minus_distance(int score_fn) { return score_fn == SCORE_TRANSE || score_fn == SCORE_ROTATE; }
+enum ScoreFn : int { SCORE_TRANSE = 0, SCORE_DISTMULT = 1, SCORE_COMPLEX = 2, SCORE_ROTATE = 3, SCORE_TRANSH = 4 };
+// TransE, RotatE and TransH score by gamma - distance (src/poplar_kge.cpp:492-499, 532-537, 552-565); the others by the raw product.
+__host__ __device__ inline bool score_is_gamma_minus_distance(int score_fn) { return score_fn == SCORE_TRANSE || score_fn == SCORE_ROTATE || score_fn == SCORE_TRANSH; }
 
 // RotatE's relation row holds one angle per complex pair.  The reference casts the angles to
 // float16 and takes sine and cosine in float16 (src/poplar_kge.cpp:522-525): restated as the
@@ -1684,7 +1684,7 @@ __global__ void __launch_bounds__(64 * kRelationLanes)
 k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__ rel_perm,
                 const uint32_t* __restrict__ rel_off, int n_rel, int D,
                 const float* __restrict__ proj_partial, int n_net, int splits, size_t proj_elems,
-                float* const* __restrict__ dense_dst, int n_owner, ExchangeSync sync, int signal_kind) {
+                float* const* __restrict__ dense_dst, int n_owner, ExchangeSync sync, int signal_kind, int row_offset) {
     grid_dependency_sync();
     __shared__ float part[kRelationLanes][64 * V];
     __shared__ uint32_t s_perm[64 * kRelationLanes];
@@ -1695,8 +1695,9 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
         const int rho = blockIdx.x, col = threadIdx.x & 63, lane = threadIdx.x >> 6;
         const uint32_t q0 = rel_off[rho], q1 = rel_off[rho + 1];
         // the row goes to the process that owns this slice of the dense vector
-        const int owner = rho % n_owner;
-        float* __restrict__ dst_row = dense_dst[owner] + (size_t)(rho / n_owner) * D;
+        // (row_offset: where these rows begin in the dense vector; 0 for the relation table)
+        const int owner = (rho + row_offset) % n_owner;
+        float* __restrict__ dst_row = dense_dst[owner] + (size_t)((rho + row_offset) / n_owner) * D;
         if (q0 == q1) {
             for (int c = threadIdx.x; c < D; c += blockDim.x) dst_row[c] = 0.f;
             exchange_signal(sync, signal_kind, gridDim.x);
@@ -1780,7 +1781,7 @@ struct DenseUpdateArgs {
     // row_width elements each; its j-th row is row j of every slot.
     size_t n_own, row_width;
     size_t bounds[4];       // parameter p covers the elements [bounds[p], bounds[p+1])
-    float lr_modifier[3];
+    float lr_modifier[4];
     const float* step_size;
     AdamParams ap;
     ExchangeSync sync;
@@ -1800,7 +1801,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
     exchange_wait(a.sync, XCHG_DENSE_PARTIALS);  // every process's partial gradients are complete
     const float base_alpha = *a.step_size;
     const size_t W = a.row_width, total = a.n_own * W;
-    const bool vec = ((W | a.bounds[1] | a.bounds[2]) & 3) == 0;
+    const bool vec = ((W | a.bounds[1] | a.bounds[2] | a.bounds[3]) & 3) == 0;
     if (vec) {
         for (size_t le = 4 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x); le < total; le += 4 * (size_t)gridDim.x * blockDim.x) {
             const size_t j = le / W, e = (j * a.n_replica + self) * W + (le - j * W);  // slot index -> dense index
@@ -1810,7 +1811,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
                 const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + le);
                 g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
             }
-            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
+            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : (e < a.bounds[3] ? 2 : 3));
             const float alpha = base_alpha * a.lr_modifier[p];
             float4 x = *reinterpret_cast<const float4*>(a.replicas[self] + e);
             float4 m = *reinterpret_cast<const float4*>(a.adam_m + e), v = *reinterpret_cast<const float4*>(a.adam_v + e);
@@ -1831,7 +1832,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
             const size_t j = le / W, e = (j * a.n_replica + self) * W + (le - j * W);
             float g = 0.f;
             for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][le];
-            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : 2);
+            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : (e < a.bounds[3] ? 2 : 3));
             const float alpha = base_alpha * a.lr_modifier[p];
             float m = a.adam_m[e], v = a.adam_v[e];
             const float x = dense_adam(a.replicas[self][e], g, m, v, alpha, a.ap);

@@ -490,6 +490,8 @@ class Engine:
         else:
             relation = self.random_normal(rel_shape)
         self.write_variable("relation_embedding", (self.init_scale * relation).astype(np.float32))
+        if m.score_fn == "TransH":  # the hyperplane normals (src/python/poplar_kge.py:643-650)
+            self.write_variable("relation_normal", (self.init_scale * self.random_normal(rel_shape)).astype(np.float32))
         prefixes = [""] if m.share_feature_networks else ["head_", "tail_"]
         for prefix in prefixes:
             w = self.random_normal((m.entity_feature_size, m.embedding_size))

@@ -236,6 +236,12 @@ def predict_tail(cfg: StepConfig, h: np.ndarray, r: np.ndarray) -> np.ndarray:
         re, im = h[..., :half], h[..., half:]
         sin, cos = _rotate_sin_cos(r, h.dtype)
         return np.concatenate([re * cos - im * sin, im * cos + re * sin], axis=-1)
+    if cfg.score_fn == "TransH":  # :539-550: r = relation row | normal row; returns unit normal | predicted tail
+        d = h.shape[-1]
+        rel, w = r[..., :d], r[..., d:]
+        n = w / np.sqrt(np.sum(w * w, axis=-1, keepdims=True))
+        projected = h - n * np.sum(n * h, axis=-1, keepdims=True)
+        return np.concatenate([n, projected + rel], axis=-1)
     raise ValueError(f"score_fn {cfg.score_fn!r} is not covered by the oracle")
 
 
@@ -276,7 +282,41 @@ def predict_tail_grad(cfg: StepConfig, h, r, dp) -> Tuple[np.ndarray, np.ndarray
         via_cos = f16(-d_cos.astype(np.float64) * f16(sin).astype(np.float64))
         d_theta = f16(via_sin.astype(np.float64) + via_cos.astype(np.float64)).astype(h.dtype)
         return dh, d_theta
+    if cfg.score_fn == "TransH":  # backward of :539-550; dp = d unit normal | d predicted tail
+        d = h.shape[-1]
+        w = r[..., d:]
+        norm = np.sqrt(np.sum(w * w, axis=-1, keepdims=True))
+        n = w / norm
+        d_n, d_pt = dp[..., :d], dp[..., d:]
+        a = np.sum(n * h, axis=-1, keepdims=True)
+        b = np.sum(n * d_pt, axis=-1, keepdims=True)
+        d_h = d_pt - n * b
+        d_n = d_n - a * d_pt - h * b
+        d_w = (d_n - n * np.sum(n * d_n, axis=-1, keepdims=True)) / norm  # through w / |w|
+        return d_h, np.concatenate([d_pt, d_w], axis=-1)
     raise ValueError(cfg.score_fn)
+
+
+def transh_distance(p: np.ndarray, tails: np.ndarray):
+    """sum_k |pt_ik - (t_jk - n_ik (n_i . t_j))| (src/poplar_kge.cpp:552-565) for p = unit normal |
+    predicted tail; also the per-pair element differences' signs and the projections n_i . t_j."""
+    d = tails.shape[-1]
+    n, pt = p[..., :d], p[..., d:]
+    s = n @ tails.T  # [B, T]
+    e = pt[:, None, :] - tails[None, :, :] + n[:, None, :] * s[:, :, None]
+    return np.sum(np.abs(e), axis=-1), np.sign(e), s
+
+
+def transh_distance_grad(p: np.ndarray, tails: np.ndarray, g: np.ndarray):
+    """Gradients of transh_distance times g [B, T] with respect to p [B, 2D] and tails [T, D]."""
+    d = tails.shape[-1]
+    n = p[..., :d]
+    _, sg, s = transh_distance(p, tails)
+    u = np.einsum("ijk,ik->ij", sg, n)  # the signs' sum along the normal
+    d_pt = np.einsum("ij,ijk->ik", g, sg)
+    d_n = np.einsum("ij,ijk->ik", g * s, sg) + (g * u) @ tails
+    d_t = -np.einsum("ij,ijk->jk", g, sg) + (g * u).T @ n
+    return np.concatenate([d_n, d_pt], axis=-1), d_t
 
 
 def _distance(cfg: StepConfig, a, b):  # src/poplar_kge.cpp:469-486
@@ -303,6 +343,9 @@ def score(cfg: StepConfig, p: np.ndarray, tails: np.ndarray):
     TransE: gamma - distance (:492-499).  DistMult / ComplEx: distance(p, tails)
     as is (:512-514, :571-573), normally with distance_fn "MatMul".
     """
+    if cfg.score_fn == "TransH":  # :552-565, whatever distance_fn says
+        dist = transh_distance(p, tails)[0]
+        return p.dtype.type(_f32(cfg.gamma)) - dist, dist
     dist = _distance(cfg, p, tails)
     if cfg.score_fn in ("TransE", "RotatE"):  # :492-499, :532-537
         return p.dtype.type(_f32(cfg.gamma)) - dist, dist
@@ -310,6 +353,8 @@ def score(cfg: StepConfig, p: np.ndarray, tails: np.ndarray):
 
 
 def score_grad(cfg: StepConfig, p, tails, dist, g):
+    if cfg.score_fn == "TransH":
+        return transh_distance_grad(p, tails, -g)
     if cfg.score_fn in ("TransE", "RotatE"):
         g = -g
     return _distance_grad(cfg, p, tails, dist, g)
@@ -395,6 +440,8 @@ class Oracle:
         self.variables: Dict[str, np.ndarray] = {}
         # RotatE's relations are angles, one per complex pair (src/poplar_kge.cpp:248-251)
         shapes = {"relation_embedding": (cfg.n_relation_type, d // 2 if cfg.score_fn == "RotatE" else d)}
+        if cfg.score_fn == "TransH":  # src/poplar_kge.cpp:252-255
+            shapes["relation_normal"] = (cfg.n_relation_type, d)
         for name in cfg.projection_names:
             shapes[name] = (f, d)
         for name, shape in shapes.items():
@@ -423,6 +470,13 @@ class Oracle:
 
     # -- training ----------------------------------------------------------
 
+    def _relation_rows(self) -> np.ndarray:
+        """The rows predict_tail gathers: the relation embedding, for TransH followed by the normal."""
+        rel = self.variables["relation_embedding"]
+        if self.cfg.score_fn == "TransH":
+            return np.concatenate([rel, self.variables["relation_normal"]], axis=-1)
+        return rel
+
     def _projection(self, part: str) -> str:
         if self.cfg.share_feature_networks:
             return "feature_projection"
@@ -435,7 +489,7 @@ class Oracle:
         remote, a2a, head, relation, tail = (
             np.asarray(x).astype(np.int64) for x in (remote, a2a, head, relation, tail)
         )
-        rel = self.variables["relation_embedding"]
+        rel = self._relation_rows()
         w_head = self.variables[self._projection("head")]
         w_tail = self.variables[self._projection("tail")]
 
@@ -516,6 +570,8 @@ class Oracle:
             d_fh_h, d_fh_t = d_fh_h * keep_h * (fh_h != 0), d_fh_t * keep_t * (fh_t != 0)
         losses = losses + reg_loss
         grads = {"relation_embedding": d_rel}
+        if cfg.score_fn == "TransH":
+            grads = {"relation_embedding": d_rel[:, :d], "relation_normal": d_rel[:, d:]}
         if cfg.share_feature_networks:
             grads["feature_projection"] = np.einsum("srf,srd->fd", feat, d_fh_h + d_fh_t)
         else:
@@ -578,9 +634,7 @@ class Oracle:
         q = np.asarray(shard_idx_relation).astype(np.int64)
         hid_h = self.hidden_all("head")
         hid_t = self.hidden_all("tail").reshape(-1, cfg.embedding_size)
-        pred = predict_tail(
-            cfg, hid_h[q[:, 0], q[:, 1]], self.variables["relation_embedding"][q[:, 2]]
-        )
+        pred = predict_tail(cfg, hid_h[q[:, 0], q[:, 1]], self._relation_rows()[q[:, 2]])
         scores, _ = score(cfg, pred, hid_t)
         valid = np.zeros((cfg.n_shard, cfg.n_entity), bool)
         for s, count in enumerate(shard_to_count):

@@ -69,14 +69,18 @@ def random_state(cfg: StepConfig, seed: int, fp16_features: bool = False, warm: 
         state["relation_embedding"] = (rng.normal(size=(cfg.n_relation_type, d)) / np.sqrt(d)).astype(np.float32)
     for name in cfg.projection_names:
         state[name] = (rng.normal(size=(f, d)) / np.sqrt(max(f, 1)) / np.sqrt(d)).astype(np.float32)
-    for name in ("relation_embedding",) + cfg.projection_names:
+    dense_names = ("relation_embedding",) + cfg.projection_names
+    if cfg.score_fn == "TransH":  # hyperplane normals, normalised on use
+        state["relation_normal"] = (np.random.RandomState(seed + 7919).normal(size=(cfg.n_relation_type, d)) / np.sqrt(d)).astype(np.float32)
+        dense_names += ("relation_normal",)
+    for name in dense_names:
         state[name + "/adam_m"] = np.zeros_like(state[name])
         state[name + "/adam_v"] = np.zeros_like(state[name])
     if warm:
         scale = float(cfg.loss_scale) * 1e-3
         rows[..., d : 2 * d] = scale * rng.normal(size=rows[..., :d].shape)
         rows[..., 2 * d : 3 * d] = np.abs(scale * rng.normal(size=rows[..., :d].shape)) + 0.1 * scale
-        for name in ("relation_embedding",) + cfg.projection_names:
+        for name in dense_names:
             state[name + "/adam_m"] = (scale * rng.normal(size=state[name].shape)).astype(np.float32)
             state[name + "/adam_v"] = ((scale * rng.normal(size=state[name].shape)) ** 2 + (0.1 * scale) ** 2).astype(np.float32)
         state["step"][:] = 37

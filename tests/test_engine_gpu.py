@@ -110,6 +110,18 @@ CASES = {
                                             distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
                                             feature_dropout=0.5),
                              seed=25),
+    # TransH: heads and tails projected onto the relation's hyperplane; a second relation parameter
+    # (the normals) with its own gradient and optimiser state
+    "transh_logsigmoid": dict(cfg=StepConfig(n_shard=2, n_entity=300, n_relation_type=4, embedding_size=32,
+                                             entity_feature_size=24, batch_size=16, a2a_size=12, score_fn="TransH",
+                                             distance_fn="L1", gamma=6.0, loss_type="logsigmoid",
+                                             learning_rate_modifiers={"relation_normal": 0.5}),
+                              seed=26, feature_dtype="float16"),
+    "transh_softmax_ragged": dict(cfg=StepConfig(n_shard=3, n_entity=101, n_relation_type=6, embedding_size=10,
+                                                 entity_feature_size=6, batch_size=9, a2a_size=5, score_fn="TransH",
+                                                 distance_fn="L1", gamma=3.0, loss_type="softmax", correction_weight=1.0,
+                                                 share_feature_networks=False),
+                                  seed=27),
     "single_shard": dict(cfg=StepConfig(n_shard=1, n_entity=400, n_relation_type=5, embedding_size=64,
                                         entity_feature_size=32, batch_size=64, a2a_size=96, score_fn="TransE",
                                         distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
@@ -181,16 +193,16 @@ def test_single_step_matches_oracle(name, warm, tensor_cores):
         tails = engine.debug_fetch("tails", s, T * D).reshape(T, D)
         assert_close(tails, last["tails"][s], RTOL, f"{name}: tails[{s}]")
         pred = engine.debug_fetch("pred", s, B * D).reshape(B, D)
-        assert_close(pred, last["pred"][s], RTOL, f"{name}: predicted tails[{s}]")
+        assert_close(pred, last["pred"][s][:, -D:], RTOL, f"{name}: predicted tails[{s}]")  # TransH: unit normal | predicted tail
         raw = engine.debug_fetch("raw_score", s, B * T).reshape(B, T)
-        scores = cfg.gamma - raw if cfg.score_fn in ("TransE", "RotatE") else raw
+        scores = cfg.gamma - raw if cfg.score_fn in ("TransE", "RotatE", "TransH") else raw
         assert_close(scores, last["scores"][s], RTOL, f"{name}: scores[{s}]")
         d_hidden = engine.debug_fetch("d_hidden", s, R * D).reshape(R, D)
         if cfg.share_feature_networks or cfg.entity_feature_size == 0:
             assert_close(d_hidden, last["d_feature_hidden"][s], RTOL, f"{name}: d hidden[{s}]")
     dense = engine.debug_fetch("dense_grad", 0, 1 << 24)
     n_rel = cfg.n_relation_type * D
-    assert dense.size == n_rel + len(cfg.projection_names) * cfg.entity_feature_size * D * (cfg.entity_feature_size > 0)
+    assert dense.size == n_rel * (2 if cfg.score_fn == "TransH" else 1) + len(cfg.projection_names) * cfg.entity_feature_size * D * (cfg.entity_feature_size > 0)
     _compare_state(engine, cfg, oracle, name, RTOL, case.get("rel_rtol"))
     engine.close()
 
@@ -212,7 +224,7 @@ def test_exchange_routing_is_bit_exact():
     engine.close()
 
 
-@pytest.mark.parametrize("name", ["config1_transe_l1", "transe_l2_softmax_features", "complex_softmax", "dropout_shared"])
+@pytest.mark.parametrize("name", ["config1_transe_l1", "transe_l2_softmax_features", "complex_softmax", "dropout_shared", "transh_logsigmoid"])
 def test_step_loop_and_graph_replay(name):
     """Several steps per call, twice: replaying the captured graph gives bit-identical results to
     plain launches, and both follow the oracle."""

@@ -50,7 +50,7 @@ def test_settings_errors_precede_the_device():
     with pytest.raises(ValueError, match="Key not found 'training.loss.correction_weight'"):
         capi.CEngine({**good, "training.loss.type": "softmax"})
     with pytest.raises(ValueError, match="not supported by this engine"):
-        capi.CEngine({**good, "model.score_fn": "TransH"})
+        capi.CEngine({**good, "model.feature_mlp_size": 64})
 
 
 def test_attach_failure_is_a_runtime_error():

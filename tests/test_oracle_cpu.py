@@ -127,6 +127,8 @@ VARIANTS = [
     dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
          embedding_regularisation=(2.0, 0.05), feature_regularisation=(2.5, 0.01), hidden_regularisation=(3.0, 0.02)),
     dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", feature_dropout=0.3, feature_regularisation=(2.0, 0.03)),
+    dict(score_fn="TransH", distance_fn="L1", loss_type="logsigmoid"),
+    dict(score_fn="TransH", distance_fn="L1", loss_type="softmax", correction_weight=1.0, share_feature_networks=False),
 ]
 
 
@@ -152,6 +154,7 @@ def test_hand_derived_backward_matches_autograd(variant):
     value = torch.stack([rows[s, idx["remote"][s], :d] for s in range(n)]).requires_grad_(True)
     feat = torch.stack([rows[s, idx["remote"][s], 3 * d :] for s in range(n)])
     rel = t(state["relation_embedding"]).requires_grad_(True)
+    normal = t(state["relation_normal"]).requires_grad_(True) if cfg.score_fn == "TransH" else None
     w = {name: t(state[name]).requires_grad_(True) for name in cfg.projection_names}
     w_h = w[cfg.projection_names[0]]
     w_t = w[cfg.projection_names[-1]]
@@ -183,17 +186,24 @@ def test_hand_derived_backward_matches_autograd(variant):
         h = heads[s]
         if cfg.score_fn == "TransE":
             p = h + r
+        elif cfg.score_fn == "TransH":  # src/poplar_kge.cpp:539-565
+            nv = normal[idx["relation"][s]]
+            nv = nv / torch.sqrt((nv * nv).sum(-1, keepdim=True))
+            p = h - nv * (nv * h).sum(-1, keepdim=True) + r
         elif cfg.score_fn == "DistMult":
             p = h * r
         else:
             half = d // 2
             p = torch.cat([h[:, :half] * r[:, :half] - h[:, half:] * r[:, half:],
                            h[:, :half] * r[:, half:] + h[:, half:] * r[:, :half]], dim=1)
-        if cfg.distance_fn == "MatMul":
+        if cfg.score_fn == "TransH":
+            projected = tails[s][None, :, :] - nv[:, None, :] * (nv @ tails[s].T)[:, :, None]
+            dist = (p[:, None, :] - projected).abs().sum(-1)
+        elif cfg.distance_fn == "MatMul":
             dist = p @ tails[s].T
         else:
             dist = torch.cdist(p, tails[s], p=1 if cfg.distance_fn == "L1" else 2)
-        scores = cfg.gamma - dist if cfg.score_fn == "TransE" else dist
+        scores = cfg.gamma - dist if cfg.score_fn in ("TransE", "TransH") else dist
         onehot = torch.nn.functional.one_hot(idx["tail"][s], cfg.n_tail).double()
         if cfg.loss_type == "softmax":
             shift = float(np.float32(cfg.correction_weight) * np.float32(so.softmax_correction(cfg))) if cfg.correction_weight else 0.0
@@ -212,6 +222,8 @@ def test_hand_derived_backward_matches_autograd(variant):
     total.backward(torch.tensor(float(cfg.loss_scale), dtype=torch.float64))
     np.testing.assert_allclose(oracle.last["d_value"], value.grad.numpy(), rtol=1e-9, atol=1e-12)
     np.testing.assert_allclose(oracle.last["grads"]["relation_embedding"], rel.grad.numpy(), rtol=1e-9, atol=1e-12)
+    if normal is not None:
+        np.testing.assert_allclose(oracle.last["grads"]["relation_normal"], normal.grad.numpy(), rtol=1e-9, atol=1e-12)
     for name in cfg.projection_names:
         np.testing.assert_allclose(oracle.last["grads"][name], w[name].grad.numpy(), rtol=1e-9, atol=1e-12)
 
