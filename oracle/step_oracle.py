@@ -48,6 +48,7 @@ class StepConfig:
     feature_regularisation: Tuple[float, float] = (2.0, 0.0)
     hidden_regularisation: Tuple[float, float] = (2.0, 0.0)
     feature_dropout: float = 0.0  # src/poplar_kge.cpp:459-461
+    feature_mlp_size: int = 0  # src/poplar_kge.cpp:453-458
 
     def __post_init__(self) -> None:
         if self.loss_scale is None:
@@ -444,6 +445,10 @@ class Oracle:
             shapes["relation_normal"] = (cfg.n_relation_type, d)
         for name in cfg.projection_names:
             shapes[name] = (f, d)
+            if cfg.feature_mlp_size > 0:  # src/poplar_kge.cpp:260-265
+                prefix = name[: -len("feature_projection")]
+                shapes[prefix + "mlp_up_projection"] = (2 * d, cfg.feature_mlp_size)
+                shapes[prefix + "mlp_down_projection"] = (cfg.feature_mlp_size, d)
         for name, shape in shapes.items():
             for suffix in ("", "/adam_m", "/adam_v"):
                 self.variables[name + suffix] = np.zeros(shape, dtype)
@@ -477,6 +482,10 @@ class Oracle:
             return np.concatenate([rel, self.variables["relation_normal"]], axis=-1)
         return rel
 
+    def _mlp(self, part: str, kind: str) -> str:
+        prefix = "" if self.cfg.share_feature_networks else f"{part}_"
+        return f"{prefix}mlp_{kind}_projection"
+
     def _projection(self, part: str) -> str:
         if self.cfg.share_feature_networks:
             return "feature_projection"
@@ -503,7 +512,18 @@ class Oracle:
         )
         value = value.copy()
         # 2. hidden, lookups, exchange (:676-681, :439-467)
+        mlp = []  # per call: (concatenated input, pre-activation, up projection, down projection)
         fh_h, fh_t = feat @ w_head, feat @ w_tail
+        if cfg.feature_mlp_size > 0:
+            # :453-458: featureHidden = relu(concat(value, featureHidden) . up) . down
+            outs = []
+            for part, fh0 in (("head", fh_h), ("tail", fh_t)):
+                up, down = self.variables[self._mlp(part, "up")], self.variables[self._mlp(part, "down")]
+                cat = np.concatenate([value, fh0], axis=-1)
+                pre = cat @ up
+                outs.append(np.maximum(pre, 0) @ down)
+                mlp.append((cat, pre, up, down))
+            fh_h, fh_t = outs
         keep_h = keep_t = None
         if cfg.feature_dropout > 0 and cfg.entity_feature_size > 0:
             # frnn::dropout (src/pag/pag.cpp:596-617): kept with probability 1 - p, scaled by 1 / (1 - p);
@@ -572,6 +592,21 @@ class Oracle:
         grads = {"relation_embedding": d_rel}
         if cfg.score_fn == "TransH":
             grads = {"relation_embedding": d_rel[:, :d], "relation_normal": d_rel[:, d:]}
+        keep["d_mlp_output"] = d_fh_h + d_fh_t if cfg.share_feature_networks else d_fh_h
+        if mlp:
+            # backward of the MLP; max(x, 0) passes the gradient where x equals the output, zero included
+            # (src/pag/pag.cpp:650-658)
+            back = []
+            for part, d_out, (cat, pre, up, down) in (("head", d_fh_h, mlp[0]), ("tail", d_fh_t, mlp[1])):
+                boom = np.maximum(pre, 0)
+                d_pre = (d_out @ down.T) * (pre == boom)
+                for kind, grad in (("down", np.einsum("srm,srd->md", boom, d_out)), ("up", np.einsum("src,srm->cm", cat, d_pre))):
+                    name = self._mlp(part, kind)
+                    grads[name] = grads.get(name, 0) + grad
+                d_cat = d_pre @ up.T
+                d_value = d_value + d_cat[..., :d]
+                back.append(d_cat[..., d:])
+            d_fh_h, d_fh_t = back
         if cfg.share_feature_networks:
             grads["feature_projection"] = np.einsum("srf,srd->fd", feat, d_fh_h + d_fh_t)
         else:
@@ -620,7 +655,11 @@ class Oracle:
     def hidden_all(self, part: str) -> np.ndarray:
         d = self.cfg.embedding_size
         w = self.variables[self._projection(part)]
-        return self.entity_data[..., :d] + self.entity_data[..., 3 * d :] @ w
+        value, fh = self.entity_data[..., :d], self.entity_data[..., 3 * d :] @ w
+        if self.cfg.feature_mlp_size > 0:
+            pre = np.concatenate([value, fh], axis=-1) @ self.variables[self._mlp(part, "up")]
+            fh = np.maximum(pre, 0) @ self.variables[self._mlp(part, "down")]
+        return value + fh
 
     def predict(self, shard_idx_relation: np.ndarray, shard_to_count: np.ndarray, n_best: int):
         """Brute-force ranking of every real entity for (head shard, head index, relation)

@@ -19,7 +19,7 @@ def engine_settings(cfg: StepConfig, n_step: int = 1, dtype: str = "float32",
         "model.seed": seed, "model.score_fn": cfg.score_fn, "model.distance_fn": cfg.distance_fn,
         "model.n_shard": cfg.n_shard, "model.n_entity": cfg.n_entity,
         "model.n_relation_type": cfg.n_relation_type, "model.embedding_size": cfg.embedding_size,
-        "model.entity_feature_size": cfg.entity_feature_size, "model.feature_mlp_size": 0,
+        "model.entity_feature_size": cfg.entity_feature_size, "model.feature_mlp_size": int(cfg.feature_mlp_size),
         "model.feature_dropout": float(cfg.feature_dropout), "model.share_feature_networks": cfg.share_feature_networks,
         "model.gamma": float(cfg.gamma), "model.init_scale": 1.0,
         "model.negative_adversarial_scale": float(cfg.negative_adversarial_scale),
@@ -70,6 +70,13 @@ def random_state(cfg: StepConfig, seed: int, fp16_features: bool = False, warm: 
     for name in cfg.projection_names:
         state[name] = (rng.normal(size=(f, d)) / np.sqrt(max(f, 1)) / np.sqrt(d)).astype(np.float32)
     dense_names = ("relation_embedding",) + cfg.projection_names
+    if cfg.feature_mlp_size > 0:
+        mrng, m = np.random.RandomState(seed + 104729), cfg.feature_mlp_size
+        for name in cfg.projection_names:
+            prefix = name[: -len("feature_projection")]
+            state[prefix + "mlp_up_projection"] = (mrng.normal(size=(2 * d, m)) / np.sqrt(2 * d)).astype(np.float32)
+            state[prefix + "mlp_down_projection"] = (mrng.normal(size=(m, d)) / np.sqrt(m)).astype(np.float32)
+            dense_names += (prefix + "mlp_up_projection", prefix + "mlp_down_projection")
     if cfg.score_fn == "TransH":  # hyperplane normals, normalised on use
         state["relation_normal"] = (np.random.RandomState(seed + 7919).normal(size=(cfg.n_relation_type, d)) / np.sqrt(d)).astype(np.float32)
         dense_names += ("relation_normal",)

@@ -127,6 +127,9 @@ VARIANTS = [
     dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
          embedding_regularisation=(2.0, 0.05), feature_regularisation=(2.5, 0.01), hidden_regularisation=(3.0, 0.02)),
     dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", feature_dropout=0.3, feature_regularisation=(2.0, 0.03)),
+    dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", feature_mlp_size=10, hidden_regularisation=(2.0, 0.02)),
+    dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False, feature_mlp_size=6,
+         feature_dropout=0.3),
     dict(score_fn="TransH", distance_fn="L1", loss_type="logsigmoid"),
     dict(score_fn="TransH", distance_fn="L1", loss_type="softmax", correction_weight=1.0, share_feature_networks=False),
 ]
@@ -159,6 +162,12 @@ def test_hand_derived_backward_matches_autograd(variant):
     w_h = w[cfg.projection_names[0]]
     w_t = w[cfg.projection_names[-1]]
     fh_h, fh_t = feat @ w_h, feat @ w_t
+    mlp_w = {}
+    if cfg.feature_mlp_size > 0:  # src/poplar_kge.cpp:453-458
+        prefixes = [""] if cfg.share_feature_networks else ["head_", "tail_"]
+        mlp_w = {pre + kind: t(state[pre + kind]).requires_grad_(True) for pre in prefixes for kind in ("mlp_up_projection", "mlp_down_projection")}
+        boom = lambda fh0, pre: torch.relu(torch.cat([value, fh0], dim=-1) @ mlp_w[pre + "mlp_up_projection"]) @ mlp_w[pre + "mlp_down_projection"]  # noqa: E731
+        fh_h, fh_t = boom(fh_h, prefixes[0]), boom(fh_t, prefixes[-1])
     if cfg.feature_dropout > 0:  # kept with probability 1 - p, scaled by 1 / (1 - p); a mask per call
         scale = 1.0 / (1.0 - float(np.float32(cfg.feature_dropout)))
         fh_h, fh_t = fh_h * t(masks[0]) * scale, fh_t * t(masks[1]) * scale
@@ -222,6 +231,8 @@ def test_hand_derived_backward_matches_autograd(variant):
     total.backward(torch.tensor(float(cfg.loss_scale), dtype=torch.float64))
     np.testing.assert_allclose(oracle.last["d_value"], value.grad.numpy(), rtol=1e-9, atol=1e-12)
     np.testing.assert_allclose(oracle.last["grads"]["relation_embedding"], rel.grad.numpy(), rtol=1e-9, atol=1e-12)
+    for name, tensor in mlp_w.items():
+        np.testing.assert_allclose(oracle.last["grads"][name], tensor.grad.numpy(), rtol=1e-9, atol=1e-12)
     if normal is not None:
         np.testing.assert_allclose(oracle.last["grads"]["relation_normal"], normal.grad.numpy(), rtol=1e-9, atol=1e-12)
     for name in cfg.projection_names:
