@@ -149,7 +149,7 @@ Config parse_config(const SettingMap& s) {
     else
         fail(KGE_INVALID_ARGUMENT, msg() << "'training.loss.type' must be one of 'logsigmoid' or 'softmax', not '"
                                          << loss << "'");
-    if (mlp > 0) fail(KGE_INVALID_ARGUMENT, "'model.feature_mlp_size' > 0 is not supported by this engine");
+    c.mlp = mlp;
     if (!(dropout >= 0.f && dropout < 1.f)) fail(KGE_INVALID_ARGUMENT, msg() << "'model.feature_dropout' must be in [0, 1), actual: " << dropout);
     c.dropout = dropout;
     if (c.state_type == ST_F16 && c.feature_type != ST_F16)
@@ -167,9 +167,17 @@ Config parse_config(const SettingMap& s) {
                                             "execution.world_size (" << c.world << ") and rank < world_size");
     divisible("relation_embedding", c.n_relation_type, c.d);
     if (c.f) divisible(c.share_networks ? "feature_projection" : "head_feature_projection", c.f, c.d);
+    if (c.f && c.mlp) {  // src/poplar_kge.cpp:260-265
+        divisible(c.share_networks ? "mlp_up_projection" : "head_mlp_up_projection", 2 * c.d, c.mlp);
+        divisible(c.share_networks ? "mlp_down_projection" : "head_mlp_down_projection", c.mlp, c.d);
+    }
     for (auto& kv : c.lr_modifiers) {
         const bool known = kv.first == "entity_embedding" || kv.first == "relation_embedding" ||
                            (c.score_fn == SCORE_TRANSH && kv.first == "relation_normal") ||
+                           (c.mlp && c.f && c.share_networks && (kv.first == "mlp_up_projection" || kv.first == "mlp_down_projection")) ||
+                           (c.mlp && c.f && !c.share_networks &&
+                            (kv.first == "head_mlp_up_projection" || kv.first == "head_mlp_down_projection" ||
+                             kv.first == "tail_mlp_up_projection" || kv.first == "tail_mlp_down_projection")) ||
                            (c.share_networks ? kv.first == "feature_projection"
                                              : (kv.first == "head_feature_projection" ||
                                                 kv.first == "tail_feature_projection"));
@@ -280,7 +288,12 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     dense_bounds_[2] = dense_bounds_[1] + (cfg_.n_net() >= 1 ? proj_elems_ : 0);
     dense_bounds_[3] = dense_bounds_[2] + (cfg_.n_net() >= 2 ? proj_elems_ : 0);
     dense_bounds_[4] = dense_bounds_[3] + (cfg_.score_fn == SCORE_TRANSH ? (size_t)cfg_.n_relation_type * cfg_.d : 0);
-    n_dense_ = dense_bounds_[4];
+    for (unsigned net = 0; net < 2; ++net) {  // the feature MLP's projections: up [2D, M], down [M, D]
+        const bool present = cfg_.mlp > 0 && net < cfg_.n_net();
+        dense_bounds_[5 + 2 * net] = dense_bounds_[4 + 2 * net] + (present ? (size_t)2 * cfg_.d * cfg_.mlp : 0);
+        dense_bounds_[6 + 2 * net] = dense_bounds_[5 + 2 * net] + (present ? (size_t)cfg_.mlp * cfg_.d : 0);
+    }
+    n_dense_ = dense_bounds_[kDenseParams];
     auto modifier = [&](const std::string& name) {
         auto it = cfg_.lr_modifiers.find(name);
         return it == cfg_.lr_modifiers.end() ? 1.0f : it->second;
@@ -298,10 +311,10 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
                          : std::vector<std::string>{"head_feature_projection", "tail_feature_projection"};
     for (size_t i = 0; i < proj_names.size() && i < 2; ++i) dense_lr_mod_[1 + i] = modifier(proj_names[i]);
 
-    auto add_variable = [&](const std::string& name, size_t rows, size_t cols, size_t offset) {
+    auto add_variable = [&](const std::string& name, size_t rows, size_t cols, size_t offset, bool flat = false) {
         const char* suffix[3] = {"", "/adam_m", "/adam_v"};
         for (int k = 0; k < 3; ++k)
-            variables_.push_back({name + suffix[k], KGE_F32, {rows, cols}, offset, k});
+            variables_.push_back({name + suffix[k], KGE_F32, {rows, cols}, offset, k, flat});
     };
     // RotatE's relations are angles, one per complex pair (src/poplar_kge.cpp:248-251); the table keeps
     // rows of d floats all the same and uses their first half
@@ -312,11 +325,20 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
         add_variable("relation_normal", cfg_.n_relation_type, cfg_.d, dense_bounds_[3]);
         dense_lr_mod_[3] = modifier("relation_normal");
     }
-    variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3});
+    if (cfg_.mlp > 0 && cfg_.n_net() > 0)
+        for (unsigned net = 0; net < cfg_.n_net(); ++net) {
+            const std::string prefix = proj_names[net].substr(0, proj_names[net].size() - std::string("feature_projection").size());
+            add_variable(prefix + "mlp_up_projection", 2 * cfg_.d, cfg_.mlp, dense_bounds_[4 + 2 * net], true);
+            add_variable(prefix + "mlp_down_projection", cfg_.mlp, cfg_.d, dense_bounds_[5 + 2 * net]);
+            dense_lr_mod_[4 + 2 * net] = modifier(prefix + "mlp_up_projection");
+            dense_lr_mod_[5 + 2 * net] = modifier(prefix + "mlp_down_projection");
+        }
+    variables_.push_back({"step", KGE_U32, {cfg_.n_shard}, 0, 3, false});
 
     // Every process owns (reduces and updates) an equal share of the rows of the dense vector, dealt
     // out in turn: row r belongs to process r % world, as its row r / world.
-    const size_t dense_rows = cfg_.n_relation_type + (size_t)cfg_.n_net() * cfg_.f + (cfg_.score_fn == SCORE_TRANSH ? cfg_.n_relation_type : 0);
+    const size_t dense_rows = cfg_.n_relation_type + (size_t)cfg_.n_net() * cfg_.f + (cfg_.score_fn == SCORE_TRANSH ? cfg_.n_relation_type : 0) +
+                              (cfg_.mlp > 0 ? (size_t)cfg_.n_net() * 3 * cfg_.mlp : 0);
     dense_chunk_rows_ = std::max<size_t>(1, (dense_rows + cfg_.world - 1) / cfg_.world);
     dense_chunk_ = dense_chunk_rows_ * cfg_.d;
     own_rows_ = dense_rows > cfg_.rank ? (dense_rows - cfg_.rank + cfg_.world - 1) / cfg_.world : 0;
@@ -341,6 +363,7 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     planes_ = cfg_.tensor_cores && cfg_.d % 4 == 0 && cfg_.batch_size % 4 == 0 && cfg_.n_tail() % 4 == 0 &&
               cfg_.n_remote() <= (unsigned)tc::kRouteMaxLookups;
     if (const char* v = std::getenv("KGE_PLANE_CONTRACTIONS")) planes_ = planes_ && std::atoi(v) != 0;
+    if (mlp_on()) planes_ = false;  // the MLP sits between the projection and the lookups: the step of separate kernels
     if (cfg_.score_fn == SCORE_TRANSH) {
         planes_ = false;  // its score has no contraction form: the step of separate kernels
         if (transh_score_smem() > 200 * 1024) fail(KGE_INVALID_ARGUMENT, "TransH: model.embedding_size is limited to 1600");
@@ -405,6 +428,19 @@ void Engine::allocate() {
         b.d_pred = (float*)device_alloc((size_t)B * D * 4);
         b.d_head = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
         b.d_relrow = multiplicative ? (float*)device_alloc((size_t)B * D * 4) : b.d_pred;
+        if (mlp_on()) {
+            const size_t M = cfg_.mlp;
+            for (unsigned net = 0; net < cfg_.n_net(); ++net) {
+                b.mlp_cat[net] = (float*)device_alloc((size_t)R * 2 * D * 4);
+                b.mlp_pre[net] = (float*)device_alloc((size_t)R * M * 4);
+            }
+            b.mlp_out = (float*)device_alloc((size_t)R * D * 4);
+            b.mlp_d_pre = (float*)device_alloc((size_t)R * M * 4);
+            b.mlp_d_cat = (float*)device_alloc((size_t)R * 2 * D * 4);
+            b.d_val = (float*)device_alloc((size_t)R * D * 4);
+            b.mlp_dw_up = (float*)device_alloc((size_t)2 * D * M * 4);
+            b.mlp_dw_down = (float*)device_alloc((size_t)M * D * 4);
+        }
         if (cfg_.score_fn == SCORE_TRANSH) {
             b.nrm = (float*)device_alloc((size_t)B * D * 4);
             b.d_nrm = (float*)device_alloc((size_t)B * D * 4);
@@ -1134,6 +1170,78 @@ void Engine::launch_planes(const char* name, tc::PlaneProblem* problems, int n_p
     KGE_CUDA(err);
 }
 
+// The feature MLP on `n_rows` rows whose hidden buffer holds value + feature . W (src/poplar_kge.cpp:453-458):
+// hid = value + relu(concat(value, hid - value) . up) . down, the values read from rows `index[i]` (or
+// start + i) of `rows`.  Leaves the MLP's input in `cat` and its pre-activations in `pre` for the backward.
+void Engine::launch_mlp_forward(const uint8_t* rows, const uint32_t* index, uint32_t start, unsigned n_rows, int net, float* hid,
+                                float* cat, float* pre, float* out) {
+    const unsigned D = cfg_.d, M = cfg_.mlp;
+    const float* up = dense_ + dense_bounds_[4 + 2 * net];
+    const float* down = dense_ + dense_bounds_[5 + 2 * net];
+    const dim3 grid(std::min(ceil_div(n_rows * D, 256), 148u * 8));
+    if (cfg_.state_type == ST_F32)
+        KGE_LAUNCH("mlp", KGE_CUDA(launch_dependent(k_mlp_concat<float>, grid, dim3(256), 0, stream_, rows, layout_, index, start, (int)n_rows, (const float*)hid, cat)));
+    else
+        KGE_LAUNCH("mlp", KGE_CUDA(launch_dependent(k_mlp_concat<__half>, grid, dim3(256), 0, stream_, rows, layout_, index, start, (int)n_rows, (const float*)hid, cat)));
+    SgemmArgs g{};
+    g.A = cat; g.lda = 2 * D; g.B = up; g.ldb = M; g.C = pre; g.ldc = M; g.M = (int)n_rows; g.N = (int)M; g.K = (int)(2 * D);
+    KGE_LAUNCH("mlp", KGE_CUDA(launch_sgemm(g, stream_)));
+    g = SgemmArgs{};
+    g.A = pre; g.lda = M; g.a_relu = 1; g.B = down; g.ldb = D; g.C = out; g.ldc = D; g.M = (int)n_rows; g.N = (int)D; g.K = (int)M;
+    KGE_LAUNCH("mlp", KGE_CUDA(launch_sgemm(g, stream_)));
+    if (cfg_.state_type == ST_F32)
+        KGE_LAUNCH("mlp", KGE_CUDA(launch_dependent(k_mlp_finish<float>, grid, dim3(256), 0, stream_, rows, layout_, index, start, (int)n_rows, (const float*)out, hid)));
+    else
+        KGE_LAUNCH("mlp", KGE_CUDA(launch_dependent(k_mlp_finish<__half>, grid, dim3(256), 0, stream_, rows, layout_, index, start, (int)n_rows, (const float*)out, hid)));
+}
+
+// Backward of the MLP for local shard l, after the entity update has left the gradients of the
+// MLP's outputs in d_hid_h / d_hid_t and the value's gradient so far in d_val: this shard's
+// gradients of the up and down projections go to their owners, the input gradient's first half
+// joins d_val, its second half replaces d_hid (the projection gradient's operand), and the rows
+// get their Adam step.
+void Engine::launch_mlp_backward(unsigned l, unsigned step) {
+    ShardBuffers& b = shards_[l];
+    const unsigned D = cfg_.d, M = cfg_.mlp, R = cfg_.n_remote();
+    const size_t sidx = (size_t)l * cfg_.n_step + step;
+    for (unsigned net = 0; net < cfg_.n_net(); ++net) {
+        float* d_out = net ? b.d_hid_t : b.d_hid_h;
+        const float* up = dense_ + dense_bounds_[4 + 2 * net];
+        const float* down = dense_ + dense_bounds_[5 + 2 * net];
+        SgemmArgs g{};  // d down = relu(pre)^T . d_out
+        g.A = b.mlp_pre[net]; g.lda = M; g.a_trans = 1; g.a_relu = 1; g.B = d_out; g.ldb = D; g.C = b.mlp_dw_down; g.ldc = D;
+        g.M = (int)M; g.N = (int)D; g.K = (int)R;
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_sgemm(g, stream_)));
+        g = SgemmArgs{};  // d pre = (d_out . down^T) where pre >= 0
+        g.A = d_out; g.lda = D; g.B = down; g.ldb = D; g.b_trans = 1; g.C = b.mlp_d_pre; g.ldc = M; g.M = (int)R; g.N = (int)M; g.K = (int)D;
+        g.pass = b.mlp_pre[net]; g.ldpass = M;
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_sgemm(g, stream_)));
+        g = SgemmArgs{};  // d up = cat^T . d pre
+        g.A = b.mlp_cat[net]; g.lda = 2 * D; g.a_trans = 1; g.B = b.mlp_d_pre; g.ldb = M; g.C = b.mlp_dw_up; g.ldc = M;
+        g.M = (int)(2 * D); g.N = (int)M; g.K = (int)R;
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_sgemm(g, stream_)));
+        g = SgemmArgs{};  // d cat = d pre . up^T
+        g.A = b.mlp_d_pre; g.lda = M; g.B = up; g.ldb = M; g.b_trans = 1; g.C = b.mlp_d_cat; g.ldc = 2 * D; g.M = (int)R; g.N = (int)(2 * D); g.K = (int)M;
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_sgemm(g, stream_)));
+        const dim3 pgrid(std::min(ceil_div(2 * M * D, 256), 148u * 4));
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_dependent(k_push_dense_rows, pgrid, dim3(256), 0, stream_, (const float*)b.mlp_dw_up, (int)(2 * M),
+                                                        (int)(dense_bounds_[4 + 2 * net] / D), (int)D, b.dense_dst, (int)cfg_.world)));
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_dependent(k_push_dense_rows, pgrid, dim3(256), 0, stream_, (const float*)b.mlp_dw_down, (int)M,
+                                                        (int)(dense_bounds_[5 + 2 * net] / D), (int)D, b.dense_dst, (int)cfg_.world)));
+        const dim3 sgrid(std::min(ceil_div(R * D, 256), 148u * 8));
+        KGE_LAUNCH("mlp_bwd", KGE_CUDA(launch_dependent(k_mlp_split, sgrid, dim3(256), 0, stream_, (const float*)b.mlp_d_cat, b.d_val, d_out, (int)R, (int)D)));
+    }
+    const dim3 agrid(std::min(ceil_div(R * D, 256), 148u * 8));
+    const uint8_t* rows_c = b.rows_c2[step & 1];
+    const uint32_t* remote = d_remote_ + sidx * R;
+    if (cfg_.state_type == ST_F32)
+        KGE_LAUNCH("row_adam", KGE_CUDA(launch_dependent(k_row_adam<float>, agrid, dim3(256), 0, stream_, b.table, rows_c, layout_, remote, (const uint32_t*)(d_first_slot_ + sidx * R),
+                                                         (const float*)b.d_val, (const float*)(d_step_size_ + step), entity_lr_mod_, adam_, (int)R)));
+    else
+        KGE_LAUNCH("row_adam", KGE_CUDA(launch_dependent(k_row_adam<__half>, agrid, dim3(256), 0, stream_, b.table, rows_c, layout_, remote, (const uint32_t*)(d_first_slot_ + sidx * R),
+                                                         (const float*)b.d_val, (const float*)(d_step_size_ + step), entity_lr_mod_, adam_, (int)R)));
+}
+
 // The norm regularisers of local shard l's gathered rows (k_regularise): after the hidden rows,
 // before the loss (which adds their loss term) and the entity update (which adds their gradients).
 void Engine::launch_regularise(unsigned l, const uint8_t* rows_c) {
@@ -1158,6 +1266,7 @@ RelationRows Engine::with_regularisers(RelationRows rr, unsigned l, unsigned ste
     rr.reg_h = b.reg_h;
     rr.reg_t = b.reg_t;
     rr.drop = dropout_params(l, step);
+    rr.defer_grad = b.d_val;
     return rr;
 }
 
@@ -1336,7 +1445,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const size_t sidx = (size_t)l * cfg_.n_step + step;
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
         const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
-                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}}, l, step);
+                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}, nullptr}, l, step);
         const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
         if (cfg_.state_type == ST_F32)
             KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
@@ -1389,8 +1498,8 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         da.adam_v = dense_v_;
         da.n_own = own_rows_;
         da.row_width = D;
-        for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
-        for (int i = 0; i < 4; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
+        for (int i = 0; i <= kDenseParams; ++i) da.bounds[i] = dense_bounds_[i];
+        for (int i = 0; i < kDenseParams; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
         da.step_size = d_step_size_ + step;
         da.ap = adam_;
         const unsigned blocks = (unsigned)std::min<size_t>((own_rows_ * D / 4 + 255) / 256, 148 * 8);
@@ -1469,6 +1578,9 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* a2a = step_ptr(d_a2a_, l, T);
         const uint32_t* head = step_ptr(d_head_, l, B);
         const uint32_t* relation = step_ptr(d_relation_, l, B);
+        if (mlp_on())
+            for (unsigned net = 0; net < cfg_.n_net(); ++net)
+                launch_mlp_forward(rows_c, nullptr, 0u, R, (int)net, net ? b.hid_t : b.hid_h, b.mlp_cat[net], b.mlp_pre[net], b.mlp_out);
         if (dropout_on()) launch_dropout(l, step, rows_c);
         const int route_fn = transh ? SCORE_TRANSE : cfg_.score_fn;  // TransH: the tails are routed, the prediction follows
         if (vec)
@@ -1629,6 +1741,8 @@ void Engine::launch_one_step(unsigned step) {
         }
     }
     KGE_CUDA(cudaGetLastError());
+    if (mlp_on())
+        for (unsigned l = 0; l < n_local_; ++l) launch_mlp_backward(l, step);
     if (proj_direct && (side_streams_ & 1u)) side_join(0);  // the relation rows of the partial dense gradient are in place
     const bool gather_ahead = step + 1 < cfg_.n_step;
     const bool gather_beside = gather_ahead && (side_streams_ & 2u);
@@ -1703,8 +1817,8 @@ void Engine::launch_one_step(unsigned step) {
         da.adam_v = dense_v_;
         da.n_own = own_rows_;
         da.row_width = D;
-        for (int i = 0; i < 4; ++i) da.bounds[i] = dense_bounds_[i];
-        for (int i = 0; i < 4; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
+        for (int i = 0; i <= kDenseParams; ++i) da.bounds[i] = dense_bounds_[i];
+        for (int i = 0; i < kDenseParams; ++i) da.lr_modifier[i] = dense_lr_mod_[i];
         da.step_size = d_step_size_ + step;
         da.ap = adam_;
         // The parameter itself is read from this process's own replica (entry `rank`).
@@ -1847,7 +1961,8 @@ void Engine::cmd_read_write_variable(std::vector<HostArray>& arrays, const std::
     float* base = var->kind == 0 ? dense_ : var->kind == 1 ? dense_m_ : dense_v_;
     // Rows of the dense vector are d floats wide; a variable may show fewer columns of them to the
     // host (RotatE's angles are the first half of their rows).
-    const size_t D = cfg_.d, cols = var->shape[1], n_rows = var->shape[0], row0 = var->offset / D, W = cfg_.world;
+    const size_t D = cfg_.d, row0 = var->offset / D, W = cfg_.world;
+    const size_t cols = var->flat ? D : var->shape[1], n_rows = var->flat ? count / D : var->shape[0];
     float* host = static_cast<float*>(value.data);
     if (write) {
         // on the engine's stream, so that the kernel that derives the lower plane is ordered behind the copy
@@ -1892,6 +2007,12 @@ void Engine::ensure_predict_buffers() {
         p_chunk_lo_ = (float*)device_alloc((size_t)predict_chunk_ * D * 4);
         p_query_lo_ = (float*)device_alloc(Q * D * 4);
         if (cfg_.f) p_feat_ = (float*)device_alloc((size_t)predict_chunk_ * feat_stride_ * 4);
+    }
+    if (mlp_on()) {
+        const size_t rows = std::max<size_t>(cfg_.predict_hr, predict_chunk_);
+        p_mlp_cat_ = (float*)device_alloc(rows * 2 * D * 4);
+        p_mlp_pre_ = (float*)device_alloc(rows * cfg_.mlp * 4);
+        p_mlp_out_ = (float*)device_alloc(rows * D * 4);
     }
     d_iota_ = (uint32_t*)device_alloc((size_t)cfg_.predict_hr * 4);
     std::vector<uint32_t> iota(cfg_.predict_hr);
@@ -1951,6 +2072,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
         KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<grid, 256, 0, stream_>>>(
                                                                 shards_[l].table, layout_, d_head + l * hr, 0u, (int)hr, W_head,
                                                                 nullptr, p_head_hidden_, nullptr)));
+        if (mlp_on()) launch_mlp_forward(shards_[l].table, d_head + l * hr, 0u, (unsigned)hr, 0, p_head_hidden_, p_mlp_cat_, p_mlp_pre_, p_mlp_out_);
         for (unsigned p = 0; p < cfg_.world; ++p) {
             float* dst = (float*)(peer_arena_[p] + arena_offset_predict(0)) + (size_t)(shard0_ + l) * hr * D;
             if (cfg_.score_fn == SCORE_TRANSH) {
@@ -1993,6 +2115,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
             KGE_LAUNCH("predict_hidden", KGE_DISPATCH_ROW(cfg_, k_hidden<ST, FT><<<hgrid, 256, 0, stream_>>>(
                                                                     b.table, layout_, nullptr, start, (int)c, W_tail, nullptr,
                                                                     p_chunk_hidden_, nullptr)));
+            if (mlp_on()) launch_mlp_forward(b.table, nullptr, start, c, two_nets ? 1 : 0, p_chunk_hidden_, p_mlp_cat_, p_mlp_pre_, p_mlp_out_);
             if (cfg_.score_fn == SCORE_TRANSH) {
                 const dim3 grid(ceil_div((unsigned)Q, kTranshRows), std::max(1u, std::min(ceil_div(c, 8u), 2 * 148 / std::max(1u, ceil_div((unsigned)Q, kTranshRows)))));
                 KGE_LAUNCH("predict_score", k_transh_score<<<grid, 256, transh_score_smem(), stream_>>>(

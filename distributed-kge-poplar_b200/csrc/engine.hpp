@@ -13,6 +13,7 @@
 #include "tc_gemm.cuh"
 #include "tc_planes.cuh"
 #include "transh.cuh"
+#include "mlp.cuh"
 
 namespace kge {
 
@@ -36,6 +37,7 @@ struct Config {
     // Norm regularisers of the gathered rows' values, feature-network outputs and hidden rows
     // (training.embedding_regularisation, .feature_regularisation, .hidden_regularisation): power and weight.
     float reg_power[3], reg_weight[3];
+    unsigned mlp;   // model.feature_mlp_size: width of the feature MLP's hidden layer, 0 = none
     float dropout;  // model.feature_dropout: drop probability of the feature network's output while training
     bool regularised() const { return reg_weight[0] > 0.f || reg_weight[1] > 0.f || reg_weight[2] > 0.f; }
     float beta_m, beta_v, epsilon, weight_decay;
@@ -68,6 +70,9 @@ struct Variable {
     std::vector<size_t> shape;
     size_t offset;  // element offset inside the dense vector (params / adam_m / adam_v)
     int kind;       // 0 = parameter, 1 = adam_m, 2 = adam_v, 3 = step
+    // true: stored contiguously, whatever its column count (a multiple of d floats in all); false:
+    // one row of the variable per d-float row of the dense vector, of which it shows shape[1] columns
+    bool flat = false;
 };
 
 struct HostArray {
@@ -116,6 +121,11 @@ class Engine {
         // TransH: unit normals of the batch's relations, n_i . t_j and the signs' sums along the normal
         // ([B, T]), gradients of the normals from the scores, per-triple gradients of the raw normals
         float *nrm = nullptr, *pair_s = nullptr, *pair_u = nullptr, *d_nrm = nullptr, *d_normrow = nullptr;
+        // Feature MLP, per network: its input rows [R, 2D] and pre-activations [R, M]; then its output
+        // [R, D], the gradients of the pre-activations and of the input, the value's deferred gradient,
+        // and this shard's gradients of the two projections
+        float *mlp_cat[2] = {nullptr, nullptr}, *mlp_pre[2] = {nullptr, nullptr};
+        float *mlp_out = nullptr, *mlp_d_pre = nullptr, *mlp_d_cat = nullptr, *d_val = nullptr, *mlp_dw_up = nullptr, *mlp_dw_down = nullptr;
         float *reg_val = nullptr, *reg_h = nullptr, *reg_t = nullptr, *reg_loss_rows = nullptr;  // regularisers' terms, [R, D] and [R]
         float *tails = nullptr, *grad_recv = nullptr, *dense_partial = nullptr;  // inside the arena
         float** send_dst = nullptr;  // device table [n_shard]
@@ -228,8 +238,8 @@ class Engine {
     float** d_replicas_ = nullptr;        // [world]
 
     // dense parameters: relation table | projection(s)
-    size_t n_dense_ = 0, proj_elems_ = 0, dense_bounds_[5] = {0, 0, 0, 0, 0};  // relation table | projection(s) | TransH normals
-    float dense_lr_mod_[4] = {1.f, 1.f, 1.f, 1.f};
+    size_t n_dense_ = 0, proj_elems_ = 0, dense_bounds_[kDenseParams + 1] = {};  // relation table | projection(s) | TransH normals | MLP up, down per network
+    float dense_lr_mod_[kDenseParams] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
     float entity_lr_mod_ = 1.f;
     float *dense_ = nullptr, *dense_m_ = nullptr, *dense_v_ = nullptr;
     float* dense_lo_ = nullptr;      // lower TF32 plane of the dense vector (same layout, inside the arena)
@@ -248,6 +258,11 @@ class Engine {
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
     unsigned* d_loss_counter_ = nullptr;
     size_t transh_score_smem() const { return (size_t)2 * kTranshRows * cfg_.d * sizeof(float); }
+    bool mlp_on() const { return cfg_.mlp > 0 && cfg_.f > 0; }
+    void launch_mlp_forward(const uint8_t* rows, const uint32_t* index, uint32_t start, unsigned n_rows, int net, float* hid,
+                            float* cat, float* pre, float* out);
+    void launch_mlp_backward(unsigned l, unsigned step);
+    float *p_mlp_cat_ = nullptr, *p_mlp_pre_ = nullptr, *p_mlp_out_ = nullptr;  // predict's MLP buffers
     uint32_t* d_step_key_ = nullptr;   // [n_step] numbers of the staged training steps (keys of the dropout masks)
     bool dropout_on() const { return cfg_.dropout > 0.f && cfg_.f > 0; }
     DropoutParams dropout_params(unsigned l, unsigned step) const;

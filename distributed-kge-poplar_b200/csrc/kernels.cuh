@@ -1253,6 +1253,9 @@ struct RelationRows {
     const float* reg_h;
     const float* reg_t;
     DropoutParams drop;  // threshold 0: none.  Masks the gradients of the feature network's outputs.
+    // Non-null: the value's gradient is left here ([R, D]) and the rows are not updated; k_row_adam
+    // does that once the rest of the gradient is known (the feature MLP reads the value too).
+    float* defer_grad;
 };
 
 template <int V, int LANES>
@@ -1461,6 +1464,11 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         } else {
             d_hid_h[o] = d_hid_t ? gh[0] : gh[0] + gt[0];
             if (d_hid_t) d_hid_t[o] = gt[0];
+        }
+        if (rr.defer_grad) {
+#pragma unroll
+            for (int u = 0; u < V; ++u) rr.defer_grad[o + u] = gv[u];
+            return;
         }
         if (!writes_row) return;
         float x[V], m[V], qq[V];
@@ -1769,6 +1777,7 @@ k_dense_partial(const float* __restrict__ d_relrow, const uint32_t* __restrict__
 // (src/poplar_kge.cpp:329-339) and the write of the new values into every replica
 // (the all-gather on next use, :341-348).  Pointer tables live in device memory; entries
 // may point into peers' memory.
+constexpr int kDenseParams = 8;
 struct DenseUpdateArgs {
     const float* const* partials;  // [n_partial] the shards' slots in this process's receive buffer
     int n_partial;
@@ -1780,12 +1789,20 @@ struct DenseUpdateArgs {
     // This process owns the rows self, self + n_replica, ... of the dense vector: n_own of them,
     // row_width elements each; its j-th row is row j of every slot.
     size_t n_own, row_width;
-    size_t bounds[4];       // parameter p covers the elements [bounds[p], bounds[p+1])
-    float lr_modifier[4];
+    // parameter p covers the elements [bounds[p], bounds[p+1]): relation table, projection(s), TransH
+    // normals, the feature MLP's up / down projections per network; absent ones are empty
+    size_t bounds[kDenseParams + 1];
+    float lr_modifier[kDenseParams];
     const float* step_size;
     AdamParams ap;
     ExchangeSync sync;
 };
+
+__device__ __forceinline__ int dense_param_of(const DenseUpdateArgs& a, size_t e) {
+    int p = 0;
+    while (p + 1 < kDenseParams && e >= a.bounds[p + 1]) ++p;
+    return p;
+}
 
 __device__ __forceinline__ float dense_adam(float x, float g, float& m, float& v, float alpha, const AdamParams& ap) {
     m = ap.beta_m * m + ap.one_minus_beta_m * g;
@@ -1801,7 +1818,9 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
     exchange_wait(a.sync, XCHG_DENSE_PARTIALS);  // every process's partial gradients are complete
     const float base_alpha = *a.step_size;
     const size_t W = a.row_width, total = a.n_own * W;
-    const bool vec = ((W | a.bounds[1] | a.bounds[2] | a.bounds[3]) & 3) == 0;
+    size_t all_bounds = W;
+    for (int p = 1; p <= kDenseParams; ++p) all_bounds |= a.bounds[p];
+    const bool vec = (all_bounds & 3) == 0;
     if (vec) {
         for (size_t le = 4 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x); le < total; le += 4 * (size_t)gridDim.x * blockDim.x) {
             const size_t j = le / W, e = (j * a.n_replica + self) * W + (le - j * W);  // slot index -> dense index
@@ -1811,7 +1830,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
                 const float4 t = *reinterpret_cast<const float4*>(a.partials[s] + le);
                 g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
             }
-            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : (e < a.bounds[3] ? 2 : 3));
+            const int p = dense_param_of(a, e);
             const float alpha = base_alpha * a.lr_modifier[p];
             float4 x = *reinterpret_cast<const float4*>(a.replicas[self] + e);
             float4 m = *reinterpret_cast<const float4*>(a.adam_m + e), v = *reinterpret_cast<const float4*>(a.adam_v + e);
@@ -1832,7 +1851,7 @@ static __global__ void __launch_bounds__(256) k_dense_update(DenseUpdateArgs a, 
             const size_t j = le / W, e = (j * a.n_replica + self) * W + (le - j * W);
             float g = 0.f;
             for (int s = 0; s < a.n_partial; ++s) g += a.partials[s][le];
-            const int p = e < a.bounds[1] ? 0 : (e < a.bounds[2] ? 1 : (e < a.bounds[3] ? 2 : 3));
+            const int p = dense_param_of(a, e);
             const float alpha = base_alpha * a.lr_modifier[p];
             float m = a.adam_m[e], v = a.adam_v[e];
             const float x = dense_adam(a.replicas[self][e], g, m, v, alpha, a.ap);

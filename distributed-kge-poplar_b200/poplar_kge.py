@@ -497,6 +497,11 @@ class Engine:
             w = self.random_normal((m.entity_feature_size, m.embedding_size))
             scale = self.init_scale / np.sqrt(max(1, m.entity_feature_size))
             self.write_variable(f"{prefix}feature_projection", (scale * w).astype(np.float32))
+            if m.feature_mlp_size > 0 and m.entity_feature_size > 0:  # src/python/poplar_kge.py:665-688
+                up = self.random_normal((2 * m.embedding_size, m.feature_mlp_size))
+                self.write_variable(f"{prefix}mlp_up_projection", (self.init_scale / np.sqrt(2 * m.embedding_size) * up).astype(np.float32))
+                down = self.random_normal((m.feature_mlp_size, m.embedding_size))
+                self.write_variable(f"{prefix}mlp_down_projection", (self.init_scale / np.sqrt(m.feature_mlp_size) * down).astype(np.float32))
 
     # -- entity rows ---------------------------------------------------------
 

@@ -31,9 +31,9 @@ def main() -> None:
     kw = dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", correction_weight=1.0, gamma=10.0)
     if variant == "distmult":
         kw = dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid")
-    if variant == "transh":  # the step of separate kernels, a fourth dense parameter, dropout masks per global shard, regularisers
+    if variant == "transh":  # the step of separate kernels, more dense parameters (normals, the MLP's projections), dropout masks per global shard, regularisers
         kw = dict(score_fn="TransH", distance_fn="L1", loss_type="logsigmoid", gamma=6.0, feature_dropout=0.25,
-                  hidden_regularisation=(2.0, 0.02))
+                  hidden_regularisation=(2.0, 0.02), feature_mlp_size=16)
     cfg = StepConfig(n_shard=2 * world, n_entity=400, n_relation_type=8, embedding_size=32, entity_feature_size=16,
                      batch_size=24, a2a_size=10, **kw)
     n_local, n_step, rw, lr = cfg.n_shard // world, 3, 64, 2e-3

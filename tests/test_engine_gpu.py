@@ -122,6 +122,19 @@ CASES = {
                                                  distance_fn="L1", gamma=3.0, loss_type="softmax", correction_weight=1.0,
                                                  share_feature_networks=False),
                                   seed=27),
+    # The feature MLP between the projection and the hidden rows: two more parameters per network, the
+    # value's gradient also flows through the MLP's input, the row update waits for it
+    "mlp_shared": dict(cfg=StepConfig(n_shard=2, n_entity=300, n_relation_type=4, embedding_size=32,
+                                      entity_feature_size=24, batch_size=16, a2a_size=12, score_fn="TransE",
+                                      distance_fn="L2", gamma=6.0, loss_type="softmax", correction_weight=1.0,
+                                      feature_mlp_size=40, hidden_regularisation=(2.0, 0.01),
+                                      learning_rate_modifiers={"mlp_up_projection": 0.5}),
+                       seed=28, feature_dtype="float16"),
+    "mlp_separate_dropout": dict(cfg=StepConfig(n_shard=2, n_entity=200, n_relation_type=4, embedding_size=18,
+                                                entity_feature_size=12, batch_size=8, a2a_size=6, score_fn="DistMult",
+                                                distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
+                                                feature_mlp_size=10, feature_dropout=0.25),
+                                 seed=29),
     "single_shard": dict(cfg=StepConfig(n_shard=1, n_entity=400, n_relation_type=5, embedding_size=64,
                                         entity_feature_size=32, batch_size=64, a2a_size=96, score_fn="TransE",
                                         distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
@@ -202,7 +215,8 @@ def test_single_step_matches_oracle(name, warm, tensor_cores):
             assert_close(d_hidden, last["d_feature_hidden"][s], RTOL, f"{name}: d hidden[{s}]")
     dense = engine.debug_fetch("dense_grad", 0, 1 << 24)
     n_rel = cfg.n_relation_type * D
-    assert dense.size == n_rel * (2 if cfg.score_fn == "TransH" else 1) + len(cfg.projection_names) * cfg.entity_feature_size * D * (cfg.entity_feature_size > 0)
+    n_net = len(cfg.projection_names) * (cfg.entity_feature_size > 0)
+    assert dense.size == n_rel * (2 if cfg.score_fn == "TransH" else 1) + n_net * (cfg.entity_feature_size + 3 * cfg.feature_mlp_size) * D
     _compare_state(engine, cfg, oracle, name, RTOL, case.get("rel_rtol"))
     engine.close()
 
@@ -224,7 +238,7 @@ def test_exchange_routing_is_bit_exact():
     engine.close()
 
 
-@pytest.mark.parametrize("name", ["config1_transe_l1", "transe_l2_softmax_features", "complex_softmax", "dropout_shared", "transh_logsigmoid"])
+@pytest.mark.parametrize("name", ["config1_transe_l1", "transe_l2_softmax_features", "complex_softmax", "dropout_shared", "transh_logsigmoid", "mlp_shared"])
 def test_step_loop_and_graph_replay(name):
     """Several steps per call, twice: replaying the captured graph gives bit-identical results to
     plain launches, and both follow the oracle."""

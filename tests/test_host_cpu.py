@@ -49,8 +49,10 @@ def test_settings_errors_precede_the_device():
         capi.CEngine({**good, "training.learning_rate_modifiers": {"nope": 2.0}})
     with pytest.raises(ValueError, match="Key not found 'training.loss.correction_weight'"):
         capi.CEngine({**good, "training.loss.type": "softmax"})
-    with pytest.raises(ValueError, match="not supported by this engine"):
-        capi.CEngine({**good, "model.feature_mlp_size": 64})
+    with pytest.raises(ValueError, match="'model.feature_dropout' must be in"):
+        capi.CEngine({**good, "model.feature_dropout": 1.0})
+    with pytest.raises(ValueError, match="regularisation.power' must be at least 1"):
+        capi.CEngine({**good, "training.hidden_regularisation.power": 0.5, "training.hidden_regularisation.weight": 0.1})
 
 
 def test_attach_failure_is_a_runtime_error():

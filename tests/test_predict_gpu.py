@@ -53,11 +53,15 @@ def _clear(score, tol=1e-5):
     return np.concatenate([gaps[:, :1], gaps[:, :-1] & gaps[:, 1:], gaps[:, -1:]], axis=1)
 
 
+@pytest.mark.parametrize("mlp", [0, 21], ids=["plain", "mlp"])
 @pytest.mark.parametrize("score_fn,distance_fn", [("TransE", "L1"), ("TransE", "L2"), ("DistMult", "MatMul"), ("ComplEx", "MatMul"), ("RotatE", "L2"),
                                                   ("TransH", "L1")])
-def test_predict_matches_oracle(score_fn, distance_fn):
-    cfg = StepConfig(n_shard=3, n_entity=700, n_relation_type=6, embedding_size=32, entity_feature_size=12,
-                     batch_size=6, a2a_size=4, score_fn=score_fn, distance_fn=distance_fn, gamma=5.0)
+def test_predict_matches_oracle(score_fn, distance_fn, mlp):
+    if mlp and (score_fn, distance_fn) not in (("TransE", "L2"), ("TransH", "L1")):
+        pytest.skip("the feature MLP is covered with two of the score functions")
+    cfg = StepConfig(n_shard=3, n_entity=700, n_relation_type=6, embedding_size=36, entity_feature_size=12,
+                     batch_size=6, a2a_size=4, score_fn=score_fn, distance_fn=distance_fn, gamma=5.0, feature_mlp_size=mlp,
+                     share_feature_networks=not mlp)
     hr, n_best = 8, 5
     state = random_state(cfg, 21, warm=False)
     engine = capi.CEngine(engine_settings(cfg, rw_batch=RW))
