@@ -590,11 +590,12 @@ inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int
         if (sync.world > 1) return cudaErrorNotSupported;
         return launch_dependent(k_score<FN>, dim3((T + 63) / 64, (B + 31) / 32), dim3(128), 0, stream, P, Tl, raw, B, T, D);
     }
-    static bool configured = false;  // one attribute call per instantiation and process is enough
-    if (!configured) {
+    static bool configured[kMaxDeviceOrdinals] = {};  // one attribute call per instantiation and device is enough
+    const int slot = current_device_slot();
+    if (slot < 0 || !configured[slot]) {
         cudaError_t err = cudaFuncSetAttribute(k_score_wide<FN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreWideSmem);
         if (err != cudaSuccess) return err;
-        configured = true;
+        if (slot >= 0) configured[slot] = true;
     }
     return launch_dependent(k_score_wide<FN>, dim3((T + 31) / 32, (B + 31) / 32), dim3(32 * kScoreWarps), kScoreWideSmem, stream,
                             P, Tl, raw, B, T, D, sync);

@@ -24,6 +24,15 @@ __device__ __forceinline__ void grid_dependency_sync() {
 }
 #endif
 
+// State that CUDA keeps per device (function attributes, occupancy answers) is cached per device:
+// the slot of the current device, or -1 when it cannot be cached (then the caller asks CUDA again).
+constexpr int kMaxDeviceOrdinals = 64;
+inline int current_device_slot() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDeviceOrdinals) return -1;
+    return device;
+}
+
 // Process-wide switch (on by default; KGE_NO_DEPENDENT_LAUNCH=1 in the environment turns it off).
 bool dependent_launch_enabled();
 

@@ -993,12 +993,13 @@ static __global__ void __launch_bounds__(256) k_tc_reduce(const __grid_constant_
 // Host side: grid = (ceil(M / 128), ceil(N / BN), splits).
 template <int BN, bool A_EXACT, bool ROWSUM>
 inline cudaError_t launch(const GemmArgs& g, int splits, cudaStream_t stream) {
-    static bool configured = false;  // one attribute call per instantiation and process is enough
+    static bool configured[kMaxDeviceOrdinals] = {};  // one attribute call per instantiation and device is enough
+    const int slot = current_device_slot();
     auto kernel = k_tc_gemm<BN, A_EXACT, ROWSUM>;
-    if (!configured) {
+    if (slot < 0 || !configured[slot]) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<BN>());
         if (err != cudaSuccess) return err;
-        configured = true;
+        if (slot >= 0) configured[slot] = true;
     }
     dim3 grid((g.M + kBM - 1) / kBM, (g.N + BN - 1) / BN, splits);
     return launch_dependent(kernel, grid, dim3(kThreads), smem_bytes<BN>(), stream, g);
@@ -1045,10 +1046,11 @@ inline cudaError_t make_operand_map(const Operand& op, int mn, int k, int rows, 
 // How many clusters of `splits` blocks of the pipelined kernel the device can hold at once
 // (a cluster needs its blocks on SMs of one GPC, one block per SM).  0 when the query fails.
 inline int max_resident_clusters(int splits) {
-    static int cached[kMaxClusterSplits + 1] = {0};
-    static bool known[kMaxClusterSplits + 1] = {false};
+    static int cached[kMaxDeviceOrdinals][kMaxClusterSplits + 1] = {};
+    static bool known[kMaxDeviceOrdinals][kMaxClusterSplits + 1] = {};
     if (splits < 1 || splits > kMaxClusterSplits) return 0;
-    if (known[splits]) return cached[splits];
+    const int slot = current_device_slot();
+    if (slot >= 0 && known[slot][splits]) return cached[slot][splits];
     auto kernel = k_tc_gemm_async<64, false, false>;
     int n = 0;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_async<64>()) == cudaSuccess) {
@@ -1068,8 +1070,10 @@ inline int max_resident_clusters(int splits) {
             (void)cudaGetLastError();
         }
     }
-    known[splits] = true;
-    cached[splits] = n;
+    if (slot >= 0) {
+        known[slot][splits] = true;
+        cached[slot][splits] = n;
+    }
     return n;
 }
 
@@ -1104,12 +1108,13 @@ inline cudaError_t launch_pair(const GemmArgs* problems, int n_problems, int spl
         }
         return cudaSuccess;
     }
-    static bool configured = false;
+    static bool configured[kMaxDeviceOrdinals] = {};
+    const int slot = current_device_slot();
     auto kernel = k_tc_gemm_async<BN, A_EXACT, ROWSUM>;
-    if (!configured) {
+    if (slot < 0 || !configured[slot]) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_async<BN>());
         if (err != cudaSuccess) return err;
-        configured = true;
+        if (slot >= 0) configured[slot] = true;
     }
     GemmPair gp{};
     gp.p[0] = problems[0];

@@ -636,14 +636,6 @@ __device__ __forceinline__ void store_planes4(float* hi, float* lo, size_t e, fl
 // ---------------------------------------------------------------------------
 // Host side
 
-// State that CUDA keeps per device (function attributes, occupancy answers) is cached per device.
-constexpr int kMaxDeviceOrdinals = 64;
-inline int current_device_slot() {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDeviceOrdinals) return -1;
-    return device;
-}
-
 // The map of one plane: boxes of [rows x 32 k] (k-major) or [32 k x 32 mn] (mn-major) under the
 // 128-byte swizzle, zeros outside the matrix.
 inline cudaError_t make_plane_map(const float* base, const PlaneOperand& op, int mn, int k, int rows, CUtensorMap* map) {
