@@ -1447,16 +1447,18 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
                                                                (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}, nullptr}, l, step);
         const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
-        if (cfg_.state_type == ST_F32)
-            KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
-                                                 step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,
-                                                 b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step, entity_lr_mod_, adam_, sync, heavy,
-                                                 (int)R, rr)));
-        else
-            KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_,
-                                                 step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,
-                                                 b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step, entity_lr_mod_, adam_, sync, heavy,
-                                                 (int)R, rr)));
+#define KGE_ENTITY_UPDATE(ST_, EXTRAS_)                                                                                                          \
+    KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<ST_, 4, EXTRAS_>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_, \
+                                         step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,      \
+                                         b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, d_step_size_ + step, entity_lr_mod_, adam_, sync, heavy,       \
+                                         (int)R, rr)))
+        const bool extras = cfg_.regularised() || dropout_on() || mlp_on();
+        if (cfg_.state_type == ST_F32) {
+            if (extras) KGE_ENTITY_UPDATE(float, true); else KGE_ENTITY_UPDATE(float, false);
+        } else {
+            if (extras) KGE_ENTITY_UPDATE(__half, true); else KGE_ENTITY_UPDATE(__half, false);
+        }
+#undef KGE_ENTITY_UPDATE
     }
     KGE_CUDA(cudaGetLastError());
     const bool gather_ahead = step + 1 < cfg_.n_step;
@@ -1720,25 +1722,19 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* first = d_first_slot_ + sidx * R;
         const float* alpha = d_step_size_ + step;
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
+#define KGE_ENTITY_UPDATE(ST_, V_, EXTRAS_)                                                                                                              \
+    KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<ST_, V_, EXTRAS_>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), \
+                                         0, stream_, b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, alpha,  \
+                                         entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))))
+        const bool extras = cfg_.regularised() || dropout_on() || mlp_on();
         if (cfg_.state_type == ST_F32) {
-            if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
-                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
-            else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<float, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
-                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
+            if (vec) { if (extras) KGE_ENTITY_UPDATE(float, 4, true); else KGE_ENTITY_UPDATE(float, 4, false); }
+            else { if (extras) KGE_ENTITY_UPDATE(float, 1, true); else KGE_ENTITY_UPDATE(float, 1, false); }
         } else {
-            if (vec)
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 4>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
-                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
-            else
-                KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<__half, 1>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), 0, stream_,
-                                                b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B,
-                                                b.d_hid_h, b.d_hid_t, alpha, entity_lr_mod_, adam_, sync, heavy, (int)R, with_regularisers(RelationRows{}, l, step))));
+            if (vec) { if (extras) KGE_ENTITY_UPDATE(__half, 4, true); else KGE_ENTITY_UPDATE(__half, 4, false); }
+            else { if (extras) KGE_ENTITY_UPDATE(__half, 1, true); else KGE_ENTITY_UPDATE(__half, 1, false); }
         }
+#undef KGE_ENTITY_UPDATE
     }
     KGE_CUDA(cudaGetLastError());
     if (mlp_on())

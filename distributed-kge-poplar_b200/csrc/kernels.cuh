@@ -1314,7 +1314,9 @@ __device__ __forceinline__ void relation_row_sum(const RelationRows& rr, int rho
     }
 }
 
-template <class ST, int V>
+// EXTRAS: the regularisers' terms, the dropout masks and the deferred row update are compiled in
+// (they cost 20 registers, a third of the resident blocks, which the plain step does not pay).
+template <class ST, int V, bool EXTRAS = false>
 __global__ void __launch_bounds__(64 * kSegmentLanes)
 k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c, RowLayout L,
                 const uint32_t* __restrict__ remote, const uint32_t* __restrict__ perm,
@@ -1431,7 +1433,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         float gv[V];  // the value's gradient: the lookups' sums (+ the regularisers' terms for the value)
 #pragma unroll
         for (int u = 0; u < V; ++u) gv[u] = gh[u] + gt[u];
-        if (rr.reg_val) {
+        if (EXTRAS && rr.reg_val) {
             // gh / gt become the gradients of the feature network's output
 #pragma unroll
             for (int u = 0; u < V; ++u) {
@@ -1440,7 +1442,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
                 if (rr.reg_t) gt[u] += rr.reg_t[o + u];
             }
         }
-        if (rr.drop.threshold) {
+        if (EXTRAS && rr.drop.threshold) {
             // through the dropout of each call: kept elements pass g / (1 - p)
             const uint32_t keep_h = dropout_keep4(rr.drop, 0u, (uint32_t)r, (uint32_t)c >> 2), keep_t = dropout_keep4(rr.drop, 1u, (uint32_t)r, (uint32_t)c >> 2);
 #pragma unroll
@@ -1466,7 +1468,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             d_hid_h[o] = d_hid_t ? gh[0] : gh[0] + gt[0];
             if (d_hid_t) d_hid_t[o] = gt[0];
         }
-        if (rr.defer_grad) {
+        if (EXTRAS && rr.defer_grad) {
 #pragma unroll
             for (int u = 0; u < V; ++u) rr.defer_grad[o + u] = gv[u];
             return;
