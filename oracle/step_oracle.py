@@ -634,7 +634,11 @@ class Oracle:
         adam_update(value, adam_m, adam_v, d_value, alpha * mod, cfg)
         new_rows = np.concatenate([value, adam_m, np.sqrt(adam_v), feat], axis=-1)
         for s in range(n):
-            self.entity_data[s, remote[s]] = new_rows[s]
+            # `remote` names the padding row 0 once per padded slot.  The reference scatters all slots
+            # (setEntityData, :412-417), which leaves open whose update of row 0 lasts; the slots agree
+            # unless dropout gives each its own mask.  Here the first slot's update is kept.
+            _, first = np.unique(remote[s], return_index=True)
+            self.entity_data[s, remote[s][first]] = new_rows[s][first]
         return losses
 
     def train_step_loop(self, lr: float, batch: Dict[str, np.ndarray]) -> np.ndarray:

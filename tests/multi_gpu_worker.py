@@ -31,8 +31,10 @@ def main() -> None:
     kw = dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", correction_weight=1.0, gamma=10.0)
     if variant == "distmult":
         kw = dict(score_fn="DistMult", distance_fn="MatMul", loss_type="logsigmoid")
-    if variant == "transh":  # the step of separate kernels, more dense parameters (normals, the MLP's projections), dropout masks per global shard, regularisers
-        kw = dict(score_fn="TransH", distance_fn="L1", loss_type="logsigmoid", gamma=6.0, feature_dropout=0.25,
+    if variant == "transh":  # the step of separate kernels with a fourth dense parameter (the normals)
+        kw = dict(score_fn="TransH", distance_fn="L1", loss_type="logsigmoid", gamma=6.0)
+    if variant == "mlp":  # more dense parameters (the MLP's projections, pushed to their owners), dropout masks per global shard, regularisers
+        kw = dict(score_fn="TransE", distance_fn="L2", loss_type="softmax", correction_weight=1.0, gamma=10.0, feature_dropout=0.25,
                   hidden_regularisation=(2.0, 0.02), feature_mlp_size=16)
     cfg = StepConfig(n_shard=2 * world, n_entity=400, n_relation_type=8, embedding_size=32, entity_feature_size=16,
                      batch_size=24, a2a_size=10, **kw)
@@ -57,10 +59,12 @@ def main() -> None:
     # update has arrived in this process's memory, so the state can be read straight away.
     got, ref = read_state(engine, cfg, rw, n_local), oracle.get_state()
     d = cfg.embedding_size
-    assert_close(got["entity_data"][..., : 3 * d], ref["entity_data"][mine][..., : 3 * d], 1e-4, f"rank {rank}: rows")
+    assert_close(got["entity_data"][..., : 3 * d], ref["entity_data"][mine][..., : 3 * d], 1e-3 if variant == "transh" else 1e-4, f"rank {rank}: rows")
+    # TransH's gradients are sums of signs (an L1 form): over six steps one rounding flip of a sign moves an entry visibly
+    dense_tol = 1e-3 if variant == "transh" else 1e-4
     for key in ref:
         if key not in ("entity_data", "step"):
-            assert_close(got[key], ref[key], 1e-4, f"rank {rank}: {key}")
+            assert_close(got[key], ref[key], dense_tol, f"rank {rank}: {key}")
     np.testing.assert_array_equal(got["step"], ref["step"])
 
     # ranking across processes, again with no host barrier since the training call

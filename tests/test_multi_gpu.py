@@ -18,7 +18,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("variant", ["l2", "distmult", "transh"])
+@pytest.mark.parametrize("variant", ["l2", "distmult", "transh", "mlp"])
 def test_two_processes_match_the_oracle(variant):
     import torch
 
