@@ -376,6 +376,47 @@ k_route(const float* __restrict__ hid_h, const float* __restrict__ hid_t,
     exchange_signal(sync, XCHG_TAILS, gridDim.x);
 }
 
+// The lookups of the rows with many lookups (the parts k_prepare_segments cut them into for the
+// entity update): block p copies hidden row parts[p].x to the lookups perm[parts[p].y .. parts[p].z),
+// heads (+ or * their relation row) into `pred`, tails into the owning shards' buffers, each with
+// its companion plane.  The hidden kernel's routing epilogue leaves these rows out, so that no
+// single block stores hundreds of copies of one row; this kernel then publishes the tails hand-over.
+// TransE and DistMult (the score functions whose routing is fused).
+static __global__ void __launch_bounds__(256)
+k_route_heavy(const float* __restrict__ hid_h, const float* __restrict__ hid_t, const uint4* __restrict__ parts,
+              const uint32_t* __restrict__ count, const uint32_t* __restrict__ perm, const uint32_t* __restrict__ relation,
+              const float* __restrict__ rel_table, float* const* __restrict__ send_dst, float* const* __restrict__ send_lo_dst,
+              float* __restrict__ pred, float* __restrict__ pred_lo, int B, int a2a, int D, int score_fn, int lo_bf16, ExchangeSync sync) {
+    grid_dependency_sync();
+    if (blockIdx.x < *count) {
+        // every (lookup, 4 columns) pair is one unit of work: all of a part's copies are in flight at once
+        const uint4 part = parts[blockIdx.x];
+        const int quads = D / 4, n_units = (int)(part.z - part.y) * quads;
+        for (int u = threadIdx.x; u < n_units; u += blockDim.x) {
+            const uint32_t q = part.y + (uint32_t)(u / quads), e = perm[q];
+            const int c = (u % quads) * 4;
+            const bool head = e < (uint32_t)B;
+            float4 o = load4((head ? hid_h : hid_t) + (size_t)part.x * D + c);
+            float *dst, *dst_lo;
+            if (head) {
+                const float4 r = load4(rel_table + (size_t)relation[e] * D + c);
+                o = score_fn == SCORE_TRANSE ? make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w)
+                                             : make_float4(o.x * r.x, o.y * r.y, o.z * r.z, o.w * r.w);
+                dst = pred + (size_t)e * D;
+                dst_lo = lo_bf16 ? pred_lo + (size_t)e * D / 2 : pred_lo + (size_t)e * D;
+            } else {
+                const uint32_t j = e - (uint32_t)B, shard = j / (uint32_t)a2a, slot = j - shard * (uint32_t)a2a;
+                dst = send_dst[shard] + (size_t)slot * D;
+                dst_lo = lo_bf16 ? send_lo_dst[shard] + (size_t)slot * D / 2 : send_lo_dst[shard] + (size_t)slot * D;
+            }
+            store4(dst + c, o);
+            if (lo_bf16) store4(reinterpret_cast<__nv_bfloat16*>(dst_lo) + c, o);
+            else store4(dst_lo + c, tf32_lower4(o));
+        }
+    }
+    exchange_signal(sync, XCHG_TAILS, gridDim.x);  // the tail rows are in their consumers' memory
+}
+
 // ---------------------------------------------------------------------------
 // raw[i, j] = sum_k |p_ik - t_jk|  (L1),  sqrt(sum_k (p_ik - t_jk)^2)  (L2),  sum_k p_ik t_jk (dot)
 // src/poplar_extensions/distance.cpp:70-104,151-185 and the codelets' l1dist / l2dist;
@@ -1317,7 +1358,7 @@ __device__ __forceinline__ void relation_row_sum(const RelationRows& rr, int rho
 // EXTRAS: the regularisers' terms, the dropout masks and the deferred row update are compiled in
 // (they cost 20 registers, a third of the resident blocks, which the plain step does not pay).
 template <class ST, int V, bool EXTRAS = false>
-__global__ void __launch_bounds__(64 * kSegmentLanes)
+__global__ void __launch_bounds__(64 * kSegmentLanes, EXTRAS ? 2 : 4)
 k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c, RowLayout L,
                 const uint32_t* __restrict__ remote, const uint32_t* __restrict__ perm,
                 const uint32_t* __restrict__ off,

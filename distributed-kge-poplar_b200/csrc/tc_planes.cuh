@@ -78,7 +78,12 @@ struct RouteArgs {
     int B, a2a, n_shard, score_fn;
     int mode[2];
     int lo_bf16;  // the companion planes hold the bfloat16 rounding of the rows instead of the lower TF32 part
+    // Per gathered row, bit 1 set: the row has so many lookups that they are routed in parts by
+    // k_route_heavy (a row that half of a step's lookups name would otherwise keep one block storing
+    // for 10 us after all others are done).  Null: every row is routed here.
+    const uint32_t* first_slot;
 };
+constexpr uint32_t kRouteSkip = 0xffffffffu;
 constexpr int kRouteMaxLookups = 4096;  // lookups one block may have to route (batch_size + n_shard * a2a_size)
 
 struct PlanePair {
@@ -212,6 +217,8 @@ __device__ __forceinline__ void route_rows(const RouteArgs& rt, int mode, const 
             live[b] = u < n_units;
             const int i = live[b] ? u / kQuads : 0, q = u % kQuads;
             look[b] = s_look[i];
+            live[b] = live[b] && look[b] != kRouteSkip;
+            if (!live[b]) look[b] = 0u;
             const uint32_t e = look[b] & 0xffffu;
             head[b] = e < (uint32_t)rt.B;
             live[b] = live[b] && n0 + q * 4 < D && ((head[b] ? mode & 1 : mode & 2) != 0);
@@ -260,8 +267,9 @@ __device__ __forceinline__ int route_stage(const RouteArgs& rt, int row0, int n_
             const int mid = (lo + hi) >> 1;
             if (s_off[mid] <= q) lo = mid; else hi = mid;
         }
-        s_look[i] = e | ((uint32_t)lo << 16);
-        s_rel[i] = e < (uint32_t)rt.B ? rt.relation[e] : 0u;
+        const bool elsewhere = rt.first_slot && (rt.first_slot[row0 + lo] & 2u);
+        s_look[i] = elsewhere ? kRouteSkip : e | ((uint32_t)lo << 16);
+        s_rel[i] = e < (uint32_t)rt.B && !elsewhere ? rt.relation[e] : 0u;
     }
     return n_look;
 }

@@ -497,11 +497,14 @@ def test_initialise_entities_fills_the_table_from_the_counter_based_generator():
     assert abs(feat.mean()) < 0.05 and 0.95 < feat.std() < 1.05
 
 
+@pytest.mark.parametrize("routed_in_parts", [False, True], ids=["epilogue", "route_heavy"])
 @pytest.mark.parametrize("separate", [False, True], ids=["shared_net", "two_nets"])
-def test_popular_rows_are_summed_in_parts(separate):
+def test_popular_rows_are_summed_in_parts(separate, routed_in_parts, monkeypatch):
     """Skewed lookups: one gathered row is named by most heads and tails of a shard, a second one by
-    about a hundred (entity popularity in real graphs is Zipf-like).  Rows with more than 64 lookups
-    are cut into parts that separate blocks sum; the result must match the oracle like any other."""
+    about a hundred (entity popularity in real graphs is Zipf-like).  Rows with many lookups are cut
+    into parts that separate blocks sum, and (the default with four or more processes, forced here)
+    whose lookups a kernel of its own routes; the result must match the oracle like any other."""
+    monkeypatch.setenv("KGE_ROUTE_POPULAR_ROWS", "1" if routed_in_parts else "0")
     cfg = StepConfig(n_shard=2, n_entity=700, n_relation_type=6, embedding_size=64, entity_feature_size=32,
                      batch_size=256, a2a_size=160, score_fn="TransE", distance_fn="L2", gamma=8.0,
                      loss_type="softmax", correction_weight=1.0, share_feature_networks=not separate)
