@@ -2023,6 +2023,9 @@ void Engine::ensure_predict_buffers() {
         p_mlp_pre_ = (float*)device_alloc(rows * cfg_.mlp * 4);
         p_mlp_out_ = (float*)device_alloc(rows * D * 4);
     }
+    p_cand_ = (unsigned long long*)device_alloc(Q * kTopkCandidates * sizeof(unsigned long long));
+    p_cand_count_ = (int*)device_alloc(Q * sizeof(int));
+    KGE_CUDA(cudaMemset(p_cand_count_, 0, Q * sizeof(int)));
     d_iota_ = (uint32_t*)device_alloc((size_t)cfg_.predict_hr * 4);
     std::vector<uint32_t> iota(cfg_.predict_hr);
     for (unsigned i = 0; i < cfg_.predict_hr; ++i) iota[i] = i;
@@ -2031,6 +2034,16 @@ void Engine::ensure_predict_buffers() {
         b.topk_state = (unsigned long long*)device_alloc(Q * kTopkCapacity * sizeof(unsigned long long));
         b.topk_count = (int*)device_alloc(Q * sizeof(int));
     }
+}
+
+// Merges the scores of rows start .. start + c - 1 (in p_raw_) into every query's best list: the filter at
+// full bandwidth, then one warp per query on what it left.
+void Engine::launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp) {
+    const unsigned Q = (unsigned)tp.n_query;
+    const dim3 fgrid(std::max(1u, std::min(ceil_div(c, 4 * 256), 8u)), Q);
+    KGE_LAUNCH("predict_topk", k_topk_filter<<<fgrid, 256, 0, stream_>>>(p_raw_, (int)c, start, last, b.topk_state, b.topk_count, p_cand_, p_cand_count_, tp));
+    KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div(Q, 4), 128, 0, stream_>>>(p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp, p_cand_,
+                                                                                 p_cand_count_));
 }
 
 // Ranks every real row of the local shards as a tail for the queries of all shards
@@ -2116,8 +2129,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
             const unsigned c = std::min<uint32_t>(predict_chunk_, last - start + 1);
             if (predict_planes_) {
                 predict_pass_planes(b, start, c, queries, (unsigned)Q, W_tail == W_head ? 0 : 1);
-                KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div((unsigned)Q, 4), 128, 0, stream_>>>(
-                                               p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp));
+                launch_topk(b, c, start, last, tp);
                 continue;
             }
             dim3 hgrid(ceil_div(c, 64), dtiles, 1);
@@ -2131,8 +2143,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
                                                 queries, queries + Q * D, p_chunk_hidden_, p_raw_, nullptr, nullptr, (int)Q, (int)c, (int)D, ExchangeSync{}));
             } else
             KGE_LAUNCH("predict_score", KGE_CUDA(launch_score(cfg_.dist_fn, queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D, stream_)));
-            KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div((unsigned)Q, 4), 128, 0, stream_>>>(
-                                           p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp));
+            launch_topk(b, c, start, last, tp);
         }
         KGE_LAUNCH("predict_finish", k_topk_finish<<<(unsigned)Q, 128, 0, stream_>>>(
                                          b.topk_state, b.topk_count, (int)Q, (int)hr, (int)nb, b.predict_score_dst,

@@ -262,6 +262,9 @@ class Engine {
     void launch_mlp_forward(const uint8_t* rows, const uint32_t* index, uint32_t start, unsigned n_rows, int net, float* hid,
                             float* cat, float* pre, float* out);
     void launch_mlp_backward(unsigned l, unsigned step);
+    unsigned long long* p_cand_ = nullptr;  // [Q, kTopkCandidates] a batch's keys above each query's cut-off
+    int* p_cand_count_ = nullptr;
+    void launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp);
     float *p_mlp_cat_ = nullptr, *p_mlp_pre_ = nullptr, *p_mlp_out_ = nullptr;  // predict's MLP buffers
     bool heavy_route_ = false;  // rows with many lookups are routed in parts by k_route_heavy (KGE_ROUTE_POPULAR_ROWS=0: by the hidden kernel's epilogue)
     uint32_t* d_step_key_ = nullptr;   // [n_step] numbers of the staged training steps (keys of the dropout masks)

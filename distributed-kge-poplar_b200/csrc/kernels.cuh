@@ -1998,12 +1998,65 @@ struct TopkParams {
     float gamma;
 };
 
+// A batch of scores is merged in two kernels.  k_topk_filter reads all of it at full bandwidth
+// (four scores per thread) and leaves, per query, the keys that beat the query's cut-off as it
+// stands before the batch in `cand` (at most kTopkCandidates; the count goes on past that).
+// k_topk_update, one warp per query, then merges those few keys; a query whose candidates did not
+// fit (the first batches, before a cut-off exists) scans its row of scores itself, as it would
+// without the filter.  The candidates' order in `cand` depends on timing, the merged result does
+// not: it is the n_best largest keys of the old list and the candidates, and keys are unique.
+constexpr int kTopkCandidates = 1024;
+
+static __global__ void __launch_bounds__(256)
+k_topk_filter(const float* __restrict__ raw, int n_cols, uint32_t first_row, uint32_t last_valid_row,
+              const unsigned long long* __restrict__ state, const int* __restrict__ counts,
+              unsigned long long* __restrict__ cand, int* __restrict__ cand_count, TopkParams tp) {
+    const int q = blockIdx.y, lane = threadIdx.x & 31;
+    const unsigned long long cutoff = counts[q] >= tp.n_best ? state[(size_t)q * kTopkCapacity + tp.n_best - 1] : 0ull;
+    if (cutoff == 0ull) {  // no cut-off yet: every score is a candidate, the query scans its row itself
+        if (blockIdx.x == 0 && threadIdx.x == 0) cand_count[q] = kTopkCandidates + 1;
+        return;
+    }
+    const float* __restrict__ row = raw + (size_t)q * n_cols;
+    const bool vec = (n_cols & 3) == 0;
+    // a warp walks 128 consecutive scores at a time; its lanes stay together for the ballots
+    for (int w0 = 4 * (blockIdx.x * 256 + (threadIdx.x & ~31)); w0 < n_cols; w0 += 4 * 256 * gridDim.x) {
+        const int j0 = w0 + 4 * lane;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (j0 < n_cols) {
+            if (vec) {
+                const float4 x = *reinterpret_cast<const float4*>(row + j0);
+                v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+            } else {
+                for (int u = 0; u < 4 && j0 + u < n_cols; ++u) v[u] = row[j0 + u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u;
+            unsigned long long key = 0ull;
+            if (j < n_cols && first_row + (uint32_t)j <= last_valid_row)
+                key = topk_key(tp.score_is_gamma_minus ? tp.gamma - v[u] : v[u], first_row + (uint32_t)j);
+            const bool pass = key > cutoff;
+            const unsigned mask = __ballot_sync(0xffffffffu, pass);
+            if (mask == 0) continue;
+            int base = 0;
+            if (lane == __ffs(mask) - 1) base = atomicAdd(cand_count + q, __popc(mask));  // one addition per warp
+            base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
+            const int slot = base + __popc(mask & ((1u << lane) - 1));
+            if (pass && slot < kTopkCandidates) cand[(size_t)q * kTopkCandidates + slot] = key;
+        }
+    }
+}
+
 // raw [n_query, n_cols] holds distances / dot products against rows first_row .. first_row+n_cols-1;
 // rows above last_valid_row are padding of the shard and are skipped (src/poplar_kge.cpp:836-842).
 // state [n_query, kTopkCapacity] keys, counts [n_query].  4 warps per block, one query each.
+// cand / cand_count (may be null): the filter's output for this batch; the counts are cleared for the next.
 static __global__ void __launch_bounds__(128)
 k_topk_update(const float* __restrict__ raw, int n_cols, uint32_t first_row, uint32_t last_valid_row,
-              unsigned long long* __restrict__ state, int* __restrict__ counts, TopkParams tp) {
+              unsigned long long* __restrict__ state, int* __restrict__ counts, TopkParams tp,
+              const unsigned long long* __restrict__ cand, int* __restrict__ cand_count) {
     __shared__ unsigned long long buffers[4][kTopkCapacity];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = blockIdx.x * 4 + warp;
@@ -2014,6 +2067,36 @@ k_topk_update(const float* __restrict__ raw, int n_cols, uint32_t first_row, uin
     for (int i = lane; i < kTopkCapacity; i += 32) buf[i] = i < count ? mine[i] : 0ull;
     __syncwarp();
     unsigned long long cutoff = count >= tp.n_best ? buf[tp.n_best - 1] : 0ull;
+    const int n_cand = cand_count ? cand_count[q] : kTopkCandidates + 1;
+    __syncwarp();
+    if (cand_count && lane == 0) cand_count[q] = 0;
+    if (n_cand == 0) return;  // nothing in this batch beats the cut-off: the list stands
+    if (n_cand <= kTopkCandidates) {
+        // the filter's keys for this query: all beat the old cut-off; the cut-off rises as they are merged
+        const unsigned long long* __restrict__ keys = cand + (size_t)q * kTopkCandidates;
+        for (int base = 0; base < n_cand; base += 32) {
+            const unsigned long long key = base + lane < n_cand ? keys[base + lane] : 0ull;
+            const bool pass = key > cutoff;
+            if (__ballot_sync(0xffffffffu, pass) == 0) continue;
+            if (count + 32 > kTopkCapacity) {
+                warp_sort_desc(buf);
+                count = min(count, tp.n_best);
+                for (int i = count + lane; i < kTopkCapacity; i += 32) buf[i] = 0ull;
+                __syncwarp();
+                cutoff = count >= tp.n_best ? buf[tp.n_best - 1] : 0ull;
+            }
+            const bool still = pass && key > cutoff;
+            const unsigned mask2 = __ballot_sync(0xffffffffu, still);
+            if (still) buf[count + __popc(mask2 & ((1u << lane) - 1))] = key;
+            count += __popc(mask2);
+            __syncwarp();
+        }
+        warp_sort_desc(buf);
+        count = min(count, tp.n_best);
+        for (int i = lane; i < kTopkCapacity; i += 32) mine[i] = i < count ? buf[i] : 0ull;
+        if (lane == 0) counts[q] = count;
+        return;
+    }
     const float* __restrict__ row = raw + (size_t)q * n_cols;
     constexpr int kAhead = 8;  // scores fetched before the first of them is looked at: the loads overlap
     for (int base0 = 0; base0 < n_cols; base0 += 32 * kAhead) {
