@@ -729,25 +729,33 @@ void Engine::stage_batch(std::vector<HostArray>& arrays) {
                 fail(KGE_INVALID_ARGUMENT, msg() << "'" << a.name << "' holds index " << p[i] << " at position " << i
                                                  << ", which is not below " << what << " (" << limit << ")");
     };
-    check_below(remote, cfg_.n_entity, "model.n_entity");
-    check_below(a2a, (uint32_t)R, "the number of gathered rows");
-    check_below(head, (uint32_t)R, "the number of gathered rows");
-    check_below(relation, cfg_.n_relation_type, "model.n_relation_type");
-    check_below(tail, (uint32_t)T, "n_shard * a2a_size");
-
-    uint8_t* stage = pinned_;
-    auto upload = [&](const HostArray& a, uint32_t* dst) {
-        const size_t bytes = a.count() * 4;
-        std::memcpy(stage, a.data, bytes);
-        KGE_CUDA(cudaMemcpyAsync(dst, stage, bytes, cudaMemcpyHostToDevice, stream_));
-        stage += bytes;
-    };
+    // One pass per stream: copy into the pinned buffer and take the maximum (a loop without an exit,
+    // which the compiler vectorises); only a stream with a bad index is walked again for its position.
+    // A batch that fails a check is not staged: the engine refuses to train until one passes all five.
+    staged_ = false;
     KGE_CUDA(cudaStreamSynchronize(stream_));  // the pinned buffer may still be in flight
-    upload(remote, d_remote_);
-    upload(a2a, d_a2a_);
-    upload(head, d_head_);
-    upload(relation, d_relation_);
-    upload(tail, d_tail_);
+    uint8_t* stage = pinned_;
+    struct Upload { const HostArray* a; uint32_t* dst; uint32_t limit; const char* what; };
+    const Upload uploads[5] = {{&remote, d_remote_, cfg_.n_entity, "model.n_entity"},
+                               {&a2a, d_a2a_, (uint32_t)R, "the number of gathered rows"},
+                               {&head, d_head_, (uint32_t)R, "the number of gathered rows"},
+                               {&relation, d_relation_, cfg_.n_relation_type, "model.n_relation_type"},
+                               {&tail, d_tail_, (uint32_t)T, "n_shard * a2a_size"}};
+    for (const Upload& u : uploads) {
+        const uint32_t* __restrict__ src = static_cast<const uint32_t*>(u.a->data);
+        uint32_t* __restrict__ out = reinterpret_cast<uint32_t*>(stage);
+        const size_t count = u.a->count();
+        uint32_t highest = 0;
+        for (size_t i = 0; i < count; ++i) {
+            const uint32_t v = src[i];
+            out[i] = v;
+            highest = v > highest ? v : highest;
+        }
+        if (highest >= u.limit) check_below(*u.a, u.limit, u.what);
+        // the transfer of this stream runs while the next one is copied and checked
+        KGE_CUDA(cudaMemcpyAsync(u.dst, stage, count * 4, cudaMemcpyHostToDevice, stream_));
+        stage += count * 4;
+    }
     prepare_staged();
 }
 
