@@ -290,7 +290,7 @@ int kge_op_scatter_add_rows(const float* grad_rows, const uint32_t* indices, siz
         // All n lookups are passed as "head" lookups; there are no tail and no relation lookups.
         k_prepare_segments<<<1, 512>>>(di.as<uint32_t>(), di.as<uint32_t>(), nullptr, nullptr, (int)n, 0,
                                        (int)rows, 0, dperm.as<uint32_t>(), doff.as<uint32_t>(),
-                                       nullptr, nullptr, nullptr, nullptr, nullptr);
+                                       nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
         k_segment_sum_rows<<<(unsigned)rows, 128>>>(dg.as<float>(), dperm.as<uint32_t>(), doff.as<uint32_t>(), width,
                                                     dout.as<float>());
         finish_kernels();
@@ -606,7 +606,15 @@ int kge_microbench_rows(int kind, size_t table_rows, size_t d, const uint32_t* i
         KGE_CUDA(gather());
         finish_kernels();
         const AdamParams ap{0.9f, 0.999f, 0.1f, 0.001f, 1e-8f, 0.f};
-        const HeavyRows heavy{nullptr, heavy_count.as<uint32_t>(), nullptr, nullptr};
+        // the rows' descriptors, as k_prepare_segments leaves them: one lookup per row, every row writes
+        std::vector<uint4> info(2 * n);
+        for (size_t i = 0; i < n; ++i) {
+            info[2 * i] = make_uint4((uint32_t)i, 1u, 1u, indices[i]);
+            info[2 * i + 1] = make_uint4((uint32_t)i, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+        }
+        DeviceBuffer row_info(2 * n * sizeof(uint4));
+        to_device(row_info, info.data(), 2 * n * sizeof(uint4));
+        const HeavyRows heavy{nullptr, heavy_count.as<uint32_t>(), nullptr, nullptr, row_info.as<uint4>()};
         *mean_us = timed_launches(repeat, [&] {
             return launch_dependent(k_entity_update<float, 4>, dim3((unsigned)(kHeavySlots + blocks_for(n, kRowsPerBlock))), dim3(64 * kSegmentLanes), 0, nullptr, table.as<uint8_t>(),
                                     rows_c.as<uint8_t>(), L, idx.as<uint32_t>(), perm.as<uint32_t>(), off.as<uint32_t>(), first.as<uint32_t>(),
@@ -710,7 +718,7 @@ int kge_op_scatter_add_rows_noalloc(const float* grad_rows, const uint32_t* indi
         // Every entry the second kernel reads (perm[0, n) and offsets[0, rows]) is rewritten by the
         // first, so nothing left by an earlier call is ever read and nothing needs clearing.
         k_prepare_segments<<<1, 512, 0, stream>>>(indices, indices, nullptr, nullptr, (int)n, 0, (int)rows, 0, scratch->perm,
-                                                  scratch->offsets, nullptr, nullptr, nullptr, nullptr, nullptr);
+                                                  scratch->offsets, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
         k_segment_sum_rows<<<(unsigned)rows, 128, 0, stream>>>(grad_rows, scratch->perm, scratch->offsets, width, grad_table);
         KGE_CUDA(cudaGetLastError());
     });

@@ -522,6 +522,7 @@ void Engine::allocate() {
     d_rel_off_ = (uint32_t*)device_alloc(steps * (cfg_.n_relation_type + 1) * 4);
     d_first_slot_ = (uint32_t*)device_alloc(steps * R * 4);
     d_heavy_parts_ = (uint4*)device_alloc(steps * kHeavySlots * sizeof(uint4));
+    d_row_info_ = (uint4*)device_alloc(steps * 2 * R * sizeof(uint4));
     d_heavy_count_ = (uint32_t*)device_alloc(steps * 4);
     KGE_CUDA(cudaMemset(d_heavy_count_, 0, steps * 4));
     d_step_size_ = (float*)device_alloc(cfg_.n_step * 4);
@@ -765,7 +766,7 @@ void Engine::prepare_staged() {
     KGE_CUDA(cudaEventRecord(ev_stage_[0], stream_));
     k_prepare_segments<<<(unsigned)(n * S), 512, 0, stream_>>>(
         d_head_, d_a2a_, d_relation_, d_remote_, (int)B, (int)T, (int)R, (int)cfg_.n_relation_type, d_ent_perm_,
-        d_ent_off_, d_rel_perm_, d_rel_off_, d_first_slot_, split_popular_rows_ ? d_heavy_parts_ : nullptr, d_heavy_count_);
+        d_ent_off_, d_rel_perm_, d_rel_off_, d_first_slot_, split_popular_rows_ ? d_heavy_parts_ : nullptr, d_heavy_count_, d_row_info_);
     KGE_CUDA(cudaGetLastError());
     KGE_CUDA(cudaEventRecord(ev_stage_[1], stream_));
     staged_ = true;
@@ -1469,7 +1470,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
     for (unsigned l = 0; l < n_local_; ++l) {
         ShardBuffers& b = shards_[l];
         const size_t sidx = (size_t)l * cfg_.n_step + step;
-        const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
+        const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter, d_row_info_ + sidx * 2 * R};
         const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
                                                                (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}, nullptr}, l, step);
         const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
@@ -1747,7 +1748,7 @@ void Engine::launch_one_step(unsigned step) {
         const uint32_t* off = d_ent_off_ + sidx * (R + 1);
         const uint32_t* first = d_first_slot_ + sidx * R;
         const float* alpha = d_step_size_ + step;
-        const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter};
+        const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter, d_row_info_ + sidx * 2 * R};
 #define KGE_ENTITY_UPDATE(ST_, V_, EXTRAS_)                                                                                                              \
     KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<ST_, V_, EXTRAS_>, dim3(ceil_div(R, kRowsPerBlock) + kHeavySlots), dim3(64 * kSegmentLanes), \
                                          0, stream_, b.table, rows_c, layout_, remote, perm, off, first, b.d_head, b.grad_recv, (int)B, b.d_hid_h, b.d_hid_t, alpha,  \

@@ -255,6 +255,7 @@ class Engine {
     uint32_t *d_ent_perm_ = nullptr, *d_ent_off_ = nullptr, *d_rel_perm_ = nullptr,
              *d_rel_off_ = nullptr, *d_first_slot_ = nullptr, *d_heavy_count_ = nullptr;
     uint4* d_heavy_parts_ = nullptr;
+    uint4* d_row_info_ = nullptr;  // [n_local * n_step][R][2] per gathered row: offsets, flags, table row, first four lookups
     float *d_step_size_ = nullptr, *d_loss_total_ = nullptr, *d_loss_last_ = nullptr;
     unsigned* d_loss_counter_ = nullptr;
     size_t transh_score_smem() const { return (size_t)2 * kTranshRows * cfg_.d * sizeof(float); }

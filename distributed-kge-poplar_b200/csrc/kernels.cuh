@@ -1030,7 +1030,7 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
                    int T, int R, int n_rel, uint32_t* __restrict__ ent_perm,
                    uint32_t* __restrict__ ent_off, uint32_t* __restrict__ rel_perm,
                    uint32_t* __restrict__ rel_off, uint32_t* __restrict__ first_slot,
-                   uint4* __restrict__ heavy_parts, uint32_t* __restrict__ heavy_count) {
+                   uint4* __restrict__ heavy_parts, uint32_t* __restrict__ heavy_count, uint4* __restrict__ row_info) {
     __shared__ unsigned long long keys[kMaxSortItems];
     const int s = blockIdx.x;
     head += (size_t)s * B;
@@ -1085,7 +1085,7 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
         const bool first = i == 0 || (keys[i - 1] >> 32) != (keys[i] >> 32);
         first_slot[(uint32_t)keys[i]] = first ? 1u : 0u;
     }
-    if (!heavy_parts) return;
+    if (heavy_parts) {
     // Rows with many lookups are cut into parts for k_entity_update (bit 1 of first_slot marks them).
     // All threads look for such rows (there are at most (B + T) / kHeavyMin of them); one thread
     // then orders them by row, so that the slots do not depend on the timing, and hands out the parts.
@@ -1123,6 +1123,18 @@ k_prepare_segments(const uint32_t* __restrict__ head, const uint32_t* __restrict
             used += parts;
         }
         heavy_count[s] = (uint32_t)used;
+    }
+    }
+    if (!row_info) return;
+    // A row's descriptor for k_entity_update: one sector holds what four scattered loads would fetch.
+    __syncthreads();
+    row_info += (size_t)s * 2 * R;
+    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+        const uint32_t q0 = ent_off[r], count = ent_off[r + 1] - q0;
+        uint32_t e[4];
+        for (int u = 0; u < 4; ++u) e[u] = (uint32_t)u < count ? ent_perm[q0 + u] : 0xffffffffu;
+        row_info[2 * r] = make_uint4(q0, count, first_slot[r], remote[r]);
+        row_info[2 * r + 1] = make_uint4(e[0], e[1], e[2], e[3]);
     }
 }
 
@@ -1284,6 +1296,10 @@ struct HeavyRows {
     const uint32_t* count;   // parts in use
     float* partial;          // [kHeavySlots][2][D] sums of a part: head lookups | tail lookups
     unsigned* counter;       // [kHeavySlots] parts of a row that have arrived (indexed by the row's first slot)
+    // Optional, [R][2]: everything a row's warp needs before it can load gradient rows, in one 32-byte
+    // sector: {first lookup's position, lookups, first_slot word, table row} and the row's first four
+    // lookups (k_prepare_segments writes it); null: the warp reads off / first_slot / remote / perm.
+    const uint4* row_info;
 };
 
 // The relation part of a shard's dense gradient, summed by blocks appended to the entity update's
@@ -1395,20 +1411,28 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
     const int col = threadIdx.x & 63, lane = threadIdx.x >> 6;
     const bool helper = (int)blockIdx.x < kHeavySlots;
     int r;
-    uint32_t q0, q1, info = 0;
+    uint32_t q0, q1, info = 0, slot_word;
+    size_t row;
+    uint4 first4 = make_uint4(0u, 0u, 0u, 0u);
     if (helper) {
         if (blockIdx.x >= *heavy.count) return;
         const uint4 h = heavy.parts[blockIdx.x];
         r = (int)h.x; q0 = h.y; q1 = h.z; info = h.w;
+        slot_word = first_slot[r]; row = remote[r];
     } else {
         // one warp per gathered row: nothing in a row's update needs more than a warp, and a block of
         // eight independent warps keeps eight rows' loads in flight
         r = ((int)blockIdx.x - kHeavySlots) * kRowsPerBlock + (int)(threadIdx.x >> 5);
         if (r >= R) return;
-        if (first_slot[r] & 2u) return;  // its lookups are summed part by part by the first blocks
-        q0 = off[r]; q1 = off[r + 1];
+        if (heavy.row_info) {
+            const uint4 a = heavy.row_info[2 * r];
+            first4 = heavy.row_info[2 * r + 1];
+            q0 = a.x; q1 = a.x + a.y; slot_word = a.z; row = a.w;
+        } else {
+            slot_word = first_slot[r]; q0 = off[r]; q1 = off[r + 1]; row = remote[r];
+        }
+        if (slot_word & 2u) return;  // its lookups are summed part by part by the first blocks
     }
-    const size_t row = remote[r];
     ST* __restrict__ xv = reinterpret_cast<ST*>(table + row * L.row_bytes);
     ST* __restrict__ mv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_m);
     ST* __restrict__ qv = reinterpret_cast<ST*>(table + row * L.row_bytes + L.off_q);
@@ -1417,7 +1441,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
     const ST* __restrict__ ms = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes + L.off_m);
     const ST* __restrict__ qs = reinterpret_cast<const ST*>(rows_c + (size_t)r * L.row_bytes + L.off_q);
     const float alpha = *step_size * lr_modifier;
-    const bool writes_row = (first_slot[r] & 1u) != 0;
+    const bool writes_row = (slot_word & 1u) != 0;
 
     // Sums of the lookups [q0, q1) for the columns c .. c+V-1, separately for head and tail lookups;
     // complete in the threads of lane 0.  Lane l sums the lookups q0 + l, q0 + l + lanes, ... in
@@ -1571,8 +1595,12 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
             for (uint32_t q = q0; q < q1; q += 4) {
                 uint32_t e[4];
                 float4 ga[4], gb[4];
+                if (heavy.row_info && q == q0) {  // the first four lookups came with the row's descriptor
+                    e[0] = first4.x; e[1] = first4.y; e[2] = first4.z; e[3] = first4.w;
+                } else {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) e[u] = q + u < q1 ? perm[q + u] : 0xffffffffu;
+                    for (int u = 0; u < 4; ++u) e[u] = q + u < q1 ? perm[q + u] : 0xffffffffu;
+                }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     ga[u] = gb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
