@@ -1585,6 +1585,16 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
         // the row's lookups in position order, four lookups and two column chunks (eight loads) in
         // flight; head and tail lookups apart
         const int wl = threadIdx.x & 31;
+        if (writes_row && (wl & 7) == 0) {
+            // The row's state is needed only after its gradient rows have been summed, but its address is
+            // known now: ask L2 for it (one request per 128-byte line, no registers held).
+            for (int c = wl * V; c < D; c += 32 * V) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(L.value_bf16 ? reinterpret_cast<const void*>(reinterpret_cast<const __nv_bfloat16*>(xs) + c)
+                                                                             : reinterpret_cast<const void*>(xs + c)));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(ms + c));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(qs + c));
+            }
+        }
         for (int c0 = 0; c0 < D; c0 += 64 * V) {
             const int ca = c0 + wl * V, cb = ca + 32 * V;
             if (ca >= D) continue;
