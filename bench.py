@@ -323,7 +323,7 @@ def nvlink_block(trace: dict, n_shard: int) -> dict:
     T, n_rel = BATCH + NEGATIVES, int(n_shard * np.ceil(N_RELATION / n_shard))
     away = (n_shard - 1) / n_shard
     payload = {
-        "tails": T * D * 4 * away,                          # rows only: the receiver derives their lower TF32 plane
+        "tails": 2 * T * D * 4 * away,                      # rows and their lower TF32 plane
         "tail_grads": T * D * 4 * away,
         "dense_partials": (n_rel + F) * D * 4 * away,        # each row to the process that owns it
         "dense_params": ((n_rel + 2 * F) * D * 4 / n_shard) * (n_shard - 1),  # owned rows (+ lower plane of W) to every other replica

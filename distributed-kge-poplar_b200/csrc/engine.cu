@@ -1317,9 +1317,6 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
     const unsigned B = cfg_.batch_size, T = cfg_.n_tail(), R = cfg_.n_remote(), D = cfg_.d, F = cfg_.f;
     const unsigned n_rel = cfg_.n_relation_type, parity = step & 1;
     const bool two_nets = cfg_.n_net() == 2, l2 = cfg_.dist_fn == DIST_L2, l1 = cfg_.dist_fn == DIST_L1;
-    // The tails' lower TF32 plane is an operand of the score gradients' contraction only (L2 in the direct
-    // form): the shard that receives the tails derives it in its score kernel, and the senders send half as much.
-    const bool tails_lo_by_receiver = l2 && !cfg_.l2_contraction && !bf16_planes_ && cfg_.d % 4 == 0;
     // bf16 embeddings: the dot-product scores and their gradients multiply bfloat16 copies of pred,
     // tails and the coefficients (written by their producers into the companion planes)
     const bool bf16 = bf16_planes_;
@@ -1367,7 +1364,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             route.relation = relation;
             route.rel_table = rel_table;
             route.send_dst = b.send_dst;
-            route.send_lo_dst = tails_lo_by_receiver ? nullptr : b.send_lo_dst;
+            route.send_lo_dst = b.send_lo_dst;
             route.pred = b.pred;
             route.pred_lo = b.pred_lo;
             route.B = (int)B; route.a2a = (int)cfg_.a2a_size; route.n_shard = (int)cfg_.n_shard; route.score_fn = cfg_.score_fn;
@@ -1382,8 +1379,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             if (heavy_route)
                 KGE_LAUNCH("route_heavy", KGE_CUDA(launch_dependent(k_route_heavy, dim3(kHeavySlots), dim3(256), 0, stream_, (const float*)b.hid_h, (const float*)b.hid_t,
                                                                     (const uint4*)(d_heavy_parts_ + sidx * kHeavySlots), (const uint32_t*)(d_heavy_count_ + sidx),
-                                                                    (const uint32_t*)(d_ent_perm_ + sidx * (B + T)), relation, rel_table, b.send_dst,
-                                                                    tails_lo_by_receiver ? (float* const*)nullptr : (float* const*)b.send_lo_dst,
+                                                                    (const uint32_t*)(d_ent_perm_ + sidx * (B + T)), relation, rel_table, b.send_dst, b.send_lo_dst,
                                                                     b.pred, b.pred_lo, (int)B, (int)cfg_.a2a_size, (int)D, cfg_.score_fn, bf16 ? 1 : 0, sync)));
         } else {
             // no features: the hidden rows are the gathered values
@@ -1396,7 +1392,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         if (!fused_route)
             KGE_LAUNCH("route", KGE_CUDA(launch_dependent(k_route<4>, dim3(T + B), dim3(64), 0, stream_, b.hid_h, b.hid_t, a2a, head, relation, rel_table,
                                                           b.send_dst, b.pred, (int)T, (int)cfg_.a2a_size, (int)B, (int)D, cfg_.score_fn, sync,
-                                                          tails_lo_by_receiver ? (float* const*)nullptr : (float* const*)b.send_lo_dst, b.pred_lo, bf16 ? 1 : 0)));
+                                                          b.send_lo_dst, b.pred_lo, bf16 ? 1 : 0)));
         if (cfg_.regularised()) launch_regularise(l, rows_c);
     }
     KGE_CUDA(cudaGetLastError());
@@ -1423,8 +1419,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             p.g.epilogue = tc::EPI_L2_DISTANCE; p.g.out = b.raw; p.g.ldc = T; p.g.block_rows = 1;
             launch_planes("score", &p, 1, tc::SIDE_NORMS, XCHG_TAILS, -1);
         } else {
-            KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_, sync,
-                                                      tails_lo_by_receiver ? b.tails_lo : nullptr)));
+            KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_, sync)));
         }
         // 3. loss and the coefficients of the score gradients
         KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,

@@ -407,10 +407,9 @@ k_route_heavy(const float* __restrict__ hid_h, const float* __restrict__ hid_t, 
             } else {
                 const uint32_t j = e - (uint32_t)B, shard = j / (uint32_t)a2a, slot = j - shard * (uint32_t)a2a;
                 dst = send_dst[shard] + (size_t)slot * D;
-                dst_lo = !send_lo_dst ? nullptr : lo_bf16 ? send_lo_dst[shard] + (size_t)slot * D / 2 : send_lo_dst[shard] + (size_t)slot * D;
+                dst_lo = lo_bf16 ? send_lo_dst[shard] + (size_t)slot * D / 2 : send_lo_dst[shard] + (size_t)slot * D;
             }
             store4(dst + c, o);
-            if (!dst_lo) continue;  // the receiving shard derives the tails' lower plane itself
             if (lo_bf16) store4(reinterpret_cast<__nv_bfloat16*>(dst_lo) + c, o);
             else store4(dst_lo + c, tf32_lower4(o));
         }
@@ -537,7 +536,7 @@ __device__ __forceinline__ void score_copy16(float* dst_smem, const float* src) 
 template <int FN>
 __global__ void __launch_bounds__(32 * kScoreWarps, 3)
 k_score_wide(const float* __restrict__ P, const float* __restrict__ Tl, float* __restrict__ raw, int B,
-             int T, int D, ExchangeSync sync, float* __restrict__ t_lo) {
+             int T, int D, ExchangeSync sync) {
     grid_dependency_sync();
     exchange_wait(sync, XCHG_TAILS);  // the tail rows come from the other processes
     extern __shared__ __align__(16) float score_smem[];
@@ -568,16 +567,6 @@ k_score_wide(const float* __restrict__ P, const float* __restrict__ Tl, float* _
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncwarp();
-        if (t_lo && blockIdx.y == 0) {
-            // The first band of blocks reads every tail row once: it also writes the rows' lower TF32 plane
-            // (an operand of the score gradients' contraction), which the sending shards then need not send.
-#pragma unroll 2
-            for (int it = 0; it < 8; ++it) {
-                const int row = it * 4 + (lane >> 3), k4 = (lane & 7) * 4;
-                if (j0 + row < T && k0 + k4 < D)
-                    store4(t_lo + (size_t)(j0 + row) * D + k0 + k4, tf32_lower4(load4(Ts + row * kScoreStride + k4)));
-            }
-        }
 #pragma unroll 1
         for (int k4 = 0; k4 < 32; k4 += 4) {
             float4 pv[4];
@@ -636,10 +625,10 @@ k_score_wide(const float* __restrict__ P, const float* __restrict__ Tl, float* _
 // 16-byte-copy form can; returns cudaErrorNotSupported otherwise so that the caller waits first).
 template <int FN>
 inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream,
-                                const ExchangeSync& sync = ExchangeSync{}, float* t_lo = nullptr) {
+                                const ExchangeSync& sync = ExchangeSync{}) {
     const bool aligned = (D % 4) == 0 && reinterpret_cast<uintptr_t>(P) % 16 == 0 && reinterpret_cast<uintptr_t>(Tl) % 16 == 0;
     if (!aligned) {
-        if (sync.world > 1 || t_lo) return cudaErrorNotSupported;
+        if (sync.world > 1) return cudaErrorNotSupported;
         return launch_dependent(k_score<FN>, dim3((T + 63) / 64, (B + 31) / 32), dim3(128), 0, stream, P, Tl, raw, B, T, D);
     }
     static bool configured[kMaxDeviceOrdinals] = {};  // one attribute call per instantiation and device is enough
@@ -650,7 +639,7 @@ inline cudaError_t launch_score(const float* P, const float* Tl, float* raw, int
         if (slot >= 0) configured[slot] = true;
     }
     return launch_dependent(k_score_wide<FN>, dim3((T + 31) / 32, (B + 31) / 32), dim3(32 * kScoreWarps), kScoreWideSmem, stream,
-                            P, Tl, raw, B, T, D, sync, t_lo);
+                            P, Tl, raw, B, T, D, sync);
 }
 
 inline bool score_rows_aligned(const float* P, const float* Tl, int D) {
@@ -658,11 +647,11 @@ inline bool score_rows_aligned(const float* P, const float* Tl, int D) {
 }
 
 inline cudaError_t launch_score(int dist_fn, const float* P, const float* Tl, float* raw, int B, int T, int D, cudaStream_t stream,
-                                const ExchangeSync& sync = ExchangeSync{}, float* t_lo = nullptr) {
+                                const ExchangeSync& sync = ExchangeSync{}) {
     switch (dist_fn) {
-        case DIST_L1: return launch_score<DIST_L1>(P, Tl, raw, B, T, D, stream, sync, t_lo);
-        case DIST_L2: return launch_score<DIST_L2>(P, Tl, raw, B, T, D, stream, sync, t_lo);
-        default: return launch_score<DIST_DOT>(P, Tl, raw, B, T, D, stream, sync, t_lo);
+        case DIST_L1: return launch_score<DIST_L1>(P, Tl, raw, B, T, D, stream, sync);
+        case DIST_L2: return launch_score<DIST_L2>(P, Tl, raw, B, T, D, stream, sync);
+        default: return launch_score<DIST_DOT>(P, Tl, raw, B, T, D, stream, sync);
     }
 }
 

@@ -72,7 +72,7 @@ struct RouteArgs {
     const uint32_t* relation;
     const float* rel_table;
     float* const* send_dst;     // [n_shard] this shard's slot in every shard's tail buffer
-    float* const* send_lo_dst;  // [n_shard] the same in the lo plane; null: the receivers derive it
+    float* const* send_lo_dst;  // [n_shard] the same in the lo plane
     float* pred;
     float* pred_lo;
     int B, a2a, n_shard, score_fn;
@@ -242,13 +242,9 @@ __device__ __forceinline__ void route_rows(const RouteArgs& rt, int mode, const 
             } else {
                 const uint32_t j = e - (uint32_t)rt.B, shard = j / (uint32_t)rt.a2a, slot = j - shard * (uint32_t)rt.a2a;
                 dst = rt.send_dst[shard] + (size_t)slot * D;
-                // (null table: the receiving shard derives the tails' lower plane itself, in its score kernel)
-                dst_lo = !rt.send_lo_dst ? nullptr
-                         : rt.lo_bf16   ? rt.send_lo_dst[shard] + (size_t)slot * D / 2
-                                        : rt.send_lo_dst[shard] + (size_t)slot * D;
+                dst_lo = rt.lo_bf16 ? rt.send_lo_dst[shard] + (size_t)slot * D / 2 : rt.send_lo_dst[shard] + (size_t)slot * D;
             }
             *reinterpret_cast<float4*>(dst + n0 + q * 4) = o;
-            if (!dst_lo) continue;
             if (rt.lo_bf16) store4(reinterpret_cast<__nv_bfloat16*>(dst_lo) + n0 + q * 4, o);
             else *reinterpret_cast<float4*>(dst_lo + n0 + q * 4) = make_float4(tf32_lo(o.x), tf32_lo(o.y), tf32_lo(o.z), tf32_lo(o.w));
         }
