@@ -135,6 +135,11 @@ CASES = {
                                                 distance_fn="MatMul", loss_type="logsigmoid", share_feature_networks=False,
                                                 feature_mlp_size=10, feature_dropout=0.25),
                                  seed=29),
+    # the L2 forward as |p|^2 + |t|^2 - 2 p.t on the tensor cores (execution.l2_contraction), direct where that cancels
+    "l2_contraction_form": dict(cfg=StepConfig(n_shard=2, n_entity=500, n_relation_type=6, embedding_size=32,
+                                               entity_feature_size=24, batch_size=32, a2a_size=24, score_fn="TransE",
+                                               distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
+                                seed=30, feature_dtype="float16", settings={"execution.l2_contraction": True}),
     "single_shard": dict(cfg=StepConfig(n_shard=1, n_entity=400, n_relation_type=5, embedding_size=64,
                                         entity_feature_size=32, batch_size=64, a2a_size=96, score_fn="TransE",
                                         distance_fn="L2", gamma=10.0, loss_type="softmax", correction_weight=1.0),
@@ -147,7 +152,7 @@ def _build(case, n_step=1, warm=False, cuda_graph=True, pad=0, tensor_cores=True
     fdt = case.get("feature_dtype")
     state = random_state(cfg, case["seed"], fp16_features=fdt == "float16", warm=warm)
     engine = capi.CEngine(engine_settings(cfg, n_step=n_step, feature_dtype=fdt, rw_batch=RW, cuda_graph=cuda_graph,
-                                          **{"execution.tensor_cores": tensor_cores}))
+                                          **{"execution.tensor_cores": tensor_cores, **case.get("settings", {})}))
     write_state(engine, cfg, state, RW)
     batch = random_batch(cfg, n_step, case["seed"] + 100, pad=pad)
     return cfg, state, engine, batch
