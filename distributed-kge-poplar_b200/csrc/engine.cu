@@ -354,6 +354,7 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     // measured 85.0 against 82.9 us per step on one GPU, where nobody waits.
     heavy_route_ = cfg_.world >= 4;
     if (const char* v = std::getenv("KGE_ROUTE_POPULAR_ROWS")) heavy_route_ = std::atoi(v) != 0;
+    if (const char* v = std::getenv("KGE_FUSE_DENSE_UPDATE")) fuse_dense_env_ = std::atoi(v) != 0;
     // Which work runs beside the step's chain: bit 0 the relation gradients, bit 1 the next step's gather.
     side_streams_ = 3u;
     if (const char* v = std::getenv("KGE_SIDE_STREAMS")) side_streams_ = (unsigned)std::atoi(v) & 3u;
@@ -373,6 +374,9 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
         if (transh_score_smem() > 200 * 1024) fail(KGE_INVALID_ARGUMENT, "TransH: model.embedding_size is limited to 1600");
         KGE_CUDA(cudaFuncSetAttribute(k_transh_score, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)transh_score_smem()));
     }
+    // With one shard in all a dense gradient has a single contributor: the projection gradient's contraction and the
+    // relation rows' blocks of the entity update apply the Adam step themselves and k_dense_update is not launched.
+    fuse_dense_ = fuse_dense_env_ && planes_ && cfg_.n_shard == 1 && cfg_.world == 1;
     // fp16 features are widened into rows of their own; the lower plane of fp32 features keeps the
     // stride of the rows whose feature part is its upper plane (one stride per operand)
     bf16_planes_ = planes_ && cfg_.value_bf16 && cfg_.dist_fn == DIST_DOT && cfg_.d % 8 == 0 && cfg_.n_tail() % 8 == 0 && cfg_.batch_size % 8 == 0 &&
@@ -1467,7 +1471,9 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const size_t sidx = (size_t)l * cfg_.n_step + step;
         const HeavyRows heavy{d_heavy_parts_ + sidx * kHeavySlots, d_heavy_count_ + sidx, b.heavy_partial, b.heavy_counter, d_row_info_ + sidx * 2 * R};
         const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
-                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}, nullptr}, l, step);
+                                                               (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}, nullptr,
+                                                               fuse_dense_ ? dense_ : nullptr, fuse_dense_ ? dense_m_ : nullptr, fuse_dense_ ? dense_v_ : nullptr,
+                                                               dense_lr_mod_[0]}, l, step);
         const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
 #define KGE_ENTITY_UPDATE(ST_, EXTRAS_)                                                                                                          \
     KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<ST_, 4, EXTRAS_>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_, \
@@ -1503,6 +1509,15 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             g.epilogue = tc::EPI_STORE;
             g.out = nullptr; g.out_blocks = b.dense_dst; g.block_rows = 1; g.block_cyclic = (int)cfg_.world;
             g.block_row_offset = (int)(n_rel + net * F); g.ldc = D;
+            if (fuse_dense_) {
+                // one shard in all: this gradient is the whole gradient, and the epilogue is the projection's Adam step
+                g.epilogue = tc::EPI_DENSE_ADAM;
+                g.out_blocks = nullptr;
+                g.x_base = reinterpret_cast<const uint8_t*>(dense_ + dense_bounds_[1 + net]);
+                g.x_row_stride_bytes = (long long)D * 4;
+                g.adam = tc::DenseAdamArgs{dense_, dense_lo_, dense_m_, dense_v_, d_step_size_ + step, dense_lr_mod_[1 + net], adam_.beta_m, adam_.beta_v,
+                                           adam_.one_minus_beta_m, adam_.one_minus_beta_v, adam_.epsilon, adam_.weight_decay};
+            }
         }
         if (F > 0) launch_planes("projection_bwd", nets, (int)cfg_.n_net(), tc::SIDE_NONE, -1, XCHG_DENSE_PARTIALS);
         else launch_exchange_signal(XCHG_DENSE_PARTIALS);  // the relation rows of the entity update are all there is
@@ -1510,7 +1525,7 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
     KGE_CUDA(cudaGetLastError());
     if (gather_ahead && !gather_beside) launch_gather(step + 1, stream_);
     // 7. dense parameters: reduce over shards, Adam on the owned rows, new values and their lower planes into every replica
-    {
+    if (!fuse_dense_) {
         DenseUpdateArgs da{};
         da.sync = sync;
         da.partials = d_partials_;

@@ -268,6 +268,7 @@ class Engine {
     void launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp);
     float *p_mlp_cat_ = nullptr, *p_mlp_pre_ = nullptr, *p_mlp_out_ = nullptr;  // predict's MLP buffers
     bool heavy_route_ = false;  // rows with many lookups are routed in parts by k_route_heavy (KGE_ROUTE_POPULAR_ROWS=0: by the hidden kernel's epilogue)
+    bool fuse_dense_ = false, fuse_dense_env_ = true;  // single shard: dense Adam steps inside the kernels that produce the gradients (KGE_FUSE_DENSE_UPDATE=0: k_dense_update)
     uint32_t* d_step_key_ = nullptr;   // [n_step] numbers of the staged training steps (keys of the dropout masks)
     bool dropout_on() const { return cfg_.dropout > 0.f && cfg_.f > 0; }
     DropoutParams dropout_params(unsigned l, unsigned step) const;

@@ -1314,15 +1314,36 @@ struct RelationRows {
     // Non-null: the value's gradient is left here ([R, D]) and the rows are not updated; k_row_adam
     // does that once the rest of the gradient is known (the feature MLP reads the value too).
     float* defer_grad;
+    // Non-null (one shard in all: no other shard's gradient to wait for): a relation row's block applies
+    // the row's Adam step itself instead of handing its sum to k_dense_update.
+    float* rel_w;
+    float* rel_m;
+    float* rel_v;
+    float rel_lr_modifier;
 };
 
 template <int V, int LANES>
-__device__ __forceinline__ void relation_row_sum(const RelationRows& rr, int rho, int D, float (*part)[64 * V], uint32_t* s_perm) {
+__device__ __forceinline__ void relation_row_sum(const RelationRows& rr, int rho, int D, float (*part)[64 * V], uint32_t* s_perm,
+                                                 const float* __restrict__ step_size, const AdamParams& ap) {
     const int col = threadIdx.x & 63, lane = threadIdx.x >> 6;
     const uint32_t q0 = rr.off[rho], q1 = rr.off[rho + 1];
-    float* __restrict__ dst_row = rr.dense_dst[rho % rr.n_owner] + (size_t)(rho / rr.n_owner) * D;
+    // where the row's gradient goes: into its owner's receive buffer, or (one shard in all) straight into the row's Adam step
+    auto deliver = [&](int c, float total) {
+        if (!rr.rel_w) {
+            rr.dense_dst[rho % rr.n_owner][(size_t)(rho / rr.n_owner) * D + c] = total;
+            return;
+        }
+        const size_t e = (size_t)rho * D + c;
+        const float alpha = *step_size * rr.rel_lr_modifier;
+        const float mo = ap.beta_m * rr.rel_m[e] + ap.one_minus_beta_m * total;
+        const float ve = ap.beta_v * rr.rel_v[e] + ap.one_minus_beta_v * total * total;
+        const float x = rr.rel_w[e];
+        rr.rel_w[e] = x - alpha * (mo / (sqrtf(ve) + ap.epsilon) + ap.weight_decay * x);
+        rr.rel_m[e] = mo;
+        rr.rel_v[e] = ve;
+    };
     if (q0 == q1) {
-        for (int c = threadIdx.x; c < D; c += blockDim.x) dst_row[c] = 0.f;
+        for (int c = threadIdx.x; c < D; c += blockDim.x) deliver(c, 0.f);
         return;
     }
     for (int c0 = 0; c0 < D; c0 += 64 * V) {
@@ -1365,7 +1386,7 @@ __device__ __forceinline__ void relation_row_sum(const RelationRows& rr, int rho
                 float total = part[0][col * V + u];
 #pragma unroll
                 for (int l = 1; l < LANES; ++l) total += part[l][col * V + u];
-                dst_row[c + u] = total;
+                deliver(c + u, total);
             }
         }
     }
@@ -1388,7 +1409,7 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
     if ((int)blockIdx.x >= kHeavySlots + row_blocks) {  // a relation row: needs nothing from the other processes
         __shared__ float rel_part[kSegmentLanes][64 * V];
         __shared__ uint32_t rel_perm[64 * kSegmentLanes];
-        relation_row_sum<V, kSegmentLanes>(rr, (int)blockIdx.x - kHeavySlots - row_blocks, (int)L.d, rel_part, rel_perm);
+        relation_row_sum<V, kSegmentLanes>(rr, (int)blockIdx.x - kHeavySlots - row_blocks, (int)L.d, rel_part, rel_perm, step_size, ap);
         return;
     }
     exchange_wait(sync, XCHG_TAIL_GRADS);  // grad_recv is written by the other processes

@@ -41,7 +41,21 @@ constexpr int kBK = 32;       // fp32 elements per k slice: one 128-byte swizzle
 constexpr int kStages = 2;
 constexpr int kThreads = 128;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_ADD_TABLE_VALUE = 1, EPI_ROWSUM_X_MINUS = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD_TABLE_VALUE = 1, EPI_ROWSUM_X_MINUS = 2, EPI_DENSE_ADAM = 4 };  // (3: the L2 distance of tc_planes.cuh)
+
+// EPI_DENSE_ADAM: the contraction is the gradient of a dense parameter that no other shard contributes
+// to, and the epilogue is the parameter's Adam step (src/fructose/frnn.cpp:61-90) in place: output
+// element (m, n) is element (m + block_row_offset) * ldc + n of the dense vector.  X is the parameter
+// itself (x_base, fetched while the partial tiles travel).  Null w: not in use.
+struct DenseAdamArgs {
+    float* w;
+    float* w_lo;  // lower TF32 plane of the parameter (null: none kept)
+    float* m;
+    float* v;
+    const float* step_size;  // on the device: a replayed graph keeps its arguments
+    float lr_modifier;
+    float beta_m, beta_v, one_minus_beta_m, one_minus_beta_v, epsilon, weight_decay;
+};
 
 // One operand as it lies in global memory.  Element (r, c) of the stored matrix is at
 //   base + (gather ? gather[r] : r) * row_stride_bytes + c * (is_half ? 2 : 4).
@@ -77,6 +91,7 @@ struct GemmArgs {
     const uint32_t* x_gather;
     uint32_t x_row_base;
     int x_is_half;              // EPI_ADD_TABLE_VALUE: 0 fp32 values, 1 fp16, 2 bfloat16
+    DenseAdamArgs adam;         // EPI_DENSE_ADAM
     unsigned* status;           // device error word; non-zero = a bounded wait gave up
     // k split with a deterministic reduction (pipelined kernel only).  Every split writes its raw
     // partial tile to ws [splits, M, N] (and its partial row sums to ws_rowsum [splits, M]);
@@ -579,6 +594,11 @@ __device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw,
 __device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, float (&x)[4]) {
     x[0] = x[1] = x[2] = x[3] = 0.f;
     if (g.epilogue == EPI_STORE) return;
+    if (g.epilogue == EPI_DENSE_ADAM) {  // the moments are wanted right after X: ask L2 for them now
+        const size_t e = (size_t)(m + g.block_row_offset) * g.ldc + n;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(g.adam.m + e));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(g.adam.v + e));
+    }
     const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
     const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
     const int narrow = g.epilogue == EPI_ADD_TABLE_VALUE ? g.x_is_half : 0;  // 1: fp16 values, 2: bf16 values
@@ -604,6 +624,49 @@ __device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, 
     } else if (g.epilogue == EPI_ROWSUM_X_MINUS) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[j] = rs * x[j] - acc[j];
+    }
+    if (g.epilogue == EPI_DENSE_ADAM) {
+        const DenseAdamArgs& a = g.adam;
+        const size_t e = (size_t)(m + g.block_row_offset) * g.ldc + n;
+        const float alpha = *a.step_size * a.lr_modifier;
+        const bool vec = n + 3 < g.N && (e & 3) == 0;
+        float mo[4], ve[4], w[4], lo[4];
+        if (vec) {
+            const float4 m4 = *reinterpret_cast<const float4*>(a.m + e), v4 = *reinterpret_cast<const float4*>(a.v + e);
+            mo[0] = m4.x; mo[1] = m4.y; mo[2] = m4.z; mo[3] = m4.w;
+            ve[0] = v4.x; ve[1] = v4.y; ve[2] = v4.z; ve[3] = v4.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                mo[j] = n + j < g.N ? a.m[e + j] : 0.f;
+                ve[j] = n + j < g.N ? a.v[e + j] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float grad = acc[j];
+            mo[j] = a.beta_m * mo[j] + a.one_minus_beta_m * grad;
+            ve[j] = a.beta_v * ve[j] + a.one_minus_beta_v * grad * grad;
+            w[j] = x[j] - alpha * (mo[j] / (sqrtf(ve[j]) + a.epsilon) + a.weight_decay * x[j]);
+            const float hi = __uint_as_float(__float_as_uint(w[j]) & 0xffffe000u);
+            lo[j] = __uint_as_float(__float_as_uint(w[j] - hi) & 0xffffe000u);
+        }
+        if (vec) {
+            *reinterpret_cast<float4*>(a.m + e) = make_float4(mo[0], mo[1], mo[2], mo[3]);
+            *reinterpret_cast<float4*>(a.v + e) = make_float4(ve[0], ve[1], ve[2], ve[3]);
+            *reinterpret_cast<float4*>(a.w + e) = make_float4(w[0], w[1], w[2], w[3]);
+            if (a.w_lo) *reinterpret_cast<float4*>(a.w_lo + e) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (n + j >= g.N) break;
+                a.m[e + j] = mo[j];
+                a.v[e + j] = ve[j];
+                a.w[e + j] = w[j];
+                if (a.w_lo) a.w_lo[e + j] = lo[j];
+            }
+        }
+        return;
     }
     float* out_row;
     if (g.out_blocks) {
