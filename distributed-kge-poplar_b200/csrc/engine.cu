@@ -1426,9 +1426,9 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
             KGE_LAUNCH("score", KGE_CUDA(launch_score(cfg_.dist_fn, b.pred, b.tails, b.raw, (int)B, (int)T, (int)D, stream_, sync)));
         }
         // 3. loss and the coefficients of the score gradients
-        KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,
-                                                d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0, (int)B, stream_,
-                                                d_reg_loss_ ? d_reg_loss_ + 2 * l : nullptr)));
+        // (the rows' loss terms are added up by a block of the entity update, off the chain)
+        KGE_LAUNCH("loss", KGE_CUDA(launch_loss(b.raw, tail, b.coeff, b.loss_rows, lp, 1.0f / normaliser, nullptr, nullptr,
+                                                d_loss_counter_ + l, l1 ? nullptr : b.coeff_lo, bf16 ? 1 : 0, (int)B, stream_, nullptr)));
         // 4. score gradients; the tails' rows go straight to the shards that own them
         if (l1) {
             PairBwdArgs pa{};
@@ -1473,8 +1473,9 @@ void Engine::launch_step_planes(unsigned step, const LossParams& lp, float norma
         const RelationRows rr = with_regularisers(RelationRows{b.d_relrow, d_rel_perm_ + sidx * B, d_rel_off_ + sidx * (n_rel + 1), b.dense_dst,
                                                                (int)n_rel, (int)cfg_.world, b.d_hid_h_lo, b.d_hid_t_lo, nullptr, nullptr, nullptr, DropoutParams{}, nullptr,
                                                                fuse_dense_ ? dense_ : nullptr, fuse_dense_ ? dense_m_ : nullptr, fuse_dense_ ? dense_v_ : nullptr,
-                                                               dense_lr_mod_[0]}, l, step);
-        const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel), block(64 * kSegmentLanes);
+                                                               dense_lr_mod_[0], b.loss_rows, (int)B, 1.0f / normaliser, d_loss_total_ + l, d_loss_last_ + l,
+                                                               d_reg_loss_ ? d_reg_loss_ + 2 * l : nullptr}, l, step);
+        const dim3 grid(kHeavySlots + ceil_div(R, kRowsPerBlock) + n_rel + 1), block(64 * kSegmentLanes);  // + the loss block
 #define KGE_ENTITY_UPDATE(ST_, EXTRAS_)                                                                                                          \
     KGE_LAUNCH("entity_update", KGE_CUDA(launch_dependent(k_entity_update<ST_, 4, EXTRAS_>, grid, block, 0, stream_, b.table, b.rows_c2[parity], layout_, \
                                          step_ptr(d_remote_, l, R), d_ent_perm_ + sidx * (B + T), d_ent_off_ + sidx * (R + 1), d_first_slot_ + sidx * R,      \

@@ -744,7 +744,7 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
             if (c16) c16[j] = __float2bfloat16_rn(cj);
             if (j == lab) loss_rows[i] = -logp;
         }
-        finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch, extra_loss);
+        if (loss_total) finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch, extra_loss);
         return;
     }
     // log-sigmoid, optionally with self-adversarial weights from a detached softmax
@@ -781,7 +781,8 @@ k_loss(const float* __restrict__ raw, const uint32_t* __restrict__ label, float*
     }
     part = block_sum<THREADS>(part, scratch);
     if (threadIdx.x == 0) loss_rows[i] = -part;
-    finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch, extra_loss);
+    // (null loss_total: a later kernel of the step adds the rows' terms, off the step's critical chain)
+    if (loss_total) finish_step_loss<THREADS>(loss_rows, (int)gridDim.x, inv_normaliser, loss_total, loss_last, counter, scratch, extra_loss);
 }
 
 inline cudaError_t launch_loss(const float* raw, const uint32_t* label, float* coeff, float* loss_rows, const LossParams& lp, float inv_normaliser,
@@ -1320,6 +1321,14 @@ struct RelationRows {
     float* rel_m;
     float* rel_v;
     float rel_lr_modifier;
+    // Non-null: one more block at the end of the grid adds the step's loss terms (loss_rows [loss_n], left by
+    // k_loss) in row order into the run's total: beside the row updates instead of at the end of k_loss.
+    const float* loss_rows;
+    int loss_n;
+    float inv_normaliser;
+    float* loss_total;
+    float* loss_last;
+    const float* extra_loss;
 };
 
 template <int V, int LANES>
@@ -1441,7 +1450,19 @@ k_entity_update(uint8_t* __restrict__ table, const uint8_t* __restrict__ rows_c,
     if ((int)blockIdx.x >= kHeavySlots + row_blocks) {  // a relation row: needs nothing from the other processes
         __shared__ float rel_part[kSegmentLanes][64 * V];
         __shared__ uint32_t rel_perm[64 * kSegmentLanes];
-        relation_row_sum<V, kSegmentLanes>(rr, (int)blockIdx.x - kHeavySlots - row_blocks, (int)L.d, rel_part, rel_perm, step_size, ap);
+        const int rho = (int)blockIdx.x - kHeavySlots - row_blocks;
+        if (rho >= rr.n_rel) {  // the loss block
+            float part = 0.f;
+            for (int i = threadIdx.x; i < rr.loss_n; i += 64 * kSegmentLanes) part += rr.loss_rows[i];
+            part = block_sum<64 * kSegmentLanes>(part, &rel_part[0][0]);
+            if (threadIdx.x == 0) {
+                const float step_loss = part * rr.inv_normaliser + (rr.extra_loss ? *rr.extra_loss : 0.f);
+                *rr.loss_total += step_loss;
+                *rr.loss_last = step_loss;
+            }
+            return;
+        }
+        relation_row_sum<V, kSegmentLanes>(rr, rho, (int)L.d, rel_part, rel_perm, step_size, ap);
         return;
     }
     exchange_wait(sync, XCHG_TAIL_GRADS);  // grad_recv is written by the other processes
