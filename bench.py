@@ -282,8 +282,8 @@ def step_flops() -> dict:
 # the direct L2 distance on the FP32 pipe.
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture of the same kernels on a
 # small table (the step's kernels touch the same rows whatever the table size).
-NCU_TRAFFIC: dict = {"hidden": 7_063_808, "projection_bwd": 6_648_320, "score_bwd": 5_864_960, "score": 1_329_408,
-                     "loss": 1_611_776}
+NCU_TRAFFIC: dict = {"hidden": 7_066_880, "projection_bwd": 9_015_552, "score_bwd": 5_872_128, "score": 1_329_408,
+                     "loss": 1_612_544, "entity_update": 8_143_360}
 
 TENSOR_KERNELS = ("hidden", "projection_bwd", "score_bwd")
 FP32_KERNELS = ("score",)
