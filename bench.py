@@ -282,8 +282,11 @@ def step_flops() -> dict:
 # the direct L2 distance on the FP32 pipe.
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture of the same kernels on a
 # small table (the step's kernels touch the same rows whatever the table size).
-NCU_TRAFFIC: dict = {"hidden": 7_066_880, "projection_bwd": 9_015_552, "score_bwd": 5_872_128, "score": 1_329_408,
-                     "loss": 1_612_544, "entity_update": 8_143_360}
+NCU_TRAFFIC: dict = {
+    "train": {"hidden": 7_066_880, "projection_bwd": 9_015_552, "score_bwd": 5_872_128, "score": 1_329_408,
+              "loss": 1_612_544, "entity_update": 8_143_360},
+    "config4": {"score_bwd": 7_416_832, "score": 3_221_760, "loss": 8_430_592, "entity_update": 32_069_376},
+}
 
 TENSOR_KERNELS = ("hidden", "projection_bwd", "score_bwd")
 FP32_KERNELS = ("score",)
@@ -628,7 +631,7 @@ def run_ours(args) -> None:
                                "d2h_bytes_per_step": loss.nbytes, "ms_per_step": 1e3 * sampled_s / args.steps,
                                "note": "\"train_step_loop_sampled\": positives, negatives, unique rows and routing indices are drawn on the GPU"},
         "gpu_launches": int(launches),
-        "roofline": {**roofline, "traffic": NCU_TRAFFIC.get(dominant), "us_per_launch": dom["us_per_launch"],
+        "roofline": {**roofline, "traffic": NCU_TRAFFIC.get(args.workload, {}).get(dominant), "us_per_launch": dom["us_per_launch"],
                      "step_us": step_us, "step_hbm_gb_per_s": traffic["step"] / (step_us * 1e-6) / 1e9,
                      "step_frac_of_hbm": traffic["step"] / (step_us * 1e-6) / 1e9 / peak},
         "kernels": kernels,
