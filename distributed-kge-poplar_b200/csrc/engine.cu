@@ -355,6 +355,7 @@ Engine::Engine(const SettingMap& settings) : cfg_(parse_config(settings)) {
     heavy_route_ = cfg_.world >= 4;
     if (const char* v = std::getenv("KGE_ROUTE_POPULAR_ROWS")) heavy_route_ = std::atoi(v) != 0;
     if (const char* v = std::getenv("KGE_FUSE_DENSE_UPDATE")) fuse_dense_env_ = std::atoi(v) != 0;
+    if (const char* v = std::getenv("KGE_PREDICT_FILTER_IN_SCORES")) filter_in_scores_ = std::atoi(v) != 0;
     // Which work runs beside the step's chain: bit 0 the relation gradients, bit 1 the next step's gather.
     side_streams_ = 3u;
     if (const char* v = std::getenv("KGE_SIDE_STREAMS")) side_streams_ = (unsigned)std::atoi(v) & 3u;
@@ -2063,10 +2064,11 @@ void Engine::ensure_predict_buffers() {
 
 // Merges the scores of rows start .. start + c - 1 (in p_raw_) into every query's best list: the filter at
 // full bandwidth, then one warp per query on what it left.
-void Engine::launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp) {
+void Engine::launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp, bool filtered) {
     const unsigned Q = (unsigned)tp.n_query;
     const dim3 fgrid(std::max(1u, std::min(ceil_div(c, 4 * 256), 8u)), Q);
-    KGE_LAUNCH("predict_topk", k_topk_filter<<<fgrid, 256, 0, stream_>>>(p_raw_, (int)c, start, last, b.topk_state, b.topk_count, p_cand_, p_cand_count_, tp));
+    if (!filtered)  // else the score kernel's epilogue has left the candidates
+        KGE_LAUNCH("predict_topk", k_topk_filter<<<fgrid, 256, 0, stream_>>>(p_raw_, (int)c, start, last, b.topk_state, b.topk_count, p_cand_, p_cand_count_, tp));
     KGE_LAUNCH("predict_topk", k_topk_update<<<ceil_div(Q, 4), 128, 0, stream_>>>(p_raw_, (int)c, start, last, b.topk_state, b.topk_count, tp, p_cand_,
                                                                                  p_cand_count_));
 }
@@ -2153,8 +2155,8 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
         for (uint32_t start = 1; start <= last; start += predict_chunk_) {
             const unsigned c = std::min<uint32_t>(predict_chunk_, last - start + 1);
             if (predict_planes_) {
-                predict_pass_planes(b, start, c, queries, (unsigned)Q, W_tail == W_head ? 0 : 1);
-                launch_topk(b, c, start, last, tp);
+                const bool filtered = predict_pass_planes(b, start, c, last, tp, queries, (unsigned)Q, W_tail == W_head ? 0 : 1);
+                launch_topk(b, c, start, last, tp, filtered);
                 continue;
             }
             dim3 hgrid(ceil_div(c, 64), dtiles, 1);
@@ -2168,7 +2170,7 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
                                                 queries, queries + Q * D, p_chunk_hidden_, p_raw_, nullptr, nullptr, (int)Q, (int)c, (int)D, ExchangeSync{}));
             } else
             KGE_LAUNCH("predict_score", KGE_CUDA(launch_score(cfg_.dist_fn, queries, p_chunk_hidden_, p_raw_, (int)Q, (int)c, (int)D, stream_)));
-            launch_topk(b, c, start, last, tp);
+            launch_topk(b, c, start, last, tp, false);
         }
         KGE_LAUNCH("predict_finish", k_topk_finish<<<(unsigned)Q, 128, 0, stream_>>>(
                                          b.topk_state, b.topk_count, (int)Q, (int)hr, (int)nb, b.predict_score_dst,
@@ -2190,7 +2192,10 @@ void Engine::cmd_predict(std::vector<HostArray>& arrays) {
 // the L2 distance as |q|^2 + |t|^2 - 2 q.t with the direct form where that cancels, so identical
 // rows still score identically and an exact match still scores gamma
 // (src/poplar_kge.cpp:812-855; src/poplar_extensions/distance.cpp:151-185).
-void Engine::predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, const float* queries, unsigned Q, int net) {
+// Returns whether the score kernel has also filtered the pass's scores against the queries' cut-offs
+// (the L2 form; dot products leave that to k_topk_filter).
+bool Engine::predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, uint32_t last, const TopkParams& tp, const float* queries, unsigned Q,
+                                 int net) {
     const unsigned D = cfg_.d, F = cfg_.f;
     const uint8_t* rows = b.table + (size_t)start * layout_.row_bytes;
     if (F > 0) {
@@ -2227,8 +2232,11 @@ void Engine::predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, co
     const bool l2 = cfg_.dist_fn == DIST_L2;
     s.g.epilogue = l2 ? tc::EPI_L2_DISTANCE : tc::EPI_STORE;
     s.g.out = p_raw_; s.g.ldc = c; s.g.block_rows = 1;
+    const bool filtered = l2 && filter_in_scores_;
+    if (filtered) s.filter = tc::TopkFilterArgs{b.topk_state, b.topk_count, p_cand_, p_cand_count_, start, last, tp.n_best, tp.score_is_gamma_minus, tp.gamma};
     launch_planes("predict_score", &s, 1, l2 ? tc::SIDE_NORMS : tc::SIDE_NONE, -1, -1);
     KGE_CUDA(cudaGetLastError());
+    return filtered;
 }
 
 size_t Engine::debug_fetch(const std::string& what, size_t shard, float* out, size_t capacity) {

@@ -265,8 +265,9 @@ class Engine {
     void launch_mlp_backward(unsigned l, unsigned step);
     unsigned long long* p_cand_ = nullptr;  // [Q, kTopkCandidates] a batch's keys above each query's cut-off
     int* p_cand_count_ = nullptr;
-    void launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp);
+    void launch_topk(ShardBuffers& b, unsigned c, uint32_t start, uint32_t last, const TopkParams& tp, bool filtered);
     float *p_mlp_cat_ = nullptr, *p_mlp_pre_ = nullptr, *p_mlp_out_ = nullptr;  // predict's MLP buffers
+    bool filter_in_scores_ = true;  // predict's L2 score contraction also filters the scores against the queries' cut-offs (KGE_PREDICT_FILTER_IN_SCORES=0: k_topk_filter)
     bool heavy_route_ = false;  // rows with many lookups are routed in parts by k_route_heavy (KGE_ROUTE_POPULAR_ROWS=0: by the hidden kernel's epilogue)
     bool fuse_dense_ = false, fuse_dense_env_ = true;  // single shard: dense Adam steps inside the kernels that produce the gradients (KGE_FUSE_DENSE_UPDATE=0: k_dense_update)
     uint32_t* d_step_key_ = nullptr;   // [n_step] numbers of the staged training steps (keys of the dropout masks)
@@ -285,7 +286,7 @@ class Engine {
     uint32_t sample_run_ = 0;  // program runs sampled so far: part of the generator's key
     // predict: buffers made on first use
     void ensure_predict_buffers();
-    void predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, const float* queries, unsigned Q, int net);
+    bool predict_pass_planes(ShardBuffers& b, uint32_t start, unsigned c, uint32_t last, const TopkParams& tp, const float* queries, unsigned Q, int net);
     float *p_head_hidden_ = nullptr, *p_chunk_hidden_ = nullptr, *p_raw_ = nullptr;
     uint32_t* d_iota_ = nullptr;
     // table rows scored per pass: 4096 on the FP32 pipe, 16384 when hidden rows and scores are tensor-core contractions

@@ -53,9 +53,24 @@ struct PlaneOperand {
 
 // One contraction: the planes of both operands and, in `g`, sizes, k split, epilogue and output
 // (g.A and g.B are not used).
+// EPI_L2_DISTANCE as predict's score pass: the distances of output row m (a query) that beat the
+// query's cut-off as it stands before the pass go straight into its candidate list, which
+// k_topk_filter would otherwise collect by reading the whole score matrix back.  Output column n is
+// table row first_row + n.  Null `cand`: none.
+struct TopkFilterArgs {
+    const unsigned long long* state;  // [M, kTopkCapacity] the queries' lists so far
+    const int* counts;                // [M]
+    unsigned long long* cand;         // [M, kTopkCandidates]
+    int* cand_count;                  // [M]
+    uint32_t first_row, last_valid_row;
+    int n_best, score_is_gamma_minus;
+    float gamma;
+};
+
 struct PlaneProblem {
     PlaneOperand A, B;
     GemmArgs g;
+    TopkFilterArgs filter;
 };
 
 // Folded into the epilogue of hidden = value + feature . W: the lookups of the step and the send
@@ -281,34 +296,50 @@ __device__ __forceinline__ int route_stage(const RouteArgs& rt, int row0, int n_
 // could pass 5e-6, so it is recomputed there in the direct form from the rows themselves, which
 // also returns the exact zero for identical rows that the gradient rule tests for
 // (l2distance.codelet.cpp:149-158).  Both operands are k-major; `acc` = a.b, an = |a|^2, bn = |b|^2.
-__device__ __forceinline__ void finish_l2_four(const PlaneProblem& pp, int m, int n, float (&acc)[4], float an, const float (&bn)[4]) {
+// The squared distance of two k-major rows in the direct form (the rare path: out of line).
+static __device__ __noinline__ float l2_squared_direct(const float* __restrict__ a, const float* __restrict__ b, int K) {
+    float s0 = 0.f, s1 = 0.f;
+    int k = 0;
+    for (; k + 7 < K; k += 8) {
+        const float4 x0 = *reinterpret_cast<const float4*>(a + k), y0 = *reinterpret_cast<const float4*>(b + k);
+        const float4 x1 = *reinterpret_cast<const float4*>(a + k + 4), y1 = *reinterpret_cast<const float4*>(b + k + 4);
+        float d;
+        d = x0.x - y0.x; s0 = fmaf(d, d, s0); d = x0.y - y0.y; s0 = fmaf(d, d, s0);
+        d = x0.z - y0.z; s0 = fmaf(d, d, s0); d = x0.w - y0.w; s0 = fmaf(d, d, s0);
+        d = x1.x - y1.x; s1 = fmaf(d, d, s1); d = x1.y - y1.y; s1 = fmaf(d, d, s1);
+        d = x1.z - y1.z; s1 = fmaf(d, d, s1); d = x1.w - y1.w; s1 = fmaf(d, d, s1);
+    }
+    for (; k < K; ++k) {
+        const float d = a[k] - b[k];
+        s0 = fmaf(d, d, s0);
+    }
+    return s0 + s1;
+}
+
+// acc = a.b of output row m, columns n .. n + 3 becomes the distances: straight-line arithmetic
+// except for one test per four outputs that sends near-cancelling pairs to the direct form.
+__device__ __forceinline__ void l2_distance_four(const PlaneProblem& pp, int m, int n, float (&acc)[4], float an, const float (&bn)[4],
+                                                 bool live = true) {
     const GemmArgs& g = pp.g;
-    const float* a = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.A.hi) + (size_t)m * pp.A.row_stride_bytes);
+    float d2[4];
+    bool direct = false;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        if (n + j >= g.N) continue;
-        float d2 = an + bn[j] - 2.f * acc[j];
-        if (d2 < 0.2f * (an + bn[j])) {
-            const float* b = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.B.hi) + (size_t)(n + j) * pp.B.row_stride_bytes);
-            float s0 = 0.f, s1 = 0.f;
-            int k = 0;
-            for (; k + 7 < g.K; k += 8) {
-                const float4 x0 = *reinterpret_cast<const float4*>(a + k), y0 = *reinterpret_cast<const float4*>(b + k);
-                const float4 x1 = *reinterpret_cast<const float4*>(a + k + 4), y1 = *reinterpret_cast<const float4*>(b + k + 4);
-                float d;
-                d = x0.x - y0.x; s0 = fmaf(d, d, s0); d = x0.y - y0.y; s0 = fmaf(d, d, s0);
-                d = x0.z - y0.z; s0 = fmaf(d, d, s0); d = x0.w - y0.w; s0 = fmaf(d, d, s0);
-                d = x1.x - y1.x; s1 = fmaf(d, d, s1); d = x1.y - y1.y; s1 = fmaf(d, d, s1);
-                d = x1.z - y1.z; s1 = fmaf(d, d, s1); d = x1.w - y1.w; s1 = fmaf(d, d, s1);
-            }
-            for (; k < g.K; ++k) {
-                const float d = a[k] - b[k];
-                s0 = fmaf(d, d, s0);
-            }
-            d2 = s0 + s1;
-        }
-        acc[j] = sqrtf(fmaxf(d2, 0.f));
+        d2[j] = an + bn[j] - 2.f * acc[j];
+        direct |= n + j < g.N && d2[j] < 0.2f * (an + bn[j]);
     }
+    if (direct && live) {  // not for units past the problem's edge: their rows do not exist
+        const float* a = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.A.hi) + (size_t)m * pp.A.row_stride_bytes);
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j)
+            if (n + j < g.N && d2[j] < 0.2f * (an + bn[j]))
+                d2[j] = l2_squared_direct(a, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.B.hi) + (size_t)(n + j) * pp.B.row_stride_bytes), g.K);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = sqrtf(fmaxf(d2[j], 0.f));
+}
+
+__device__ __forceinline__ void store_four(const GemmArgs& g, int m, int n, const float (&acc)[4]) {
     float* out_row = g.out + (size_t)m * g.ldc;
     if ((g.N & 3) == 0 && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(out_row) & 15) == 0) {
         *reinterpret_cast<float4*>(out_row + n) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -316,6 +347,30 @@ __device__ __forceinline__ void finish_l2_four(const PlaneProblem& pp, int m, in
 #pragma unroll
         for (int j = 0; j < 4; ++j)
             if (n + j < g.N) out_row[n + j] = acc[j];
+    }
+}
+
+__device__ __forceinline__ void finish_l2_four(const PlaneProblem& pp, int m, int n, float (&acc)[4], float an, const float (&bn)[4]) {
+    l2_distance_four(pp, m, n, acc, an, bn);
+    store_four(pp.g, m, n, acc);
+}
+
+// predict's filter on four finished scores of query m (TopkFilterArgs): `cut` is the score of the
+// query's cut-off key (+inf while there is none), `cutoff` the key itself.
+__device__ __forceinline__ void topk_filter_four(const TopkFilterArgs& f, int N, int m, int n, const float (&dist)[4], float cut,
+                                                 const unsigned long long* cutoff) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float score = f.score_is_gamma_minus ? f.gamma - dist[j] : dist[j];
+        if (score >= cut) {  // rare once a cut-off exists; ties are decided by the keys
+            const uint32_t table_row = f.first_row + (uint32_t)(n + j);
+            if (n + j >= N || table_row > f.last_valid_row) continue;
+            const unsigned long long key = topk_key(score, table_row);
+            if (key > *cutoff) {
+                const int slot = atomicAdd(f.cand_count + m, 1);
+                if (slot < kTopkCandidates) f.cand[(size_t)m * kTopkCandidates + slot] = key;
+            }
+        }
     }
 }
 
@@ -345,8 +400,10 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     __shared__ uint64_t bar_full[kPlMaxStages], bar_empty[kPlMaxStages], bar_acc_ready[kPlTmemSlots], bar_acc_free[kPlTmemSlots];
     __shared__ uint64_t bar_reduce;
     __shared__ uint32_t tmem_slot;
-    __shared__ float s_rowsum[2][kBM];
-    __shared__ float s_colsum[2][BN];
+    __shared__ __align__(16) float s_rowsum[2][kBM];
+    __shared__ __align__(16) float s_colsum[2][BN];  // read in 16-byte pieces
+    __shared__ unsigned long long s_cutoff[SIDE == SIDE_NORMS ? kBM : 1];  // the tile's queries' top-k cut-offs (TopkFilterArgs)
+    __shared__ float s_cut_score[SIDE == SIDE_NORMS ? kBM : 1];            // their scores: a score below it cannot pass
     constexpr bool ROWSUM = SIDE != SIDE_NONE;
 
     const int which = (int)blockIdx.x >= gp.tiles_m0 ? 1 : 0;
@@ -396,6 +453,18 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     grid_dependency_sync();
     exchange_wait(gp.sync, gp.wait_kind);
     const uint32_t tmem_base = tmem_slot;
+    if (SIDE == SIDE_NORMS && pp.filter.cand != nullptr && tid >= 64 && tid < 64 + kBM) {
+        const TopkFilterArgs& f = pp.filter;
+        const int r = tid - 64, m = m0 + r;
+        unsigned long long cutoff = ~0ull;  // rows past the problem: nothing passes
+        if (m < g.M) {
+            cutoff = f.counts[m] >= f.n_best ? f.state[(size_t)m * kTopkCapacity + f.n_best - 1] : 0ull;
+            // no cut-off yet: every score is a candidate and the query scans its row of scores itself
+            if (cutoff == 0ull && n0 == 0) f.cand_count[m] = kTopkCandidates + 1;
+        }
+        s_cutoff[r] = cutoff;  // read after the block-wide barrier that ends the k loop
+        s_cut_score[r] = cutoff == 0ull || cutoff == ~0ull ? __int_as_float(0x7f800000) : topk_score(cutoff);
+    }
 
     float acc[CPT];
 #pragma unroll
@@ -530,6 +599,36 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
         float* receive = staging + (size_t)n_split * slot_floats;         // [source][rows_each][BN] + sums, what I own
         if (!clustered) fin = reinterpret_cast<float*>(smem + 72 * 1024);  // one slot of 67 KB only: the finished rows follow it
         if (clustered && tid == 0) mbar_arrive_expect(&bar_reduce, (uint32_t)(n_split - 1) * slot_bytes);
+        // A whole tile of distances (predict's score pass): the thread that holds a row of the
+        // accumulator turns its dot products into distances before they are staged, as one stretch
+        // of straight-line code, so that the arithmetic of all of them overlaps; what follows the
+        // staging is then a plain copy.  The two rare cases leave a bit each and are dealt with after
+        // the staging, in shared memory: near-cancelling pairs (recomputed in the direct form) and,
+        // for predict's top-k (TopkFilterArgs), scores that reach the row's cut-off.  The square root
+        // is the approximate one (relative error 2^-23, exact at zero): the form's own error is larger.
+        uint32_t direct_bits[CPT / 32] = {}, pass_bits[CPT / 32] = {};
+        const bool whole_tile = SIDE == SIDE_NORMS && !clustered && acc_warp;
+        const bool filtering = whole_tile && pp.filter.cand != nullptr && m < g.M;
+        if (whole_tile) {
+            const float an = s_rowsum[0][row] + s_rowsum[1][row];
+            const float cut = filtering ? s_cut_score[row] : __int_as_float(0x7f800000);
+            const float sign = pp.filter.score_is_gamma_minus ? -1.f : 1.f, offset = pp.filter.score_is_gamma_minus ? pp.filter.gamma : 0.f;
+#pragma unroll
+            for (int j0 = 0; j0 < CPT; j0 += 4) {
+                const int tc0 = (nc0 - n0) + j0;  // tile column of acc[j0]
+                const float4 c0 = *reinterpret_cast<const float4*>(&s_colsum[0][tc0]), c1 = *reinterpret_cast<const float4*>(&s_colsum[1][tc0]);
+                const float bn[4] = {c0.x + c1.x, c0.y + c1.y, c0.z + c1.z, c0.w + c1.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float both = an + bn[t], d2 = both - 2.f * acc[j0 + t];
+                    direct_bits[(j0 + t) >> 5] |= (uint32_t)(d2 < 0.2f * both) << ((j0 + t) & 31);
+                    float dist;
+                    asm("sqrt.approx.f32 %0, %1;" : "=f"(dist) : "f"(fmaxf(d2, 0.f)));
+                    acc[j0 + t] = dist;
+                    pass_bits[(j0 + t) >> 5] |= (uint32_t)(fmaf(sign, dist, offset) >= cut) << ((j0 + t) & 31);
+                }
+            }
+        }
         if (acc_warp) {
             // 16-byte chunk c of tile row `row` lies at chunk c ^ (row & 7): the lanes of a warp hold
             // 32 different rows, and this spreads their stores over all banks
@@ -540,6 +639,34 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             for (int j = 0; j < CPT; j += 4)
                 *reinterpret_cast<float4*>(mine + (((c0 + (j >> 2)) ^ (row & 7)) << 2)) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
             if (ROWSUM && nc0 == n0) staging[(size_t)owner * slot_floats + off_rowsum + local] = s_rowsum[0][row] + s_rowsum[1][row];
+            if (whole_tile && m < g.M) {
+                const float* a_row = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.A.hi) + (size_t)m * pp.A.row_stride_bytes);
+#pragma unroll
+                for (int w = 0; w < CPT / 32; ++w) {
+                    uint32_t todo = direct_bits[w] | (filtering ? pass_bits[w] : 0u);
+                    while (todo) {
+                        const int bit = __ffs(todo) - 1, tcol = (nc0 - n0) + w * 32 + bit, col = n0 + tcol;
+                        todo &= todo - 1;
+                        if (col >= g.N) continue;
+                        float* cell = mine + (((tcol >> 2) ^ (row & 7)) << 2) + (tcol & 3);
+                        if ((direct_bits[w] >> bit) & 1u) {
+                            const float d2 = l2_squared_direct(a_row, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(pp.B.hi) + (size_t)col * pp.B.row_stride_bytes), g.K);
+                            *cell = sqrtf(d2);
+                        }
+                        if (filtering) {
+                            const TopkFilterArgs& f = pp.filter;
+                            const float score = f.score_is_gamma_minus ? f.gamma - *cell : *cell;
+                            const uint32_t table_row = f.first_row + (uint32_t)col;
+                            if (table_row > f.last_valid_row) continue;
+                            const unsigned long long key = topk_key(score, table_row);
+                            if (key > s_cutoff[row]) {  // ties with the cut-off are decided by the keys
+                                const int slot = atomicAdd(f.cand_count + m, 1);
+                                if (slot < kTopkCandidates) f.cand[(size_t)m * kTopkCandidates + slot] = key;
+                            }
+                        }
+                    }
+                }
+            }
         }
         if (SIDE == SIDE_NORMS)  // every owner gets this split's part of the column norms
             for (int u = tid; u < n_split * BN; u += kPlThreads)
@@ -593,6 +720,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
             if (mm >= g.M || nn >= g.N) return;
             if (SIDE == SIDE_NORMS) {
                 finish_l2_four(pp, mm, nn, sum, row_total, col_total);
+                if (pp.filter.cand != nullptr) topk_filter_four(pp.filter, g.N, mm, nn, sum, s_cut_score[trow], &s_cutoff[trow]);
             } else {
                 float x[4];
                 if (x_ready) {
@@ -609,6 +737,15 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
 #pragma unroll
             for (int i = 0; i < kUnits; ++i)
                 if (tid + i * kPlThreads < n_units) finish_unit(tid + i * kPlThreads, xv[i]);
+        } else if (SIDE == SIDE_NORMS) {
+            // the staged rows are finished distances: whole rows go out in 16-byte pieces
+#pragma unroll 4
+            for (int u = tid; u < n_units; u += kPlThreads) {
+                const int local = u / kQuads, q = u % kQuads, mm = m0 + local, nn = n0 + q * 4;
+                const float4 v = *reinterpret_cast<const float4*>(staging + (size_t)local * BN + ((q ^ (local & 7)) << 2));
+                const float four[4] = {v.x, v.y, v.z, v.w};
+                if (mm < g.M && nn < g.N) store_four(g, mm, nn, four);
+            }
         } else {
             for (int u = tid; u < n_units; u += kPlThreads) finish_unit(u, nullptr);
         }
