@@ -2035,7 +2035,11 @@ void Engine::ensure_predict_buffers() {
     p_head_hidden_ = (float*)device_alloc((size_t)cfg_.predict_hr * D * 4);
     // L1 has no contraction form; everything else ranks with the plane-fed tensor-core kernel
     predict_planes_ = planes_ && cfg_.dist_fn != DIST_L1;
-    predict_chunk_ = predict_planes_ ? 16384u : 4096u;
+    // Rows per pass over the table.  On the tensor cores: 148 tiles of 128 rows, so that the hidden
+    // rows' contraction (2 column tiles) and the scores' (10 query tiles at 1250 queries) both fill
+    // whole waves of 148 blocks.
+    predict_chunk_ = predict_planes_ ? 148u * 128u : 4096u;
+    if (const char* v = std::getenv("KGE_PREDICT_PASS_ROWS")) predict_chunk_ = std::max(64u, (unsigned)std::atoi(v) / 4u * 4u);
     p_chunk_hidden_ = (float*)device_alloc((size_t)predict_chunk_ * D * 4);
     p_raw_ = (float*)device_alloc(Q * predict_chunk_ * 4);
     if (predict_planes_) {

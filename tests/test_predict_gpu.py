@@ -80,6 +80,33 @@ def test_predict_matches_oracle(score_fn, distance_fn, mlp):
     engine.close()
 
 
+@pytest.mark.parametrize("score_fn,distance_fn", [("TransE", "L2"), ("DistMult", "MatMul")])
+@pytest.mark.parametrize("filter_in_scores", ["1", "0"])
+def test_predict_in_many_passes_matches_oracle(monkeypatch, score_fn, distance_fn, filter_in_scores):
+    """Seven passes of 100 rows over each shard: from the second pass on the queries have
+    cut-offs, and a pass's scores reach the lists only through the filter (inside the L2 score
+    kernel, or the kernel of its own) and the merge.  n_best = 60 of 100 rows per pass keeps both
+    ends busy: passes that overflow nothing and passes whose candidates all pass."""
+    monkeypatch.setenv("KGE_PREDICT_PASS_ROWS", "100")
+    monkeypatch.setenv("KGE_PREDICT_FILTER_IN_SCORES", filter_in_scores)
+    cfg = StepConfig(n_shard=2, n_entity=700, n_relation_type=6, embedding_size=36, entity_feature_size=12,
+                     batch_size=6, a2a_size=4, score_fn=score_fn, distance_fn=distance_fn, gamma=5.0)
+    hr, n_best = 8, 60
+    state = random_state(cfg, 22, warm=False)
+    engine = capi.CEngine(engine_settings(cfg, rw_batch=RW, **{"execution.predict_hr_batch_size": hr, "execution.predict_n_best": n_best}))
+    write_state(engine, cfg, state, RW)
+    oracle = make_oracle(cfg, state)
+    counts = np.array([699, 655])
+    rng = np.random.RandomState(5)
+    queries = np.stack([rng.randint(2, size=13), 1 + rng.randint(600, size=13), rng.randint(6, size=13)], axis=1)
+    got_idx, got_score = _predict(engine, cfg, queries, counts, hr, n_best)
+    want_idx, want_score = oracle.predict(queries, counts, n_best)
+    np.testing.assert_allclose(got_score, want_score, rtol=1e-5, atol=1e-5)
+    clear = _clear(want_score)
+    np.testing.assert_array_equal(got_idx[clear], want_idx[clear])
+    engine.close()
+
+
 def test_predict_ties_are_broken_by_row():
     cfg = StepConfig(n_shard=1, n_entity=300, n_relation_type=2, embedding_size=8, entity_feature_size=0,
                      batch_size=4, a2a_size=4, score_fn="TransE", distance_fn="L1", gamma=1.0)
@@ -93,11 +120,16 @@ def test_predict_ties_are_broken_by_row():
     engine.close()
 
 
-def test_predict_ties_across_table_passes_and_shards():
-    """Ties between rows that different passes over the table score (a pass covers 4096 rows, so
-    rows 4096 and 4097 meet only in the running top-k) and between rows of different shards: the
-    best candidates are returned in ascending (shard, row) order.  Every tied row equals the
-    predicted tail exactly, so its distance is an exact zero on any arithmetic."""
+@pytest.mark.parametrize("filter_in_scores", ["1", "0"])
+def test_predict_ties_across_table_passes_and_shards(monkeypatch, filter_in_scores):
+    """Ties between rows that different passes over the table score (a pass is set to 4096 rows, so
+    rows 4096 and 4097 meet only in the running top-k, after a cut-off exists) and between rows of
+    different shards: the best candidates are returned in ascending (shard, row) order.  Every tied
+    row equals the predicted tail exactly, so its distance is an exact zero on any arithmetic.
+    Both ways of filtering a pass's scores against the cut-offs: inside the score kernel, and by
+    the kernel of its own."""
+    monkeypatch.setenv("KGE_PREDICT_PASS_ROWS", "4096")
+    monkeypatch.setenv("KGE_PREDICT_FILTER_IN_SCORES", filter_in_scores)
     cfg = StepConfig(n_shard=2, n_entity=4300, n_relation_type=2, embedding_size=8, entity_feature_size=0,
                      batch_size=4, a2a_size=4, score_fn="TransE", distance_fn="L2", gamma=3.0)
     state = random_state(cfg, 8)
