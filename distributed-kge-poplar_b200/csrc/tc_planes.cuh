@@ -453,6 +453,16 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     grid_dependency_sync();
     exchange_wait(gp.sync, gp.wait_kind);
     const uint32_t tmem_base = tmem_slot;
+    if (g.epilogue == EPI_ADD_TABLE_VALUE && g.cluster_splits <= 1 && tid >= 64 && tid < 64 + kBM && m0 + tid - 64 < g.M) {
+        // A whole tile without a k split (predict's hidden rows): the table values that the epilogue
+        // adds are asked into L2 now, a row per thread, so that the finishing loop, which fetches
+        // them one unit after the other, waits for L2 and not for DRAM.
+        const int m = m0 + tid - 64, elem = g.x_is_half ? 2 : 4;
+        const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
+        const uint8_t* x = g.x_base + xr * (size_t)g.x_row_stride_bytes + (size_t)n0 * elem;
+        const int bytes = min(BN, g.N - n0) * elem;
+        for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(x + o));
+    }
     if (SIDE == SIDE_NORMS && pp.filter.cand != nullptr && tid >= 64 && tid < 64 + kBM) {
         const TopkFilterArgs& f = pp.filter;
         const int r = tid - 64, m = m0 + r;
@@ -747,6 +757,8 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                 if (mm < g.M && nn < g.N) store_four(g, mm, nn, four);
             }
         } else {
+            // one unit after the other: unrolling this loop costs more in instruction fetches (the body
+            // holds every epilogue) than the overlap gains
             for (int u = tid; u < n_units; u += kPlThreads) finish_unit(u, nullptr);
         }
         if (clustered) cluster_wait();
