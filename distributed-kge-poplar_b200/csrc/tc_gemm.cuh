@@ -591,17 +591,19 @@ __device__ __forceinline__ void split_raw(const Operand& op, const uint8_t* raw,
 
 // The epilogue's second operand for four neighbouring output columns (m, n .. n+3): the value part
 // of the table row (EPI_ADD_TABLE_VALUE) or X[m, n ..] (EPI_ROWSUM_X_MINUS); zeros for EPI_STORE.
-__device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, float (&x)[4]) {
+// `fixed` >= 0: the epilogue is known where the call is compiled (the other kinds' code drops out).
+__device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, float (&x)[4], int fixed = -1) {
+    const int epilogue = fixed >= 0 ? fixed : g.epilogue;
     x[0] = x[1] = x[2] = x[3] = 0.f;
-    if (g.epilogue == EPI_STORE) return;
-    if (g.epilogue == EPI_DENSE_ADAM) {  // the moments are wanted right after X: ask L2 for them now
+    if (epilogue == EPI_STORE) return;
+    if (epilogue == EPI_DENSE_ADAM) {  // the moments are wanted right after X: ask L2 for them now
         const size_t e = (size_t)(m + g.block_row_offset) * g.ldc + n;
         asm volatile("prefetch.global.L2 [%0];" ::"l"(g.adam.m + e));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(g.adam.v + e));
     }
     const size_t xr = g.x_gather ? g.x_gather[m] : (size_t)g.x_row_base + (size_t)m;
     const uint8_t* x_row = g.x_base + xr * (size_t)g.x_row_stride_bytes;
-    const int narrow = g.epilogue == EPI_ADD_TABLE_VALUE ? g.x_is_half : 0;  // 1: fp16 values, 2: bf16 values
+    const int narrow = epilogue == EPI_ADD_TABLE_VALUE ? g.x_is_half : 0;  // 1: fp16 values, 2: bf16 values
     if (!narrow && n + 3 < g.N && ((reinterpret_cast<uintptr_t>(x_row) + (size_t)n * 4) & 15) == 0) {
         const float4 v = *reinterpret_cast<const float4*>(x_row + (size_t)n * 4);
         x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
@@ -617,15 +619,16 @@ __device__ __forceinline__ void load_x_four(const GemmArgs& g, int m, int n, flo
 
 // Epilogue and store of four neighbouring output columns whose k range is complete.
 __device__ __forceinline__ void finish_four(const GemmArgs& g, float* out_base, int m, int n, float (&acc)[4],
-                                            const float (&x)[4], float rs) {
-    if (g.epilogue == EPI_ADD_TABLE_VALUE) {
+                                            const float (&x)[4], float rs, int fixed = -1) {
+    const int epilogue = fixed >= 0 ? fixed : g.epilogue;
+    if (epilogue == EPI_ADD_TABLE_VALUE) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[j] = x[j] + acc[j];
-    } else if (g.epilogue == EPI_ROWSUM_X_MINUS) {
+    } else if (epilogue == EPI_ROWSUM_X_MINUS) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[j] = rs * x[j] - acc[j];
     }
-    if (g.epilogue == EPI_DENSE_ADAM) {
+    if (epilogue == EPI_DENSE_ADAM) {
         const DenseAdamArgs& a = g.adam;
         const size_t e = (size_t)(m + g.block_row_offset) * g.ldc + n;
         const float alpha = *a.step_size * a.lr_modifier;

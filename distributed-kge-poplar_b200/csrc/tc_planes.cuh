@@ -391,9 +391,14 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-template <int BN, int SIDE>
+// EPI >= 0: an instantiation for the training step's contractions, whose epilogue is known at
+// compile time and which always run with fp32 planes and a k split over a cluster.  A block runs
+// this kernel once on an SM whose instruction cache has never seen it, and most of it is
+// straight-line code executed once: what the instantiation does not need is not fetched.
+template <int BN, int SIDE, int EPI = -1>
 __global__ void __launch_bounds__(kPlThreads, 1)
 k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneMaps maps) {
+    constexpr bool kLean = EPI >= 0;
     static_assert(BN == 64 || BN == 128, "tile widths: 64 or 128 columns");
     constexpr int CPT = BN / 2;  // accumulator columns per accumulating thread: a warp reads one half of its 32 lanes' columns
     extern __shared__ uint8_t smem_raw[];
@@ -421,7 +426,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t kATile = kBM * 128, kBTile = BN * 128;
     const int k_begin = blockIdx.z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
-    const int bf16 = gp.bf16, slice_k = bf16 ? 64 : kBK;
+    const int bf16 = kLean ? 0 : gp.bf16, slice_k = bf16 ? 64 : kBK;
     const int n_slices = max(0, (k_end - k_begin + slice_k - 1) / slice_k);
     const bool a_two = pp.A.lo != nullptr, b_two = pp.B.lo != nullptr;
     // a ring stage: A hi [| A lo] | B hi [| B lo]
@@ -453,7 +458,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
     grid_dependency_sync();
     exchange_wait(gp.sync, gp.wait_kind);
     const uint32_t tmem_base = tmem_slot;
-    if (g.epilogue == EPI_ADD_TABLE_VALUE && g.cluster_splits <= 1 && tid >= 64 && tid < 64 + kBM && m0 + tid - 64 < g.M) {
+    if (!kLean && g.epilogue == EPI_ADD_TABLE_VALUE && g.cluster_splits <= 1 && tid >= 64 && tid < 64 + kBM && m0 + tid - 64 < g.M) {
         // A whole tile without a k split (predict's hidden rows): the table values that the epilogue
         // adds are asked into L2 now, a row per thread, so that the finishing loop, which fetches
         // them one unit after the other, waits for L2 and not for DRAM.
@@ -580,7 +585,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
 
     // Routing (hidden rows to their lookups): the finished rows and the staged lookups live in the
     // idle ring, behind what the k-split exchange uses.
-    const bool routing = gp.route.perm != nullptr && gp.route.mode[which] != 0;
+    const bool routing = (!kLean || EPI == EPI_ADD_TABLE_VALUE) && gp.route.perm != nullptr && gp.route.mode[which] != 0;
     float* fin = reinterpret_cast<float*>(smem + 150 * 1024);                              // [<= 64 rows][BN], or [128][BN] at offset 0 without a k split
     uint32_t* s_look = reinterpret_cast<uint32_t*>(smem + 184 * 1024);                      // [kRouteMaxLookups]
     uint32_t* s_rel = s_look + kRouteMaxLookups;                                            // [kRouteMaxLookups]
@@ -598,7 +603,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
         // barrier (arrive here, wait before the copies are issued).  Without a k split the block is
         // the only owner: its rows take the same way through shared memory, which turns one thread's
         // row of the accumulator into whole rows stored by neighbouring threads.
-        const bool clustered = g.cluster_splits > 1;
+        const bool clustered = kLean || g.cluster_splits > 1;
         if (clustered) cluster_arrive_relaxed();
         const int n_split = clustered ? g.cluster_splits : 1, rank = clustered ? (int)cluster_rank() : 0;
         const int rows_each = (kBM + n_split - 1) / n_split;
@@ -693,7 +698,7 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
                 const int u = tid + i * kPlThreads;
                 const int mm = m0 + r_begin + u / kQuads, nn = n0 + (u % kQuads) * 4;
                 xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
-                if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i]);
+                if (u < n_units && mm < g.M && nn < g.N) load_x_four(g, mm, nn, xv[i], EPI);
             }
         }
         if (routing) route_n = route_stage(gp.route, m0 + r_begin, max(0, min(r_end, g.M - m0) - r_begin), s_off, s_look, s_rel, kPlThreads);
@@ -737,9 +742,9 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
 #pragma unroll
                     for (int j = 0; j < 4; ++j) x[j] = x_ready[j];
                 } else {
-                    load_x_four(g, mm, nn, x);
+                    load_x_four(g, mm, nn, x, EPI);
                 }
-                finish_four(g, g.out, mm, nn, sum, x, row_total);
+                finish_four(g, g.out, mm, nn, sum, x, row_total, EPI);
             }
             if (routing) *reinterpret_cast<float4*>(fin + (size_t)local * BN + q * 4) = make_float4(sum[0], sum[1], sum[2], sum[3]);
         };
@@ -817,12 +822,12 @@ inline bool planes_aligned(const PlaneOperand& op) {
     return reinterpret_cast<uintptr_t>(op.hi) % 16 == 0 && reinterpret_cast<uintptr_t>(op.lo) % 16 == 0 && op.row_stride_bytes % 16 == 0;
 }
 
-template <int BN, int SIDE>
+template <int BN, int SIDE, int EPI = -1>
 inline cudaError_t configure_planes() {
     static bool configured[kMaxDeviceOrdinals] = {};
     const int slot = current_device_slot();
     if (slot >= 0 && configured[slot]) return cudaSuccess;
-    cudaError_t err = cudaFuncSetAttribute(k_tc_planes<BN, SIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plane_smem_bytes());
+    cudaError_t err = cudaFuncSetAttribute(k_tc_planes<BN, SIDE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plane_smem_bytes());
     if (err == cudaSuccess && slot >= 0) configured[slot] = true;
     return err;
 }
@@ -912,6 +917,14 @@ inline cudaError_t prepare_planes(const PlaneProblem* problems, int n_problems, 
     return cudaSuccess;
 }
 
+template <int SIDE, int EPI>
+inline cudaError_t launch_lean(const PlaneLaunch& l, cudaStream_t stream) {
+    cudaError_t err = configure_planes<128, SIDE, EPI>();
+    if (err != cudaSuccess) return err;
+    return launch_dependent_cluster(k_tc_planes<128, SIDE, EPI>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream, (unsigned)l.splits, l.gp,
+                                    l.maps);
+}
+
 template <int SIDE>
 inline cudaError_t launch_prepared(const PlaneLaunch& l, cudaStream_t stream) {
     if (SIDE != SIDE_NONE && l.gp.bf16) return cudaErrorInvalidValue;  // the side sums read fp32 tiles
@@ -919,6 +932,16 @@ inline cudaError_t launch_prepared(const PlaneLaunch& l, cudaStream_t stream) {
         for (int i = 0; i < 2; ++i)
             if (l.gp.p[i].A.mn_major || l.gp.p[i].B.mn_major || l.gp.p[i].g.out_blocks) return cudaErrorInvalidValue;
     if (l.tile_n == 128) {
+        // the training step's contractions (fp32 planes, k split over a cluster, one epilogue for the launch)
+        const int epilogue = l.gp.p[0].g.epilogue;
+        const bool lean = SIDE != SIDE_NORMS && !l.gp.bf16 && l.splits > 1 && l.gp.p[1].g.epilogue == epilogue;
+        if constexpr (SIDE == SIDE_NONE) {
+            if (lean && epilogue == EPI_ADD_TABLE_VALUE) return launch_lean<SIDE_NONE, EPI_ADD_TABLE_VALUE>(l, stream);
+            if (lean && epilogue == EPI_DENSE_ADAM) return launch_lean<SIDE_NONE, EPI_DENSE_ADAM>(l, stream);
+            if (lean && epilogue == EPI_STORE) return launch_lean<SIDE_NONE, EPI_STORE>(l, stream);
+        } else if constexpr (SIDE == SIDE_ROWSUM) {
+            if (lean && epilogue == EPI_ROWSUM_X_MINUS) return launch_lean<SIDE_ROWSUM, EPI_ROWSUM_X_MINUS>(l, stream);
+        }
         cudaError_t err = configure_planes<128, SIDE>();
         if (err != cudaSuccess) return err;
         return launch_dependent_cluster(k_tc_planes<128, SIDE>, l.grid, dim3(kPlThreads), plane_smem_bytes(), stream,
