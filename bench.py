@@ -283,8 +283,8 @@ def step_flops() -> dict:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture of the same kernels on a
 # small table (the step's kernels touch the same rows whatever the table size).
 NCU_TRAFFIC: dict = {
-    "train": {"hidden": 7_066_880, "projection_bwd": 9_015_552, "score_bwd": 5_872_128, "score": 1_329_408,
-              "loss": 1_612_544, "entity_update": 8_143_360},
+    "train": {"hidden": 7_043_328, "projection_bwd": 8_984_832, "score_bwd": 5_841_408, "score": 1_329_408,
+              "loss": 1_612_800, "entity_update": 8_143_360},
     "config4": {"score_bwd": 7_416_832, "score": 3_221_760, "loss": 8_430_592, "entity_update": 32_069_376},
 }
 
