@@ -753,8 +753,8 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
 #pragma unroll
             for (int i = 0; i < kUnits; ++i)
                 if (tid + i * kPlThreads < n_units) finish_unit(tid + i * kPlThreads, xv[i]);
-        } else if (SIDE == SIDE_NORMS) {
-            // the staged rows are finished distances: whole rows go out in 16-byte pieces
+        } else if (SIDE == SIDE_NORMS || (g.epilogue == EPI_STORE && g.out_blocks == nullptr && !routing)) {
+            // the staged rows are finished (distances, or a plain product): whole rows go out in 16-byte pieces
 #pragma unroll 4
             for (int u = tid; u < n_units; u += kPlThreads) {
                 const int local = u / kQuads, q = u % kQuads, mm = m0 + local, nn = n0 + q * 4;
