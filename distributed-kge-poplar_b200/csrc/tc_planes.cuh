@@ -289,13 +289,6 @@ __device__ __forceinline__ int route_stage(const RouteArgs& rt, int row0, int n_
     return n_look;
 }
 
-// Distances of A row m to the B rows n .. n+3 from the contraction: d^2 = |a|^2 + |b|^2 - 2 a.b
-// (src/poplar_extensions/distance.cpp:151-185 computes sqrt(sum (a - b)^2); the reference's own
-// comment at src/poplar_kge.cpp:376-396 names this expansion).  The expansion loses the distance
-// when the rows are close: where d^2 comes out below a fifth of |a|^2 + |b|^2 its relative error
-// could pass 5e-6, so it is recomputed there in the direct form from the rows themselves, which
-// also returns the exact zero for identical rows that the gradient rule tests for
-// (l2distance.codelet.cpp:149-158).  Both operands are k-major; `acc` = a.b, an = |a|^2, bn = |b|^2.
 // The squared distance of two k-major rows in the direct form (the rare path: out of line).
 static __device__ __noinline__ float l2_squared_direct(const float* __restrict__ a, const float* __restrict__ b, int K) {
     float s0 = 0.f, s1 = 0.f;
@@ -316,7 +309,14 @@ static __device__ __noinline__ float l2_squared_direct(const float* __restrict__
     return s0 + s1;
 }
 
-// acc = a.b of output row m, columns n .. n + 3 becomes the distances: straight-line arithmetic
+// Distances of A row m to the B rows n .. n+3 from the contraction: d^2 = |a|^2 + |b|^2 - 2 a.b
+// (src/poplar_extensions/distance.cpp:151-185 computes sqrt(sum (a - b)^2); the reference's own
+// comment at src/poplar_kge.cpp:376-396 names this expansion).  The expansion loses the distance
+// when the rows are close: where d^2 comes out below a fifth of |a|^2 + |b|^2 its relative error
+// could pass 5e-6, so it is recomputed there in the direct form from the rows themselves, which
+// also returns the exact zero for identical rows that the gradient rule tests for
+// (l2distance.codelet.cpp:149-158).  Both operands are k-major; `acc` = a.b, an = |a|^2, bn = |b|^2.
+// Here acc = a.b of output row m, columns n .. n + 3, becomes the distances: straight-line arithmetic
 // except for one test per four outputs that sends near-cancelling pairs to the direct form.
 __device__ __forceinline__ void l2_distance_four(const PlaneProblem& pp, int m, int n, float (&acc)[4], float an, const float (&bn)[4],
                                                  bool live = true) {
