@@ -179,3 +179,17 @@ def test_predict_chunk_count_is_the_same_on_every_process():
     holder.settings = settings
     assert poplar_kge.Engine.predict_chunks(holder, np.zeros(0, np.int64)) == 0
     assert poplar_kge.Engine.predict_chunks(holder, np.array([1] * 30)) == 1
+
+
+def test_documented_switches_are_the_ones_the_sources_read():
+    """Every KGE_* environment switch that the engine or the Python twin reads is described in the
+    integration notes, and the notes describe no switch that nothing reads."""
+    documented = set(re.findall(r"`(KGE_[A-Z0-9_]+)", (ROOT / "INTEGRATION.md").read_text()))
+    read = set()
+    for path in (ROOT / "distributed-kge-poplar_b200").rglob("*"):
+        if path.suffix in (".cu", ".cuh", ".hpp", ".cpp", ".py"):
+            text = path.read_text()
+            read |= set(re.findall(r'getenv\("(KGE_[A-Z0-9_]+)"', text))
+            read |= set(re.findall(r'environ(?:\.get)?\(?\[?"(KGE_[A-Z0-9_]+)"', text))
+    assert read, "no switch found: the patterns above no longer match the sources"
+    assert documented == read
