@@ -689,8 +689,8 @@ k_tc_planes(const __grid_constant__ PlanePair gp, const __grid_constant__ PlaneM
         if (clustered) fence_async_shared();  // the copy engine reads what the threads have just written
         const int r_begin = rank * rows_each, r_end = min(kBM, r_begin + rows_each);
         constexpr int kQuads = BN / 4;
-        // a split owns at most 64 rows x BN / 4 quads (32 rows in the training step's instantiations: four splits or more)
-        constexpr int kUnits = ((kLean ? 32 : 64) * kQuads + kPlThreads - 1) / kPlThreads;
+        // a split owns at most 64 rows x BN / 4 quads (22 rows in the training step's instantiations: six splits or more)
+        constexpr int kUnits = ((kLean ? 22 : 64) * kQuads + kPlThreads - 1) / kPlThreads;
         const int n_units = max(0, r_end - r_begin) * kQuads;
         float xv[kUnits][4];
         if (clustered) {
@@ -935,7 +935,7 @@ inline cudaError_t launch_prepared(const PlaneLaunch& l, cudaStream_t stream) {
     if (l.tile_n == 128) {
         // the training step's contractions (fp32 planes, k split over a cluster, one epilogue for the launch)
         const int epilogue = l.gp.p[0].g.epilogue;
-        const bool lean = SIDE != SIDE_NORMS && !l.gp.bf16 && l.splits >= 4 && l.gp.p[1].g.epilogue == epilogue;
+        const bool lean = SIDE != SIDE_NORMS && !l.gp.bf16 && l.splits >= 6 && l.gp.p[1].g.epilogue == epilogue;
         if constexpr (SIDE == SIDE_NONE) {
             if (lean && epilogue == EPI_ADD_TABLE_VALUE) return launch_lean<SIDE_NONE, EPI_ADD_TABLE_VALUE>(l, stream);
             if (lean && epilogue == EPI_DENSE_ADAM) return launch_lean<SIDE_NONE, EPI_DENSE_ADAM>(l, stream);
